@@ -1,0 +1,59 @@
+/*
+ * shv_cuda_b200.h -- entry points of libshield_v_cuda.so that the reference library does not have.
+ *
+ * The reference engine fills its device token slots from frames it encodes itself (store_slots of a request,
+ * engine/include/shv_cuda.h:122,54-59).  This library has no frame encoder, so a caller that keeps per-participant
+ * token rings on the device needs another way in.
+ */
+#ifndef SHV_CUDA_B200_H
+#define SHV_CUDA_B200_H
+
+#include "shv_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+/* Copies n host token blocks (n x 6144 fp32, frame embeddings before positions) into device token slots
+ * slots[0..n) (each in [0, token_slots), no duplicates within max_host_tokens consecutive entries).  Goes through the
+ * job queue, so it is ordered against windows exactly like a store_slots request of the reference: windows submitted
+ * earlier see the old contents, windows submitted later the new ones.  Blocks; 0 on success, -1 on error. */
+int shv_cuda_b200_upload_tokens(shv_cuda_model* m, const float* tokens, size_t n, const int32_t* slots);
+
+/* Number of kernels one GPU batch launches (for launch accounting in benchmarks). */
+int shv_cuda_b200_launches_per_batch(const shv_cuda_model* m);
+
+/* ---------------------------------------------------------------- engine core for harnesses
+ * The reference's internal C++ engine API (engine/cuda/engine.hpp:20-62: make_engine, Engine::slot, Engine::classify,
+ * set_dump_dir), which its kernel benchmark and dump tools compile against (bench/gpu_kbench.cu:55-103,
+ * bench/gpu_dump.cu:16-36), as plain C so that a harness in any language can time classify on tokens that already
+ * live in device memory, on a stream it owns.  No worker thread, no staging; NOT thread-safe (one driver thread).
+ * max_windows may exceed the 4096 cap of the job API.  Every int function returns 0 or -1 (+ shv_cuda_last_error). */
+typedef struct shvb_engine shvb_engine;
+shvb_engine* shvb_engine_create(const char* weights, const char* mode, int device, int max_windows, int use_graphs);
+void shvb_engine_destroy(shvb_engine* e);
+/* Points window w, frame f of `slot` (0 or 1) at d_tokens + (w*20 + f)*6144: B windows of device-resident tokens
+ * [B][20][16][384] fp32.  The table upload is enqueued on `stream`. */
+int shvb_engine_bind_tokens(shvb_engine* e, int slot, const float* d_tokens, int B, void* stream);
+/* Enqueues the whole sequence stack for B windows on `stream`; logits land in shvb_engine_logits(e, slot)[0..B). */
+int shvb_engine_classify(shvb_engine* e, int slot, int B, void* stream);
+float* shvb_engine_logits(shvb_engine* e, int slot);                 /* device pointer, [max_windows] */
+/* Waits for `stream`, then copies the first n logits of `slot` to host memory. */
+int shvb_engine_read_logits(shvb_engine* e, int slot, float* host, int n, void* stream);
+int shvb_engine_window_bucket(const shvb_engine* e, int B);          /* size class a batch of B is padded to */
+int shvb_engine_launches(const shvb_engine* e);                      /* kernels per classify */
+int shvb_engine_status(const shvb_engine* e);                        /* nonzero: a kernel's bounded wait gave up */
+size_t shvb_engine_bytes(const shvb_engine* e, int which);           /* 0 weights, 1 activations, 2 one slot */
+/* Debug: classify writes raw float32 intermediates of window 0 (<name>.f32) into dir; "" turns it off. */
+int shvb_engine_set_dump_dir(shvb_engine* e, const char* dir);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHV_CUDA_B200_H */

@@ -1,0 +1,93 @@
+/*
+ * shv_seq_kernels.h -- thin C launch layer over the sm_100a sequence kernels of the SHIELD-V engine.
+ *
+ * Host C++ (engine.cpp, api.cpp) reaches the GPU only through these functions; they are also exported from
+ * libshield_v_cuda.so so that a kernel can be driven and checked in isolation.  Plain pointers and sizes only:
+ * every pointer is a device pointer unless stated otherwise, `stream` is a cudaStream_t passed as void*, every
+ * function only enqueues work and returns a cudaError_t value (0 = success).  Storage type codes: 0 = float32,
+ * 1 = bfloat16, 2 = float16.
+ *
+ * Each entry replaces one launcher (or a fused group of launchers) of the reference engine; citations are to the
+ * reference tree.
+ */
+#ifndef SHV_SEQ_KERNELS_H
+#define SHV_SEQ_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+enum { SHVK_F32 = 0, SHVK_BF16 = 1, SHVK_F16 = 2 };
+
+/* h[b*321 + t] = tokens(b, t/16, t%16) + pos[t] (t < 320), readout (t == 320), and in the same pass
+ * xn = rmsnorm(h) * norm_w in storage type xn_dtype.  tok_ptrs: [B*20] device pointers to 16x384 fp32 blocks.
+ * Replaces launch_assemble + the first launch_rmsnorm (engine/cuda/seq.cu:27-69, engine.cu:409,416). */
+int shvk_assemble_norm(const float* const* tok_ptrs, const float* pos, const float* readout, const float* norm_w,
+                       float* h, void* xn, int xn_dtype, int B, void* stream);
+
+/* out[r] = (x[r] * (1/sqrt(mean(x[r]^2) + 1e-6))) * w over rows of 384; x row pitch ldx, out row pitch ldo
+ * (elements).  Replaces launch_rmsnorm<T> (engine/cuda/seq.cu:44-69,356-359). */
+int shvk_rmsnorm(const float* x, long long ldx, const float* w, void* out, int out_dtype, long long ldo, int rows,
+                 void* stream);
+
+/* C = epilogue(A * W^T): A [M,K] row-major (pitch lda), W [N,K] row-major (pitch ldw) = Linear weight layout.
+ * Epilogue, in this order: + bias[n]; SiLU if act == 1; residual C = R + v / r_div (R fp32, may alias C);
+ * swiglu: columns (2j, 2j+1) = (gate, up), writes silu(gate)*up at column j.  Never splits K.
+ * Replaces GemmParams / gemm<T> (engine/cuda/gemm.cuh:16-29,435; gemm.cu:76-109). */
+typedef struct shvk_gemm_args {
+    int M, N, K;
+    const void* A; long long lda;
+    const void* W; long long ldw;
+    void* C; long long ldc; int c_dtype;
+    const float* bias;
+    int act;
+    const float* R; long long ldr; float r_div;
+    int swiglu;
+} shvk_gemm_args;
+/* IEEE fp32 FMA chain on CUDA cores, k in order (exact tier and the fp32-only last-row projections). A, W fp32. */
+int shvk_gemm_f32(const shvk_gemm_args* g, void* stream);
+/* tcgen05 tensor-core GEMM, A and W in ab_dtype (bf16 or fp16), fp32 accumulation in tensor memory, operands
+ * staged by TMA.  Needs K % 64 == 0, 16-byte aligned operands and pitches.  shvk_gemm_tc_plan encodes the two TMA
+ * tensor maps and the tile shape for exactly these operands into a host-side plan that launches reuse. */
+int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* host_plan /* >= 512 bytes, host, 64-byte aligned */);
+int shvk_gemm_tc(const void* host_plan, void* stream);
+/* Same plan, first `rows` <= M rows only (a smaller batch in buffers sized for the planned M). */
+int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream);
+/* Device status word of the tensor-core path: nonzero after a bounded wait inside a kernel gave up. */
+int shvk_gemm_tc_status(int* status_out);
+
+/* Fused GatedDeltaNet core of one mixer over B clips: causal short conv (k=4, bias) + SiLU on q|k|v, L2 norm of q
+ * (then * 0.125) and k, decay = exp(-exp(A_log) * softplus(a + dt_bias)), beta = sigmoid(b), the gated delta rule
+ * from a zero state with the head's 64x128 state held in registers, and the gated RMSNorm
+ * ((o * rstd) * w) * silu(gate).  P: [B*321][2320] fp32 fused projection output; on: [B*321][768] storage type.
+ * Replaces launch_gdn_prep + launch_delta + launch_gated_norm (engine/cuda/seq.cu:72-214,360-371). */
+int shvk_gdn_scan(const float* P, const float* conv_w, const float* conv_b, const float* a_log, const float* dt_bias,
+                  const float* o_norm_w, void* on, int on_dtype, int B, void* stream);
+
+/* SISA attention of the readout row per (clip, head): -softplus(alpha), logsigmoid(forget), theta prefix sums in
+ * double rounded to fp32, pair rotation of B (all rows) and C (row 320), scores, softmax over 321 keys, y = P V.
+ * S: [B*321][1072] fp32; QC: [B][576] fp32; Y: [B][384] fp32.
+ * Replaces launch_sisa_attn (engine/cuda/seq.cu:217-306,372-374). */
+int shvk_sisa_attn(const float* S, const float* QC, const float* lambda_raw, float* Y, int B, void* stream);
+
+/* Final RMSNorm + Linear(384,128) + SiLU + Linear(128,1).  w0t: [384][128] (transposed head.0.weight).
+ * Replaces launch_head (engine/cuda/seq.cu:309-336,375-378). */
+int shvk_head(const float* X, const float* norm_w, const float* w0t, const float* b0, const float* w2, const float* b2,
+              float* logits, int B, void* stream);
+
+/* pool[slots[f]] = tokens[f] (6144 floats) for slots[f] >= 0.  Replaces launch_store_tokens (seq.cu:338-351). */
+int shvk_store_tokens(const float* tokens, const int32_t* slots, float* pool, int F, void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHV_SEQ_KERNELS_H */

@@ -1,0 +1,384 @@
+// Sequence engine core.  Launch order of one classify (B windows, M = 321*B rows), following the reference's
+// run_classify (engine/cuda/engine.cu:406-470) with the memory-bound steps between GEMMs fused:
+//
+//   assemble+norm -> h (fp32), xn
+//   3 mixers (GDN-A once, GDN-B twice with the same weights, delta / sqrt(2)):
+//       in-proj GEMM xn -> P [M,2320] fp32 | fused scan (conv, L2, gates, delta rule, gated norm) P -> on
+//       | o-proj GEMM + residual -> h | norm h -> xn
+//   2 FFNs: up GEMM + SwiGLU -> hid | down GEMM + residual -> h | norm -> xn
+//   SISA: all-row GEMM + bias -> S [M,1072] fp32 (aliases P); readout row: norm, QC GEMM, attention kernel,
+//       W_O + residual, norm, FFN, head -> logits.  Everything on the readout row is fp32 in every mode.
+//
+// Storage policy (engine/cuda/engine.cu:150-164,213-219): h, P/S and the readout-row buffers are fp32 always; xn, on,
+// hid and the all-row weights are the storage type of the mode.  fp32 mode runs the all-row GEMMs on CUDA cores
+// (IEEE fma chain), bf16/fp16 modes on the tcgen05 tensor-core kernel.
+#include "engine.hpp"
+#include "shv_seq_kernels.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <map>
+
+namespace shv {
+
+const char* precision_name(Precision p) {
+    return p == Precision::FP32 ? "fp32" : p == Precision::BF16 ? "bf16" : p == Precision::FP16 ? "fp16" : "?";
+}
+bool parse_precision(const std::string& s, Precision* p) {
+    for (Precision c : {Precision::FP32, Precision::BF16, Precision::FP16})
+        if (s == precision_name(c)) { *p = c; return true; }
+    return false;
+}
+
+namespace {
+
+void cuda_ok(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA error ") + cudaGetErrorString(e) + " in " + what);
+}
+void launch_ok(int code, const char* what) { cuda_ok(cudaError_t(code), what); }
+
+// Size classes a batch is padded to so that one captured graph serves a range of batch sizes: 1..6, then two steps
+// per octave up to 16, four per octave above, capped by the configured maximum (which is always a class).
+std::vector<int> size_classes(int maxv) {
+    std::vector<int> out;
+    for (int v : {1, 2, 3, 4, 5, 6, 8, 10, 12})
+        if (v < maxv) out.push_back(v);
+    for (int base = 16; base < maxv; base *= 2)
+        for (int q = 4; q < 8; ++q) {
+            const int v = base / 4 * q;
+            if (v < maxv) out.push_back(v);
+        }
+    out.push_back(maxv);
+    return out;
+}
+int class_of(const std::vector<int>& classes, int n) {
+    for (int v : classes)
+        if (v >= n) return v;
+    throw std::runtime_error("batch larger than the configured maximum");
+}
+
+// Bump allocator over one device allocation, 256-byte granularity; `reserve` first, `commit` once, then `at`.
+class Arena {
+public:
+    ~Arena() { if (base_) cudaFree(base_); }
+    size_t reserve(size_t bytes) {
+        const size_t off = size_;
+        size_ = (size_ + bytes + 255) & ~size_t(255);
+        return off;
+    }
+    void commit(const char* what) {
+        cuda_ok(cudaMalloc(&base_, size_ ? size_ : 256), what);
+        cuda_ok(cudaMemset(base_, 0, size_ ? size_ : 256), what);
+    }
+    template <typename U> U* at(size_t off) const { return reinterpret_cast<U*>(static_cast<uint8_t*>(base_) + off); }
+    size_t size() const { return size_; }
+
+private:
+    void* base_ = nullptr;
+    size_t size_ = 0;
+};
+
+int dtype_code(Precision p) { return p == Precision::FP32 ? SHVK_F32 : p == Precision::BF16 ? SHVK_BF16 : SHVK_F16; }
+size_t dtype_bytes(Precision p) { return p == Precision::FP32 ? 4 : 2; }
+
+std::vector<uint8_t> to_storage(const std::vector<float>& v, Precision p) {
+    std::vector<uint8_t> out(v.size() * dtype_bytes(p));
+    if (p == Precision::FP32) {
+        std::memcpy(out.data(), v.data(), out.size());
+    } else if (p == Precision::BF16) {
+        __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(out.data());
+        for (size_t i = 0; i < v.size(); ++i) d[i] = __float2bfloat16_rn(v[i]);
+    } else {
+        __half* d = reinterpret_cast<__half*>(out.data());
+        for (size_t i = 0; i < v.size(); ++i) d[i] = __float2half_rn(v[i]);
+    }
+    return out;
+}
+
+struct GdnDev {
+    const float *norm_w, *ffn_norm_w, *conv_w, *conv_b, *a_log, *dt_bias, *o_norm_w;
+    const void *in_w, *o_proj, *ffn_up, *ffn_down;   // storage type
+};
+
+// One all-row GEMM of the launch sequence: its argument block for the planned maximum row count and, in the 16-bit
+// modes, the tensor-core plan (TMA maps) made once for these buffers.
+struct Site {
+    shvk_gemm_args args{};
+    alignas(64) unsigned char plan[512];
+    bool planned = false;
+};
+
+class SeqEngine final : public Engine {
+public:
+    SeqEngine(const HostModel& hm, Precision p, const EngineConfig& cfg) {
+        prec_ = p;
+        cfg_ = cfg;
+        if (cfg_.max_frames < 1 || cfg_.max_windows < 1 || cfg_.slots < 1 || cfg_.slots > 4)
+            throw std::runtime_error("invalid engine configuration");
+        if ((long long)cfg_.max_windows * NTOK > 0x7fffffffLL / 4) throw std::runtime_error("max_windows too large");
+        fbuckets_ = size_classes(cfg_.max_frames);
+        wbuckets_ = size_classes(cfg_.max_windows);
+        dt_ = dtype_code(p);
+        upload(hm);
+        allocate();
+        plan_sites();
+    }
+    ~SeqEngine() override {
+        for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second);
+    }
+
+    void encode(int, int F, cudaStream_t) override {
+        if (F <= 0) return;
+        throw std::runtime_error("encode: this engine holds the sequence stages only (no frame encoder); pass tokens");
+    }
+
+    void classify(int slot, int B, cudaStream_t s) override {
+        if (B <= 0) return;
+        if (slot < 0 || slot >= cfg_.slots) throw std::runtime_error("classify: bad slot");
+        if (B > cfg_.max_windows) throw std::runtime_error("classify: too many windows");
+        if (!cfg_.use_graphs || !dump_dir_.empty()) { run(slot, B, s); return; }
+        const int n = class_of(wbuckets_, B);
+        const long long key = ((long long)slot << 32) | (long long)n;
+        auto it = graphs_.find(key);
+        if (it == graphs_.end()) {
+            cudaGraph_t g = nullptr;
+            cuda_ok(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal), "graph capture");
+            try {
+                run(slot, n, s);
+            } catch (...) {
+                cudaStreamEndCapture(s, &g);
+                if (g) cudaGraphDestroy(g);
+                throw;
+            }
+            cuda_ok(cudaStreamEndCapture(s, &g), "graph capture");
+            cudaGraphExec_t ex = nullptr;
+            const cudaError_t e = cudaGraphInstantiate(&ex, g, 0);
+            cudaGraphDestroy(g);
+            cuda_ok(e, "graph instantiate");
+            it = graphs_.emplace(key, ex).first;
+        }
+        cuda_ok(cudaGraphLaunch(it->second, s), "graph launch");
+    }
+
+    int device_status() const override {
+        if (prec_ == Precision::FP32) return 0;
+        int st = 0;
+        return shvk_gemm_tc_status(&st) == 0 ? st : -1;
+    }
+    int launches_per_classify() const override { return 28; }
+
+private:
+    int dt_ = SHVK_F32;
+    Arena wts_, acts_;
+    std::vector<std::unique_ptr<Arena>> slot_mem_;
+    const float *pos_ = nullptr, *readout_ = nullptr;
+    GdnDev gdn_[2]{};
+    const float *s_attn_norm_ = nullptr, *s_b_all_ = nullptr, *s_w_qc_ = nullptr, *s_w_o_ = nullptr, *s_lambda_ = nullptr;
+    const float *s_ffn_norm_ = nullptr, *s_ffn_up_ = nullptr, *s_ffn_down_ = nullptr;
+    const void* s_w_all_ = nullptr;
+    const float *fn_w_ = nullptr, *h_w0t_ = nullptr, *h_b0_ = nullptr, *h_w2_ = nullptr, *h_b2_ = nullptr;
+    // activations
+    float *h_ = nullptr, *P_ = nullptr;
+    void *xn_ = nullptr, *on_ = nullptr, *hid_ = nullptr;
+    float *xl_ = nullptr, *qc_ = nullptr, *y_ = nullptr, *x1_ = nullptr, *x2_ = nullptr, *hidl_ = nullptr;
+    Site in_[2], oproj_[2], up_[2], down_[2], sisa_in_;
+    std::map<long long, cudaGraphExec_t> graphs_;
+
+    // ---------------------------------------------------------------- weights
+    void upload(const HostModel& hm) {
+        std::vector<uint8_t> host;
+        struct Fix { const void** dst; size_t off; };
+        std::vector<Fix> fixes;
+        auto put = [&](const void** dst, const void* src, size_t bytes) {
+            const size_t off = wts_.reserve(bytes);
+            host.resize(wts_.size());
+            std::memcpy(host.data() + off, src, bytes);
+            fixes.push_back({dst, off});
+        };
+        auto f32 = [&](const float** dst, const std::vector<float>& v) {
+            put(reinterpret_cast<const void**>(dst), v.data(), v.size() * 4);
+        };
+        auto stor = [&](const void** dst, const std::vector<float>& v) {
+            const std::vector<uint8_t> b = to_storage(v, prec_);
+            put(dst, b.data(), b.size());
+        };
+        f32(&pos_, hm.pos);
+        f32(&readout_, hm.readout);
+        const GdnHost* gh[2] = {&hm.gdn_a, &hm.gdn_b};
+        for (int i = 0; i < 2; ++i) {
+            GdnDev& g = gdn_[i];
+            f32(&g.norm_w, gh[i]->norm_w); f32(&g.ffn_norm_w, gh[i]->ffn_norm_w);
+            f32(&g.conv_w, gh[i]->conv_w); f32(&g.conv_b, gh[i]->conv_b);
+            f32(&g.a_log, gh[i]->a_log); f32(&g.dt_bias, gh[i]->dt_bias); f32(&g.o_norm_w, gh[i]->o_norm_w);
+            stor(&g.in_w, gh[i]->in_w); stor(&g.o_proj, gh[i]->o_proj);
+            stor(&g.ffn_up, gh[i]->ffn_up); stor(&g.ffn_down, gh[i]->ffn_down);
+        }
+        const SisaHost& sh = hm.sisa;
+        f32(&s_attn_norm_, sh.attn_norm_w);
+        stor(&s_w_all_, sh.w_all);
+        f32(&s_b_all_, sh.b_all); f32(&s_w_qc_, sh.w_qc); f32(&s_w_o_, sh.w_o); f32(&s_lambda_, sh.lambda_raw);
+        f32(&s_ffn_norm_, sh.ffn_norm_w); f32(&s_ffn_up_, sh.ffn_up); f32(&s_ffn_down_, sh.ffn_down);
+        f32(&fn_w_, hm.final_norm_w);
+        std::vector<float> w0t(size_t(D) * 128);            // [D][128]: the head kernel reads consecutive outputs
+        for (int o = 0; o < 128; ++o)
+            for (int k = 0; k < D; ++k) w0t[size_t(k) * 128 + o] = hm.head_w0[size_t(o) * D + k];
+        f32(&h_w0t_, w0t); f32(&h_b0_, hm.head_b0); f32(&h_w2_, hm.head_w2); f32(&h_b2_, hm.head_b2);
+        wts_.commit("weight upload");
+        cuda_ok(cudaMemcpy(wts_.at<void>(0), host.data(), host.size(), cudaMemcpyHostToDevice), "weight upload");
+        for (const Fix& f : fixes) *f.dst = wts_.at<uint8_t>(f.off);
+        weight_bytes_ = wts_.size();
+    }
+
+    // ---------------------------------------------------------------- buffers
+    void allocate() {
+        const size_t Bm = size_t(cfg_.max_windows), Mm = Bm * NTOK, Fm = size_t(cfg_.max_frames), ts = dtype_bytes(prec_);
+        const size_t o_h = acts_.reserve(Mm * D * 4), o_p = acts_.reserve(Mm * GLD * 4), o_xn = acts_.reserve(Mm * D * ts);
+        const size_t o_on = acts_.reserve(Mm * VD * ts), o_hid = acts_.reserve(Mm * DFF * ts);
+        const size_t o_xl = acts_.reserve(Bm * D * 4), o_qc = acts_.reserve(Bm * SQN * 4), o_y = acts_.reserve(Bm * D * 4);
+        const size_t o_x1 = acts_.reserve(Bm * D * 4), o_x2 = acts_.reserve(Bm * D * 4), o_hl = acts_.reserve(Bm * DFF * 4);
+        acts_.commit("activation arena");
+        h_ = acts_.at<float>(o_h); P_ = acts_.at<float>(o_p);
+        xn_ = acts_.at<void>(o_xn); on_ = acts_.at<void>(o_on); hid_ = acts_.at<void>(o_hid);
+        xl_ = acts_.at<float>(o_xl); qc_ = acts_.at<float>(o_qc); y_ = acts_.at<float>(o_y);
+        x1_ = acts_.at<float>(o_x1); x2_ = acts_.at<float>(o_x2); hidl_ = acts_.at<float>(o_hl);
+        act_bytes_ = acts_.size();
+
+        slots_.resize(size_t(cfg_.slots));
+        for (int i = 0; i < cfg_.slots; ++i) {
+            slot_mem_.emplace_back(new Arena());
+            Arena& a = *slot_mem_.back();
+            const size_t o_tok = a.reserve(Fm * 16 * D * 4), o_stage = a.reserve(Bm * FRAMES * 16 * D * 4);
+            const size_t o_ptr = a.reserve(Bm * FRAMES * sizeof(float*)), o_log = a.reserve(Bm * 4);
+            a.commit("slot buffers");
+            Slot& sl = slots_[size_t(i)];
+            sl.d_tokens = a.at<float>(o_tok);
+            sl.d_tok_stage = a.at<float>(o_stage);
+            sl.d_tokptr = a.at<const float*>(o_ptr);
+            sl.d_logits = a.at<float>(o_log);
+            // every table entry starts as a valid pointer: padding windows of a bucket dereference it
+            std::vector<const float*> init(Bm * FRAMES, sl.d_tokens);
+            cuda_ok(cudaMemcpy(sl.d_tokptr, init.data(), init.size() * sizeof(float*), cudaMemcpyHostToDevice), "slot init");
+            slot_bytes_ = a.size();
+        }
+    }
+
+    void make_site(Site& st, int N, int K, const void* A, const void* W, void* C, long long ldc, int c_dtype) {
+        shvk_gemm_args& a = st.args;
+        a.M = cfg_.max_windows * NTOK; a.N = N; a.K = K;
+        a.A = A; a.lda = K; a.W = W; a.ldw = K;
+        a.C = C; a.ldc = ldc; a.c_dtype = c_dtype;
+        a.r_div = 1.0f;
+    }
+    void plan_sites() {
+        const float inv_div[2] = {1.0f, float(std::sqrt(2.0))};
+        for (int i = 0; i < 2; ++i) {
+            const GdnDev& g = gdn_[i];
+            make_site(in_[i], GN, D, xn_, g.in_w, P_, GLD, SHVK_F32);
+            make_site(oproj_[i], D, VD, on_, g.o_proj, h_, D, SHVK_F32);
+            oproj_[i].args.R = h_; oproj_[i].args.ldr = D; oproj_[i].args.r_div = inv_div[i];
+            make_site(up_[i], 2 * DFF, D, xn_, g.ffn_up, hid_, DFF, dt_);
+            up_[i].args.swiglu = 1;
+            make_site(down_[i], D, DFF, hid_, g.ffn_down, h_, D, SHVK_F32);
+            down_[i].args.R = h_; down_[i].args.ldr = D;
+        }
+        make_site(sisa_in_, SN, D, xn_, s_w_all_, P_, SLD, SHVK_F32);
+        sisa_in_.args.bias = s_b_all_;
+        if (prec_ == Precision::FP32) return;
+        for (Site* st : {&in_[0], &in_[1], &oproj_[0], &oproj_[1], &up_[0], &up_[1], &down_[0], &down_[1], &sisa_in_}) {
+            launch_ok(shvk_gemm_tc_plan(&st->args, dt_, st->plan), "tensor-core GEMM plan");
+            st->planned = true;
+        }
+    }
+    void rows_gemm(const Site& st, int rows, cudaStream_t s) {
+        if (st.planned) {
+            launch_ok(shvk_gemm_tc_rows(st.plan, rows, s), "tensor-core GEMM");
+        } else {
+            shvk_gemm_args a = st.args;
+            a.M = rows;
+            launch_ok(shvk_gemm_f32(&a, s), "fp32 GEMM");
+        }
+    }
+    // fp32 GEMM on the B readout rows
+    void last_gemm(int B, int N, int K, const float* A, const float* W, float* C, const float* R, long long ldr, int swiglu,
+                   cudaStream_t s) {
+        shvk_gemm_args a{};
+        a.M = B; a.N = N; a.K = K; a.A = A; a.lda = K; a.W = W; a.ldw = K;
+        a.C = C; a.ldc = swiglu ? N / 2 : N; a.c_dtype = SHVK_F32;
+        a.R = R; a.ldr = ldr; a.r_div = 1.0f; a.swiglu = swiglu;
+        launch_ok(shvk_gemm_f32(&a, s), "readout-row GEMM");
+    }
+
+    // ---------------------------------------------------------------- debug dumps
+    void dump(const char* name, const void* dev, size_t n, int dtype, cudaStream_t s) {
+        if (dump_dir_.empty()) return;
+        cuda_ok(cudaStreamSynchronize(s), "dump");
+        std::vector<float> f(n);
+        if (dtype == SHVK_F32) {
+            cuda_ok(cudaMemcpy(f.data(), dev, n * 4, cudaMemcpyDeviceToHost), "dump");
+        } else {
+            std::vector<uint16_t> raw(n);
+            cuda_ok(cudaMemcpy(raw.data(), dev, n * 2, cudaMemcpyDeviceToHost), "dump");
+            for (size_t i = 0; i < n; ++i)
+                f[i] = dtype == SHVK_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(raw.data())[i])
+                                          : __half2float(reinterpret_cast<const __half*>(raw.data())[i]);
+        }
+        std::ofstream o(dump_dir_ + "/" + name + ".f32", std::ios::binary);
+        o.write(reinterpret_cast<const char*>(f.data()), std::streamsize(n * 4));
+    }
+
+    // ---------------------------------------------------------------- the launch sequence
+    void run(int slot, int B, cudaStream_t s) {
+        const Slot& sl = slots_[size_t(slot)];
+        const int M = B * NTOK;
+        launch_ok(shvk_assemble_norm(sl.d_tokptr, pos_, readout_, gdn_[0].norm_w, h_, xn_, dt_, B, s), "assemble");
+        dump("h0", h_, size_t(NTOK) * D, SHVK_F32, s);
+        for (int st = 0; st < 2; ++st) {
+            const GdnDev& g = gdn_[st];
+            const int reps = st == 0 ? 1 : 2;
+            for (int r = 0; r < reps; ++r) {
+                rows_gemm(in_[st], M, s);
+                launch_ok(shvk_gdn_scan(P_, g.conv_w, g.conv_b, g.a_log, g.dt_bias, g.o_norm_w, on_, dt_, B, s), "gdn scan");
+                if (st == 0) dump("gdn_a.o_gated", on_, size_t(NTOK) * VD, dt_, s);
+                rows_gemm(oproj_[st], M, s);
+                const float* next_norm = r + 1 < reps ? g.norm_w : g.ffn_norm_w;
+                launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_, dt_, D, M, s), "rmsnorm");
+            }
+            rows_gemm(up_[st], M, s);
+            rows_gemm(down_[st], M, s);
+            dump(st == 0 ? "after_gdn_a" : "after_gdn_b", h_, size_t(NTOK) * D, SHVK_F32, s);
+            const float* next_norm = st == 0 ? gdn_[1].norm_w : s_attn_norm_;
+            launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_, dt_, D, M, s), "rmsnorm");
+        }
+        float* S = P_;
+        rows_gemm(sisa_in_, M, s);
+        const float* h_last = h_ + size_t(NTOK - 1) * D;
+        const long long ld_last = (long long)NTOK * D;
+        launch_ok(shvk_rmsnorm(h_last, ld_last, s_attn_norm_, xl_, SHVK_F32, D, B, s), "rmsnorm (readout)");
+        last_gemm(B, SQN, D, xl_, s_w_qc_, qc_, nullptr, 0, 0, s);
+        launch_ok(shvk_sisa_attn(S, qc_, s_lambda_, y_, B, s), "sisa attention");
+        dump("sisa.y", y_, size_t(D), SHVK_F32, s);
+        last_gemm(B, D, D, y_, s_w_o_, x1_, h_last, ld_last, 0, s);
+        launch_ok(shvk_rmsnorm(x1_, D, s_ffn_norm_, xl_, SHVK_F32, D, B, s), "rmsnorm (readout ffn)");
+        last_gemm(B, 2 * DFF, D, xl_, s_ffn_up_, hidl_, nullptr, 0, 1, s);
+        last_gemm(B, D, DFF, hidl_, s_ffn_down_, x2_, x1_, D, 0, s);
+        dump("after_sisa_row", x2_, size_t(D), SHVK_F32, s);
+        launch_ok(shvk_head(x2_, fn_w_, h_w0t_, h_b0_, h_w2_, h_b2_, sl.d_logits, B, s), "head");
+        dump("logit", sl.d_logits, 1, SHVK_F32, s);
+    }
+};
+
+}  // namespace
+
+int Engine::frame_bucket(int F) const { return cfg_.use_graphs ? class_of(fbuckets_, F) : F; }
+int Engine::window_bucket(int B) const { return cfg_.use_graphs ? class_of(wbuckets_, B) : B; }
+
+std::unique_ptr<Engine> make_engine(const HostModel& hm, Precision p, const EngineConfig& cfg) {
+    return std::unique_ptr<Engine>(new SeqEngine(hm, p, cfg));
+}
+
+}  // namespace shv

@@ -1,0 +1,106 @@
+// Plain-C face of the engine core (include/shv_cuda_b200.h, shvb_engine_*): what the reference's kernel benchmark
+// does in C++ against engine.hpp (bench/gpu_kbench.cu:55-103), callable from any language.
+#include "shv_cuda_b200.h"
+#include "engine.hpp"
+
+#include <cstring>
+
+// defined in api.cpp: the thread-local error string behind shv_cuda_last_error
+void shv_cuda_set_error(const std::string& s);
+
+struct shvb_engine {
+    std::unique_ptr<shv::Engine> eng;
+    int device = 0;
+    std::vector<const float*> table;
+};
+
+namespace {
+template <class F> int guard(F&& f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::exception& e) {
+        shv_cuda_set_error(e.what());
+        return -1;
+    }
+}
+void cuda_ok(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA error ") + cudaGetErrorString(e) + " in " + what);
+}
+}  // namespace
+
+extern "C" {
+
+shvb_engine* shvb_engine_create(const char* weights, const char* mode, int device, int max_windows, int use_graphs) {
+    shvb_engine* out = nullptr;
+    guard([&] {
+        if (!weights) throw std::runtime_error("null weights path");
+        shv::Precision p;
+        if (!shv::parse_precision(mode ? mode : "fp32", &p)) throw std::runtime_error("unknown mode (fp32, bf16, fp16)");
+        cuda_ok(cudaSetDevice(device), "cudaSetDevice");
+        const shv::HostModel hm = shv::load_host_model(weights);
+        shv::check_sidecar_sha(weights, hm.sha256);
+        shv::EngineConfig cfg;
+        cfg.max_frames = 1;
+        cfg.max_windows = max_windows;
+        cfg.use_graphs = use_graphs != 0;
+        cfg.slots = 2;
+        auto e = std::unique_ptr<shvb_engine>(new shvb_engine());
+        e->eng = shv::make_engine(hm, p, cfg);
+        e->device = device;
+        out = e.release();
+    });
+    return out;
+}
+
+void shvb_engine_destroy(shvb_engine* e) { delete e; }
+
+int shvb_engine_bind_tokens(shvb_engine* e, int slot, const float* d_tokens, int B, void* stream) {
+    return guard([&] {
+        if (!e || !d_tokens || slot < 0 || slot >= e->eng->slots() || B < 1 || B > e->eng->max_windows())
+            throw std::runtime_error("bind_tokens: bad argument");
+        e->table.resize(size_t(B) * 20);
+        for (size_t i = 0; i < e->table.size(); ++i) e->table[i] = d_tokens + i * SHV_CUDA_TOKEN_FLOATS;
+        cuda_ok(cudaMemcpyAsync(e->eng->slot(slot).d_tokptr, e->table.data(), e->table.size() * sizeof(float*),
+                                cudaMemcpyHostToDevice, cudaStream_t(stream)), "pointer table upload");
+        cuda_ok(cudaStreamSynchronize(cudaStream_t(stream)), "pointer table upload");   // the host table is reused
+    });
+}
+
+int shvb_engine_classify(shvb_engine* e, int slot, int B, void* stream) {
+    return guard([&] {
+        if (!e) throw std::runtime_error("null engine");
+        e->eng->classify(slot, B, cudaStream_t(stream));
+    });
+}
+
+float* shvb_engine_logits(shvb_engine* e, int slot) {
+    return e && slot >= 0 && slot < e->eng->slots() ? e->eng->slot(slot).d_logits : nullptr;
+}
+int shvb_engine_read_logits(shvb_engine* e, int slot, float* host, int n, void* stream) {
+    return guard([&] {
+        if (!e || !host || slot < 0 || slot >= e->eng->slots() || n < 0 || n > e->eng->max_windows())
+            throw std::runtime_error("read_logits: bad argument");
+        cuda_ok(cudaStreamSynchronize(cudaStream_t(stream)), "read_logits");
+        cuda_ok(cudaMemcpy(host, e->eng->slot(slot).d_logits, size_t(n) * 4, cudaMemcpyDeviceToHost), "read_logits");
+    });
+}
+int shvb_engine_window_bucket(const shvb_engine* e, int B) {
+    int out = -1;
+    guard([&] { out = e ? e->eng->window_bucket(B) : -1; });
+    return out;
+}
+int shvb_engine_launches(const shvb_engine* e) { return e ? e->eng->launches_per_classify() : 0; }
+int shvb_engine_status(const shvb_engine* e) { return e ? e->eng->device_status() : -1; }
+size_t shvb_engine_bytes(const shvb_engine* e, int which) {
+    if (!e) return 0;
+    return which == 0 ? e->eng->weight_bytes() : which == 1 ? e->eng->activation_bytes() : e->eng->slot_bytes();
+}
+int shvb_engine_set_dump_dir(shvb_engine* e, const char* dir) {
+    return guard([&] {
+        if (!e) throw std::runtime_error("null engine");
+        e->eng->set_dump_dir(dir ? dir : "");
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,107 @@
+// Row-wise kernels of the residual stream: token assembly fused with the first RMSNorm, RMSNorm, token-slot store.
+// One warp owns one row of 384 floats (three float4 per lane), so every access is a 512-byte coalesced segment
+// and the mean of squares is a single shuffle reduction.
+#include "device_utils.cuh"
+#include "shv_seq_kernels.h"
+
+namespace sb {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+template <typename T>
+__device__ __forceinline__ void norm_store(const float4 (&v)[3], const float* __restrict__ w, T* __restrict__ out, int lane) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / float(kD) + 1e-6f);
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        const int c = i * 128 + lane * 4;
+        const float4 g = *reinterpret_cast<const float4*>(w + c);
+        store_quad<T>(out + c, (v[i].x * r) * g.x, (v[i].y * r) * g.y, (v[i].z * r) * g.z, (v[i].w * r) * g.w);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+assemble_norm_kernel(const float* const* __restrict__ tok_ptrs, const float* __restrict__ pos,
+                     const float* __restrict__ readout, const float* __restrict__ norm_w, float* __restrict__ h,
+                     T* __restrict__ xn, long long rows) {
+    const long long row = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const long long clip = row / kTok;
+    const int t = int(row - clip * kTok);
+    float4 v[3];
+    if (t == kTok - 1) {
+#pragma unroll
+        for (int i = 0; i < 3; ++i) v[i] = *reinterpret_cast<const float4*>(readout + i * 128 + lane * 4);
+    } else {
+        const float* tok = tok_ptrs[clip * kFrames + (t >> 4)] + (t & 15) * kD;
+        const float* pe = pos + (long long)t * kD;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const float4 a = *reinterpret_cast<const float4*>(tok + i * 128 + lane * 4);
+            const float4 p = *reinterpret_cast<const float4*>(pe + i * 128 + lane * 4);
+            v[i] = make_float4(a.x + p.x, a.y + p.y, a.z + p.z, a.w + p.w);
+        }
+    }
+    float* hr = h + row * kD;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) *reinterpret_cast<float4*>(hr + i * 128 + lane * 4) = v[i];
+    norm_store<T>(v, norm_w, xn + row * kD, lane);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w, T* __restrict__ out,
+               long long ldo, long long rows) {
+    const long long row = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* xr = x + row * ldx;
+    float4 v[3];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) v[i] = *reinterpret_cast<const float4*>(xr + i * 128 + lane * 4);
+    norm_store<T>(v, w, out + row * ldo, lane);
+}
+
+__global__ void __launch_bounds__(256)
+store_tokens_kernel(const float* __restrict__ src, const int32_t* __restrict__ slots, float* __restrict__ pool) {
+    const int f = blockIdx.x;
+    const int s = slots[f];
+    if (s < 0) return;
+    const float4* from = reinterpret_cast<const float4*>(src + (long long)f * 16 * kD);
+    float4* to = reinterpret_cast<float4*>(pool + (long long)s * 16 * kD);
+    for (int i = threadIdx.x; i < 16 * kD / 4; i += 256) to[i] = from[i];
+}
+
+}  // namespace
+}  // namespace sb
+
+extern "C" int shvk_assemble_norm(const float* const* tok_ptrs, const float* pos, const float* readout,
+                                  const float* norm_w, float* h, void* xn, int xn_dtype, int B, void* stream) {
+    if (B <= 0) return 0;
+    const long long rows = (long long)B * sb::kTok;
+    const unsigned grid = unsigned((rows + sb::kWarpsPerBlock - 1) / sb::kWarpsPerBlock);
+    SB_DISPATCH_DTYPE(xn_dtype, T, (sb::assemble_norm_kernel<T><<<grid, sb::kWarpsPerBlock * 32, 0, cudaStream_t(stream)>>>(
+                                       tok_ptrs, pos, readout, norm_w, h, static_cast<T*>(xn), rows)));
+    return int(cudaGetLastError());
+}
+
+extern "C" int shvk_rmsnorm(const float* x, long long ldx, const float* w, void* out, int out_dtype, long long ldo,
+                            int rows, void* stream) {
+    if (rows <= 0) return 0;
+    const unsigned grid = unsigned((rows + sb::kWarpsPerBlock - 1) / sb::kWarpsPerBlock);
+    SB_DISPATCH_DTYPE(out_dtype, T, (sb::rmsnorm_kernel<T><<<grid, sb::kWarpsPerBlock * 32, 0, cudaStream_t(stream)>>>(
+                                        x, ldx, w, static_cast<T*>(out), ldo, rows)));
+    return int(cudaGetLastError());
+}
+
+extern "C" int shvk_store_tokens(const float* tokens, const int32_t* slots, float* pool, int F, void* stream) {
+    if (F <= 0) return 0;
+    sb::store_tokens_kernel<<<F, 256, 0, cudaStream_t(stream)>>>(tokens, slots, pool);
+    return int(cudaGetLastError());
+}

@@ -1,0 +1,181 @@
+// SISA attention for the readout row (token 320), one CTA per (clip, head).
+//
+// Only row 320 leaves the SISA block, so Q and C exist for that row alone while K, V, B, theta, alpha and forget
+// cover all 321 rows (engine/cuda/engine.cu:445-453; engine/model/isa_impl.hpp:996-1069).  Phases:
+//   1  per-token terms -softplus(alpha), logsigmoid(forget), theta[16] -> shared memory (fp32)
+//   2  18 inclusive prefix sums over the 321 tokens, accumulated in double and rounded to fp32 per element (the
+//      cumsum semantics both reference engines keep, seq.cu:249-258).  A warp scans one column: each lane sums 11
+//      consecutive tokens, a shuffle scan combines the lane totals, all in double.
+//   3  rotate C (row 320) by phi[320]; per token rotate B by phi[t], score = q.k/8 + softplus(lambda) *
+//      exp(g_last - g_t) * (c_rot . b_rot) + (f_last - f_t); thread per token, rows read as float4
+//   4  softmax over the 321 scores, y = sum_t p_t v_t with 4 token groups x 64 columns
+#include "device_utils.cuh"
+#include "shv_seq_kernels.h"
+
+namespace sb {
+namespace {
+
+constexpr int NT = 256, NCOL = 18, PER_LANE = 11;   // 32 * 11 = 352 >= 321
+
+__global__ void __launch_bounds__(NT)
+sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, const float* __restrict__ lambda_raw,
+                 float* __restrict__ Y) {
+    const int clip = blockIdx.x / kHeads, head = blockIdx.x % kHeads;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* S0 = S + (long long)clip * kTok * kSLD;
+    __shared__ float term[NCOL][kTok + 3];     // column-major: a scan walks one row of this array
+    __shared__ float score[kTok];
+    __shared__ __align__(16) float sq[kDK];
+    __shared__ __align__(16) float sc[kState];
+    __shared__ float red[NT / 32];
+    __shared__ float ypart[4][kDK];
+
+    for (int i = tid; i < kTok * NCOL; i += NT) {
+        const int t = i / NCOL, c = i - t * NCOL;
+        const int col = c == 0 ? kSAlpha + head : c == 1 ? kSForget + head : kSTheta + head * kPairs + (c - 2);
+        const float x = S0[(long long)t * kSLD + col];
+        term[c][t] = c == 0 ? -softplus_f(x) : c == 1 ? logsigmoid_f(x) : x;
+    }
+    if (tid < kDK) sq[tid] = QC[(long long)clip * kSQN + kSQ + head * kDK + tid];
+    else if (tid < kDK + kState) sc[tid - kDK] = QC[(long long)clip * kSQN + kSC + head * kState + (tid - kDK)];
+    __syncthreads();
+
+    for (int c = warp; c < NCOL; c += NT / 32) {
+        const int t0 = lane * PER_LANE;
+        double loc[PER_LANE];
+        double run = 0.0;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int t = t0 + i;
+            run += t < kTok ? double(term[c][t]) : 0.0;
+            loc[i] = run;
+        }
+        double incl = run;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const double base = incl - run;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int t = t0 + i;
+            if (t < kTok) term[c][t] = float(base + loc[i]);
+        }
+    }
+    __syncthreads();
+
+    if (tid < kPairs) {
+        float si, co;
+        sincosf(term[2 + tid][kTok - 1], &si, &co);
+        const float e = sc[2 * tid], o = sc[2 * tid + 1];
+        __syncwarp(0x0000ffffu);
+        sc[2 * tid] = e * co - o * si;
+        sc[2 * tid + 1] = e * si + o * co;
+    }
+    __syncthreads();
+
+    const float lam = softplus_f(lambda_raw[head]);
+    const float g_last = term[0][kTok - 1], f_last = term[1][kTok - 1];
+    float lmax = -INFINITY;
+    for (int t = tid; t < kTok; t += NT) {
+        const float4* kr = reinterpret_cast<const float4*>(S0 + (long long)t * kSLD + kSK + head * kDK);
+        float content = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kDK / 4; ++j) {
+            const float4 kk = kr[j];
+            const float4 qq = *reinterpret_cast<const float4*>(&sq[j * 4]);
+            content = fmaf(qq.x, kk.x, content); content = fmaf(qq.y, kk.y, content);
+            content = fmaf(qq.z, kk.z, content); content = fmaf(qq.w, kk.w, content);
+        }
+        content *= 0.125f;
+        const float4* br = reinterpret_cast<const float4*>(S0 + (long long)t * kSLD + kSB + head * kState);
+        float ssm = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kState / 4; ++j) {
+            const float4 bb = br[j];
+            float s0, c0, s1, c1;
+            sincosf(term[2 + 2 * j][t], &s0, &c0);
+            sincosf(term[3 + 2 * j][t], &s1, &c1);
+            ssm = fmaf(sc[4 * j], bb.x * c0 - bb.y * s0, ssm);
+            ssm = fmaf(sc[4 * j + 1], bb.x * s0 + bb.y * c0, ssm);
+            ssm = fmaf(sc[4 * j + 2], bb.z * c1 - bb.w * s1, ssm);
+            ssm = fmaf(sc[4 * j + 3], bb.z * s1 + bb.w * c1, ssm);
+        }
+        float s = content + (lam * expf(g_last - term[0][t])) * ssm;
+        s = s + (f_last - term[1][t]);
+        score[t] = s;
+        lmax = fmaxf(lmax, s);
+    }
+    lmax = warp_max(lmax);
+    if (lane == 0) red[warp] = lmax;
+    __syncthreads();
+    float mx = red[0];
+#pragma unroll
+    for (int i = 1; i < NT / 32; ++i) mx = fmaxf(mx, red[i]);
+    __syncthreads();
+    float lsum = 0.0f;
+    for (int t = tid; t < kTok; t += NT) {
+        const float e = expf(score[t] - mx);
+        score[t] = e;
+        lsum += e;
+    }
+    lsum = warp_sum(lsum);
+    if (lane == 0) red[warp] = lsum;
+    __syncthreads();
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NT / 32; ++i) sum += red[i];
+    const float inv = 1.0f / sum;
+    const int j = tid & (kDK - 1), grp = tid >> 6;
+    float y = 0.0f;
+    for (int t = grp; t < kTok; t += 4) y = fmaf(score[t] * inv, S0[(long long)t * kSLD + kSV + head * kDK + j], y);
+    ypart[grp][j] = y;
+    __syncthreads();
+    if (tid < kDK) Y[(long long)clip * kD + head * kDK + tid] = (ypart[0][tid] + ypart[1][tid]) + (ypart[2][tid] + ypart[3][tid]);
+}
+
+// Final RMSNorm + Linear(384,128) + bias + SiLU + Linear(128,1) + bias; one CTA of 128 threads per clip.
+__global__ void __launch_bounds__(128)
+head_kernel(const float* __restrict__ X, const float* __restrict__ nw, const float* __restrict__ w0t,
+            const float* __restrict__ b0, const float* __restrict__ w2, const float* __restrict__ b2,
+            float* __restrict__ logits) {
+    const int clip = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float z[kD];
+    __shared__ float red[4];
+    const float* x = X + (long long)clip * kD;
+    const float v0 = x[tid], v1 = x[tid + 128], v2 = x[tid + 256];
+    float ss = warp_sum((v0 * v0 + v1 * v1) + v2 * v2);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    const float r = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / float(kD) + 1e-6f);
+    z[tid] = (v0 * r) * nw[tid];
+    z[tid + 128] = (v1 * r) * nw[tid + 128];
+    z[tid + 256] = (v2 * r) * nw[tid + 256];
+    __syncthreads();
+    float acc = 0.0f;
+#pragma unroll 8
+    for (int k = 0; k < kD; ++k) acc = fmaf(w0t[k * 128 + tid], z[k], acc);
+    const float hid = silu_f(acc + b0[tid]);
+    const float dot = warp_sum(w2[tid] * hid);
+    __syncthreads();
+    if (lane == 0) red[warp] = dot;
+    __syncthreads();
+    if (tid == 0) logits[clip] = ((red[0] + red[1]) + (red[2] + red[3])) + b2[0];
+}
+
+}  // namespace
+}  // namespace sb
+
+extern "C" int shvk_sisa_attn(const float* S, const float* QC, const float* lambda_raw, float* Y, int B, void* stream) {
+    if (B <= 0) return 0;
+    sb::sisa_attn_kernel<<<unsigned(B) * sb::kHeads, sb::NT, 0, cudaStream_t(stream)>>>(S, QC, lambda_raw, Y);
+    return int(cudaGetLastError());
+}
+
+extern "C" int shvk_head(const float* X, const float* norm_w, const float* w0t, const float* b0, const float* w2,
+                         const float* b2, float* logits, int B, void* stream) {
+    if (B <= 0) return 0;
+    sb::head_kernel<<<unsigned(B), 128, 0, cudaStream_t(stream)>>>(X, norm_w, w0t, b0, w2, b2, logits);
+    return int(cudaGetLastError());
+}

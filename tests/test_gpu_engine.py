@@ -1,0 +1,154 @@
+"""End-to-end parity of the sequence stack through the C ABI: golden vectors from the reference's PyTorch oracle and CPU
+engine, the numpy oracle on fresh seeds, stage dumps, all three modes, batch invariance."""
+import numpy as np
+import pytest
+
+from oracle import ref_cpu, seq_oracle as O
+from shield_sisa_b200 import binding, weights as W
+from tests.helpers import dev, load_golden, rel_err, stream_ptr, sync
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-4          # absolute, stage outputs and logits, fp32 mode
+LOWP_TOL = 2e-2          # max|err| / max|ref| per tensor, bf16 and fp16 modes
+CASES = ["w3_s1_t2_b3", "w1_s1_t1_b2", "w3_s5_t7_b2"]
+
+
+def golden_inputs(name, weight_files):
+    g = load_golden(name)
+    path, w = weight_files(str(g["recipe"]), int(g["weight_seed"]))
+    return g, path, w, W.synth_tokens(int(g["batch"]), int(g["token_seed"]))
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_fp32_logits_match_golden(case, weight_files):
+    g, path, _, tok = golden_inputs(case, weight_files)
+    with binding.CudaModel(path, "fp32") as m:
+        assert m.mode == "fp32" and m.fingerprint == W.sha256_file(path) and m.threshold == 0.5
+        logits = m.classify(tok)
+    assert np.abs(logits - g["logits_f64"]).max() < FP32_TOL
+    assert np.abs(logits - g["logits_cpu_engine"]).max() < FP32_TOL
+
+
+@pytest.mark.parametrize("case", CASES[:2])
+def test_fp32_stage_dumps_match_golden(case, weight_files, tmp_path):
+    g, path, _, tok = golden_inputs(case, weight_files)
+    import torch
+    eng = binding.EngineCore(path, "fp32", max_windows=4, use_graphs=False)
+    eng.set_dump_dir(tmp_path)
+    T = dev(tok[:1])
+    eng.bind_tokens(0, T.data_ptr(), 1, stream_ptr())
+    eng.classify(0, 1, stream_ptr())
+    sync()
+    rows = g["rows"]
+    for name in ("h0", "after_gdn_a", "after_gdn_b"):
+        got = np.fromfile(tmp_path / f"{name}.f32", dtype="<f4").reshape(321, 384)[rows]
+        assert np.abs(got - g["trace:" + name][0]).max() < FP32_TOL, name
+        assert np.abs(got - g["cpu:" + name]).max() < FP32_TOL, name
+    got = np.fromfile(tmp_path / "after_sisa_row.f32", dtype="<f4")
+    assert np.abs(got - g["after_sisa_last"][0]).max() < FP32_TOL
+    assert np.abs(got - g["cpu:after_sisa_last"]).max() < FP32_TOL
+    og = np.fromfile(tmp_path / "gdn_a.o_gated.f32", dtype="<f4").reshape(321, 6, 128)[rows]
+    ref = g["trace:gdn_a.rep0.o_gated"][0]
+    assert np.abs(og - ref).max() < FP32_TOL * max(1.0, np.abs(ref).max())
+    y = np.fromfile(tmp_path / "sisa.y.f32", dtype="<f4")
+    assert np.abs(y - g["trace:sisa.attn_y"][0, -1].reshape(384)).max() < FP32_TOL
+    logit = np.fromfile(tmp_path / "logit.f32", dtype="<f4")
+    assert abs(float(logit[0]) - float(g["logits_f64"][0])) < FP32_TOL
+    eng.close()
+
+
+@pytest.mark.parametrize("recipe,wseed,tseed,batch", [("W3", 1, 1, 128), ("W3", 7, 9, 37)])
+def test_fp32_matches_oracle_on_fresh_inputs(recipe, wseed, tseed, batch, weight_files):
+    """The B=128 exact-mode configuration (random-init weights seed 1, tokens N(0,1)); the oracle is evaluated in
+    float64 on a subset of windows to keep the CPU side short."""
+    path, w = weight_files(recipe, wseed)
+    tok = W.synth_tokens(batch, tseed)
+    with binding.CudaModel(path, "fp32") as m:
+        logits = m.classify(tok)
+    pick = np.unique(np.linspace(0, batch - 1, 6).astype(int))
+    ref = O.classify_tokens(w, tok[pick], np.float64)
+    assert np.abs(logits[pick] - ref).max() < FP32_TOL
+    if ref_cpu.available():
+        eng = ref_cpu.RefCpuEngine(path, threads=4)
+        cpu = eng.classify(tok)
+        eng.close()
+        assert np.abs(logits - cpu).max() < FP32_TOL
+
+
+@pytest.mark.parametrize("mode", ["bf16", "fp16"])
+@pytest.mark.parametrize("case", CASES)
+def test_16_bit_modes_within_tolerance(mode, case, weight_files, tmp_path):
+    g, path, _, tok = golden_inputs(case, weight_files)
+    with binding.CudaModel(path, mode) as m:
+        logits = m.classify(tok)
+    ref = g["logits_f64"]
+    assert np.isfinite(logits).all()
+    assert np.abs(logits - ref).max() <= LOWP_TOL * max(1.0, np.abs(ref).max()), (logits, ref)
+    if "cpu:after_gdn_a" in g:
+        eng = binding.EngineCore(path, mode, max_windows=2, use_graphs=False)
+        eng.set_dump_dir(tmp_path)
+        T = dev(tok[:1])
+        eng.bind_tokens(0, T.data_ptr(), 1, stream_ptr())
+        eng.classify(0, 1, stream_ptr())
+        sync()
+        assert eng.status() == 0
+        for name in ("after_gdn_a", "after_gdn_b"):
+            got = np.fromfile(tmp_path / f"{name}.f32", dtype="<f4").reshape(321, 384)[g["rows"]]
+            assert rel_err(got, g["trace:" + name][0]) <= LOWP_TOL, name
+        got = np.fromfile(tmp_path / "after_sisa_row.f32", dtype="<f4")
+        assert rel_err(got, g["after_sisa_last"][0]) <= LOWP_TOL
+        eng.close()
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16", "fp16"])
+def test_logit_is_bitwise_independent_of_the_batch(mode, weight_files):
+    """Row independence (reference shv_cuda.h:31-34): alone, in a batch, shuffled, padded to another size class."""
+    path, _ = weight_files("W3", 1)
+    tok = W.synth_tokens(11, 5)
+    with binding.CudaModel(path, mode, max_windows=16, max_host_tokens=320) as m:
+        full = m.classify(tok)
+        alone = np.concatenate([m.classify(tok[i:i + 1]) for i in (0, 4, 10)])
+        perm = np.random.default_rng(0).permutation(11)
+        shuffled = m.classify(tok[perm])
+        seven = m.classify(tok[:7])
+    np.testing.assert_array_equal(alone.view(np.uint32), full[[0, 4, 10]].view(np.uint32))
+    np.testing.assert_array_equal(shuffled.view(np.uint32), full[perm].view(np.uint32))
+    np.testing.assert_array_equal(seven.view(np.uint32), full[:7].view(np.uint32))
+
+
+def test_graphs_and_eager_agree_and_buckets(weight_files):
+    import torch
+    path, _ = weight_files("W3", 1)
+    tok = W.synth_tokens(5, 3)
+    T = dev(tok)
+    outs = []
+    for graphs in (True, False):
+        eng = binding.EngineCore(path, "fp32", max_windows=24, use_graphs=graphs)
+        assert eng.window_bucket(5) == 5
+        assert eng.window_bucket(7) == (8 if graphs else 7)
+        assert eng.window_bucket(21) == (24 if graphs else 21)
+        eng.bind_tokens(1, T.data_ptr(), 5, stream_ptr())
+        for _ in range(2):                                 # second call replays the captured graph
+            eng.classify(1, 5, stream_ptr())
+        sync()
+        host = eng.read_logits(1, 5, stream_ptr())
+        outs.append(host.copy())
+        assert eng.launches() == 28
+        b = eng.bytes()
+        assert b["weights"] > 20e6 and b["activations"] > 0 and b["slot"] > 0
+        eng.close()
+    np.testing.assert_array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+
+
+def test_classify_splits_large_requests(weight_files):
+    """More windows than max_windows / max_host_tokens allow in one batch: the synchronous call splits and the result
+    equals one large batch (limits as engine/cuda/api.cu:682-703)."""
+    path, _ = weight_files("W1", 1)
+    tok = W.synth_tokens(23, 8)
+    with binding.CudaModel(path, "fp32", max_windows=8, max_host_tokens=100) as small, \
+            binding.CudaModel(path, "fp32", max_windows=32, max_host_tokens=640) as big:
+        assert small.limits() == {"max_frames": 640, "max_windows": 8, "max_host_tokens": 100, "token_slots": 0}
+        a = small.classify(tok)          # step = min(8, 100 // 20) = 5 windows per job
+        b = big.classify(tok)
+    np.testing.assert_array_equal(a.view(np.uint32), b.view(np.uint32))

@@ -1,0 +1,326 @@
+"""Each sm_100a kernel driven alone through the C launch layer (include/shv_seq_kernels.h) against the numpy oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import seq_oracle as O
+from shield_sisa_b200 import binding, weights as W
+from tests.helpers import dev, rel_err, stream_ptr, sync
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def L():
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return binding.load_library(True)
+
+
+def ok(rc):
+    assert rc == 0, f"launcher returned cudaError {rc}"
+
+
+def gemm_args(M, N, K, A, Wt, Cm, ldc, c_dtype=0, bias=None, act=0, R=None, ldr=0, r_div=1.0, swiglu=0):
+    g = binding.GemmArgs()
+    g.M, g.N, g.K = M, N, K
+    g.A, g.lda, g.W, g.ldw = A.data_ptr(), K, Wt.data_ptr(), K
+    g.C, g.ldc, g.c_dtype = Cm.data_ptr(), ldc, c_dtype
+    g.bias = bias.data_ptr() if bias is not None else None
+    g.act = act
+    g.R = R.data_ptr() if R is not None else None
+    g.ldr, g.r_div, g.swiglu = ldr, r_div, swiglu
+    return g
+
+
+def silu(x):
+    return x / (1.0 + np.exp(-x))
+
+
+# ---------------------------------------------------------------------------------------------- fp32 GEMM
+@pytest.mark.parametrize("M,N,K", [(1, 576, 384), (3, 384, 384), (321, 2316, 384), (700, 384, 768), (130, 128, 960)])
+def test_gemm_f32_plain(L, M, N, K):
+    import torch
+    rng = np.random.default_rng(M + N)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    ldc = (N + 3) // 4 * 4 + 4
+    A, Wt = dev(a), dev(w)
+    Cm = torch.full((M, ldc), 7.0, device="cuda")
+    ok(L.shvk_gemm_f32(gemm_args(M, N, K, A, Wt, Cm, ldc), stream_ptr()))
+    sync()
+    got = Cm.cpu().numpy()
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(got[:, :N] - ref).max() < 2e-5
+    assert (got[:, N:] == 7.0).all()                       # columns beyond N are never written
+
+
+def test_gemm_f32_epilogues(L):
+    import torch
+    rng = np.random.default_rng(5)
+    M, K = 333, 384
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    # bias + SiLU
+    w = (rng.standard_normal((128, K)) / 20).astype(np.float32)
+    b = rng.standard_normal(128).astype(np.float32)
+    Cm = torch.zeros((M, 128), device="cuda")
+    A, Wt, Bt = dev(a), dev(w), dev(b)
+    ok(L.shvk_gemm_f32(gemm_args(M, 128, K, A, Wt, Cm, 128, bias=Bt, act=1), stream_ptr()))
+    sync()
+    assert np.abs(Cm.cpu().numpy() - silu(a.astype(np.float64) @ w.T + b)).max() < 2e-5
+    # residual in place with divisor
+    w = (rng.standard_normal((384, K)) / 20).astype(np.float32)
+    r = rng.standard_normal((M, 384)).astype(np.float32)
+    H, Wt = dev(r), dev(w)
+    ok(L.shvk_gemm_f32(gemm_args(M, 384, K, A, Wt, H, 384, R=H, ldr=384, r_div=float(np.float32(np.sqrt(2.0)))),
+                       stream_ptr()))
+    sync()
+    assert np.abs(H.cpu().numpy() - (r + (a.astype(np.float64) @ w.T) / np.sqrt(2.0))).max() < 2e-5
+    # SwiGLU: interleaved (gate, up) rows -> silu(gate) * up
+    w = (rng.standard_normal((1920, K)) / 20).astype(np.float32)
+    Cm = torch.zeros((M, 960), device="cuda")
+    Wt = dev(w)
+    ok(L.shvk_gemm_f32(gemm_args(M, 1920, K, A, Wt, Cm, 960, swiglu=1), stream_ptr()))
+    sync()
+    full = a.astype(np.float64) @ w.T
+    assert np.abs(Cm.cpu().numpy() - silu(full[:, 0::2]) * full[:, 1::2]).max() < 2e-5
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch(L):
+    import torch
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal((400, 768)).astype(np.float32)
+    w = rng.standard_normal((384, 768)).astype(np.float32)
+    Wt, A, A1 = dev(w), dev(a), dev(a[257:258])
+    big = torch.zeros((400, 384), device="cuda")
+    ok(L.shvk_gemm_f32(gemm_args(400, 384, 768, A, Wt, big, 384), stream_ptr()))
+    one = torch.zeros((1, 384), device="cuda")
+    ok(L.shvk_gemm_f32(gemm_args(1, 384, 768, A1, Wt, one, 384), stream_ptr()))
+    sync()
+    assert torch.equal(big[257], one[0])                   # bitwise
+
+
+# ---------------------------------------------------------------------------------------------- tensor-core GEMM
+def tc_plan(L, g, dtype_code):
+    buf = (C.c_char * 1024)()
+    addr = (C.addressof(buf) + 63) & ~63
+    ok(L.shvk_gemm_tc_plan(g, dtype_code, addr))
+    return buf, addr
+
+
+def tc_status(L):
+    st = C.c_int(-1)
+    ok(L.shvk_gemm_tc_status(C.byref(st)))
+    return st.value
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (321, 2316, 384), (1000, 384, 768), (642, 1068, 384), (257, 384, 960)])
+def test_gemm_tc_plain(L, dtype, M, N, K):
+    import torch
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    rng = np.random.default_rng(N + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    A, Wt = dev(a, tdt), dev(w, tdt)
+    ldc = (N + 3) // 4 * 4 + 4
+    Cm = torch.full((M, ldc), 7.0, device="cuda")
+    g = gemm_args(M, N, K, A, Wt, Cm, ldc)
+    keep, plan = tc_plan(L, g, binding.DTYPES[dtype])
+    ok(L.shvk_gemm_tc(plan, stream_ptr()))
+    sync()
+    assert tc_status(L) == 0
+    got = Cm.cpu().numpy()
+    ref = A.float().cpu().numpy().astype(np.float64) @ Wt.float().cpu().numpy().astype(np.float64).T
+    assert np.abs(got[:, :N] - ref).max() < 1e-4           # operands are exact in 16 bits; only fp32 accumulation differs
+    assert (got[:, N:] == 7.0).all()
+
+
+def test_gemm_tc_epilogues_and_partial_rows(L):
+    import torch
+    rng = np.random.default_rng(21)
+    M, K = 1500, 384
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    A = dev(a, torch.bfloat16)
+    a16 = A.float().cpu().numpy().astype(np.float64)
+    # SwiGLU into 16-bit storage
+    w = (rng.standard_normal((1920, K)) / 20).astype(np.float32)
+    Wt = dev(w, torch.bfloat16)
+    w16 = Wt.float().cpu().numpy().astype(np.float64)
+    Cm = torch.zeros((M, 960), device="cuda", dtype=torch.bfloat16)
+    g = gemm_args(M, 1920, K, A, Wt, Cm, 960, c_dtype=1, swiglu=1)
+    keep, plan = tc_plan(L, g, 1)
+    ok(L.shvk_gemm_tc_rows(plan, 777, stream_ptr()))       # only the first 777 rows
+    sync()
+    full = a16 @ w16.T
+    ref = silu(full[:, 0::2]) * full[:, 1::2]
+    got = Cm.float().cpu().numpy()
+    assert rel_err(got[:777], ref[:777]) < 1e-2            # bf16 rounding of the output
+    assert (got[777:] == 0).all()
+    # residual in place / sqrt(2), fp32 output; bias
+    w = (rng.standard_normal((384, K)) / 20).astype(np.float32)
+    Wt = dev(w, torch.bfloat16)
+    w16 = Wt.float().cpu().numpy().astype(np.float64)
+    r = rng.standard_normal((M, 384)).astype(np.float32)
+    H = dev(r)
+    g = gemm_args(M, 384, K, A, Wt, H, 384, R=H, ldr=384, r_div=float(np.float32(np.sqrt(2.0))))
+    keep2, plan2 = tc_plan(L, g, 1)
+    ok(L.shvk_gemm_tc(plan2, stream_ptr()))
+    sync()
+    assert np.abs(H.cpu().numpy() - (r + (a16 @ w16.T) / np.sqrt(2.0))).max() < 1e-4
+    b = rng.standard_normal(384).astype(np.float32)
+    Cm = torch.zeros((M, 384), device="cuda")
+    Bt = dev(b)
+    g = gemm_args(M, 384, K, A, Wt, Cm, 384, bias=Bt)
+    keep3, plan3 = tc_plan(L, g, 1)
+    ok(L.shvk_gemm_tc(plan3, stream_ptr()))
+    sync()
+    assert np.abs(Cm.cpu().numpy() - (a16 @ w16.T + b)).max() < 1e-4
+    assert tc_status(L) == 0
+
+
+def test_gemm_tc_rows_do_not_depend_on_the_batch(L):
+    import torch
+    rng = np.random.default_rng(33)
+    a = rng.standard_normal((900, 384)).astype(np.float32)
+    w = rng.standard_normal((2316, 384)).astype(np.float32)
+    A, Wt = dev(a, torch.float16), dev(w, torch.float16)
+    big = torch.zeros((900, 2320), device="cuda")
+    k1, p1 = tc_plan(L, gemm_args(900, 2316, 384, A, Wt, big, 2320), 2)
+    ok(L.shvk_gemm_tc(p1, stream_ptr()))
+    one_a = A[515:516].contiguous()
+    one = torch.zeros((1, 2320), device="cuda")
+    k2, p2 = tc_plan(L, gemm_args(1, 2316, 384, one_a, Wt, one, 2320), 2)
+    ok(L.shvk_gemm_tc(p2, stream_ptr()))
+    sync()
+    assert torch.equal(big[515], one[0])
+
+
+# ---------------------------------------------------------------------------------------------- row kernels
+def test_assemble_norm_and_rmsnorm(L, weight_files):
+    import torch
+    _, w = weight_files("W3", 1)
+    B = 3
+    tok = W.synth_tokens(B, 4)
+    T = dev(tok)
+    ptrs = np.array([T.data_ptr() + i * 6144 * 4 for i in range(B * 20)], dtype=np.uint64)
+    P = dev(ptrs.view(np.int64))
+    pos = O.positions(w, np.dtype(np.float32))
+    nw = (1.0 + 0.1 * np.random.default_rng(0).standard_normal(384)).astype(np.float32)
+    h = torch.zeros((B * 321, 384), device="cuda")
+    d_pos, d_ro, d_nw = dev(pos), dev(w["readout"].reshape(384)), dev(nw)
+    for code, tdt, tol in ((0, torch.float32, 2e-6), (1, torch.bfloat16, 8e-3), (2, torch.float16, 1e-3)):
+        xn = torch.zeros((B * 321, 384), device="cuda", dtype=tdt)
+        ok(L.shvk_assemble_norm(P.data_ptr(), d_pos.data_ptr(), d_ro.data_ptr(), d_nw.data_ptr(), h.data_ptr(),
+                                xn.data_ptr(), code, B, stream_ptr()))
+        sync()
+        href = np.empty((B, 321, 384), np.float32)
+        href[:, :320] = tok.reshape(B, 320, 384) + pos
+        href[:, 320] = w["readout"].reshape(384)
+        np.testing.assert_array_equal(h.cpu().numpy().reshape(B, 321, 384), href)
+        ref = O.rms_norm(href.astype(np.float64), nw.astype(np.float64)).reshape(B * 321, 384)
+        assert rel_err(xn.float().cpu().numpy(), ref) < tol
+    # strided rows: the readout row of every clip
+    out = torch.zeros((B, 384), device="cuda")
+    ok(L.shvk_rmsnorm(h.data_ptr() + 320 * 384 * 4, 321 * 384, d_nw.data_ptr(), out.data_ptr(), 0, 384, B, stream_ptr()))
+    sync()
+    ref = O.rms_norm(href[:, 320].astype(np.float64), nw.astype(np.float64))
+    assert np.abs(out.cpu().numpy() - ref).max() < 2e-6
+
+
+# ---------------------------------------------------------------------------------------------- fused GDN scan
+def gdn_inputs(w, stage, B, seed):
+    """xn (float64) and the fused projection P (float32 [B*321, 2320]) of one mixer."""
+    rng = np.random.default_rng(seed)
+    xn = rng.standard_normal((B, 321, 384))
+    m = f"{stage}.mixer"
+    P = np.zeros((B, 321, 2320), np.float64)
+    P[..., 0:384] = xn @ w[f"{m}.q_proj.weight"].astype(np.float64).T
+    P[..., 384:768] = xn @ w[f"{m}.k_proj.weight"].astype(np.float64).T
+    P[..., 768:1536] = xn @ w[f"{m}.v_proj.weight"].astype(np.float64).T
+    P[..., 1536:2304] = xn @ w[f"{m}.g_proj.weight"].astype(np.float64).T
+    P[..., 2304:2310] = xn @ w[f"{m}.a_proj.weight"].astype(np.float64).T
+    P[..., 2310:2316] = xn @ w[f"{m}.b_proj.weight"].astype(np.float64).T
+    return xn, P.reshape(B * 321, 2320).astype(np.float32)
+
+
+@pytest.mark.parametrize("recipe,stage,B", [("W3", "gdn_a", 2), ("W3", "gdn_b", 1), ("W1", "gdn_a", 3)])
+def test_gdn_scan_matches_oracle(L, weight_files, recipe, stage, B):
+    import torch
+    _, w = weight_files(recipe, 1)
+    xn, P = gdn_inputs(w, stage, B, 17)
+    tr = {}
+    O.gdn_mixer(w, f"{stage}.mixer", xn, tr, "t")
+    m = f"{stage}.mixer"
+    conv_w = np.concatenate([w[f"{m}.{n}_conv1d.weight"].reshape(-1, 4) for n in "qkv"]).astype(np.float32)
+    conv_b = np.concatenate([w[f"{m}.{n}_conv1d.bias"] for n in "qkv"]).astype(np.float32)
+    # the synthetic files carry o_norm gain 1: test a non-trivial gain by rescaling the oracle's output
+    ow = (1.0 + 0.1 * np.random.default_rng(1).standard_normal(128)).astype(np.float32)
+    ref = (tr["t.o_gated"] * ow.astype(np.float64)).reshape(B * 321, 768)
+    assert np.all(w[f"{m}.o_norm.weight"] == 1.0)
+    Pd, d_cw, d_cb, d_al, d_dt, d_ow = dev(P), dev(conv_w), dev(conv_b), dev(w[f"{m}.A_log"]), dev(w[f"{m}.dt_bias"]), dev(ow)
+    for code, tdt, tol in ((0, torch.float32, None), (1, torch.bfloat16, 8e-3), (2, torch.float16, 1e-3)):
+        on = torch.zeros((B * 321, 768), device="cuda", dtype=tdt)
+        ok(L.shvk_gdn_scan(Pd.data_ptr(), d_cw.data_ptr(), d_cb.data_ptr(), d_al.data_ptr(), d_dt.data_ptr(),
+                           d_ow.data_ptr(), on.data_ptr(), code, B, stream_ptr()))
+        sync()
+        got = on.float().cpu().numpy()
+        if tol is None:
+            assert np.abs(got - ref).max() < 1e-4 * max(1.0, np.abs(ref).max())
+        else:
+            assert rel_err(got, ref) < tol
+
+
+# ---------------------------------------------------------------------------------------------- SISA attention + head
+def test_sisa_attention_matches_oracle(L, weight_files):
+    import torch
+    _, w = weight_files("W3", 1)
+    B = 3
+    rng = np.random.default_rng(23)
+    h = rng.standard_normal((B, 321, 384)) * 1.5
+    tr = {}
+    O.sisa_last_row(w, h, tr)
+    a = "sisa.attn"
+    xn = O.rms_norm(h, w["sisa.attn_norm.weight"].astype(np.float64))
+    S = np.zeros((B, 321, 1072))
+    S[..., 0:384] = xn @ w[f"{a}.W_K.weight"].astype(np.float64).T
+    S[..., 384:768] = xn @ w[f"{a}.W_V.weight"].astype(np.float64).T
+    S[..., 768:960] = xn @ w[f"{a}.W_B.weight"].astype(np.float64).T
+    S[..., 960:1056] = xn @ w[f"{a}.theta_proj.weight"].astype(np.float64).T
+    S[..., 1056:1062] = xn @ w[f"{a}.alpha_proj.weight"].astype(np.float64).T + w[f"{a}.alpha_proj.bias"]
+    S[..., 1062:1068] = xn @ w[f"{a}.forget_proj.weight"].astype(np.float64).T + w[f"{a}.forget_proj.bias"]
+    QC = np.concatenate([xn[:, 320] @ w[f"{a}.W_Q.weight"].astype(np.float64).T,
+                         xn[:, 320] @ w[f"{a}.W_C.weight"].astype(np.float64).T], axis=1)
+    Y = torch.zeros((B, 384), device="cuda")
+    d_s, d_qc, d_lam = dev(S.reshape(B * 321, 1072).astype(np.float32)), dev(QC.astype(np.float32)), dev(w[f"{a}.lambda_raw"])
+    ok(L.shvk_sisa_attn(d_s.data_ptr(), d_qc.data_ptr(), d_lam.data_ptr(), Y.data_ptr(), B, stream_ptr()))
+    sync()
+    assert np.abs(Y.cpu().numpy() - tr["sisa.attn_y_last"]).max() < 5e-5
+
+
+def test_head_matches_oracle(L, weight_files):
+    import torch
+    _, w = weight_files("W3", 1)
+    B = 5
+    x = np.random.default_rng(3).standard_normal((B, 384)) * 2
+    z = O.rms_norm(x, w["final_norm.weight"].astype(np.float64))
+    hid = silu(z @ w["head.0.weight"].astype(np.float64).T + w["head.0.bias"])
+    ref = hid @ w["head.2.weight"].astype(np.float64).reshape(128) + w["head.2.bias"][0]
+    out = torch.zeros(B, device="cuda")
+    t = [dev(x.astype(np.float32)), dev(w["final_norm.weight"]), dev(np.ascontiguousarray(w["head.0.weight"].T)),
+         dev(w["head.0.bias"]), dev(w["head.2.weight"].reshape(128)), dev(w["head.2.bias"])]
+    ok(L.shvk_head(*[v.data_ptr() for v in t], out.data_ptr(), B, stream_ptr()))
+    sync()
+    assert np.abs(out.cpu().numpy() - ref).max() < 1e-5
+
+
+def test_store_tokens(L):
+    import torch
+    blocks = torch.arange(4 * 6144, device="cuda", dtype=torch.float32).reshape(4, 6144)
+    pool = torch.zeros((6, 6144), device="cuda")
+    slots = dev(np.array([5, -1, 0, 2], np.int32))
+    ok(L.shvk_store_tokens(blocks.data_ptr(), slots.data_ptr(), pool.data_ptr(), 4, stream_ptr()))
+    sync()
+    assert torch.equal(pool[5], blocks[0]) and torch.equal(pool[0], blocks[2]) and torch.equal(pool[2], blocks[3])
+    assert (pool[[1, 3, 4]] == 0).all()
