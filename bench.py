@@ -1,0 +1,371 @@
+"""Benchmark of the SHIELD-V sequence stack (GDN-A, GDN-B x2, SISA, head) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--mode bf16|fp16|fp32] [--batch B] [--impl reference]
+
+One "step" = one pass of the whole sequence stack over B clips (20 frames x 16 tokens x 384 + readout = 321 rows per
+clip) per GPU.  Default workload: B = 4096 clips per GPU, bf16 mode, synthetic N(0,1) frame embeddings and seeded
+random-init weights (recipe W3 of shield_sisa_b200/weights.py); clips are sharded by batch across GPUs, no
+collective on the data path (weak scaling).  Rank 0 prints one JSON line:
+
+  value      clips/s of the whole job with tokens already resident in HBM, timed with CUDA events on the launching
+             stream, max over ranks
+  e2e        the same metric through the C ABI (shv_cuda_classify) with host buffers: pinned tokens are DMA'd to the
+             device and logits read back inside the timed region, every step
+  roofline   for the kernel with the largest share of the step: algorithmic bytes (or flops) per launch / its mean
+             launch time, measured here with CUDA events, against the measured peak in MEASURED_PEAKS.json
+  cpu_baseline  the reference's exact-FP32 CPU engine (oracle/_ref) on the host cores, on a bounded sample (N=1 only)
+
+`--impl reference` times the reference's own CPU implementation of this path on all host cores (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "clips_per_s_gdn_sisa_stack_b4096_t20"
+UNIT = "clips/s"
+NTOK, D = 321, 384
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def algorithmic_work(name: str, storage_bytes: int):
+    """(HBM bytes, tensor flops) per clip of one launch of kernel `name`: every tensor that crosses the kernel's
+    boundary is read or written once (GEMM-boundary model; weights are L2-resident and not counted)."""
+    s = storage_bytes
+    h = NTOK * D * 4
+    xn, on, hid = NTOK * D * s, NTOK * 768 * s, NTOK * 960 * s
+    p_out, s_out = NTOK * 2316 * 4, NTOK * 1068 * 4
+    table = {
+        "assemble_norm": (20 * 6144 * 4 + h + xn, 0),
+        "rmsnorm": (h + xn, 0),
+        "gemm.in_proj": (xn + p_out, 2 * NTOK * 2316 * 384),
+        "gdn_scan": (p_out + on, 0),
+        "gemm.o_proj": (on + 2 * h, 2 * NTOK * 384 * 768),
+        "gemm.ffn_up": (xn + hid, 2 * NTOK * 1920 * 384),
+        "gemm.ffn_down": (hid + 2 * h, 2 * NTOK * 384 * 960),
+        "gemm.sisa_in": (xn + s_out, 2 * NTOK * 1068 * 384),
+        "sisa_attn": (s_out, 0),
+    }
+    return table.get(name, (0, 0))
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples of one GPU while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_weights(tag: str):
+    from shield_sisa_b200 import weights as W
+    path = Path(tempfile.gettempdir()) / f"shv_bench_{os.getuid()}_{tag}" / "w3_seed1.weights"
+    if not path.exists() or not Path(str(path) + ".json").exists():
+        W.synth_weight_file(path, seed=1, recipe="W3")
+    return path
+
+
+# ---------------------------------------------------------------------------------------------- CPU baseline
+def cpu_reference_rate(weights_path, tokens_host, budget_s: float, threads: int | None = None):
+    """Windows/s of the reference CPU engine (oracle/_ref) on `threads` host threads over a bounded sample of
+    `tokens_host`; falls back to the numpy port of the oracle when the compiled reference did not travel."""
+    from oracle import ref_cpu, seq_oracle
+    cores = os.cpu_count() or 1
+    if ref_cpu.available():
+        threads = min(64, threads or cores)                   # a team is capped at 64 threads by the reference API
+        eng = ref_cpu.RefCpuEngine(weights_path, threads=threads)
+        n0 = min(len(tokens_host), max(threads, 8))
+        eng.classify(tokens_host[:n0])                        # warm-up: workspaces, page-in
+        t0 = time.perf_counter()
+        eng.classify(tokens_host[:n0])
+        rate0 = n0 / (time.perf_counter() - t0)
+        n = int(min(len(tokens_host), max(n0, rate0 * budget_s)))
+        t0 = time.perf_counter()
+        eng.classify(tokens_host[:n])
+        dt = time.perf_counter() - t0
+        isa = eng.isa
+        eng.close()
+        return {"value": n / dt, "unit": UNIT, "cores": threads, "kind": "reference",
+                "sample": f"{n} of the workload's clips, reference engine/model exact fp32 ({isa}), {threads} threads of "
+                          f"{cores} host cores, one timed call after a warm-up call, {dt:.1f} s"}
+    from shield_sisa_b200 import weights as W
+    w = W.read_shldv(weights_path)
+    n = min(len(tokens_host), 4)
+    t0 = time.perf_counter()
+    seq_oracle.classify_tokens(w, tokens_host[:n], np.float32)
+    dt = time.perf_counter() - t0
+    return {"value": n / dt, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"{n} clips through the numpy restatement (oracle/seq_oracle.py, float32), {dt:.1f} s"}
+
+
+# ---------------------------------------------------------------------------------------------- reference arm
+def run_reference(args, rank: int):
+    """The reference's own CPU implementation of the path on all host cores; one step = one bounded sample."""
+    if rank != 0:
+        return
+    from shield_sisa_b200 import weights as W
+    wpath = make_weights("ref")
+    cores = os.cpu_count() or 1
+    sample = int(os.environ.get("SHV_BENCH_REF_SAMPLE", max(64, min(args.batch, 16 * min(cores, 64)))))
+    tok = W.synth_tokens(sample, seed=2)
+    from oracle import ref_cpu
+    times = []
+    if ref_cpu.available():
+        threads = min(64, cores)
+        eng = ref_cpu.RefCpuEngine(wpath, threads=threads)
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            eng.classify(tok)
+            if i >= args.warmup:
+                times.append(time.perf_counter() - t0)
+        kind, desc = "reference", f"reference engine/model exact fp32 ({eng.isa})"
+        eng.close()
+    else:
+        from oracle import seq_oracle
+        threads, sample = 1, min(sample, 4)
+        w = W.read_shldv(wpath)
+        for i in range(min(args.warmup, 1) + args.steps):
+            t0 = time.perf_counter()
+            seq_oracle.classify_tokens(w, tok[:sample], np.float32)
+            if i >= min(args.warmup, 1):
+                times.append(time.perf_counter() - t0)
+        kind, desc = "port", "numpy restatement oracle/seq_oracle.py float32"
+    ms = 1000.0 * sum(times) / len(times)
+    value = sample / (ms / 1000.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"GDN+SISA sequence stack, B={args.batch} clips x 321 rows x 384, {args.mode} on the GPU arm",
+                   "sample_clips_per_step": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind,
+                         "sample": f"{sample} clips per step, {desc}, {threads} threads of {cores} host cores"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------- our arm
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+
+    from shield_sisa_b200 import binding
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    B, mode = args.batch, args.mode
+    storage = 4 if mode == "fp32" else 2
+    wpath = make_weights(f"r{rank}")
+    gen = torch.Generator(device="cuda").manual_seed(2 + rank)
+    tokens = torch.randn((B, 20, 16, D), device="cuda", dtype=torch.float32, generator=gen)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    # ------------------------------------------------------------ device-resident throughput
+    eng = binding.EngineCore(wpath, mode, device=local_rank, max_windows=B, use_graphs=True)
+    eng.bind_tokens(0, tokens.data_ptr(), B, stream)
+    for _ in range(args.warmup):
+        eng.classify(0, B, stream)
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        eng.classify(0, B, stream)
+    ev1.record()
+    barrier()
+    ms_step = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
+    clocks = sampler.stop() if sampler else None
+    if eng.status() != 0:
+        raise SystemExit(f"device status word {eng.status()}: a tensor-core kernel gave up waiting")
+    value = world * B / (ms_step / 1000.0)
+
+    # ------------------------------------------------------------ per-kernel times (CUDA events after every launch)
+    totals, counts = {}, {}
+    reps = 3
+    for _ in range(reps):
+        for name, ms in eng.profile(0, B, stream):
+            totals[name] = totals.get(name, 0.0) + ms
+            counts[name] = counts.get(name, 0) + 1
+    step_ms_eager = sum(totals.values()) / reps
+    pk, pk_src = peaks()
+    kernels = {}
+    for name, tot in totals.items():
+        avg = tot / counts[name]
+        nbytes, flops = algorithmic_work(name, storage)
+        kernels[name] = {"launches_per_step": counts[name] // reps, "avg_ms": avg, "share": tot / reps / step_ms_eager,
+                         "gbs": B * nbytes / avg / 1e6 if nbytes else None,
+                         "tflops": B * flops / avg / 1e9 if flops else None}
+    top = max(totals, key=totals.get)
+    k = kernels[top]
+    nbytes, flops = algorithmic_work(top, storage)
+    t_hbm = B * nbytes / (pk["hbm_gbs"] * 1e9)
+    t_tensor = B * flops / (pk["bf16_tflops_sustained"] * 1e12)
+    if flops and t_tensor > t_hbm:
+        roof = {"bound": "tensor", "achieved": k["tflops"], "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                "frac": k["tflops"] / pk["bf16_tflops_sustained"]}
+    else:
+        roof = {"bound": "hbm", "achieved": k["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": k["gbs"] / pk["hbm_gbs"]}
+    roof.update({"kernel": top, "peak_source": pk_src, "share_of_step": k["share"], "avg_launch_ms": k["avg_ms"],
+                 "algorithmic_bytes_per_launch": B * nbytes, "traffic": None})
+    alg_bytes_clip = 45853824 if mode == "fp32" else 37471872
+    stack_frac = B * alg_bytes_clip / (ms_step / 1000.0) / (pk["hbm_gbs"] * 1e9)
+    launches = eng.launches() * args.steps * world
+    eng.close()
+    del eng
+    torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------ end to end through the C ABI with host buffers
+    e2e = None
+    if B <= 4096:
+        model = binding.CudaModel(wpath, mode, device=local_rank, experimental=True, max_windows=B,
+                                  max_host_tokens=20 * B)
+        pin = binding.PinnedBuffer(model.L, (B, 20, 16, D))
+        pin.array[...] = tokens.cpu().numpy()
+        out = np.empty(B, np.float32)
+        for _ in range(max(1, min(args.warmup, 3))):
+            model.classify(pin.array, out)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            model.classify(pin.array, out)
+        dt = time.perf_counter() - t0
+        barrier()
+        e2e_ms = max_over_ranks(1000.0 * dt / args.steps)
+        if not np.isfinite(out).all():
+            raise SystemExit("end-to-end run returned non-finite logits")
+        e2e = {"value": world * B / (e2e_ms / 1000.0), "unit": UNIT, "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": B * 20 * 6144 * 4 + B * 20 * 8, "d2h_bytes_per_step": B * 4,
+               "api": "shv_cuda_classify, pinned host tokens (shv_cuda_host_alloc), max_windows = B"}
+        model.close()
+        pin.free()
+
+    # ------------------------------------------------------------ CPU baseline beside it (rank 0, N = 1)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        n = min(B, 2048)
+        cpu = cpu_reference_rate(wpath, tokens[:n].cpu().numpy(), budget_s=float(os.environ.get("SHV_BENCH_CPU_SECONDS", 15)))
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {"fp32": "f32", "bf16": "bf16", "fp16": "f16"}[mode], "data": "synthetic",
+            "config": {"workload": f"GDN+SISA sequence stack, B={B} clips per GPU x 321 rows x 384 (20 frames x 16 tokens + "
+                                   f"readout), {mode} mode, weights W3 seed 1, tokens N(0,1)",
+                       "l2": "inputs and activations exceed L2 (tokens 2 GB, activation arena ~20 GB per step)",
+                       "graphs": True, "sharding": f"{world} x {B} clips by batch, no collective"},
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
+            "stack_hbm_fraction": {"algorithmic_bytes_per_clip": alg_bytes_clip, "frac": stack_frac,
+                                   "note": "whole stack against the GEMM-boundary byte model and the measured HBM peak"},
+            "kernels": kernels,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="bf16", choices=["fp32", "bf16", "fp16"])
+    ap.add_argument("--batch", type=int, default=4096)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -47,6 +47,10 @@ int shvb_engine_window_bucket(const shvb_engine* e, int B);          /* size cla
 int shvb_engine_launches(const shvb_engine* e);                      /* kernels per classify */
 int shvb_engine_status(const shvb_engine* e);                        /* nonzero: a kernel's bounded wait gave up */
 size_t shvb_engine_bytes(const shvb_engine* e, int which);           /* 0 weights, 1 activations, 2 one slot */
+/* One eager classify of B windows with a CUDA event after every launch.  Writes up to `cap` per-launch times
+ * (milliseconds, launch order) to ms and the kernel names, separated by ';', to names (names_cap bytes).  Returns the
+ * number of launches, or -1.  Synchronises the stream. */
+int shvb_engine_profile(shvb_engine* e, int slot, int B, void* stream, float* ms, int cap, char* names, int names_cap);
 /* Debug: classify writes raw float32 intermediates of window 0 (<name>.f32) into dir; "" turns it off. */
 int shvb_engine_set_dump_dir(shvb_engine* e, const char* dir);
 

@@ -92,6 +92,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvb_engine_status": (i32, [vp]),
         "shvb_engine_bytes": (sz, [vp, i32]),
         "shvb_engine_set_dump_dir": (i32, [vp, C.c_char_p]),
+        "shvb_engine_profile": (i32, [vp, i32, i32, vp, vp, i32, C.c_char_p, i32]),
         "shvk_assemble_norm": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, vp]),
         "shvk_rmsnorm": (i32, [vp, C.c_longlong, vp, vp, i32, C.c_longlong, i32, vp]),
         "shvk_gemm_f32": (i32, [C.POINTER(GemmArgs), vp]),
@@ -296,6 +297,15 @@ class EngineCore:
         out = np.empty(n, np.float32)
         self._ok(self.L.shvb_engine_read_logits(self.e, slot, out.ctypes.data, n, stream))
         return out
+
+    def profile(self, slot, batch, stream=0):
+        """[(kernel name, ms)] of one eager classify, one entry per launch."""
+        ms = (C.c_float * 64)()
+        names = C.create_string_buffer(4096)
+        n = self.L.shvb_engine_profile(self.e, slot, batch, stream, ms, 64, names, 4096)
+        if n < 0:
+            raise RuntimeError(last_error(self.L))
+        return list(zip(names.value.decode().split(";"), [float(ms[i]) for i in range(n)]))
 
     def window_bucket(self, batch):
         return self.L.shvb_engine_window_bucket(self.e, batch)

@@ -130,6 +130,7 @@ public:
     }
     ~SeqEngine() override {
         for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second);
+        if (capture_) cudaStreamDestroy(capture_);
     }
 
     void encode(int, int F, cudaStream_t) override {
@@ -146,16 +147,19 @@ public:
         const long long key = ((long long)slot << 32) | (long long)n;
         auto it = graphs_.find(key);
         if (it == graphs_.end()) {
+            // captured on a stream the engine owns: the caller's stream may be the legacy default stream, which
+            // cannot be captured; the instantiated graph is then launched into the caller's stream
             cudaGraph_t g = nullptr;
-            cuda_ok(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal), "graph capture");
+            cudaStream_t cs = capture_stream();
+            cuda_ok(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal), "graph capture");
             try {
-                run(slot, n, s);
+                run(slot, n, cs);
             } catch (...) {
-                cudaStreamEndCapture(s, &g);
+                cudaStreamEndCapture(cs, &g);
                 if (g) cudaGraphDestroy(g);
                 throw;
             }
-            cuda_ok(cudaStreamEndCapture(s, &g), "graph capture");
+            cuda_ok(cudaStreamEndCapture(cs, &g), "graph capture");
             cudaGraphExec_t ex = nullptr;
             const cudaError_t e = cudaGraphInstantiate(&ex, g, 0);
             cudaGraphDestroy(g);
@@ -171,6 +175,37 @@ public:
         return shvk_gemm_tc_status(&st) == 0 ? st : -1;
     }
     int launches_per_classify() const override { return 28; }
+
+    // One eager classify with an event after every launch; returns (kernel name, milliseconds) per launch.
+    std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) override {
+        if (B <= 0 || B > cfg_.max_windows || slot < 0 || slot >= cfg_.slots) throw std::runtime_error("profile: bad argument");
+        std::vector<std::pair<std::string, cudaEvent_t>> marks;
+        cudaEvent_t t0 = nullptr;
+        cuda_ok(cudaEventCreate(&t0), "event");
+        cuda_ok(cudaEventRecord(t0, s), "event");
+        marks_ = &marks;
+        try {
+            run(slot, B, s);
+        } catch (...) {
+            marks_ = nullptr;
+            for (auto& m : marks) cudaEventDestroy(m.second);
+            cudaEventDestroy(t0);
+            throw;
+        }
+        marks_ = nullptr;
+        cuda_ok(cudaStreamSynchronize(s), "profile");
+        std::vector<std::pair<std::string, float>> out;
+        cudaEvent_t prev = t0;
+        for (auto& m : marks) {
+            float ms = 0.0f;
+            cudaEventElapsedTime(&ms, prev, m.second);
+            out.emplace_back(m.first, ms);
+            prev = m.second;
+        }
+        cudaEventDestroy(t0);
+        for (auto& m : marks) cudaEventDestroy(m.second);
+        return out;
+    }
 
 private:
     int dt_ = SHVK_F32;
@@ -188,6 +223,20 @@ private:
     float *xl_ = nullptr, *qc_ = nullptr, *y_ = nullptr, *x1_ = nullptr, *x2_ = nullptr, *hidl_ = nullptr;
     Site in_[2], oproj_[2], up_[2], down_[2], sisa_in_;
     std::map<long long, cudaGraphExec_t> graphs_;
+    cudaStream_t capture_ = nullptr;
+    cudaStream_t capture_stream() {
+        if (!capture_) cuda_ok(cudaStreamCreateWithFlags(&capture_, cudaStreamNonBlocking), "capture stream");
+        return capture_;
+    }
+    std::vector<std::pair<std::string, cudaEvent_t>>* marks_ = nullptr;   // non-null only inside profile()
+
+    void mark(const char* name, cudaStream_t s) {
+        if (!marks_) return;
+        cudaEvent_t e = nullptr;
+        cuda_ok(cudaEventCreate(&e), "event");
+        cuda_ok(cudaEventRecord(e, s), "event");
+        marks_->emplace_back(name, e);
+    }
 
     // ---------------------------------------------------------------- weights
     void upload(const HostModel& hm) {
@@ -336,38 +385,55 @@ private:
         const Slot& sl = slots_[size_t(slot)];
         const int M = B * NTOK;
         launch_ok(shvk_assemble_norm(sl.d_tokptr, pos_, readout_, gdn_[0].norm_w, h_, xn_, dt_, B, s), "assemble");
+        mark("assemble_norm", s);
         dump("h0", h_, size_t(NTOK) * D, SHVK_F32, s);
         for (int st = 0; st < 2; ++st) {
             const GdnDev& g = gdn_[st];
             const int reps = st == 0 ? 1 : 2;
             for (int r = 0; r < reps; ++r) {
                 rows_gemm(in_[st], M, s);
+                mark("gemm.in_proj", s);
                 launch_ok(shvk_gdn_scan(P_, g.conv_w, g.conv_b, g.a_log, g.dt_bias, g.o_norm_w, on_, dt_, B, s), "gdn scan");
+                mark("gdn_scan", s);
                 if (st == 0) dump("gdn_a.o_gated", on_, size_t(NTOK) * VD, dt_, s);
                 rows_gemm(oproj_[st], M, s);
+                mark("gemm.o_proj", s);
                 const float* next_norm = r + 1 < reps ? g.norm_w : g.ffn_norm_w;
                 launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_, dt_, D, M, s), "rmsnorm");
+                mark("rmsnorm", s);
             }
             rows_gemm(up_[st], M, s);
+            mark("gemm.ffn_up", s);
             rows_gemm(down_[st], M, s);
+            mark("gemm.ffn_down", s);
             dump(st == 0 ? "after_gdn_a" : "after_gdn_b", h_, size_t(NTOK) * D, SHVK_F32, s);
             const float* next_norm = st == 0 ? gdn_[1].norm_w : s_attn_norm_;
             launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_, dt_, D, M, s), "rmsnorm");
+            mark("rmsnorm", s);
         }
         float* S = P_;
         rows_gemm(sisa_in_, M, s);
+        mark("gemm.sisa_in", s);
         const float* h_last = h_ + size_t(NTOK - 1) * D;
         const long long ld_last = (long long)NTOK * D;
         launch_ok(shvk_rmsnorm(h_last, ld_last, s_attn_norm_, xl_, SHVK_F32, D, B, s), "rmsnorm (readout)");
+        mark("readout.rmsnorm", s);
         last_gemm(B, SQN, D, xl_, s_w_qc_, qc_, nullptr, 0, 0, s);
+        mark("readout.gemm_qc", s);
         launch_ok(shvk_sisa_attn(S, qc_, s_lambda_, y_, B, s), "sisa attention");
+        mark("sisa_attn", s);
         dump("sisa.y", y_, size_t(D), SHVK_F32, s);
         last_gemm(B, D, D, y_, s_w_o_, x1_, h_last, ld_last, 0, s);
+        mark("readout.gemm_wo", s);
         launch_ok(shvk_rmsnorm(x1_, D, s_ffn_norm_, xl_, SHVK_F32, D, B, s), "rmsnorm (readout ffn)");
+        mark("readout.rmsnorm", s);
         last_gemm(B, 2 * DFF, D, xl_, s_ffn_up_, hidl_, nullptr, 0, 1, s);
+        mark("readout.gemm_ffn_up", s);
         last_gemm(B, D, DFF, hidl_, s_ffn_down_, x2_, x1_, D, 0, s);
+        mark("readout.gemm_ffn_down", s);
         dump("after_sisa_row", x2_, size_t(D), SHVK_F32, s);
         launch_ok(shvk_head(x2_, fn_w_, h_w0t_, h_b0_, h_w2_, h_b2_, sl.d_logits, B, s), "head");
+        mark("head", s);
         dump("logit", sl.d_logits, 1, SHVK_F32, s);
     }
 };

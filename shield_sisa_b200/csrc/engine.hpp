@@ -15,6 +15,7 @@
 #include <memory>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace shv {
@@ -62,6 +63,9 @@ public:
     virtual int device_status() const = 0;
     // Kernels launched by one classify of B windows (for launch accounting in benchmarks).
     virtual int launches_per_classify() const = 0;
+    // One eager classify of B windows with a CUDA event after every launch: (kernel name, milliseconds) per launch,
+    // in launch order.  Synchronises the stream.
+    virtual std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) = 0;
 
 protected:
     Precision prec_ = Precision::FP32;

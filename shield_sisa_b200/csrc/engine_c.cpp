@@ -96,6 +96,22 @@ size_t shvb_engine_bytes(const shvb_engine* e, int which) {
     if (!e) return 0;
     return which == 0 ? e->eng->weight_bytes() : which == 1 ? e->eng->activation_bytes() : e->eng->slot_bytes();
 }
+int shvb_engine_profile(shvb_engine* e, int slot, int B, void* stream, float* ms, int cap, char* names, int names_cap) {
+    int n = -1;
+    guard([&] {
+        if (!e || !ms || !names || cap < 1 || names_cap < 1) throw std::runtime_error("profile: bad argument");
+        const auto rows = e->eng->profile(slot, B, cudaStream_t(stream));
+        std::string joined;
+        for (size_t i = 0; i < rows.size(); ++i) {
+            if (int(i) < cap) ms[i] = rows[i].second;
+            joined += (i ? ";" : "") + rows[i].first;
+        }
+        std::strncpy(names, joined.c_str(), size_t(names_cap) - 1);
+        names[names_cap - 1] = 0;
+        n = int(rows.size());
+    });
+    return n;
+}
 int shvb_engine_set_dump_dir(shvb_engine* e, const char* dir) {
     return guard([&] {
         if (!e) throw std::runtime_error("null engine");

@@ -85,7 +85,7 @@ def test_16_bit_modes_within_tolerance(mode, case, weight_files, tmp_path):
     ref = g["logits_f64"]
     assert np.isfinite(logits).all()
     assert np.abs(logits - ref).max() <= LOWP_TOL * max(1.0, np.abs(ref).max()), (logits, ref)
-    if "cpu:after_gdn_a" in g:
+    if "trace:after_gdn_a" in g:
         eng = binding.EngineCore(path, mode, max_windows=2, use_graphs=False)
         eng.set_dump_dir(tmp_path)
         T = dev(tok[:1])
