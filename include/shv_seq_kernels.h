@@ -64,11 +64,13 @@ int shvk_gemm_tc_status(int* status_out);
 
 /* Fused GatedDeltaNet core of one mixer over B clips: causal short conv (k=4, bias) + SiLU on q|k|v, L2 norm of q
  * (then * 0.125) and k, decay = exp(-exp(A_log) * softplus(a + dt_bias)), beta = sigmoid(b), the gated delta rule
- * from a zero state with the head's 64x128 state held in registers, and the gated RMSNorm
+ * from a zero state with the head's 64x128 state held in registers (operands staged by TMA), and the gated RMSNorm
  * ((o * rstd) * w) * silu(gate).  P: [B*321][2320] fp32 fused projection output; on: [B*321][768] storage type.
  * Replaces launch_gdn_prep + launch_delta + launch_gated_norm (engine/cuda/seq.cu:72-214,360-371). */
 int shvk_gdn_scan(const float* P, const float* conv_w, const float* conv_b, const float* a_log, const float* dt_bias,
                   const float* o_norm_w, void* on, int on_dtype, int B, void* stream);
+/* Device status word of the scan kernel: nonzero after a bounded wait on a TMA barrier gave up. */
+int shvk_gdn_scan_status(int* status_out);
 
 /* SISA attention of the readout row per (clip, head): -softplus(alpha), logsigmoid(forget), theta prefix sums in
  * double rounded to fp32, pair rotation of B (all rows) and C (row 320), scores, softmax over 321 keys, y = P V.

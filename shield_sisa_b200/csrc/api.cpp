@@ -327,7 +327,7 @@ private:
                 if (cudaEventElapsedTime(&gpu_ms, h.start, h.end) != cudaSuccess) { cudaGetLastError(); gpu_ms = 0.0f; }
                 if (engine->device_status() != 0) {
                     b.failed = true;
-                    b.error = "a tensor-core kernel gave up waiting on its pipeline (device status word set)";
+                    b.error = "a kernel gave up waiting on its TMA / tensor-core pipeline (device status word set)";
                 }
             }
         } else {

@@ -170,9 +170,10 @@ public:
     }
 
     int device_status() const override {
-        if (prec_ == Precision::FP32) return 0;
-        int st = 0;
-        return shvk_gemm_tc_status(&st) == 0 ? st : -1;
+        int scan = 0, gemm = 0;
+        if (shvk_gdn_scan_status(&scan) != 0) return -1;
+        if (prec_ != Precision::FP32 && shvk_gemm_tc_status(&gemm) != 0) return -1;
+        return scan ? 16 + scan : gemm;
     }
     int launches_per_classify() const override { return 28; }
 

@@ -27,7 +27,9 @@ namespace {
 
 constexpr int TILE_M = 128, TILE_K = 64, MAX_BN = 256, STAGES = 4, NTHREADS = 192;
 constexpr int A_BYTES = TILE_M * TILE_K * 2, B_BYTES = MAX_BN * TILE_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int STAGE_PITCH = 36;                                  // floats per staged row: 16-byte aligned, conflict-free
+constexpr int EPI_BYTES = 4 * 32 * STAGE_PITCH * 4;              // one 32 x 32 fp32 transpose buffer per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + EPI_BYTES;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of ~64 ns each before a wait gives up (about a quarter second)
 
 __device__ int g_tc_status = 0;   // 0 ok; else 1 + role of the wait that gave up
@@ -111,56 +113,75 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return d;
 }
 
+// Epilogue of one 32-row x (16 or 32)-column block held by one warp, one accumulator row per lane.  The block is
+// transposed through the warp's private shared-memory buffer so that global traffic is coalesced: in the second phase
+// a lane owns four consecutive columns and eight lanes cover a row, so every 128-bit access of a warp touches whole
+// 32-byte sectors of four rows (a lane-per-row store would touch 32 rows with 16 bytes each).
 template <typename T>
-__device__ __forceinline__ void epilogue_chunk(const TcParams& p, long long m, int n, const uint32_t (&r)[16]) {
-    float v[16];
+__device__ __forceinline__ void epilogue_block(const TcParams& p, float* stage, long long m0, int n0, int ncols, int lane,
+                                               const uint32_t (&r)[32]) {
+    float* mine = stage + lane * STAGE_PITCH;
+    if (p.swiglu) {
+        // (gate, up) pairs sit in adjacent accumulator columns of this lane's row: combine before the transpose
+        const int nout = ncols >> 1;                                  // 8 or 16 outputs per row
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-    if (p.swiglu) {                                  // 8 (gate, up) pairs -> 8 outputs at column n/2
-        if (n >= p.N) return;
-        float o[8];
+        for (int q = 0; q < 4; ++q) {
+            if (4 * q < nout) {
+                float o[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = silu_f(v[2 * j]) * v[2 * j + 1];
-        T* c = static_cast<T*>(p.C) + m * p.ldc + (n >> 1);
-        if (n + 16 <= p.N) {
-            store_quad<T>(c, o[0], o[1], o[2], o[3]);
-            store_quad<T>(c + 4, o[4], o[5], o[6], o[7]);
-        } else {
-            for (int j = 0; j < 8 && n + 2 * j < p.N; ++j) c[j] = from_float<T>(o[j]);
+                for (int j = 0; j < 4; ++j)
+                    o[j] = silu_f(__uint_as_float(r[8 * q + 2 * j])) * __uint_as_float(r[8 * q + 2 * j + 1]);
+                *reinterpret_cast<float4*>(mine + 4 * q) = make_float4(o[0], o[1], o[2], o[3]);
+            }
         }
+        __syncwarp();
+        const int lanes_per_row = nout >> 2;                          // 2 or 4 lanes of four outputs
+        const int rows_per_pass = 32 / lanes_per_row;
+        const int sub = lane % lanes_per_row, rsel = lane / lanes_per_row;
+        const int col = (n0 >> 1) + 4 * sub;                          // output column
+        for (int r0 = 0; r0 < 32; r0 += rows_per_pass) {
+            const int row = r0 + rsel;
+            const long long m = m0 + row;
+            if (m < p.M && 2 * col < p.N) {
+                const float4 v = *reinterpret_cast<const float4*>(stage + row * STAGE_PITCH + 4 * sub);
+                store_quad<T>(static_cast<T*>(p.C) + m * p.ldc + col, v.x, v.y, v.z, v.w);
+            }
+        }
+        __syncwarp();
         return;
     }
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const int nq = n + 4 * q;
-        if (nq >= p.N) break;
-        float x[4] = {v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]};
-        const bool full = nq + 4 <= p.N;
-        if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) if (full || nq + j < p.N) x[j] += p.bias[nq + j];
-        }
-        if (p.act == 1) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) x[j] = silu_f(x[j]);
-        }
-        if (p.R) {
-            const float* rr = p.R + m * p.ldr + nq;
-            float rv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (full) {
-                const float4 t = *reinterpret_cast<const float4*>(rr);
-                rv[0] = t.x; rv[1] = t.y; rv[2] = t.z; rv[3] = t.w;
-            } else {
-                for (int j = 0; j < 4 && nq + j < p.N; ++j) rv[j] = rr[j];
+    for (int q = 0; q < 8; ++q)
+        if (4 * q < ncols)
+            *reinterpret_cast<float4*>(mine + 4 * q) = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                                   __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+    __syncwarp();
+    const int lanes_per_row = ncols >> 2;                             // 4 or 8
+    const int rows_per_pass = 32 / lanes_per_row;
+    const int sub = lane % lanes_per_row, rsel = lane / lanes_per_row;
+    const int n = n0 + 4 * sub;
+    const bool col_ok = n < p.N;                                      // N is a multiple of 4: a quad is all in or all out
+    float4 bias = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (p.bias && col_ok) bias = *reinterpret_cast<const float4*>(p.bias + n);
+    for (int r0 = 0; r0 < 32; r0 += rows_per_pass) {
+        const int row = r0 + rsel;
+        const long long m = m0 + row;
+        if (m < p.M && col_ok) {
+            float4 v = *reinterpret_cast<const float4*>(stage + row * STAGE_PITCH + 4 * sub);
+            v.x += bias.x; v.y += bias.y; v.z += bias.z; v.w += bias.w;
+            if (p.act == 1) { v.x = silu_f(v.x); v.y = silu_f(v.y); v.z = silu_f(v.z); v.w = silu_f(v.w); }
+            if (p.R) {
+                const float4 rr = *reinterpret_cast<const float4*>(p.R + m * p.ldr + n);
+                if (p.r_div != 1.0f) {
+                    v.x = rr.x + v.x / p.r_div; v.y = rr.y + v.y / p.r_div; v.z = rr.z + v.z / p.r_div; v.w = rr.w + v.w / p.r_div;
+                } else {
+                    v.x = rr.x + v.x; v.y = rr.y + v.y; v.z = rr.z + v.z; v.w = rr.w + v.w;
+                }
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) x[j] = p.r_div != 1.0f ? rv[j] + x[j] / p.r_div : rv[j] + x[j];
+            store_quad<T>(static_cast<T*>(p.C) + m * p.ldc + n, v.x, v.y, v.z, v.w);
         }
-        T* c = static_cast<T*>(p.C) + m * p.ldc + nq;
-        if (full) store_quad<T>(c, x[0], x[1], x[2], x[3]);
-        else
-            for (int j = 0; j < 4 && nq + j < p.N; ++j) c[j] = from_float<T>(x[j]);
     }
+    __syncwarp();
 }
 
 template <typename T>
@@ -169,6 +190,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = base + STAGES * STAGE_BYTES;           // full[4], empty[4], acc_full[2], acc_empty[2]
+    const uint32_t epi_base = bars + 256;                        // four per-warp transpose buffers
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -251,13 +273,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int mt = int(tile / p.n_tiles), nt = int(tile - (long long)mt * p.n_tiles);
             if (!mbar_wait(accf_bar(acc), acc_phase, abortp)) { ok = false; break; }
             tc_fence_after();
-            const long long m = (long long)mt * TILE_M + quad * 32 + lane;
+            const long long m0 = (long long)mt * TILE_M + quad * 32;
             const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * MAX_BN);
-            for (int c = 0; c < p.BN; c += 16) {
-                uint32_t r[16];
-                tc_ld16(taddr + uint32_t(c), r);
+            float* stage = reinterpret_cast<float*>(smem_raw + (epi_base - smem_u32(smem_raw))) + (warp - 2) * 32 * STAGE_PITCH;
+            for (int c = 0; c < p.BN; c += 32) {
+                const int ncols = p.BN - c >= 32 ? 32 : 16;            // BN is a multiple of 16
+                uint32_t r[32];
+                tc_ld16(taddr + uint32_t(c), *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
+                if (ncols == 32) tc_ld16(taddr + uint32_t(c + 16), *reinterpret_cast<uint32_t(*)[16]>(&r[16]));
                 tc_wait_ld();
-                if (m < p.M) epilogue_chunk<T>(p, m, nt * p.BN + c, r);
+                epilogue_block<T>(p, stage, m0, nt * p.BN + c, ncols, lane, r);
             }
             tc_fence_before();
             __syncwarp();
@@ -341,7 +366,7 @@ extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* ho
     if (!g || !host_plan || (reinterpret_cast<uintptr_t>(host_plan) & 63)) return int(cudaErrorInvalidValue);
     if (ab_dtype != DT_BF16 && ab_dtype != DT_F16) return int(cudaErrorInvalidValue);
     if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->K % TILE_K || (g->lda & 7) || (g->ldw & 7) ||
-        ((reinterpret_cast<uintptr_t>(g->A) | reinterpret_cast<uintptr_t>(g->W)) & 15) || (g->swiglu && (g->N & 1)) ||
+        ((reinterpret_cast<uintptr_t>(g->A) | reinterpret_cast<uintptr_t>(g->W)) & 15) || (g->N & 3) || (g->swiglu && (g->N & 7)) ||
         (g->ldc & 3) || (g->R && (g->ldr & 3)) || (reinterpret_cast<uintptr_t>(g->C) & 15))
         return int(cudaErrorInvalidValue);
     HostPlan* hp = static_cast<HostPlan*>(host_plan);
