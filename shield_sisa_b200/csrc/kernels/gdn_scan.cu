@@ -9,7 +9,9 @@
 // overwrites v; the gated norm reads it back with the gate tile and writes the result to global memory.
 //
 // Arithmetic.  The head's 64 x 128 state stays in registers for the whole sequence: thread (g, s) with g = tid / 4,
-// s = tid % 4 holds the 16 x 4 block S[16s .. 16s+15][4g .. 4g+3] as eight float2 pairs along the key dimension, so the
+// s = tid % 4 holds 16 keys x 4 value columns of it, keys {16 j + 4 s + e : j, e < 4} (the four slices interleave at
+// float4 granularity, so that the slices' 128-bit reads of one k or q row fall on distinct banks) and columns
+// 4g .. 4g+3, as eight float2 pairs along the key dimension, so the
 // update and the two contractions over keys run as packed fp32x2 FMAs (fma.rn.f32x2) whose k / q operands come
 // straight out of 128-bit shared-memory loads (13 per token per thread), followed by a two-step shuffle reduction
 // over the four key slices.  The L2 normalisations are folded into scalars: with kr, qr the un-normalised conv
@@ -106,9 +108,9 @@ gdn_scan_kernel(const __grid_constant__ ScanMaps maps, const float* __restrict__
     float y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;   // raw v projection at t-1, t-2, t-3
     const float neg_rate = -expf(a_log[head]), dtb = dt_bias[head];
 
-    // scan role: key slice [16 ks, 16 ks + 16), value columns [4 cg, 4 cg + 4)
+    // scan role: key slice ks (keys 16 j + 4 ks + e), value columns [4 cg, 4 cg + 4)
     const int ks = tid & 3, cg = tid >> 2;
-    float2 S[8][4];                          // S[jp][c] = state rows 16 ks + 2 jp, + 1 of column 4 cg + c
+    float2 S[8][4];                          // S[2 j + h][c] = state rows 16 j + 4 ks + 2 h, + 1 of column 4 cg + c
 #pragma unroll
     for (int jp = 0; jp < 8; ++jp)
 #pragma unroll
@@ -190,7 +192,7 @@ gdn_scan_kernel(const __grid_constant__ ScanMaps maps, const float* __restrict__
             for (int c = 0; c < 4; ++c) acc[c] = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int jq = 0; jq < 4; ++jq) {
-                const float4 kk = *reinterpret_cast<const float4*>(&b.k[0][ks * 16 + jq * 4]);
+                const float4 kk = *reinterpret_cast<const float4*>(&b.k[0][(jq * 4 + ks) * 4]);
                 const float2 k01 = make_float2(kk.x, kk.y), k23 = make_float2(kk.z, kk.w);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -218,9 +220,9 @@ gdn_scan_kernel(const __grid_constant__ ScanMaps maps, const float* __restrict__
             for (int c = 0; c < 4; ++c) { o2[c] = make_float2(0.0f, 0.0f); n2[c] = make_float2(0.0f, 0.0f); }
 #pragma unroll
             for (int jq = 0; jq < 4; ++jq) {
-                const float4 kk = *reinterpret_cast<const float4*>(&b.k[i][ks * 16 + jq * 4]);
-                const float4 qq = *reinterpret_cast<const float4*>(&b.q[i][ks * 16 + jq * 4]);
-                const float4 kn = *reinterpret_cast<const float4*>(&b.k[0][0] + (i + 1) * kDK + ks * 16 + jq * 4);
+                const float4 kk = *reinterpret_cast<const float4*>(&b.k[i][(jq * 4 + ks) * 4]);
+                const float4 qq = *reinterpret_cast<const float4*>(&b.q[i][(jq * 4 + ks) * 4]);
+                const float4 kn = *reinterpret_cast<const float4*>(&b.k[0][0] + (i + 1) * kDK + (jq * 4 + ks) * 4);
                 const float2 kp[2] = {make_float2(kk.x, kk.y), make_float2(kk.z, kk.w)};
                 const float2 qp[2] = {make_float2(qq.x, qq.y), make_float2(qq.z, qq.w)};
                 const float2 np[2] = {make_float2(kn.x, kn.y), make_float2(kn.z, kn.w)};

@@ -1,14 +1,15 @@
 // Projection GEMMs on the 5th-generation tensor cores: C = epilogue(A * W^T), A [M,K] and W [N,K] both K-contiguous,
 // 16-bit operands (bf16 or fp16), fp32 accumulation in tensor memory.
 //
-// One persistent CTA per SM, 192 threads in three roles:
+// One persistent CTA per SM, 320 threads in three roles:
 //   warp 0      TMA producer: one lane streams 128 x 64 tiles of A and BN x 64 tiles of W (128-byte swizzle) into a
 //               4-deep shared-memory ring, completion counted in bytes on an mbarrier per stage
 //   warp 1      MMA issuer: one lane issues tcgen05.mma (M 128, N = BN, K 16, four per stage) from shared-memory
 //               descriptors into one of two TMEM accumulators; tcgen05.commit releases the stage to the producer and,
 //               after the last k block, hands the accumulator to the epilogue.  This warp also owns TMEM alloc/free.
-//   warps 2-5   epilogue: warp w reads TMEM lanes 32*(w%4).. (its hardware quadrant), 16 columns at a time, applies
-//               bias / SiLU / residual / SwiGLU and writes C, while the MMA warp already fills the other accumulator.
+//   warps 2-9   epilogue: warp w reads TMEM lanes 32*(w%4).. (its hardware quadrant; two warps per quadrant take
+//               alternate 32-column blocks), transposes each block through shared memory, applies bias / SiLU /
+//               residual / SwiGLU and writes C coalesced, while the MMA warp already fills the other accumulator.
 // K is walked in order and never split and every output is produced by exactly one accumulator, so a row of C does
 // not depend on M or on the other rows of the batch (engine/include/shv_cuda.h:31-34, engine/cuda/gemm.cuh:5-10).
 // No load uses cluster multicast: weight tiles are fetched per CTA and served from L2.
@@ -20,15 +21,16 @@
 #include "shv_seq_kernels.h"
 
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace sb {
 namespace {
 
-constexpr int TILE_M = 128, TILE_K = 64, MAX_BN = 256, STAGES = 4, NTHREADS = 192;
+constexpr int TILE_M = 128, TILE_K = 64, MAX_BN = 240, ACC_COLS = 256, STAGES = 4, EPI_WARPS = 8, NTHREADS = 64 + 32 * EPI_WARPS;
 constexpr int A_BYTES = TILE_M * TILE_K * 2, B_BYTES = MAX_BN * TILE_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STAGE_PITCH = 36;                                  // floats per staged row: 16-byte aligned, conflict-free
-constexpr int EPI_BYTES = 4 * 32 * STAGE_PITCH * 4;              // one 32 x 32 fp32 transpose buffer per epilogue warp
+constexpr int EPI_BYTES = EPI_WARPS * 32 * STAGE_PITCH * 4;      // one 32 x 32 fp32 transpose buffer per epilogue warp
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + EPI_BYTES;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of ~64 ns each before a wait gives up (about a quarter second)
 
@@ -41,6 +43,7 @@ struct TcParams {
     const float* R; long long ldr; float r_div;
     int swiglu;
     uint32_t idesc;
+    int probe;      // timing probes (SHVK_TC_PROBE, development only): 1 no global stores, 2 no epilogue work, 4 no MMA, 8 no W load, 16 no A load
 };
 
 // ---------------------------------------------------------------------------------------------- PTX wrappers
@@ -163,22 +166,33 @@ __device__ __forceinline__ void epilogue_block(const TcParams& p, float* stage, 
     const bool col_ok = n < p.N;                                      // N is a multiple of 4: a quad is all in or all out
     float4 bias = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (p.bias && col_ok) bias = *reinterpret_cast<const float4*>(p.bias + n);
-    for (int r0 = 0; r0 < 32; r0 += rows_per_pass) {
-        const int row = r0 + rsel;
+    // residual rows first, all passes at once: R may alias C, so the compiler cannot move these loads above the stores
+    // of an earlier pass by itself, and one dependent global load per pass would serialise on memory latency
+    float4 res[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        res[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const int row = k * rows_per_pass + rsel;
         const long long m = m0 + row;
-        if (m < p.M && col_ok) {
+        if (p.R && k * rows_per_pass < 32 && m < p.M && col_ok) res[k] = *reinterpret_cast<const float4*>(p.R + m * p.ldr + n);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int row = k * rows_per_pass + rsel;
+        const long long m = m0 + row;
+        if (k * rows_per_pass < 32 && m < p.M && col_ok) {
             float4 v = *reinterpret_cast<const float4*>(stage + row * STAGE_PITCH + 4 * sub);
             v.x += bias.x; v.y += bias.y; v.z += bias.z; v.w += bias.w;
             if (p.act == 1) { v.x = silu_f(v.x); v.y = silu_f(v.y); v.z = silu_f(v.z); v.w = silu_f(v.w); }
             if (p.R) {
-                const float4 rr = *reinterpret_cast<const float4*>(p.R + m * p.ldr + n);
+                const float4 rr = res[k];
                 if (p.r_div != 1.0f) {
                     v.x = rr.x + v.x / p.r_div; v.y = rr.y + v.y / p.r_div; v.z = rr.z + v.z / p.r_div; v.w = rr.w + v.w / p.r_div;
                 } else {
                     v.x = rr.x + v.x; v.y = rr.y + v.y; v.z = rr.z + v.z; v.w = rr.w + v.w;
                 }
             }
-            store_quad<T>(static_cast<T*>(p.C) + m * p.ldc + n, v.x, v.y, v.z, v.w);
+            if (!(p.probe & 1)) store_quad<T>(static_cast<T*>(p.C) + m * p.ldc + n, v.x, v.y, v.z, v.w);
         }
     }
     __syncwarp();
@@ -202,7 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -229,10 +243,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int mt = int(tile / p.n_tiles), nt = int(tile - (long long)mt * p.n_tiles);
                 for (int kb = 0; kb < nk; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(stage), stage_tx);
                     const uint32_t sa = base + stage * STAGE_BYTES, sb_ = sa + A_BYTES;
-                    tma_load_2d(sa, &map_a, kb * TILE_K, mt * TILE_M, full_bar(stage));
-                    tma_load_2d(sb_, &map_w, kb * TILE_K, nt * p.BN, full_bar(stage));
+                    const bool la = !(p.probe & 16), lw = !(p.probe & 8);
+                    if (la || lw) {
+                        mbar_expect_tx(full_bar(stage), (la ? uint32_t(A_BYTES) : 0u) + (lw ? stage_tx - uint32_t(A_BYTES) : 0u));
+                        if (la) tma_load_2d(sa, &map_a, kb * TILE_K, mt * TILE_M, full_bar(stage));
+                        if (lw) tma_load_2d(sb_, &map_w, kb * TILE_K, nt * p.BN, full_bar(stage));
+                    } else {
+                        mbar_arrive(full_bar(stage));
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -246,7 +265,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (long long tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
                 if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abortp)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + uint32_t(acc * MAX_BN);
+                const uint32_t d_tmem = tmem_base + uint32_t(acc * ACC_COLS);
                 for (int kb = 0; kb < nk; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, abortp)) { ok = false; break; }
                     tc_fence_after();
@@ -254,7 +273,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb_);
 #pragma unroll
                     for (int k = 0; k < TILE_K / 16; ++k)          // 16 elements = 32 bytes = 2 descriptor units
-                        tc_mma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
+                        if (!(p.probe & 4)) tc_mma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
                     tc_commit(empty_bar(stage));
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -274,15 +293,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!mbar_wait(accf_bar(acc), acc_phase, abortp)) { ok = false; break; }
             tc_fence_after();
             const long long m0 = (long long)mt * TILE_M + quad * 32;
-            const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * MAX_BN);
+            const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * ACC_COLS);
             float* stage = reinterpret_cast<float*>(smem_raw + (epi_base - smem_u32(smem_raw))) + (warp - 2) * 32 * STAGE_PITCH;
-            for (int c = 0; c < p.BN; c += 32) {
-                const int ncols = p.BN - c >= 32 ? 32 : 16;            // BN is a multiple of 16
-                uint32_t r[32];
+            // The two warps of a quadrant take alternate 32-column blocks.  The TMEM read of the next block is issued
+            // before the current one is transposed and written, so its latency hides behind the stores.
+            const int nblk = (p.BN + 31) >> 5;
+            const int half = (warp - 2) >> 2;
+            uint32_t ra[32], rb[32];
+            auto fetch = [&](int blk, uint32_t (&r)[32]) {
+                const int c = blk << 5;
+                if (p.probe & 32) return;
                 tc_ld16(taddr + uint32_t(c), *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
-                if (ncols == 32) tc_ld16(taddr + uint32_t(c + 16), *reinterpret_cast<uint32_t(*)[16]>(&r[16]));
+                if (p.BN - c >= 32) tc_ld16(taddr + uint32_t(c + 16), *reinterpret_cast<uint32_t(*)[16]>(&r[16]));
+            };
+            auto emit = [&](int blk, const uint32_t (&r)[32]) {
+                const int c = blk << 5;
+                if (p.probe & 64) return;
+                epilogue_block<T>(p, stage, m0, nt * p.BN + c, p.BN - c >= 32 ? 32 : 16, lane, r);
+            };
+            int blk = (p.probe & 2) ? nblk : half;
+            if (blk < nblk) fetch(blk, ra);
+            while (blk < nblk) {
                 tc_wait_ld();
-                epilogue_block<T>(p, stage, m0, nt * p.BN + c, ncols, lane, r);
+                if (blk + 2 < nblk) fetch(blk + 2, rb);
+                emit(blk, ra);
+                blk += 2;
+                if (blk >= nblk) break;
+                tc_wait_ld();
+                if (blk + 2 < nblk) fetch(blk + 2, ra);
+                emit(blk, rb);
+                blk += 2;
             }
             tc_fence_before();
             __syncwarp();
@@ -334,9 +374,9 @@ static_assert(sizeof(HostPlan) <= 512, "plan must fit the caller's 512-byte buff
 // bn/2 tensor cycles and moves 32*(128+bn) bytes out of shared memory at 128 bytes per cycle, so a tile costs
 // max(bn/2, (128+bn)/4); padded columns of the last tile count in full.  Ties go to the wider tile.
 int choose_bn(int n) {
-    int best = 256;
+    int best = MAX_BN;
     long long best_cost = -1;
-    for (int bn = 256; bn >= 64; bn -= 16) {
+    for (int bn = MAX_BN; bn >= 64; bn -= 16) {
         const long long tiles = (n + bn - 1) / bn;
         const long long per_tile = 2 * bn > 128 + bn ? 2 * bn : 128 + bn;    // 4 x max(bn/2, (128+bn)/4)
         const long long cost = tiles * per_tile;
@@ -382,6 +422,7 @@ extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* ho
     p.bias = g->bias; p.act = g->act;
     p.R = g->R; p.ldr = g->ldr; p.r_div = g->r_div == 0.0f ? 1.0f : g->r_div;
     p.swiglu = g->swiglu;
+    { const char* e = getenv("SHVK_TC_PROBE"); p.probe = e ? atoi(e) : 0; }
     const uint32_t fmt = ab_dtype == DT_BF16 ? 1u : 0u;
     // instruction descriptor: D fp32 (bits 4-5 = 1), A/B format (bits 7-9, 10-12), both K-major, N/8 at bit 17,
     // M/16 at bit 24
