@@ -3,13 +3,18 @@
 //
 // One persistent CTA per SM, 320 threads in three roles:
 //   warp 0      TMA producer: one lane streams 128 x 64 tiles of A and BN x 64 tiles of W (128-byte swizzle) into a
-//               4-deep shared-memory ring, completion counted in bytes on an mbarrier per stage
+//               shared-memory ring, completion counted in bytes on an mbarrier per stage
 //   warp 1      MMA issuer: one lane issues tcgen05.mma (M 128, N = BN, K 16, four per stage) from shared-memory
 //               descriptors into one of two TMEM accumulators; tcgen05.commit releases the stage to the producer and,
 //               after the last k block, hands the accumulator to the epilogue.  This warp also owns TMEM alloc/free.
-//   warps 2-9   epilogue: warp w reads TMEM lanes 32*(w%4).. (its hardware quadrant; two warps per quadrant take
-//               alternate 32-column blocks), transposes each block through shared memory, applies bias / SiLU /
-//               residual / SwiGLU and writes C coalesced, while the MMA warp already fills the other accumulator.
+//   warps 2-9   epilogue: warp w owns TMEM lanes 32*(w%4).. (its hardware quadrant), the two warps of a quadrant take
+//               alternate 32-column blocks.  A block goes TMEM -> registers (one accumulator row per lane) -> a
+//               swizzled 32 x 128-byte shared-memory tile -> global memory by a TMA tile store, which coalesces the
+//               rows and clips at the matrix edge.  For the residual epilogue the same tile is first filled by a TMA
+//               load of R (prefetched one block ahead), updated in place and stored back.
+// The epilogue costs a few dozen instructions per block and no address arithmetic per element, so it keeps up
+// with the tensor pipe; the MMA warp fills the other accumulator meanwhile.
+//
 // K is walked in order and never split and every output is produced by exactly one accumulator, so a row of C does
 // not depend on M or on the other rows of the batch (engine/include/shv_cuda.h:31-34, engine/cuda/gemm.cuh:5-10).
 // No load uses cluster multicast: weight tiles are fetched per CTA and served from L2.
@@ -27,23 +32,26 @@
 namespace sb {
 namespace {
 
-constexpr int TILE_M = 128, TILE_K = 64, MAX_BN = 240, ACC_COLS = 256, STAGES = 4, EPI_WARPS = 8, NTHREADS = 64 + 32 * EPI_WARPS;
+constexpr int TILE_M = 128, TILE_K = 64, MAX_BN = 240, ACC_COLS = 256, STAGES = 3, EPI_WARPS = 8;
+constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
 constexpr int A_BYTES = TILE_M * TILE_K * 2, B_BYTES = MAX_BN * TILE_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGE_PITCH = 36;                                  // floats per staged row: 16-byte aligned, conflict-free
-constexpr int EPI_BYTES = EPI_WARPS * 32 * STAGE_PITCH * 4;      // one 32 x 32 fp32 transpose buffer per epilogue warp
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + EPI_BYTES;
+constexpr int EPI_TILE = 32 * 128;                               // 32 rows x 128 bytes
+constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_TILE;              // two tiles per epilogue warp
+constexpr int NUM_BARS = 2 * STAGES + 4 + 2 * EPI_WARPS;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 256 /* barriers */ + 1024 /* alignment slack */;
+static_assert(STAGE_BYTES % 1024 == 0 && NUM_BARS * 8 <= 256, "swizzled tiles need 1024-byte alignment");
 constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of ~64 ns each before a wait gives up (about a quarter second)
+
+enum : int { EPI_PLAIN = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
 
 __device__ int g_tc_status = 0;   // 0 ok; else 1 + role of the wait that gave up
 
 struct TcParams {
     int M, N, K, BN, n_tiles, m_tiles;
-    void* C; long long ldc; int c_dtype;
-    const float* bias; int act;
-    const float* R; long long ldr; float r_div;
-    int swiglu;
+    const float* bias;
+    float r_div;
     uint32_t idesc;
-    int probe;      // timing probes (SHVK_TC_PROBE, development only): 1 no global stores, 2 no epilogue work, 4 no MMA, 8 no W load, 16 no A load
+    int probe;      // development timing probes (SHVK_TC_PROBE): 2 no epilogue work, 4 no MMA, 8 no W load, 16 no A load
 };
 
 // ---------------------------------------------------------------------------------------------- PTX wrappers
@@ -83,6 +91,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until all but the newest N store groups of this thread have finished reading shared memory.
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -95,7 +114,7 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t da, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
@@ -103,6 +122,17 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void sts128(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void sts128u(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
 
 // Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows of 128 bytes, groups of
 // 8 rows 1024 bytes apart (stride byte offset), leading byte offset unused (1), descriptor version 1, layout type 2.
@@ -116,95 +146,80 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return d;
 }
 
-// Epilogue of one 32-row x (16 or 32)-column block held by one warp, one accumulator row per lane.  The block is
-// transposed through the warp's private shared-memory buffer so that global traffic is coalesced: in the second phase
-// a lane owns four consecutive columns and eight lanes cover a row, so every 128-bit access of a warp touches whole
-// 32-byte sectors of four rows (a lane-per-row store would touch 32 rows with 16 bytes each).
-template <typename T>
-__device__ __forceinline__ void epilogue_block(const TcParams& p, float* stage, long long m0, int n0, int ncols, int lane,
-                                               const uint32_t (&r)[32]) {
-    float* mine = stage + lane * STAGE_PITCH;
-    if (p.swiglu) {
-        // (gate, up) pairs sit in adjacent accumulator columns of this lane's row: combine before the transpose
-        const int nout = ncols >> 1;                                  // 8 or 16 outputs per row
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            if (4 * q < nout) {
-                float o[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    o[j] = silu_f(__uint_as_float(r[8 * q + 2 * j])) * __uint_as_float(r[8 * q + 2 * j + 1]);
-                *reinterpret_cast<float4*>(mine + 4 * q) = make_float4(o[0], o[1], o[2], o[3]);
-            }
-        }
-        __syncwarp();
-        const int lanes_per_row = nout >> 2;                          // 2 or 4 lanes of four outputs
-        const int rows_per_pass = 32 / lanes_per_row;
-        const int sub = lane % lanes_per_row, rsel = lane / lanes_per_row;
-        const int col = (n0 >> 1) + 4 * sub;                          // output column
-        for (int r0 = 0; r0 < 32; r0 += rows_per_pass) {
-            const int row = r0 + rsel;
-            const long long m = m0 + row;
-            if (m < p.M && 2 * col < p.N) {
-                const float4 v = *reinterpret_cast<const float4*>(stage + row * STAGE_PITCH + 4 * sub);
-                store_quad<T>(static_cast<T*>(p.C) + m * p.ldc + col, v.x, v.y, v.z, v.w);
-            }
-        }
-        __syncwarp();
-        return;
-    }
-#pragma unroll
-    for (int q = 0; q < 8; ++q)
-        if (4 * q < ncols)
-            *reinterpret_cast<float4*>(mine + 4 * q) = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                                                   __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-    __syncwarp();
-    const int lanes_per_row = ncols >> 2;                             // 4 or 8
-    const int rows_per_pass = 32 / lanes_per_row;
-    const int sub = lane % lanes_per_row, rsel = lane / lanes_per_row;
-    const int n = n0 + 4 * sub;
-    const bool col_ok = n < p.N;                                      // N is a multiple of 4: a quad is all in or all out
-    float4 bias = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (p.bias && col_ok) bias = *reinterpret_cast<const float4*>(p.bias + n);
-    // residual rows first, all passes at once: R may alias C, so the compiler cannot move these loads above the stores
-    // of an earlier pass by itself, and one dependent global load per pass would serialise on memory latency
-    float4 res[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        res[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        const int row = k * rows_per_pass + rsel;
-        const long long m = m0 + row;
-        if (p.R && k * rows_per_pass < 32 && m < p.M && col_ok) res[k] = *reinterpret_cast<const float4*>(p.R + m * p.ldr + n);
-    }
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const int row = k * rows_per_pass + rsel;
-        const long long m = m0 + row;
-        if (k * rows_per_pass < 32 && m < p.M && col_ok) {
-            float4 v = *reinterpret_cast<const float4*>(stage + row * STAGE_PITCH + 4 * sub);
-            v.x += bias.x; v.y += bias.y; v.z += bias.z; v.w += bias.w;
-            if (p.act == 1) { v.x = silu_f(v.x); v.y = silu_f(v.y); v.z = silu_f(v.z); v.w = silu_f(v.w); }
-            if (p.R) {
-                const float4 rr = res[k];
-                if (p.r_div != 1.0f) {
-                    v.x = rr.x + v.x / p.r_div; v.y = rr.y + v.y / p.r_div; v.z = rr.z + v.z / p.r_div; v.w = rr.w + v.w / p.r_div;
-                } else {
-                    v.x = rr.x + v.x; v.y = rr.y + v.y; v.z = rr.z + v.z; v.w = rr.w + v.w;
-                }
-            }
-            if (!(p.probe & 1)) store_quad<T>(static_cast<T*>(p.C) + m * p.ldc + n, v.x, v.y, v.z, v.w);
-        }
-    }
-    __syncwarp();
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <typename T>
+struct TcMaps {
+    CUtensorMap a, w;             // operands, 128-byte swizzle
+    CUtensorMap c_full, c_half;   // output: boxes of 32 rows x (32 | 16) accumulator columns
+    CUtensorMap r_full, r_half;   // residual input (fp32), same boxes; only read by EPI_RESID
+};
+
+// Writes one epilogue block into its shared-memory tile.  Lane = accumulator row, r = its 32 (or 16) fp32 columns.
+//   fp32 tiles, 32 columns: 128-byte rows, 16-byte chunk j of row l at chunk j ^ (l & 7) (the TMA 128-byte swizzle,
+//                           which also makes these stores bank-conflict free); 16 columns: dense 64-byte rows
+//   EPI_RESID: the tile already holds R (TMA load); v = R + acc / r_div overwrites it in place
+//   EPI_SWIGLU: adjacent accumulator columns are (gate, up): silu(gate) * up in storage type T, dense rows
+template <typename T, int EPI>
+__device__ __forceinline__ void stage_block(const TcParams& p, uint32_t tile, int lane, bool full, int n, const uint32_t* r) {
+    if constexpr (EPI == EPI_SWIGLU) {
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (j < 4 || full) {
+                const float a = silu_f(__uint_as_float(r[4 * j])) * __uint_as_float(r[4 * j + 1]);
+                const float b = silu_f(__uint_as_float(r[4 * j + 2])) * __uint_as_float(r[4 * j + 3]);
+                o[j] = pack2<T>(a, b);
+            }
+        }
+        if (full) {
+            sts128u(tile + lane * 32, o[0], o[1], o[2], o[3]);
+            sts128u(tile + lane * 32 + 16, o[4], o[5], o[6], o[7]);
+        } else {
+            sts128u(tile + lane * 16, o[0], o[1], o[2], o[3]);
+        }
+    } else {
+        const uint32_t row = tile + uint32_t(lane) * (full ? 128u : 64u);
+        const uint32_t sw = full ? uint32_t(lane & 7) : 0u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (j < 4 || full) {
+                const uint32_t addr = row + ((uint32_t(j) ^ sw) << 4);
+                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                       __uint_as_float(r[4 * j + 3]));
+                if constexpr (EPI == EPI_RESID) {
+                    const float4 rr = lds128(addr);
+                    if (p.r_div != 1.0f) {
+                        v.x = rr.x + v.x / p.r_div; v.y = rr.y + v.y / p.r_div; v.z = rr.z + v.z / p.r_div; v.w = rr.w + v.w / p.r_div;
+                    } else {
+                        v.x = rr.x + v.x; v.y = rr.y + v.y; v.z = rr.z + v.z; v.w = rr.w + v.w;
+                    }
+                } else if (p.bias) {
+                    if (n + 4 * j < p.N) {
+                        const float4 b = *reinterpret_cast<const float4*>(p.bias + n + 4 * j);
+                        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                    }
+                }
+                sts128(addr, v.x, v.y, v.z, v.w);
+            }
+        }
+    }
+}
+
+template <typename T, int EPI>
 __global__ void __launch_bounds__(NTHREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const TcParams p) {
+gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = base + STAGES * STAGE_BYTES;           // full[4], empty[4], acc_full[2], acc_empty[2]
-    const uint32_t epi_base = bars + 256;                        // four per-warp transpose buffers
+    const uint32_t epi_base = base + STAGES * STAGE_BYTES;       // 16 tiles of 4 KB, 1024-byte aligned
+    const uint32_t bars = epi_base + EPI_BYTES;                  // full[S], empty[S], acc_full[2], acc_empty[2], r[8][2]
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -212,13 +227,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto accf_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
     auto acce_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    auto r_bar = [&](int ew, int b) { return bars + 8u * (2 * STAGES + 4 + 2 * ew + b); };
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), EPI_WARPS); }
+        for (int e = 0; e < EPI_WARPS; ++e) { mbar_init(r_bar(e, 0), 1); mbar_init(r_bar(e, 1), 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        fence_proxy_async();
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
@@ -247,8 +264,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const bool la = !(p.probe & 16), lw = !(p.probe & 8);
                     if (la || lw) {
                         mbar_expect_tx(full_bar(stage), (la ? uint32_t(A_BYTES) : 0u) + (lw ? stage_tx - uint32_t(A_BYTES) : 0u));
-                        if (la) tma_load_2d(sa, &map_a, kb * TILE_K, mt * TILE_M, full_bar(stage));
-                        if (lw) tma_load_2d(sb_, &map_w, kb * TILE_K, nt * p.BN, full_bar(stage));
+                        if (la) tma_load_2d(sa, &maps.a, kb * TILE_K, mt * TILE_M, full_bar(stage));
+                        if (lw) tma_load_2d(sb_, &maps.w, kb * TILE_K, nt * p.BN, full_bar(stage));
                     } else {
                         mbar_arrive(full_bar(stage));
                     }
@@ -284,51 +301,95 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!ok && !*abortp) { *abortp = 1; atomicCAS(&g_tc_status, 0, 2); }
         }
     } else {
-        const int quad = warp & 3;                                  // TMEM lane quadrant this warp may read
+        // ------------------------------------------------------------------------------------------ epilogue
+        const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
+        const int nblk = (p.BN + 31) >> 5;
+        const uint32_t tiles[2] = {epi_base + uint32_t(2 * ew) * EPI_TILE, epi_base + uint32_t(2 * ew + 1) * EPI_TILE};
+        const uint32_t rbars[2] = {r_bar(ew, 0), r_bar(ew, 1)};
+        const bool active = half < nblk && !(p.probe & 2);          // this warp has blocks to write
+        uint32_t rphase[2] = {0u, 0u};
+        uint32_t nb = 0;                                            // blocks done by this warp; tile buffer = nb & 1
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
+        // lane 0 only: TMA load of R for block (tile, blk) into tile buffer b
+        auto load_r = [&](long long tile, int blk, int b) {
+            const int mt = int(tile / p.n_tiles), nt = int(tile - (long long)mt * p.n_tiles);
+            const int c = blk << 5;
+            const bool full = p.BN - c >= 32;
+            mbar_expect_tx(rbars[b], full ? 4096u : 2048u);
+            tma_load_2d(tiles[b], full ? &maps.r_full : &maps.r_half, nt * p.BN + c, mt * TILE_M + quad * 32, rbars[b]);
+        };
+        if (EPI == EPI_RESID && active && lane == 0 && (long long)blockIdx.x < total) load_r(blockIdx.x, half, 0);
+
         for (long long tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
             const int mt = int(tile / p.n_tiles), nt = int(tile - (long long)mt * p.n_tiles);
             if (!mbar_wait(accf_bar(acc), acc_phase, abortp)) { ok = false; break; }
             tc_fence_after();
-            const long long m0 = (long long)mt * TILE_M + quad * 32;
+            const int m0 = mt * TILE_M + quad * 32;
             const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * ACC_COLS);
-            float* stage = reinterpret_cast<float*>(smem_raw + (epi_base - smem_u32(smem_raw))) + (warp - 2) * 32 * STAGE_PITCH;
-            // The two warps of a quadrant take alternate 32-column blocks.  The TMEM read of the next block is issued
-            // before the current one is transposed and written, so its latency hides behind the stores.
-            const int nblk = (p.BN + 31) >> 5;
-            const int half = (warp - 2) >> 2;
             uint32_t ra[32], rb[32];
-            auto fetch = [&](int blk, uint32_t (&r)[32]) {
+            auto fetch = [&](int blk, uint32_t* r) {
                 const int c = blk << 5;
-                if (p.probe & 32) return;
-                tc_ld16(taddr + uint32_t(c), *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
-                if (p.BN - c >= 32) tc_ld16(taddr + uint32_t(c + 16), *reinterpret_cast<uint32_t(*)[16]>(&r[16]));
+                tc_ld16(taddr + uint32_t(c), r);
+                if (p.BN - c >= 32) tc_ld16(taddr + uint32_t(c + 16), r + 16);
             };
-            auto emit = [&](int blk, const uint32_t (&r)[32]) {
+            // one block: (prefetch the next R), wait for R / for the tile buffer, stage, TMA store
+            auto emit = [&](int blk, const uint32_t* r) -> bool {
+                const int b = int(nb & 1u);
                 const int c = blk << 5;
-                if (p.probe & 64) return;
-                epilogue_block<T>(p, stage, m0, nt * p.BN + c, p.BN - c >= 32 ? 32 : 16, lane, r);
+                const bool full = p.BN - c >= 32;
+                const int n = nt * p.BN + c;
+                if constexpr (EPI == EPI_RESID) {
+                    if (lane == 0) {
+                        long long ntile = tile;
+                        int nblk2 = blk + 2;
+                        if (nblk2 >= nblk) { ntile = tile + gridDim.x; nblk2 = half; }
+                        if (ntile < total) {
+                            bulk_wait_read<0>();                  // the store that last read the other buffer is done with it
+                            load_r(ntile, nblk2, b ^ 1);
+                        }
+                    }
+                    if (!mbar_wait(rbars[b], rphase[b], abortp)) return false;
+                    rphase[b] ^= 1u;
+                } else {
+                    if (lane == 0) bulk_wait_read<1>();           // the store issued two blocks ago has left this buffer
+                    __syncwarp();
+                }
+                stage_block<T, EPI>(p, tiles[b], lane, full, n, r);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    const int x = EPI == EPI_SWIGLU ? (n >> 1) : n;
+                    tma_store_2d(full ? &maps.c_full : &maps.c_half, x, m0, tiles[b]);
+                    bulk_commit();
+                }
+                ++nb;
+                return true;
             };
-            int blk = (p.probe & 2) ? nblk : half;
-            if (blk < nblk) fetch(blk, ra);
-            while (blk < nblk) {
-                tc_wait_ld();
-                if (blk + 2 < nblk) fetch(blk + 2, rb);
-                emit(blk, ra);
-                blk += 2;
-                if (blk >= nblk) break;
-                tc_wait_ld();
-                if (blk + 2 < nblk) fetch(blk + 2, ra);
-                emit(blk, rb);
-                blk += 2;
+            if (active) {
+                int blk = half;
+                fetch(blk, ra);
+                while (true) {
+                    tc_wait_ld();
+                    if (blk + 2 < nblk) fetch(blk + 2, rb);
+                    if (!emit(blk, ra)) { ok = false; break; }
+                    blk += 2;
+                    if (blk >= nblk) break;
+                    tc_wait_ld();
+                    if (blk + 2 < nblk) fetch(blk + 2, ra);
+                    if (!emit(blk, rb)) { ok = false; break; }
+                    blk += 2;
+                    if (blk >= nblk) break;
+                }
+                if (!ok) break;
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar(acc));
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
+        if (lane == 0) bulk_wait_all();                             // stores must have left shared memory before exit
         if (!ok && lane == 0 && !*abortp) { *abortp = 1; atomicCAS(&g_tc_status, 0, 3); }
     }
 
@@ -362,15 +423,32 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// Row-major matrix [rows][cols] of elem_bytes-wide elements, row pitch ld elements, box box_rows x box_cols.
+bool make_map(CUtensorMap* map, const void* ptr, int elem_bytes, long long rows, long long cols, long long ld, int box_rows,
+              int box_cols, bool swizzle128) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(ld) * cuuint64_t(elem_bytes)};
+    const cuuint32_t box[2] = {cuuint32_t(box_cols), cuuint32_t(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    // 16-bit operands (bf16 or fp16 alike) travel as opaque 16-bit elements
+    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    return fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 struct HostPlan {
     CUtensorMap map_a, map_w;       // 128 bytes each, 64-byte aligned
     TcParams p;
-    int ab_dtype;
-    int valid;
+    void* C; long long ldc; int c_dtype;
+    const float* R; long long ldr;
+    int epi, ab_dtype, valid;
 };
 static_assert(sizeof(HostPlan) <= 512, "plan must fit the caller's 512-byte buffer");
 
-// Accumulator width (multiple of 16, 64..256) with the least time per row block.  Per 16-deep k step one MMA costs
+// Accumulator width (multiple of 16, 64..240) with the least time per row block.  Per 16-deep k step one MMA costs
 // bn/2 tensor cycles and moves 32*(128+bn) bytes out of shared memory at 128 bytes per cycle, so a tile costs
 // max(bn/2, (128+bn)/4); padded columns of the last tile count in full.  Ties go to the wider tile.
 int choose_bn(int n) {
@@ -385,17 +463,21 @@ int choose_bn(int n) {
     return best;
 }
 
-bool make_map(CUtensorMap* map, const void* ptr, long long rows, int k, long long ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
-    const cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
-    const cuuint32_t box[2] = {cuuint32_t(TILE_K), cuuint32_t(box_rows)};
-    const cuuint32_t estr[2] = {1, 1};
-    // bf16 and fp16 are both moved as opaque 16-bit elements
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+template <typename T, int EPI> int launch_tc(const HostPlan& hp, const TcMaps& maps, const TcParams& p, cudaStream_t s) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    static unsigned long long attr_done = 0;   // one bit per device ordinal: dynamic shared memory opt-in is per device
+    if (dev < 64 && !((attr_done >> dev) & 1ull)) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<T, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return int(e);
+        attr_done |= 1ull << dev;
+    }
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long total = (long long)p.m_tiles * p.n_tiles;
+    const unsigned grid = unsigned(total < sms ? total : sms);
+    (void)hp;
+    gemm_tc_kernel<T, EPI><<<grid, NTHREADS, SMEM_BYTES, s>>>(maps, p);
+    return int(cudaGetLastError());
 }
 
 }  // namespace
@@ -405,64 +487,76 @@ extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* ho
     using namespace sb;
     if (!g || !host_plan || (reinterpret_cast<uintptr_t>(host_plan) & 63)) return int(cudaErrorInvalidValue);
     if (ab_dtype != DT_BF16 && ab_dtype != DT_F16) return int(cudaErrorInvalidValue);
-    if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->K % TILE_K || (g->lda & 7) || (g->ldw & 7) ||
-        ((reinterpret_cast<uintptr_t>(g->A) | reinterpret_cast<uintptr_t>(g->W)) & 15) || (g->N & 3) || (g->swiglu && (g->N & 7)) ||
-        (g->ldc & 3) || (g->R && (g->ldr & 3)) || (reinterpret_cast<uintptr_t>(g->C) & 15))
+    if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->K % TILE_K || (g->lda & 7) || (g->ldw & 7) || (g->N & 3) ||
+        ((reinterpret_cast<uintptr_t>(g->A) | reinterpret_cast<uintptr_t>(g->W) | reinterpret_cast<uintptr_t>(g->C)) & 15) ||
+        (g->R && ((g->ldr & 3) || (reinterpret_cast<uintptr_t>(g->R) & 15))) || g->act != 0)
         return int(cudaErrorInvalidValue);
+    // supported epilogues: fp32 C (+ bias), fp32 C = R + acc / r_div, SwiGLU into 16-bit C
+    int epi;
+    if (g->swiglu) {
+        if ((g->N & 7) || g->c_dtype == DT_F32 || g->R || g->bias || (g->ldc & 7)) return int(cudaErrorInvalidValue);
+        epi = EPI_SWIGLU;
+    } else {
+        if (g->c_dtype != DT_F32 || (g->ldc & 3) || (g->R && g->bias)) return int(cudaErrorInvalidValue);
+        epi = g->R ? EPI_RESID : EPI_PLAIN;
+    }
     HostPlan* hp = static_cast<HostPlan*>(host_plan);
     memset(hp, 0, sizeof(HostPlan));
     const int bn = choose_bn(g->N);
-    if (!make_map(&hp->map_a, g->A, g->M, g->K, g->lda, TILE_M)) return int(cudaErrorNotSupported);
-    if (!make_map(&hp->map_w, g->W, g->N, g->K, g->ldw, bn)) return int(cudaErrorNotSupported);
+    if (!make_map(&hp->map_a, g->A, 2, g->M, g->K, g->lda, TILE_M, TILE_K, true)) return int(cudaErrorNotSupported);
+    if (!make_map(&hp->map_w, g->W, 2, g->N, g->K, g->ldw, bn, TILE_K, true)) return int(cudaErrorNotSupported);
     TcParams& p = hp->p;
     p.M = g->M; p.N = g->N; p.K = g->K; p.BN = bn;
     p.n_tiles = (g->N + bn - 1) / bn;
     p.m_tiles = (g->M + TILE_M - 1) / TILE_M;
-    p.C = g->C; p.ldc = g->ldc; p.c_dtype = g->c_dtype;
-    p.bias = g->bias; p.act = g->act;
-    p.R = g->R; p.ldr = g->ldr; p.r_div = g->r_div == 0.0f ? 1.0f : g->r_div;
-    p.swiglu = g->swiglu;
-    { const char* e = getenv("SHVK_TC_PROBE"); p.probe = e ? atoi(e) : 0; }
+    p.bias = g->bias;
+    p.r_div = g->r_div == 0.0f ? 1.0f : g->r_div;
     const uint32_t fmt = ab_dtype == DT_BF16 ? 1u : 0u;
     // instruction descriptor: D fp32 (bits 4-5 = 1), A/B format (bits 7-9, 10-12), both K-major, N/8 at bit 17,
     // M/16 at bit 24
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(TILE_M >> 4) << 24);
+    { const char* e = getenv("SHVK_TC_PROBE"); p.probe = e ? atoi(e) : 0; }
+    hp->C = g->C; hp->ldc = g->ldc; hp->c_dtype = g->c_dtype;
+    hp->R = g->R; hp->ldr = g->ldr;
+    hp->epi = epi;
     hp->ab_dtype = ab_dtype;
     hp->valid = 0x5b200;
     return 0;
 }
 
-namespace sb {
-namespace {
-template <typename T> int launch_tc(const HostPlan& hp, int M, cudaStream_t s) {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    static unsigned long long attr_done = 0;   // one bit per device ordinal: dynamic shared memory opt-in is per device
-    if (dev < 64 && !((attr_done >> dev) & 1ull)) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return int(e);
-        attr_done |= 1ull << dev;
-    }
-    TcParams p = hp.p;
-    p.M = M;
-    p.m_tiles = (M + TILE_M - 1) / TILE_M;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const long long total = (long long)p.m_tiles * p.n_tiles;
-    const unsigned grid = unsigned(total < sms ? total : sms);
-    gemm_tc_kernel<T><<<grid, NTHREADS, SMEM_BYTES, s>>>(hp.map_a, hp.map_w, p);
-    return int(cudaGetLastError());
-}
-}  // namespace
-}  // namespace sb
-
-// `rows` <= the M the plan was made for (the tensor map covers the planned extent; rows beyond `rows` are not written).
+// `rows` <= the M the plan was made for; rows beyond `rows` are neither read for the residual nor written (the output
+// tensor maps are encoded for exactly `rows` rows, so the TMA stores clip there).
 extern "C" int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream) {
     using namespace sb;
     const HostPlan* hp = static_cast<const HostPlan*>(host_plan);
     if (!hp || hp->valid != 0x5b200 || rows > hp->p.M) return int(cudaErrorInvalidValue);
     if (rows <= 0) return 0;
-    SB_DISPATCH_DTYPE(hp->p.c_dtype, T, return launch_tc<T>(*hp, rows, cudaStream_t(stream)));
-    return int(cudaErrorInvalidValue);
+    TcParams p = hp->p;
+    p.M = rows;
+    p.m_tiles = (rows + TILE_M - 1) / TILE_M;
+    TcMaps maps;
+    maps.a = hp->map_a;
+    maps.w = hp->map_w;
+    bool ok;
+    if (hp->epi == EPI_SWIGLU) {
+        ok = make_map(&maps.c_full, hp->C, 2, rows, p.N / 2, hp->ldc, 32, 16, false) &&
+             make_map(&maps.c_half, hp->C, 2, rows, p.N / 2, hp->ldc, 32, 8, false);
+        maps.r_full = maps.c_full;
+        maps.r_half = maps.c_half;
+    } else {
+        ok = make_map(&maps.c_full, hp->C, 4, rows, p.N, hp->ldc, 32, 32, true) &&
+             make_map(&maps.c_half, hp->C, 4, rows, p.N, hp->ldc, 32, 16, false);
+        if (hp->epi == EPI_RESID)
+            ok = ok && make_map(&maps.r_full, hp->R, 4, rows, p.N, hp->ldr, 32, 32, true) &&
+                 make_map(&maps.r_half, hp->R, 4, rows, p.N, hp->ldr, 32, 16, false);
+        else { maps.r_full = maps.c_full; maps.r_half = maps.c_half; }
+    }
+    if (!ok) return int(cudaErrorNotSupported);
+    cudaStream_t s = cudaStream_t(stream);
+    if (hp->epi == EPI_PLAIN) return launch_tc<float, EPI_PLAIN>(*hp, maps, p, s);
+    if (hp->epi == EPI_RESID) return launch_tc<float, EPI_RESID>(*hp, maps, p, s);
+    if (hp->c_dtype == DT_BF16) return launch_tc<__nv_bfloat16, EPI_SWIGLU>(*hp, maps, p, s);
+    return launch_tc<__half, EPI_SWIGLU>(*hp, maps, p, s);
 }
 
 extern "C" int shvk_gemm_tc(const void* host_plan, void* stream) {
