@@ -174,8 +174,10 @@ __device__ __forceinline__ void stage_block(const TcParams& p, uint32_t tile, in
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             if (j < 4 || full) {
-                const float a = silu_f(__uint_as_float(r[4 * j])) * __uint_as_float(r[4 * j + 1]);
-                const float b = silu_f(__uint_as_float(r[4 * j + 2])) * __uint_as_float(r[4 * j + 3]);
+                // hardware exp / reciprocal: the product is rounded to 16 bits right after
+                const float g0 = __uint_as_float(r[4 * j]), g1 = __uint_as_float(r[4 * j + 2]);
+                const float a = __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(r[4 * j + 1]);
+                const float b = __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(r[4 * j + 3]);
                 o[j] = pack2<T>(a, b);
             }
         }
