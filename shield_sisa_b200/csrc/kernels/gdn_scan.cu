@@ -28,6 +28,9 @@
 #include "device_utils.cuh"
 #include "shv_seq_kernels.h"
 #include "tma_utils.cuh"
+#include "gdn_scan_mma.cuh"
+
+#include <stdlib.h>
 
 namespace sb {
 namespace {
@@ -272,6 +275,11 @@ extern "C" int shvk_gdn_scan(const float* P, const float* conv_w, const float* c
     using namespace sb;
     if (B <= 0) return 0;
     if (reinterpret_cast<uintptr_t>(P) & 15) return int(cudaErrorInvalidValue);
+    // 16-bit output = a 16-bit mode: the chunked tensor-core form of the recurrence (gdn_scan_mma.cu).  The exact tier
+    // (fp32 output) keeps the per-token fp32 kernel below; SHVK_SCAN_EXACT=1 forces it everywhere (A/B measurements).
+    static const bool force_exact = [] { const char* e = getenv("SHVK_SCAN_EXACT"); return e && *e == '1'; }();
+    if (on_dtype != DT_F32 && !force_exact)
+        return launch_gdn_scan_mma(P, conv_w, conv_b, a_log, dt_bias, o_norm_w, on, on_dtype, B, cudaStream_t(stream));
     ScanMaps maps;
     const long long rows = (long long)B * kTok;
     if (!tma::make_map_f32(&maps.qk, P, rows, kGLD, kGLD, TC, kDK) || !tma::make_map_f32(&maps.vg, P, rows, kGLD, kGLD, TC, kDV) ||
@@ -288,8 +296,9 @@ extern "C" int shvk_gdn_scan(const float* P, const float* conv_w, const float* c
 }
 
 extern "C" int shvk_gdn_scan_status(int* status_out) {
-    int v = 0;
+    int v = 0, m = 0;
     const cudaError_t e = cudaMemcpyFromSymbol(&v, sb::g_scan_status, sizeof(int));
-    if (status_out) *status_out = v;
-    return int(e);
+    const int e2 = sb::gdn_scan_mma_status(&m);
+    if (status_out) *status_out = v ? v : (m ? 8 + m : 0);
+    return e != cudaSuccess ? int(e) : e2;
 }

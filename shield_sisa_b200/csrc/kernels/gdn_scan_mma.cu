@@ -1,0 +1,435 @@
+// Fused GatedDeltaNet core for the 16-bit modes: the delta rule in chunks of 16 tokens on the tensor cores.
+//
+// Same inputs, outputs and fusion as gdn_scan.cu (TMA-staged slices of the projection P, conv + SiLU, L2 norms, gates,
+// delta rule, gated RMSNorm), but the recurrence is evaluated 16 tokens at a time in its WY form, so that the 64 x 128
+// state is touched by matrix products instead of per-token sweeps.  For a chunk with inclusive cumulative log decay
+// c_i, e_i = exp(c_i), state S0 (keys x values) entering the chunk:
+//     A = K K^T, B = Q K^T                                      (16 x 16, contraction over the 64 keys)
+//     L_ij = beta_i exp(c_i - c_j) A_ij (j < i),  T = (I + L)^-1,  T2 = T diag(beta),  M_ij = exp(c_i - c_j) B_ij (j <= i)
+//     R = K S0,  QS = Q S0                                       (16 x 128)
+//     U = T2 (V - diag(e) R)                                    (16 x 128)
+//     O = M U + diag(e) QS
+//     S' = e_16 S0 + K^T diag(exp(c_16 - c_j)) U
+// Everything is computed transposed (value dimension = MMA rows), which makes every hand-over between products a
+// register-only repack: warp w owns value columns 32w .. 32w+31, keeps its slice of S^T (32 x 64, fp32) as the
+// accumulator fragments of mma.sync.m16n8k16, and the accumulator layout of one product (rows = values, columns =
+// tokens) is exactly the A-operand layout of the next.  Only K, Q, T2 and M pass through shared memory (bf16 tiles
+// written once per chunk, read as B fragments), and the 16 x 16 triangular inverse is a 16-lane forward substitution
+// in fp32.  Operands are rounded to bf16, the state and all accumulation stay fp32: the error against the exact
+// recurrence is a few 1e-3 relative on the delta-rule output (measured against the oracle in the tests), inside the
+// 2e-2 budget of the 16-bit modes.  The exact tier keeps the per-token fp32 kernel of gdn_scan.cu.
+//
+// Warp-level mma.sync rather than tcgen05: per 16-token chunk the products form a dependency chain five deep on tiles
+// of 16 tokens; tcgen05 needs M >= 64 rows and an asynchronous issue / commit / tensor-memory round trip per link of
+// that chain, which costs more than the products themselves.  tcgen05 carries the projections (gemm_tc.cu).
+//
+// Reference: engine/cuda/seq.cu:72-214 (gdn_prep + delta + gated_norm), oracle/shieldv_ref.py:121-163,186-197.
+#include "device_utils.cuh"
+#include "gdn_scan_mma.cuh"
+#include "tma_utils.cuh"
+
+namespace sb {
+namespace {
+
+constexpr int TC = 16;
+constexpr uint32_t WAIT_POLLS = 1u << 22;    // about a quarter second
+constexpr int KB_PITCH = 72;                 // bf16 per row of the K / Q tiles (144 bytes: conflict-free fragment reads)
+constexpr int KT_PITCH = 24;                 // bf16 per row of K^T, T2, M tiles (48 bytes)
+constexpr int VT_PITCH = 20;                 // floats per row of V^T
+
+__device__ int g_scan_mma_status = 0;
+
+struct RawBuf {                              // TMA targets, one chunk
+    float q[TC][kDK];                        // raw q -> silu(conv q), fp32, un-normalised
+    float k[TC][kDK];
+    float v[TC][kDV];                        // raw v; after prep reused as the chunk's output tile o[token][value]
+    float ab[TC][16];
+};
+static_assert(sizeof(RawBuf) == 17408 && sizeof(RawBuf) % 128 == 0, "tile offsets must stay 128-byte aligned");
+
+struct MmaSmem {
+    RawBuf raw[2];
+    float g[TC][kDV];                        // output gate tile of the current chunk (single buffer)
+    float vt[kDV][VT_PITCH];                 // silu(conv v), transposed: [value][token]
+    __nv_bfloat16 kb[TC][KB_PITCH];          // normalised k, [token][key]
+    __nv_bfloat16 qb[TC][KB_PITCH];          // normalised q * 0.125
+    __nv_bfloat16 kt[kDK][KT_PITCH];         // normalised k, [key][token]
+    __nv_bfloat16 t2[TC][KT_PITCH];          // (I + L)^-1 diag(beta)
+    __nv_bfloat16 mq[TC][KT_PITCH];          // decay-masked Q K^T
+    float lf[TC][TC + 1];                    // L, fp32, for the triangular inverse
+    float part[TC][4];
+    float iq[TC], ik[TC], lg[TC], beta[TC];  // 0.125/|q|, 1/|k|, log decay, beta (0 beyond the sequence end)
+    float cum[TC], eg[TC], dj[TC];           // c_i, exp(c_i), exp(c_last - c_i)
+    unsigned long long full[2], gfull;       // mbarriers
+};
+constexpr int MMA_SMEM_BYTES = int(sizeof(MmaSmem)) + 128;
+
+struct MmaMaps {
+    CUtensorMap qk;    // box 16 x 64
+    CUtensorMap vg;    // box 16 x 128
+    CUtensorMap ab;    // box 16 x 16
+};
+
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// D (16x8, fp32) += A (16x16, bf16, row) * B (16x8, bf16, col)
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128, 3)
+gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restrict__ conv_w, const float* __restrict__ conv_b,
+                    const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ o_norm_w,
+                    T* __restrict__ on) {
+    extern __shared__ uint8_t mma_smem_raw[];
+    MmaSmem& sm = *reinterpret_cast<MmaSmem*>((reinterpret_cast<uintptr_t>(mma_smem_raw) + 127) & ~uintptr_t(127));
+    const int clip = blockIdx.x / kHeads, head = blockIdx.x % kHeads;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;               // mma fragment coordinates
+    const int row_base = clip * kTok;
+    const int dvb = warp * 32;                           // this warp's value columns
+
+    // prep role: one q or k channel and one v column per thread; conv tap j multiplies x[t - 3 + j]
+    const bool is_k = tid >= kDK;
+    const int ch = tid & (kDK - 1);
+    const int qk_w = (is_k ? 384 : 0) + head * kDK + ch;
+    const float4 wqk = *reinterpret_cast<const float4*>(conv_w + qk_w * 4);
+    const float bqk = conv_b[qk_w];
+    const int v_w = 768 + head * kDV + tid;
+    const float4 wv = *reinterpret_cast<const float4*>(conv_w + v_w * 4);
+    const float bv = conv_b[v_w];
+    float x1 = 0.0f, x2 = 0.0f, x3 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;   // zero history = causal padding
+    const float neg_rate = -expf(a_log[head]), dtb = dt_bias[head];
+
+    // S^T slice of this warp as accumulator fragments: S[mi][nj][.] = values dvb + 16 mi + {g, g + 8}, keys 8 nj + 2t, + 1
+    float S[2][8][4];
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int nj = 0; nj < 8; ++nj)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) S[mi][nj][e] = 0.0f;
+
+    const uint32_t bar0 = tma::smem_addr(&sm.full[0]), bar1 = tma::smem_addr(&sm.full[1]), gbar = tma::smem_addr(&sm.gfull);
+    auto issue = [&](int chunk) {                         // thread 0: q, k, v, a|b tiles of `chunk`
+        RawBuf& b = sm.raw[chunk & 1];
+        const uint32_t bar = (chunk & 1) ? bar1 : bar0;
+        const int row = row_base + chunk * TC;
+        tma::mbar_expect_tx(bar, uint32_t(sizeof(RawBuf)));
+        tma::load_2d(tma::smem_addr(&b.q[0][0]), &maps.qk, kGQ + head * kDK, row, bar);
+        tma::load_2d(tma::smem_addr(&b.k[0][0]), &maps.qk, kGK + head * kDK, row, bar);
+        tma::load_2d(tma::smem_addr(&b.v[0][0]), &maps.vg, kGV + head * kDV, row, bar);
+        tma::load_2d(tma::smem_addr(&b.ab[0][0]), &maps.ab, kGA, row, bar);
+    };
+    if (tid == 0) {
+        tma::mbar_init(bar0, 1);
+        tma::mbar_init(bar1, 1);
+        tma::mbar_init(gbar, 1);
+        tma::fence_barrier_init();
+        tma::fence_proxy_async();
+        issue(0);
+    }
+    __syncthreads();
+
+    constexpr int NCHUNK = (kTok + TC - 1) / TC;
+    for (int chunk = 0; chunk < NCHUNK; ++chunk) {
+        const int t0 = chunk * TC, nt = min(TC, kTok - t0);
+        RawBuf& b = sm.raw[chunk & 1];
+        if (tid == 0) {
+            tma::fence_proxy_async();
+            if (chunk + 1 < NCHUNK) issue(chunk + 1);     // the other raw buffer is free since the closing barrier
+            tma::mbar_expect_tx(gbar, uint32_t(sizeof(sm.g)));
+            tma::load_2d(tma::smem_addr(&sm.g[0][0]), &maps.vg, kGG + head * kDV, row_base + t0, gbar);
+        }
+        if (!tma::mbar_wait_bounded((chunk & 1) ? bar1 : bar0, uint32_t(chunk >> 1) & 1u, WAIT_POLLS)) {
+            if (tid == 0) atomicCAS(&g_scan_mma_status, 0, 1);
+            return;                                       // every thread times out on the same barrier and leaves
+        }
+        // ---------------------------------------------------------------- prep: conv + SiLU, sums of squares, gates
+#pragma unroll 4
+        for (int i = 0; i < TC; ++i) {
+            float* pqk = is_k ? &b.k[i][ch] : &b.q[i][ch];
+            const float raw_qk = *pqk, raw_v = b.v[i][tid];
+            float acc = wqk.x * x3;
+            acc = fmaf(wqk.y, x2, acc);
+            acc = fmaf(wqk.z, x1, acc);
+            acc = fmaf(wqk.w, raw_qk, acc);
+            const float val = silu_fast(acc + bqk);
+            *pqk = val;
+            x3 = x2; x2 = x1; x1 = raw_qk;
+            float accv = wv.x * y3;
+            accv = fmaf(wv.y, y2, accv);
+            accv = fmaf(wv.z, y1, accv);
+            accv = fmaf(wv.w, raw_v, accv);
+            sm.vt[tid][i] = silu_fast(accv + bv);
+            y3 = y2; y2 = y1; y1 = raw_v;
+            const float ss = warp_sum(val * val);
+            if (lane == 0) sm.part[i][warp] = ss;
+        }
+        if (tid < TC) {                                   // tokens past the sequence end are made inert: beta = 0, no decay
+            const bool valid = tid < nt;
+            sm.lg[tid] = valid ? neg_rate * softplus_f(b.ab[tid][head] + dtb) : 0.0f;
+            sm.beta[tid] = valid ? sigmoid_f(b.ab[tid][6 + head]) : 0.0f;
+        }
+        __syncthreads();
+        if (tid < 2 * TC) {
+            const int i = tid & (TC - 1);
+            if (tid < TC) sm.iq[i] = (1.0f / sqrtf(sm.part[i][0] + sm.part[i][1] + 1e-6f)) * 0.125f;
+            else sm.ik[i] = 1.0f / sqrtf(sm.part[i][2] + sm.part[i][3] + 1e-6f);
+        }
+        if (warp == 2) {                                  // inclusive prefix sum of the log decays over the chunk
+            float c = lane < TC ? sm.lg[lane] : 0.0f;
+#pragma unroll
+            for (int o = 1; o < TC; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, c, o);
+                if (lane >= o) c += up;
+            }
+            const float last = __shfl_sync(0xffffffffu, c, TC - 1);
+            if (lane < TC) {
+                sm.cum[lane] = c;
+                sm.eg[lane] = expf(c);
+                sm.dj[lane] = expf(last - c);
+            }
+        }
+        __syncthreads();
+        // ---------------------------------------------------------------- bf16 operand tiles, norms applied
+        if (is_k) {
+            uint32_t packed[TC / 2];
+#pragma unroll
+            for (int i = 0; i < TC; i += 2) {
+                const float a = b.k[i][ch] * sm.ik[i], c = b.k[i + 1][ch] * sm.ik[i + 1];
+                sm.kb[i][ch] = __float2bfloat16_rn(a);
+                sm.kb[i + 1][ch] = __float2bfloat16_rn(c);
+                packed[i / 2] = pack_bf16(a, c);
+            }
+            uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.kt[ch][0]);
+#pragma unroll
+            for (int i = 0; i < TC / 2; ++i) dst[i] = packed[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < TC; ++i) sm.qb[i][ch] = __float2bfloat16_rn(b.q[i][ch] * sm.iq[i]);
+        }
+        __syncthreads();
+        const uint32_t* kbw = reinterpret_cast<const uint32_t*>(&sm.kb[0][0]);   // 36 words per token row
+        const uint32_t* qbw = reinterpret_cast<const uint32_t*>(&sm.qb[0][0]);
+        // ---------------------------------------------------------------- warp 0: L and T2; warp 1: masked Q K^T
+        if (warp < 2) {
+            const uint32_t* xa = warp == 0 ? kbw : qbw;
+            float acc[2][4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[ni][e] = 0.0f;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const uint32_t a[4] = {xa[g * 36 + 8 * p + t], xa[(g + 8) * 36 + 8 * p + t], xa[g * 36 + 8 * p + t + 4],
+                                       xa[(g + 8) * 36 + 8 * p + t + 4]};
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni)
+                    mma16816(acc[ni], a, kbw[(8 * ni + g) * 36 + 8 * p + t], kbw[(8 * ni + g) * 36 + 8 * p + t + 4]);
+            }
+            // acc[ni][0,1]: row i = g, columns j = 8 ni + 2t, + 1;  acc[ni][2,3]: row i = g + 8
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = g + (e >> 1) * 8, j = 8 * ni + 2 * t + (e & 1);
+                    const bool keep = warp == 0 ? j < i : j <= i;
+                    const float dec = expf(keep ? sm.cum[i] - sm.cum[j] : 0.0f);
+                    float v = keep ? dec * acc[ni][e] : 0.0f;
+                    if (warp == 0) v *= sm.beta[i];
+                    acc[ni][e] = v;
+                }
+            if (warp == 0) {
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sm.lf[g + (e >> 1) * 8][8 * ni + 2 * t + (e & 1)] = acc[ni][e];
+                __syncwarp();
+                if (lane < TC) {                          // column `lane` of (I + L)^-1 by forward substitution
+                    float x[TC];
+#pragma unroll
+                    for (int i = 0; i < TC; ++i) {
+                        float s = i == lane ? 1.0f : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < i; ++j) s = fmaf(-sm.lf[i][j], x[j], s);
+                        x[i] = s;
+                    }
+                    const float bc = sm.beta[lane];
+#pragma unroll
+                    for (int i = 0; i < TC; ++i) sm.t2[i][lane] = __float2bfloat16_rn(x[i] * bc);
+                }
+            } else {
+                uint32_t* mw = reinterpret_cast<uint32_t*>(&sm.mq[0][0]);        // 12 words per row
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) {
+                    mw[g * 12 + 4 * ni + t] = pack_bf16(acc[ni][0], acc[ni][1]);
+                    mw[(g + 8) * 12 + 4 * ni + t] = pack_bf16(acc[ni][2], acc[ni][3]);
+                }
+            }
+        }
+        // ---------------------------------------------------------------- R^T = S0^T K^T and (Q S0)^T, all warps
+        float R[2][2][4], QS[2][2][4];
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { R[mi][ni][e] = 0.0f; QS[mi][ni][e] = 0.0f; }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            uint32_t bk[2][2], bq[2][2];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+                bk[ni][0] = kbw[(8 * ni + g) * 36 + 8 * p + t]; bk[ni][1] = kbw[(8 * ni + g) * 36 + 8 * p + t + 4];
+                bq[ni][0] = qbw[(8 * ni + g) * 36 + 8 * p + t]; bq[ni][1] = qbw[(8 * ni + g) * 36 + 8 * p + t + 4];
+            }
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi) {
+                // keys 16p .. 16p+15 of the state as an A fragment: two adjacent accumulator tiles, rounded to bf16
+                const uint32_t sa[4] = {pack_bf16(S[mi][2 * p][0], S[mi][2 * p][1]), pack_bf16(S[mi][2 * p][2], S[mi][2 * p][3]),
+                                        pack_bf16(S[mi][2 * p + 1][0], S[mi][2 * p + 1][1]),
+                                        pack_bf16(S[mi][2 * p + 1][2], S[mi][2 * p + 1][3])};
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) {
+                    mma16816(R[mi][ni], sa, bk[ni][0], bk[ni][1]);
+                    mma16816(QS[mi][ni], sa, bq[ni][0], bq[ni][1]);
+                }
+            }
+        }
+        __syncthreads();                                  // T2 and the masked Q K^T tile are in shared memory
+        // ---------------------------------------------------------------- U^T = (V - diag(e) R)^T T2^T
+        const uint32_t* t2w = reinterpret_cast<const uint32_t*>(&sm.t2[0][0]);   // 12 words per row
+        const uint32_t* mqw = reinterpret_cast<const uint32_t*>(&sm.mq[0][0]);
+        const uint32_t* ktw = reinterpret_cast<const uint32_t*>(&sm.kt[0][0]);
+        float eg2[2][2], dj2[2][2];                       // exp(c), exp(c_last - c) of this lane's tokens 8 ni + 2t, + 1
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                eg2[ni][e] = sm.eg[8 * ni + 2 * t + e];
+                dj2[ni][e] = sm.dj[8 * ni + 2 * t + e];
+            }
+        uint32_t bt[2][2], bm[2][2];
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni) {
+            bt[ni][0] = t2w[(8 * ni + g) * 12 + t]; bt[ni][1] = t2w[(8 * ni + g) * 12 + t + 4];
+            bm[ni][0] = mqw[(8 * ni + g) * 12 + t]; bm[ni][1] = mqw[(8 * ni + g) * 12 + t + 4];
+        }
+        float* otile = &b.v[0][0];                        // raw v is consumed: the tile now collects o[token][value]
+        uint32_t da[2][4];                                // decay-scaled U^T as A fragments, for the state update
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+            const int r0 = dvb + 16 * mi + g, r1 = r0 + 8;
+            uint32_t va[4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+                const float2 v0 = *reinterpret_cast<const float2*>(&sm.vt[r0][8 * ni + 2 * t]);
+                const float2 v1 = *reinterpret_cast<const float2*>(&sm.vt[r1][8 * ni + 2 * t]);
+                va[2 * ni] = pack_bf16(v0.x - eg2[ni][0] * R[mi][ni][0], v0.y - eg2[ni][1] * R[mi][ni][1]);
+                va[2 * ni + 1] = pack_bf16(v1.x - eg2[ni][0] * R[mi][ni][2], v1.y - eg2[ni][1] * R[mi][ni][3]);
+            }
+            float U[2][4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) U[ni][e] = 0.0f;
+                mma16816(U[ni], va, bt[ni][0], bt[ni][1]);
+            }
+            uint32_t ua[4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+                ua[2 * ni] = pack_bf16(U[ni][0], U[ni][1]);
+                ua[2 * ni + 1] = pack_bf16(U[ni][2], U[ni][3]);
+                da[mi][2 * ni] = pack_bf16(U[ni][0] * dj2[ni][0], U[ni][1] * dj2[ni][1]);
+                da[mi][2 * ni + 1] = pack_bf16(U[ni][2] * dj2[ni][0], U[ni][3] * dj2[ni][1]);
+            }
+            // O^T = U^T M^T + diag(e) (Q S0)^T
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+                float O[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                mma16816(O, ua, bm[ni][0], bm[ni][1]);
+                const int tok = 8 * ni + 2 * t;
+                otile[tok * kDV + r0] = O[0] + eg2[ni][0] * QS[mi][ni][0];
+                otile[(tok + 1) * kDV + r0] = O[1] + eg2[ni][1] * QS[mi][ni][1];
+                otile[tok * kDV + r1] = O[2] + eg2[ni][0] * QS[mi][ni][2];
+                otile[(tok + 1) * kDV + r1] = O[3] + eg2[ni][1] * QS[mi][ni][3];
+            }
+        }
+        // ---------------------------------------------------------------- S^T <- e_last S^T + (diag(d) U)^T K
+        {
+            const float elast = sm.eg[TC - 1];
+#pragma unroll
+            for (int nj = 0; nj < 8; ++nj) {
+                const uint32_t b0 = ktw[(8 * nj + g) * 12 + t], b1 = ktw[(8 * nj + g) * 12 + t + 4];
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) S[mi][nj][e] *= elast;
+                    mma16816(S[mi][nj], da[mi], b0, b1);
+                }
+            }
+        }
+        __syncthreads();
+        // ---------------------------------------------------------------- post: gated RMSNorm, warp per token
+        if (!tma::mbar_wait_bounded(gbar, uint32_t(chunk) & 1u, WAIT_POLLS)) {
+            if (tid == 0) atomicCAS(&g_scan_mma_status, 0, 2);
+            return;
+        }
+        for (int i = warp; i < nt; i += 4) {
+            const long long row = (long long)row_base + t0 + i;
+            const float4 o = *reinterpret_cast<const float4*>(&otile[i * kDV + lane * 4]);
+            const float4 gt = *reinterpret_cast<const float4*>(&sm.g[i][lane * 4]);
+            const float4 w = *reinterpret_cast<const float4*>(o_norm_w + lane * 4);
+            const float ss = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
+            const float rstd = 1.0f / sqrtf(ss / float(kDV) + 1e-6f);
+            store_quad<T>(on + row * kVD + head * kDV + lane * 4, ((o.x * rstd) * w.x) * silu_fast(gt.x),
+                          ((o.y * rstd) * w.y) * silu_fast(gt.y), ((o.z * rstd) * w.z) * silu_fast(gt.z),
+                          ((o.w * rstd) * w.w) * silu_fast(gt.w));
+        }
+        __syncthreads();                                  // the raw buffer, the gate tile and the operand tiles are free again
+    }
+}
+
+}  // namespace
+
+int launch_gdn_scan_mma(const float* P, const float* conv_w, const float* conv_b, const float* a_log, const float* dt_bias,
+                        const float* o_norm_w, void* on, int on_dtype, int B, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (reinterpret_cast<uintptr_t>(P) & 15) return int(cudaErrorInvalidValue);
+    MmaMaps maps;
+    const long long rows = (long long)B * kTok;
+    if (!tma::make_map_f32(&maps.qk, P, rows, kGLD, kGLD, TC, kDK) || !tma::make_map_f32(&maps.vg, P, rows, kGLD, kGLD, TC, kDV) ||
+        !tma::make_map_f32(&maps.ab, P, rows, kGLD, kGLD, TC, 16))
+        return int(cudaErrorNotSupported);
+    const unsigned grid = unsigned(B) * kHeads;
+    if (on_dtype == DT_BF16) {
+        const cudaError_t e = cudaFuncSetAttribute(gdn_scan_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM_BYTES);
+        if (e != cudaSuccess) return int(e);
+        gdn_scan_mma_kernel<__nv_bfloat16><<<grid, 128, MMA_SMEM_BYTES, stream>>>(maps, conv_w, conv_b, a_log, dt_bias, o_norm_w,
+                                                                                   static_cast<__nv_bfloat16*>(on));
+    } else if (on_dtype == DT_F16) {
+        const cudaError_t e = cudaFuncSetAttribute(gdn_scan_mma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM_BYTES);
+        if (e != cudaSuccess) return int(e);
+        gdn_scan_mma_kernel<__half><<<grid, 128, MMA_SMEM_BYTES, stream>>>(maps, conv_w, conv_b, a_log, dt_bias, o_norm_w,
+                                                                           static_cast<__half*>(on));
+    } else {
+        return int(cudaErrorInvalidValue);
+    }
+    return int(cudaGetLastError());
+}
+
+int gdn_scan_mma_status(int* status_out) {
+    int v = 0;
+    const cudaError_t e = cudaMemcpyFromSymbol(&v, g_scan_mma_status, sizeof(int));
+    if (status_out) *status_out = v;
+    return int(e);
+}
+
+}  // namespace sb

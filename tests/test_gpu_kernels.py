@@ -260,7 +260,8 @@ def test_gdn_scan_matches_oracle(L, weight_files, recipe, stage, B):
     ref = (tr["t.o_gated"] * ow.astype(np.float64)).reshape(B * 321, 768)
     assert np.all(w[f"{m}.o_norm.weight"] == 1.0)
     Pd, d_cw, d_cb, d_al, d_dt, d_ow = dev(P), dev(conv_w), dev(conv_b), dev(w[f"{m}.A_log"]), dev(w[f"{m}.dt_bias"]), dev(ow)
-    for code, tdt, tol in ((0, torch.float32, None), (1, torch.bfloat16, 8e-3), (2, torch.float16, 1e-3)):
+    # 16-bit outputs select the chunked tensor-core form (bf16 operands, fp32 state): judged by the 16-bit modes' budget
+    for code, tdt, tol in ((0, torch.float32, None), (1, torch.bfloat16, 2e-2), (2, torch.float16, 2e-2)):
         on = torch.zeros((B * 321, 768), device="cuda", dtype=tdt)
         ok(L.shvk_gdn_scan(Pd.data_ptr(), d_cw.data_ptr(), d_cb.data_ptr(), d_al.data_ptr(), d_dt.data_ptr(),
                            d_ow.data_ptr(), on.data_ptr(), code, B, stream_ptr()))
@@ -269,7 +270,10 @@ def test_gdn_scan_matches_oracle(L, weight_files, recipe, stage, B):
         if tol is None:
             assert np.abs(got - ref).max() < 1e-4 * max(1.0, np.abs(ref).max())
         else:
-            assert rel_err(got, ref) < tol
+            err = rel_err(got, ref)
+            rms = float(np.sqrt(((got - ref) ** 2).mean() / (ref ** 2).mean()))
+            print(f"gdn_scan {recipe} {stage} dtype {code}: max-rel {err:.3e} rms-rel {rms:.3e}")
+            assert err < tol and rms < tol
 
 
 # ---------------------------------------------------------------------------------------------- SISA attention + head
