@@ -15,7 +15,9 @@
 // accumulator fragments of mma.sync.m16n8k16, and the accumulator layout of one product (rows = values, columns =
 // tokens) is exactly the A-operand layout of the next.  Only K, Q, T2 and M pass through shared memory (bf16 tiles
 // written once per chunk, read as B fragments), and the 16 x 16 triangular inverse is a 16-lane forward substitution
-// in fp32.  Operands are rounded to bf16, the state and all accumulation stay fp32: the error against the exact
+// in fp32.  k and q enter the tiles un-normalised; their L2 norms are the diagonals of the Gram products K K^T and
+// Q Q^T and are applied as per-token scalars (rows of L and M, the decay factors of R, Q S0 and the state update).
+// Operands are rounded to bf16, the state and all accumulation stay fp32: the error against the exact
 // recurrence is a few 1e-3 relative on the delta-rule output (measured against the oracle in the tests), inside the
 // 2e-2 budget of the 16-bit modes.  The exact tier keeps the per-token fp32 kernel of gdn_scan.cu.
 //
@@ -40,8 +42,8 @@ constexpr int VT_PITCH = 20;                 // floats per row of V^T
 __device__ int g_scan_mma_status = 0;
 
 struct RawBuf {                              // TMA targets, one chunk
-    float q[TC][kDK];                        // raw q -> silu(conv q), fp32, un-normalised
-    float k[TC][kDK];
+    float q[TC][kDK];                        // raw q projection
+    float k[TC][kDK];                        // raw k projection
     float v[TC][kDV];                        // raw v; after prep reused as the chunk's output tile o[token][value]
     float ab[TC][16];
 };
@@ -51,14 +53,13 @@ struct MmaSmem {
     RawBuf raw[2];
     float g[TC][kDV];                        // output gate tile of the current chunk (single buffer)
     float vt[kDV][VT_PITCH];                 // silu(conv v), transposed: [value][token]
-    __nv_bfloat16 kb[TC][KB_PITCH];          // normalised k, [token][key]
-    __nv_bfloat16 qb[TC][KB_PITCH];          // normalised q * 0.125
-    __nv_bfloat16 kt[kDK][KT_PITCH];         // normalised k, [key][token]
+    __nv_bfloat16 kb[TC][KB_PITCH];          // silu(conv k), un-normalised, [token][key]
+    __nv_bfloat16 qb[TC][KB_PITCH];          // silu(conv q), un-normalised
+    __nv_bfloat16 kt[kDK][KT_PITCH];         // the k tile transposed: [key][token]
     __nv_bfloat16 t2[TC][KT_PITCH];          // (I + L)^-1 diag(beta)
     __nv_bfloat16 mq[TC][KT_PITCH];          // decay-masked Q K^T
     float lf[TC][TC + 1];                    // L, fp32, for the triangular inverse
-    float part[TC][4];
-    float iq[TC], ik[TC], lg[TC], beta[TC];  // 0.125/|q|, 1/|k|, log decay, beta (0 beyond the sequence end)
+    float iq[TC], ik[TC], lg[TC], beta[TC];  // 0.125/|q|, 1/|k|, warp 1's copy of 1/|k|, beta (0 beyond the sequence end)
     float cum[TC], eg[TC], dj[TC];           // c_i, exp(c_i), exp(c_last - c_i)
     unsigned long long full[2], gfull;       // mbarriers
 };
@@ -70,7 +71,14 @@ struct MmaMaps {
     CUtensorMap ab;    // box 16 x 16
 };
 
-__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+// x * sigmoid(x) = 0.5 x (1 + tanh(x / 2)) with the hardware tanh: absolute error ~5e-4 |x|, below the bf16 rounding
+// that follows every use in this kernel
+__device__ __forceinline__ float silu_tanh(float x) {
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * x));
+    const float hx = 0.5f * x;
+    return fmaf(hx, th, hx);
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -151,40 +159,46 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             if (tid == 0) atomicCAS(&g_scan_mma_status, 0, 1);
             return;                                       // every thread times out on the same barrier and leaves
         }
-        // ---------------------------------------------------------------- prep: conv + SiLU, sums of squares, gates
-#pragma unroll 4
-        for (int i = 0; i < TC; ++i) {
-            float* pqk = is_k ? &b.k[i][ch] : &b.q[i][ch];
-            const float raw_qk = *pqk, raw_v = b.v[i][tid];
-            float acc = wqk.x * x3;
-            acc = fmaf(wqk.y, x2, acc);
-            acc = fmaf(wqk.z, x1, acc);
-            acc = fmaf(wqk.w, raw_qk, acc);
-            const float val = silu_fast(acc + bqk);
-            *pqk = val;
-            x3 = x2; x2 = x1; x1 = raw_qk;
-            float accv = wv.x * y3;
-            accv = fmaf(wv.y, y2, accv);
-            accv = fmaf(wv.z, y1, accv);
-            accv = fmaf(wv.w, raw_v, accv);
-            sm.vt[tid][i] = silu_fast(accv + bv);
-            y3 = y2; y2 = y1; y1 = raw_v;
-            const float ss = warp_sum(val * val);
-            if (lane == 0) sm.part[i][warp] = ss;
+        // ---------------------------------------------------------------- prep: conv + SiLU -> bf16 operand tiles, gates
+        // k and q go into the tiles un-normalised; their norms come out of the Gram products below and enter every
+        // later formula as per-token scalars.
+        {
+            uint32_t ktp[TC / 2];                         // this key's row of K^T, two tokens per word
+            float prev = 0.0f;
+#pragma unroll
+            for (int i = 0; i < TC; ++i) {
+                const float raw_qk = is_k ? b.k[i][ch] : b.q[i][ch], raw_v = b.v[i][tid];
+                float acc = wqk.x * x3;
+                acc = fmaf(wqk.y, x2, acc);
+                acc = fmaf(wqk.z, x1, acc);
+                acc = fmaf(wqk.w, raw_qk, acc);
+                const float val = silu_tanh(acc + bqk);
+                x3 = x2; x2 = x1; x1 = raw_qk;
+                if (is_k) {
+                    sm.kb[i][ch] = __float2bfloat16_rn(val);
+                    if (i & 1) ktp[i >> 1] = pack_bf16(prev, val);
+                    prev = val;
+                } else {
+                    sm.qb[i][ch] = __float2bfloat16_rn(val);
+                }
+                float accv = wv.x * y3;
+                accv = fmaf(wv.y, y2, accv);
+                accv = fmaf(wv.z, y1, accv);
+                accv = fmaf(wv.w, raw_v, accv);
+                sm.vt[tid][i] = silu_tanh(accv + bv);
+                y3 = y2; y2 = y1; y1 = raw_v;
+            }
+            if (is_k) {
+                uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.kt[ch][0]);
+#pragma unroll
+                for (int i = 0; i < TC / 2; ++i) dst[i] = ktp[i];
+            }
         }
-        if (tid < TC) {                                   // tokens past the sequence end are made inert: beta = 0, no decay
-            const bool valid = tid < nt;
-            sm.lg[tid] = valid ? neg_rate * softplus_f(b.ab[tid][head] + dtb) : 0.0f;
-            sm.beta[tid] = valid ? sigmoid_f(b.ab[tid][6 + head]) : 0.0f;
-        }
-        __syncthreads();
-        if (tid < 2 * TC) {
-            const int i = tid & (TC - 1);
-            if (tid < TC) sm.iq[i] = (1.0f / sqrtf(sm.part[i][0] + sm.part[i][1] + 1e-6f)) * 0.125f;
-            else sm.ik[i] = 1.0f / sqrtf(sm.part[i][2] + sm.part[i][3] + 1e-6f);
-        }
-        if (warp == 2) {                                  // inclusive prefix sum of the log decays over the chunk
-            float c = lane < TC ? sm.lg[lane] : 0.0f;
+        if (warp == 3) {                                  // gates and the inclusive prefix sum of the log decays
+            // tokens past the sequence end are made inert: beta = 0, no decay
+            const bool valid = lane < nt;
+            float c = valid ? neg_rate * softplus_f(b.ab[lane & (TC - 1)][head] + dtb) : 0.0f;
+            const float bt_ = valid ? sigmoid_f(b.ab[lane & (TC - 1)][6 + head]) : 0.0f;
 #pragma unroll
             for (int o = 1; o < TC; o <<= 1) {
                 const float up = __shfl_up_sync(0xffffffffu, c, o);
@@ -192,49 +206,56 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             }
             const float last = __shfl_sync(0xffffffffu, c, TC - 1);
             if (lane < TC) {
+                sm.beta[lane] = bt_;
                 sm.cum[lane] = c;
                 sm.eg[lane] = expf(c);
                 sm.dj[lane] = expf(last - c);
             }
         }
         __syncthreads();
-        // ---------------------------------------------------------------- bf16 operand tiles, norms applied
-        if (is_k) {
-            uint32_t packed[TC / 2];
-#pragma unroll
-            for (int i = 0; i < TC; i += 2) {
-                const float a = b.k[i][ch] * sm.ik[i], c = b.k[i + 1][ch] * sm.ik[i + 1];
-                sm.kb[i][ch] = __float2bfloat16_rn(a);
-                sm.kb[i + 1][ch] = __float2bfloat16_rn(c);
-                packed[i / 2] = pack_bf16(a, c);
-            }
-            uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.kt[ch][0]);
-#pragma unroll
-            for (int i = 0; i < TC / 2; ++i) dst[i] = packed[i];
-        } else {
-#pragma unroll
-            for (int i = 0; i < TC; ++i) sm.qb[i][ch] = __float2bfloat16_rn(b.q[i][ch] * sm.iq[i]);
-        }
-        __syncthreads();
         const uint32_t* kbw = reinterpret_cast<const uint32_t*>(&sm.kb[0][0]);   // 36 words per token row
         const uint32_t* qbw = reinterpret_cast<const uint32_t*>(&sm.qb[0][0]);
-        // ---------------------------------------------------------------- warp 0: L and T2; warp 1: masked Q K^T
+        // ---------------------------------------------------------------- warp 0: norms of k, L, T2; warp 1: norms, masked Q K^T
         if (warp < 2) {
-            const uint32_t* xa = warp == 0 ? kbw : qbw;
-            float acc[2][4];
+            // Gram products over the 64 keys: warp 0 K K^T; warp 1 Q K^T, and the diagonals of Q Q^T and K K^T
+            float acc[2][4], dq[2][4], dk[2][4];
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) acc[ni][e] = 0.0f;
+                for (int e = 0; e < 4; ++e) { acc[ni][e] = 0.0f; dq[ni][e] = 0.0f; dk[ni][e] = 0.0f; }
+            const uint32_t* xa = warp == 0 ? kbw : qbw;
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
                 const uint32_t a[4] = {xa[g * 36 + 8 * p + t], xa[(g + 8) * 36 + 8 * p + t], xa[g * 36 + 8 * p + t + 4],
                                        xa[(g + 8) * 36 + 8 * p + t + 4]};
 #pragma unroll
-                for (int ni = 0; ni < 2; ++ni)
-                    mma16816(acc[ni], a, kbw[(8 * ni + g) * 36 + 8 * p + t], kbw[(8 * ni + g) * 36 + 8 * p + t + 4]);
+                for (int ni = 0; ni < 2; ++ni) {
+                    const uint32_t k0 = kbw[(8 * ni + g) * 36 + 8 * p + t], k1 = kbw[(8 * ni + g) * 36 + 8 * p + t + 4];
+                    mma16816(acc[ni], a, k0, k1);
+                    if (warp == 1) {
+                        mma16816(dq[ni], a, qbw[(8 * ni + g) * 36 + 8 * p + t], qbw[(8 * ni + g) * 36 + 8 * p + t + 4]);
+                        const uint32_t ka[4] = {kbw[g * 36 + 8 * p + t], kbw[(g + 8) * 36 + 8 * p + t], kbw[g * 36 + 8 * p + t + 4],
+                                                kbw[(g + 8) * 36 + 8 * p + t + 4]};
+                        mma16816(dk[ni], ka, k0, k1);
+                    }
+                }
             }
+            // diagonal entries: row g sits in tile 0 at column 2t + e == g, row g + 8 in tile 1 at the same lane / slot
+            if (t == (g >> 1)) {
+                const int e = g & 1;
+                if (warp == 0) {
+                    sm.ik[g] = 1.0f / sqrtf(acc[0][e] + 1e-6f);
+                    sm.ik[g + 8] = 1.0f / sqrtf(acc[1][2 + e] + 1e-6f);
+                } else {
+                    sm.iq[g] = (1.0f / sqrtf(dq[0][e] + 1e-6f)) * 0.125f;
+                    sm.iq[g + 8] = (1.0f / sqrtf(dq[1][2 + e] + 1e-6f)) * 0.125f;
+                    sm.lg[g] = 1.0f / sqrtf(dk[0][e] + 1e-6f);            // warp 1's own copy of 1/|k| (sm.lg is free here)
+                    sm.lg[g + 8] = 1.0f / sqrtf(dk[1][2 + e] + 1e-6f);
+                }
+            }
+            __syncwarp();
             // acc[ni][0,1]: row i = g, columns j = 8 ni + 2t, + 1;  acc[ni][2,3]: row i = g + 8
+            const float* ikv = warp == 0 ? sm.ik : sm.lg;
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni)
 #pragma unroll
@@ -242,9 +263,8 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                     const int i = g + (e >> 1) * 8, j = 8 * ni + 2 * t + (e & 1);
                     const bool keep = warp == 0 ? j < i : j <= i;
                     const float dec = expf(keep ? sm.cum[i] - sm.cum[j] : 0.0f);
-                    float v = keep ? dec * acc[ni][e] : 0.0f;
-                    if (warp == 0) v *= sm.beta[i];
-                    acc[ni][e] = v;
+                    const float rowf = warp == 0 ? sm.beta[i] * ikv[i] : sm.iq[i];
+                    acc[ni][e] = keep ? dec * acc[ni][e] * rowf * ikv[j] : 0.0f;
                 }
             if (warp == 0) {
 #pragma unroll
@@ -308,13 +328,18 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         const uint32_t* t2w = reinterpret_cast<const uint32_t*>(&sm.t2[0][0]);   // 12 words per row
         const uint32_t* mqw = reinterpret_cast<const uint32_t*>(&sm.mq[0][0]);
         const uint32_t* ktw = reinterpret_cast<const uint32_t*>(&sm.kt[0][0]);
-        float eg2[2][2], dj2[2][2];                       // exp(c), exp(c_last - c) of this lane's tokens 8 ni + 2t, + 1
+        // per-token scalars of this lane's tokens 8 ni + 2t, + 1, with the norms folded in:
+        //   er = exp(c) / |k|  (R = K S0),  eq = exp(c) * 0.125 / |q|  (Q S0),  dj2 = exp(c_last - c) / |k|  (state update)
+        float er[2][2], eq[2][2], dj2[2][2];
 #pragma unroll
         for (int ni = 0; ni < 2; ++ni)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                eg2[ni][e] = sm.eg[8 * ni + 2 * t + e];
-                dj2[ni][e] = sm.dj[8 * ni + 2 * t + e];
+                const int tok = 8 * ni + 2 * t + e;
+                const float egv = sm.eg[tok], ikv = sm.ik[tok];
+                er[ni][e] = egv * ikv;
+                eq[ni][e] = egv * sm.iq[tok];
+                dj2[ni][e] = sm.dj[tok] * ikv;
             }
         uint32_t bt[2][2], bm[2][2];
 #pragma unroll
@@ -332,8 +357,8 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             for (int ni = 0; ni < 2; ++ni) {
                 const float2 v0 = *reinterpret_cast<const float2*>(&sm.vt[r0][8 * ni + 2 * t]);
                 const float2 v1 = *reinterpret_cast<const float2*>(&sm.vt[r1][8 * ni + 2 * t]);
-                va[2 * ni] = pack_bf16(v0.x - eg2[ni][0] * R[mi][ni][0], v0.y - eg2[ni][1] * R[mi][ni][1]);
-                va[2 * ni + 1] = pack_bf16(v1.x - eg2[ni][0] * R[mi][ni][2], v1.y - eg2[ni][1] * R[mi][ni][3]);
+                va[2 * ni] = pack_bf16(v0.x - er[ni][0] * R[mi][ni][0], v0.y - er[ni][1] * R[mi][ni][1]);
+                va[2 * ni + 1] = pack_bf16(v1.x - er[ni][0] * R[mi][ni][2], v1.y - er[ni][1] * R[mi][ni][3]);
             }
             float U[2][4];
 #pragma unroll
@@ -356,10 +381,10 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 float O[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 mma16816(O, ua, bm[ni][0], bm[ni][1]);
                 const int tok = 8 * ni + 2 * t;
-                otile[tok * kDV + r0] = O[0] + eg2[ni][0] * QS[mi][ni][0];
-                otile[(tok + 1) * kDV + r0] = O[1] + eg2[ni][1] * QS[mi][ni][1];
-                otile[tok * kDV + r1] = O[2] + eg2[ni][0] * QS[mi][ni][2];
-                otile[(tok + 1) * kDV + r1] = O[3] + eg2[ni][1] * QS[mi][ni][3];
+                otile[tok * kDV + r0] = O[0] + eq[ni][0] * QS[mi][ni][0];
+                otile[(tok + 1) * kDV + r0] = O[1] + eq[ni][1] * QS[mi][ni][1];
+                otile[tok * kDV + r1] = O[2] + eq[ni][0] * QS[mi][ni][2];
+                otile[(tok + 1) * kDV + r1] = O[3] + eq[ni][1] * QS[mi][ni][3];
             }
         }
         // ---------------------------------------------------------------- S^T <- e_last S^T + (diag(d) U)^T K
@@ -389,9 +414,9 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             const float4 w = *reinterpret_cast<const float4*>(o_norm_w + lane * 4);
             const float ss = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
             const float rstd = 1.0f / sqrtf(ss / float(kDV) + 1e-6f);
-            store_quad<T>(on + row * kVD + head * kDV + lane * 4, ((o.x * rstd) * w.x) * silu_fast(gt.x),
-                          ((o.y * rstd) * w.y) * silu_fast(gt.y), ((o.z * rstd) * w.z) * silu_fast(gt.z),
-                          ((o.w * rstd) * w.w) * silu_fast(gt.w));
+            store_quad<T>(on + row * kVD + head * kDV + lane * 4, ((o.x * rstd) * w.x) * silu_tanh(gt.x),
+                          ((o.y * rstd) * w.y) * silu_tanh(gt.y), ((o.z * rstd) * w.z) * silu_tanh(gt.z),
+                          ((o.w * rstd) * w.w) * silu_tanh(gt.w));
         }
         __syncthreads();                                  // the raw buffer, the gate tile and the operand tiles are free again
     }

@@ -17,7 +17,7 @@ namespace {
 
 constexpr int NT = 256, NCOL = 18, PER_LANE = 11;   // 32 * 11 = 352 >= 321
 
-__global__ void __launch_bounds__(NT)
+__global__ void __launch_bounds__(NT, 3)
 sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, const float* __restrict__ lambda_raw,
                  float* __restrict__ Y) {
     const int clip = blockIdx.x / kHeads, head = blockIdx.x % kHeads;
@@ -30,11 +30,18 @@ sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, cons
     __shared__ float red[NT / 32];
     __shared__ float ypart[4][kDK];
 
-    for (int i = tid; i < kTok * NCOL; i += NT) {
-        const int t = i / NCOL, c = i - t * NCOL;
-        const int col = c == 0 ? kSAlpha + head : c == 1 ? kSForget + head : kSTheta + head * kPairs + (c - 2);
-        const float x = S0[(long long)t * kSLD + col];
-        term[c][t] = c == 0 ? -softplus_f(x) : c == 1 ? logsigmoid_f(x) : x;
+    // per-token terms: theta[16] of this head is one 64-byte run, alpha and forget are single floats
+    for (int tk = tid; tk < kTok; tk += NT) {
+        const float* row = S0 + (long long)tk * kSLD;
+        const float4* th = reinterpret_cast<const float4*>(row + kSTheta + head * kPairs);
+        const float4 t0 = th[0], t1 = th[1], t2 = th[2], t3 = th[3];
+        const float al = row[kSAlpha + head], fg = row[kSForget + head];
+        term[0][tk] = -softplus_f(al);
+        term[1][tk] = logsigmoid_f(fg);
+        term[2][tk] = t0.x; term[3][tk] = t0.y; term[4][tk] = t0.z; term[5][tk] = t0.w;
+        term[6][tk] = t1.x; term[7][tk] = t1.y; term[8][tk] = t1.z; term[9][tk] = t1.w;
+        term[10][tk] = t2.x; term[11][tk] = t2.y; term[12][tk] = t2.z; term[13][tk] = t2.w;
+        term[14][tk] = t3.x; term[15][tk] = t3.y; term[16][tk] = t3.z; term[17][tk] = t3.w;
     }
     if (tid < kDK) sq[tid] = QC[(long long)clip * kSQN + kSQ + head * kDK + tid];
     else if (tid < kDK + kState) sc[tid - kDK] = QC[(long long)clip * kSQN + kSC + head * kState + (tid - kDK)];
@@ -129,6 +136,7 @@ sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, cons
     const float inv = 1.0f / sum;
     const int j = tid & (kDK - 1), grp = tid >> 6;
     float y = 0.0f;
+#pragma unroll 8
     for (int t = grp; t < kTok; t += 4) y = fmaf(score[t] * inv, S0[(long long)t * kSLD + kSV + head * kDK + j], y);
     ypart[grp][j] = y;
     __syncthreads();
