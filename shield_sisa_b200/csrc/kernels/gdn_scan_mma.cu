@@ -114,6 +114,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
     const float bv = conv_b[v_w];
     float x1 = 0.0f, x2 = 0.0f, x3 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;   // zero history = causal padding
     const float neg_rate = -expf(a_log[head]), dtb = dt_bias[head];
+    const float4 onw = *reinterpret_cast<const float4*>(o_norm_w + lane * 4);   // gated-norm weights of this lane's columns
 
     // S^T slice of this warp as accumulator fragments: S[mi][nj][.] = values dvb + 16 mi + {g, g + 8}, keys 8 nj + 2t, + 1
     float S[2][8][4];
@@ -276,10 +277,17 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                     float x[TC];
 #pragma unroll
                     for (int i = 0; i < TC; ++i) {
-                        float s = i == lane ? 1.0f : 0.0f;
+                        // four partial sums: the dependent chain per row is i / 4 long instead of i
+                        float s0 = i == lane ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-                        for (int j = 0; j < i; ++j) s = fmaf(-sm.lf[i][j], x[j], s);
-                        x[i] = s;
+                        for (int j = 0; j < i; ++j) {
+                            const float l = sm.lf[i][j];
+                            if ((j & 3) == 0) s0 = fmaf(-l, x[j], s0);
+                            else if ((j & 3) == 1) s1 = fmaf(-l, x[j], s1);
+                            else if ((j & 3) == 2) s2 = fmaf(-l, x[j], s2);
+                            else s3 = fmaf(-l, x[j], s3);
+                        }
+                        x[i] = (s0 + s1) + (s2 + s3);
                     }
                     const float bc = sm.beta[lane];
 #pragma unroll
@@ -411,7 +419,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             const long long row = (long long)row_base + t0 + i;
             const float4 o = *reinterpret_cast<const float4*>(&otile[i * kDV + lane * 4]);
             const float4 gt = *reinterpret_cast<const float4*>(&sm.g[i][lane * 4]);
-            const float4 w = *reinterpret_cast<const float4*>(o_norm_w + lane * 4);
+            const float4 w = onw;
             const float ss = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
             const float rstd = 1.0f / sqrtf(ss / float(kDV) + 1e-6f);
             store_quad<T>(on + row * kVD + head * kDV + lane * 4, ((o.x * rstd) * w.x) * silu_tanh(gt.x),

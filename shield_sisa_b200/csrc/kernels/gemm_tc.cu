@@ -32,14 +32,19 @@
 namespace sb {
 namespace {
 
-constexpr int TILE_M = 128, TILE_K = 64, MAX_BN = 240, ACC_COLS = 256, STAGES = 3, EPI_WARPS = 8;
-constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
+constexpr int TILE_M = 128, TILE_K = 64, MAX_BN = 240, ACC_COLS = 256;
 constexpr int A_BYTES = TILE_M * TILE_K * 2, B_BYTES = MAX_BN * TILE_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_TILE = 32 * 128;                               // 32 rows x 128 bytes
-constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_TILE;              // two tiles per epilogue warp
-constexpr int NUM_BARS = 2 * STAGES + 4 + 2 * EPI_WARPS;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 256 /* barriers */ + 1024 /* alignment slack */;
-static_assert(STAGE_BYTES % 1024 == 0 && NUM_BARS * 8 <= 256, "swizzled tiles need 1024-byte alignment");
+constexpr int BAR_BYTES = 512;
+static_assert(STAGE_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+// Shape of one kernel variant: operand ring depth, epilogue warps (4 or 8), output tiles in flight per epilogue warp.
+template <int STAGES_, int EPI_WARPS_, int NBUF_> struct Shape {
+    static constexpr int STAGES = STAGES_, EPI_WARPS = EPI_WARPS_, NBUF = NBUF_;
+    static constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
+    static constexpr int EPI_BYTES = EPI_WARPS * NBUF * EPI_TILE;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024 /* alignment slack */;
+    static_assert((2 * STAGES + 4 + EPI_WARPS * NBUF) * 8 <= BAR_BYTES && SMEM_BYTES <= 232448, "shape does not fit");
+};
 constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of ~64 ns each before a wait gives up (about a quarter second)
 
 enum : int { EPI_PLAIN = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
@@ -215,12 +220,13 @@ __device__ __forceinline__ void stage_block(const TcParams& p, uint32_t tile, in
     }
 }
 
-template <typename T, int EPI>
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <typename T, int EPI, typename SH>
+__global__ void __launch_bounds__(SH::NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
+    constexpr int STAGES = SH::STAGES, EPI_WARPS = SH::EPI_WARPS, NBUF = SH::NBUF, EPI_BYTES = SH::EPI_BYTES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t epi_base = base + STAGES * STAGE_BYTES;       // 16 tiles of 4 KB, 1024-byte aligned
+    const uint32_t epi_base = base + STAGES * STAGE_BYTES;       // output tiles of 4 KB, 1024-byte aligned
     const uint32_t bars = epi_base + EPI_BYTES;                  // full[S], empty[S], acc_full[2], acc_empty[2], r[8][2]
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -229,13 +235,14 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto accf_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
     auto acce_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
-    auto r_bar = [&](int ew, int b) { return bars + 8u * (2 * STAGES + 4 + 2 * ew + b); };
+    auto r_bar = [&](int ew, int b) { return bars + 8u * (2 * STAGES + 4 + NBUF * ew + b); };
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), EPI_WARPS); }
-        for (int e = 0; e < EPI_WARPS; ++e) { mbar_init(r_bar(e, 0), 1); mbar_init(r_bar(e, 1), 1); }
+        for (int e = 0; e < EPI_WARPS; ++e)
+            for (int b = 0; b < NBUF; ++b) mbar_init(r_bar(e, b), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
@@ -304,13 +311,18 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         }
     } else {
         // ------------------------------------------------------------------------------------------ epilogue
+        constexpr int PER_QUAD = EPI_WARPS / 4;                      // warps sharing a TMEM quadrant take alternate blocks
         const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
         const int nblk = (p.BN + 31) >> 5;
-        const uint32_t tiles[2] = {epi_base + uint32_t(2 * ew) * EPI_TILE, epi_base + uint32_t(2 * ew + 1) * EPI_TILE};
-        const uint32_t rbars[2] = {r_bar(ew, 0), r_bar(ew, 1)};
+        uint32_t tiles[NBUF], rbars[NBUF], rphase[NBUF];
+#pragma unroll
+        for (int i = 0; i < NBUF; ++i) {
+            tiles[i] = epi_base + uint32_t(NBUF * ew + i) * EPI_TILE;
+            rbars[i] = r_bar(ew, i);
+            rphase[i] = 0u;
+        }
         const bool active = half < nblk && !(p.probe & 2);          // this warp has blocks to write
-        uint32_t rphase[2] = {0u, 0u};
-        uint32_t nb = 0;                                            // blocks done by this warp; tile buffer = nb & 1
+        uint32_t nb = 0;                                            // blocks done by this warp; tile buffer = nb % NBUF
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -338,24 +350,24 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             };
             // one block: (prefetch the next R), wait for R / for the tile buffer, stage, TMA store
             auto emit = [&](int blk, const uint32_t* r) -> bool {
-                const int b = int(nb & 1u);
+                const int b = int(nb % uint32_t(NBUF)), bn_ = int((nb + 1u) % uint32_t(NBUF));
                 const int c = blk << 5;
                 const bool full = p.BN - c >= 32;
                 const int n = nt * p.BN + c;
                 if constexpr (EPI == EPI_RESID) {
                     if (lane == 0) {
                         long long ntile = tile;
-                        int nblk2 = blk + 2;
+                        int nblk2 = blk + PER_QUAD;
                         if (nblk2 >= nblk) { ntile = tile + gridDim.x; nblk2 = half; }
                         if (ntile < total) {
-                            bulk_wait_read<0>();                  // the store that last read the other buffer is done with it
-                            load_r(ntile, nblk2, b ^ 1);
+                            bulk_wait_read<NBUF - 2>();           // the store that last read the next buffer is done with it
+                            load_r(ntile, nblk2, bn_);
                         }
                     }
                     if (!mbar_wait(rbars[b], rphase[b], abortp)) return false;
                     rphase[b] ^= 1u;
                 } else {
-                    if (lane == 0) bulk_wait_read<1>();           // the store issued two blocks ago has left this buffer
+                    if (lane == 0) bulk_wait_read<NBUF - 1>();    // the store that last used this buffer has left it
                     __syncwarp();
                 }
                 stage_block<T, EPI>(p, tiles[b], lane, full, n, r);
@@ -374,14 +386,14 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 fetch(blk, ra);
                 while (true) {
                     tc_wait_ld();
-                    if (blk + 2 < nblk) fetch(blk + 2, rb);
+                    if (blk + PER_QUAD < nblk) fetch(blk + PER_QUAD, rb);
                     if (!emit(blk, ra)) { ok = false; break; }
-                    blk += 2;
+                    blk += PER_QUAD;
                     if (blk >= nblk) break;
                     tc_wait_ld();
-                    if (blk + 2 < nblk) fetch(blk + 2, ra);
+                    if (blk + PER_QUAD < nblk) fetch(blk + PER_QUAD, ra);
                     if (!emit(blk, rb)) { ok = false; break; }
-                    blk += 2;
+                    blk += PER_QUAD;
                     if (blk >= nblk) break;
                 }
                 if (!ok) break;
@@ -465,22 +477,26 @@ int choose_bn(int n) {
     return best;
 }
 
-template <typename T, int EPI> int launch_tc(const HostPlan& hp, const TcMaps& maps, const TcParams& p, cudaStream_t s) {
+template <typename T, int EPI, typename SH> int launch_tc(const TcMaps& maps, const TcParams& p, cudaStream_t s) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     static unsigned long long attr_done = 0;   // one bit per device ordinal: dynamic shared memory opt-in is per device
     if (dev < 64 && !((attr_done >> dev) & 1ull)) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<T, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<T, EPI, SH>, cudaFuncAttributeMaxDynamicSharedMemorySize, SH::SMEM_BYTES);
         if (e != cudaSuccess) return int(e);
         attr_done |= 1ull << dev;
     }
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long total = (long long)p.m_tiles * p.n_tiles;
     const unsigned grid = unsigned(total < sms ? total : sms);
-    (void)hp;
-    gemm_tc_kernel<T, EPI><<<grid, NTHREADS, SMEM_BYTES, s>>>(maps, p);
+    gemm_tc_kernel<T, EPI, SH><<<grid, SH::NTHREADS, SH::SMEM_BYTES, s>>>(maps, p);
     return int(cudaGetLastError());
 }
+
+// Three operand stages, eight epilogue warps, two output tiles in flight per warp.  Measured on the in-projection
+// shape (M = 657k, N = 2316, K = 384): <3,8,2> 1.72 ms, <3,4,4> 1.66 ms, <2,8,4> 1.99 ms, so the epilogue is not limited
+// by its own pipeline depth, and a two-stage operand ring starves the tensor pipe.
+using ShapeDefault = Shape<3, 8, 2>;
 
 }  // namespace
 }  // namespace sb
@@ -555,10 +571,10 @@ extern "C" int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream) 
     }
     if (!ok) return int(cudaErrorNotSupported);
     cudaStream_t s = cudaStream_t(stream);
-    if (hp->epi == EPI_PLAIN) return launch_tc<float, EPI_PLAIN>(*hp, maps, p, s);
-    if (hp->epi == EPI_RESID) return launch_tc<float, EPI_RESID>(*hp, maps, p, s);
-    if (hp->c_dtype == DT_BF16) return launch_tc<__nv_bfloat16, EPI_SWIGLU>(*hp, maps, p, s);
-    return launch_tc<__half, EPI_SWIGLU>(*hp, maps, p, s);
+    if (hp->epi == EPI_PLAIN) return launch_tc<float, EPI_PLAIN, ShapeDefault>(maps, p, s);
+    if (hp->epi == EPI_RESID) return launch_tc<float, EPI_RESID, ShapeDefault>(maps, p, s);
+    if (hp->c_dtype == DT_BF16) return launch_tc<__nv_bfloat16, EPI_SWIGLU, ShapeDefault>(maps, p, s);
+    return launch_tc<__half, EPI_SWIGLU, ShapeDefault>(maps, p, s);
 }
 
 extern "C" int shvk_gemm_tc(const void* host_plan, void* stream) {
