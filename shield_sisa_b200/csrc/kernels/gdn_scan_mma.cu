@@ -45,20 +45,19 @@ struct RawBuf {                              // TMA targets, one chunk
     float q[TC][kDK];                        // raw q projection
     float k[TC][kDK];                        // raw k projection
     float v[TC][kDV];                        // raw v; after prep reused as the chunk's output tile o[token][value]
-    float ab[TC][16];
+    float ab[TC][16];                        // a | b gate projections; after the gates are taken, the 16 x 16 matrix L
 };
+// Once q and k are converted, their two tiles (contiguous, 8 KB) receive the chunk's output-gate tile [16][128].
 static_assert(sizeof(RawBuf) == 17408 && sizeof(RawBuf) % 128 == 0, "tile offsets must stay 128-byte aligned");
 
 struct MmaSmem {
     RawBuf raw[2];
-    float g[TC][kDV];                        // output gate tile of the current chunk (single buffer)
     float vt[kDV][VT_PITCH];                 // silu(conv v), transposed: [value][token]
     __nv_bfloat16 kb[TC][KB_PITCH];          // silu(conv k), un-normalised, [token][key]
     __nv_bfloat16 qb[TC][KB_PITCH];          // silu(conv q), un-normalised
     __nv_bfloat16 kt[kDK][KT_PITCH];         // the k tile transposed: [key][token]
     __nv_bfloat16 t2[TC][KT_PITCH];          // (I + L)^-1 diag(beta)
     __nv_bfloat16 mq[TC][KT_PITCH];          // decay-masked Q K^T
-    float lf[TC][TC + 1];                    // L, fp32, for the triangular inverse
     float iq[TC], ik[TC], lg[TC], beta[TC];  // 0.125/|q|, 1/|k|, warp 1's copy of 1/|k|, beta (0 beyond the sequence end)
     float cum[TC], eg[TC], dj[TC];           // c_i, exp(c_i), exp(c_last - c_i)
     unsigned long long full[2], gfull;       // mbarriers
@@ -153,8 +152,6 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         if (tid == 0) {
             tma::fence_proxy_async();
             if (chunk + 1 < NCHUNK) issue(chunk + 1);     // the other raw buffer is free since the closing barrier
-            tma::mbar_expect_tx(gbar, uint32_t(sizeof(sm.g)));
-            tma::load_2d(tma::smem_addr(&sm.g[0][0]), &maps.vg, kGG + head * kDV, row_base + t0, gbar);
         }
         if (!tma::mbar_wait_bounded((chunk & 1) ? bar1 : bar0, uint32_t(chunk >> 1) & 1u, WAIT_POLLS)) {
             if (tid == 0) atomicCAS(&g_scan_mma_status, 0, 1);
@@ -214,6 +211,13 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             }
         }
         __syncthreads();
+        float* gtile = &b.q[0][0];                        // q and k are consumed: their 8 KB now take the gate tile
+        float (*lf)[TC] = reinterpret_cast<float (*)[TC]>(&b.ab[0][0]);       // and the a|b tile takes L
+        if (tid == 0) {
+            tma::fence_proxy_async();
+            tma::mbar_expect_tx(gbar, uint32_t(TC * kDV * 4));
+            tma::load_2d(tma::smem_addr(gtile), &maps.vg, kGG + head * kDV, row_base + t0, gbar);
+        }
         const uint32_t* kbw = reinterpret_cast<const uint32_t*>(&sm.kb[0][0]);   // 36 words per token row
         const uint32_t* qbw = reinterpret_cast<const uint32_t*>(&sm.qb[0][0]);
         // ---------------------------------------------------------------- warp 0: norms of k, L, T2; warp 1: norms, masked Q K^T
@@ -271,7 +275,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
 #pragma unroll
                 for (int ni = 0; ni < 2; ++ni)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) sm.lf[g + (e >> 1) * 8][8 * ni + 2 * t + (e & 1)] = acc[ni][e];
+                    for (int e = 0; e < 4; ++e) lf[g + (e >> 1) * 8][8 * ni + 2 * t + (e & 1)] = acc[ni][e];
                 __syncwarp();
                 if (lane < TC) {                          // column `lane` of (I + L)^-1 by forward substitution
                     float x[TC];
@@ -281,7 +285,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                         float s0 = i == lane ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
                         for (int j = 0; j < i; ++j) {
-                            const float l = sm.lf[i][j];
+                            const float l = lf[i][j];
                             if ((j & 3) == 0) s0 = fmaf(-l, x[j], s0);
                             else if ((j & 3) == 1) s1 = fmaf(-l, x[j], s1);
                             else if ((j & 3) == 2) s2 = fmaf(-l, x[j], s2);
@@ -418,7 +422,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         for (int i = warp; i < nt; i += 4) {
             const long long row = (long long)row_base + t0 + i;
             const float4 o = *reinterpret_cast<const float4*>(&otile[i * kDV + lane * 4]);
-            const float4 gt = *reinterpret_cast<const float4*>(&sm.g[i][lane * 4]);
+            const float4 gt = *reinterpret_cast<const float4*>(&gtile[i * kDV + lane * 4]);
             const float4 w = onw;
             const float ss = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
             const float rstd = 1.0f / sqrtf(ss / float(kDV) + 1e-6f);
@@ -426,7 +430,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                           ((o.y * rstd) * w.y) * silu_tanh(gt.y), ((o.z * rstd) * w.z) * silu_tanh(gt.z),
                           ((o.w * rstd) * w.w) * silu_tanh(gt.w));
         }
-        __syncthreads();                                  // the raw buffer, the gate tile and the operand tiles are free again
+        __syncthreads();                                  // the raw buffer (with the gate tile in it) and the operand tiles are free again
     }
 }
 
