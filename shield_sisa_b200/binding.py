@@ -102,6 +102,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_gemm_tc_status": (i32, [C.POINTER(i32)]),
         "shvk_gdn_scan": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp]),
         "shvk_gdn_scan_status": (i32, [C.POINTER(i32)]),
+        "shvk_gdn_chunked": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, vp]),
         "shvk_sisa_attn": (i32, [vp, vp, vp, vp, i32, vp]),
         "shvk_head": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, vp]),
         "shvk_store_tokens": (i32, [vp, vp, vp, i32, vp]),
