@@ -51,7 +51,7 @@ struct RawBuf {                              // TMA targets, one chunk
 static_assert(sizeof(RawBuf) == 17408 && sizeof(RawBuf) % 128 == 0, "tile offsets must stay 128-byte aligned");
 
 struct MmaSmem {
-    RawBuf raw[2];
+    RawBuf raw[3];                           // ring: chunk c uses raw[c % 3] until its deferred gated norm is done
     float vt[kDV][VT_PITCH];                 // silu(conv v), transposed: [value][token]
     __nv_bfloat16 kb[TC][KB_PITCH];          // silu(conv k), un-normalised, [token][key]
     __nv_bfloat16 qb[TC][KB_PITCH];          // silu(conv q), un-normalised
@@ -60,7 +60,7 @@ struct MmaSmem {
     __nv_bfloat16 mq[TC][KT_PITCH];          // decay-masked Q K^T
     float iq[TC], ik[TC], lg[TC], beta[TC];  // 0.125/|q|, 1/|k|, warp 1's copy of 1/|k|, beta (0 beyond the sequence end)
     float cum[TC], eg[TC], dj[TC];           // c_i, exp(c_i), exp(c_last - c_i)
-    unsigned long long full[2], gfull;       // mbarriers
+    unsigned long long full[3], gfull[3];    // mbarriers: raw tiles / gate tile of the chunk in ring slot i landed
 };
 constexpr int MMA_SMEM_BYTES = int(sizeof(MmaSmem)) + 128;
 
@@ -124,10 +124,10 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
 #pragma unroll
             for (int e = 0; e < 4; ++e) S[mi][nj][e] = 0.0f;
 
-    const uint32_t bar0 = tma::smem_addr(&sm.full[0]), bar1 = tma::smem_addr(&sm.full[1]), gbar = tma::smem_addr(&sm.gfull);
+    const uint32_t bars0 = tma::smem_addr(&sm.full[0]), gbars0 = tma::smem_addr(&sm.gfull[0]);   // + 8 * ring slot
     auto issue = [&](int chunk) {                         // thread 0: q, k, v, a|b tiles of `chunk`
-        RawBuf& b = sm.raw[chunk & 1];
-        const uint32_t bar = (chunk & 1) ? bar1 : bar0;
+        RawBuf& b = sm.raw[chunk % 3];
+        const uint32_t bar = bars0 + 8u * uint32_t(chunk % 3);
         const int row = row_base + chunk * TC;
         tma::mbar_expect_tx(bar, uint32_t(sizeof(RawBuf)));
         tma::load_2d(tma::smem_addr(&b.q[0][0]), &maps.qk, kGQ + head * kDK, row, bar);
@@ -136,9 +136,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         tma::load_2d(tma::smem_addr(&b.ab[0][0]), &maps.ab, kGA, row, bar);
     };
     if (tid == 0) {
-        tma::mbar_init(bar0, 1);
-        tma::mbar_init(bar1, 1);
-        tma::mbar_init(gbar, 1);
+        for (int i = 0; i < 3; ++i) { tma::mbar_init(bars0 + 8u * i, 1); tma::mbar_init(gbars0 + 8u * i, 1); }
         tma::fence_barrier_init();
         tma::fence_proxy_async();
         issue(0);
@@ -146,14 +144,36 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
     __syncthreads();
 
     constexpr int NCHUNK = (kTok + TC - 1) / TC;
+    // Gated RMSNorm of chunk pc (its o tile and gate tile sit in ring slot pc % 3), tokens first, first + step, ...
+    // Returns false if the gate tile never arrived.
+    auto gated_norm = [&](int pc, int first, int step) -> bool {
+        RawBuf& pb = sm.raw[pc % 3];
+        if (!tma::mbar_wait_bounded(gbars0 + 8u * uint32_t(pc % 3), uint32_t(pc / 3) & 1u, WAIT_POLLS)) return false;
+        const float* ot = &pb.v[0][0];
+        const float* gt_ = &pb.q[0][0];
+        const int pnt = min(TC, kTok - pc * TC);
+        for (int i = first; i < pnt; i += step) {
+            const long long row = (long long)row_base + pc * TC + i;
+            const float4 o = *reinterpret_cast<const float4*>(&ot[i * kDV + lane * 4]);
+            const float4 gt = *reinterpret_cast<const float4*>(&gt_[i * kDV + lane * 4]);
+            const float ss = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
+            const float rstd = 1.0f / sqrtf(ss / float(kDV) + 1e-6f);
+            store_quad<T>(on + row * kVD + head * kDV + lane * 4, ((o.x * rstd) * onw.x) * silu_tanh(gt.x),
+                          ((o.y * rstd) * onw.y) * silu_tanh(gt.y), ((o.z * rstd) * onw.z) * silu_tanh(gt.z),
+                          ((o.w * rstd) * onw.w) * silu_tanh(gt.w));
+        }
+        return true;
+    };
     for (int chunk = 0; chunk < NCHUNK; ++chunk) {
         const int t0 = chunk * TC, nt = min(TC, kTok - t0);
-        RawBuf& b = sm.raw[chunk & 1];
+        RawBuf& b = sm.raw[chunk % 3];
+        (void)nt;
         if (tid == 0) {
+            // ring slot (chunk + 1) % 3 was last used by chunk - 2, whose gated norm ended before the previous barrier
             tma::fence_proxy_async();
-            if (chunk + 1 < NCHUNK) issue(chunk + 1);     // the other raw buffer is free since the closing barrier
+            if (chunk + 1 < NCHUNK) issue(chunk + 1);
         }
-        if (!tma::mbar_wait_bounded((chunk & 1) ? bar1 : bar0, uint32_t(chunk >> 1) & 1u, WAIT_POLLS)) {
+        if (!tma::mbar_wait_bounded(bars0 + 8u * uint32_t(chunk % 3), uint32_t(chunk / 3) & 1u, WAIT_POLLS)) {
             if (tid == 0) atomicCAS(&g_scan_mma_status, 0, 1);
             return;                                       // every thread times out on the same barrier and leaves
         }
@@ -215,6 +235,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         float (*lf)[TC] = reinterpret_cast<float (*)[TC]>(&b.ab[0][0]);       // and the a|b tile takes L
         if (tid == 0) {
             tma::fence_proxy_async();
+            const uint32_t gbar = gbars0 + 8u * uint32_t(chunk % 3);
             tma::mbar_expect_tx(gbar, uint32_t(TC * kDV * 4));
             tma::load_2d(tma::smem_addr(gtile), &maps.vg, kGG + head * kDV, row_base + t0, gbar);
         }
@@ -305,6 +326,10 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                     mw[(g + 8) * 12 + 4 * ni + t] = pack_bf16(acc[ni][2], acc[ni][3]);
                 }
             }
+        }
+        // warps 2 and 3 meanwhile finish the previous chunk: its gated RMSNorm, eight tokens each
+        if (warp >= 2 && chunk > 0) {
+            if (!gated_norm(chunk - 1, warp - 2, 2)) atomicCAS(&g_scan_mma_status, 0, 2);
         }
         // ---------------------------------------------------------------- R^T = S0^T K^T and (Q S0)^T, all warps
         float R[2][2][4], QS[2][2][4];
@@ -413,25 +438,9 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 }
             }
         }
-        __syncthreads();
-        // ---------------------------------------------------------------- post: gated RMSNorm, warp per token
-        if (!tma::mbar_wait_bounded(gbar, uint32_t(chunk) & 1u, WAIT_POLLS)) {
-            if (tid == 0) atomicCAS(&g_scan_mma_status, 0, 2);
-            return;
-        }
-        for (int i = warp; i < nt; i += 4) {
-            const long long row = (long long)row_base + t0 + i;
-            const float4 o = *reinterpret_cast<const float4*>(&otile[i * kDV + lane * 4]);
-            const float4 gt = *reinterpret_cast<const float4*>(&gtile[i * kDV + lane * 4]);
-            const float4 w = onw;
-            const float ss = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
-            const float rstd = 1.0f / sqrtf(ss / float(kDV) + 1e-6f);
-            store_quad<T>(on + row * kVD + head * kDV + lane * 4, ((o.x * rstd) * w.x) * silu_tanh(gt.x),
-                          ((o.y * rstd) * w.y) * silu_tanh(gt.y), ((o.z * rstd) * w.z) * silu_tanh(gt.z),
-                          ((o.w * rstd) * w.w) * silu_tanh(gt.w));
-        }
-        __syncthreads();                                  // the raw buffer (with the gate tile in it) and the operand tiles are free again
+        __syncthreads();                                  // o tile complete; operand tiles free for the next chunk
     }
+    if (!gated_norm(NCHUNK - 1, warp, 4)) atomicCAS(&g_scan_mma_status, 0, 2);
 }
 
 }  // namespace
