@@ -54,7 +54,8 @@ typedef struct shvk_gemm_args {
 int shvk_gemm_f32(const shvk_gemm_args* g, void* stream);
 /* tcgen05 tensor-core GEMM, A and W in ab_dtype (bf16 or fp16), fp32 accumulation in tensor memory, operands
  * staged by TMA.  Needs K % 64 == 0, 16-byte aligned operands and pitches.  shvk_gemm_tc_plan encodes the two TMA
- * tensor maps and the tile shape for exactly these operands into a host-side plan that launches reuse. */
+ * tensor maps and the tile shape for exactly these operands into a host-side plan that launches reuse.  Plain fp32
+ * output with ldc - N < 8: the padding columns N .. ldc-1 may be written with zeros (whole 32-byte sectors per row). */
 int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* host_plan /* >= 512 bytes, host, 64-byte aligned */);
 int shvk_gemm_tc(const void* host_plan, void* stream);
 /* Same plan, first `rows` <= M rows only (a smaller batch in buffers sized for the planned M). */

@@ -56,7 +56,9 @@ struct TcParams {
     const float* bias;
     float r_div;
     uint32_t idesc;
-    int probe;      // development timing probes (SHVK_TC_PROBE): 2 no epilogue work, 4 no MMA, 8 no W load, 16 no A load
+    int m_major;    // tile order: 1 = a CTA finishes all column tiles of a row block before its next row block
+    int probe;      // development timing probes (SHVK_TC_PROBE): 2 no epilogue work, 4 no MMA, 8 no W load, 16 no A load,
+                    // 32 column-tile-major order always, 64 padding columns left unwritten, 128 no L2 eviction hints
 };
 
 // ---------------------------------------------------------------------------------------------- PTX wrappers
@@ -99,6 +101,27 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+// L2 eviction policies for the streams of one GEMM: C (written once, never re-read by this kernel) leaves first, W
+// (re-read by every row block) leaves last, A stays on the default policy.
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, int c0, int c1, uint32_t src, uint64_t pol) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(src), "l"(pol) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until all but the newest N store groups of this thread have finished reading shared memory.
@@ -220,6 +243,22 @@ __device__ __forceinline__ void stage_block(const TcParams& p, uint32_t tile, in
     }
 }
 
+// The it-th tile of this CTA; false past the end.  Row-block-major order (m_major) lets one CTA write whole rows of
+// C within a few tiles' time, which DRAM takes about a third faster than column tiles of many row blocks interleaved.
+__device__ __forceinline__ bool tile_at(const TcParams& p, long long it, int& mt, int& nt) {
+    if (p.m_major) {
+        const long long round = it / p.n_tiles;
+        const long long m = round * gridDim.x + blockIdx.x;
+        nt = int(it - round * p.n_tiles);
+        mt = int(m);
+        return m < p.m_tiles;
+    }
+    const long long tile = blockIdx.x + it * gridDim.x;
+    mt = int(tile / p.n_tiles);
+    nt = int(tile - (long long)mt * p.n_tiles);
+    return tile < (long long)p.m_tiles * p.n_tiles;
+}
+
 template <typename T, int EPI, typename SH>
 __global__ void __launch_bounds__(SH::NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
@@ -257,7 +296,6 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     volatile int* abortp = &abort_flag;
 
     const int nk = p.K / TILE_K;
-    const long long total = (long long)p.m_tiles * p.n_tiles;
     const uint32_t stage_tx = uint32_t(A_BYTES + p.BN * TILE_K * 2);
 
     if (warp == 0) {
@@ -265,8 +303,10 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-                const int mt = int(tile / p.n_tiles), nt = int(tile - (long long)mt * p.n_tiles);
+            int mt, nt;
+            const uint64_t pol_w = policy_evict_last();
+            const bool hint = !(p.probe & 128);
+            for (long long it = 0; ok && tile_at(p, it, mt, nt); ++it) {
                 for (int kb = 0; kb < nk; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp)) { ok = false; break; }
                     const uint32_t sa = base + stage * STAGE_BYTES, sb_ = sa + A_BYTES;
@@ -274,7 +314,10 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                     if (la || lw) {
                         mbar_expect_tx(full_bar(stage), (la ? uint32_t(A_BYTES) : 0u) + (lw ? stage_tx - uint32_t(A_BYTES) : 0u));
                         if (la) tma_load_2d(sa, &maps.a, kb * TILE_K, mt * TILE_M, full_bar(stage));
-                        if (lw) tma_load_2d(sb_, &maps.w, kb * TILE_K, nt * p.BN, full_bar(stage));
+                        if (lw) {
+                            if (hint) tma_load_2d_hint(sb_, &maps.w, kb * TILE_K, nt * p.BN, full_bar(stage), pol_w);
+                            else tma_load_2d(sb_, &maps.w, kb * TILE_K, nt * p.BN, full_bar(stage));
+                        }
                     } else {
                         mbar_arrive(full_bar(stage));
                     }
@@ -288,7 +331,8 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+            int mt, nt;
+            for (long long it = 0; ok && tile_at(p, it, mt, nt); ++it) {
                 if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abortp)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + uint32_t(acc * ACC_COLS);
@@ -322,22 +366,23 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             rphase[i] = 0u;
         }
         const bool active = half < nblk && !(p.probe & 2);          // this warp has blocks to write
+        const uint64_t pol_c = policy_evict_first();
+        const bool hint = !(p.probe & 128);
         uint32_t nb = 0;                                            // blocks done by this warp; tile buffer = nb % NBUF
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         // lane 0 only: TMA load of R for block (tile, blk) into tile buffer b
-        auto load_r = [&](long long tile, int blk, int b) {
-            const int mt = int(tile / p.n_tiles), nt = int(tile - (long long)mt * p.n_tiles);
+        auto load_r = [&](int mt, int nt, int blk, int b) {
             const int c = blk << 5;
             const bool full = p.BN - c >= 32;
             mbar_expect_tx(rbars[b], full ? 4096u : 2048u);
             tma_load_2d(tiles[b], full ? &maps.r_full : &maps.r_half, nt * p.BN + c, mt * TILE_M + quad * 32, rbars[b]);
         };
-        if (EPI == EPI_RESID && active && lane == 0 && (long long)blockIdx.x < total) load_r(blockIdx.x, half, 0);
+        int mt, nt;
+        if (EPI == EPI_RESID && active && lane == 0 && tile_at(p, 0, mt, nt)) load_r(mt, nt, half, 0);
 
-        for (long long tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-            const int mt = int(tile / p.n_tiles), nt = int(tile - (long long)mt * p.n_tiles);
+        for (long long it = 0; ok && tile_at(p, it, mt, nt); ++it) {
             if (!mbar_wait(accf_bar(acc), acc_phase, abortp)) { ok = false; break; }
             tc_fence_after();
             const int m0 = mt * TILE_M + quad * 32;
@@ -356,12 +401,12 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 const int n = nt * p.BN + c;
                 if constexpr (EPI == EPI_RESID) {
                     if (lane == 0) {
-                        long long ntile = tile;
-                        int nblk2 = blk + PER_QUAD;
-                        if (nblk2 >= nblk) { ntile = tile + gridDim.x; nblk2 = half; }
-                        if (ntile < total) {
+                        int mt2 = mt, nt2 = nt, nblk2 = blk + PER_QUAD;
+                        bool more = true;
+                        if (nblk2 >= nblk) { more = tile_at(p, it + 1, mt2, nt2); nblk2 = half; }
+                        if (more) {
                             bulk_wait_read<NBUF - 2>();           // the store that last read the next buffer is done with it
-                            load_r(ntile, nblk2, bn_);
+                            load_r(mt2, nt2, nblk2, bn_);
                         }
                     }
                     if (!mbar_wait(rbars[b], rphase[b], abortp)) return false;
@@ -375,7 +420,8 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 __syncwarp();
                 if (lane == 0) {
                     const int x = EPI == EPI_SWIGLU ? (n >> 1) : n;
-                    tma_store_2d(full ? &maps.c_full : &maps.c_half, x, m0, tiles[b]);
+                    if (hint) tma_store_2d_hint(full ? &maps.c_full : &maps.c_half, x, m0, tiles[b], pol_c);
+                    else tma_store_2d(full ? &maps.c_full : &maps.c_half, x, m0, tiles[b]);
                     bulk_commit();
                 }
                 ++nb;
@@ -489,7 +535,10 @@ template <typename T, int EPI, typename SH> int launch_tc(const TcMaps& maps, co
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long total = (long long)p.m_tiles * p.n_tiles;
     const unsigned grid = unsigned(total < sms ? total : sms);
-    gemm_tc_kernel<T, EPI, SH><<<grid, SH::NTHREADS, SH::SMEM_BYTES, s>>>(maps, p);
+    TcParams q = p;
+    // whole row blocks per CTA once there are enough of them to keep every SM equally busy (under 1/8 idle at the tail)
+    q.m_major = p.n_tiles > 1 && p.m_tiles >= 8ll * grid && !(p.probe & 32);
+    gemm_tc_kernel<T, EPI, SH><<<grid, SH::NTHREADS, SH::SMEM_BYTES, s>>>(maps, q);
     return int(cudaGetLastError());
 }
 
@@ -562,8 +611,13 @@ extern "C" int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream) 
         maps.r_full = maps.c_full;
         maps.r_half = maps.c_half;
     } else {
-        ok = make_map(&maps.c_full, hp->C, 4, rows, p.N, hp->ldc, 32, 32, true) &&
-             make_map(&maps.c_half, hp->C, 4, rows, p.N, hp->ldc, 32, 16, false);
+        // up to seven padding columns right of N are written too where the last column tile covers them (zeros: the
+        // weight rows there read as zero fill); a row that ended inside a 32-byte sector would cost a DRAM
+        // read-modify-write per row
+        const bool pad = hp->epi == EPI_PLAIN && hp->ldc - p.N < 8 && hp->ldc <= (long long)p.n_tiles * p.BN && !(p.probe & 64);
+        const long long c_cols = pad ? hp->ldc : p.N;
+        ok = make_map(&maps.c_full, hp->C, 4, rows, c_cols, hp->ldc, 32, 32, true) &&
+             make_map(&maps.c_half, hp->C, 4, rows, c_cols, hp->ldc, 32, 16, false);
         if (hp->epi == EPI_RESID)
             ok = ok && make_map(&maps.r_full, hp->R, 4, rows, p.N, hp->ldr, 32, 32, true) &&
                  make_map(&maps.r_half, hp->R, 4, rows, p.N, hp->ldr, 32, 16, false);

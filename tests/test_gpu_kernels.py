@@ -134,7 +134,8 @@ def test_gemm_tc_plain(L, dtype, M, N, K):
     got = Cm.cpu().numpy()
     ref = A.float().cpu().numpy().astype(np.float64) @ Wt.float().cpu().numpy().astype(np.float64).T
     assert np.abs(got[:, :N] - ref).max() < 1e-4           # operands are exact in 16 bits; only fp32 accumulation differs
-    assert (got[:, N:] == 7.0).all()
+    # fewer than eight padding columns may be written along with the row (zeros), so that rows end on a whole sector
+    assert ((got[:, N:] == 0.0) | (got[:, N:] == 7.0)).all()
 
 
 def test_gemm_tc_epilogues_and_partial_rows(L):
