@@ -60,6 +60,7 @@ struct MmaSmem {
     __nv_bfloat16 mq[TC][KT_PITCH];          // decay-masked Q K^T
     float iq[TC], ik[TC], lg[TC], beta[TC];  // 0.125/|q|, 1/|k|, warp 1's copy of 1/|k|, beta (0 beyond the sequence end)
     float cum[TC], eg[TC], dj[TC];           // c_i, exp(c_i), exp(c_last - c_i)
+    float ssq[TC][4];                        // per token: each warp's share of sum(o^2) over its 32 value columns
     unsigned long long full[3], gfull[3];    // mbarriers: raw tiles / gate tile of the chunk in ring slot i landed
 };
 constexpr int MMA_SMEM_BYTES = int(sizeof(MmaSmem)) + 128;
@@ -77,6 +78,28 @@ __device__ __forceinline__ float silu_tanh(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * x));
     const float hx = 0.5f * x;
     return fmaf(hx, th, hx);
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(*reinterpret_cast<uint64_t*>(&d))
+        : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)), "l"(*reinterpret_cast<uint64_t*>(&c)));
+    return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;"
+        : "=l"(*reinterpret_cast<uint64_t*>(&d))
+        : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
+    return d;
+}
+// SiLU of two values at once: packed multiply and FMA around the two hardware tanh
+__device__ __forceinline__ float2 silu_tanh2(float2 x) {
+    const float2 hx = fmul2(x, make_float2(0.5f, 0.5f));
+    float2 th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th.x) : "f"(hx.x));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th.y) : "f"(hx.y));
+    return ffma2(hx, th, hx);
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -102,16 +125,18 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
     const int row_base = clip * kTok;
     const int dvb = warp * 32;                           // this warp's value columns
 
-    // prep role: one q or k channel and one v column per thread; conv tap j multiplies x[t - 3 + j]
-    const bool is_k = tid >= kDK;
-    const int ch = tid & (kDK - 1);
-    const int qk_w = (is_k ? 384 : 0) + head * kDK + ch;
-    const float4 wqk = *reinterpret_cast<const float4*>(conv_w + qk_w * 4);
-    const float bqk = conv_b[qk_w];
-    const int v_w = 768 + head * kDV + tid;
-    const float4 wv = *reinterpret_cast<const float4*>(conv_w + v_w * 4);
-    const float bv = conv_b[v_w];
-    float x1 = 0.0f, x2 = 0.0f, x3 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;   // zero history = causal padding
+    // prep role: two adjacent channels per thread, computed as packed fp32 pairs.  Warp 0: q channels 2 lane, + 1;
+    // warp 1: k channels; warps 2, 3: v columns 2 (tid - 64), + 1.  Conv tap j multiplies x[t - 3 + j].
+    const int pc0 = warp == 0 ? 2 * lane : warp == 1 ? 2 * lane : 2 * (tid - 64);       // first channel within its stream
+    const int cw0 = (warp == 0 ? 0 : warp == 1 ? 384 : 768) + head * (warp < 2 ? kDK : kDV) + pc0;
+    float2 wx, wy, wz, ww, bc2;
+    {
+        const float4 w0 = *reinterpret_cast<const float4*>(conv_w + cw0 * 4);
+        const float4 w1 = *reinterpret_cast<const float4*>(conv_w + cw0 * 4 + 4);
+        wx = make_float2(w0.x, w1.x); wy = make_float2(w0.y, w1.y); wz = make_float2(w0.z, w1.z); ww = make_float2(w0.w, w1.w);
+        bc2 = make_float2(conv_b[cw0], conv_b[cw0 + 1]);
+    }
+    float2 x1 = make_float2(0.0f, 0.0f), x2 = x1, x3 = x1;   // zero history = causal padding
     const float neg_rate = -expf(a_log[head]), dtb = dt_bias[head];
     const float4 onw = *reinterpret_cast<const float4*>(o_norm_w + lane * 4);   // gated-norm weights of this lane's columns
 
@@ -144,23 +169,27 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
     __syncthreads();
 
     constexpr int NCHUNK = (kTok + TC - 1) / TC;
-    // Gated RMSNorm of chunk pc (its o tile and gate tile sit in ring slot pc % 3), tokens first, first + step, ...
-    // Returns false if the gate tile never arrived.
-    auto gated_norm = [&](int pc, int first, int step) -> bool {
+    // Gated RMSNorm of chunk pc (its o tile and gate tile sit in ring slot pc % 3), tokens first .. first + count - 1
+    // (count <= 6).  Loads and arithmetic run unconditionally (the tile rows exist), only the store is guarded, so the
+    // unrolled tokens overlap.  Returns false if the gate tile never arrived.
+    auto gated_norm = [&](int pc, int first, int count) -> bool {
         RawBuf& pb = sm.raw[pc % 3];
         if (!tma::mbar_wait_bounded(gbars0 + 8u * uint32_t(pc % 3), uint32_t(pc / 3) & 1u, WAIT_POLLS)) return false;
         const float* ot = &pb.v[0][0];
         const float* gt_ = &pb.q[0][0];
-        const int pnt = min(TC, kTok - pc * TC);
-        for (int i = first; i < pnt; i += step) {
+        const int pnt = min(min(TC, kTok - pc * TC), first + count);
+#pragma unroll
+        for (int k = 0; k < 6; ++k) {
+            const int i = min(first + k, TC - 1);
             const long long row = (long long)row_base + pc * TC + i;
             const float4 o = *reinterpret_cast<const float4*>(&ot[i * kDV + lane * 4]);
             const float4 gt = *reinterpret_cast<const float4*>(&gt_[i * kDV + lane * 4]);
-            const float ss = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
-            const float rstd = 1.0f / sqrtf(ss / float(kDV) + 1e-6f);
-            store_quad<T>(on + row * kVD + head * kDV + lane * 4, ((o.x * rstd) * onw.x) * silu_tanh(gt.x),
-                          ((o.y * rstd) * onw.y) * silu_tanh(gt.y), ((o.z * rstd) * onw.z) * silu_tanh(gt.z),
-                          ((o.w * rstd) * onw.w) * silu_tanh(gt.w));
+            const float4 pp = *reinterpret_cast<const float4*>(&sm.ssq[i][0]);   // the four warps' partial sums of o^2
+            const float rstd = rsqrtf(((pp.x + pp.y) + (pp.z + pp.w)) * (1.0f / float(kDV)) + 1e-6f);
+            if (first + k < pnt)
+                store_quad<T>(on + row * kVD + head * kDV + lane * 4, ((o.x * rstd) * onw.x) * silu_tanh(gt.x),
+                              ((o.y * rstd) * onw.y) * silu_tanh(gt.y), ((o.z * rstd) * onw.z) * silu_tanh(gt.z),
+                              ((o.w * rstd) * onw.w) * silu_tanh(gt.w));
         }
         return true;
     };
@@ -180,43 +209,61 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         // ---------------------------------------------------------------- prep: conv + SiLU -> bf16 operand tiles, gates
         // k and q go into the tiles un-normalised; their norms come out of the Gram products below and enter every
         // later formula as per-token scalars.
-        {
-            uint32_t ktp[TC / 2];                         // this key's row of K^T, two tokens per word
-            float prev = 0.0f;
+        if (warp < 2) {
+            const float* src = warp == 0 ? &b.q[0][pc0] : &b.k[0][pc0];
+            uint32_t* dst = reinterpret_cast<uint32_t*>(warp == 0 ? &sm.qb[0][pc0] : &sm.kb[0][pc0]);
+            uint32_t kt0[TC / 2], kt1[TC / 2];             // warp 1: two rows of K^T, two tokens per word
+            float2 prev = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int i = 0; i < TC; ++i) {
-                const float raw_qk = is_k ? b.k[i][ch] : b.q[i][ch], raw_v = b.v[i][tid];
-                float acc = wqk.x * x3;
-                acc = fmaf(wqk.y, x2, acc);
-                acc = fmaf(wqk.z, x1, acc);
-                acc = fmaf(wqk.w, raw_qk, acc);
-                const float val = silu_tanh(acc + bqk);
-                x3 = x2; x2 = x1; x1 = raw_qk;
-                if (is_k) {
-                    sm.kb[i][ch] = __float2bfloat16_rn(val);
-                    if (i & 1) ktp[i >> 1] = pack_bf16(prev, val);
+                const float2 raw = *reinterpret_cast<const float2*>(src + i * kDK);
+                float2 acc = ffma2(wx, x3, bc2);
+                acc = ffma2(wy, x2, acc);
+                acc = ffma2(wz, x1, acc);
+                acc = ffma2(ww, raw, acc);
+                const float2 val = silu_tanh2(acc);
+                x3 = x2; x2 = x1; x1 = raw;
+                dst[i * (KB_PITCH / 2)] = pack_bf16(val.x, val.y);
+                if (warp == 1) {
+                    if (i & 1) { kt0[i >> 1] = pack_bf16(prev.x, val.x); kt1[i >> 1] = pack_bf16(prev.y, val.y); }
                     prev = val;
-                } else {
-                    sm.qb[i][ch] = __float2bfloat16_rn(val);
                 }
-                float accv = wv.x * y3;
-                accv = fmaf(wv.y, y2, accv);
-                accv = fmaf(wv.z, y1, accv);
-                accv = fmaf(wv.w, raw_v, accv);
-                sm.vt[tid][i] = silu_tanh(accv + bv);
-                y3 = y2; y2 = y1; y1 = raw_v;
             }
-            if (is_k) {
-                uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.kt[ch][0]);
+            if (warp == 1) {
+                uint4* r0 = reinterpret_cast<uint4*>(&sm.kt[pc0][0]);             // rows of 48 bytes: 16-byte aligned
+                uint4* r1 = reinterpret_cast<uint4*>(&sm.kt[pc0 + 1][0]);
+                r0[0] = make_uint4(kt0[0], kt0[1], kt0[2], kt0[3]); r0[1] = make_uint4(kt0[4], kt0[5], kt0[6], kt0[7]);
+                r1[0] = make_uint4(kt1[0], kt1[1], kt1[2], kt1[3]); r1[1] = make_uint4(kt1[4], kt1[5], kt1[6], kt1[7]);
+            }
+        } else {
+            const float* src = &b.v[0][pc0];
+            float4* r0 = reinterpret_cast<float4*>(&sm.vt[pc0][0]);                // rows of 80 bytes: 16-byte aligned
+            float4* r1 = reinterpret_cast<float4*>(&sm.vt[pc0 + 1][0]);
 #pragma unroll
-                for (int i = 0; i < TC / 2; ++i) dst[i] = ktp[i];
+            for (int i4 = 0; i4 < TC / 4; ++i4) {
+                float c0[4], c1[4];
+#pragma unroll
+                for (int ii = 0; ii < 4; ++ii) {
+                    const float2 raw = *reinterpret_cast<const float2*>(src + (4 * i4 + ii) * kDV);
+                    float2 acc = ffma2(wx, x3, bc2);
+                    acc = ffma2(wy, x2, acc);
+                    acc = ffma2(wz, x1, acc);
+                    acc = ffma2(ww, raw, acc);
+                    const float2 val = silu_tanh2(acc);
+                    x3 = x2; x2 = x1; x1 = raw;
+                    c0[ii] = val.x; c1[ii] = val.y;
+                }
+                r0[i4] = make_float4(c0[0], c0[1], c0[2], c0[3]);
+                r1[i4] = make_float4(c1[0], c1[1], c1[2], c1[3]);
             }
         }
         if (warp == 3) {                                  // gates and the inclusive prefix sum of the log decays
             // tokens past the sequence end are made inert: beta = 0, no decay
             const bool valid = lane < nt;
-            float c = valid ? neg_rate * softplus_f(b.ab[lane & (TC - 1)][head] + dtb) : 0.0f;
-            const float bt_ = valid ? sigmoid_f(b.ab[lane & (TC - 1)][6 + head]) : 0.0f;
+            // hardware exp / log: absolute error ~1e-7 on the log decay and on beta, far below the bf16 operands
+            const float ax = b.ab[lane & (TC - 1)][head] + dtb;
+            float c = valid ? neg_rate * (ax > 15.0f ? ax : __logf(1.0f + __expf(ax))) : 0.0f;
+            const float bt_ = valid ? __fdividef(1.0f, 1.0f + __expf(-b.ab[lane & (TC - 1)][6 + head])) : 0.0f;
 #pragma unroll
             for (int o = 1; o < TC; o <<= 1) {
                 const float up = __shfl_up_sync(0xffffffffu, c, o);
@@ -226,8 +273,8 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             if (lane < TC) {
                 sm.beta[lane] = bt_;
                 sm.cum[lane] = c;
-                sm.eg[lane] = expf(c);
-                sm.dj[lane] = expf(last - c);
+                sm.eg[lane] = __expf(c);
+                sm.dj[lane] = __expf(last - c);
             }
         }
         __syncthreads();
@@ -268,15 +315,15 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             }
             // diagonal entries: row g sits in tile 0 at column 2t + e == g, row g + 8 in tile 1 at the same lane / slot
             if (t == (g >> 1)) {
-                const int e = g & 1;
+                const bool odd = g & 1;                   // selects, not a runtime index: the fragments stay in registers
                 if (warp == 0) {
-                    sm.ik[g] = 1.0f / sqrtf(acc[0][e] + 1e-6f);
-                    sm.ik[g + 8] = 1.0f / sqrtf(acc[1][2 + e] + 1e-6f);
+                    sm.ik[g] = rsqrtf((odd ? acc[0][1] : acc[0][0]) + 1e-6f);
+                    sm.ik[g + 8] = rsqrtf((odd ? acc[1][3] : acc[1][2]) + 1e-6f);
                 } else {
-                    sm.iq[g] = (1.0f / sqrtf(dq[0][e] + 1e-6f)) * 0.125f;
-                    sm.iq[g + 8] = (1.0f / sqrtf(dq[1][2 + e] + 1e-6f)) * 0.125f;
-                    sm.lg[g] = 1.0f / sqrtf(dk[0][e] + 1e-6f);            // warp 1's own copy of 1/|k| (sm.lg is free here)
-                    sm.lg[g + 8] = 1.0f / sqrtf(dk[1][2 + e] + 1e-6f);
+                    sm.iq[g] = rsqrtf((odd ? dq[0][1] : dq[0][0]) + 1e-6f) * 0.125f;
+                    sm.iq[g + 8] = rsqrtf((odd ? dq[1][3] : dq[1][2]) + 1e-6f) * 0.125f;
+                    sm.lg[g] = rsqrtf((odd ? dk[0][1] : dk[0][0]) + 1e-6f);   // warp 1's own copy of 1/|k| (sm.lg is free here)
+                    sm.lg[g + 8] = rsqrtf((odd ? dk[1][3] : dk[1][2]) + 1e-6f);
                 }
             }
             __syncwarp();
@@ -288,7 +335,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 for (int e = 0; e < 4; ++e) {
                     const int i = g + (e >> 1) * 8, j = 8 * ni + 2 * t + (e & 1);
                     const bool keep = warp == 0 ? j < i : j <= i;
-                    const float dec = expf(keep ? sm.cum[i] - sm.cum[j] : 0.0f);
+                    const float dec = __expf(keep ? sm.cum[i] - sm.cum[j] : 0.0f);
                     const float rowf = warp == 0 ? sm.beta[i] * ikv[i] : sm.iq[i];
                     acc[ni][e] = keep ? dec * acc[ni][e] * rowf * ikv[j] : 0.0f;
                 }
@@ -327,9 +374,12 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 }
             }
         }
-        // warps 2 and 3 meanwhile finish the previous chunk: its gated RMSNorm, eight tokens each
-        if (warp >= 2 && chunk > 0) {
-            if (!gated_norm(chunk - 1, warp - 2, 2)) atomicCAS(&g_scan_mma_status, 0, 2);
+        // meanwhile the previous chunk is finished: its gated RMSNorm, six tokens each on warps 2 and 3 and the
+        // remaining four behind the shorter Gram work of warps 0 (one) and 1 (three)
+        if (chunk > 0) {
+            const int first = warp == 0 ? 15 : warp == 1 ? 12 : 6 * (warp - 2);
+            const int count = warp == 0 ? 1 : warp == 1 ? 3 : 6;
+            if (!gated_norm(chunk - 1, first, count)) atomicCAS(&g_scan_mma_status, 0, 2);
         }
         // ---------------------------------------------------------------- R^T = S0^T K^T and (Q S0)^T, all warps
         float R[2][2][4], QS[2][2][4];
@@ -385,6 +435,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             bm[ni][0] = mqw[(8 * ni + g) * 12 + t]; bm[ni][1] = mqw[(8 * ni + g) * 12 + t + 4];
         }
         float* otile = &b.v[0][0];                        // raw v is consumed: the tile now collects o[token][value]
+        float sq[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};    // sum of o^2 over this thread's value rows, per token 8 ni + 2t + e
         uint32_t da[2][4];                                // decay-scaled U^T as A fragments, for the state update
 #pragma unroll
         for (int mi = 0; mi < 2; ++mi) {
@@ -418,12 +469,27 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 float O[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 mma16816(O, ua, bm[ni][0], bm[ni][1]);
                 const int tok = 8 * ni + 2 * t;
-                otile[tok * kDV + r0] = O[0] + eq[ni][0] * QS[mi][ni][0];
-                otile[(tok + 1) * kDV + r0] = O[1] + eq[ni][1] * QS[mi][ni][1];
-                otile[tok * kDV + r1] = O[2] + eq[ni][0] * QS[mi][ni][2];
-                otile[(tok + 1) * kDV + r1] = O[3] + eq[ni][1] * QS[mi][ni][3];
+                const float o00 = O[0] + eq[ni][0] * QS[mi][ni][0], o01 = O[1] + eq[ni][1] * QS[mi][ni][1];
+                const float o10 = O[2] + eq[ni][0] * QS[mi][ni][2], o11 = O[3] + eq[ni][1] * QS[mi][ni][3];
+                otile[tok * kDV + r0] = o00;
+                otile[(tok + 1) * kDV + r0] = o01;
+                otile[tok * kDV + r1] = o10;
+                otile[(tok + 1) * kDV + r1] = o11;
+                sq[ni][0] = fmaf(o00, o00, fmaf(o10, o10, sq[ni][0]));
+                sq[ni][1] = fmaf(o01, o01, fmaf(o11, o11, sq[ni][1]));
             }
         }
+        // this warp's share of sum(o^2): reduce over the eight row groups g (lane bits 2-4), lanes 0-3 publish it
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float v = sq[ni][e];
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                if (g == 0) sm.ssq[8 * ni + 2 * t + e][warp] = v;
+            }
         // ---------------------------------------------------------------- S^T <- e_last S^T + (diag(d) U)^T K
         {
             const float elast = sm.eg[TC - 1];
@@ -440,7 +506,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         }
         __syncthreads();                                  // o tile complete; operand tiles free for the next chunk
     }
-    if (!gated_norm(NCHUNK - 1, warp, 4)) atomicCAS(&g_scan_mma_status, 0, 2);
+    if (!gated_norm(NCHUNK - 1, 4 * warp, 4)) atomicCAS(&g_scan_mma_status, 0, 2);
 }
 
 }  // namespace
