@@ -38,17 +38,22 @@ constexpr uint32_t WAIT_POLLS = 1u << 22;    // about a quarter second
 constexpr int KB_PITCH = 72;                 // bf16 per row of the K / Q tiles (144 bytes: conflict-free fragment reads)
 constexpr int KT_PITCH = 24;                 // bf16 per row of K^T, T2, M tiles (48 bytes)
 constexpr int VT_PITCH = 20;                 // floats per row of V^T
+constexpr int OT_PITCH = kDV + 4;            // floats per token row of the o tile: the fragment stores of a warp (eight value rows
+                                             // x four token pairs) then fall into 32 different banks
 
 __device__ int g_scan_mma_status = 0;
 
 struct RawBuf {                              // TMA targets, one chunk
     float q[TC][kDK];                        // raw q projection
     float k[TC][kDK];                        // raw k projection
-    float v[TC][kDV];                        // raw v; after prep reused as the chunk's output tile o[token][value]
-    float ab[TC][16];                        // a | b gate projections; after the gates are taken, the 16 x 16 matrix L
+    float v[TC][kDV];                        // raw v; after prep reused as the chunk's output tile o[token][value], whose
+                                             // padded rows (OT_PITCH) run 256 bytes into ab, dead by then
+    float ab[TC][16];                        // a | b gate projections; after the gates are taken, the 16 x 16 matrix L (until the
+                                             // inverse is done, before the o tile is written)
 };
 // Once q and k are converted, their two tiles (contiguous, 8 KB) receive the chunk's output-gate tile [16][128].
 static_assert(sizeof(RawBuf) == 17408 && sizeof(RawBuf) % 128 == 0, "tile offsets must stay 128-byte aligned");
+static_assert(TC * OT_PITCH * 4 <= int(sizeof(float) * TC * (kDV + 16)), "padded o tile must end inside v + ab");
 
 struct MmaSmem {
     RawBuf raw[3];                           // ring: chunk c uses raw[c % 3] until its deferred gated norm is done
@@ -129,16 +134,12 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
     // warp 1: k channels; warps 2, 3: v columns 2 (tid - 64), + 1.  Conv tap j multiplies x[t - 3 + j].
     const int pc0 = warp == 0 ? 2 * lane : warp == 1 ? 2 * lane : 2 * (tid - 64);       // first channel within its stream
     const int cw0 = (warp == 0 ? 0 : warp == 1 ? 384 : 768) + head * (warp < 2 ? kDK : kDV) + pc0;
-    float2 wx, wy, wz, ww, bc2;
-    {
-        const float4 w0 = *reinterpret_cast<const float4*>(conv_w + cw0 * 4);
-        const float4 w1 = *reinterpret_cast<const float4*>(conv_w + cw0 * 4 + 4);
-        wx = make_float2(w0.x, w1.x); wy = make_float2(w0.y, w1.y); wz = make_float2(w0.z, w1.z); ww = make_float2(w0.w, w1.w);
-        bc2 = make_float2(conv_b[cw0], conv_b[cw0 + 1]);
-    }
+    // taps and bias of the channel pair are re-read per chunk (L1 hits, issued ahead of the TMA wait) rather than held
+    // in ten registers across the whole recurrence
+    const float4* cwp = reinterpret_cast<const float4*>(conv_w + cw0 * 4);
+    const float2* cbp = reinterpret_cast<const float2*>(conv_b + cw0);
     float2 x1 = make_float2(0.0f, 0.0f), x2 = x1, x3 = x1;   // zero history = causal padding
     const float neg_rate = -expf(a_log[head]), dtb = dt_bias[head];
-    const float4 onw = *reinterpret_cast<const float4*>(o_norm_w + lane * 4);   // gated-norm weights of this lane's columns
 
     // S^T slice of this warp as accumulator fragments: S[mi][nj][.] = values dvb + 16 mi + {g, g + 8}, keys 8 nj + 2t, + 1
     float S[2][8][4];
@@ -177,12 +178,13 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         if (!tma::mbar_wait_bounded(gbars0 + 8u * uint32_t(pc % 3), uint32_t(pc / 3) & 1u, WAIT_POLLS)) return false;
         const float* ot = &pb.v[0][0];
         const float* gt_ = &pb.q[0][0];
+        const float4 onw = __ldg(reinterpret_cast<const float4*>(o_norm_w + lane * 4));
         const int pnt = min(min(TC, kTok - pc * TC), first + count);
 #pragma unroll
         for (int k = 0; k < 6; ++k) {
             const int i = min(first + k, TC - 1);
             const long long row = (long long)row_base + pc * TC + i;
-            const float4 o = *reinterpret_cast<const float4*>(&ot[i * kDV + lane * 4]);
+            const float4 o = *reinterpret_cast<const float4*>(&ot[i * OT_PITCH + lane * 4]);
             const float4 gt = *reinterpret_cast<const float4*>(&gt_[i * kDV + lane * 4]);
             const float4 pp = *reinterpret_cast<const float4*>(&sm.ssq[i][0]);   // the four warps' partial sums of o^2
             const float rstd = rsqrtf(((pp.x + pp.y) + (pp.z + pp.w)) * (1.0f / float(kDV)) + 1e-6f);
@@ -202,6 +204,9 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             tma::fence_proxy_async();
             if (chunk + 1 < NCHUNK) issue(chunk + 1);
         }
+        const float4 w0 = __ldg(cwp), w1 = __ldg(cwp + 1);
+        const float2 bc2 = __ldg(cbp);
+        const float2 wx = make_float2(w0.x, w1.x), wy = make_float2(w0.y, w1.y), wz = make_float2(w0.z, w1.z), ww = make_float2(w0.w, w1.w);
         if (!tma::mbar_wait_bounded(bars0 + 8u * uint32_t(chunk % 3), uint32_t(chunk / 3) & 1u, WAIT_POLLS)) {
             if (tid == 0) atomicCAS(&g_scan_mma_status, 0, 1);
             return;                                       // every thread times out on the same barrier and leaves
@@ -214,9 +219,13 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             uint32_t* dst = reinterpret_cast<uint32_t*>(warp == 0 ? &sm.qb[0][pc0] : &sm.kb[0][pc0]);
             uint32_t kt0[TC / 2], kt1[TC / 2];             // warp 1: two rows of K^T, two tokens per word
             float2 prev = make_float2(0.0f, 0.0f);
+            // all loads first: a tile store between them would order every later load behind it and serialise the tokens
+            float2 rawv[TC];
+#pragma unroll
+            for (int i = 0; i < TC; ++i) rawv[i] = *reinterpret_cast<const float2*>(src + i * kDK);
 #pragma unroll
             for (int i = 0; i < TC; ++i) {
-                const float2 raw = *reinterpret_cast<const float2*>(src + i * kDK);
+                const float2 raw = rawv[i];
                 float2 acc = ffma2(wx, x3, bc2);
                 acc = ffma2(wy, x2, acc);
                 acc = ffma2(wz, x1, acc);
@@ -239,12 +248,15 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             const float* src = &b.v[0][pc0];
             float4* r0 = reinterpret_cast<float4*>(&sm.vt[pc0][0]);                // rows of 80 bytes: 16-byte aligned
             float4* r1 = reinterpret_cast<float4*>(&sm.vt[pc0 + 1][0]);
+            float2 rawv[TC];
+#pragma unroll
+            for (int i = 0; i < TC; ++i) rawv[i] = *reinterpret_cast<const float2*>(src + i * kDV);
 #pragma unroll
             for (int i4 = 0; i4 < TC / 4; ++i4) {
                 float c0[4], c1[4];
 #pragma unroll
                 for (int ii = 0; ii < 4; ++ii) {
-                    const float2 raw = *reinterpret_cast<const float2*>(src + (4 * i4 + ii) * kDV);
+                    const float2 raw = rawv[4 * i4 + ii];
                     float2 acc = ffma2(wx, x3, bc2);
                     acc = ffma2(wy, x2, acc);
                     acc = ffma2(wz, x1, acc);
@@ -257,7 +269,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 r1[i4] = make_float4(c1[0], c1[1], c1[2], c1[3]);
             }
         }
-        if (warp == 3) {                                  // gates and the inclusive prefix sum of the log decays
+        if (warp == 0) {                                  // gates and the inclusive prefix sum of the log decays
             // tokens past the sequence end are made inert: beta = 0, no decay
             const bool valid = lane < nt;
             // hardware exp / log: absolute error ~1e-7 on the log decay and on beta, far below the bf16 operands
@@ -437,14 +449,27 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         float* otile = &b.v[0][0];                        // raw v is consumed: the tile now collects o[token][value]
         float sq[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};    // sum of o^2 over this thread's value rows, per token 8 ni + 2t + e
         uint32_t da[2][4];                                // decay-scaled U^T as A fragments, for the state update
+        // every shared-memory load of this phase is issued before its first o-tile store (a store would hold back the
+        // loads behind it): V^T for both row halves and the K^T fragments of the state update
+        float2 vv[2][2][2];
+        uint32_t kf[8][2];
+#pragma unroll
+        for (int nj = 0; nj < 8; ++nj) { kf[nj][0] = ktw[(8 * nj + g) * 12 + t]; kf[nj][1] = ktw[(8 * nj + g) * 12 + t + 4]; }
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+                vv[mi][ni][0] = *reinterpret_cast<const float2*>(&sm.vt[dvb + 16 * mi + g][8 * ni + 2 * t]);
+                vv[mi][ni][1] = *reinterpret_cast<const float2*>(&sm.vt[dvb + 16 * mi + g + 8][8 * ni + 2 * t]);
+            }
 #pragma unroll
         for (int mi = 0; mi < 2; ++mi) {
             const int r0 = dvb + 16 * mi + g, r1 = r0 + 8;
             uint32_t va[4];
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni) {
-                const float2 v0 = *reinterpret_cast<const float2*>(&sm.vt[r0][8 * ni + 2 * t]);
-                const float2 v1 = *reinterpret_cast<const float2*>(&sm.vt[r1][8 * ni + 2 * t]);
+                const float2 v0 = vv[mi][ni][0];
+                const float2 v1 = vv[mi][ni][1];
                 va[2 * ni] = pack_bf16(v0.x - er[ni][0] * R[mi][ni][0], v0.y - er[ni][1] * R[mi][ni][1]);
                 va[2 * ni + 1] = pack_bf16(v1.x - er[ni][0] * R[mi][ni][2], v1.y - er[ni][1] * R[mi][ni][3]);
             }
@@ -471,12 +496,26 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 const int tok = 8 * ni + 2 * t;
                 const float o00 = O[0] + eq[ni][0] * QS[mi][ni][0], o01 = O[1] + eq[ni][1] * QS[mi][ni][1];
                 const float o10 = O[2] + eq[ni][0] * QS[mi][ni][2], o11 = O[3] + eq[ni][1] * QS[mi][ni][3];
-                otile[tok * kDV + r0] = o00;
-                otile[(tok + 1) * kDV + r0] = o01;
-                otile[tok * kDV + r1] = o10;
-                otile[(tok + 1) * kDV + r1] = o11;
+                otile[tok * OT_PITCH + r0] = o00;
+                otile[(tok + 1) * OT_PITCH + r0] = o01;
+                otile[tok * OT_PITCH + r1] = o10;
+                otile[(tok + 1) * OT_PITCH + r1] = o11;
                 sq[ni][0] = fmaf(o00, o00, fmaf(o10, o10, sq[ni][0]));
                 sq[ni][1] = fmaf(o01, o01, fmaf(o11, o11, sq[ni][1]));
+            }
+        }
+        // ---------------------------------------------------------------- S^T <- e_last S^T + (diag(d) U)^T K
+        {
+            const float elast = sm.eg[TC - 1];
+#pragma unroll
+            for (int nj = 0; nj < 8; ++nj) {
+                const uint32_t b0 = kf[nj][0], b1 = kf[nj][1];
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) S[mi][nj][e] *= elast;
+                    mma16816(S[mi][nj], da[mi], b0, b1);
+                }
             }
         }
         // this warp's share of sum(o^2): reduce over the eight row groups g (lane bits 2-4), lanes 0-3 publish it
@@ -490,20 +529,6 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 v += __shfl_xor_sync(0xffffffffu, v, 16);
                 if (g == 0) sm.ssq[8 * ni + 2 * t + e][warp] = v;
             }
-        // ---------------------------------------------------------------- S^T <- e_last S^T + (diag(d) U)^T K
-        {
-            const float elast = sm.eg[TC - 1];
-#pragma unroll
-            for (int nj = 0; nj < 8; ++nj) {
-                const uint32_t b0 = ktw[(8 * nj + g) * 12 + t], b1 = ktw[(8 * nj + g) * 12 + t + 4];
-#pragma unroll
-                for (int mi = 0; mi < 2; ++mi) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) S[mi][nj][e] *= elast;
-                    mma16816(S[mi][nj], da[mi], b0, b1);
-                }
-            }
-        }
         __syncthreads();                                  // o tile complete; operand tiles free for the next chunk
     }
     if (!gated_norm(NCHUNK - 1, 4 * warp, 4)) atomicCAS(&g_scan_mma_status, 0, 2);

@@ -218,6 +218,13 @@ __device__ __forceinline__ void stage_block(const TcParams& p, uint32_t tile, in
     } else {
         const uint32_t row = tile + uint32_t(lane) * (full ? 128u : 64u);
         const uint32_t sw = full ? uint32_t(lane & 7) : 0u;
+        float4 rr[8];
+        if constexpr (EPI == EPI_RESID) {
+            // all residual loads first: a store in between would hold back every load behind it
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j < 4 || full) rr[j] = lds128(row + ((uint32_t(j) ^ sw) << 4));
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             if (j < 4 || full) {
@@ -225,11 +232,10 @@ __device__ __forceinline__ void stage_block(const TcParams& p, uint32_t tile, in
                 float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
                                        __uint_as_float(r[4 * j + 3]));
                 if constexpr (EPI == EPI_RESID) {
-                    const float4 rr = lds128(addr);
                     if (p.r_div != 1.0f) {
-                        v.x = rr.x + v.x / p.r_div; v.y = rr.y + v.y / p.r_div; v.z = rr.z + v.z / p.r_div; v.w = rr.w + v.w / p.r_div;
+                        v.x = rr[j].x + v.x / p.r_div; v.y = rr[j].y + v.y / p.r_div; v.z = rr[j].z + v.z / p.r_div; v.w = rr[j].w + v.w / p.r_div;
                     } else {
-                        v.x = rr.x + v.x; v.y = rr.y + v.y; v.z = rr.z + v.z; v.w = rr.w + v.w;
+                        v.x = rr[j].x + v.x; v.y = rr[j].y + v.y; v.z = rr[j].z + v.z; v.w = rr[j].w + v.w;
                     }
                 } else if (p.bias) {
                     if (n + 4 * j < p.N) {
