@@ -42,6 +42,10 @@ METRIC = "clips_per_s_gdn_sisa_stack_b4096_t20"
 UNIT = "clips/s"
 NTOK, D = 321, 384
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per clip of one launch, from the ncu captures at B = 512 in the 16-bit
+# modes that are summarised under profiles/ (traffic grows in proportion to the clips of a launch: every clip's tiles
+# are fetched and written once); scaled to the bench's B for the `traffic` key
+NCU_TRAFFIC_PER_CLIP = {"gdn_scan": (1.596182e9 + 0.245206e9) / 512, "gemm.in_proj": (0.128123e9 + 1.469240e9) / 512}
 
 
 def peaks():
@@ -289,7 +293,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     else:
         roof = {"bound": "hbm", "achieved": k["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": k["gbs"] / pk["hbm_gbs"]}
     roof.update({"kernel": top, "peak_source": pk_src, "share_of_step": k["share"], "avg_launch_ms": k["avg_ms"],
-                 "algorithmic_bytes_per_launch": B * nbytes, "traffic": None})
+                 "algorithmic_bytes_per_launch": B * nbytes,
+                 "traffic": B * NCU_TRAFFIC_PER_CLIP[top] if storage == 2 and top in NCU_TRAFFIC_PER_CLIP else None,
+                 "traffic_source": "ncu capture at B = 512, scaled by clips" if storage == 2 and top in NCU_TRAFFIC_PER_CLIP else None})
     alg_bytes_clip = 45853824 if mode == "fp32" else 37471872
     stack_frac = B * alg_bytes_clip / (ms_step / 1000.0) / (pk["hbm_gbs"] * 1e9)
     launches = eng.launches() * args.steps * world
