@@ -9,10 +9,12 @@ collective on the data path (weak scaling).  Rank 0 prints one JSON line:
 
   value      clips/s of the whole job with tokens already resident in HBM, timed with CUDA events on the launching
              stream, max over ranks
-  e2e        the same metric through the C ABI (one synchronous shv_cuda_classify of B clips per step) with host
+  e2e        the same metric through the C ABI (synchronous shv_cuda_classify calls covering B clips per step) with host
              buffers: pinned tokens are DMA'd to the device and logits read back inside the timed region, every step.
-             The scheduler option max_windows (--e2e-windows, default 512) makes classify split the call into jobs
-             whose uploads overlap the previous job's kernels (measured: 4096 -> 49k, 1024 -> 69k, 512 -> 74k clips/s)
+             The scheduler option max_windows (--e2e-windows, default 1024) makes classify split a call into jobs
+             whose uploads overlap the previous job's kernels, and --e2e-threads (default 2) host threads each classify
+             their share of the batch so that the queue does not drain between steps (measured, one caller:
+             max_windows 4096 -> 49k, 1024 -> 69k, 512 -> 79k clips/s; two callers: 512 -> 84k, 1024 -> 85k)
   roofline   for the kernel with the largest share of the step: algorithmic bytes (or flops) per launch / its mean
              launch time, measured here with CUDA events, against the measured peak in MEASURED_PEAKS.json
   cpu_baseline  the reference's exact-FP32 CPU engine (oracle/_ref) on the host cores, on a bounded sample (N=1 only)
@@ -312,12 +314,37 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         pin = binding.PinnedBuffer(model.L, (B, 20, 16, D))
         pin.array[...] = tokens.cpu().numpy()
         out = np.empty(B, np.float32)
-        for _ in range(max(1, min(args.warmup, 3))):
-            model.classify(pin.array, out)
+        # Callers: `nthr` host threads, each classifying its own contiguous share of the B clips with one synchronous
+        # call per step (the C ABI is thread-safe on one model).  With more than one caller the scheduler's queue does
+        # not drain between steps, so the upload of a call's first job overlaps the previous call's last kernels.
+        nthr = max(1, min(args.e2e_threads, B))
+        cuts = [B * i // nthr for i in range(nthr + 1)]
+
+        def caller(i, n_steps, errs):
+            lo, hi = cuts[i], cuts[i + 1]
+            try:
+                for _ in range(n_steps):
+                    model.classify(pin.array[lo:hi], out[lo:hi])
+            except Exception as e:                      # surfaced after the join
+                errs.append(e)
+
+        def run_steps(n_steps):
+            errs = []
+            if nthr == 1:
+                caller(0, n_steps, errs)
+            else:
+                ts = [threading.Thread(target=caller, args=(i, n_steps, errs)) for i in range(nthr)]
+                for th in ts:
+                    th.start()
+                for th in ts:
+                    th.join()
+            if errs:
+                raise errs[0]
+
+        run_steps(max(1, min(args.warmup, 3)))
         barrier()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
-            model.classify(pin.array, out)
+        run_steps(args.steps)
         dt = time.perf_counter() - t0
         barrier()
         e2e_ms = max_over_ranks(1000.0 * dt / args.steps)
@@ -325,7 +352,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             raise SystemExit("end-to-end run returned non-finite logits")
         e2e = {"value": world * B / (e2e_ms / 1000.0), "unit": UNIT, "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": B * 20 * 6144 * 4 + B * 20 * 8, "d2h_bytes_per_step": B * 4,
-               "api": "shv_cuda_classify(B clips), pinned host tokens (shv_cuda_host_alloc), max_windows = %d" % mw}
+               "api": "%d host thread(s), each one synchronous shv_cuda_classify of its B/%d clips per step; pinned host "
+                      "tokens (shv_cuda_host_alloc), max_windows = %d" % (nthr, nthr, mw)}
         model.close()
         pin.free()
 
@@ -363,7 +391,9 @@ def main():
     ap.add_argument("--mode", default="bf16", choices=["fp32", "bf16", "fp16"])
     ap.add_argument("--batch", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--e2e-windows", type=int, default=512,
+    ap.add_argument("--e2e-threads", type=int, default=2,
+                    help="host threads of the end-to-end leg, each calling shv_cuda_classify on its share of the batch")
+    ap.add_argument("--e2e-windows", type=int, default=1024,
                     help="scheduler option max_windows of the end-to-end leg: shv_cuda_classify splits a call into jobs of "
                          "this many clips, and the scheduler uploads job i+1 while job i computes")
     args = ap.parse_args()
