@@ -228,6 +228,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
     torch.cuda.set_device(local_rank)
     if world > 1 and not dist.is_initialized():
+        # NCCL writes its version banner to stdout; stdout carries the one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     def barrier():
