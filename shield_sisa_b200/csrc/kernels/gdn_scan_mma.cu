@@ -35,6 +35,8 @@
 // that chain, which costs more than the products themselves.  tcgen05 carries the projections (gemm_tc.cu).
 //
 // Reference: engine/cuda/seq.cu:72-214 (gdn_prep + delta + gated_norm), oracle/shieldv_ref.py:121-163,186-197.
+#include <type_traits>
+
 #include "device_utils.cuh"
 #include "gdn_scan_mma.cuh"
 #include "tma_utils.cuh"
@@ -170,23 +172,23 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
 
     constexpr int NCHUNK = (kTok + TC - 1) / TC;
     // Gated RMSNorm of chunk pc (its o tile and gate tile sit in ring slot pc % 3), tokens first .. first + count - 1
-    // (count <= 6).  Loads and arithmetic run unconditionally (the tile rows exist), only the store is guarded, so the
+    // Loads and arithmetic run unconditionally (the tile rows exist), only the store is guarded, so the
     // unrolled tokens overlap.  Returns false if the gate tile never arrived.
-    auto gated_norm = [&](int pc, int first, int count) -> bool {
+    auto gated_norm = [&](int pc, int first, auto count_c) -> bool {
+        constexpr int count = decltype(count_c)::value;   // compile-time, so a warp with few tokens does only their work
         RawBuf& pb = sm.raw[pc % 3];
         if (!tma::mbar_wait_bounded(gbars0 + 8u * uint32_t(pc % 3), uint32_t(pc / 3) & 1u, WAIT_POLLS)) return false;
         const float* ot = &pb.v[0][0];
         const float* gt_ = &pb.q[0][0];
         const float4 onw = __ldg(reinterpret_cast<const float4*>(o_norm_w + lane * 4));
         const int pnt = min(min(TC, kTok - pc * TC), first + count);
-        // rows first .. first + 5 at constant offsets; rows past the tile are read (they lie inside this structure) and
-        // dropped by the store guard
+        // rows first .. first + count - 1 at constant offsets
         const float* op = ot + first * OT_PITCH + lane * 4;
         const float* gp = gt_ + first * kDV + lane * 4;
         const float* sp = &sm.ssq[first][0];
         T* dst = on + ((long long)row_base + pc * TC + first) * kVD + head * kDV + lane * 4;
 #pragma unroll
-        for (int k = 0; k < 6; ++k) {
+        for (int k = 0; k < count; ++k) {
             const float4 o = *reinterpret_cast<const float4*>(op + k * OT_PITCH);
             const float4 gt = *reinterpret_cast<const float4*>(gp + k * kDV);
             const float4 pp = *reinterpret_cast<const float4*>(sp + 4 * k);   // the four warps' partial sums of o^2
@@ -388,12 +390,14 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 }
             }
         }
-        // meanwhile the previous chunk is finished: its gated RMSNorm, six tokens each on warps 2 and 3 and the
-        // remaining four behind the shorter Gram work of warps 0 (one) and 1 (three)
+        // meanwhile the previous chunk is finished: its gated RMSNorm, seven tokens each on warps 2 and 3 and two behind
+        // the Gram work of warp 1 (warp 0 has the inverse)
         if (chunk > 0) {
-            const int first = warp == 0 ? 15 : warp == 1 ? 12 : 6 * (warp - 2);
-            const int count = warp == 0 ? 1 : warp == 1 ? 3 : 6;
-            if (!gated_norm(chunk - 1, first, count)) atomicCAS(&g_scan_mma_status, 0, 2);
+            bool ok;
+            if (warp == 0) ok = true;
+            else if (warp == 1) ok = gated_norm(chunk - 1, 14, std::integral_constant<int, 2>());
+            else ok = gated_norm(chunk - 1, 7 * (warp - 2), std::integral_constant<int, 7>());
+            if (!ok) atomicCAS(&g_scan_mma_status, 0, 2);
         }
         // ---------------------------------------------------------------- R^T = S0^T K^T and (Q S0)^T, all warps
         float R[2][2][4], QS[2][2][4];
@@ -533,7 +537,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             }
         __syncthreads();                                  // o tile complete; operand tiles free for the next chunk
     }
-    if (!gated_norm(NCHUNK - 1, 4 * warp, 4)) atomicCAS(&g_scan_mma_status, 0, 2);
+    if (!gated_norm(NCHUNK - 1, 4 * warp, std::integral_constant<int, 4>())) atomicCAS(&g_scan_mma_status, 0, 2);
 }
 
 }  // namespace
