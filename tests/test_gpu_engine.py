@@ -152,3 +152,22 @@ def test_classify_splits_large_requests(weight_files):
         a = small.classify(tok)          # step = min(8, 100 // 20) = 5 windows per job
         b = big.classify(tok)
     np.testing.assert_array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_full_size_batch_is_row_independent_and_within_tolerance(weight_files):
+    """The bench's size (4096 clips in one batch, bf16): every logit equals, bit for bit, the logit of the same clip in
+    a 64-clip batch of another size class (duplicates included), and three clips are checked against the float64
+    oracle."""
+    path, w = weight_files("W3", 1)
+    base = W.synth_tokens(64, 11)
+    idx = np.random.default_rng(3).integers(0, 64, 4096)
+    idx[:64] = np.arange(64)
+    tok = np.ascontiguousarray(base[idx])
+    with binding.CudaModel(path, "bf16", max_windows=4096, max_host_tokens=20 * 4096, experimental=True) as big, \
+            binding.CudaModel(path, "bf16", max_windows=64, max_host_tokens=1280, experimental=True) as small:
+        full = big.classify(tok)
+        ref64 = small.classify(base)
+    assert np.isfinite(full).all()
+    np.testing.assert_array_equal(full.view(np.uint32), ref64[idx].view(np.uint32))
+    want = O.classify_tokens(w, base[:3].astype(np.float64), np.float64)
+    assert rel_err(full[:3], want) <= LOWP_TOL
