@@ -75,7 +75,7 @@ struct MmaSmem {
     __nv_bfloat16 t2[TC][KT_PITCH];          // (I + L)^-1 diag(beta)
     __nv_bfloat16 mq[TC][KT_PITCH];          // decay-masked Q K^T
     float ssq[TC][4];                        // per token: each warp's share of sum(o^2) over its 32 value columns
-    float iq[TC], ik[TC], lg[TC], beta[TC];  // 0.125/|q|, 1/|k|, warp 1's copy of 1/|k|, beta (0 beyond the sequence end)
+    float iq[TC], ik[TC], beta[TC];          // 0.125/|q|, 1/|k|, beta (0 beyond the sequence end)
     float cum[TC], eg[TC], dj[TC];           // c_i, exp(c_i), exp(c_last - c_i)
     unsigned long long full[3], gfull[3];    // mbarriers: raw tiles / gate tile of the chunk in ring slot i landed
 };
@@ -306,12 +306,12 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         const uint32_t* qbw = reinterpret_cast<const uint32_t*>(&sm.qb[0][0]);
         // ---------------------------------------------------------------- warp 0: norms of k, L, T2; warp 1: norms, masked Q K^T
         if (warp < 2) {
-            // Gram products over the 64 keys: warp 0 K K^T; warp 1 Q K^T, and the diagonals of Q Q^T and K K^T
-            float acc[2][4], dq[2][4], dk[2][4];
+            // Gram products over the 64 keys: warp 0 K K^T; warp 1 Q K^T and the diagonal of Q Q^T
+            float acc[2][4], dq[2][4];
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) { acc[ni][e] = 0.0f; dq[ni][e] = 0.0f; dk[ni][e] = 0.0f; }
+                for (int e = 0; e < 4; ++e) { acc[ni][e] = 0.0f; dq[ni][e] = 0.0f; }
             const uint32_t* xa = warp == 0 ? kbw : qbw;
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
@@ -321,12 +321,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 for (int ni = 0; ni < 2; ++ni) {
                     const uint32_t k0 = kbw[(8 * ni + g) * 36 + 8 * p + t], k1 = kbw[(8 * ni + g) * 36 + 8 * p + t + 4];
                     mma16816(acc[ni], a, k0, k1);
-                    if (warp == 1) {
-                        mma16816(dq[ni], a, qbw[(8 * ni + g) * 36 + 8 * p + t], qbw[(8 * ni + g) * 36 + 8 * p + t + 4]);
-                        const uint32_t ka[4] = {kbw[g * 36 + 8 * p + t], kbw[(g + 8) * 36 + 8 * p + t], kbw[g * 36 + 8 * p + t + 4],
-                                                kbw[(g + 8) * 36 + 8 * p + t + 4]};
-                        mma16816(dk[ni], ka, k0, k1);
-                    }
+                    if (warp == 1) mma16816(dq[ni], a, qbw[(8 * ni + g) * 36 + 8 * p + t], qbw[(8 * ni + g) * 36 + 8 * p + t + 4]);
                 }
             }
             // diagonal entries: row g sits in tile 0 at column 2t + e == g, row g + 8 in tile 1 at the same lane / slot
@@ -338,13 +333,10 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 } else {
                     sm.iq[g] = rsqrtf((odd ? dq[0][1] : dq[0][0]) + 1e-6f) * 0.125f;
                     sm.iq[g + 8] = rsqrtf((odd ? dq[1][3] : dq[1][2]) + 1e-6f) * 0.125f;
-                    sm.lg[g] = rsqrtf((odd ? dk[0][1] : dk[0][0]) + 1e-6f);   // warp 1's own copy of 1/|k| (sm.lg is free here)
-                    sm.lg[g + 8] = rsqrtf((odd ? dk[1][3] : dk[1][2]) + 1e-6f);
                 }
             }
             __syncwarp();
             // acc[ni][0,1]: row i = g, columns j = 8 ni + 2t, + 1;  acc[ni][2,3]: row i = g + 8
-            const float* ikv = warp == 0 ? sm.ik : sm.lg;
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni)
 #pragma unroll
@@ -352,8 +344,9 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                     const int i = g + (e >> 1) * 8, j = 8 * ni + 2 * t + (e & 1);
                     const bool keep = warp == 0 ? j < i : j <= i;
                     const float dec = __expf(keep ? sm.cum[i] - sm.cum[j] : 0.0f);
-                    const float rowf = warp == 0 ? sm.beta[i] * ikv[i] : sm.iq[i];
-                    acc[ni][e] = keep ? dec * acc[ni][e] * rowf * ikv[j] : 0.0f;
+                    // warp 0: L_ij carries both key norms; warp 1: the key norm of column j is applied to U in the O product
+                    const float f = warp == 0 ? sm.beta[i] * sm.ik[i] * sm.ik[j] : sm.iq[i];
+                    acc[ni][e] = keep ? dec * acc[ni][e] * f : 0.0f;
                 }
             if (warp == 0) {
 #pragma unroll
@@ -435,7 +428,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
         const uint32_t* ktw = reinterpret_cast<const uint32_t*>(&sm.kt[0][0]);
         // per-token scalars of this lane's tokens 8 ni + 2t, + 1, with the norms folded in:
         //   er = exp(c) / |k|  (R = K S0),  eq = exp(c) * 0.125 / |q|  (Q S0),  dj2 = exp(c_last - c) / |k|  (state update)
-        float er[2][2], eq[2][2], dj2[2][2];
+        float er[2][2], eq[2][2], dj2[2][2], ikt[2][2];
 #pragma unroll
         for (int ni = 0; ni < 2; ++ni)
 #pragma unroll
@@ -445,6 +438,7 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
                 er[ni][e] = egv * ikv;
                 eq[ni][e] = egv * sm.iq[tok];
                 dj2[ni][e] = sm.dj[tok] * ikv;
+                ikt[ni][e] = ikv;
             }
         uint32_t bt[2][2], bm[2][2];
 #pragma unroll
@@ -489,8 +483,8 @@ gdn_scan_mma_kernel(const __grid_constant__ MmaMaps maps, const float* __restric
             uint32_t ua[4];
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni) {
-                ua[2 * ni] = pack_bf16(U[ni][0], U[ni][1]);
-                ua[2 * ni + 1] = pack_bf16(U[ni][2], U[ni][3]);
+                ua[2 * ni] = pack_bf16(U[ni][0] * ikt[ni][0], U[ni][1] * ikt[ni][1]);      // U / |k| for the O product
+                ua[2 * ni + 1] = pack_bf16(U[ni][2] * ikt[ni][0], U[ni][3] * ikt[ni][1]);
                 da[mi][2 * ni] = pack_bf16(U[ni][0] * dj2[ni][0], U[ni][1] * dj2[ni][1]);
                 da[mi][2 * ni + 1] = pack_bf16(U[ni][2] * dj2[ni][0], U[ni][3] * dj2[ni][1]);
             }

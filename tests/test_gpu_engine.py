@@ -156,8 +156,8 @@ def test_classify_splits_large_requests(weight_files):
 
 def test_full_size_batch_is_row_independent_and_within_tolerance(weight_files):
     """The bench's size (4096 clips in one batch, bf16): every logit equals, bit for bit, the logit of the same clip in
-    a 64-clip batch of another size class (duplicates included), and three clips are checked against the float64
-    oracle."""
+    a 64-clip batch of another size class (duplicates included), and the distinct clips are checked against the
+    reference CPU engine."""
     path, w = weight_files("W3", 1)
     base = W.synth_tokens(64, 11)
     idx = np.random.default_rng(3).integers(0, 64, 4096)
@@ -169,5 +169,16 @@ def test_full_size_batch_is_row_independent_and_within_tolerance(weight_files):
         ref64 = small.classify(base)
     assert np.isfinite(full).all()
     np.testing.assert_array_equal(full.view(np.uint32), ref64[idx].view(np.uint32))
-    want = O.classify_tokens(w, base[:3].astype(np.float64), np.float64)
-    assert rel_err(full[:3], want) <= LOWP_TOL
+    # the 64 distinct clips against the reference's exact-fp32 CPU engine (the float64 oracle on a few clips where the
+    # compiled reference is not present); the error is normalised by the largest logit of the set
+    if ref_cpu.available():
+        eng = ref_cpu.RefCpuEngine(path, threads=8)
+        want = eng.classify(base)
+        eng.close()
+        got = ref64
+    else:
+        want = O.classify_tokens(w, base[:8].astype(np.float64), np.float64)
+        got = ref64[:8]
+    err = rel_err(got, want)
+    print(f"full-size bf16 logits: rel err {err:.3e} over {len(want)} clips")
+    assert err <= LOWP_TOL
