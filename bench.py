@@ -47,7 +47,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per clip of one launch, from the ncu captures at B = 512 in the 16-bit
 # modes that are summarised under profiles/ (traffic grows in proportion to the clips of a launch: every clip's tiles
 # are fetched and written once); scaled to the bench's B for the `traffic` key
-NCU_TRAFFIC_PER_CLIP = {"gdn_scan": (1.596182e9 + 0.245206e9) / 512, "gemm.in_proj": (0.128123e9 + 1.469240e9) / 512}
+NCU_TRAFFIC_PER_CLIP = {"gdn_scan": (1.596298e9 + 0.246092e9) / 512, "gemm.in_proj": (0.128123e9 + 1.469240e9) / 512}
 
 
 def peaks():
