@@ -1,6 +1,6 @@
 """Regenerates tests/golden/*.npz by running the REFERENCE's own code on seeded synthetic inputs.
 
-Runs only where the reference checkout is present (pass its path, default /root/reference): it imports the
+Runs only where the reference checkout is present (pass its path as the first argument): it imports the
 reference's PyTorch oracle (oracle/shieldv_ref.py) and, if oracle/_ref/libshield_v_cpu.so has been built by
 oracle/Makefile, also runs the reference's exact-FP32 CPU engine.  The tests read only the .npz files; inputs are
 regenerated from the seeds stored in them (shield_sisa_b200/weights.py), so no weights or tokens are committed.
