@@ -34,7 +34,7 @@ template <int DK> struct ChunkSmem {
     __nv_bfloat16 t2[CB][CT_PITCH];
     __nv_bfloat16 mq[CB][CT_PITCH];
     float lf[CB][CB + 1];
-    float otile[CB][CDV];
+    float otile[CB][CDV + 4];                // padded rows: the fragment stores of a warp fall into 32 different banks
     float beta[CB], cum[CB], eg[CB], dj[CB];
 };
 
@@ -140,8 +140,8 @@ gdn_chunked_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __r
             if (lane < CB) {
                 sm.beta[lane] = pbeta;
                 sm.cum[lane] = c;
-                sm.eg[lane] = expf(c);
-                sm.dj[lane] = expf(last - c);
+                sm.eg[lane] = __expf(c);
+                sm.dj[lane] = __expf(last - c);
             }
         }
         if (t0 + CB < T) prefetch(t0 + CB);               // next block's loads fly while this one is computed
@@ -168,7 +168,7 @@ gdn_chunked_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __r
                 for (int e = 0; e < 4; ++e) {
                     const int i = g + (e >> 1) * 8, j = 8 * ni + 2 * t + (e & 1);
                     const bool keep = warp == 0 ? j < i : j <= i;
-                    const float dec = expf(keep ? sm.cum[i] - sm.cum[j] : 0.0f);
+                    const float dec = __expf(keep ? sm.cum[i] - sm.cum[j] : 0.0f);
                     const float rowf = warp == 0 ? sm.beta[i] : scale;
                     acc[ni][e] = keep ? dec * acc[ni][e] * rowf : 0.0f;
                 }
@@ -182,13 +182,17 @@ gdn_chunked_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __r
                     float x[CB];
 #pragma unroll
                     for (int i = 0; i < CB; ++i) {
-                        float s0 = i == lane ? 1.0f : 0.0f, s1 = 0.0f;
+                        // four partial sums: the dependent chain per row is i / 4 long instead of i
+                        float s0 = i == lane ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
                         for (int j = 0; j < i; ++j) {
-                            if (j & 1) s1 = fmaf(-sm.lf[i][j], x[j], s1);
-                            else s0 = fmaf(-sm.lf[i][j], x[j], s0);
+                            const float l = sm.lf[i][j];
+                            if ((j & 3) == 0) s0 = fmaf(-l, x[j], s0);
+                            else if ((j & 3) == 1) s1 = fmaf(-l, x[j], s1);
+                            else if ((j & 3) == 2) s2 = fmaf(-l, x[j], s2);
+                            else s3 = fmaf(-l, x[j], s3);
                         }
-                        x[i] = s0 + s1;
+                        x[i] = (s0 + s1) + (s2 + s3);
                     }
                     const float bc = sm.beta[lane];
 #pragma unroll
@@ -249,14 +253,23 @@ gdn_chunked_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __r
             bm[ni][0] = mqw[(8 * ni + g) * 12 + t]; bm[ni][1] = mqw[(8 * ni + g) * 12 + t + 4];
         }
         uint32_t da[MI][4];
+        // V^T for all row tiles is loaded before the first o-tile store (a store would hold back the loads behind it)
+        float2 vv[MI][2][2];
+#pragma unroll
+        for (int mi = 0; mi < MI; ++mi)
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+                vv[mi][ni][0] = *reinterpret_cast<const float2*>(&sm.vt[dvb + 16 * mi + g][8 * ni + 2 * t]);
+                vv[mi][ni][1] = *reinterpret_cast<const float2*>(&sm.vt[dvb + 16 * mi + g + 8][8 * ni + 2 * t]);
+            }
 #pragma unroll
         for (int mi = 0; mi < MI; ++mi) {
             const int r0 = dvb + 16 * mi + g, r1 = r0 + 8;
             uint32_t va[4];
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni) {
-                const float2 v0 = *reinterpret_cast<const float2*>(&sm.vt[r0][8 * ni + 2 * t]);
-                const float2 v1 = *reinterpret_cast<const float2*>(&sm.vt[r1][8 * ni + 2 * t]);
+                const float2 v0 = vv[mi][ni][0];
+                const float2 v1 = vv[mi][ni][1];
                 va[2 * ni] = cpack(v0.x - er[ni][0] * R[mi][ni][0], v0.y - er[ni][1] * R[mi][ni][1]);
                 va[2 * ni + 1] = cpack(v1.x - er[ni][0] * R[mi][ni][2], v1.y - er[ni][1] * R[mi][ni][3]);
             }
