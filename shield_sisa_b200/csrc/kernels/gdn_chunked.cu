@@ -77,7 +77,9 @@ gdn_chunked_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __r
 #pragma unroll
             for (int e = 0; e < 4; ++e) S[mi][nj][e] = 0.0f;
 
-    // global -> register prefetch of one block: 16-byte vectors of q and k rows (DK / 8 per row), v rows (16 per row)
+    // global -> register prefetch of one block: 16-byte vectors of q and k rows (DK / 8 per row), v rows (16 per row).
+    // Lanes run over the 16 tokens first (two adjacent vectors per token and warp instruction = whole 32-byte
+    // sectors): the transposing stores into K^T and V^T then hit 16 different banks instead of one.
     constexpr int QK_VECS = CB * DK / 8, V_VECS = CB * CDV / 8;
     constexpr int QK_PER = (QK_VECS + NTHR - 1) / NTHR, V_PER = V_VECS / NTHR;
     uint4 pq[QK_PER], pk[QK_PER], pv[V_PER];
@@ -85,14 +87,14 @@ gdn_chunked_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __r
     auto prefetch = [&](int t0) {
 #pragma unroll
         for (int r = 0; r < QK_PER; ++r) {
-            const int idx = tid + r * NTHR, row = idx / (DK / 8), c8 = idx % (DK / 8);
+            const int idx = tid + r * NTHR, row = idx % CB, c8 = idx / CB;
             const bool ok = idx < QK_VECS && t0 + row < T;
             pq[r] = ok ? *reinterpret_cast<const uint4*>(Qs + (long long)(t0 + row) * tok_stride_k + c8 * 8) : make_uint4(0, 0, 0, 0);
             pk[r] = ok ? *reinterpret_cast<const uint4*>(Ks + (long long)(t0 + row) * tok_stride_k + c8 * 8) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int r = 0; r < V_PER; ++r) {
-            const int idx = tid + r * NTHR, row = idx / 16, c8 = idx % 16;
+            const int idx = tid + r * NTHR, row = idx % CB, c8 = idx / CB;
             pv[r] = t0 + row < T ? *reinterpret_cast<const uint4*>(Vs + (long long)(t0 + row) * tok_stride_v + c8 * 8) : make_uint4(0, 0, 0, 0);
         }
         if (tid < CB) {                                   // tokens past the end are inert: no decay, beta = 0
@@ -113,7 +115,7 @@ gdn_chunked_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __r
         // ---------------------------------------------------------------- registers -> operand tiles
 #pragma unroll
         for (int r = 0; r < QK_PER; ++r) {
-            const int idx = tid + r * NTHR, row = idx / (DK / 8), c8 = idx % (DK / 8);
+            const int idx = tid + r * NTHR, row = idx % CB, c8 = idx / CB;
             if (idx < QK_VECS) {
                 *reinterpret_cast<uint4*>(&sm.qb[row][c8 * 8]) = pq[r];
                 *reinterpret_cast<uint4*>(&sm.kb[row][c8 * 8]) = pk[r];
@@ -124,7 +126,7 @@ gdn_chunked_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __r
         }
 #pragma unroll
         for (int r = 0; r < V_PER; ++r) {
-            const int idx = tid + r * NTHR, row = idx / 16, c8 = idx % 16;
+            const int idx = tid + r * NTHR, row = idx % CB, c8 = idx / CB;
             const __nv_bfloat16* vv = reinterpret_cast<const __nv_bfloat16*>(&pv[r]);
 #pragma unroll
             for (int e = 0; e < 8; ++e) sm.vt[c8 * 8 + e][row] = __bfloat162float(vv[e]);
