@@ -214,7 +214,7 @@ def run_reference(args, rank: int):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ---------------------------------------------------------------------------------------------- our arm
@@ -379,12 +379,26 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                    "note": "whole stack against the GEMM-boundary byte model and the measured HBM peak"},
             "kernels": kernels,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+RESULT_FD = None     # a duplicate of the real stdout, kept for the one JSON line
+
+
+def emit(line: dict):
+    data = (json.dumps(line) + "\n").encode()
+    os.write(RESULT_FD if RESULT_FD is not None else 1, data)
+
+
 def main():
+    # stdout carries the one JSON line only: everything else a library may print there (NCCL's version banner, for
+    # one) is sent to stderr for the whole run
+    global RESULT_FD
+    sys.stdout.flush()
+    RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
