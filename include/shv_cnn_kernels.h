@@ -1,0 +1,69 @@
+/*
+ * shv_cnn_kernels.h -- thin C launch layer over the sm_100a frame-encoder kernels of the SHIELD-V engine
+ * (MobileNetV3-Large features on 320x180 crops, 4x4 pooling; the 960 -> 384 token projection is shvk_gemm_f32).
+ *
+ * Same conventions as shv_seq_kernels.h: every pointer is a device pointer, `stream` is a cudaStream_t passed as
+ * void*, every function only enqueues work and returns a cudaError_t value (0 = success).  Activations are float32 in
+ * NHWC order ([frame][row][column][channel]); BatchNorm is folded into weights and biases by the caller.
+ * Activation codes: 0 none, 1 ReLU, 2 Hardswish (x * relu6(x + 3) / 6), 4 Hardsigmoid (relu6(x + 3) / 6).
+ *
+ * Each entry replaces one launcher of the reference engine; citations are to the reference tree.
+ */
+#ifndef SHV_CNN_KERNELS_H
+#define SHV_CNN_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+enum { SHVK_ACT_NONE = 0, SHVK_ACT_RELU = 1, SHVK_ACT_HSWISH = 2, SHVK_ACT_HSIGMOID = 4 };
+
+/* Stem: uint8 RGB crops [F][180][320][3] -> normalisation through lut ([3][256]: ((u / 255) - mean_c) / std_c)
+ * -> 3x3 convolution, stride 2, padding 1, 16 output channels -> + b -> Hardswish -> out [F][90][160][16].
+ * w: [27][16], tap-major: ((kh * 3 + kw) * 3 + ci) * 16 + co.
+ * Replaces launch_stem (engine/cuda/cnn.cu:8-50,164-167). */
+int shvk_cnn_stem(const uint8_t* frames, const float* lut, const float* w, const float* b, float* out, int F,
+                  void* stream);
+
+/* Depthwise KxK convolution (K 3 or 5, stride 1 or 2, padding (K-1)/2) + b + activation.
+ * in [F][H][W][C] -> out [F][Ho][Wo][C]; w: [K*K][C] tap-major; C a multiple of 4.
+ * Replaces launch_dw (engine/cuda/cnn.cu:52-95,169-179). */
+int shvk_cnn_depthwise(const float* in, const float* w, const float* b, float* out, int F, int H, int W, int C, int K,
+                       int stride, int Ho, int Wo, int act, void* stream);
+
+/* Squeeze-excite gate of F frames: mean over the HW pixels of each channel, fc1 + ReLU, fc2 + Hardsigmoid.
+ * x [F][HW][C]; w1 [CS][C], b1 [CS]; w2 [C][CS], b2 [C]; gate [F][C].  The mean is taken in two stages with a split
+ * that depends only on HW (64-pixel groups, combined in order), so a frame's gate does not depend on F.
+ * `partial` is scratch the caller provides: shvk_cnn_se_partial_floats(F, HW, C) floats; it need not be cleared.
+ * Replaces launch_se_pool and the two squeeze-excite GEMMs (engine/cuda/cnn.cu:97-131,181-186;
+ * engine/cuda/engine.cu:367-376). */
+size_t shvk_cnn_se_partial_floats(int F, int HW, int C);
+int shvk_cnn_se_gate(const float* x, float* partial, const float* w1, const float* b1, const float* w2, const float* b2,
+                     float* gate, int F, int HW, int C, int CS, void* stream);
+
+/* 1x1 convolution as a row GEMM: out[m][n] = act(sum_k (A[m][k] * gate[m / gate_rows][k]) * W[n][k] + b[n]) (+ R[m][n]).
+ * A [M][K] (pitch K), W [N][K], out and R [M][N] (R may alias out); gate NULL = no squeeze-excite scaling, else
+ * [M / gate_rows][K]; K and N multiples of 4.  Each output is one fma chain over k in order.
+ * Replaces gemm<T> as used by the frame encoder (engine/cuda/engine.cu:351-355,378-382,398-400;
+ * engine/cuda/gemm.cuh:16-29). */
+int shvk_cnn_pointwise(const float* A, const float* W, const float* b, const float* gate, int gate_rows, const float* R,
+                       float* out, int M, int N, int K, int act, void* stream);
+
+/* Adaptive 4x4 average pooling of the [F][6][10][960] feature map: token r*4+c averages rows floor(6r/4) ..
+ * ceil(6(r+1)/4)-1 and columns floor(10c/4) .. ceil(10(c+1)/4)-1.  out [F][16][960].
+ * Replaces launch_pool (engine/cuda/cnn.cu:133-160,188-191). */
+int shvk_cnn_pool_tokens(const float* in, float* out, int F, void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHV_CNN_KERNELS_H */

@@ -34,7 +34,19 @@ int shv_cuda_b200_launches_per_batch(const shv_cuda_model* m);
  * max_windows may exceed the 4096 cap of the job API.  Every int function returns 0 or -1 (+ shv_cuda_last_error). */
 typedef struct shvb_engine shvb_engine;
 shvb_engine* shvb_engine_create(const char* weights, const char* mode, int device, int max_windows, int use_graphs);
+/* The same with a frame budget: slots hold up to max_frames RGB crops and their tokens (shvb_engine_create gives 1). */
+shvb_engine* shvb_engine_create_ex(const char* weights, const char* mode, int device, int max_frames, int max_windows,
+                                   int use_graphs);
 void shvb_engine_destroy(shvb_engine* e);
+/* Frame encoder (Engine::encode, engine/cuda/engine.hpp:46): reads F uint8 RGB crops [F][180][320][3] from
+ * shvb_engine_frames(e, slot) and writes their tokens [F][16][384] fp32 to shvb_engine_tokens(e, slot), on `stream`. */
+uint8_t* shvb_engine_frames(shvb_engine* e, int slot);               /* device pointer, [max_frames][172800] */
+float* shvb_engine_tokens(shvb_engine* e, int slot);                 /* device pointer, [max_frames][6144] */
+int shvb_engine_encode(shvb_engine* e, int slot, int F, void* stream);
+int shvb_engine_frame_bucket(const shvb_engine* e, int F);           /* size class a batch of F frames is padded to */
+int shvb_engine_encode_launches(const shvb_engine* e);               /* kernels per encode */
+/* shvb_engine_profile for one eager encode of F frames. */
+int shvb_engine_profile_encode(shvb_engine* e, int slot, int F, void* stream, float* ms, int cap, char* names, int names_cap);
 /* Points window w, frame f of `slot` (0 or 1) at d_tokens + (w*20 + f)*6144: B windows of device-resident tokens
  * [B][20][16][384] fp32.  The table upload is enqueued on `stream`. */
 int shvb_engine_bind_tokens(shvb_engine* e, int slot, const float* d_tokens, int B, void* stream);

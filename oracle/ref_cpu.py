@@ -36,6 +36,10 @@ class RefCpuEngine:
         L.shv_cpu_free.argtypes = [C.c_void_p]
         L.shv_cpu_classify.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
         L.shv_cpu_classify.restype = C.c_int
+        L.shv_cpu_encode_frames.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.shv_cpu_encode_frames.restype = C.c_int
+        L.shv_cpu_predict.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.shv_cpu_predict.restype = C.c_int
         L.shv_cpu_last_error.restype = C.c_char_p
         L.shv_cpu_isa.restype = C.c_char_p
         L.shv_cpu_isa.argtypes = [C.c_void_p]
@@ -55,6 +59,26 @@ class RefCpuEngine:
             raise ValueError("expected [B,20,16,384] float32 tokens")
         out = np.empty(t.shape[0], np.float32)
         if self.lib.shv_cpu_classify(self.h, t.ctypes.data, t.shape[0], out.ctypes.data):
+            raise RuntimeError(self.lib.shv_cpu_last_error().decode())
+        return out
+
+    def encode_frames(self, frames) -> np.ndarray:
+        """uint8 crops [N,180,320,3] -> tokens [N,16,384] (shv_cpu_encode_frames, engine/include/shv_cpu.h:99-101)."""
+        f = np.ascontiguousarray(frames, dtype=np.uint8)
+        if f.ndim != 4 or f.shape[1:] != (180, 320, 3):
+            raise ValueError("expected [N,180,320,3] uint8 crops")
+        out = np.empty((f.shape[0], 16, 384), np.float32)
+        if self.lib.shv_cpu_encode_frames(self.h, f.ctypes.data, f.shape[0], out.ctypes.data):
+            raise RuntimeError(self.lib.shv_cpu_last_error().decode())
+        return out
+
+    def predict(self, clips) -> np.ndarray:
+        """uint8 clips [B,20,180,320,3] -> logits [B] (shv_cpu_predict, engine/include/shv_cpu.h:111-112)."""
+        c = np.ascontiguousarray(clips, dtype=np.uint8)
+        if c.ndim != 5 or c.shape[1:] != (20, 180, 320, 3):
+            raise ValueError("expected [B,20,180,320,3] uint8 clips")
+        out = np.empty(c.shape[0], np.float32)
+        if self.lib.shv_cpu_predict(self.h, c.ctypes.data, c.shape[0], out.ctypes.data):
             raise RuntimeError(self.lib.shv_cpu_last_error().decode())
         return out
 

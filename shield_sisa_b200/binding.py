@@ -82,7 +82,14 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shv_cuda_b200_upload_tokens": (i32, [vp, vp, sz, vp]),
         "shv_cuda_b200_launches_per_batch": (i32, [vp]),
         "shvb_engine_create": (vp, [C.c_char_p, C.c_char_p, i32, i32, i32]),
+        "shvb_engine_create_ex": (vp, [C.c_char_p, C.c_char_p, i32, i32, i32, i32]),
         "shvb_engine_destroy": (None, [vp]),
+        "shvb_engine_frames": (vp, [vp, i32]),
+        "shvb_engine_tokens": (vp, [vp, i32]),
+        "shvb_engine_encode": (i32, [vp, i32, i32, vp]),
+        "shvb_engine_frame_bucket": (i32, [vp, i32]),
+        "shvb_engine_encode_launches": (i32, [vp]),
+        "shvb_engine_profile_encode": (i32, [vp, i32, i32, vp, vp, i32, C.c_char_p, i32]),
         "shvb_engine_bind_tokens": (i32, [vp, i32, vp, i32, vp]),
         "shvb_engine_classify": (i32, [vp, i32, i32, vp]),
         "shvb_engine_logits": (vp, [vp, i32]),
@@ -106,6 +113,12 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_sisa_attn": (i32, [vp, vp, vp, vp, i32, vp]),
         "shvk_head": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, vp]),
         "shvk_store_tokens": (i32, [vp, vp, vp, i32, vp]),
+        "shvk_cnn_stem": (i32, [vp, vp, vp, vp, vp, i32, vp]),
+        "shvk_cnn_depthwise": (i32, [vp, vp, vp, vp] + [i32] * 9 + [vp]),
+        "shvk_cnn_se_partial_floats": (sz, [i32, i32, i32]),
+        "shvk_cnn_se_gate": (i32, [vp] * 7 + [i32] * 4 + [vp]),
+        "shvk_cnn_pointwise": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp]),
+        "shvk_cnn_pool_tokens": (i32, [vp, vp, i32, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -275,12 +288,14 @@ class CudaModel:
 class EngineCore:
     """shvb_engine_*: the engine core driven directly on device-resident tokens and a caller-owned stream."""
 
-    def __init__(self, weights, mode="fp32", device=0, max_windows=512, use_graphs=True, experimental=True):
+    def __init__(self, weights, mode="fp32", device=0, max_windows=512, use_graphs=True, experimental=True, max_frames=1):
         self.L = load_library(experimental)
-        self.e = self.L.shvb_engine_create(str(weights).encode(), mode.encode(), device, max_windows, int(use_graphs))
+        self.e = self.L.shvb_engine_create_ex(str(weights).encode(), mode.encode(), device, max_frames, max_windows,
+                                              int(use_graphs))
         if not self.e:
             raise RuntimeError(last_error(self.L))
         self.max_windows = max_windows
+        self.max_frames = max_frames
 
     def _ok(self, rc):
         if rc:
@@ -300,14 +315,38 @@ class EngineCore:
         self._ok(self.L.shvb_engine_read_logits(self.e, slot, out.ctypes.data, n, stream))
         return out
 
-    def profile(self, slot, batch, stream=0):
-        """[(kernel name, ms)] of one eager classify, one entry per launch."""
-        ms = (C.c_float * 64)()
-        names = C.create_string_buffer(4096)
-        n = self.L.shvb_engine_profile(self.e, slot, batch, stream, ms, 64, names, 4096)
+    def frames_ptr(self, slot):
+        """Device address of the slot's uint8 crop buffer [max_frames][180][320][3]."""
+        return self.L.shvb_engine_frames(self.e, slot)
+
+    def tokens_ptr(self, slot):
+        """Device address of the slot's encoded tokens [max_frames][16][384] fp32."""
+        return self.L.shvb_engine_tokens(self.e, slot)
+
+    def encode(self, slot, frames, stream=0):
+        self._ok(self.L.shvb_engine_encode(self.e, slot, frames, stream))
+
+    def frame_bucket(self, frames):
+        return self.L.shvb_engine_frame_bucket(self.e, frames)
+
+    def encode_launches(self):
+        return self.L.shvb_engine_encode_launches(self.e)
+
+    def _profile(self, fn, slot, n_items, stream):
+        ms = (C.c_float * 128)()
+        names = C.create_string_buffer(8192)
+        n = fn(self.e, slot, n_items, stream, ms, 128, names, 8192)
         if n < 0:
             raise RuntimeError(last_error(self.L))
         return list(zip(names.value.decode().split(";"), [float(ms[i]) for i in range(n)]))
+
+    def profile(self, slot, batch, stream=0):
+        """[(kernel name, ms)] of one eager classify, one entry per launch."""
+        return self._profile(self.L.shvb_engine_profile, slot, batch, stream)
+
+    def profile_encode(self, slot, frames, stream=0):
+        """[(kernel name, ms)] of one eager encode, one entry per launch."""
+        return self._profile(self.L.shvb_engine_profile_encode, slot, frames, stream)
 
     def window_bucket(self, batch):
         return self.L.shvb_engine_window_bucket(self.e, batch)

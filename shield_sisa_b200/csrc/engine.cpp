@@ -9,15 +9,21 @@
 //   SISA: all-row GEMM + bias -> S [M,1072] fp32 (aliases P); readout row: norm, QC GEMM, attention kernel,
 //       W_O + residual, norm, FFN, head -> logits.  Everything on the readout row is fp32 in every mode.
 //
+// encode (F frames, reference run_encode engine/cuda/engine.cu:338-403): stem -> 15 inverted-residual blocks
+//   (expand 1x1 | depthwise | squeeze-excite gate | project 1x1 with the gate applied to its input rows, + residual)
+//   -> 1x1 160 -> 960 -> 4x4 pooling -> 960 -> 384 token projection into slot.d_tokens.  float32 NHWC in every mode.
+//
 // Storage policy (engine/cuda/engine.cu:150-164,213-219): h, P/S and the readout-row buffers are fp32 always; xn, on,
 // hid and the all-row weights are the storage type of the mode.  fp32 mode runs the all-row GEMMs on CUDA cores
 // (IEEE fma chain), bf16/fp16 modes on the tcgen05 tensor-core kernel.
 #include "engine.hpp"
 #include "shv_seq_kernels.h"
+#include "shv_cnn_kernels.h"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -105,6 +111,11 @@ struct GdnDev {
     const void *in_w, *o_proj, *ffn_up, *ffn_down;   // storage type
 };
 
+struct CnnBlockDev {
+    const float *exp_w = nullptr, *exp_b = nullptr, *dw_w = nullptr, *dw_b = nullptr, *se_w1 = nullptr, *se_b1 = nullptr;
+    const float *se_w2 = nullptr, *se_b2 = nullptr, *proj_w = nullptr, *proj_b = nullptr;
+};
+
 // One all-row GEMM of the launch sequence: its argument block for the planned maximum row count and, in the 16-bit
 // modes, the tensor-core plan (TMA maps) made once for these buffers.
 struct Site {
@@ -121,9 +132,11 @@ public:
         if (cfg_.max_frames < 1 || cfg_.max_windows < 1 || cfg_.slots < 1 || cfg_.slots > 4)
             throw std::runtime_error("invalid engine configuration");
         if ((long long)cfg_.max_windows * NTOK > 0x7fffffffLL / 4) throw std::runtime_error("max_windows too large");
+        if (cfg_.max_frames > 65535) throw std::runtime_error("max_frames too large");
         fbuckets_ = size_classes(cfg_.max_frames);
         wbuckets_ = size_classes(cfg_.max_windows);
         dt_ = dtype_code(p);
+        cnn_ = fold_cnn(hm);
         upload(hm);
         allocate();
         plan_sites();
@@ -133,9 +146,13 @@ public:
         if (capture_) cudaStreamDestroy(capture_);
     }
 
-    void encode(int, int F, cudaStream_t) override {
+    void encode(int slot, int F, cudaStream_t s) override {
         if (F <= 0) return;
-        throw std::runtime_error("encode: this engine holds the sequence stages only (no frame encoder); pass tokens");
+        if (slot < 0 || slot >= cfg_.slots) throw std::runtime_error("encode: bad slot");
+        if (F > cfg_.max_frames) throw std::runtime_error("encode: too many frames");
+        if (!cfg_.use_graphs || !dump_dir_.empty()) { run_encode(slot, F, s); return; }
+        const int n = class_of(fbuckets_, F);
+        launch_graph((1LL << 40) | ((long long)slot << 32) | (long long)n, s, [&](cudaStream_t cs) { run_encode(slot, n, cs); });
     }
 
     void classify(int slot, int B, cudaStream_t s) override {
@@ -144,16 +161,68 @@ public:
         if (B > cfg_.max_windows) throw std::runtime_error("classify: too many windows");
         if (!cfg_.use_graphs || !dump_dir_.empty()) { run(slot, B, s); return; }
         const int n = class_of(wbuckets_, B);
-        const long long key = ((long long)slot << 32) | (long long)n;
+        launch_graph(((long long)slot << 32) | (long long)n, s, [&](cudaStream_t cs) { run(slot, n, cs); });
+    }
+
+    int device_status() const override {
+        int scan = 0, gemm = 0;
+        if (shvk_gdn_scan_status(&scan) != 0) return -1;
+        if (prec_ != Precision::FP32 && shvk_gemm_tc_status(&gemm) != 0) return -1;
+        return scan ? 16 + scan : gemm;
+    }
+    int launches_per_classify() const override { return 28; }
+
+    // One eager classify / encode with an event after every launch; returns (kernel name, milliseconds) per launch.
+    std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) override {
+        if (B <= 0 || B > cfg_.max_windows || slot < 0 || slot >= cfg_.slots) throw std::runtime_error("profile: bad argument");
+        return timed(s, [&] { run(slot, B, s); });
+    }
+    std::vector<std::pair<std::string, float>> profile_encode(int slot, int F, cudaStream_t s) override {
+        if (F <= 0 || F > cfg_.max_frames || slot < 0 || slot >= cfg_.slots) throw std::runtime_error("profile: bad argument");
+        return timed(s, [&] { run_encode(slot, F, s); });
+    }
+    int launches_per_encode() const override {
+        int n = 4;                                       // stem, last conv, pooling, token projection
+        for (const CnnBlock& b : cnn_.blocks) n += 2 + (b.has_expand ? 1 : 0) + (b.se ? 2 : 0);
+        return n;
+    }
+
+private:
+    int dt_ = SHVK_F32;
+    Arena wts_, acts_;
+    std::vector<std::unique_ptr<Arena>> slot_mem_;
+    const float *pos_ = nullptr, *readout_ = nullptr;
+    GdnDev gdn_[2]{};
+    const float *s_attn_norm_ = nullptr, *s_b_all_ = nullptr, *s_w_qc_ = nullptr, *s_w_o_ = nullptr, *s_lambda_ = nullptr;
+    const float *s_ffn_norm_ = nullptr, *s_ffn_up_ = nullptr, *s_ffn_down_ = nullptr;
+    const void* s_w_all_ = nullptr;
+    const float *fn_w_ = nullptr, *h_w0t_ = nullptr, *h_b0_ = nullptr, *h_w2_ = nullptr, *h_b2_ = nullptr;
+    // activations
+    float *h_ = nullptr, *P_ = nullptr;
+    void *xn_ = nullptr, *on_ = nullptr, *hid_ = nullptr;
+    float *xl_ = nullptr, *qc_ = nullptr, *y_ = nullptr, *x1_ = nullptr, *x2_ = nullptr, *hidl_ = nullptr;
+    Site in_[2], oproj_[2], up_[2], down_[2], sisa_in_;
+    // frame encoder
+    CnnHost cnn_;
+    const float *lut_ = nullptr, *stem_w_ = nullptr, *stem_b_ = nullptr, *last_w_ = nullptr, *last_b_ = nullptr, *tokproj_ = nullptr;
+    CnnBlockDev blk_[15];
+    float *cx_ = nullptr, *ce_ = nullptr, *cd_ = nullptr, *se_part_ = nullptr, *se_gate_ = nullptr, *pooled_ = nullptr;
+    std::map<long long, cudaGraphExec_t> graphs_;
+    cudaStream_t capture_ = nullptr;
+    cudaStream_t capture_stream() {
+        if (!capture_) cuda_ok(cudaStreamCreateWithFlags(&capture_, cudaStreamNonBlocking), "capture stream");
+        return capture_;
+    }
+    // Launches the graph stored under `key` into `s`, capturing `body` first if there is none yet.  Captured on a
+    // stream the engine owns: the caller's stream may be the legacy default stream, which cannot be captured.
+    template <typename Body> void launch_graph(long long key, cudaStream_t s, Body body) {
         auto it = graphs_.find(key);
         if (it == graphs_.end()) {
-            // captured on a stream the engine owns: the caller's stream may be the legacy default stream, which
-            // cannot be captured; the instantiated graph is then launched into the caller's stream
             cudaGraph_t g = nullptr;
             cudaStream_t cs = capture_stream();
             cuda_ok(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal), "graph capture");
             try {
-                run(slot, n, cs);
+                body(cs);
             } catch (...) {
                 cudaStreamEndCapture(cs, &g);
                 if (g) cudaGraphDestroy(g);
@@ -168,25 +237,16 @@ public:
         }
         cuda_ok(cudaGraphLaunch(it->second, s), "graph launch");
     }
+    std::vector<std::pair<std::string, cudaEvent_t>>* marks_ = nullptr;   // non-null only inside profile()
 
-    int device_status() const override {
-        int scan = 0, gemm = 0;
-        if (shvk_gdn_scan_status(&scan) != 0) return -1;
-        if (prec_ != Precision::FP32 && shvk_gemm_tc_status(&gemm) != 0) return -1;
-        return scan ? 16 + scan : gemm;
-    }
-    int launches_per_classify() const override { return 28; }
-
-    // One eager classify with an event after every launch; returns (kernel name, milliseconds) per launch.
-    std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) override {
-        if (B <= 0 || B > cfg_.max_windows || slot < 0 || slot >= cfg_.slots) throw std::runtime_error("profile: bad argument");
+    template <typename Body> std::vector<std::pair<std::string, float>> timed(cudaStream_t s, Body body) {
         std::vector<std::pair<std::string, cudaEvent_t>> marks;
         cudaEvent_t t0 = nullptr;
         cuda_ok(cudaEventCreate(&t0), "event");
         cuda_ok(cudaEventRecord(t0, s), "event");
         marks_ = &marks;
         try {
-            run(slot, B, s);
+            body();
         } catch (...) {
             marks_ = nullptr;
             for (auto& m : marks) cudaEventDestroy(m.second);
@@ -207,29 +267,6 @@ public:
         for (auto& m : marks) cudaEventDestroy(m.second);
         return out;
     }
-
-private:
-    int dt_ = SHVK_F32;
-    Arena wts_, acts_;
-    std::vector<std::unique_ptr<Arena>> slot_mem_;
-    const float *pos_ = nullptr, *readout_ = nullptr;
-    GdnDev gdn_[2]{};
-    const float *s_attn_norm_ = nullptr, *s_b_all_ = nullptr, *s_w_qc_ = nullptr, *s_w_o_ = nullptr, *s_lambda_ = nullptr;
-    const float *s_ffn_norm_ = nullptr, *s_ffn_up_ = nullptr, *s_ffn_down_ = nullptr;
-    const void* s_w_all_ = nullptr;
-    const float *fn_w_ = nullptr, *h_w0t_ = nullptr, *h_b0_ = nullptr, *h_w2_ = nullptr, *h_b2_ = nullptr;
-    // activations
-    float *h_ = nullptr, *P_ = nullptr;
-    void *xn_ = nullptr, *on_ = nullptr, *hid_ = nullptr;
-    float *xl_ = nullptr, *qc_ = nullptr, *y_ = nullptr, *x1_ = nullptr, *x2_ = nullptr, *hidl_ = nullptr;
-    Site in_[2], oproj_[2], up_[2], down_[2], sisa_in_;
-    std::map<long long, cudaGraphExec_t> graphs_;
-    cudaStream_t capture_ = nullptr;
-    cudaStream_t capture_stream() {
-        if (!capture_) cuda_ok(cudaStreamCreateWithFlags(&capture_, cudaStreamNonBlocking), "capture stream");
-        return capture_;
-    }
-    std::vector<std::pair<std::string, cudaEvent_t>>* marks_ = nullptr;   // non-null only inside profile()
 
     void mark(const char* name, cudaStream_t s) {
         if (!marks_) return;
@@ -278,6 +315,16 @@ private:
         for (int o = 0; o < 128; ++o)
             for (int k = 0; k < D; ++k) w0t[size_t(k) * 128 + o] = hm.head_w0[size_t(o) * D + k];
         f32(&h_w0t_, w0t); f32(&h_b0_, hm.head_b0); f32(&h_w2_, hm.head_w2); f32(&h_b2_, hm.head_b2);
+        f32(&lut_, cnn_.lut); f32(&stem_w_, cnn_.stem_w); f32(&stem_b_, cnn_.stem_b);
+        for (int i = 0; i < 15; ++i) {
+            const CnnBlock& b = cnn_.blocks[i];
+            CnnBlockDev& d = blk_[i];
+            if (b.has_expand) { f32(&d.exp_w, b.exp_w); f32(&d.exp_b, b.exp_b); }
+            f32(&d.dw_w, b.dw_w); f32(&d.dw_b, b.dw_b);
+            if (b.se) { f32(&d.se_w1, b.se_w1); f32(&d.se_b1, b.se_b1); f32(&d.se_w2, b.se_w2); f32(&d.se_b2, b.se_b2); }
+            f32(&d.proj_w, b.proj_w); f32(&d.proj_b, b.proj_b);
+        }
+        f32(&last_w_, cnn_.last_w); f32(&last_b_, cnn_.last_b); f32(&tokproj_, hm.proj);
         wts_.commit("weight upload");
         cuda_ok(cudaMemcpy(wts_.at<void>(0), host.data(), host.size(), cudaMemcpyHostToDevice), "weight upload");
         for (const Fix& f : fixes) *f.dst = wts_.at<uint8_t>(f.off);
@@ -291,7 +338,21 @@ private:
         const size_t o_on = acts_.reserve(Mm * VD * ts), o_hid = acts_.reserve(Mm * DFF * ts);
         const size_t o_xl = acts_.reserve(Bm * D * 4), o_qc = acts_.reserve(Bm * SQN * 4), o_y = acts_.reserve(Bm * D * 4);
         const size_t o_x1 = acts_.reserve(Bm * D * 4), o_x2 = acts_.reserve(Bm * D * 4), o_hl = acts_.reserve(Bm * DFF * 4);
+        // frame encoder: block input / output X, expanded E, depthwise output Dd (largest layer of each kind), the
+        // squeeze-excite partial sums and gates, the pooled map
+        size_t x_fl = size_t(90) * 160 * 16, e_fl = size_t(60) * CNN_OUT, d_fl = 0, part_fl = 0;
+        for (const CnnBlock& b : cnn_.blocks) {
+            x_fl = std::max(x_fl, size_t(b.h_out) * b.w_out * b.out);
+            if (b.has_expand) e_fl = std::max(e_fl, size_t(b.h_in) * b.w_in * b.exp);
+            d_fl = std::max(d_fl, size_t(b.h_out) * b.w_out * b.exp);
+            if (b.se) part_fl = std::max(part_fl, shvk_cnn_se_partial_floats(1, b.h_out * b.w_out, b.exp));
+        }
+        const size_t o_cx = acts_.reserve(Fm * x_fl * 4), o_ce = acts_.reserve(Fm * e_fl * 4), o_cd = acts_.reserve(Fm * d_fl * 4);
+        const size_t o_sp = acts_.reserve(Fm * part_fl * 4), o_sg = acts_.reserve(Fm * CNN_OUT * 4);
+        const size_t o_po = acts_.reserve(Fm * 16 * CNN_OUT * 4);
         acts_.commit("activation arena");
+        cx_ = acts_.at<float>(o_cx); ce_ = acts_.at<float>(o_ce); cd_ = acts_.at<float>(o_cd);
+        se_part_ = acts_.at<float>(o_sp); se_gate_ = acts_.at<float>(o_sg); pooled_ = acts_.at<float>(o_po);
         h_ = acts_.at<float>(o_h); P_ = acts_.at<float>(o_p);
         xn_ = acts_.at<void>(o_xn); on_ = acts_.at<void>(o_on); hid_ = acts_.at<void>(o_hid);
         xl_ = acts_.at<float>(o_xl); qc_ = acts_.at<float>(o_qc); y_ = acts_.at<float>(o_y);
@@ -302,10 +363,12 @@ private:
         for (int i = 0; i < cfg_.slots; ++i) {
             slot_mem_.emplace_back(new Arena());
             Arena& a = *slot_mem_.back();
+            const size_t o_frm = a.reserve(Fm * IMG_H * IMG_W * 3);
             const size_t o_tok = a.reserve(Fm * 16 * D * 4), o_stage = a.reserve(Bm * FRAMES * 16 * D * 4);
             const size_t o_ptr = a.reserve(Bm * FRAMES * sizeof(float*)), o_log = a.reserve(Bm * 4);
             a.commit("slot buffers");
             Slot& sl = slots_[size_t(i)];
+            sl.d_frames = a.at<uint8_t>(o_frm);
             sl.d_tokens = a.at<float>(o_tok);
             sl.d_tok_stage = a.at<float>(o_stage);
             sl.d_tokptr = a.at<const float*>(o_ptr);
@@ -379,6 +442,56 @@ private:
         }
         std::ofstream o(dump_dir_ + "/" + name + ".f32", std::ios::binary);
         o.write(reinterpret_cast<const char*>(f.data()), std::streamsize(n * 4));
+    }
+
+    // ---------------------------------------------------------------- frame encoder
+    void run_encode(int slot, int F, cudaStream_t s) {
+        const Slot& sl = slots_[size_t(slot)];
+        launch_ok(shvk_cnn_stem(sl.d_frames, lut_, stem_w_, stem_b_, cx_, F, s), "stem");
+        mark("cnn.stem", s);
+        dump("cnn_stem_f0", cx_, size_t(16) * 90 * 160, SHVK_F32, s);
+        for (int i = 0; i < 15; ++i) {
+            const CnnBlock& b = cnn_.blocks[i];
+            const CnnBlockDev& d = blk_[i];
+            const int hw_in = b.h_in * b.w_in, hw_out = b.h_out * b.w_out;
+            const float* dw_in = cx_;
+            if (b.has_expand) {
+                launch_ok(shvk_cnn_pointwise(cx_, d.exp_w, d.exp_b, nullptr, 1, nullptr, ce_, F * hw_in, b.exp, b.in, b.act, s),
+                          "expand");
+                mark("cnn.expand", s);
+                dw_in = ce_;
+            }
+            launch_ok(shvk_cnn_depthwise(dw_in, d.dw_w, d.dw_b, cd_, F, b.h_in, b.w_in, b.exp, b.k, b.stride, b.h_out, b.w_out,
+                                         b.act, s), "depthwise");
+            mark("cnn.depthwise", s);
+            const float* gate = nullptr;
+            if (b.se) {
+                launch_ok(shvk_cnn_se_gate(cd_, se_part_, d.se_w1, d.se_b1, d.se_w2, d.se_b2, se_gate_, F, hw_out, b.exp, b.cs, s),
+                          "squeeze-excite");
+                mark("cnn.se_gate", s);
+                gate = se_gate_;
+            }
+            launch_ok(shvk_cnn_pointwise(cd_, d.proj_w, d.proj_b, gate, hw_out, b.residual ? cx_ : nullptr, cx_, F * hw_out, b.out,
+                                         b.exp, SHVK_ACT_NONE, s), "project");
+            mark("cnn.project", s);
+            if (!dump_dir_.empty()) {
+                char name[32];
+                std::snprintf(name, sizeof name, "cnn_block%02d_f0", i + 1);
+                dump(name, cx_, size_t(b.out) * hw_out, SHVK_F32, s);
+            }
+        }
+        launch_ok(shvk_cnn_pointwise(cx_, last_w_, last_b_, nullptr, 1, nullptr, ce_, F * 60, CNN_OUT, 160, SHVK_ACT_HSWISH, s),
+                  "last conv");
+        mark("cnn.last", s);
+        dump("cnn_map_f0", ce_, size_t(60) * CNN_OUT, SHVK_F32, s);
+        launch_ok(shvk_cnn_pool_tokens(ce_, pooled_, F, s), "pool");
+        mark("cnn.pool", s);
+        shvk_gemm_args a{};
+        a.M = F * 16; a.N = D; a.K = CNN_OUT; a.A = pooled_; a.lda = CNN_OUT; a.W = tokproj_; a.ldw = CNN_OUT;
+        a.C = sl.d_tokens; a.ldc = D; a.c_dtype = SHVK_F32; a.r_div = 1.0f;
+        launch_ok(shvk_gemm_f32(&a, s), "token projection");
+        mark("cnn.token_proj", s);
+        dump("tokens", sl.d_tokens, size_t(16) * D, SHVK_F32, s);
     }
 
     // ---------------------------------------------------------------- the launch sequence

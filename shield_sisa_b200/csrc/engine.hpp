@@ -1,10 +1,9 @@
-// Sequence engine core: device-resident weights, activation arena, bucketed CUDA graphs, classify().
+// Engine core: device-resident weights, activation arena, bucketed CUDA graphs, encode() and classify().
 //
 // Same internal C++ interface as the reference engine core (engine/cuda/engine.hpp:12-62): EngineConfig, the
 // abstract Engine with encode / classify / slot / buckets / byte counters / set_dump_dir, and make_engine,
 // parse_precision, precision_name.  A harness written against the reference's engine.hpp drives this engine as is.
-// Differences: encode() throws (this engine holds the sequence stages only; tokens come from the caller), and
-// max_windows may exceed 4096 when the engine is used directly.
+// Difference: max_windows may exceed 4096 when the engine is used directly.
 //
 // NOT thread-safe: one thread drives an engine (the API worker).  Errors are std::runtime_error.
 #pragma once
@@ -38,7 +37,7 @@ public:
     int slots() const { return cfg_.slots; }
 
     struct Slot {
-        uint8_t* d_frames = nullptr;      // unused by this engine (no frame encoder); kept for interface parity
+        uint8_t* d_frames = nullptr;      // [max_frames][180][320][3] RGB crops to encode
         float* d_tokens = nullptr;        // [max_frames][16*384] tokens of encoded frames
         float* d_tok_stage = nullptr;     // [max_windows*20][16*384] tokens uploaded by the host
         const float** d_tokptr = nullptr; // [max_windows*20] device pointers to 16x384 token blocks
@@ -46,7 +45,8 @@ public:
     };
     const Slot& slot(int i) const { return slots_[size_t(i)]; }
 
-    // Enqueue on `s` and return without synchronising.  classify reads slot.d_tokptr[0 .. 20*B) and writes
+    // Enqueue on `s` and return without synchronising.  encode reads slot.d_frames[0 .. F) and writes the tokens of
+    // frame f to slot.d_tokens + f*6144.  classify reads slot.d_tokptr[0 .. 20*B) and writes
     // slot.d_logits[0 .. B); with graphs on, B is padded to its bucket and the padding windows are computed from
     // whatever valid pointers the table holds, then ignored.
     virtual void encode(int slot, int F, cudaStream_t s) = 0;
@@ -66,6 +66,9 @@ public:
     // One eager classify of B windows with a CUDA event after every launch: (kernel name, milliseconds) per launch,
     // in launch order.  Synchronises the stream.
     virtual std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) = 0;
+    // The same for one eager encode of F frames.
+    virtual std::vector<std::pair<std::string, float>> profile_encode(int slot, int F, cudaStream_t s) = 0;
+    virtual int launches_per_encode() const = 0;
 
 protected:
     Precision prec_ = Precision::FP32;

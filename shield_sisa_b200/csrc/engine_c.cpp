@@ -32,6 +32,11 @@ void cuda_ok(cudaError_t e, const char* what) {
 extern "C" {
 
 shvb_engine* shvb_engine_create(const char* weights, const char* mode, int device, int max_windows, int use_graphs) {
+    return shvb_engine_create_ex(weights, mode, device, 1, max_windows, use_graphs);
+}
+
+shvb_engine* shvb_engine_create_ex(const char* weights, const char* mode, int device, int max_frames, int max_windows,
+                                   int use_graphs) {
     shvb_engine* out = nullptr;
     guard([&] {
         if (!weights) throw std::runtime_error("null weights path");
@@ -41,7 +46,7 @@ shvb_engine* shvb_engine_create(const char* weights, const char* mode, int devic
         const shv::HostModel hm = shv::load_host_model(weights);
         shv::check_sidecar_sha(weights, hm.sha256);
         shv::EngineConfig cfg;
-        cfg.max_frames = 1;
+        cfg.max_frames = max_frames;
         cfg.max_windows = max_windows;
         cfg.use_graphs = use_graphs != 0;
         cfg.slots = 2;
@@ -85,6 +90,24 @@ int shvb_engine_read_logits(shvb_engine* e, int slot, float* host, int n, void* 
         cuda_ok(cudaMemcpy(host, e->eng->slot(slot).d_logits, size_t(n) * 4, cudaMemcpyDeviceToHost), "read_logits");
     });
 }
+uint8_t* shvb_engine_frames(shvb_engine* e, int slot) {
+    return e && slot >= 0 && slot < e->eng->slots() ? e->eng->slot(slot).d_frames : nullptr;
+}
+float* shvb_engine_tokens(shvb_engine* e, int slot) {
+    return e && slot >= 0 && slot < e->eng->slots() ? e->eng->slot(slot).d_tokens : nullptr;
+}
+int shvb_engine_encode(shvb_engine* e, int slot, int F, void* stream) {
+    return guard([&] {
+        if (!e) throw std::runtime_error("null engine");
+        e->eng->encode(slot, F, cudaStream_t(stream));
+    });
+}
+int shvb_engine_frame_bucket(const shvb_engine* e, int F) {
+    int out = -1;
+    guard([&] { out = e ? e->eng->frame_bucket(F) : -1; });
+    return out;
+}
+int shvb_engine_encode_launches(const shvb_engine* e) { return e ? e->eng->launches_per_encode() : 0; }
 int shvb_engine_window_bucket(const shvb_engine* e, int B) {
     int out = -1;
     guard([&] { out = e ? e->eng->window_bucket(B) : -1; });
@@ -96,11 +119,13 @@ size_t shvb_engine_bytes(const shvb_engine* e, int which) {
     if (!e) return 0;
     return which == 0 ? e->eng->weight_bytes() : which == 1 ? e->eng->activation_bytes() : e->eng->slot_bytes();
 }
-int shvb_engine_profile(shvb_engine* e, int slot, int B, void* stream, float* ms, int cap, char* names, int names_cap) {
+namespace {
+int profile_any(shvb_engine* e, bool encode, int slot, int n_items, void* stream, float* ms, int cap, char* names, int names_cap) {
     int n = -1;
     guard([&] {
         if (!e || !ms || !names || cap < 1 || names_cap < 1) throw std::runtime_error("profile: bad argument");
-        const auto rows = e->eng->profile(slot, B, cudaStream_t(stream));
+        const auto rows = encode ? e->eng->profile_encode(slot, n_items, cudaStream_t(stream))
+                                 : e->eng->profile(slot, n_items, cudaStream_t(stream));
         std::string joined;
         for (size_t i = 0; i < rows.size(); ++i) {
             if (int(i) < cap) ms[i] = rows[i].second;
@@ -111,6 +136,13 @@ int shvb_engine_profile(shvb_engine* e, int slot, int B, void* stream, float* ms
         n = int(rows.size());
     });
     return n;
+}
+}  // namespace
+int shvb_engine_profile(shvb_engine* e, int slot, int B, void* stream, float* ms, int cap, char* names, int names_cap) {
+    return profile_any(e, false, slot, B, stream, ms, cap, names, names_cap);
+}
+int shvb_engine_profile_encode(shvb_engine* e, int slot, int F, void* stream, float* ms, int cap, char* names, int names_cap) {
+    return profile_any(e, true, slot, F, stream, ms, cap, names, names_cap);
 }
 int shvb_engine_set_dump_dir(shvb_engine* e, const char* dir) {
     return guard([&] {

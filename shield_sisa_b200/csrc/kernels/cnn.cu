@@ -1,0 +1,340 @@
+// Frame encoder kernels: MobileNetV3-Large features of 320x180 RGB crops (engine/cuda/cnn.cu, engine.cu:338-403 of
+// the reference; CPU form engine/model/isa_impl.hpp:558-851; oracle/shieldv_ref.py:380-392).
+//
+// Layout: activations float32, NHWC, so that a 1x1 convolution is a row GEMM over pixels and the depthwise and
+// pooling kernels read 16-byte channel quads.  BatchNorm arrives folded into weights and biases.  Every kernel is
+// deterministic and computes a frame independently of the other frames of the batch (fixed reduction splits).
+#include "device_utils.cuh"
+#include "shv_cnn_kernels.h"
+
+namespace sb {
+namespace {
+
+constexpr int kImgH = 180, kImgW = 320, kStemH = 90, kStemW = 160, kStemC = 16, kMapH = 6, kMapW = 10, kMapC = 960;
+
+__device__ __forceinline__ float relu6_shift(float x) { return fminf(fmaxf(x + 3.0f, 0.0f), 6.0f); }
+__device__ __forceinline__ float activate(float x, int act) {
+    if (act == SHVK_ACT_RELU) return fmaxf(x, 0.0f);
+    if (act == SHVK_ACT_HSWISH) return x * relu6_shift(x) / 6.0f;
+    if (act == SHVK_ACT_HSIGMOID) return relu6_shift(x) / 6.0f;
+    return x;
+}
+
+// ---------------------------------------------------------------------------------------------------- stem
+// One thread per output pixel, 16 output channels in registers; lookup table and the 27x16 filter in shared memory.
+__global__ void __launch_bounds__(256)
+stem_kernel(const uint8_t* __restrict__ frames, const float* __restrict__ lut, const float* __restrict__ w,
+            const float* __restrict__ b, float* __restrict__ out, long long npix) {
+    __shared__ float s_lut[3 * 256];
+    __shared__ __align__(16) float s_w[27 * kStemC];
+    __shared__ float s_b[kStemC];
+    for (int i = threadIdx.x; i < 3 * 256; i += blockDim.x) s_lut[i] = lut[i];
+    for (int i = threadIdx.x; i < 27 * kStemC; i += blockDim.x) s_w[i] = w[i];
+    if (threadIdx.x < kStemC) s_b[threadIdx.x] = b[threadIdx.x];
+    __syncthreads();
+    const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= npix) return;
+    const int ox = int(p % kStemW), oy = int((p / kStemW) % kStemH);
+    const long long f = p / (kStemW * kStemH);
+    const uint8_t* img = frames + f * (long long)(kImgH * kImgW * 3);
+    float acc[kStemC];
+#pragma unroll
+    for (int c = 0; c < kStemC; ++c) acc[c] = 0.0f;
+#pragma unroll
+    for (int ky = 0; ky < 3; ++ky) {
+        const int iy = 2 * oy - 1 + ky;
+        if (iy < 0 || iy >= kImgH) continue;
+#pragma unroll
+        for (int kx = 0; kx < 3; ++kx) {
+            const int ix = 2 * ox - 1 + kx;
+            if (ix < 0 || ix >= kImgW) continue;
+            const uint8_t* px = img + ((long long)iy * kImgW + ix) * 3;
+#pragma unroll
+            for (int ci = 0; ci < 3; ++ci) {
+                const float x = s_lut[ci * 256 + px[ci]];
+                const float4* wr = reinterpret_cast<const float4*>(s_w + ((ky * 3 + kx) * 3 + ci) * kStemC);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 wv = wr[q];
+                    acc[4 * q + 0] = fmaf(wv.x, x, acc[4 * q + 0]);
+                    acc[4 * q + 1] = fmaf(wv.y, x, acc[4 * q + 1]);
+                    acc[4 * q + 2] = fmaf(wv.z, x, acc[4 * q + 2]);
+                    acc[4 * q + 3] = fmaf(wv.w, x, acc[4 * q + 3]);
+                }
+            }
+        }
+    }
+    float4* o = reinterpret_cast<float4*>(out + p * kStemC);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        o[q] = make_float4(activate(acc[4 * q] + s_b[4 * q], SHVK_ACT_HSWISH), activate(acc[4 * q + 1] + s_b[4 * q + 1], SHVK_ACT_HSWISH),
+                           activate(acc[4 * q + 2] + s_b[4 * q + 2], SHVK_ACT_HSWISH),
+                           activate(acc[4 * q + 3] + s_b[4 * q + 3], SHVK_ACT_HSWISH));
+}
+
+// ---------------------------------------------------------------------------------------------------- depthwise
+// One thread per (output pixel, channel quad); taps visited row by row, out-of-image taps skipped.
+template <int KS, int S>
+__global__ void __launch_bounds__(256)
+depthwise_kernel(const float* __restrict__ in, const float* __restrict__ w, const float* __restrict__ b,
+                 float* __restrict__ out, long long total, int H, int W, int C, int Ho, int Wo, int act) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int C4 = C >> 2;
+    const int c = int(i % C4) * 4;
+    const long long pix = i / C4;
+    const int ox = int(pix % Wo), oy = int((pix / Wo) % Ho);
+    const long long f = pix / ((long long)Wo * Ho);
+    constexpr int PAD = (KS - 1) / 2;
+    const float* img = in + f * (long long)H * W * C;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int ky = 0; ky < KS; ++ky) {
+        const int iy = oy * S - PAD + ky;
+        if (iy < 0 || iy >= H) continue;
+#pragma unroll
+        for (int kx = 0; kx < KS; ++kx) {
+            const int ix = ox * S - PAD + kx;
+            if (ix < 0 || ix >= W) continue;
+            const float4 x = *reinterpret_cast<const float4*>(img + ((long long)iy * W + ix) * C + c);
+            const float4 k = __ldg(reinterpret_cast<const float4*>(w + (ky * KS + kx) * C + c));
+            acc.x = fmaf(k.x, x.x, acc.x);
+            acc.y = fmaf(k.y, x.y, acc.y);
+            acc.z = fmaf(k.z, x.z, acc.z);
+            acc.w = fmaf(k.w, x.w, acc.w);
+        }
+    }
+    const float4 bias = __ldg(reinterpret_cast<const float4*>(b + c));
+    *reinterpret_cast<float4*>(out + pix * C + c) =
+        make_float4(activate(acc.x + bias.x, act), activate(acc.y + bias.y, act), activate(acc.z + bias.z, act),
+                    activate(acc.w + bias.w, act));
+}
+
+// ---------------------------------------------------------------------------------------------------- squeeze-excite
+// Stage 1: partial[f][s][c] = sum over the 64 pixels of group s, eight strided pixel rows per block combined in order.
+constexpr int kSeGroup = 64;
+__global__ void __launch_bounds__(256)
+se_partial_kernel(const float* __restrict__ x, float* __restrict__ partial, int HW, int C, int S) {
+    __shared__ float4 red[8][32];
+    const int f = blockIdx.x, s = blockIdx.y, lane = threadIdx.x & 31, pg = threadIdx.x >> 5;
+    const int c = (blockIdx.z * 32 + lane) * 4;
+    const int p0 = s * kSeGroup, p1 = min(HW, p0 + kSeGroup);
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (c < C)
+        for (int p = p0 + pg; p < p1; p += 8) {
+            const float4 v = *reinterpret_cast<const float4*>(x + ((long long)f * HW + p) * C + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    red[pg][lane] = acc;
+    __syncthreads();
+    if (pg == 0 && c < C) {
+        float4 t = red[0][lane];
+#pragma unroll
+        for (int r = 1; r < 8; ++r) {
+            const float4 v = red[r][lane];
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+        *reinterpret_cast<float4*>(partial + ((long long)f * S + s) * C + c) = t;
+    }
+}
+// Stage 2, one block per frame: mean, fc1 + ReLU, fc2 + Hardsigmoid; a warp per output, lanes over the inputs.
+__global__ void __launch_bounds__(256)
+se_gate_kernel(const float* __restrict__ partial, const float* __restrict__ w1, const float* __restrict__ b1,
+               const float* __restrict__ w2, const float* __restrict__ b2, float* __restrict__ gate, int HW, int C, int CS,
+               int S) {
+    extern __shared__ float se_smem[];
+    float* pooled = se_smem;          // [C]
+    float* hid = se_smem + C;         // [CS]
+    const int f = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float t = 0.0f;
+        for (int s = 0; s < S; ++s) t += partial[((long long)f * S + s) * C + c];
+        pooled[c] = t / float(HW);
+    }
+    __syncthreads();
+    for (int j = warp; j < CS; j += nwarp) {
+        const float* wr = w1 + (long long)j * C;
+        float t = 0.0f;
+        for (int c = lane; c < C; c += 32) t = fmaf(wr[c], pooled[c], t);
+        t = warp_sum(t);
+        if (lane == 0) hid[j] = fmaxf(t + b1[j], 0.0f);
+    }
+    __syncthreads();
+    for (int c = warp; c < C; c += nwarp) {
+        const float* wr = w2 + (long long)c * CS;
+        float t = 0.0f;
+        for (int j = lane; j < CS; j += 32) t = fmaf(wr[j], hid[j], t);
+        t = warp_sum(t);
+        if (lane == 0) gate[(long long)f * C + c] = activate(t + b2[c], SHVK_ACT_HSIGMOID);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- 1x1 convolution
+// Row GEMM on CUDA cores: tile 64 pixels x 64 output channels x 8 input channels, 256 threads, 4 x 4 outputs per
+// thread, next tile fetched into registers while the current one is consumed.  One fma chain over k per output.
+constexpr int PW_M = 64, PW_N = 64, PW_K = 8, PW_PITCH = 68;
+__global__ void __launch_bounds__(256)
+pointwise_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
+                 const float* __restrict__ gate, int gate_rows, const float* R, float* out, int M, int N, int K, int act) {
+    __shared__ __align__(16) float sa[2][PW_K][PW_PITCH];
+    __shared__ __align__(16) float sw[2][PW_K][PW_PITCH];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const long long m0 = (long long)blockIdx.x * PW_M;
+    const int n0 = blockIdx.y * PW_N;
+    // loader role: threads 0..127 fetch A (row tid / 2, k quad tid % 2), threads 128..255 fetch W
+    const bool is_a = tid < 128;
+    const int lrow = (tid & 127) >> 1, lk = (tid & 1) * 4;
+    const long long arow = m0 + lrow;
+    const int wrow = n0 + lrow;
+    const bool live = is_a ? arow < M : wrow < N;
+    const float* src = is_a ? A + arow * K : W + (long long)wrow * K;
+    const float* gsrc = (is_a && gate && live) ? gate + (arow / gate_rows) * K : nullptr;
+    float4 reg;
+    auto fetch = [&](int k0) {
+        reg = live ? *reinterpret_cast<const float4*>(src + k0 + lk) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (gsrc) {
+            const float4 g = *reinterpret_cast<const float4*>(gsrc + k0 + lk);
+            reg.x *= g.x; reg.y *= g.y; reg.z *= g.z; reg.w *= g.w;
+        }
+    };
+    auto stash = [&](int buf) {
+        float (*dst)[PW_PITCH] = is_a ? sa[buf] : sw[buf];
+        dst[lk + 0][lrow] = reg.x; dst[lk + 1][lrow] = reg.y; dst[lk + 2][lrow] = reg.z; dst[lk + 3][lrow] = reg.w;
+    };
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    const int nk = K / PW_K;
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    for (int kb = 0; kb < nk; ++kb) {
+        const int buf = kb & 1;
+        if (kb + 1 < nk) fetch((kb + 1) * PW_K);
+#pragma unroll
+        for (int k = 0; k < PW_K; ++k) {
+            const float4 a = *reinterpret_cast<const float4*>(&sa[buf][k][ty * 4]);
+            const float4 w = *reinterpret_cast<const float4*>(&sw[buf][k][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        }
+        if (kb + 1 < nk) {
+            stash(buf ^ 1);
+            __syncthreads();
+        }
+    }
+    const int n = n0 + tx * 4;
+    if (n >= N) return;
+    const float4 bv = bias ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long m = m0 + ty * 4 + i;
+        if (m >= M) break;
+        float4 v = make_float4(activate(acc[i][0] + bv.x, act), activate(acc[i][1] + bv.y, act),
+                               activate(acc[i][2] + bv.z, act), activate(acc[i][3] + bv.w, act));
+        if (R) {
+            const float4 r = *reinterpret_cast<const float4*>(R + m * N + n);
+            v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+        }
+        *reinterpret_cast<float4*>(out + m * N + n) = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- 4x4 pooling
+__global__ void __launch_bounds__(256)
+pool_tokens_kernel(const float* __restrict__ in, float* __restrict__ out, long long total) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    constexpr int C4 = kMapC / 4;
+    const int c = int(i % C4) * 4, tok = int((i / C4) % 16);
+    const long long f = i / (16 * C4);
+    const int r = tok >> 2, q = tok & 3;
+    const int y0 = (r * kMapH) / 4, y1 = ((r + 1) * kMapH + 3) / 4, x0 = (q * kMapW) / 4, x1 = ((q + 1) * kMapW + 3) / 4;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int y = y0; y < y1; ++y)
+        for (int x = x0; x < x1; ++x) {
+            const float4 v = *reinterpret_cast<const float4*>(in + ((f * kMapH + y) * kMapW + x) * kMapC + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    const float cnt = float((y1 - y0) * (x1 - x0));
+    *reinterpret_cast<float4*>(out + (f * 16 + tok) * kMapC + c) = make_float4(acc.x / cnt, acc.y / cnt, acc.z / cnt, acc.w / cnt);
+}
+
+inline unsigned blocks_for(long long n, int per) { return unsigned((n + per - 1) / per); }
+inline bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
+
+}  // namespace
+}  // namespace sb
+
+extern "C" int shvk_cnn_stem(const uint8_t* frames, const float* lut, const float* w, const float* b, float* out, int F,
+                             void* stream) {
+    if (F <= 0) return 0;
+    if (sb::misaligned(out)) return int(cudaErrorInvalidValue);
+    const long long npix = (long long)F * sb::kStemH * sb::kStemW;
+    sb::stem_kernel<<<sb::blocks_for(npix, 256), 256, 0, cudaStream_t(stream)>>>(frames, lut, w, b, out, npix);
+    return int(cudaGetLastError());
+}
+
+extern "C" int shvk_cnn_depthwise(const float* in, const float* w, const float* b, float* out, int F, int H, int W, int C,
+                                  int K, int stride, int Ho, int Wo, int act, void* stream) {
+    if (F <= 0) return 0;
+    const int pad = (K - 1) / 2;
+    if ((K != 3 && K != 5) || (stride != 1 && stride != 2) || (C & 3) || H <= 0 || W <= 0 ||
+        Ho != (H + 2 * pad - K) / stride + 1 || Wo != (W + 2 * pad - K) / stride + 1 || sb::misaligned(in) ||
+        sb::misaligned(out) || sb::misaligned(w) || sb::misaligned(b))
+        return int(cudaErrorInvalidValue);
+    const long long total = (long long)F * Ho * Wo * (C / 4);
+    const unsigned grid = sb::blocks_for(total, 256);
+    cudaStream_t s = cudaStream_t(stream);
+    if (K == 3 && stride == 1) sb::depthwise_kernel<3, 1><<<grid, 256, 0, s>>>(in, w, b, out, total, H, W, C, Ho, Wo, act);
+    else if (K == 3) sb::depthwise_kernel<3, 2><<<grid, 256, 0, s>>>(in, w, b, out, total, H, W, C, Ho, Wo, act);
+    else if (stride == 1) sb::depthwise_kernel<5, 1><<<grid, 256, 0, s>>>(in, w, b, out, total, H, W, C, Ho, Wo, act);
+    else sb::depthwise_kernel<5, 2><<<grid, 256, 0, s>>>(in, w, b, out, total, H, W, C, Ho, Wo, act);
+    return int(cudaGetLastError());
+}
+
+extern "C" size_t shvk_cnn_se_partial_floats(int F, int HW, int C) {
+    if (F <= 0 || HW <= 0 || C <= 0) return 0;
+    return size_t(F) * size_t((HW + sb::kSeGroup - 1) / sb::kSeGroup) * size_t(C);
+}
+
+extern "C" int shvk_cnn_se_gate(const float* x, float* partial, const float* w1, const float* b1, const float* w2,
+                                const float* b2, float* gate, int F, int HW, int C, int CS, void* stream) {
+    if (F <= 0) return 0;
+    if (HW <= 0 || C <= 0 || (C & 3) || CS <= 0 || !partial || sb::misaligned(x) || sb::misaligned(partial))
+        return int(cudaErrorInvalidValue);
+    const int S = (HW + sb::kSeGroup - 1) / sb::kSeGroup;
+    if (S > 65535) return int(cudaErrorInvalidValue);
+    cudaStream_t s = cudaStream_t(stream);
+    sb::se_partial_kernel<<<dim3(unsigned(F), unsigned(S), unsigned((C + 127) / 128)), 256, 0, s>>>(x, partial, HW, C, S);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return int(e);
+    const size_t smem = size_t(C + CS) * sizeof(float);
+    if (smem > 48 * 1024) return int(cudaErrorInvalidValue);
+    sb::se_gate_kernel<<<unsigned(F), 256, smem, s>>>(partial, w1, b1, w2, b2, gate, HW, C, CS, S);
+    return int(cudaGetLastError());
+}
+
+extern "C" int shvk_cnn_pointwise(const float* A, const float* W, const float* b, const float* gate, int gate_rows,
+                                  const float* R, float* out, int M, int N, int K, int act, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K % sb::PW_K) || (N & 3) || (gate && gate_rows <= 0) || sb::misaligned(A) || sb::misaligned(W) ||
+        sb::misaligned(out) || (R && sb::misaligned(R)) || (b && sb::misaligned(b)) || (gate && sb::misaligned(gate)))
+        return int(cudaErrorInvalidValue);
+    const dim3 grid(sb::blocks_for(M, sb::PW_M), unsigned((N + sb::PW_N - 1) / sb::PW_N));
+    sb::pointwise_kernel<<<grid, 256, 0, cudaStream_t(stream)>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+    return int(cudaGetLastError());
+}
+
+extern "C" int shvk_cnn_pool_tokens(const float* in, float* out, int F, void* stream) {
+    if (F <= 0) return 0;
+    if (sb::misaligned(in) || sb::misaligned(out)) return int(cudaErrorInvalidValue);
+    const long long total = (long long)F * 16 * (sb::kMapC / 4);
+    sb::pool_tokens_kernel<<<sb::blocks_for(total, 256), 256, 0, cudaStream_t(stream)>>>(in, out, total);
+    return int(cudaGetLastError());
+}

@@ -328,4 +328,107 @@ std::string check_certificate(const std::string& weights, const std::string& sha
     return "mode " + mode + " has no passing certificate for weights " + sha + " at compute revision " + revision + " in " + path;
 }
 
+// ---------------------------------------------------------------------------------------------------- frame encoder
+namespace {
+
+const std::vector<float>& cnn_tensor(const HostModel& hm, const std::string& name) {
+    const auto it = hm.cnn.find(name);
+    if (it == hm.cnn.end()) throw std::runtime_error("missing tensor " + name);
+    return it->second.data;
+}
+
+// conv weight [out][per_out] followed by BatchNorm `bn`: scales the rows in place, returns the folded bias
+std::vector<float> fold_batchnorm(const HostModel& hm, const std::string& bn, int out, int per_out, std::vector<float>& w) {
+    const std::vector<float>&g = cnn_tensor(hm, bn + ".weight"), &beta = cnn_tensor(hm, bn + ".bias"),
+                            &mean = cnn_tensor(hm, bn + ".running_mean"), &var = cnn_tensor(hm, bn + ".running_var");
+    std::vector<float> b(size_t(out), 0.0f);
+    for (int o = 0; o < out; ++o) {
+        const double s = double(g[size_t(o)]) / std::sqrt(double(var[size_t(o)]) + 1e-3);
+        for (int i = 0; i < per_out; ++i) {
+            float& x = w[size_t(o) * per_out + i];
+            x = float(double(x) * s);
+        }
+        b[size_t(o)] = float(double(beta[size_t(o)]) - double(mean[size_t(o)]) * s);
+    }
+    return b;
+}
+
+}  // namespace
+
+CnnHost fold_cnn(const HostModel& hm) {
+    struct Cfg { int in, k, exp, out; bool se; int act, stride; };
+    static const Cfg table[15] = {
+        {16, 3, 16, 16, false, 1, 1},   {16, 3, 64, 24, false, 1, 2},   {24, 3, 72, 24, false, 1, 1},
+        {24, 5, 72, 40, true, 1, 2},    {40, 5, 120, 40, true, 1, 1},   {40, 5, 120, 40, true, 1, 1},
+        {40, 3, 240, 80, false, 2, 2},  {80, 3, 200, 80, false, 2, 1},  {80, 3, 184, 80, false, 2, 1},
+        {80, 3, 184, 80, false, 2, 1},  {80, 3, 480, 112, true, 2, 1},  {112, 3, 672, 112, true, 2, 1},
+        {112, 5, 672, 160, true, 2, 2}, {160, 5, 960, 160, true, 2, 1}, {160, 5, 960, 160, true, 2, 1}};
+    CnnHost c;
+    // normalisation table: x = u / 255, y = x - mean, y / std, every step a float32 operation (prepare_clips of the
+    // reference pipeline; engine/cuda/engine.cu:76-87)
+    const float mean[3] = {0.485f, 0.456f, 0.406f}, stdv[3] = {0.229f, 0.224f, 0.225f};
+    c.lut.resize(768);
+    for (int ch = 0; ch < 3; ++ch)
+        for (int u = 0; u < 256; ++u) {
+            volatile float x = float(u) / 255.0f;
+            volatile float y = x - mean[ch];
+            c.lut[size_t(ch) * 256 + u] = y / stdv[ch];
+        }
+    {
+        std::vector<float> w = cnn_tensor(hm, "cnn.0.0.weight");           // [16][3][3][3] = [co][ci][kh][kw]
+        c.stem_b = fold_batchnorm(hm, "cnn.0.1", 16, 27, w);
+        c.stem_w.resize(27 * 16);
+        for (int co = 0; co < 16; ++co)
+            for (int ci = 0; ci < 3; ++ci)
+                for (int kh = 0; kh < 3; ++kh)
+                    for (int kw = 0; kw < 3; ++kw)
+                        c.stem_w[size_t(((kh * 3 + kw) * 3 + ci) * 16 + co)] = w[size_t(((co * 3 + ci) * 3 + kh) * 3 + kw)];
+    }
+    int h = 90, wd = 160;
+    for (int i = 0; i < 15; ++i) {
+        const Cfg& t = table[i];
+        CnnBlock& b = c.blocks[i];
+        b.in = t.in; b.k = t.k; b.exp = t.exp; b.out = t.out; b.se = t.se; b.act = t.act; b.stride = t.stride;
+        b.has_expand = t.exp != t.in;
+        b.residual = t.stride == 1 && t.in == t.out;
+        const std::string pre = "cnn." + std::to_string(i + 1) + ".block.";
+        int idx = 0;
+        if (b.has_expand) {
+            const std::string p = pre + std::to_string(idx++);
+            b.exp_w = cnn_tensor(hm, p + ".0.weight");
+            b.exp_b = fold_batchnorm(hm, p + ".1", t.exp, t.in, b.exp_w);
+        }
+        {
+            const std::string p = pre + std::to_string(idx++);
+            std::vector<float> w = cnn_tensor(hm, p + ".0.weight");        // [exp][1][k][k]
+            b.dw_b = fold_batchnorm(hm, p + ".1", t.exp, t.k * t.k, w);
+            b.dw_w.resize(size_t(t.k) * t.k * t.exp);
+            for (int ch = 0; ch < t.exp; ++ch)
+                for (int tap = 0; tap < t.k * t.k; ++tap) b.dw_w[size_t(tap) * t.exp + ch] = w[size_t(ch) * t.k * t.k + tap];
+        }
+        if (t.se) {
+            const std::string p = pre + std::to_string(idx++);
+            b.se_w1 = cnn_tensor(hm, p + ".fc1.weight");
+            b.se_b1 = cnn_tensor(hm, p + ".fc1.bias");
+            b.se_w2 = cnn_tensor(hm, p + ".fc2.weight");
+            b.se_b2 = cnn_tensor(hm, p + ".fc2.bias");
+            b.cs = int(b.se_b1.size());
+        }
+        {
+            const std::string p = pre + std::to_string(idx);
+            b.proj_w = cnn_tensor(hm, p + ".0.weight");
+            b.proj_b = fold_batchnorm(hm, p + ".1", t.out, t.exp, b.proj_w);
+        }
+        b.h_in = h; b.w_in = wd;
+        const int pad = (t.k - 1) / 2;
+        h = (h + 2 * pad - t.k) / t.stride + 1;
+        wd = (wd + 2 * pad - t.k) / t.stride + 1;
+        b.h_out = h; b.w_out = wd;
+    }
+    if (h != 6 || wd != 10) throw std::runtime_error("unexpected frame-encoder output size");
+    c.last_w = cnn_tensor(hm, "cnn.16.0.weight");
+    c.last_b = fold_batchnorm(hm, "cnn.16.1", CNN_OUT, 160, c.last_w);
+    return c;
+}
+
 }  // namespace shv

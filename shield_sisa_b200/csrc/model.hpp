@@ -3,7 +3,7 @@
 // Mirrors the types the reference engine exposes to its callers (engine/cuda/model.hpp:10-18,44-70): the same
 // dimension constants, the same fused projection layouts and `load_host_model`, so code written against the
 // reference's internal engine API compiles against this one.  The frame-encoder (MobileNetV3) tensors are validated
-// and kept verbatim in `cnn`; this engine does not run them.
+// and kept verbatim in `cnn`; `fold_cnn` turns them into the folded, NHWC-ordered form the encoder kernels read.
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -61,6 +61,26 @@ struct HostModel {
     SisaHost sisa;
     std::vector<float> final_norm_w, head_w0 /*[128][D]*/, head_b0 /*[128]*/, head_w2 /*[128]*/, head_b2 /*[1]*/;
 };
+
+// MobileNetV3-Large frame encoder with BatchNorm (eps 1e-3) folded into each convolution in double precision
+// (w' = w g / sqrt(var + eps), b' = beta - mean g / sqrt(var + eps)), as engine/cuda/model.cpp:56-91,182-214 does.
+struct CnnBlock {
+    int in = 0, k = 0, exp = 0, out = 0, stride = 1, act = 1;   // act: 1 ReLU, 2 Hardswish
+    bool se = false, has_expand = false, residual = false;
+    int h_in = 0, w_in = 0, h_out = 0, w_out = 0, cs = 0;       // cs: squeeze width, read from the file
+    std::vector<float> exp_w, exp_b;      // [exp][in], [exp]
+    std::vector<float> dw_w, dw_b;        // [k*k][exp] tap-major, [exp]
+    std::vector<float> se_w1, se_b1;      // [cs][exp], [cs]
+    std::vector<float> se_w2, se_b2;      // [exp][cs], [exp]
+    std::vector<float> proj_w, proj_b;    // [out][exp], [out]
+};
+struct CnnHost {
+    std::vector<float> lut;               // [3][256]: ((u / 255) - mean_c) / std_c, each step rounded to float32
+    std::vector<float> stem_w, stem_b;    // [27][16] with index ((kh*3 + kw)*3 + ci)*16 + co, [16]
+    CnnBlock blocks[15];
+    std::vector<float> last_w, last_b;    // [960][160], [960]
+};
+CnnHost fold_cnn(const HostModel& hm);
 
 // Reads and validates a SHLDV001 file: every tensor of the architecture present with its exact shape, all values
 // finite, nothing else in the file; hashes the file; reads "threshold" (must lie in (0,1)) from "<path>.json".

@@ -12,6 +12,10 @@ the reference architecture.  Two recipes:
         gated RMSNorm runs in its eps-dominated regime.
   "W3"  as W1, but every 2-D weight of the sequence stages ~ N(0, 1/fan_in) and the short-conv taps ~ N(0, 0.25),
         which gives O(1) activations, decay factors across (0, 1) and logits of order +-1: a much stricter test.
+  "W5"  as W3, and the frame encoder is scaled too: every convolution and squeeze-excite weight ~ N(0, 1/fan_in),
+        the token projection ~ N(0, 1/960), BatchNorm shifts and squeeze-excite biases ~ N(0, 0.25), so that the
+        feature maps stay O(1) through all 15 blocks and the encoder's tokens are O(1) (under W1 / W3 they are
+        about 1e-2 and test little).
 
 Values come from numpy's PCG64 `default_rng(seed)`, consumed in table order, so any machine regenerates the same file.
 """
@@ -103,8 +107,8 @@ def _is_gain(name: str, shape) -> bool:
 
 def synth_weights(seed: int = 1, recipe: str = "W3", sigma: float = 0.02) -> dict[str, np.ndarray]:
     """Seeded synthetic weights of the reference architecture (see the module docstring for the recipes)."""
-    if recipe not in ("W1", "W3"):
-        raise ValueError("recipe must be 'W1' or 'W3'")
+    if recipe not in ("W1", "W3", "W5"):
+        raise ValueError("recipe must be 'W1', 'W3' or 'W5'")
     rng = np.random.default_rng(seed)
     out: dict[str, np.ndarray] = {}
     for name, shape in tensor_table():
@@ -117,7 +121,14 @@ def synth_weights(seed: int = 1, recipe: str = "W3", sigma: float = 0.02) -> dic
         else:
             z = rng.standard_normal(shape, dtype=np.float64)
             scale = sigma
-            if recipe == "W3" and not name.startswith("cnn.") and name != "projection.weight":
+            if recipe == "W5" and (name.startswith("cnn.") or name == "projection.weight"):
+                if len(shape) == 4:
+                    scale = np.sqrt(1.0 / (shape[1] * shape[2] * shape[3]))
+                elif len(shape) == 2:
+                    scale = 1.0 / np.sqrt(shape[1])
+                else:
+                    scale = 0.5
+            elif recipe in ("W3", "W5") and not name.startswith("cnn.") and name != "projection.weight":
                 if name.endswith("conv1d.weight"):
                     scale = 0.5
                 elif len(shape) == 2 and name.endswith(".weight"):
@@ -180,6 +191,12 @@ def synth_weight_file(path, seed: int = 1, recipe: str = "W3", threshold: float 
     w = synth_weights(seed, recipe)
     write_shldv(path, w, threshold)
     return w
+
+
+def synth_frames(n: int, seed: int) -> np.ndarray:
+    """RGB crops [n, 180, 320, 3] uint8, uniform in [0, 255]: the stand-in for face crops."""
+    rng = np.random.default_rng(seed)
+    return rng.integers(0, 256, size=(n, 180, 320, 3), dtype=np.uint8)
 
 
 def synth_tokens(batch: int, seed: int) -> np.ndarray:

@@ -10,6 +10,8 @@ regenerated from the seeds stored in them (shield_sisa_b200/weights.py), so no w
 Each case file holds: recipe / seeds / batch; float64 and float32 logits of the PyTorch oracle; logits of the CPU
 engine; and (for the first two cases), for selected rows of the first and last window, float64 intermediates under the
 oracle's trace names.
+`encoder_*.npz` pins the frame encoder: float64 tokens of the PyTorch oracle (MobileNetV3 features, pooling, projection)
+on seeded uint8 crops, samples of its feature map, the CPU engine's tokens and the logit of a whole clip (shv_cpu_predict).
 `delta_rule.npz` pins the bare recurrence (gated_delta_rule_recurrent, float64) on a long-sequence case.
 """
 from __future__ import annotations
@@ -75,6 +77,30 @@ def run_case(name, recipe, wseed, tseed, batch, with_trace):
     print(name, out["logits_f64"], out.get("logits_cpu_engine"))
 
 
+def encoder_case(name, recipe, wseed, fseed, frames):
+    """Frame encoder: uint8 crops -> tokens, PyTorch oracle in float64 and the CPU engine."""
+    from oracle import cnn_oracle as CO
+    tmp = Path(tempfile.mkdtemp())
+    wpath = tmp / "synthetic.weights"
+    W.synth_weight_file(wpath, wseed, recipe)
+    fr = W.synth_frames(frames, fseed)
+    out = {"recipe": recipe, "weight_seed": wseed, "frame_seed": fseed, "frames": frames}
+    with torch.no_grad():
+        m64 = R.load_ref_from_weights(wpath, torch.float64)
+        x = torch.from_numpy(CO.normalise(fr, np.float32)).permute(0, 3, 1, 2).double()     # prepare_clips' float32 steps
+        fmap = m64.cnn_map(x)
+        out["tokens_f64"] = m64.tokens_from_map(fmap).numpy()
+        out["map_f64_sample"] = fmap.permute(0, 2, 3, 1).numpy()[:, ::2, ::3, ::7]           # NHWC, subsampled
+    if ref_cpu.available():
+        eng = ref_cpu.RefCpuEngine(wpath, threads=4)
+        out["tokens_cpu_engine"] = eng.encode_frames(fr)
+        clip = W.synth_frames(20, fseed + 1)[None]
+        out["clip_logit_cpu_engine"] = eng.predict(clip)
+        eng.close()
+    np.savez_compressed(HERE / f"{name}.npz", **out)
+    print(name, float(np.abs(out["tokens_f64"]).max()), out.get("clip_logit_cpu_engine"))
+
+
 def delta_rule_case():
     """Bare recurrence on a long sequence: B=2, T=300, H=3, DK=64, DV=128 (and DK=DV=128), float64."""
     out = {}
@@ -88,7 +114,11 @@ def delta_rule_case():
     print("delta_rule", {k: v.shape for k, v in out.items()})
 
 
+ENCODER_CASES = [("encoder_w5_s3_f11", "W5", 3, 11, 3), ("encoder_w1_s1_f5", "W1", 1, 5, 1)]
+
 if __name__ == "__main__":
     for case in CASES:
         run_case(*case)
+    for case in ENCODER_CASES:
+        encoder_case(*case)
     delta_rule_case()

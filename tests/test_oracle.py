@@ -77,3 +77,45 @@ def test_weight_file_round_trip(tmp_path, weight_files):
     for name, shape in W.tensor_table():
         assert back[name].shape == shape
         np.testing.assert_array_equal(back[name], w[name])
+
+
+# ---------------------------------------------------------------------------------------------- frame encoder
+ENCODER_CASES = ["encoder_w5_s3_f11", "encoder_w1_s1_f5"]
+
+
+def _encoder_inputs(g, weight_files):
+    from shield_sisa_b200 import weights as W
+    _, w = weight_files(str(g["recipe"]), int(g["weight_seed"]))
+    return w, W.synth_frames(int(g["frames"]), int(g["frame_seed"]))
+
+
+@pytest.mark.parametrize("case", ENCODER_CASES)
+def test_encoder_restatement_matches_reference_oracle(case, weight_files):
+    from oracle import cnn_oracle as CO
+    g = load_golden(case)
+    w, frames = _encoder_inputs(g, weight_files)
+    trace = {}
+    tok = CO.encode_frames(w, frames, np.float64, trace)
+    assert np.abs(tok - g["tokens_f64"]).max() < 1e-10
+    assert np.abs(trace["cnn_map"][:, ::2, ::3, ::7] - g["map_f64_sample"]).max() < 1e-10
+    tok32 = CO.encode_frames(w, frames, np.float32)
+    assert tok32.dtype == np.float32
+    assert np.abs(tok32 - g["tokens_f64"]).max() < 2e-5
+
+
+@pytest.mark.parametrize("case", ENCODER_CASES)
+def test_reference_cpu_engine_encoder_matches_golden(case, weight_files):
+    from oracle import ref_cpu
+    from shield_sisa_b200 import weights as W
+    if not ref_cpu.available():
+        pytest.skip("reference CPU engine not built")
+    g = load_golden(case)
+    path, _ = weight_files(str(g["recipe"]), int(g["weight_seed"]))
+    _, frames = _encoder_inputs(g, weight_files)
+    eng = ref_cpu.RefCpuEngine(path, threads=2)
+    tok = eng.encode_frames(frames)
+    assert np.abs(tok - g["tokens_cpu_engine"]).max() < 1e-6        # thread count and ISA do not change its results
+    assert np.abs(tok - g["tokens_f64"]).max() < 1e-5
+    clip = W.synth_frames(20, int(g["frame_seed"]) + 1)[None]
+    assert np.abs(eng.predict(clip) - g["clip_logit_cpu_engine"]).max() < 1e-6
+    eng.close()
