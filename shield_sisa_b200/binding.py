@@ -11,6 +11,7 @@ from pathlib import Path
 import numpy as np
 
 LIB_DIR = Path(__file__).resolve().parent / "lib"
+FRAME_BYTES = 172800
 TOKEN_FLOATS = 6144
 DTYPES = {"fp32": 0, "bf16": 1, "fp16": 2}
 
@@ -207,6 +208,22 @@ class CudaModel:
             raise RuntimeError(last_error(self.L))
         return out
 
+    def encode_frames(self, frames):
+        """uint8 crops [n,180,320,3] -> tokens [n,16,384] (shv_cuda_encode_frames)."""
+        f = np.ascontiguousarray(frames, dtype=np.uint8).reshape(-1, FRAME_BYTES)
+        out = np.zeros((f.shape[0], 16, 384), np.float32)
+        if self.L.shv_cuda_encode_frames(self.m, f.ctypes.data, f.shape[0], out.ctypes.data):
+            raise RuntimeError(last_error(self.L))
+        return out
+
+    def predict(self, clips):
+        """uint8 clips [b,20,180,320,3] -> logits [b] (shv_cuda_predict)."""
+        c = np.ascontiguousarray(clips, dtype=np.uint8).reshape(-1, 20 * FRAME_BYTES)
+        out = np.zeros(c.shape[0], np.float32)
+        if self.L.shv_cuda_predict(self.m, c.ctypes.data, c.shape[0], out.ctypes.data):
+            raise RuntimeError(last_error(self.L))
+        return out
+
     def classify_rc(self, tokens):
         """Like classify but returns (rc, logits, error) instead of raising."""
         t = np.ascontiguousarray(tokens, dtype=np.float32)
@@ -222,7 +239,7 @@ class CudaModel:
 
     # ---- asynchronous
     def submit(self, n_windows, logits_out, window_tokens=None, window_slots=None, window_frames=None, callback=None,
-               frames=None, n_frames=0):
+               frames=None, n_frames=0, tokens_out=None, store_slots=None):
         """Returns (job handle or None, keepalive tuple).  window_tokens: list of numpy blocks (or None entries)."""
         req = Request()
         keep = [logits_out]
@@ -241,6 +258,13 @@ class CudaModel:
             req.frames = frames.ctypes.data
             keep.append(frames)
         req.n_frames = n_frames
+        if tokens_out is not None:
+            req.tokens_out = tokens_out.ctypes.data
+            keep.append(tokens_out)
+        if store_slots is not None:
+            a = np.ascontiguousarray(store_slots, dtype=np.int32)
+            req.store_slots = a.ctypes.data_as(C.POINTER(C.c_int32))
+            keep.append(a)
         if callback is not None:
             cb = CALLBACK(callback)
             req.callback = cb

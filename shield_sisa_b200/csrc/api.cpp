@@ -10,8 +10,10 @@
 //   * shv_cuda_job_free waits for completion and for the callback to return before deleting (api.cu:194-203,630-637)
 // Beyond the reference: host token blocks that live in pinned memory are DMA'd straight from the caller's buffer as
 // contiguous runs (the reference stages every block through a memcpy), staging buffers are allocated on first use,
-// and shv_cuda_b200_upload_tokens fills device token slots from host tokens, since this library has no frame
-// encoder to fill them.
+// and shv_cuda_b200_upload_tokens fills device token slots from host tokens.
+//   * frames of a request are encoded first, their tokens stored into the token slots the request names, then the
+//     windows of the batch are classified (api.cu:233-318): a window sees the frames and stores of its own request and
+//     of every earlier request
 #include "shv_cuda.h"
 #include "shv_cuda_b200.h"
 #include "engine.hpp"
@@ -37,7 +39,7 @@ namespace {
 using Clock = std::chrono::steady_clock;
 thread_local std::string t_error;
 constexpr float kNaN = std::numeric_limits<float>::quiet_NaN();
-constexpr size_t kBlockFloats = SHV_CUDA_TOKEN_FLOATS, kBlockBytes = kBlockFloats * 4;
+constexpr size_t kBlockFloats = SHV_CUDA_TOKEN_FLOATS, kBlockBytes = kBlockFloats * 4, kFrameBytes = SHV_CUDA_FRAME_BYTES;
 
 void cuda_ok(cudaError_t e, const char* what) {
     if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA error ") + cudaGetErrorString(e) + " in " + what);
@@ -64,7 +66,14 @@ struct HostRun {
 struct shv_cuda_job {
     // request
     size_t n_windows = 0;
-    std::vector<int32_t> wslots;            // per entry, -1 = host block
+    const uint8_t* frames = nullptr;        // request frames [n_frames][172800], borrowed until completion
+    size_t n_frames = 0;
+    float* tokens_out = nullptr;            // optional: tokens of the request's frames
+    bool frames_pinned = false, tokens_out_pinned = false;
+    std::vector<int32_t> frame_store;       // per frame: token slot its tokens are stored into, -1 = none (may be empty)
+    std::vector<int32_t> wframes;           // per entry: frame of this request, -1 = none (may be empty)
+    int frame_off = 0;                      // first frame of this job in its batch
+    std::vector<int32_t> wslots;            // per entry, -1 = host block or frame
     std::vector<HostRun> runs;              // host blocks in entry order
     int host_blocks = 0;
     float* logits_out = nullptr;
@@ -92,13 +101,17 @@ struct HostSide {                            // pinned companions of one engine 
     int32_t* store = nullptr;                // [max_host_tokens]
     int32_t* d_store = nullptr;              // device copy
     float* logits = nullptr;                 // [max_windows]
+    uint8_t* frames = nullptr;               // [max_frames][172800], allocated on first unpinned frame
+    float* tokens_out = nullptr;             // [max_frames][6144], allocated on first unpinned tokens_out
+    int32_t* fstore = nullptr;               // [max_frames] token slot per encoded frame
+    int32_t* d_fstore = nullptr;             // device copy
     cudaEvent_t copied = nullptr, start = nullptr, end = nullptr;
 };
 
 struct Batch {
     int slot = 0;
     std::vector<shv_cuda_job*> jobs;
-    int windows = 0;
+    int windows = 0, frames = 0;
     bool failed = false;
     std::string error;
 };
@@ -121,6 +134,10 @@ public:
             if (h.store) cudaFreeHost(h.store);
             if (h.d_store) cudaFree(h.d_store);
             if (h.logits) cudaFreeHost(h.logits);
+            if (h.frames) cudaFreeHost(h.frames);
+            if (h.tokens_out) cudaFreeHost(h.tokens_out);
+            if (h.fstore) cudaFreeHost(h.fstore);
+            if (h.d_fstore) cudaFree(h.d_fstore);
             for (cudaEvent_t e : {h.copied, h.start, h.end})
                 if (e) cudaEventDestroy(e);
         }
@@ -135,7 +152,7 @@ public:
         cuda_ok(cudaStreamCreateWithFlags(&compute_, cudaStreamNonBlocking), "stream");
         cuda_ok(cudaStreamCreateWithFlags(&copy_, cudaStreamNonBlocking), "stream");
         shv::EngineConfig ec;
-        ec.max_frames = 1;                   // no frame encoder: one token block keeps the pointer table valid
+        ec.max_frames = opt.max_frames;
         ec.max_windows = opt.max_windows;
         ec.use_graphs = opt.use_graphs != 0;
         ec.slots = 2;
@@ -149,6 +166,8 @@ public:
             cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.store), Hm * 4, cudaHostAllocDefault), "pinned alloc");
             cuda_ok(cudaMalloc(reinterpret_cast<void**>(&h.d_store), Hm * 4), "device alloc");
             cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.logits), Bm * 4, cudaHostAllocDefault), "pinned alloc");
+            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.fstore), size_t(opt.max_frames) * 4, cudaHostAllocDefault), "pinned alloc");
+            cuda_ok(cudaMalloc(reinterpret_cast<void**>(&h.d_fstore), size_t(opt.max_frames) * 4), "device alloc");
             cuda_ok(cudaEventCreateWithFlags(&h.copied, cudaEventDisableTiming), "event");
             cuda_ok(cudaEventCreate(&h.start), "event");
             cuda_ok(cudaEventCreate(&h.end), "event");
@@ -158,7 +177,7 @@ public:
             cuda_ok(cudaMemset(d_pool, 0, size_t(opt.token_slots) * kBlockBytes), "token slots");
         }
         device_bytes = engine->weight_bytes() + engine->activation_bytes() +
-                       size_t(ec.slots) * (engine->slot_bytes() + Hm * 4) + size_t(std::max(opt.token_slots, 0)) * kBlockBytes;
+                       size_t(ec.slots) * (engine->slot_bytes() + Hm * 4 + size_t(opt.max_frames) * 4) + size_t(std::max(opt.token_slots, 0)) * kBlockBytes;
         if (const char* e = std::getenv("SHV_CUDA_FAIL_EVERY")) fail_every = std::atol(e);
         cuda_ok(cudaDeviceSynchronize(), "init");
         worker_ = std::thread([this] { loop(); });
@@ -197,9 +216,11 @@ private:
     std::thread worker_;
     long batches_ = 0;
 
-    static void finish_job(shv_cuda_job* j, bool ok, const std::string& err, float gpu_ms, int windows) {
-        if (!ok)
+    static void finish_job(shv_cuda_job* j, bool ok, const std::string& err, float gpu_ms, int frames, int windows) {
+        if (!ok) {
             for (size_t i = 0; i < j->n_windows; ++i) j->logits_out[i] = kNaN;
+            if (j->tokens_out) std::fill(j->tokens_out, j->tokens_out + j->n_frames * kBlockFloats, kNaN);
+        }
         shv_cuda_callback cb;
         void* user;
         {
@@ -208,7 +229,7 @@ private:
             j->error = ok ? std::string() : err;
             j->t_done = Clock::now();
             j->gpu_ms = gpu_ms;
-            j->batch_frames = 0;
+            j->batch_frames = frames;
             j->batch_windows = windows;
             cb = j->cb;
             user = j->user;
@@ -222,23 +243,28 @@ private:
 
     // Pops queued jobs in order while the limits hold and no store hazard appears.  Caller holds mu_.
     void coalesce(std::vector<shv_cuda_job*>& out) {
-        int windows = 0, blocks = 0;
+        int windows = 0, blocks = 0, frames = 0;
         std::unordered_set<int32_t> read, stored;
         while (!queue_.empty()) {
             shv_cuda_job* j = queue_.front();
             if (!out.empty()) {
-                if (windows + int(j->n_windows) > opt.max_windows || blocks + j->host_blocks > block_cap()) break;
+                if (windows + int(j->n_windows) > opt.max_windows || blocks + j->host_blocks > block_cap() ||
+                    frames + int(j->n_frames) > opt.max_frames)
+                    break;
                 bool hazard = false;
-                for (int32_t s : j->store_slots)
-                    if (s >= 0 && (read.count(s) || stored.count(s))) { hazard = true; break; }
+                for (const std::vector<int32_t>* v : {&j->store_slots, &j->frame_store})
+                    for (int32_t s : *v)
+                        if (s >= 0 && (read.count(s) || stored.count(s))) { hazard = true; break; }
                 if (hazard) break;
             }
             queue_.pop_front();
             out.push_back(j);
             windows += int(j->n_windows);
             blocks += j->host_blocks;
-            for (int32_t s : j->store_slots)
-                if (s >= 0) stored.insert(s);
+            frames += int(j->n_frames);
+            for (const std::vector<int32_t>* v : {&j->store_slots, &j->frame_store})
+                for (int32_t s : *v)
+                    if (s >= 0) stored.insert(s);
             for (int32_t s : j->wslots)
                 if (s >= 0) read.insert(s);
         }
@@ -254,12 +280,34 @@ private:
         try {
             ++batches_;
             if (fail_every > 0 && batches_ % fail_every == 0) throw std::runtime_error("injected batch failure (SHV_CUDA_FAIL_EVERY)");
-            int windows = 0, blocks = 0, stores = 0;
+            int windows = 0, blocks = 0, stores = 0, frames = 0;
+            bool frame_stores = false;
             for (shv_cuda_job* j : jobs) {
                 j->t_start = t0;
                 j->window_off = windows;
+                j->frame_off = frames;
+                if (j->n_frames) {                              // crops: pinned sources by DMA, the rest staged
+                    uint8_t* dst = d.d_frames + size_t(frames) * kFrameBytes;
+                    const size_t bytes = j->n_frames * kFrameBytes;
+                    if (j->frames_pinned) {
+                        cuda_ok(cudaMemcpyAsync(dst, j->frames, bytes, cudaMemcpyHostToDevice, copy_), "frame upload");
+                    } else {
+                        if (!h.frames)
+                            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.frames), size_t(opt.max_frames) * kFrameBytes,
+                                                  cudaHostAllocDefault), "pinned staging");
+                        uint8_t* st = h.frames + size_t(frames) * kFrameBytes;
+                        std::memcpy(st, j->frames, bytes);
+                        cuda_ok(cudaMemcpyAsync(dst, st, bytes, cudaMemcpyHostToDevice, copy_), "frame upload");
+                    }
+                    for (size_t f = 0; f < j->n_frames; ++f) {
+                        const int32_t sl = j->frame_store.empty() ? -1 : j->frame_store[f];
+                        h.fstore[size_t(frames) + f] = sl;
+                        frame_stores |= sl >= 0;
+                    }
+                }
                 size_t e = 0;                                   // next window entry that takes a host block
                 const size_t entries = j->n_windows * 20;
+                auto from_frame = [&](size_t k) { return !j->wframes.empty() && j->wframes[k] >= 0; };
                 int stored_here = 0;
                 for (const HostRun& run : j->runs) {
                     float* dst = d.d_tok_stage + size_t(blocks) * kBlockFloats;
@@ -282,17 +330,24 @@ private:
                             ++stores;
                         } else {
                             h.store[blocks + i] = -1;
-                            while (e < entries && j->wslots[e] >= 0) ++e;
+                            while (e < entries && (j->wslots[e] >= 0 || from_frame(e))) ++e;
                             h.tokptr[size_t(windows) * 20 + e] = dev_block;
                             ++e;
                         }
                     }
                     blocks += run.blocks;
                 }
-                for (size_t k = 0; k < entries; ++k)
-                    if (j->wslots[k] >= 0) h.tokptr[size_t(windows) * 20 + k] = d_pool + size_t(j->wslots[k]) * kBlockFloats;
+                for (size_t k = 0; k < entries; ++k) {
+                    if (from_frame(k))
+                        h.tokptr[size_t(windows) * 20 + k] = d.d_tokens + size_t(frames + j->wframes[k]) * kBlockFloats;
+                    else if (j->wslots[k] >= 0)
+                        h.tokptr[size_t(windows) * 20 + k] = d_pool + size_t(j->wslots[k]) * kBlockFloats;
+                }
                 windows += int(j->n_windows);
+                frames += int(j->n_frames);
             }
+            if (frame_stores)
+                cuda_ok(cudaMemcpyAsync(h.d_fstore, h.fstore, size_t(frames) * 4, cudaMemcpyHostToDevice, copy_), "slot list upload");
             if (windows)
                 cuda_ok(cudaMemcpyAsync(d.d_tokptr, h.tokptr, size_t(windows) * 20 * sizeof(float*), cudaMemcpyHostToDevice, copy_),
                         "pointer table upload");
@@ -301,13 +356,25 @@ private:
             cuda_ok(cudaEventRecord(h.copied, copy_), "event");
             cuda_ok(cudaStreamWaitEvent(compute_, h.copied, 0), "event");
             cuda_ok(cudaEventRecord(h.start, compute_), "event");
+            if (frames) engine->encode(slot, frames, compute_);
+            if (frame_stores) cuda_ok(cudaError_t(shvk_store_tokens(d.d_tokens, h.d_fstore, d_pool, frames, compute_)), "token slot store");
             if (stores) cuda_ok(cudaError_t(shvk_store_tokens(d.d_tok_stage, h.d_store, d_pool, blocks, compute_)), "token slot store");
             if (windows) {
                 engine->classify(slot, windows, compute_);
                 cuda_ok(cudaMemcpyAsync(h.logits, d.d_logits, size_t(windows) * 4, cudaMemcpyDeviceToHost, compute_), "logit download");
             }
+            for (shv_cuda_job* j : jobs) {
+                if (!j->tokens_out || !j->n_frames) continue;
+                if (!j->tokens_out_pinned && !h.tokens_out)
+                    cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.tokens_out), size_t(opt.max_frames) * kBlockBytes,
+                                          cudaHostAllocDefault), "pinned staging");
+                float* dst = j->tokens_out_pinned ? j->tokens_out : h.tokens_out + size_t(j->frame_off) * kBlockFloats;
+                cuda_ok(cudaMemcpyAsync(dst, d.d_tokens + size_t(j->frame_off) * kBlockFloats, j->n_frames * kBlockBytes,
+                                        cudaMemcpyDeviceToHost, compute_), "token download");
+            }
             cuda_ok(cudaEventRecord(h.end, compute_), "event");
             b.windows = windows;
+            b.frames = frames;
         } catch (const std::exception& e) {
             b.failed = true;
             b.error = e.what();
@@ -335,12 +402,15 @@ private:
             cudaStreamSynchronize(copy_);
         }
         for (shv_cuda_job* j : b.jobs) {
-            if (!b.failed)
+            if (!b.failed) {
                 for (size_t i = 0; i < j->n_windows; ++i) {
                     const float v = h.logits[size_t(j->window_off) + i];
                     j->logits_out[i] = std::isfinite(v) ? v : kNaN;
                 }
-            finish_job(j, !b.failed, b.error, gpu_ms, b.windows);
+                if (j->tokens_out && !j->tokens_out_pinned && j->n_frames)
+                    std::memcpy(j->tokens_out, h.tokens_out + size_t(j->frame_off) * kBlockFloats, j->n_frames * kBlockBytes);
+            }
+            finish_job(j, !b.failed, b.error, gpu_ms, b.frames, b.windows);
         }
     }
 
@@ -418,10 +488,6 @@ int wait_and_free(std::vector<shv_cuda_job*>& jobs) {
     if (rc) t_error = err;
     return rc;
 }
-
-const char kNoEncoder[] =
-    "this library holds the SHIELD-V sequence stages only: it has no frame encoder, so frames cannot be encoded "
-    "(pass tokens through window_tokens or device token slots)";
 
 }  // namespace
 
@@ -516,21 +582,35 @@ shv_cuda_job* shv_cuda_submit(shv_cuda_model* m, const shv_cuda_request* r) {
         if (r->n_frames && !r->frames) throw std::runtime_error("null frames");
         if (r->n_windows && !r->logits_out) throw std::runtime_error("null logits_out");
         if (!r->n_frames && !r->n_windows) throw std::runtime_error("empty request");
-        if (r->n_frames) throw std::runtime_error(kNoEncoder);
         auto j = std::unique_ptr<shv_cuda_job>(new shv_cuda_job());
+        j->frames = r->frames;
+        j->n_frames = r->n_frames;
+        j->tokens_out = r->n_frames ? r->tokens_out : nullptr;
+        if (r->store_slots && r->n_frames) {
+            if (!s.d_pool) throw std::runtime_error("store_slots needs options.token_slots > 0");
+            j->frame_store.assign(r->store_slots, r->store_slots + r->n_frames);
+            std::unordered_set<int32_t> seen;
+            for (int32_t sl : j->frame_store) {
+                if (sl < -1 || sl >= o.token_slots) throw std::runtime_error("store slot out of range");
+                if (sl >= 0 && !seen.insert(sl).second) throw std::runtime_error("duplicate store slot in one request");
+            }
+        }
         j->n_windows = r->n_windows;
         j->logits_out = r->logits_out;
         j->cb = r->callback;
         j->user = r->user;
         const size_t entries = r->n_windows * 20;
         j->wslots.assign(entries, -1);
+        if (r->window_frames && r->n_frames) j->wframes.assign(entries, -1);
         std::vector<const float*> host;
         host.reserve(entries);
         for (size_t e = 0; e < entries; ++e) {
             const int32_t wf = r->window_frames ? r->window_frames[e] : -1;
             const int32_t ws = r->window_slots ? r->window_slots[e] : -1;
-            if (wf >= 0) throw std::runtime_error("window frame index out of range");     // the request has no frames
-            if (ws >= 0) {
+            if (wf >= 0) {
+                if (size_t(wf) >= r->n_frames) throw std::runtime_error("window frame index out of range");
+                j->wframes[e] = wf;
+            } else if (ws >= 0) {
                 if (!s.d_pool || ws >= o.token_slots) throw std::runtime_error("window slot out of range");
                 j->wslots[e] = ws;
             } else {
@@ -541,6 +621,8 @@ shv_cuda_job* shv_cuda_submit(shv_cuda_model* m, const shv_cuda_request* r) {
         if (host.size() > size_t(o.max_host_tokens))
             throw std::runtime_error("request has more host token blocks than max_host_tokens");
         add_runs(*j, host.data(), host.size());
+        j->frames_pinned = host_pinned(r->frames, r->n_frames * kFrameBytes);
+        j->tokens_out_pinned = j->tokens_out && host_pinned(j->tokens_out, r->n_frames * kBlockBytes);
         j->t_submit = Clock::now();
         shv_cuda_job* raw = j.release();
         if (!s.enqueue(raw)) {
@@ -609,18 +691,53 @@ void shv_cuda_host_free(void* p) {
 int shv_cuda_encode_frames(shv_cuda_model* m, const uint8_t* rgb, size_t n, float* tokens) {
     return guarded([&]() -> int {
         if (!m || (n && (!rgb || !tokens))) throw std::runtime_error("null argument");
-        if (!n) return 0;
-        std::fill(tokens, tokens + n * kBlockFloats, kNaN);
-        throw std::runtime_error(kNoEncoder);
+        const size_t step = size_t(m->sched->opt.max_frames);
+        std::vector<shv_cuda_job*> jobs;
+        for (size_t off = 0; off < n; off += step) {
+            shv_cuda_request r{};
+            r.frames = rgb + off * kFrameBytes;
+            r.n_frames = std::min(step, n - off);
+            r.tokens_out = tokens + off * kBlockFloats;
+            shv_cuda_job* j = shv_cuda_submit(m, &r);
+            if (!j) {
+                const std::string why = t_error;
+                wait_and_free(jobs);
+                std::fill(tokens, tokens + n * kBlockFloats, kNaN);
+                throw std::runtime_error(why);
+            }
+            jobs.push_back(j);
+        }
+        return wait_and_free(jobs);
     });
 }
 
 int shv_cuda_predict(shv_cuda_model* m, const uint8_t* clips, size_t b, float* logits) {
     return guarded([&]() -> int {
         if (!m || (b && (!clips || !logits))) throw std::runtime_error("null argument");
-        if (!b) return 0;
-        std::fill(logits, logits + b, kNaN);
-        throw std::runtime_error(kNoEncoder);
+        const shv_cuda_options& o = m->sched->opt;
+        const size_t step = size_t(std::min(o.max_windows, o.max_frames / 20));
+        if (step < 1) throw std::runtime_error("predict needs max_frames >= 20");
+        std::vector<int32_t> idx(step * 20);
+        for (size_t e = 0; e < idx.size(); ++e) idx[e] = int32_t(e);
+        std::vector<shv_cuda_job*> jobs;
+        for (size_t off = 0; off < b; off += step) {
+            const size_t w = std::min(step, b - off);
+            shv_cuda_request r{};
+            r.frames = clips + off * 20 * kFrameBytes;
+            r.n_frames = w * 20;
+            r.n_windows = w;
+            r.window_frames = idx.data();
+            r.logits_out = logits + off;
+            shv_cuda_job* j = shv_cuda_submit(m, &r);
+            if (!j) {
+                const std::string why = t_error;
+                wait_and_free(jobs);
+                std::fill(logits, logits + b, kNaN);
+                throw std::runtime_error(why);
+            }
+            jobs.push_back(j);
+        }
+        return wait_and_free(jobs);
     });
 }
 

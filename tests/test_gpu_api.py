@@ -79,19 +79,23 @@ def test_request_validation(model):
         (dict(n_windows=1, logits_out=out, window_tokens=[None] * 20), "window entry has no token source"),
         (dict(n_windows=1, logits_out=out, window_slots=[64] + [0] * 19), "window slot out of range"),
         (dict(n_windows=1, logits_out=out, window_frames=[0] * 20, window_tokens=blocks_of(tok)), "window frame index out of range"),
-        (dict(n_windows=0, logits_out=out, frames=np.zeros(172800, np.uint8), n_frames=1), "no frame encoder"),
+        (dict(n_windows=0, logits_out=out, frames=None, n_frames=1), "null frames"),
+        (dict(n_windows=0, logits_out=out, frames=np.zeros(172800, np.uint8), n_frames=641), "more frames than max_frames"),
+        (dict(n_windows=0, logits_out=out, frames=np.zeros(2 * 172800, np.uint8), n_frames=2, store_slots=[64, 0]),
+         "store slot out of range"),
+        (dict(n_windows=0, logits_out=out, frames=np.zeros(2 * 172800, np.uint8), n_frames=2, store_slots=[5, 5]),
+         "duplicate store slot"),
+        (dict(n_windows=1, logits_out=out, frames=np.zeros(172800, np.uint8), n_frames=1, window_frames=[1] + [0] * 19),
+         "window frame index out of range"),
     ]
     for kwargs, msg in cases:
         job, keep = model.submit(**kwargs)
         assert not job, msg
         assert msg in binding.last_error(L), (msg, binding.last_error(L))
-    # the synchronous frame entry points exist and fail loudly, with NaN outputs
-    clips = np.zeros((1, 20, 172800), np.uint8)
     lg = np.zeros(1, np.float32)
-    assert L.shv_cuda_predict(model.m, clips.ctypes.data, 1, lg.ctypes.data) == -1
-    assert np.isnan(lg).all() and "no frame encoder" in binding.last_error(L)
-    tk = np.zeros(6144, np.float32)
-    assert L.shv_cuda_encode_frames(model.m, clips.ctypes.data, 1, tk.ctypes.data) == -1 and np.isnan(tk).all()
+    assert L.shv_cuda_predict(model.m, None, 1, lg.ctypes.data) == -1 and "null argument" in binding.last_error(L)
+    assert L.shv_cuda_encode_frames(model.m, None, 1, lg.ctypes.data) == -1 and "null argument" in binding.last_error(L)
+    assert L.shv_cuda_encode_frames(model.m, None, 0, None) == 0 and L.shv_cuda_predict(model.m, None, 0, None) == 0
     assert L.shv_cuda_classify(model.m, None, 1, lg.ctypes.data) == -1 and "null argument" in binding.last_error(L)
     assert L.shv_cuda_classify(model.m, None, 0, None) == 0
 
