@@ -47,6 +47,25 @@ size_t shvk_cnn_se_partial_floats(int F, int HW, int C);
 int shvk_cnn_se_gate(const float* x, float* partial, const float* w1, const float* b1, const float* w2, const float* b2,
                      float* gate, int F, int HW, int C, int CS, void* stream);
 
+/* shvk_cnn_se_gate without caller-provided scratch and without any device allocation.  No counterpart in the reference
+ * (its engine allocates the partial-sum buffer with the rest of its arena, engine/cuda/engine.cu:246-262).
+ *
+ * For callers that cannot allocate device memory when they need the gate: a host that handed the whole GPU to its own
+ * memory pool at start-up, or a frame loop in which cudaMalloc's device-wide synchronisation and its chance of failing
+ * are not acceptable.  The partial sums live in an array that is part of the library image: SHVK_CNN_SE_STATIC_FLOATS
+ * floats (1 MiB) on every GPU that loads the library, held until the process exits.  The call is refused with
+ * cudaErrorInvalidValue, and shv_cuda_last_error() says why, when shvk_cnn_se_partial_floats(F, HW, C) exceeds that
+ * (the largest squeeze-excite layer of the encoder, 240 pixels x 672 channels, fits 97 frames).
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call outside any stream capture.  All calls share the one array: it keeps whatever the
+ * previous call left, which is harmless because every partial sum a call reads it has written first (nothing needs
+ * clearing), but two calls whose kernels overlap on the GPU (different streams, or different host threads) race on
+ * it and must be ordered by the caller.  Results are bitwise those of shvk_cnn_se_gate. */
+#define SHVK_CNN_SE_STATIC_FLOATS (1 << 18)
+int shvk_cnn_se_gate_static(const float* x, const float* w1, const float* b1, const float* w2, const float* b2, float* gate,
+                            int F, int HW, int C, int CS, void* stream);
+
 /* 1x1 convolution as a row GEMM: out[m][n] = act(sum_k (A[m][k] * gate[m / gate_rows][k]) * W[n][k] + b[n]) (+ R[m][n]).
  * A [M][K] (pitch K), W [N][K], out and R [M][N] (R may alias out); gate NULL = no squeeze-excite scaling, else
  * [M / gate_rows][K]; K and N multiples of 4.  Each output is one fma chain over k in order.
