@@ -18,6 +18,8 @@ collective on the data path (weak scaling).  Rank 0 prints one JSON line:
   roofline   for the kernel with the largest share of the step: algorithmic bytes (or flops) per launch / its mean
              launch time, measured here with CUDA events, against the measured peak in MEASURED_PEAKS.json
   cpu_baseline  the reference's exact-FP32 CPU engine (oracle/_ref) on the host cores, on a bounded sample (N=1 only)
+  encoder    beside the metric (N=1 only): frames/s of the frame encoder (Engine::encode, 512 crops resident in HBM),
+             its time by kernel kind and its fraction of the HBM peak under the layer-boundary byte model
 
 `--impl reference` times the reference's own CPU implementation of this path on all host cores (rank 0 only).
 """
@@ -126,6 +128,73 @@ class ClockSampler:
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# MobileNetV3-Large block table of the frame encoder: (in, kernel, expanded, out, squeeze-excite, stride)
+_ENC_BLOCKS = [(16, 3, 16, 16, 0, 1), (16, 3, 64, 24, 0, 2), (24, 3, 72, 24, 0, 1), (24, 5, 72, 40, 1, 2), (40, 5, 120, 40, 1, 1),
+               (40, 5, 120, 40, 1, 1), (40, 3, 240, 80, 0, 2), (80, 3, 200, 80, 0, 1), (80, 3, 184, 80, 0, 1), (80, 3, 184, 80, 0, 1),
+               (80, 3, 480, 112, 1, 1), (112, 3, 672, 112, 1, 1), (112, 5, 672, 160, 1, 2), (160, 5, 960, 160, 1, 1),
+               (160, 5, 960, 160, 1, 1)]
+
+
+def encoder_work():
+    """(HBM bytes, flops) per frame of the frame encoder under the layer-boundary model: float32 NHWC activations, every
+    tensor that crosses a kernel boundary read or written once, weights not counted."""
+    h, w = 90, 160
+    nbytes = 180 * 320 * 3 + h * w * 16 * 4
+    flops = 2 * h * w * 16 * 27
+    for cin, k, cexp, cout, se, stride in _ENC_BLOCKS:
+        hw_in = h * w
+        pad = (k - 1) // 2
+        h, w = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+        hw_out = h * w
+        if cexp != cin:
+            nbytes += hw_in * (cin + cexp) * 4
+            flops += 2 * hw_in * cin * cexp
+        nbytes += (hw_in + hw_out) * cexp * 4
+        flops += 2 * hw_out * cexp * k * k
+        if se:
+            nbytes += hw_out * cexp * 4
+        nbytes += hw_out * (cexp + cout) * 4 + (hw_out * cout * 4 if stride == 1 and cin == cout else 0)
+        flops += 2 * hw_out * cexp * cout
+    nbytes += 60 * (160 + 960) * 4 + (60 + 16) * 960 * 4 + 16 * (960 + 384) * 4
+    flops += 2 * 60 * 160 * 960 + 2 * 16 * 960 * 384
+    return nbytes, flops
+
+
+def encoder_leg(binding, torch, wpath, mode, local_rank, frames=512, steps=10, warmup=3):
+    """Frames/s of Engine::encode on crops resident in HBM (CUDA events on the launching stream, graphs on)."""
+    eng = binding.EngineCore(wpath, mode, device=local_rank, max_windows=1, max_frames=frames, use_graphs=True)
+    crops = torch.randint(0, 256, (frames * 172800,), dtype=torch.uint8, device="cuda")
+
+    class _Slot:
+        __cuda_array_interface__ = {"shape": (frames * 172800,), "typestr": "|u1", "data": (int(eng.frames_ptr(0)), False),
+                                    "version": 2}
+
+    torch.as_tensor(_Slot(), device="cuda").copy_(crops)
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(warmup):
+        eng.encode(0, frames, stream)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        eng.encode(0, frames, stream)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    kinds = {}
+    for name, t in eng.profile_encode(0, frames, stream):
+        kinds[name] = kinds.get(name, 0.0) + t
+    nbytes, flops = encoder_work()
+    pk, pk_src = peaks()
+    out = {"frames_per_s": frames / (ms / 1000.0), "frames": frames, "ms_per_encode": ms, "launches": eng.encode_launches(),
+           "dtype": "f32", "ms_by_kernel": kinds, "algorithmic_bytes_per_frame": nbytes, "flops_per_frame": flops,
+           "hbm_frac": frames * nbytes / (ms / 1000.0) / (pk["hbm_gbs"] * 1e9), "peak_source": pk_src,
+           "note": "frame encoder (MobileNetV3-Large, 320x180 crops -> 16 x 384 tokens), float32 NHWC in every mode; "
+                   "crops resident in HBM; not part of `value`"}
+    eng.close()
+    return out
 
 
 def make_weights(tag: str):
@@ -307,12 +376,18 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     del eng
     torch.cuda.empty_cache()
 
+    # ------------------------------------------------------------ frame encoder beside it (rank 0, N = 1; not in `value`)
+    encoder = None
+    if rank == 0 and world == 1 and not args.no_encoder:
+        encoder = encoder_leg(binding, torch, wpath, mode, local_rank)
+        torch.cuda.empty_cache()
+
     # ------------------------------------------------------------ end to end through the C ABI with host buffers
     e2e = None
     if B <= 4096:
         mw = max(1, min(B, args.e2e_windows))
         model = binding.CudaModel(wpath, mode, device=local_rank, experimental=True, max_windows=mw,
-                                  max_host_tokens=20 * mw)
+                                  max_host_tokens=20 * mw, max_frames=1)
         pin = binding.PinnedBuffer(model.L, (B, 20, 16, D))
         pin.array[...] = tokens.cpu().numpy()
         out = np.empty(B, np.float32)
@@ -377,7 +452,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
             "stack_hbm_fraction": {"algorithmic_bytes_per_clip": alg_bytes_clip, "frac": stack_frac,
                                    "note": "whole stack against the GEMM-boundary byte model and the measured HBM peak"},
-            "kernels": kernels,
+            "kernels": kernels, "encoder": encoder,
         }
         emit(line)
     if world > 1:
@@ -407,6 +482,7 @@ def main():
     ap.add_argument("--mode", default="bf16", choices=["fp32", "bf16", "fp16"])
     ap.add_argument("--batch", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-encoder", action="store_true", help="skip the frame-encoder leg")
     ap.add_argument("--e2e-threads", type=int, default=2,
                     help="host threads of the end-to-end leg, each calling shv_cuda_classify on its share of the batch")
     ap.add_argument("--e2e-windows", type=int, default=1024,

@@ -173,42 +173,68 @@ se_gate_kernel(const float* __restrict__ partial, const float* __restrict__ w1, 
 }
 
 // ---------------------------------------------------------------------------------------------------- 1x1 convolution
-// Row GEMM on CUDA cores: tile 64 pixels x 64 output channels x 8 input channels, 256 threads, 4 x 4 outputs per
-// thread, next tile fetched into registers while the current one is consumed.  One fma chain over k per output.
-constexpr int PW_M = 64, PW_N = 64, PW_K = 8, PW_PITCH = 68;
+// Row GEMM on CUDA cores, 256 threads, k in slabs of 8, next slab fetched into registers while the current one is
+// consumed.  One fma chain over k per output, so a pixel's result does not depend on the tile shape's row count.
+// Tile shapes (pixels x output channels, per-thread outputs): 256 x 16 and 128 x 32 and 64 x 64 with 4 x 4 for the narrow
+// layers (every thread has live columns), 128 x 128 with 8 x 8 for the wide ones (half the shared-memory reads per fma).
+constexpr int PW_K = 8;
+template <int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__(256)
 pointwise_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
                  const float* __restrict__ gate, int gate_rows, const float* R, float* out, int M, int N, int K, int act) {
-    __shared__ __align__(16) float sa[2][PW_K][PW_PITCH];
-    __shared__ __align__(16) float sw[2][PW_K][PW_PITCH];
-    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const long long m0 = (long long)blockIdx.x * PW_M;
-    const int n0 = blockIdx.y * PW_N;
-    // loader role: threads 0..127 fetch A (row tid / 2, k quad tid % 2), threads 128..255 fetch W
-    const bool is_a = tid < 128;
-    const int lrow = (tid & 127) >> 1, lk = (tid & 1) * 4;
-    const long long arow = m0 + lrow;
-    const int wrow = n0 + lrow;
-    const bool live = is_a ? arow < M : wrow < N;
-    const float* src = is_a ? A + arow * K : W + (long long)wrow * K;
-    const float* gsrc = (is_a && gate && live) ? gate + (arow / gate_rows) * K : nullptr;
-    float4 reg;
+    static_assert((BM / TM) * (BN / TN) == 256, "256 threads");
+    constexpr int NX = BN / TN, PA = BM + 4, PB = BN + 4, SLOTS = (BM + BN) * 2, PER = (SLOTS + 255) / 256;
+    __shared__ __align__(16) float sa[2][PW_K][PA];
+    __shared__ __align__(16) float sw[2][PW_K][PB];
+    const int tid = threadIdx.x, tx = tid % NX, ty = tid / NX;
+    const long long m0 = (long long)blockIdx.x * BM;
+    const int n0 = blockIdx.y * BN;
+    // loader slots: slot i covers row i / 2 (A rows first, then W rows), k quad i % 2
+    const float* src[PER];
+    const float* gsrc[PER];
+    float4 reg[PER];
+#pragma unroll
+    for (int r = 0; r < PER; ++r) {
+        const int i = tid + r * 256, row = i >> 1;
+        src[r] = nullptr;
+        gsrc[r] = nullptr;
+        if (i < SLOTS) {
+            if (row < BM) {
+                const long long m = m0 + row;
+                if (m < M) {
+                    src[r] = A + m * K + (i & 1) * 4;
+                    if (gate) gsrc[r] = gate + (m / gate_rows) * K + (i & 1) * 4;
+                }
+            } else if (n0 + row - BM < N) {
+                src[r] = W + (long long)(n0 + row - BM) * K + (i & 1) * 4;
+            }
+        }
+    }
     auto fetch = [&](int k0) {
-        reg = live ? *reinterpret_cast<const float4*>(src + k0 + lk) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (gsrc) {
-            const float4 g = *reinterpret_cast<const float4*>(gsrc + k0 + lk);
-            reg.x *= g.x; reg.y *= g.y; reg.z *= g.z; reg.w *= g.w;
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+            reg[r] = src[r] ? *reinterpret_cast<const float4*>(src[r] + k0) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (gsrc[r]) {
+                const float4 g = *reinterpret_cast<const float4*>(gsrc[r] + k0);
+                reg[r].x *= g.x; reg[r].y *= g.y; reg[r].z *= g.z; reg[r].w *= g.w;
+            }
         }
     };
     auto stash = [&](int buf) {
-        float (*dst)[PW_PITCH] = is_a ? sa[buf] : sw[buf];
-        dst[lk + 0][lrow] = reg.x; dst[lk + 1][lrow] = reg.y; dst[lk + 2][lrow] = reg.z; dst[lk + 3][lrow] = reg.w;
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+            const int i = tid + r * 256, row = i >> 1, kq = (i & 1) * 4;
+            if (i >= SLOTS) continue;
+            float* dst = row < BM ? &sa[buf][kq][row] : &sw[buf][kq][row - BM];
+            const int pitch = row < BM ? PA : PB;
+            dst[0] = reg[r].x; dst[pitch] = reg[r].y; dst[2 * pitch] = reg[r].z; dst[3 * pitch] = reg[r].w;
+        }
     };
-    float acc[4][4];
+    float acc[TM][TN];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
     const int nk = K / PW_K;
     fetch(0);
     stash(0);
@@ -218,33 +244,44 @@ pointwise_kernel(const float* __restrict__ A, const float* __restrict__ W, const
         if (kb + 1 < nk) fetch((kb + 1) * PW_K);
 #pragma unroll
         for (int k = 0; k < PW_K; ++k) {
-            const float4 a = *reinterpret_cast<const float4*>(&sa[buf][k][ty * 4]);
-            const float4 w = *reinterpret_cast<const float4*>(&sw[buf][k][tx * 4]);
-            const float av[4] = {a.x, a.y, a.z, a.w}, wv[4] = {w.x, w.y, w.z, w.w};
+            float av[TM], wv[TN];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int h = 0; h < TM / 4; ++h) {       // row groups of four, BM / 2 apart when there are two
+                const float4 a = *reinterpret_cast<const float4*>(&sa[buf][k][h * (BM / 2) + ty * 4]);
+                av[4 * h] = a.x; av[4 * h + 1] = a.y; av[4 * h + 2] = a.z; av[4 * h + 3] = a.w;
+            }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+            for (int h = 0; h < TN / 4; ++h) {
+                const float4 w = *reinterpret_cast<const float4*>(&sw[buf][k][h * (BN / 2) + tx * 4]);
+                wv[4 * h] = w.x; wv[4 * h + 1] = w.y; wv[4 * h + 2] = w.z; wv[4 * h + 3] = w.w;
+            }
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
         }
         if (kb + 1 < nk) {
             stash(buf ^ 1);
             __syncthreads();
         }
     }
-    const int n = n0 + tx * 4;
-    if (n >= N) return;
-    const float4 bv = bias ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const long long m = m0 + ty * 4 + i;
-        if (m >= M) break;
-        float4 v = make_float4(activate(acc[i][0] + bv.x, act), activate(acc[i][1] + bv.y, act),
-                               activate(acc[i][2] + bv.z, act), activate(acc[i][3] + bv.w, act));
-        if (R) {
-            const float4 r = *reinterpret_cast<const float4*>(R + m * N + n);
-            v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+    for (int hj = 0; hj < TN / 4; ++hj) {
+        const int n = n0 + hj * (BN / 2) + tx * 4;
+        if (n >= N) continue;
+        const float4 bv = bias ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const long long m = m0 + (i / 4) * (BM / 2) + ty * 4 + (i & 3);
+            if (m >= M) continue;
+            float4 v = make_float4(activate(acc[i][4 * hj] + bv.x, act), activate(acc[i][4 * hj + 1] + bv.y, act),
+                                   activate(acc[i][4 * hj + 2] + bv.z, act), activate(acc[i][4 * hj + 3] + bv.w, act));
+            if (R) {
+                const float4 r = *reinterpret_cast<const float4*>(R + m * N + n);
+                v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+            }
+            *reinterpret_cast<float4*>(out + m * N + n) = v;
         }
-        *reinterpret_cast<float4*>(out + m * N + n) = v;
     }
 }
 
@@ -378,8 +415,25 @@ extern "C" int shvk_cnn_pointwise(const float* A, const float* W, const float* b
     if (K <= 0 || (K % sb::PW_K) || (N & 3) || (gate && gate_rows <= 0) || sb::misaligned(A) || sb::misaligned(W) ||
         sb::misaligned(out) || (R && sb::misaligned(R)) || (b && sb::misaligned(b)) || (gate && sb::misaligned(gate)))
         return int(cudaErrorInvalidValue);
-    const dim3 grid(sb::blocks_for(M, sb::PW_M), unsigned((N + sb::PW_N - 1) / sb::PW_N));
-    sb::pointwise_kernel<<<grid, 256, 0, cudaStream_t(stream)>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+    cudaStream_t s = cudaStream_t(stream);
+    // tile width: wide layers take 128 columns; narrow ones the width in {16, 32, 64} that pads N least (ties: wider)
+    int bn = 128;
+    if (N < 112) {
+        int best = 1 << 30;
+        for (int c : {64, 32, 16}) {
+            const int padded = (N + c - 1) / c * c;
+            if (padded < best) { best = padded; bn = c; }
+        }
+    }
+    const unsigned gy = unsigned((N + bn - 1) / bn);
+    if (bn == 128)
+        sb::pointwise_kernel<128, 128, 8, 8><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+    else if (bn == 64)
+        sb::pointwise_kernel<64, 64, 4, 4><<<dim3(sb::blocks_for(M, 64), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+    else if (bn == 32)
+        sb::pointwise_kernel<128, 32, 4, 4><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+    else
+        sb::pointwise_kernel<256, 16, 4, 4><<<dim3(sb::blocks_for(M, 256), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
     return int(cudaGetLastError());
 }
 
