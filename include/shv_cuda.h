@@ -7,14 +7,12 @@
  * (the AV service, gpu_bench, gpu_cli) links against this library unchanged.  Each declaration cites the reference
  * line it replaces.
  *
- * What this library computes: the sequence stages of SHIELD-V -- 20 frames x 16 tokens x 384 (frame embeddings
- * before position embeddings) + readout token -> GDN-A -> GDN-B x2 -> SISA (readout row) -> RMSNorm -> head ->
- * one logit per window.  score = sigmoid(logit) in double on the caller's side; alert iff score >= threshold.
- * A NaN logit means "unavailable" (failed job or non-finite result), never a score.
- *
- * What it does not compute: the MobileNetV3 frame encoder.  Requests that carry frames (n_frames > 0),
- * shv_cuda_encode_frames and shv_cuda_predict fail with an explanatory error; windows take their tokens from host
- * pointers (window_tokens) or from device token slots that a frame-encoding engine sharing the device would fill.
+ * What this library computes: the frame encoder -- 320x180 RGB crop -> MobileNetV3-Large features -> 4x4 pooling ->
+ * 16 tokens x 384 (float32 in every mode) -- and the sequence stages of SHIELD-V -- 20 frames x 16 tokens x 384
+ * (frame embeddings before position embeddings) + readout token -> GDN-A -> GDN-B x2 -> SISA (readout row) ->
+ * RMSNorm -> head -> one logit per window.  score = sigmoid(logit) in double on the caller's side; alert iff
+ * score >= threshold.  A NaN logit means "unavailable" (failed job or non-finite result), never a score.
+ * Windows take their 16x384 blocks from frames of the same request, from device token slots, or from host pointers.
  *
  * MODES  "fp32": IEEE fp32 everywhere (exact tier, always loadable).  "bf16" / "fp16": 16-bit operands for the
  * all-row projections on the tensor cores, fp32 accumulation; norms, the delta-rule recurrence, the residual stream
@@ -83,8 +81,8 @@ size_t shv_cuda_weight_bytes(const shv_cuda_model* m);                          
 size_t shv_cuda_device_bytes(const shv_cuda_model* m);                                    /* shv_cuda.h:105 */
 
 /* Synchronous calls, split into GPU batches internally (shv_cuda.h:107-113).
- * tokens: b x 20 x 16 x 384 fp32; logits: b fp32; NaN logits and -1 on failure.
- * encode_frames and predict need the frame encoder and always fail in this library. */
+ * rgb: n crops [180][320][3] uint8; tokens: n x 16 x 384 (encode_frames) or b x 20 x 16 x 384 (classify) fp32;
+ * clips: b x 20 crops; logits: b fp32.  NaN outputs and -1 on failure. */
 int shv_cuda_encode_frames(shv_cuda_model* m, const uint8_t* rgb, size_t n, float* tokens);
 int shv_cuda_classify(shv_cuda_model* m, const float* tokens, size_t b, float* logits);
 int shv_cuda_predict(shv_cuda_model* m, const uint8_t* clips, size_t b, float* logits);

@@ -1,9 +1,9 @@
 /*
  * shv_cuda_b200.h -- entry points of libshield_v_cuda.so that the reference library does not have.
  *
- * The reference engine fills its device token slots from frames it encodes itself (store_slots of a request,
- * engine/include/shv_cuda.h:122,54-59).  This library has no frame encoder, so a caller that keeps per-participant
- * token rings on the device needs another way in.
+ * The reference engine fills its device token slots only from frames it encodes itself (store_slots of a request,
+ * engine/include/shv_cuda.h:122,54-59).  A caller that encodes frames elsewhere and keeps per-participant token
+ * rings on the device needs another way in: shv_cuda_b200_upload_tokens.
  */
 #ifndef SHV_CUDA_B200_H
 #define SHV_CUDA_B200_H

@@ -11,7 +11,8 @@
 //
 // encode (F frames, reference run_encode engine/cuda/engine.cu:338-403): stem -> 15 inverted-residual blocks
 //   (expand 1x1 | depthwise | squeeze-excite gate | project 1x1 with the gate applied to its input rows, + residual)
-//   -> 1x1 160 -> 960 -> 4x4 pooling -> 960 -> 384 token projection into slot.d_tokens.  float32 NHWC in every mode.
+//   -> 1x1 160 -> 960 -> 4x4 pooling -> 960 -> 384 token projection into slot.d_tokens.  float32 NHWC storage in every
+//   mode; the 1x1 convolutions multiply in TF32 on the tensor cores in the 16-bit modes.
 //
 // Storage policy (engine/cuda/engine.cu:150-164,213-219): h, P/S and the readout-row buffers are fp32 always; xn, on,
 // hid and the all-row weights are the storage type of the mode.  fp32 mode runs the all-row GEMMs on CUDA cores
@@ -447,6 +448,8 @@ private:
     // ---------------------------------------------------------------- frame encoder
     void run_encode(int slot, int F, cudaStream_t s) {
         const Slot& sl = slots_[size_t(slot)];
+        // 1x1 convolutions: exact fma chains in fp32 mode, TF32 tensor-core products in the 16-bit modes
+        const auto pointwise = prec_ == Precision::FP32 ? shvk_cnn_pointwise : shvk_cnn_pointwise_tf32;
         launch_ok(shvk_cnn_stem(sl.d_frames, lut_, stem_w_, stem_b_, cx_, F, s), "stem");
         mark("cnn.stem", s);
         dump("cnn_stem_f0", cx_, size_t(16) * 90 * 160, SHVK_F32, s);
@@ -456,7 +459,7 @@ private:
             const int hw_in = b.h_in * b.w_in, hw_out = b.h_out * b.w_out;
             const float* dw_in = cx_;
             if (b.has_expand) {
-                launch_ok(shvk_cnn_pointwise(cx_, d.exp_w, d.exp_b, nullptr, 1, nullptr, ce_, F * hw_in, b.exp, b.in, b.act, s),
+                launch_ok(pointwise(cx_, d.exp_w, d.exp_b, nullptr, 1, nullptr, ce_, F * hw_in, b.exp, b.in, b.act, s),
                           "expand");
                 mark("cnn.expand", s);
                 dw_in = ce_;
@@ -471,7 +474,7 @@ private:
                 mark("cnn.se_gate", s);
                 gate = se_gate_;
             }
-            launch_ok(shvk_cnn_pointwise(cd_, d.proj_w, d.proj_b, gate, hw_out, b.residual ? cx_ : nullptr, cx_, F * hw_out, b.out,
+            launch_ok(pointwise(cd_, d.proj_w, d.proj_b, gate, hw_out, b.residual ? cx_ : nullptr, cx_, F * hw_out, b.out,
                                          b.exp, SHVK_ACT_NONE, s), "project");
             mark("cnn.project", s);
             if (!dump_dir_.empty()) {
@@ -480,7 +483,7 @@ private:
                 dump(name, cx_, size_t(b.out) * hw_out, SHVK_F32, s);
             }
         }
-        launch_ok(shvk_cnn_pointwise(cx_, last_w_, last_b_, nullptr, 1, nullptr, ce_, F * 60, CNN_OUT, 160, SHVK_ACT_HSWISH, s),
+        launch_ok(pointwise(cx_, last_w_, last_b_, nullptr, 1, nullptr, ce_, F * 60, CNN_OUT, 160, SHVK_ACT_HSWISH, s),
                   "last conv");
         mark("cnn.last", s);
         dump("cnn_map_f0", ce_, size_t(60) * CNN_OUT, SHVK_F32, s);

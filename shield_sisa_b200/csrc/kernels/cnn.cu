@@ -76,41 +76,58 @@ stem_kernel(const uint8_t* __restrict__ frames, const float* __restrict__ lut, c
 }
 
 // ---------------------------------------------------------------------------------------------------- depthwise
-// One thread per (output pixel, channel quad); taps visited row by row, out-of-image taps skipped.
+// One thread per (four adjacent output pixels of a row, channel quad): per filter row the input columns the four
+// outputs share are loaded once ((4 - 1) * stride + K float4 loads for 4 * K taps), taps are visited row by row in the
+// same order for every output, and positions outside the image contribute a zero.
+constexpr int DW_PX = 4;
 template <int KS, int S>
 __global__ void __launch_bounds__(256)
 depthwise_kernel(const float* __restrict__ in, const float* __restrict__ w, const float* __restrict__ b,
                  float* __restrict__ out, long long total, int H, int W, int C, int Ho, int Wo, int act) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    const int C4 = C >> 2;
+    const int C4 = C >> 2, GX = (Wo + DW_PX - 1) / DW_PX;
     const int c = int(i % C4) * 4;
-    const long long pix = i / C4;
-    const int ox = int(pix % Wo), oy = int((pix / Wo) % Ho);
-    const long long f = pix / ((long long)Wo * Ho);
-    constexpr int PAD = (KS - 1) / 2;
-    const float* img = in + f * (long long)H * W * C;
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const long long grp = i / C4;
+    const int ox0 = int(grp % GX) * DW_PX, oy = int((grp / GX) % Ho);
+    const long long f = grp / ((long long)GX * Ho);
+    constexpr int PAD = (KS - 1) / 2, NIN = (DW_PX - 1) * S + KS;
+    const float* img = in + f * (long long)H * W * C + c;
+    float4 acc[DW_PX];
+#pragma unroll
+    for (int p = 0; p < DW_PX; ++p) acc[p] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
     for (int ky = 0; ky < KS; ++ky) {
         const int iy = oy * S - PAD + ky;
         if (iy < 0 || iy >= H) continue;
+        const float* row = img + (long long)iy * W * C;
+        float4 x[NIN];
+#pragma unroll
+        for (int j = 0; j < NIN; ++j) {
+            const int ix = ox0 * S - PAD + j;
+            x[j] = (ix >= 0 && ix < W) ? *reinterpret_cast<const float4*>(row + (long long)ix * C) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
 #pragma unroll
         for (int kx = 0; kx < KS; ++kx) {
-            const int ix = ox * S - PAD + kx;
-            if (ix < 0 || ix >= W) continue;
-            const float4 x = *reinterpret_cast<const float4*>(img + ((long long)iy * W + ix) * C + c);
             const float4 k = __ldg(reinterpret_cast<const float4*>(w + (ky * KS + kx) * C + c));
-            acc.x = fmaf(k.x, x.x, acc.x);
-            acc.y = fmaf(k.y, x.y, acc.y);
-            acc.z = fmaf(k.z, x.z, acc.z);
-            acc.w = fmaf(k.w, x.w, acc.w);
+#pragma unroll
+            for (int p = 0; p < DW_PX; ++p) {
+                const float4 v = x[p * S + kx];
+                acc[p].x = fmaf(k.x, v.x, acc[p].x);
+                acc[p].y = fmaf(k.y, v.y, acc[p].y);
+                acc[p].z = fmaf(k.z, v.z, acc[p].z);
+                acc[p].w = fmaf(k.w, v.w, acc[p].w);
+            }
         }
     }
     const float4 bias = __ldg(reinterpret_cast<const float4*>(b + c));
-    *reinterpret_cast<float4*>(out + pix * C + c) =
-        make_float4(activate(acc.x + bias.x, act), activate(acc.y + bias.y, act), activate(acc.z + bias.z, act),
-                    activate(acc.w + bias.w, act));
+    float* o = out + ((f * Ho + oy) * (long long)Wo + ox0) * C + c;
+#pragma unroll
+    for (int p = 0; p < DW_PX; ++p)
+        if (ox0 + p < Wo)
+            *reinterpret_cast<float4*>(o + (long long)p * C) =
+                make_float4(activate(acc[p].x + bias.x, act), activate(acc[p].y + bias.y, act), activate(acc[p].z + bias.z, act),
+                            activate(acc[p].w + bias.w, act));
 }
 
 // ---------------------------------------------------------------------------------------------------- squeeze-excite
@@ -285,6 +302,127 @@ pointwise_kernel(const float* __restrict__ A, const float* __restrict__ W, const
     }
 }
 
+// ---------------------------------------------------------------------------------------------------- 1x1 convolution, TF32
+// The same row GEMM on the tensor cores for the 16-bit modes: operands rounded to TF32 (10-bit mantissa, float32
+// range) on their way into shared memory, mma.sync m16n8k8 with float32 accumulation, float32 in and out.  These layers
+// have K = 16 .. 160 in all but five cases and move 30 of the encoder's 46 MB per frame: they are bound by HBM, not by
+// the tensor pipe, which is why this is a register-fed mma kernel and not a TMA / tcgen05 pipeline (whose 64-wide K
+// tiles most of these layers would not fill).  256 threads = WM x WN warps, k in slabs of 16 (zero-filled past K),
+// tiles row-major with a 20-float pitch: fragment reads and the 16-byte stores are conflict-free.
+constexpr int PT_K = 16, PT_PITCH = 20;
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <int BM, int BN, int WM, int WN>
+__global__ void __launch_bounds__(256, (BM / WM / 16) * (BN / WN / 8) > 8 ? 2 : 4)
+pointwise_tf32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
+                      const float* __restrict__ gate, int gate_rows, const float* R, float* out, int M, int N, int K, int act) {
+    static_assert(WM * WN == 8, "eight warps");
+    constexpr int MT = BM / WM / 16, NT = BN / WN / 8, ROWS = BM + BN, SLOTS = ROWS * 4, PER = (SLOTS + 255) / 256;
+    __shared__ __align__(16) float tile[2][ROWS][PT_PITCH];      // rows 0 .. BM-1: pixels, then BN rows of W
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int wm = warp % WM, wn = warp / WM;
+    const long long m0 = (long long)blockIdx.x * BM;
+    const int n0 = blockIdx.y * BN;
+    // loader slots: slot i covers tile row i / 4, k quad i % 4
+    const int kq = (tid & 3) * 4;
+    float4 reg[PER];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+            const int row = (tid >> 2) + r * 64;
+            reg[r] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (k0 + kq >= K) continue;
+            if (row < BM) {
+                const long long m = m0 + row;
+                if (m < M) {
+                    reg[r] = *reinterpret_cast<const float4*>(A + m * K + k0 + kq);
+                    if (gate) {
+                        const float4 gv = *reinterpret_cast<const float4*>(gate + (m / gate_rows) * K + k0 + kq);
+                        reg[r].x *= gv.x; reg[r].y *= gv.y; reg[r].z *= gv.z; reg[r].w *= gv.w;
+                    }
+                }
+            } else if (row < ROWS && n0 + row - BM < N) {
+                reg[r] = __ldg(reinterpret_cast<const float4*>(W + (long long)(n0 + row - BM) * K + k0 + kq));
+            }
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+            const int row = (tid >> 2) + r * 64;
+            if (row >= ROWS) continue;
+            *reinterpret_cast<float4*>(&tile[buf][row][kq]) =
+                make_float4(to_tf32(reg[r].x), to_tf32(reg[r].y), to_tf32(reg[r].z), to_tf32(reg[r].w));
+        }
+    };
+    float acc[MT][NT][4];
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < NT; ++ni)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mi][ni][e] = 0.0f;
+    const int nk = (K + PT_K - 1) / PT_K;
+    const int rb = wm * (BM / WM), nb = BM + wn * (BN / WN);
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    for (int kb = 0; kb < nk; ++kb) {
+        const int buf = kb & 1;
+        if (kb + 1 < nk) fetch((kb + 1) * PT_K);
+#pragma unroll
+        for (int ks = 0; ks < PT_K / 8; ++ks) {
+            uint32_t a[MT][4];
+#pragma unroll
+            for (int mi = 0; mi < MT; ++mi) {
+                const float* r0 = &tile[buf][rb + mi * 16 + g][ks * 8 + t];
+                a[mi][0] = __float_as_uint(r0[0]);
+                a[mi][1] = __float_as_uint(r0[8 * PT_PITCH]);
+                a[mi][2] = __float_as_uint(r0[4]);
+                a[mi][3] = __float_as_uint(r0[8 * PT_PITCH + 4]);
+            }
+#pragma unroll
+            for (int ni = 0; ni < NT; ++ni) {
+                const float* w0 = &tile[buf][nb + ni * 8 + g][ks * 8 + t];
+                const uint32_t b0 = __float_as_uint(w0[0]), b1 = __float_as_uint(w0[4]);
+#pragma unroll
+                for (int mi = 0; mi < MT; ++mi) mma_tf32(acc[mi][ni], a[mi], b0, b1);
+            }
+        }
+        if (kb + 1 < nk) {
+            stash(buf ^ 1);
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int ni = 0; ni < NT; ++ni) {
+        const int n = n0 + wn * (BN / WN) + ni * 8 + 2 * t;
+        if (n >= N) continue;
+        const float2 bv = bias ? __ldg(reinterpret_cast<const float2*>(bias + n)) : make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const long long m = m0 + rb + mi * 16 + g + h * 8;
+                if (m >= M) continue;
+                float2 v = make_float2(activate(acc[mi][ni][2 * h] + bv.x, act), activate(acc[mi][ni][2 * h + 1] + bv.y, act));
+                if (R) {
+                    const float2 r = *reinterpret_cast<const float2*>(R + m * N + n);
+                    v.x += r.x; v.y += r.y;
+                }
+                *reinterpret_cast<float2*>(out + m * N + n) = v;
+            }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------- 4x4 pooling
 __global__ void __launch_bounds__(256)
 pool_tokens_kernel(const float* __restrict__ in, float* __restrict__ out, long long total) {
@@ -328,7 +466,7 @@ extern "C" int shvk_cnn_depthwise(const float* in, const float* w, const float* 
         Ho != (H + 2 * pad - K) / stride + 1 || Wo != (W + 2 * pad - K) / stride + 1 || sb::misaligned(in) ||
         sb::misaligned(out) || sb::misaligned(w) || sb::misaligned(b))
         return int(cudaErrorInvalidValue);
-    const long long total = (long long)F * Ho * Wo * (C / 4);
+    const long long total = (long long)F * Ho * ((Wo + sb::DW_PX - 1) / sb::DW_PX) * (C / 4);
     const unsigned grid = sb::blocks_for(total, 256);
     cudaStream_t s = cudaStream_t(stream);
     if (K == 3 && stride == 1) sb::depthwise_kernel<3, 1><<<grid, 256, 0, s>>>(in, w, b, out, total, H, W, C, Ho, Wo, act);
@@ -409,22 +547,32 @@ extern "C" int shvk_cnn_se_gate_static(const float* x, const float* w1, const fl
     return shvk_cnn_se_gate(x, scratch, w1, b1, w2, b2, gate, F, HW, C, CS, stream);
 }
 
+namespace sb {
+namespace {
+bool pointwise_args_bad(const float* A, const float* W, const float* b, const float* gate, int gate_rows, const float* R,
+                        const float* out, int N, int K) {
+    return K <= 0 || (K % PW_K) || (N & 3) || (gate && gate_rows <= 0) || misaligned(A) || misaligned(W) || misaligned(out) ||
+           (R && misaligned(R)) || (b && misaligned(b)) || (gate && misaligned(gate));
+}
+// tile width: wide layers take 128 columns; narrow ones the width in {16, 32, 64} that pads N least (ties: wider)
+int pointwise_tile_width(int N) {
+    if (N >= 112) return 128;
+    int bn = 64, best = 1 << 30;
+    for (int c : {64, 32, 16}) {
+        const int padded = (N + c - 1) / c * c;
+        if (padded < best) { best = padded; bn = c; }
+    }
+    return bn;
+}
+}  // namespace
+}  // namespace sb
+
 extern "C" int shvk_cnn_pointwise(const float* A, const float* W, const float* b, const float* gate, int gate_rows,
                                   const float* R, float* out, int M, int N, int K, int act, void* stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K % sb::PW_K) || (N & 3) || (gate && gate_rows <= 0) || sb::misaligned(A) || sb::misaligned(W) ||
-        sb::misaligned(out) || (R && sb::misaligned(R)) || (b && sb::misaligned(b)) || (gate && sb::misaligned(gate)))
-        return int(cudaErrorInvalidValue);
+    if (sb::pointwise_args_bad(A, W, b, gate, gate_rows, R, out, N, K)) return int(cudaErrorInvalidValue);
     cudaStream_t s = cudaStream_t(stream);
-    // tile width: wide layers take 128 columns; narrow ones the width in {16, 32, 64} that pads N least (ties: wider)
-    int bn = 128;
-    if (N < 112) {
-        int best = 1 << 30;
-        for (int c : {64, 32, 16}) {
-            const int padded = (N + c - 1) / c * c;
-            if (padded < best) { best = padded; bn = c; }
-        }
-    }
+    const int bn = sb::pointwise_tile_width(N);
     const unsigned gy = unsigned((N + bn - 1) / bn);
     if (bn == 128)
         sb::pointwise_kernel<128, 128, 8, 8><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
@@ -434,6 +582,24 @@ extern "C" int shvk_cnn_pointwise(const float* A, const float* W, const float* b
         sb::pointwise_kernel<128, 32, 4, 4><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
     else
         sb::pointwise_kernel<256, 16, 4, 4><<<dim3(sb::blocks_for(M, 256), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+    return int(cudaGetLastError());
+}
+
+extern "C" int shvk_cnn_pointwise_tf32(const float* A, const float* W, const float* b, const float* gate, int gate_rows,
+                                       const float* R, float* out, int M, int N, int K, int act, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (sb::pointwise_args_bad(A, W, b, gate, gate_rows, R, out, N, K)) return int(cudaErrorInvalidValue);
+    cudaStream_t s = cudaStream_t(stream);
+    const int bn = sb::pointwise_tile_width(N);
+    const unsigned gy = unsigned((N + bn - 1) / bn);
+    if (bn == 128)
+        sb::pointwise_tf32_kernel<128, 128, 4, 2><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+    else if (bn == 64)
+        sb::pointwise_tf32_kernel<64, 64, 4, 2><<<dim3(sb::blocks_for(M, 64), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+    else if (bn == 32)
+        sb::pointwise_tf32_kernel<128, 32, 8, 1><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+    else
+        sb::pointwise_tf32_kernel<256, 16, 8, 1><<<dim3(sb::blocks_for(M, 256), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
     return int(cudaGetLastError());
 }
 

@@ -1,13 +1,14 @@
 """GPU parity of the frame encoder: kernels one by one against numpy, and Engine::encode through the C ABI against the
 float64 oracle, the golden tokens of the reference's PyTorch oracle and the reference's CPU engine.
 
-Tolerance (fp32 arithmetic in every mode): max abs error <= 1e-4 on tokens of O(1) magnitude (recipe W5)."""
+Tolerance: fp32 mode max abs error <= 1e-4 on tokens of O(1) magnitude (recipe W5); bf16 / fp16 modes (TF32 products in
+the 1x1 convolutions, everything else float32) max |err| / max |ref| <= 2e-2."""
 import ctypes as C
 
 import numpy as np
 import pytest
 
-from tests.helpers import dev, load_golden, stream_ptr, sync
+from tests.helpers import dev, load_golden, rel_err, stream_ptr, sync
 
 pytestmark = pytest.mark.gpu
 
@@ -132,6 +133,39 @@ def test_pointwise_kernel(L, M, N, K, act, gated, resid):
     assert np.abs(out.cpu().numpy() - ref).max() < 2e-5
 
 
+@pytest.mark.parametrize("M,N,K,act,gated,resid", [(14400, 64, 16, 1, False, False), (1000, 24, 72, 0, False, True),
+                                                  (120, 160, 960, 0, True, True), (60, 960, 160, 2, False, False),
+                                                  (77, 40, 120, 0, True, False), (333, 80, 184, 0, False, True),
+                                                  (4000, 16, 16, 0, False, True)])
+def test_pointwise_tf32_kernel(L, M, N, K, act, gated, resid):
+    """Tensor-core form of the 1x1 convolution: operands rounded to TF32 (2^-11 relative), float32 accumulation."""
+    import torch
+    rng = np.random.default_rng(M + N + 1)
+    rows = 60 if gated and M % 60 == 0 else (11 if gated else 1)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    Wt = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    gate = rng.uniform(0, 1, size=((M + rows - 1) // rows, K)).astype(np.float32) if gated else None
+    R = rng.standard_normal((M, N)).astype(np.float32) if resid else None
+    out = dev(R) if resid else torch.empty((M, N), dtype=torch.float32, device="cuda")
+    g_dev = dev(gate) if gated else None
+    d_a, d_w, d_b = dev(A), dev(Wt), dev(b)
+    rc = L.shvk_cnn_pointwise_tf32(_ptr(d_a), _ptr(d_w), _ptr(d_b), _ptr(g_dev) if gated else None, rows,
+                                   _ptr(out) if resid else None, _ptr(out), M, N, K, act, stream_ptr())
+    assert rc == 0
+    sync()
+    a64 = A.astype(np.float64)
+    if gated:
+        a64 = a64 * np.repeat(gate.astype(np.float64), rows, axis=0)[:M]
+    ref = a64 @ Wt.T.astype(np.float64) + b
+    ref = np.maximum(ref, 0) if act == 1 else _hardswish(ref) if act == 2 else ref
+    if resid:
+        ref = ref + R
+    got = out.cpu().numpy()
+    assert np.abs(got - ref).max() < 4e-3                      # |a| |w| sqrt(K) 2^-11 with a ~ N(0,1), w ~ N(0,1/K): about 5e-4
+    assert np.abs(got - ref).max() > 0                         # not the exact kernel
+
+
 def test_pool_tokens_kernel(L):
     import torch
     from oracle import cnn_oracle as CO
@@ -182,7 +216,7 @@ def _wrap_f32(ptr, n):
 
 
 @pytest.mark.parametrize("case", ["encoder_w5_s3_f11", "encoder_w1_s1_f5"])
-@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+@pytest.mark.parametrize("mode", ["fp32", "bf16", "fp16"])
 def test_encode_matches_reference(case, mode, weight_files):
     from oracle import cnn_oracle as CO, ref_cpu
     from shield_sisa_b200 import binding, weights as W
@@ -192,14 +226,19 @@ def test_encode_matches_reference(case, mode, weight_files):
     eng = binding.EngineCore(path, mode, max_windows=1, max_frames=4, use_graphs=False)
     tok = _encode(eng, frames)
     assert eng.status() == 0
-    assert np.abs(tok - g["tokens_f64"]).max() <= TOL                      # reference's PyTorch oracle, float64
-    assert np.abs(tok - CO.encode_frames(w, frames, np.float64)).max() <= TOL
+    # fp32 mode: max abs error <= 1e-4.  16-bit modes (TF32 products in the 1x1 convolutions): max |err| / max |ref| <= 2e-2
+    def err(ref):
+        return np.abs(tok - ref).max() if mode == "fp32" else rel_err(tok, ref)
+    tol = TOL if mode == "fp32" else 2e-2
+    assert err(g["tokens_f64"]) <= tol                                     # reference's PyTorch oracle, float64
+    assert err(CO.encode_frames(w, frames, np.float64)) <= tol
     if "tokens_cpu_engine" in g:
-        assert np.abs(tok - g["tokens_cpu_engine"]).max() <= TOL           # reference's CPU engine (stored)
+        assert err(g["tokens_cpu_engine"]) <= tol                          # reference's CPU engine (stored)
     if ref_cpu.available():
         cpu = ref_cpu.RefCpuEngine(path, threads=2)
-        assert np.abs(tok - cpu.encode_frames(frames)).max() <= TOL        # reference's CPU engine (run here)
+        assert err(cpu.encode_frames(frames)) <= tol                       # reference's CPU engine (run here)
         cpu.close()
+    print(f"encoder {case} {mode}: err vs float64 oracle {err(g['tokens_f64']):.3e}")
     eng.close()
 
 
