@@ -1,6 +1,7 @@
 """Benchmark of the SHIELD-V sequence stack (GDN-A, GDN-B x2, SISA, head) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--mode bf16|fp16|fp32] [--batch B] [--impl reference]
+    python bench.py --workload live [--participants P] [--steps HOPS] [--mode fp16]     (streaming hops, see run_live)
 
 One "step" = one pass of the whole sequence stack over B clips (20 frames x 16 tokens x 384 + readout = 321 rows per
 clip) per GPU.  Default workload: B = 4096 clips per GPU, bf16 mode, synthetic N(0,1) frame embeddings and seeded
@@ -195,6 +196,74 @@ def encoder_leg(binding, torch, wpath, mode, local_rank, frames=512, steps=10, w
                    "crops resident in HBM; not part of `value`"}
     eng.close()
     return out
+
+
+def run_live(args, local_rank: int):
+    """Streaming load (BASELINE config 5 on one GPU): `--participants` rings of 24 device token slots; every hop each
+    participant sends 4 new uint8 crops and scores the window of its last 20 frames (one request per participant:
+    frames + store_slots + window_slots), fp16 mode by default.  Prints windows/s and frames/s over `--steps` hops after
+    the 20-frame first hop; crops start in pinned host memory, logits end in host memory."""
+    import torch
+
+    from shield_sisa_b200 import binding, live
+
+    torch.cuda.set_device(local_rank)
+    P, new = args.participants, 4
+    wpath = make_weights("live")
+    cap = min(4096, max(20, P * 20))
+    model = binding.CudaModel(wpath, args.mode, device=local_rank, experimental=True, max_frames=min(4096, cap),
+                              max_windows=min(4096, P), max_host_tokens=20, token_slots=live.RING * P)
+    rng = np.random.default_rng(4)
+    distinct = 64                                               # distinct crops, reused across participants and hops
+    pool = binding.PinnedBuffer(model.L, (distinct, 180, 320, 3), np.uint8)
+    pool.array[...] = rng.integers(0, 256, size=pool.array.shape, dtype=np.uint8)
+    drv = live.LiveDriver(model, P)
+
+    def crops_for(n):
+        # every participant reads a contiguous run of the pinned pool: DMA'd without staging
+        idx = (np.arange(P)[:, None] * 7 + np.arange(n)[None, :]) % (distinct - n)
+        return [pool.array[i[0]:i[0] + n] for i in idx]
+
+    def hop(n):
+        logits = np.full(P, np.nan, np.float32)
+        jobs, keep = [], []
+        for p, c in enumerate(crops_for(n)):
+            store, window = live.hop_slots(p, int(drv.frames_sent[p]), n)
+            j, k = model.submit(1, logits[p:p + 1], window_slots=window, frames=c, n_frames=n, store_slots=store)
+            if not j:
+                raise SystemExit(binding.last_error(model.L))
+            jobs.append(j)
+            keep.append(k)
+            drv.frames_sent[p] += n
+        sizes = []
+        for j in jobs:
+            if model.job_wait(j) != 0:
+                raise SystemExit(model.job_error(j))
+            sizes.append(model.job_timing(j)[1]["batch_windows"])
+            model.job_free(j)
+        if not np.isfinite(logits).all():
+            raise SystemExit("live run returned non-finite logits")
+        return sizes
+
+    hop(20)
+    for _ in range(max(1, args.warmup)):
+        hop(new)
+    t0 = time.perf_counter()
+    sizes = []
+    for _ in range(args.steps):
+        sizes += hop(new)
+    dt = time.perf_counter() - t0
+    line = {"metric": "windows_per_s_live_hops", "value": P * args.steps / dt, "unit": "windows/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(1, args.warmup), "ms_per_step": 1000.0 * dt / args.steps,
+            "higher_is_better": True, "dtype": {"fp32": "f32", "bf16": "bf16", "fp16": "f16"}[args.mode], "data": "synthetic",
+            "frames_per_s": P * new * args.steps / dt, "mean_batch_windows": float(np.mean(sizes)),
+            "config": {"workload": f"live hops: {P} participants x (4 new 320x180 uint8 crops + 1 window of 20 ring slots) per "
+                                   f"hop, one request per participant through shv_cuda_submit, {args.mode} mode",
+                       "device_bytes": model.device_bytes()},
+            "h2d_bytes_per_step": P * new * 172800, "d2h_bytes_per_step": P * 4}
+    model.close()
+    pool.free()
+    emit(line)
 
 
 def make_weights(tag: str):
@@ -483,6 +552,9 @@ def main():
     ap.add_argument("--batch", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-encoder", action="store_true", help="skip the frame-encoder leg")
+    ap.add_argument("--workload", default="stack", choices=["stack", "live"],
+                    help="stack: the headline metric (default); live: streaming hops with frames and device token rings")
+    ap.add_argument("--participants", type=int, default=4096, help="participants of the live workload")
     ap.add_argument("--e2e-threads", type=int, default=2,
                     help="host threads of the end-to-end leg, each calling shv_cuda_classify on its share of the batch")
     ap.add_argument("--e2e-windows", type=int, default=1024,
@@ -494,6 +566,11 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "live":
+        if world > 1:
+            raise SystemExit("the live workload runs on one GPU per process; start one process per GPU")
+        run_live(args, local_rank)
         return
     if world != args.gpus:
         if args.gpus > 1:
