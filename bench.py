@@ -2,6 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--mode bf16|fp16|fp32] [--batch B] [--impl reference]
     python bench.py --workload live [--participants P] [--steps HOPS] [--mode fp16]     (streaming hops, see run_live)
+    python bench.py --workload encoder [--frames F] [--mode bf16]                       (frame encoder alone)
 
 One "step" = one pass of the whole sequence stack over B clips (20 frames x 16 tokens x 384 + readout = 321 rows per
 clip) per GPU.  Default workload: B = 4096 clips per GPU, bf16 mode, synthetic N(0,1) frame embeddings and seeded
@@ -190,10 +191,10 @@ def encoder_leg(binding, torch, wpath, mode, local_rank, frames=512, steps=10, w
     nbytes, flops = encoder_work()
     pk, pk_src = peaks()
     out = {"frames_per_s": frames / (ms / 1000.0), "frames": frames, "ms_per_encode": ms, "launches": eng.encode_launches(),
-           "dtype": "f32", "ms_by_kernel": kinds, "algorithmic_bytes_per_frame": nbytes, "flops_per_frame": flops,
+           "dtype": "f32 storage; 1x1 convolutions fp32 fma (fp32 mode) or TF32 mma (16-bit modes)", "ms_by_kernel": kinds, "algorithmic_bytes_per_frame": nbytes, "flops_per_frame": flops,
            "hbm_frac": frames * nbytes / (ms / 1000.0) / (pk["hbm_gbs"] * 1e9), "peak_source": pk_src,
-           "note": "frame encoder (MobileNetV3-Large, 320x180 crops -> 16 x 384 tokens), float32 NHWC in every mode; "
-                   "crops resident in HBM; not part of `value`"}
+           "note": "frame encoder (MobileNetV3-Large, 320x180 crops -> 16 x 384 tokens), float32 NHWC storage in every "
+                   "mode; crops resident in HBM; not part of `value`"}
     eng.close()
     return out
 
@@ -552,8 +553,10 @@ def main():
     ap.add_argument("--batch", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-encoder", action="store_true", help="skip the frame-encoder leg")
-    ap.add_argument("--workload", default="stack", choices=["stack", "live"],
-                    help="stack: the headline metric (default); live: streaming hops with frames and device token rings")
+    ap.add_argument("--workload", default="stack", choices=["stack", "live", "encoder"],
+                    help="stack: the headline metric (default); live: streaming hops with frames and device token rings; "
+                         "encoder: the frame-encoder leg alone on --frames crops (small cases for profiling)")
+    ap.add_argument("--frames", type=int, default=512, help="crops per encode of the encoder workload")
     ap.add_argument("--participants", type=int, default=4096, help="participants of the live workload")
     ap.add_argument("--e2e-threads", type=int, default=2,
                     help="host threads of the end-to-end leg, each calling shv_cuda_classify on its share of the batch")
@@ -566,6 +569,18 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "encoder":
+        import torch
+
+        from shield_sisa_b200 import binding
+        torch.cuda.set_device(local_rank)
+        enc = encoder_leg(binding, torch, make_weights("enc"), args.mode, local_rank, frames=args.frames, steps=args.steps,
+                          warmup=args.warmup)
+        emit({"metric": "frames_per_s_encoder", "value": enc["frames_per_s"], "unit": "frames/s", "n_gpus": 1,
+              "steps": args.steps, "warmup": args.warmup, "ms_per_step": enc["ms_per_encode"], "higher_is_better": True,
+              "dtype": "f32" if args.mode == "fp32" else "tf32", "data": "synthetic",
+              "config": {"workload": f"frame encoder, {args.frames} crops per encode, {args.mode} mode"}, "encoder": enc})
         return
     if args.workload == "live":
         if world > 1:
