@@ -201,14 +201,14 @@ constexpr int PW_K = 8;
 template <int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__(256)
 pointwise_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
-                 const float* __restrict__ gate, int gate_rows, const float* R, float* out, int M, int N, int K, int act) {
+                 const float* __restrict__ gate, int gate_rows, const float* R, float* out, int M, int N, int K, int act, int col_tiles) {
     static_assert((BM / TM) * (BN / TN) == 256, "256 threads");
     constexpr int NX = BN / TN, PA = BM + 4, PB = BN + 4, SLOTS = (BM + BN) * 2, PER = (SLOTS + 255) / 256;
     __shared__ __align__(16) float sa[2][PW_K][PA];
     __shared__ __align__(16) float sw[2][PW_K][PB];
     const int tid = threadIdx.x, tx = tid % NX, ty = tid / NX;
-    const long long m0 = (long long)blockIdx.x * BM;
-    const int n0 = blockIdx.y * BN;
+    const long long m0 = (long long)(blockIdx.x / col_tiles) * BM;   // column tiles of a row tile are neighbours
+    const int n0 = int(blockIdx.x % col_tiles) * BN;
     // loader slots: slot i covers row i / 2 (A rows first, then W rows), k quad i % 2
     const float* src[PER];
     const float* gsrc[PER];
@@ -324,16 +324,16 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 template <int BM, int BN, int WM, int WN>
-__global__ void __launch_bounds__(256, (BM / WM / 16) * (BN / WN / 8) > 8 ? 2 : 4)
+__global__ void __launch_bounds__(256, (BM / WM / 16) * (BN / WN / 8) > 10 ? 2 : (BM / WM / 16) * (BN / WN / 8) > 5 ? 3 : 4)
 pointwise_tf32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
-                      const float* __restrict__ gate, int gate_rows, const float* R, float* out, int M, int N, int K, int act) {
+                      const float* __restrict__ gate, int gate_rows, const float* R, float* out, int M, int N, int K, int act, int col_tiles) {
     static_assert(WM * WN == 8, "eight warps");
     constexpr int MT = BM / WM / 16, NT = BN / WN / 8, ROWS = BM + BN, SLOTS = ROWS * 4, PER = (SLOTS + 255) / 256;
     __shared__ __align__(16) float tile[2][ROWS][PT_PITCH];      // rows 0 .. BM-1: pixels, then BN rows of W
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int wm = warp % WM, wn = warp / WM;
-    const long long m0 = (long long)blockIdx.x * BM;
-    const int n0 = blockIdx.y * BN;
+    const long long m0 = (long long)(blockIdx.x / col_tiles) * BM;   // column tiles of a row tile are neighbours
+    const int n0 = int(blockIdx.x % col_tiles) * BN;
     // loader slots: slot i covers tile row i / 4, k quad i % 4
     const int kq = (tid & 3) * 4;
     float4 reg[PER];
@@ -578,13 +578,13 @@ extern "C" int shvk_cnn_pointwise(const float* A, const float* W, const float* b
     const int bn = sb::pointwise_tile_width(N);
     const unsigned gy = unsigned((N + bn - 1) / bn);
     if (bn == 128)
-        sb::pointwise_kernel<128, 128, 8, 8><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+        sb::pointwise_kernel<128, 128, 8, 8><<<sb::blocks_for(M, 128) * gy, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(gy));
     else if (bn == 64)
-        sb::pointwise_kernel<64, 64, 4, 4><<<dim3(sb::blocks_for(M, 64), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+        sb::pointwise_kernel<64, 64, 4, 4><<<sb::blocks_for(M, 64) * gy, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(gy));
     else if (bn == 32)
-        sb::pointwise_kernel<128, 32, 4, 4><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+        sb::pointwise_kernel<128, 32, 4, 4><<<sb::blocks_for(M, 128) * gy, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(gy));
     else
-        sb::pointwise_kernel<256, 16, 4, 4><<<dim3(sb::blocks_for(M, 256), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+        sb::pointwise_kernel<256, 16, 4, 4><<<sb::blocks_for(M, 256) * gy, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(gy));
     return int(cudaGetLastError());
 }
 
@@ -593,16 +593,26 @@ extern "C" int shvk_cnn_pointwise_tf32(const float* A, const float* W, const flo
     if (M <= 0 || N <= 0) return 0;
     if (sb::pointwise_args_bad(A, W, b, gate, gate_rows, R, out, N, K)) return int(cudaErrorInvalidValue);
     cudaStream_t s = cudaStream_t(stream);
+    // layers of 24, 40, 72 or 80 output channels: one tile spans the whole row, so a block reads its pixels once and
+    // writes whole contiguous rows (power-of-two column tiles re-read A up to five times and write 64-byte row pieces)
+    if (N == 24 || N == 40 || N == 72 || N == 80) {
+        const unsigned gx = sb::blocks_for(M, 128);
+        if (N == 24) sb::pointwise_tf32_kernel<128, 24, 8, 1><<<gx, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, 1);
+        else if (N == 40) sb::pointwise_tf32_kernel<128, 40, 8, 1><<<gx, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, 1);
+        else if (N == 72) sb::pointwise_tf32_kernel<128, 72, 8, 1><<<gx, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, 1);
+        else sb::pointwise_tf32_kernel<128, 80, 8, 1><<<gx, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, 1);
+        return int(cudaGetLastError());
+    }
     const int bn = sb::pointwise_tile_width(N);
     const unsigned gy = unsigned((N + bn - 1) / bn);
     if (bn == 128)
-        sb::pointwise_tf32_kernel<128, 128, 4, 2><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+        sb::pointwise_tf32_kernel<128, 128, 4, 2><<<sb::blocks_for(M, 128) * gy, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(gy));
     else if (bn == 64)
-        sb::pointwise_tf32_kernel<64, 64, 4, 2><<<dim3(sb::blocks_for(M, 64), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+        sb::pointwise_tf32_kernel<64, 64, 4, 2><<<sb::blocks_for(M, 64) * gy, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(gy));
     else if (bn == 32)
-        sb::pointwise_tf32_kernel<128, 32, 8, 1><<<dim3(sb::blocks_for(M, 128), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+        sb::pointwise_tf32_kernel<128, 32, 8, 1><<<sb::blocks_for(M, 128) * gy, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(gy));
     else
-        sb::pointwise_tf32_kernel<256, 16, 8, 1><<<dim3(sb::blocks_for(M, 256), gy), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act);
+        sb::pointwise_tf32_kernel<256, 16, 8, 1><<<sb::blocks_for(M, 256) * gy, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(gy));
     return int(cudaGetLastError());
 }
 
