@@ -489,10 +489,15 @@ private:
         dump("cnn_map_f0", ce_, size_t(60) * CNN_OUT, SHVK_F32, s);
         launch_ok(shvk_cnn_pool_tokens(ce_, pooled_, F, s), "pool");
         mark("cnn.pool", s);
-        shvk_gemm_args a{};
-        a.M = F * 16; a.N = D; a.K = CNN_OUT; a.A = pooled_; a.lda = CNN_OUT; a.W = tokproj_; a.ldw = CNN_OUT;
-        a.C = sl.d_tokens; a.ldc = D; a.c_dtype = SHVK_F32; a.r_div = 1.0f;
-        launch_ok(shvk_gemm_f32(&a, s), "token projection");
+        if (prec_ == Precision::FP32) {
+            shvk_gemm_args a{};
+            a.M = F * 16; a.N = D; a.K = CNN_OUT; a.A = pooled_; a.lda = CNN_OUT; a.W = tokproj_; a.ldw = CNN_OUT;
+            a.C = sl.d_tokens; a.ldc = D; a.c_dtype = SHVK_F32; a.r_div = 1.0f;
+            launch_ok(shvk_gemm_f32(&a, s), "token projection");
+        } else {
+            launch_ok(shvk_cnn_pointwise_tf32(pooled_, tokproj_, nullptr, nullptr, 1, nullptr, sl.d_tokens, F * 16, D, CNN_OUT,
+                                              SHVK_ACT_NONE, s), "token projection");
+        }
         mark("cnn.token_proj", s);
         dump("tokens", sl.d_tokens, size_t(16) * D, SHVK_F32, s);
     }
