@@ -191,7 +191,7 @@ def encoder_leg(binding, torch, wpath, mode, local_rank, frames=512, steps=10, w
     nbytes, flops = encoder_work()
     pk, pk_src = peaks()
     out = {"frames_per_s": frames / (ms / 1000.0), "frames": frames, "ms_per_encode": ms, "launches": eng.encode_launches(),
-           "dtype": "f32 storage; 1x1 convolutions fp32 fma (fp32 mode) or TF32 mma (16-bit modes)", "ms_by_kernel": kinds, "algorithmic_bytes_per_frame": nbytes, "flops_per_frame": flops,
+           "dtype": "f32 storage; 1x1 convolutions fp32 fma (fp32 mode) or bf16 / fp16 mma with f32 accumulation (16-bit modes)", "ms_by_kernel": kinds, "algorithmic_bytes_per_frame": nbytes, "flops_per_frame": flops,
            "hbm_frac": frames * nbytes / (ms / 1000.0) / (pk["hbm_gbs"] * 1e9), "peak_source": pk_src,
            "note": "frame encoder (MobileNetV3-Large, 320x180 crops -> 16 x 384 tokens), float32 NHWC storage in every "
                    "mode; crops resident in HBM; not part of `value`"}
@@ -579,7 +579,7 @@ def main():
                           warmup=args.warmup)
         emit({"metric": "frames_per_s_encoder", "value": enc["frames_per_s"], "unit": "frames/s", "n_gpus": 1,
               "steps": args.steps, "warmup": args.warmup, "ms_per_step": enc["ms_per_encode"], "higher_is_better": True,
-              "dtype": "f32" if args.mode == "fp32" else "tf32", "data": "synthetic",
+              "dtype": {"fp32": "f32", "bf16": "bf16", "fp16": "f16"}[args.mode], "data": "synthetic",
               "config": {"workload": f"frame encoder, {args.frames} crops per encode, {args.mode} mode"}, "encoder": enc})
         return
     if args.workload == "live":

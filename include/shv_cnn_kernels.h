@@ -81,6 +81,13 @@ int shvk_cnn_pointwise(const float* A, const float* W, const float* b, const flo
 int shvk_cnn_pointwise_tf32(const float* A, const float* W, const float* b, const float* gate, int gate_rows, const float* R,
                             float* out, int M, int N, int K, int act, void* stream);
 
+/* And with A (after the gate) and W rounded to a 16-bit type (ab_dtype: SHVK_BF16 = 1 or SHVK_F16 = 2 of
+ * shv_seq_kernels.h), m16n8k16 tensor-core products, float32 accumulation; inputs and outputs stay float32.  k is
+ * walked in order in slabs of 32, never split.  This is the arithmetic of the reference's 16-bit modes for these
+ * layers (gemm_mma, engine/cuda/gemm.cuh:266-289), without its 16-bit activation storage. */
+int shvk_cnn_pointwise_h(const float* A, const float* W, const float* b, const float* gate, int gate_rows, const float* R,
+                         float* out, int M, int N, int K, int act, int ab_dtype, void* stream);
+
 /* Adaptive 4x4 average pooling of the [F][6][10][960] feature map: token r*4+c averages rows floor(6r/4) ..
  * ceil(6(r+1)/4)-1 and columns floor(10c/4) .. ceil(10(c+1)/4)-1.  out [F][16][960].
  * Replaces launch_pool (engine/cuda/cnn.cu:133-160,188-191). */

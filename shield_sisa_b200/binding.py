@@ -121,6 +121,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_cnn_se_gate_static": (i32, [vp] * 6 + [i32] * 4 + [vp]),
         "shvk_cnn_pointwise": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp]),
         "shvk_cnn_pointwise_tf32": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp]),
+        "shvk_cnn_pointwise_h": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp]),
         "shvk_cnn_pool_tokens": (i32, [vp, vp, i32, vp]),
     }
     for name, (res, args) in sig.items():

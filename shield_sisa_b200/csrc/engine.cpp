@@ -12,7 +12,7 @@
 // encode (F frames, reference run_encode engine/cuda/engine.cu:338-403): stem -> 15 inverted-residual blocks
 //   (expand 1x1 | depthwise | squeeze-excite gate | project 1x1 with the gate applied to its input rows, + residual)
 //   -> 1x1 160 -> 960 -> 4x4 pooling -> 960 -> 384 token projection into slot.d_tokens.  float32 NHWC storage in every
-//   mode; the 1x1 convolutions multiply in TF32 on the tensor cores in the 16-bit modes.
+//   mode; in the bf16 / fp16 modes the 1x1 convolutions round their operands to that type and multiply on the tensor cores.
 //
 // Storage policy (engine/cuda/engine.cu:150-164,213-219): h, P/S and the readout-row buffers are fp32 always; xn, on,
 // hid and the all-row weights are the storage type of the mode.  fp32 mode runs the all-row GEMMs on CUDA cores
@@ -448,8 +448,14 @@ private:
     // ---------------------------------------------------------------- frame encoder
     void run_encode(int slot, int F, cudaStream_t s) {
         const Slot& sl = slots_[size_t(slot)];
-        // 1x1 convolutions: exact fma chains in fp32 mode, TF32 tensor-core products in the 16-bit modes
-        const auto pointwise = prec_ == Precision::FP32 ? shvk_cnn_pointwise : shvk_cnn_pointwise_tf32;
+        // 1x1 convolutions: exact fma chains in fp32 mode, tensor-core products of operands rounded to the mode's 16-bit
+        // type in the bf16 / fp16 modes
+        const int ab = dt_;
+        auto pointwise = [&](const float* A, const float* W, const float* b, const float* gate, int gate_rows, const float* R,
+                             float* out, int M, int N, int K, int act, void* st) {
+            if (prec_ == Precision::FP32) return shvk_cnn_pointwise(A, W, b, gate, gate_rows, R, out, M, N, K, act, st);
+            return shvk_cnn_pointwise_h(A, W, b, gate, gate_rows, R, out, M, N, K, act, ab, st);
+        };
         launch_ok(shvk_cnn_stem(sl.d_frames, lut_, stem_w_, stem_b_, cx_, F, s), "stem");
         mark("cnn.stem", s);
         dump("cnn_stem_f0", cx_, size_t(16) * 90 * 160, SHVK_F32, s);
@@ -495,8 +501,8 @@ private:
             a.C = sl.d_tokens; a.ldc = D; a.c_dtype = SHVK_F32; a.r_div = 1.0f;
             launch_ok(shvk_gemm_f32(&a, s), "token projection");
         } else {
-            launch_ok(shvk_cnn_pointwise_tf32(pooled_, tokproj_, nullptr, nullptr, 1, nullptr, sl.d_tokens, F * 16, D, CNN_OUT,
-                                              SHVK_ACT_NONE, s), "token projection");
+            launch_ok(pointwise(pooled_, tokproj_, nullptr, nullptr, 1, nullptr, sl.d_tokens, F * 16, D, CNN_OUT, SHVK_ACT_NONE, s),
+                      "token projection");
         }
         mark("cnn.token_proj", s);
         dump("tokens", sl.d_tokens, size_t(16) * D, SHVK_F32, s);

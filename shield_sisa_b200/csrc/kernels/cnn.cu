@@ -426,6 +426,142 @@ pointwise_tf32_kernel(const float* __restrict__ A, const float* __restrict__ W, 
     }
 }
 
+// ---------------------------------------------------------------------------------------------------- 1x1 convolution, 16-bit
+// The same row GEMM with the operands rounded to the mode's 16-bit type (bf16 or fp16) on their way into shared
+// memory and mma.sync m16n8k16: twice the contraction depth per shared-memory fragment and per mma of the TF32 form,
+// k slabs of 32.  Float32 in, float32 accumulation, float32 out.
+constexpr int PH_K = 32, PH_PITCH = 20;                       // 16 words of operands + 4 of padding per tile row
+template <typename HT> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <typename HT> __device__ __forceinline__ void mma_16bit(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma_16bit<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma_16bit<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <int BM, int BN, int WM, int WN, typename HT>
+__global__ void __launch_bounds__(256, (BM / WM / 16) * (BN / WN / 8) > 8 ? 2 : ((BM / WM / 16) * (BN / WN / 8) > 5 || BM == 256) ? 3 : 4)
+pointwise_h_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
+                   const float* __restrict__ gate, int gate_rows, const float* R, float* out, int M, int N, int K, int act, int col_tiles) {
+    static_assert(WM * WN == 8, "eight warps");
+    constexpr int MT = BM / WM / 16, NT = BN / WN / 8, ROWS = BM + BN, PER = (ROWS + 63) / 64;
+    __shared__ __align__(16) uint32_t tile[2][ROWS][PH_PITCH];   // rows 0 .. BM-1: pixels, then BN rows of W; 16-bit pairs
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int wm = warp % WM, wn = warp / WM;
+    const long long m0 = (long long)(blockIdx.x / col_tiles) * BM;   // column tiles of a row tile are neighbours
+    const int n0 = int(blockIdx.x % col_tiles) * BN;
+    // loader slots: slot r of a thread covers tile row tid / 4 + 64 r, eight input channels starting at (tid % 4) * 8
+    const int k8 = (tid & 3) * 8;
+    float4 lo[PER], hi[PER];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+            const int row = (tid >> 2) + r * 64;
+            lo[r] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            hi[r] = lo[r];
+            if (k0 + k8 >= K) continue;
+            if (row < BM) {
+                const long long m = m0 + row;
+                if (m < M) {
+                    const float4* p = reinterpret_cast<const float4*>(A + m * K + k0 + k8);
+                    lo[r] = p[0];
+                    hi[r] = p[1];
+                    if (gate) {
+                        const float4* gp = reinterpret_cast<const float4*>(gate + (m / gate_rows) * K + k0 + k8);
+                        const float4 g0 = gp[0], g1 = gp[1];
+                        lo[r].x *= g0.x; lo[r].y *= g0.y; lo[r].z *= g0.z; lo[r].w *= g0.w;
+                        hi[r].x *= g1.x; hi[r].y *= g1.y; hi[r].z *= g1.z; hi[r].w *= g1.w;
+                    }
+                }
+            } else if (row < ROWS && n0 + row - BM < N) {
+                const float4* p = reinterpret_cast<const float4*>(W + (long long)(n0 + row - BM) * K + k0 + k8);
+                lo[r] = __ldg(p);
+                hi[r] = __ldg(p + 1);
+            }
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+            const int row = (tid >> 2) + r * 64;
+            if (row >= ROWS) continue;
+            *reinterpret_cast<uint4*>(&tile[buf][row][(tid & 3) * 4]) =
+                make_uint4(pack_pair<HT>(lo[r].x, lo[r].y), pack_pair<HT>(lo[r].z, lo[r].w), pack_pair<HT>(hi[r].x, hi[r].y),
+                           pack_pair<HT>(hi[r].z, hi[r].w));
+        }
+    };
+    float acc[MT][NT][4];
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < NT; ++ni)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mi][ni][e] = 0.0f;
+    const int nk = (K + PH_K - 1) / PH_K;
+    const int rb = wm * (BM / WM), nb = BM + wn * (BN / WN);
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    for (int kb = 0; kb < nk; ++kb) {
+        const int buf = kb & 1;
+        if (kb + 1 < nk) fetch((kb + 1) * PH_K);
+#pragma unroll
+        for (int ks = 0; ks < PH_K / 16; ++ks) {
+            uint32_t a[MT][4];
+#pragma unroll
+            for (int mi = 0; mi < MT; ++mi) {
+                const uint32_t* r0 = &tile[buf][rb + mi * 16 + g][ks * 8 + t];
+                a[mi][0] = r0[0];
+                a[mi][1] = r0[8 * PH_PITCH];
+                a[mi][2] = r0[4];
+                a[mi][3] = r0[8 * PH_PITCH + 4];
+            }
+#pragma unroll
+            for (int ni = 0; ni < NT; ++ni) {
+                const uint32_t* w0 = &tile[buf][nb + ni * 8 + g][ks * 8 + t];
+                const uint32_t b0 = w0[0], b1 = w0[4];
+#pragma unroll
+                for (int mi = 0; mi < MT; ++mi) mma_16bit<HT>(acc[mi][ni], a[mi], b0, b1);
+            }
+        }
+        if (kb + 1 < nk) {
+            stash(buf ^ 1);
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int ni = 0; ni < NT; ++ni) {
+        const int n = n0 + wn * (BN / WN) + ni * 8 + 2 * t;
+        if (n >= N) continue;
+        const float2 bv = bias ? __ldg(reinterpret_cast<const float2*>(bias + n)) : make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const long long m = m0 + rb + mi * 16 + g + h * 8;
+                if (m >= M) continue;
+                float2 v = make_float2(activate(acc[mi][ni][2 * h] + bv.x, act), activate(acc[mi][ni][2 * h + 1] + bv.y, act));
+                if (R) {
+                    const float2 r = *reinterpret_cast<const float2*>(R + m * N + n);
+                    v.x += r.x; v.y += r.y;
+                }
+                *reinterpret_cast<float2*>(out + m * N + n) = v;
+            }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------- 4x4 pooling
 __global__ void __launch_bounds__(256)
 pool_tokens_kernel(const float* __restrict__ in, float* __restrict__ out, long long total) {
@@ -621,6 +757,45 @@ extern "C" int shvk_cnn_pointwise_tf32(const float* A, const float* W, const flo
     else
         sb::pointwise_tf32_kernel<256, 16, 8, 1><<<sb::blocks_for(M, 256) * gy, 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(gy));
     return int(cudaGetLastError());
+}
+
+namespace sb {
+namespace {
+template <typename HT>
+int launch_pointwise_h(const float* A, const float* W, const float* b, const float* gate, int gate_rows, const float* R, float* out,
+                       int M, int N, int K, int act, cudaStream_t s) {
+#define SB_PH(BM_, BN_, WM_, WN_, GY_) \
+    pointwise_h_kernel<BM_, BN_, WM_, WN_, HT><<<blocks_for(M, BM_) * unsigned(GY_), 256, 0, s>>>(A, W, b, gate, gate_rows, R, out, M, N, K, act, int(GY_))
+    if (N == 24) SB_PH(128, 24, 8, 1, 1);
+    else if (N == 40) SB_PH(128, 40, 8, 1, 1);
+    else if (N == 72) SB_PH(128, 72, 8, 1, 1);
+    else if (N == 80) SB_PH(128, 80, 8, 1, 1);
+    else {
+        const int bn = pointwise_tile_width(N);
+        const unsigned gy = unsigned((N + bn - 1) / bn);
+        if (bn == 128) {
+            const unsigned gy64 = unsigned((N + 63) / 64);
+            if ((long long)blocks_for(M, 128) * gy64 >= 2LL * 3 * 148) SB_PH(128, 64, 4, 2, gy64);
+            else SB_PH(64, 64, 4, 2, gy64);
+        } else if (bn == 64) SB_PH(64, 64, 4, 2, gy);
+        else if (bn == 32) SB_PH(128, 32, 8, 1, gy);
+        else SB_PH(256, 16, 8, 1, gy);
+    }
+#undef SB_PH
+    return int(cudaGetLastError());
+}
+}  // namespace
+}  // namespace sb
+
+extern "C" int shvk_cnn_pointwise_h(const float* A, const float* W, const float* b, const float* gate, int gate_rows,
+                                    const float* R, float* out, int M, int N, int K, int act, int ab_dtype, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (sb::pointwise_args_bad(A, W, b, gate, gate_rows, R, out, N, K)) return int(cudaErrorInvalidValue);
+    if (ab_dtype == sb::DT_BF16)
+        return sb::launch_pointwise_h<__nv_bfloat16>(A, W, b, gate, gate_rows, R, out, M, N, K, act, cudaStream_t(stream));
+    if (ab_dtype == sb::DT_F16)
+        return sb::launch_pointwise_h<__half>(A, W, b, gate, gate_rows, R, out, M, N, K, act, cudaStream_t(stream));
+    return int(cudaErrorInvalidValue);
 }
 
 extern "C" int shvk_cnn_pool_tokens(const float* in, float* out, int F, void* stream) {

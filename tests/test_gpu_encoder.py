@@ -1,8 +1,8 @@
 """GPU parity of the frame encoder: kernels one by one against numpy, and Engine::encode through the C ABI against the
 float64 oracle, the golden tokens of the reference's PyTorch oracle and the reference's CPU engine.
 
-Tolerance: fp32 mode max abs error <= 1e-4 on tokens of O(1) magnitude (recipe W5); bf16 / fp16 modes (TF32 products in
-the 1x1 convolutions, everything else float32) max |err| / max |ref| <= 2e-2."""
+Tolerance: fp32 mode max abs error <= 1e-4 on tokens of O(1) magnitude (recipe W5); bf16 / fp16 modes (operands of the
+1x1 convolutions rounded to that type, everything else float32) max |err| / max |ref| <= 2e-2."""
 import ctypes as C
 
 import numpy as np
@@ -166,6 +166,49 @@ def test_pointwise_tf32_kernel(L, M, N, K, act, gated, resid):
     assert np.abs(got - ref).max() > 0                         # not the exact kernel
 
 
+@pytest.mark.parametrize("ab,tol", [(1, 2.5e-2), (2, 4e-3)])
+@pytest.mark.parametrize("M,N,K,act,gated,resid", [(14400, 64, 16, 1, False, False), (1000, 24, 72, 0, False, True),
+                                                  (120, 160, 960, 0, True, True), (60, 960, 160, 2, False, False),
+                                                  (77, 40, 120, 0, True, False), (333, 80, 184, 0, False, True),
+                                                  (4000, 16, 16, 0, False, True), (700, 384, 960, 0, False, False)])
+def test_pointwise_16bit_kernel(L, M, N, K, act, gated, resid, ab, tol):
+    """1x1 convolution with operands rounded to bf16 (2^-9 relative) or fp16 (2^-11), float32 accumulation."""
+    import torch
+    rng = np.random.default_rng(M + N + 2)
+    rows = 60 if gated and M % 60 == 0 else (11 if gated else 1)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    Wt = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    gate = rng.uniform(0, 1, size=((M + rows - 1) // rows, K)).astype(np.float32) if gated else None
+    R = rng.standard_normal((M, N)).astype(np.float32) if resid else None
+    out = dev(R) if resid else torch.empty((M, N), dtype=torch.float32, device="cuda")
+    g_dev = dev(gate) if gated else None
+    d_a, d_w, d_b = dev(A), dev(Wt), dev(b)
+    rc = L.shvk_cnn_pointwise_h(_ptr(d_a), _ptr(d_w), _ptr(d_b), _ptr(g_dev) if gated else None, rows,
+                                _ptr(out) if resid else None, _ptr(out), M, N, K, act, ab, stream_ptr())
+    assert rc == 0
+    sync()
+    a64 = A.astype(np.float64)
+    if gated:
+        a64 = a64 * np.repeat(gate.astype(np.float64), rows, axis=0)[:M]
+    ref = a64 @ Wt.T.astype(np.float64) + b
+    ref = np.maximum(ref, 0) if act == 1 else _hardswish(ref) if act == 2 else ref
+    if resid:
+        ref = ref + R
+    got = out.cpu().numpy()
+    assert np.abs(got - ref).max() < tol
+    # the same rounding done on the host reproduces the kernel to float32 accumulation error
+    dt = torch.bfloat16 if ab == 1 else torch.float16
+    a_r = torch.from_numpy(a64.astype(np.float32)).to(dt).double().numpy()
+    w_r = torch.from_numpy(Wt).to(dt).double().numpy()
+    ref_r = a_r @ w_r.T + b
+    ref_r = np.maximum(ref_r, 0) if act == 1 else _hardswish(ref_r) if act == 2 else ref_r
+    if resid:
+        ref_r = ref_r + R
+    assert np.abs(got - ref_r).max() < 5e-5
+    assert L.shvk_cnn_pointwise_h(_ptr(d_a), _ptr(d_w), _ptr(d_b), None, 1, None, _ptr(out), M, N, K, act, 0, stream_ptr()) != 0
+
+
 def test_pool_tokens_kernel(L):
     import torch
     from oracle import cnn_oracle as CO
@@ -226,7 +269,7 @@ def test_encode_matches_reference(case, mode, weight_files):
     eng = binding.EngineCore(path, mode, max_windows=1, max_frames=4, use_graphs=False)
     tok = _encode(eng, frames)
     assert eng.status() == 0
-    # fp32 mode: max abs error <= 1e-4.  16-bit modes (TF32 products in the 1x1 convolutions): max |err| / max |ref| <= 2e-2
+    # fp32 mode: max abs error <= 1e-4.  16-bit modes (16-bit operands in the 1x1 convolutions): max |err| / max |ref| <= 2e-2
     def err(ref):
         return np.abs(tok - ref).max() if mode == "fp32" else rel_err(tok, ref)
     tol = TOL if mode == "fp32" else 2e-2
