@@ -173,22 +173,42 @@ se_gate_kernel(const float* __restrict__ partial, const float* __restrict__ w1, 
         pooled[c] = t / float(HW);
     }
     __syncthreads();
-    for (int j = warp; j < CS; j += nwarp) {
-        const float* wr = w1 + (long long)j * C;
-        float t = 0.0f;
-#pragma unroll 4
-        for (int c = lane; c < C; c += 32) t = fmaf(__ldg(wr + c), pooled[c], t);
-        t = warp_sum(t);
-        if (lane == 0) hid[j] = fmaxf(t + b1[j], 0.0f);
+    // four outputs per warp at a time: their weight loads are in flight together; each output keeps its own
+    // lane-strided sum and shuffle reduction, so the result does not depend on the grouping
+    for (int j0 = warp * 4; j0 < CS; j0 += nwarp * 4) {
+        float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float* wr[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) wr[r] = w1 + (long long)min(j0 + r, CS - 1) * C;
+#pragma unroll 2
+        for (int c = lane; c < C; c += 32) {
+            const float p = pooled[c];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) t[r] = fmaf(__ldg(wr[r] + c), p, t[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float v = warp_sum(t[r]);
+            if (lane == 0 && j0 + r < CS) hid[j0 + r] = fmaxf(v + b1[j0 + r], 0.0f);
+        }
     }
     __syncthreads();
-    for (int c = warp; c < C; c += nwarp) {
-        const float* wr = w2 + (long long)c * CS;
-        float t = 0.0f;
-#pragma unroll 4
-        for (int j = lane; j < CS; j += 32) t = fmaf(__ldg(wr + j), hid[j], t);
-        t = warp_sum(t);
-        if (lane == 0) gate[(long long)f * C + c] = activate(t + b2[c], SHVK_ACT_HSIGMOID);
+    for (int c0 = warp * 4; c0 < C; c0 += nwarp * 4) {
+        float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float* wr[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) wr[r] = w2 + (long long)min(c0 + r, C - 1) * CS;
+#pragma unroll 2
+        for (int j = lane; j < CS; j += 32) {
+            const float h = hid[j];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) t[r] = fmaf(__ldg(wr[r] + j), h, t[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float v = warp_sum(t[r]);
+            if (lane == 0 && c0 + r < C) gate[(long long)f * C + c0 + r] = activate(v + b2[c0 + r], SHVK_ACT_HSIGMOID);
+        }
     }
 }
 
