@@ -196,6 +196,32 @@ def encoder_leg(binding, torch, wpath, mode, local_rank, frames=512, steps=10, w
            "note": "frame encoder (MobileNetV3-Large, 320x180 crops -> 16 x 384 tokens), float32 NHWC storage in every "
                    "mode; crops resident in HBM; not part of `value`"}
     eng.close()
+    del eng
+    torch.cuda.empty_cache()
+    # whole clips through the C ABI: uint8 crops in pinned host memory -> logits in host memory (shv_cuda_predict)
+    clips = 128
+    model = binding.CudaModel(wpath, mode, device=local_rank, experimental=True, max_frames=640, max_windows=64, max_host_tokens=20)
+    pin = binding.PinnedBuffer(model.L, (clips, 20, 172800), np.uint8)
+    pin.array[...] = np.random.default_rng(5).integers(0, 256, size=(8, 20, 172800), dtype=np.uint8).repeat(clips // 8, axis=0)
+    logits = np.zeros(clips, np.float32)
+
+    def predict():
+        if model.L.shv_cuda_predict(model.m, pin.ptr, clips, logits.ctypes.data):
+            raise SystemExit(binding.last_error(model.L))
+
+    predict()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        predict()
+    dt = (time.perf_counter() - t0) / 3
+    if not np.isfinite(logits).all():
+        raise SystemExit("predict returned non-finite logits")
+    out["predict"] = {"clips_per_s": clips / dt, "frames_per_s": clips * 20 / dt, "clips": clips,
+                      "h2d_bytes_per_call": clips * 20 * 172800, "d2h_bytes_per_call": clips * 4,
+                      "api": "one synchronous shv_cuda_predict of 128 clips (20 uint8 crops each) from pinned host memory, "
+                             "max_frames 640: four jobs of 32 clips, uploads overlapping the previous job's kernels"}
+    model.close()
+    pin.free()
     return out
 
 
