@@ -226,7 +226,7 @@ def encoder_leg(binding, torch, wpath, mode, local_rank, frames=512, steps=10, w
 
 
 def run_live(args, local_rank: int):
-    """Streaming load (BASELINE config 5 on one GPU): `--participants` rings of 24 device token slots; every hop each
+    """Streaming load on one GPU (the reference's live benchmark, bench/gpu_bench.cpp:141-218): `--participants` rings of 24 device token slots; every hop each
     participant sends 4 new uint8 crops and scores the window of its last 20 frames (one request per participant:
     frames + store_slots + window_slots), fp16 mode by default.  Prints windows/s and frames/s over `--steps` hops after
     the 20-frame first hop; crops start in pinned host memory, logits end in host memory."""
