@@ -35,6 +35,18 @@ def hop_slots(participant: int, frames_so_far: int, new: int):
     return store, window
 
 
+def place_participants(participant_ids, world: int):
+    """Per device of a box: the positions (in `participant_ids`) of the participants whose rings live there, in input
+    order; a participant's local ring index on its device is its position in that list.  Placement is the stable hash
+    of sharding.device_of_participant, so a participant keeps its device (and its 24 token slots) for the whole call."""
+    from .sharding import device_of_participant
+
+    placed = [[] for _ in range(world)]
+    for i, pid in enumerate(participant_ids):
+        placed[device_of_participant(pid, world)].append(i)
+    return placed
+
+
 class LiveDriver:
     """Drives hops of `participants` rings through one binding.CudaModel (which must have token_slots >= 24 * participants)."""
 

@@ -1,5 +1,7 @@
 """Streaming load: ring-slot arithmetic (CPU) and, on a GPU, hops of several participants through frames + store_slots +
 window_slots requests, checked against whole-clip predictions and the reference's CPU engine."""
+import os
+
 import numpy as np
 import pytest
 
@@ -26,6 +28,60 @@ def test_ring_slots_follow_the_reference_driver():
         live.hop_slots(0, 0, 4)                                    # first hop must fill the window
     with pytest.raises(ValueError):
         live.hop_slots(0, 20, 24)
+
+
+def _fake_window_score(store, window, hop):
+    """Stand-in for a device: any deterministic function of what a hop request carries."""
+    return float(np.dot(window.astype(np.float64) % 24, np.arange(1, 21)) + 1000.0 * hop + store.size)
+
+
+def _live_rank(rank, world, port, ids, hops, out_path):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mine = live.place_participants(ids, world)[rank]
+        sent = [0] * len(mine)
+        rows = []
+        for h in range(hops):
+            new = 20 if h == 0 else 4
+            for local, gi in enumerate(mine):                       # local ring index = position on this device
+                store, window = live.hop_slots(local, sent[local], new)
+                assert store.min() >= local * 24 and window.max() < (local + 1) * 24
+                sent[local] += new
+                rows.append((h, gi, _fake_window_score(store, window, h)))
+        gathered = [None] * world if rank == 0 else None
+        dist.gather_object(rows, gathered, dst=0)                   # host gather of the logits, as for window shards
+        if rank == 0:
+            table = np.full((hops, len(ids)), np.nan)
+            for part in gathered:
+                for h, gi, v in part:
+                    assert np.isnan(table[h, gi])                   # every participant scored by exactly one device
+                    table[h, gi] = v
+            np.save(out_path, table)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_device_placement_covers_every_participant_once(tmp_path):
+    import torch.multiprocessing as mp
+    ids = [f"participant-{i}" for i in range(37)]
+    placed = live.place_participants(ids, 2)
+    assert sorted(placed[0] + placed[1]) == list(range(37)) and placed == live.place_participants(ids, 2)
+    out = tmp_path / "live.npy"
+    port = 31000 + os.getpid() % 2000
+    mp.spawn(_live_rank, args=(2, port, ids, 3, str(out)), nprocs=2, join=True)
+    table = np.load(out)
+    assert np.isfinite(table).all()
+    # a participant's ring arithmetic depends only on its own history, so both devices produce what one device would
+    for rank_list in placed:
+        for local, gi in enumerate(rank_list):
+            sent = 0
+            for h in range(3):
+                new = 20 if h == 0 else 4
+                store, window = live.hop_slots(local, sent, new)
+                sent += new
+                assert table[h, gi] == _fake_window_score(store, window, h)
 
 
 @pytest.mark.gpu
