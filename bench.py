@@ -225,43 +225,53 @@ def encoder_leg(binding, torch, wpath, mode, local_rank, frames=512, steps=10, w
     return out
 
 
-def run_live(args, local_rank: int):
-    """Streaming load on one GPU (the reference's live benchmark, bench/gpu_bench.cpp:141-218): `--participants` rings of 24 device token slots; every hop each
-    participant sends 4 new uint8 crops and scores the window of its last 20 frames (one request per participant:
-    frames + store_slots + window_slots), fp16 mode by default.  Prints windows/s and frames/s over `--steps` hops after
-    the 20-frame first hop; crops start in pinned host memory, logits end in host memory."""
+def run_live(args, rank: int, world: int, local_rank: int):
+    """Streaming load (the reference's live benchmark, bench/gpu_bench.cpp:141-218): `--participants` rings of 24 device
+    token slots per box; every hop each participant sends 4 new uint8 crops and scores the window of its last 20 frames
+    (one request per participant: frames + store_slots + window_slots), fp16 mode by default.  With N ranks the
+    participants are placed on the GPUs by live.place_participants and every rank drives its own; there is no exchange
+    between ranks.  Prints windows/s and frames/s of the whole job over `--steps` hops after the 20-frame first hop (max
+    over ranks of the wall time); crops start in pinned host memory, logits end in host memory."""
     import torch
+    import torch.distributed as dist
 
     from shield_sisa_b200 import binding, live
 
     torch.cuda.set_device(local_rank)
-    P, new = args.participants, 4
-    wpath = make_weights("live")
-    cap = min(4096, max(20, P * 20))
-    model = binding.CudaModel(wpath, args.mode, device=local_rank, experimental=True, max_frames=min(4096, cap),
-                              max_windows=min(4096, P), max_host_tokens=20, token_slots=live.RING * P)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    total, new = args.participants, 4
+    mine = live.place_participants([f"participant-{i}" for i in range(total)], world)[rank]
+    P = len(mine)
+    wpath = make_weights(f"live{rank}")
+    model = binding.CudaModel(wpath, args.mode, device=local_rank, experimental=True, max_frames=min(4096, max(20, P * 20)),
+                              max_windows=min(4096, max(1, P)), max_host_tokens=20, token_slots=live.RING * max(1, P))
     rng = np.random.default_rng(4)
     distinct = 64                                               # distinct crops, reused across participants and hops
     pool = binding.PinnedBuffer(model.L, (distinct, 180, 320, 3), np.uint8)
     pool.array[...] = rng.integers(0, 256, size=pool.array.shape, dtype=np.uint8)
-    drv = live.LiveDriver(model, P)
-
-    def crops_for(n):
-        # every participant reads a contiguous run of the pinned pool: DMA'd without staging
-        idx = (np.arange(P)[:, None] * 7 + np.arange(n)[None, :]) % (distinct - n)
-        return [pool.array[i[0]:i[0] + n] for i in idx]
+    sent = np.zeros(P, np.int64)
 
     def hop(n):
         logits = np.full(P, np.nan, np.float32)
         jobs, keep = [], []
-        for p, c in enumerate(crops_for(n)):
-            store, window = live.hop_slots(p, int(drv.frames_sent[p]), n)
-            j, k = model.submit(1, logits[p:p + 1], window_slots=window, frames=c, n_frames=n, store_slots=store)
+        for p in range(P):
+            first = (p * 7) % (distinct - n)                    # a contiguous run of the pinned pool: DMA'd without staging
+            store, window = live.hop_slots(p, int(sent[p]), n)
+            j, k = model.submit(1, logits[p:p + 1], window_slots=window, frames=pool.array[first:first + n], n_frames=n,
+                                store_slots=store)
             if not j:
                 raise SystemExit(binding.last_error(model.L))
             jobs.append(j)
             keep.append(k)
-            drv.frames_sent[p] += n
+            sent[p] += n
         sizes = []
         for j in jobs:
             if model.job_wait(j) != 0:
@@ -275,22 +285,31 @@ def run_live(args, local_rank: int):
     hop(20)
     for _ in range(max(1, args.warmup)):
         hop(new)
+    barrier()
     t0 = time.perf_counter()
     sizes = []
     for _ in range(args.steps):
         sizes += hop(new)
     dt = time.perf_counter() - t0
-    line = {"metric": "windows_per_s_live_hops", "value": P * args.steps / dt, "unit": "windows/s", "n_gpus": 1,
-            "steps": args.steps, "warmup": max(1, args.warmup), "ms_per_step": 1000.0 * dt / args.steps,
-            "higher_is_better": True, "dtype": {"fp32": "f32", "bf16": "bf16", "fp16": "f16"}[args.mode], "data": "synthetic",
-            "frames_per_s": P * new * args.steps / dt, "mean_batch_windows": float(np.mean(sizes)),
-            "config": {"workload": f"live hops: {P} participants x (4 new 320x180 uint8 crops + 1 window of 20 ring slots) per "
-                                   f"hop, one request per participant through shv_cuda_submit, {args.mode} mode",
-                       "device_bytes": model.device_bytes()},
-            "h2d_bytes_per_step": P * new * 172800, "d2h_bytes_per_step": P * 4}
+    barrier()
+    if world > 1:
+        t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    if rank == 0:
+        emit({"metric": "windows_per_s_live_hops", "value": total * args.steps / dt, "unit": "windows/s", "n_gpus": world,
+              "steps": args.steps, "warmup": max(1, args.warmup), "ms_per_step": 1000.0 * dt / args.steps,
+              "higher_is_better": True, "scaling": "strong",
+              "dtype": {"fp32": "f32", "bf16": "bf16", "fp16": "f16"}[args.mode], "data": "synthetic",
+              "frames_per_s": total * new * args.steps / dt, "mean_batch_windows": float(np.mean(sizes)) if sizes else 0.0,
+              "config": {"workload": f"live hops: {total} participants over {world} GPU(s) x (4 new 320x180 uint8 crops + 1 window "
+                                     f"of 20 ring slots) per hop, one request per participant through shv_cuda_submit, "
+                                     f"{args.mode} mode", "participants_rank0": P, "device_bytes_rank0": model.device_bytes()},
+              "h2d_bytes_per_step": total * new * 172800, "d2h_bytes_per_step": total * 4})
     model.close()
     pool.free()
-    emit(line)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def make_weights(tag: str):
@@ -609,9 +628,7 @@ def main():
               "config": {"workload": f"frame encoder, {args.frames} crops per encode, {args.mode} mode"}, "encoder": enc})
         return
     if args.workload == "live":
-        if world > 1:
-            raise SystemExit("the live workload runs on one GPU per process; start one process per GPU")
-        run_live(args, local_rank)
+        run_live(args, rank, world, local_rank)
         return
     if world != args.gpus:
         if args.gpus > 1:
