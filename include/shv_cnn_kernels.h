@@ -74,7 +74,7 @@ int shvk_cnn_se_gate_static(const float* x, const float* w1, const float* b1, co
 int shvk_cnn_pointwise(const float* A, const float* W, const float* b, const float* gate, int gate_rows, const float* R,
                        float* out, int M, int N, int K, int act, void* stream);
 
-/* The same 1x1 convolution on the tensor cores, for the 16-bit modes: A (after the gate) and W are rounded to TF32
+/* The same 1x1 convolution on the tensor cores with float32 range: A (after the gate) and W are rounded to TF32
  * (10-bit mantissa, float32 range), products accumulate in float32; inputs and outputs stay float32.  k is walked in
  * order in slabs of 16, never split.  The reference's 16-bit modes run these layers as 16-bit tensor-core GEMMs
  * (gemm_mma, engine/cuda/gemm.cuh:266-289). */
