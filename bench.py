@@ -3,6 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--mode bf16|fp16|fp32] [--batch B] [--impl reference]
     python bench.py --workload live [--participants P] [--steps HOPS] [--mode fp16]     (streaming hops, see run_live)
     python bench.py --workload encoder [--frames F] [--mode bf16]                       (frame encoder alone)
+    python bench.py --workload chunked [--steps K]                                      (long-sequence kernel, B=64 T=2048)
 
 One "step" = one pass of the whole sequence stack over B clips (20 frames x 16 tokens x 384 + readout = 321 rows per
 clip) per GPU.  Default workload: B = 4096 clips per GPU, bf16 mode, synthetic N(0,1) frame embeddings and seeded
@@ -51,7 +52,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per clip of one launch, from the ncu captures at B = 512 in the 16-bit
 # modes that are summarised under profiles/ (traffic grows in proportion to the clips of a launch: every clip's tiles
 # are fetched and written once); scaled to the bench's B for the `traffic` key
-NCU_TRAFFIC_PER_CLIP = {"gdn_scan": (1.596298e9 + 0.246092e9) / 512, "gemm.in_proj": (0.128123e9 + 1.469240e9) / 512}
+NCU_TRAFFIC_PER_CLIP = {}
+PT_BYTES_PER_CLIP = 6 * 21 * 12416      # chunk-blocked bf16 operand tiles between the fused in-projection and the scan
 
 
 def peaks():
@@ -75,8 +77,9 @@ def algorithmic_work(name: str, storage_bytes: int):
     table = {
         "assemble_norm": (20 * 6144 * 4 + h + xn, 0),
         "rmsnorm": (h + xn, 0),
-        "gemm.in_proj": (xn + p_out, 2 * NTOK * 2316 * 384),
-        "gdn_scan": (p_out + on, 0),
+        "gemm.in_proj": (xn + p_out, 2 * NTOK * 2316 * 384),                       # fp32 mode
+        "gdn_inproj": (xn + PT_BYTES_PER_CLIP, 2 * NTOK * 2316 * 384),             # 16-bit modes: projection + conv + SiLU + gates
+        "gdn_scan": ((p_out if s == 4 else PT_BYTES_PER_CLIP) + on, 0),
         "gemm.o_proj": (on + 2 * h, 2 * NTOK * 384 * 768),
         "gemm.ffn_up": (xn + hid, 2 * NTOK * 1920 * 384),
         "gemm.ffn_down": (hid + 2 * h, 2 * NTOK * 384 * 960),
@@ -320,6 +323,68 @@ def make_weights(tag: str):
     return path
 
 
+
+# ---------------------------------------------------------------------------------------------- long-sequence kernel
+def chunked_case(torch, L, dk: int, steps: int, warmup: int):
+    """One head-dim case of the long-sequence stress configuration: B = 64, T = 2048, H = 6, DV = 128, bf16 q / k / v
+    N(0,1) seed 3 with q, k L2-normalised before rounding, log decay = logsigmoid(N(0,1)), beta = sigmoid(N(0,1)),
+    scale DK^-0.5, zero initial state.  Inputs (610 / 812 MB) exceed L2, so consecutive launches need no flush."""
+    B, T, H, DV = 64, 2048, 6, 128
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    rn = lambda *shape: torch.randn(*shape, device="cuda", generator=gen)  # noqa: E731
+    q, k, v = rn(B, T, H, dk), rn(B, T, H, dk), rn(B, T, H, DV)
+    q = (q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6)).bfloat16()
+    k = (k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)).bfloat16()
+    v = v.bfloat16()
+    g = torch.nn.functional.logsigmoid(rn(B, T, H))
+    beta = torch.sigmoid(rn(B, T, H))
+    o = torch.zeros(B, T, H, DV, device="cuda", dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def run():
+        rc = L.shvk_gdn_chunked(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), o.data_ptr(), 1,
+                                B, T, H, dk, DV, float(dk ** -0.5), stream)
+        if rc:
+            raise SystemExit(f"shvk_gdn_chunked returned cudaError {rc}")
+
+    for _ in range(max(3, warmup)):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if not bool(torch.isfinite(o.float()).all()):
+        raise SystemExit("long-sequence kernel returned non-finite outputs")
+    pk, src = peaks()
+    nbytes = B * T * H * (2 * dk * 2 + DV * 2 + 8 + DV * 2)          # q, k, v in, g and beta in, o out: per token and head
+    C = 64                                                            # flops of the chunked form at chunk 64, per chunk and head
+    flops = B * (T // C) * H * (2 * C * (3 * C * dk + 2 * C * DV + 3 * dk * DV) + C * C * C // 3)
+    return {"head_dim": dk, "ms": ms, "tokens_per_s": B * T / (ms / 1000.0), "algorithmic_bytes": nbytes,
+            "gbs": nbytes / ms / 1e6, "hbm_frac": nbytes / ms / 1e6 / pk["hbm_gbs"], "chunked_form_flops": flops,
+            "tflops": flops / ms / 1e9, "tensor_frac_of_sustained": flops / ms / 1e9 / pk["bf16_tflops_sustained"],
+            "peak_source": src}
+
+
+def run_chunked(args, local_rank: int):
+    import torch
+
+    from shield_sisa_b200 import binding
+    torch.cuda.set_device(local_rank)
+    L = binding.load_library(True)
+    cases = [chunked_case(torch, L, dk, args.steps, args.warmup) for dk in (64, 128)]
+    emit({"metric": "tokens_per_s_gdn_chunked_b64_t2048", "value": cases[0]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+          "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": cases[0]["ms"], "higher_is_better": True,
+          "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+          "config": {"workload": "long-sequence gated delta rule, chunked WY form: B=64, T=2048, H=6, DK=64 (value) and "
+                                 "DK=128, DV=128, bf16 q/k/v, seed 3", "l2": "inputs exceed L2 (610 / 812 MB per launch)"},
+          "roofline": {"bound": "hbm", "achieved": cases[0]["gbs"], "peak": peaks()[0]["hbm_gbs"], "unit": "GB/s",
+                       "frac": cases[0]["hbm_frac"], "kernel": "gdn_chunked", "traffic": None},
+          "gpu_launches": 2 * args.steps, "cases": cases})
+
 # ---------------------------------------------------------------------------------------------- CPU baseline
 def cpu_reference_rate(weights_path, tokens_host, budget_s: float, threads: int | None = None):
     """Windows/s of the reference CPU engine (oracle/_ref) on `threads` host threads over a bounded sample of
@@ -499,7 +564,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # ------------------------------------------------------------ end to end through the C ABI with host buffers
     e2e = None
-    if B <= 4096:
+    if B <= 4096 and not args.no_e2e:
         mw = max(1, min(B, args.e2e_windows))
         model = binding.CudaModel(wpath, mode, device=local_rank, experimental=True, max_windows=mw,
                                   max_host_tokens=20 * mw, max_frames=1)
@@ -549,6 +614,32 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         model.close()
         pin.free()
 
+    # ------------------------------------------------------------ extra keys beside it (rank 0, N = 1; not in `value`)
+    extras = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        extras = {}
+        # the exact tier's configuration: B = 128 clips, fp32 mode, tokens resident in HBM
+        b2 = 128
+        eng2 = binding.EngineCore(wpath, "fp32", device=local_rank, max_windows=b2, use_graphs=True)
+        eng2.bind_tokens(0, tokens.data_ptr(), b2, stream)
+        for _ in range(3):
+            eng2.classify(0, b2, stream)
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(5):
+            eng2.classify(0, b2, stream)
+        a1.record()
+        torch.cuda.synchronize()
+        ms2 = a0.elapsed_time(a1) / 5
+        extras["exact_fp32_b128"] = {"clips_per_s": b2 / (ms2 / 1000.0), "ms_per_step": ms2, "batch": b2, "dtype": "f32",
+                                     "note": "GDN+SISA stack in the exact fp32 mode at B = 128, tokens resident in HBM"}
+        eng2.close()
+        del eng2
+        torch.cuda.empty_cache()
+        extras["gdn_chunked_b64_t2048"] = [chunked_case(torch, binding.load_library(True), dk, 5, 3) for dk in (64, 128)]
+        torch.cuda.empty_cache()
+
     # ------------------------------------------------------------ CPU baseline beside it (rank 0, N = 1)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -567,7 +658,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
             "stack_hbm_fraction": {"algorithmic_bytes_per_clip": alg_bytes_clip, "frac": stack_frac,
                                    "note": "whole stack against the GEMM-boundary byte model and the measured HBM peak"},
-            "kernels": kernels, "encoder": encoder,
+            "kernels": kernels, "encoder": encoder, "extras": extras,
         }
         emit(line)
     if world > 1:
@@ -598,9 +689,12 @@ def main():
     ap.add_argument("--batch", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-encoder", action="store_true", help="skip the frame-encoder leg")
-    ap.add_argument("--workload", default="stack", choices=["stack", "live", "encoder"],
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (small cases for profiling)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the extra keys (exact-tier B = 128 line, long-sequence kernel)")
+    ap.add_argument("--workload", default="stack", choices=["stack", "live", "encoder", "chunked"],
                     help="stack: the headline metric (default); live: streaming hops with frames and device token rings; "
-                         "encoder: the frame-encoder leg alone on --frames crops (small cases for profiling)")
+                         "encoder: the frame-encoder leg alone on --frames crops (small cases for profiling); "
+                         "chunked: the long-sequence gated delta rule (B = 64, T = 2048, bf16, head dim 64 and 128)")
     ap.add_argument("--frames", type=int, default=512, help="crops per encode of the encoder workload")
     ap.add_argument("--participants", type=int, default=4096, help="participants of the live workload")
     ap.add_argument("--e2e-threads", type=int, default=2,
@@ -629,6 +723,10 @@ def main():
         return
     if args.workload == "live":
         run_live(args, rank, world, local_rank)
+        return
+    if args.workload == "chunked":
+        if rank == 0:
+            run_chunked(args, local_rank)
         return
     if world != args.gpus:
         if args.gpus > 1:

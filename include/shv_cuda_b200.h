@@ -26,6 +26,13 @@ int shv_cuda_b200_upload_tokens(shv_cuda_model* m, const float* tokens, size_t n
 /* Number of kernels one GPU batch launches (for launch accounting in benchmarks). */
 int shv_cuda_b200_launches_per_batch(const shv_cuda_model* m);
 
+/* Test hook, experimental library only (-1 in the certificate-checked library): the next `batches` GPU batches of a
+ * 16-bit model run with one launch starved of its input (kind 1: a tensor-core GEMM, 2: the scan), so that the kernel's
+ * bounded wait runs out, its status word is set and it returns.  Those batches fail (NaN logits) like any batch whose
+ * kernels gave up; the scheduler then clears the status words and later batches run normally.  Nothing faults or
+ * hangs: the wait is a poll loop with a limit, the kernel's ordinary abort path is what the test exercises. */
+int shv_cuda_b200_test_starve(shv_cuda_model* m, int kind, int batches);
+
 /* ---------------------------------------------------------------- engine core for harnesses
  * The reference's internal C++ engine API (engine/cuda/engine.hpp:20-62: make_engine, Engine::slot, Engine::classify,
  * set_dump_dir), which its kernel benchmark and dump tools compile against (bench/gpu_kbench.cu:55-103,
@@ -48,7 +55,8 @@ int shvb_engine_encode_launches(const shvb_engine* e);               /* kernels 
 /* shvb_engine_profile for one eager encode of F frames. */
 int shvb_engine_profile_encode(shvb_engine* e, int slot, int F, void* stream, float* ms, int cap, char* names, int names_cap);
 /* Points window w, frame f of `slot` (0 or 1) at d_tokens + (w*20 + f)*6144: B windows of device-resident tokens
- * [B][20][16][384] fp32.  The table upload is enqueued on `stream`. */
+ * [B][20][16][384] fp32; the entries of the padding windows up to B's size class point at engine-owned tokens, so a
+ * buffer bound earlier may be freed.  The table upload is enqueued on `stream`. */
 int shvb_engine_bind_tokens(shvb_engine* e, int slot, const float* d_tokens, int B, void* stream);
 /* Enqueues the whole sequence stack for B windows on `stream`; logits land in shvb_engine_logits(e, slot)[0..B). */
 int shvb_engine_classify(shvb_engine* e, int slot, int B, void* stream);
@@ -58,6 +66,8 @@ int shvb_engine_read_logits(shvb_engine* e, int slot, float* host, int n, void* 
 int shvb_engine_window_bucket(const shvb_engine* e, int B);          /* size class a batch of B is padded to */
 int shvb_engine_launches(const shvb_engine* e);                      /* kernels per classify */
 int shvb_engine_status(const shvb_engine* e);                        /* nonzero: a kernel's bounded wait gave up */
+/* Test hook, as shv_cuda_b200_test_starve: the next `batches` classify calls starve one launch (16-bit modes). */
+int shvb_engine_test_starve(shvb_engine* e, int kind, int batches);
 size_t shvb_engine_bytes(const shvb_engine* e, int which);           /* 0 weights, 1 activations, 2 one slot */
 /* One eager classify of B windows with a CUDA event after every launch.  Writes up to `cap` per-launch times
  * (milliseconds, launch order) to ms and the kernel names, separated by ';', to names (names_cap bytes).  Returns the

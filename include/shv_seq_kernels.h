@@ -62,6 +62,43 @@ int shvk_gemm_tc(const void* host_plan, void* stream);
 int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream);
 /* Device status word of the tensor-core path: nonzero after a bounded wait inside a kernel gave up. */
 int shvk_gemm_tc_status(int* status_out);
+/* Test launch of the same plan: the producer of every CTA withholds the first operand stage of its first tile, so the
+ * MMA role's bounded wait runs out after `polls` polls (clamped to 256 .. 2^22).  The CTA then takes its abort path
+ * (status word set, every role leaves its loop, tensor memory freed) and returns; C is left partly written.  Nothing
+ * faults or spins without bound.  Exists so that a test can watch the abort path work. */
+int shvk_gemm_tc_rows_starved(const void* host_plan, int rows, int polls, void* stream);
+
+/* The kernels' status words (tensor-core GEMMs, fp32 scan, the two 16-bit scans) are per device and per process.  These two
+ * calls enqueue on `stream`: a copy of the SHVK_STATUS_WORDS words into host_words (pinned host memory, read it after
+ * the stream has passed this point), and their reset to zero.  A scheduler fetches the words behind a batch's last
+ * kernel, fails the batch if one is set, and clears them so that later batches run normally. */
+enum { SHVK_STATUS_WORDS = 4 };
+int shvk_status_fetch_async(int* host_words, void* stream);
+int shvk_status_clear_async(void* stream);
+
+/* GDN in-projection of the 16-bit modes, fused with the steps between projection and recurrence (causal conv k = 4 +
+ * bias + SiLU on q, k, v; SiLU on the output gate; log decay and beta).  Computes W' xn^T on the tensor cores with the
+ * channels on the MMA rows and writes bf16 operand tiles in chunk blocks of 16 tokens ("PT": per clip, head and chunk
+ * q^T [64][16], k^T [64][16], v^T [128][16], gate^T [128][16], log decay [16], beta [16]; shvk_gdn_pt_bytes(B) bytes
+ * for B clips), which shvk_gdn_scan_t consumes.  xn: [max_rows][384] in ab_dtype (bf16 or fp16), rows of clip c at
+ * 321 c; w_perm: [shvk_gdn_inproj_rows()][384] in ab_dtype = the rows of the reference's fused in-projection weight
+ * [q | k | v | gate | a | b] (engine/cuda/model.cpp:109-115) in the order shvk_gdn_inproj_row_order gives (source row
+ * per row of w_perm, -1 = a zero row); conv_w [1536][4], conv_b [1536], a_log [6], dt_bias [6] fp32 as in the
+ * reference.  The plan (512 bytes, host, 64-byte aligned) holds the TMA tensor maps for exactly these buffers.
+ * Replaces the in-projection gemm<T> (engine/cuda/engine.cu:418) + launch_gdn_prep (engine/cuda/seq.cu:72-104). */
+int shvk_gdn_inproj_rows(void);
+void shvk_gdn_inproj_row_order(int32_t* src_row /* [shvk_gdn_inproj_rows()] */);
+size_t shvk_gdn_pt_bytes(int B);
+int shvk_gdn_inproj_plan(const void* xn, long long max_rows, const void* w_perm, const float* conv_w, const float* conv_b,
+                         const float* a_log, const float* dt_bias, void* pt_out, int ab_dtype, void* host_plan);
+int shvk_gdn_inproj(const void* host_plan, int B, void* stream);
+/* Gated delta rule + gated RMSNorm of one mixer over B clips from the PT tiles: 16-token chunks in WY form on the
+ * tensor cores, the head's 64 x 128 state in accumulator fragments for the whole sequence.  on: [B*321][768] in
+ * on_dtype (bf16 or fp16).  Replaces launch_delta + launch_gated_norm (engine/cuda/seq.cu:107-214,364-371). */
+int shvk_gdn_scan_t(const void* pt, const float* o_norm_w, void* on, int on_dtype, int B, void* stream);
+/* Test launch of the same kernel: no CTA ever issues the copy of its first chunk, so the wait for it runs out after
+ * `polls` polls, the status word is set and every CTA returns without writing. */
+int shvk_gdn_scan_t_starved(const void* pt, const float* o_norm_w, void* on, int on_dtype, int B, int polls, void* stream);
 
 /* Fused GatedDeltaNet core of one mixer over B clips: causal short conv (k=4, bias) + SiLU on q|k|v, L2 norm of q
  * (then * 0.125) and k, decay = exp(-exp(A_log) * softplus(a + dt_bias)), beta = sigmoid(b), the gated delta rule

@@ -82,6 +82,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shv_cuda_host_free": (None, [vp]),
         "shv_cuda_b200_upload_tokens": (i32, [vp, vp, sz, vp]),
         "shv_cuda_b200_launches_per_batch": (i32, [vp]),
+        "shv_cuda_b200_test_starve": (i32, [vp, i32, i32]),
         "shvb_engine_create": (vp, [C.c_char_p, C.c_char_p, i32, i32, i32]),
         "shvb_engine_create_ex": (vp, [C.c_char_p, C.c_char_p, i32, i32, i32, i32]),
         "shvb_engine_destroy": (None, [vp]),
@@ -98,6 +99,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvb_engine_window_bucket": (i32, [vp, i32]),
         "shvb_engine_launches": (i32, [vp]),
         "shvb_engine_status": (i32, [vp]),
+        "shvb_engine_test_starve": (i32, [vp, i32, i32]),
         "shvb_engine_bytes": (sz, [vp, i32]),
         "shvb_engine_set_dump_dir": (i32, [vp, C.c_char_p]),
         "shvb_engine_profile": (i32, [vp, i32, i32, vp, vp, i32, C.c_char_p, i32]),
@@ -108,6 +110,16 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_gemm_tc": (i32, [vp, vp]),
         "shvk_gemm_tc_rows": (i32, [vp, i32, vp]),
         "shvk_gemm_tc_status": (i32, [C.POINTER(i32)]),
+        "shvk_gemm_tc_rows_starved": (i32, [vp, i32, i32, vp]),
+        "shvk_status_fetch_async": (i32, [vp, vp]),
+        "shvk_status_clear_async": (i32, [vp]),
+        "shvk_gdn_inproj_rows": (i32, []),
+        "shvk_gdn_inproj_row_order": (None, [vp]),
+        "shvk_gdn_pt_bytes": (sz, [i32]),
+        "shvk_gdn_inproj_plan": (i32, [vp, C.c_longlong, vp, vp, vp, vp, vp, vp, i32, vp]),
+        "shvk_gdn_inproj": (i32, [vp, i32, vp]),
+        "shvk_gdn_scan_t": (i32, [vp, vp, vp, i32, i32, vp]),
+        "shvk_gdn_scan_t_starved": (i32, [vp, vp, vp, i32, i32, i32, vp]),
         "shvk_gdn_scan": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp]),
         "shvk_gdn_scan_status": (i32, [C.POINTER(i32)]),
         "shvk_gdn_chunked": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, vp]),
@@ -198,6 +210,11 @@ class CudaModel:
 
     def launches_per_batch(self):
         return self.L.shv_cuda_b200_launches_per_batch(self.m)
+
+    def test_starve(self, kind, batches=1):
+        """Test hook of the experimental library: the next GPU batches starve one launch (1 GEMM, 2 scan)."""
+        if self.L.shv_cuda_b200_test_starve(self.m, kind, batches):
+            raise RuntimeError(last_error(self.L))
 
     # ---- synchronous
     def classify(self, tokens, out=None):

@@ -105,6 +105,7 @@ struct HostSide {                            // pinned companions of one engine 
     float* tokens_out = nullptr;             // [max_frames][6144], allocated on first unpinned tokens_out
     int32_t* fstore = nullptr;               // [max_frames] token slot per encoded frame
     int32_t* d_fstore = nullptr;             // device copy
+    int* status = nullptr;                   // [SHVK_STATUS_WORDS] the kernels' status words as of the end of the batch
     cudaEvent_t copied = nullptr, start = nullptr, end = nullptr;
 };
 
@@ -138,6 +139,7 @@ public:
             if (h.tokens_out) cudaFreeHost(h.tokens_out);
             if (h.fstore) cudaFreeHost(h.fstore);
             if (h.d_fstore) cudaFree(h.d_fstore);
+            if (h.status) cudaFreeHost(h.status);
             for (cudaEvent_t e : {h.copied, h.start, h.end})
                 if (e) cudaEventDestroy(e);
         }
@@ -168,6 +170,8 @@ public:
             cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.logits), Bm * 4, cudaHostAllocDefault), "pinned alloc");
             cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.fstore), size_t(opt.max_frames) * 4, cudaHostAllocDefault), "pinned alloc");
             cuda_ok(cudaMalloc(reinterpret_cast<void**>(&h.d_fstore), size_t(opt.max_frames) * 4), "device alloc");
+            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.status), SHVK_STATUS_WORDS * sizeof(int), cudaHostAllocDefault), "pinned alloc");
+            std::memset(h.status, 0, SHVK_STATUS_WORDS * sizeof(int));
             cuda_ok(cudaEventCreateWithFlags(&h.copied, cudaEventDisableTiming), "event");
             cuda_ok(cudaEventCreate(&h.start), "event");
             cuda_ok(cudaEventCreate(&h.end), "event");
@@ -178,7 +182,10 @@ public:
         }
         device_bytes = engine->weight_bytes() + engine->activation_bytes() +
                        size_t(ec.slots) * (engine->slot_bytes() + Hm * 4 + size_t(opt.max_frames) * 4) + size_t(std::max(opt.token_slots, 0)) * kBlockBytes;
+#ifdef SHV_CUDA_EXPERIMENTAL
+        // test hook of the experimental library only: the certificate-checked library reads no environment
         if (const char* e = std::getenv("SHV_CUDA_FAIL_EVERY")) fail_every = std::atol(e);
+#endif
         cuda_ok(cudaDeviceSynchronize(), "init");
         worker_ = std::thread([this] { loop(); });
     }
@@ -190,6 +197,15 @@ public:
         }
         wake_.notify_all();
         if (worker_.joinable()) worker_.join();
+    }
+
+    // Test hook: the worker arms the engine before its next batch (the engine has one driver thread).
+    void request_starve(int kind, int batches) {
+        if (kind != 1 && kind != 2) throw std::runtime_error("starve kind: 1 = tensor-core GEMM, 2 = scan");
+        if (mode == "fp32") throw std::runtime_error("the starved test launches exist for the 16-bit modes only");
+        std::lock_guard<std::mutex> lk(mu_);
+        starve_kind_ = kind;
+        starve_batches_ = batches;
     }
 
     // Host token blocks one batch may carry: the option's limit, and what a slot's device staging area holds.
@@ -213,6 +229,7 @@ private:
     std::condition_variable wake_;
     std::deque<shv_cuda_job*> queue_;
     bool stopping_ = false;
+    int starve_kind_ = 0, starve_batches_ = 0;
     std::thread worker_;
     long batches_ = 0;
 
@@ -372,6 +389,7 @@ private:
                 cuda_ok(cudaMemcpyAsync(dst, d.d_tokens + size_t(j->frame_off) * kBlockFloats, j->n_frames * kBlockBytes,
                                         cudaMemcpyDeviceToHost, compute_), "token download");
             }
+            cuda_ok(cudaError_t(shvk_status_fetch_async(h.status, compute_)), "status fetch");
             cuda_ok(cudaEventRecord(h.end, compute_), "event");
             b.windows = windows;
             b.frames = frames;
@@ -392,9 +410,16 @@ private:
                 b.error = std::string("CUDA error: ") + cudaGetErrorString(e);
             } else {
                 if (cudaEventElapsedTime(&gpu_ms, h.start, h.end) != cudaSuccess) { cudaGetLastError(); gpu_ms = 0.0f; }
-                if (engine->device_status() != 0) {
+                bool gave_up = false;
+                for (int i = 0; i < SHVK_STATUS_WORDS; ++i) gave_up |= h.status[i] != 0;
+                if (gave_up) {
+                    // The words are shared by everything on this device: clear them behind the work already queued, so
+                    // that batches launched from now on are judged on their own.  A batch that was already in flight
+                    // fetched the set words and fails too.
                     b.failed = true;
                     b.error = "a kernel gave up waiting on its TMA / tensor-core pipeline (device status word set)";
+                    if (shvk_status_clear_async(compute_) != 0) cudaGetLastError();
+                    cudaStreamSynchronize(compute_);
                 }
             }
         } else {
@@ -436,6 +461,10 @@ private:
                         });
                     }
                     coalesce(jobs);
+                    if (!jobs.empty() && starve_batches_ > 0) {
+                        engine->inject_wait_timeout(starve_kind_, starve_batches_);
+                        starve_batches_ = 0;
+                    }
                 }
             }
             if (!jobs.empty()) {
@@ -806,5 +835,19 @@ int shv_cuda_b200_upload_tokens(shv_cuda_model* m, const float* tokens, size_t n
 }
 
 int shv_cuda_b200_launches_per_batch(const shv_cuda_model* m) { return m ? m->sched->engine->launches_per_classify() : 0; }
+
+int shv_cuda_b200_test_starve(shv_cuda_model* m, int kind, int batches) {
+#ifdef SHV_CUDA_EXPERIMENTAL
+    return guarded([&]() -> int {
+        if (!m) throw std::runtime_error("null model");
+        m->sched->request_starve(kind, batches);
+        return 0;
+    });
+#else
+    (void)m; (void)kind; (void)batches;
+    t_error = "test hooks exist in the experimental library only";
+    return -1;
+#endif
+}
 
 }  // extern "C"

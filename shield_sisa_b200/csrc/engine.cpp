@@ -110,6 +110,7 @@ std::vector<uint8_t> to_storage(const std::vector<float>& v, Precision p) {
 struct GdnDev {
     const float *norm_w, *ffn_norm_w, *conv_w, *conv_b, *a_log, *dt_bias, *o_norm_w;
     const void *in_w, *o_proj, *ffn_up, *ffn_down;   // storage type
+    const void* in_w_perm = nullptr;                 // 16-bit modes: in_w rows in the channel-tile order of the fused in-projection
 };
 
 struct CnnBlockDev {
@@ -160,6 +161,11 @@ public:
         if (B <= 0) return;
         if (slot < 0 || slot >= cfg_.slots) throw std::runtime_error("classify: bad slot");
         if (B > cfg_.max_windows) throw std::runtime_error("classify: too many windows");
+        if (starve_batches_ > 0) {                      // test hook: this batch runs eagerly with one starved launch
+            --starve_batches_;
+            run(slot, B, s, starve_kind_);
+            return;
+        }
         if (!cfg_.use_graphs || !dump_dir_.empty()) { run(slot, B, s); return; }
         const int n = class_of(wbuckets_, B);
         launch_graph(((long long)slot << 32) | (long long)n, s, [&](cudaStream_t cs) { run(slot, n, cs); });
@@ -170,6 +176,12 @@ public:
         if (shvk_gdn_scan_status(&scan) != 0) return -1;
         if (prec_ != Precision::FP32 && shvk_gemm_tc_status(&gemm) != 0) return -1;
         return scan ? 16 + scan : gemm;
+    }
+    void inject_wait_timeout(int kind, int batches) override {
+        if (prec_ == Precision::FP32) throw std::runtime_error("the starved test launches exist for the 16-bit modes only");
+        if (kind != 1 && kind != 2) throw std::runtime_error("starve kind: 1 = tensor-core GEMM, 2 = scan");
+        starve_kind_ = kind;
+        starve_batches_ = batches > 0 ? batches : 0;
     }
     int launches_per_classify() const override { return 28; }
 
@@ -203,6 +215,8 @@ private:
     void *xn_ = nullptr, *on_ = nullptr, *hid_ = nullptr;
     float *xl_ = nullptr, *qc_ = nullptr, *y_ = nullptr, *x1_ = nullptr, *x2_ = nullptr, *hidl_ = nullptr;
     Site in_[2], oproj_[2], up_[2], down_[2], sisa_in_;
+    alignas(64) unsigned char inproj_plan_[2][512];   // 16-bit modes: fused in-projection (TMA maps for xn, W', PT = P_)
+    int starve_kind_ = 0, starve_batches_ = 0;        // test hook: see inject_wait_timeout
     // frame encoder
     CnnHost cnn_;
     const float *lut_ = nullptr, *stem_w_ = nullptr, *stem_b_ = nullptr, *last_w_ = nullptr, *last_b_ = nullptr, *tokproj_ = nullptr;
@@ -303,7 +317,20 @@ private:
             f32(&g.norm_w, gh[i]->norm_w); f32(&g.ffn_norm_w, gh[i]->ffn_norm_w);
             f32(&g.conv_w, gh[i]->conv_w); f32(&g.conv_b, gh[i]->conv_b);
             f32(&g.a_log, gh[i]->a_log); f32(&g.dt_bias, gh[i]->dt_bias); f32(&g.o_norm_w, gh[i]->o_norm_w);
-            stor(&g.in_w, gh[i]->in_w); stor(&g.o_proj, gh[i]->o_proj);
+            if (prec_ == Precision::FP32) {
+                stor(&g.in_w, gh[i]->in_w);
+            } else {
+                // rows of [q | k | v | gate | a | b] regrouped per head into the 128-row channel tiles of the fused
+                // in-projection kernel; rows it does not use are zero
+                const size_t perm_rows = size_t(shvk_gdn_inproj_rows());
+                std::vector<int32_t> order(perm_rows, -1);
+                shvk_gdn_inproj_row_order(order.data());
+                std::vector<float> perm(order.size() * D, 0.0f);
+                for (size_t r = 0; r < order.size(); ++r)
+                    if (order[r] >= 0) std::memcpy(&perm[r * D], &gh[i]->in_w[size_t(order[r]) * D], D * sizeof(float));
+                stor(&g.in_w_perm, perm);
+            }
+            stor(&g.o_proj, gh[i]->o_proj);
             stor(&g.ffn_up, gh[i]->ffn_up); stor(&g.ffn_down, gh[i]->ffn_down);
         }
         const SisaHost& sh = hm.sisa;
@@ -392,7 +419,7 @@ private:
         const float inv_div[2] = {1.0f, float(std::sqrt(2.0))};
         for (int i = 0; i < 2; ++i) {
             const GdnDev& g = gdn_[i];
-            make_site(in_[i], GN, D, xn_, g.in_w, P_, GLD, SHVK_F32);
+            if (prec_ == Precision::FP32) make_site(in_[i], GN, D, xn_, g.in_w, P_, GLD, SHVK_F32);
             make_site(oproj_[i], D, VD, on_, g.o_proj, h_, D, SHVK_F32);
             oproj_[i].args.R = h_; oproj_[i].args.ldr = D; oproj_[i].args.r_div = inv_div[i];
             make_site(up_[i], 2 * DFF, D, xn_, g.ffn_up, hid_, DFF, dt_);
@@ -403,10 +430,16 @@ private:
         make_site(sisa_in_, SN, D, xn_, s_w_all_, P_, SLD, SHVK_F32);
         sisa_in_.args.bias = s_b_all_;
         if (prec_ == Precision::FP32) return;
-        for (Site* st : {&in_[0], &in_[1], &oproj_[0], &oproj_[1], &up_[0], &up_[1], &down_[0], &down_[1], &sisa_in_}) {
+        for (Site* st : {&oproj_[0], &oproj_[1], &up_[0], &up_[1], &down_[0], &down_[1], &sisa_in_}) {
             launch_ok(shvk_gemm_tc_plan(&st->args, dt_, st->plan), "tensor-core GEMM plan");
             st->planned = true;
         }
+        // the chunk-blocked operand tiles of the in-projection live where the fp32 projection of the exact tier would
+        if (shvk_gdn_pt_bytes(cfg_.max_windows) > size_t(cfg_.max_windows) * NTOK * GLD * 4)
+            throw std::runtime_error("projection buffer too small for the operand tiles");
+        for (int i = 0; i < 2; ++i)
+            launch_ok(shvk_gdn_inproj_plan(xn_, (long long)cfg_.max_windows * NTOK, gdn_[i].in_w_perm, gdn_[i].conv_w, gdn_[i].conv_b,
+                                           gdn_[i].a_log, gdn_[i].dt_bias, P_, dt_, inproj_plan_[i]), "in-projection plan");
     }
     void rows_gemm(const Site& st, int rows, cudaStream_t s) {
         if (st.planned) {
@@ -509,7 +542,7 @@ private:
     }
 
     // ---------------------------------------------------------------- the launch sequence
-    void run(int slot, int B, cudaStream_t s) {
+    void run(int slot, int B, cudaStream_t s, int starve = 0) {
         const Slot& sl = slots_[size_t(slot)];
         const int M = B * NTOK;
         launch_ok(shvk_assemble_norm(sl.d_tokptr, pos_, readout_, gdn_[0].norm_w, h_, xn_, dt_, B, s), "assemble");
@@ -519,12 +552,25 @@ private:
             const GdnDev& g = gdn_[st];
             const int reps = st == 0 ? 1 : 2;
             for (int r = 0; r < reps; ++r) {
-                rows_gemm(in_[st], M, s);
-                mark("gemm.in_proj", s);
-                launch_ok(shvk_gdn_scan(P_, g.conv_w, g.conv_b, g.a_log, g.dt_bias, g.o_norm_w, on_, dt_, B, s), "gdn scan");
+                if (prec_ == Precision::FP32) {
+                    rows_gemm(in_[st], M, s);
+                    mark("gemm.in_proj", s);
+                    launch_ok(shvk_gdn_scan(P_, g.conv_w, g.conv_b, g.a_log, g.dt_bias, g.o_norm_w, on_, dt_, B, s), "gdn scan");
+                } else {
+                    // projection + conv + SiLU + gates in one tensor-core kernel, bf16 operand tiles for the scan
+                    launch_ok(shvk_gdn_inproj(inproj_plan_[st], B, s), "gdn in-projection");
+                    mark("gdn_inproj", s);
+                    if (starve == 2 && st == 0 && r == 0)
+                        launch_ok(shvk_gdn_scan_t_starved(P_, g.o_norm_w, on_, dt_, B, 2048, s), "gdn scan (starved test launch)");
+                    else
+                        launch_ok(shvk_gdn_scan_t(P_, g.o_norm_w, on_, dt_, B, s), "gdn scan");
+                }
                 mark("gdn_scan", s);
                 if (st == 0) dump("gdn_a.o_gated", on_, size_t(NTOK) * VD, dt_, s);
-                rows_gemm(oproj_[st], M, s);
+                if (starve == 1 && st == 0 && r == 0)
+                    launch_ok(shvk_gemm_tc_rows_starved(oproj_[st].plan, M, 2048, s), "tensor-core GEMM (starved test launch)");
+                else
+                    rows_gemm(oproj_[st], M, s);
                 mark("gemm.o_proj", s);
                 const float* next_norm = r + 1 < reps ? g.norm_w : g.ffn_norm_w;
                 launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_, dt_, D, M, s), "rmsnorm");

@@ -61,6 +61,10 @@ public:
     void set_dump_dir(const std::string& dir) { dump_dir_ = dir; }
     // Nonzero once a bounded wait inside a tensor-core kernel gave up; results of that batch are invalid.
     virtual int device_status() const = 0;
+    // Test hook (16-bit modes): the next `batches` classify calls run eagerly and give one launch no input, so that its
+    // bounded wait runs out, the kernel sets its status word and returns (kind 1: the tensor-core GEMM of the first
+    // output projection, 2: the first scan).  Nothing faults or spins without bound; the batch's results are invalid.
+    virtual void inject_wait_timeout(int kind, int batches) = 0;
     // Kernels launched by one classify of B windows (for launch accounting in benchmarks).
     virtual int launches_per_classify() const = 0;
     // One eager classify of B windows with a CUDA event after every launch: (kernel name, milliseconds) per launch,

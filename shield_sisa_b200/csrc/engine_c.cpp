@@ -64,8 +64,12 @@ int shvb_engine_bind_tokens(shvb_engine* e, int slot, const float* d_tokens, int
     return guard([&] {
         if (!e || !d_tokens || slot < 0 || slot >= e->eng->slots() || B < 1 || B > e->eng->max_windows())
             throw std::runtime_error("bind_tokens: bad argument");
-        e->table.resize(size_t(B) * 20);
-        for (size_t i = 0; i < e->table.size(); ++i) e->table[i] = d_tokens + i * SHV_CUDA_TOKEN_FLOATS;
+        // With graphs on, classify pads B up to its size class and the padding windows read the table too: point them
+        // at memory the engine owns, so that no entry outlives a buffer the caller bound earlier and has freed since.
+        const int padded = e->eng->window_bucket(B);
+        e->table.resize(size_t(padded) * 20);
+        for (size_t i = 0; i < size_t(B) * 20; ++i) e->table[i] = d_tokens + i * SHV_CUDA_TOKEN_FLOATS;
+        for (size_t i = size_t(B) * 20; i < e->table.size(); ++i) e->table[i] = e->eng->slot(slot).d_tokens;
         cuda_ok(cudaMemcpyAsync(e->eng->slot(slot).d_tokptr, e->table.data(), e->table.size() * sizeof(float*),
                                 cudaMemcpyHostToDevice, cudaStream_t(stream)), "pointer table upload");
         cuda_ok(cudaStreamSynchronize(cudaStream_t(stream)), "pointer table upload");   // the host table is reused
@@ -115,6 +119,12 @@ int shvb_engine_window_bucket(const shvb_engine* e, int B) {
 }
 int shvb_engine_launches(const shvb_engine* e) { return e ? e->eng->launches_per_classify() : 0; }
 int shvb_engine_status(const shvb_engine* e) { return e ? e->eng->device_status() : -1; }
+int shvb_engine_test_starve(shvb_engine* e, int kind, int batches) {
+    return guard([&] {
+        if (!e) throw std::runtime_error("null engine");
+        e->eng->inject_wait_timeout(kind, batches);
+    });
+}
 size_t shvb_engine_bytes(const shvb_engine* e, int which) {
     if (!e) return 0;
     return which == 0 ? e->eng->weight_bytes() : which == 1 ? e->eng->activation_bytes() : e->eng->slot_bytes();

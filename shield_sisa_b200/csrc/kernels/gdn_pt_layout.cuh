@@ -1,0 +1,23 @@
+// Layout of the chunk-blocked, transposed GDN projection ("PT") that the fused in-projection kernel (gdn_inproj.cu)
+// writes and the 16-bit scan (gdn_scan_t.cu) reads.  Per clip and head the 321 tokens are padded to 21 chunks of 16;
+// one chunk block is 12,416 contiguous bytes, so the scan fetches a chunk with a single bulk copy:
+//
+//   offset     0   q^T  [64 keys  ][16 tokens] bf16   silu(conv(q projection)), not yet L2-normalised
+//           2048   k^T  [64 keys  ][16 tokens] bf16   silu(conv(k projection)), not yet L2-normalised
+//           4096   v^T  [128 values][16 tokens] bf16  silu(conv(v projection))
+//           8192   g^T  [128 values][16 tokens] bf16  silu(output-gate projection)
+//          12288   log decay [16] fp32                -exp(A_log) * softplus(a + dt_bias)
+//          12352   beta      [16] fp32                sigmoid(b)
+//
+// Blocks are ordered [clip][head][chunk].  Token slots 321 .. 335 of a clip hold zeros in every section, which makes
+// them inert in the recurrence (beta 0, no decay, zero keys and values) whatever the neighbouring clips contain.
+#pragma once
+
+namespace sb {
+namespace pt {
+constexpr int CHUNK = 16, NCHUNK = 21, TOK_PAD = CHUNK * NCHUNK;
+constexpr int Q_OFF = 0, K_OFF = 2048, V_OFF = 4096, G_OFF = 8192, DEC_OFF = 12288, BETA_OFF = 12352, BLOCK_BYTES = 12416;
+constexpr long long HEAD_BYTES = (long long)NCHUNK * BLOCK_BYTES, CLIP_BYTES = 6 * HEAD_BYTES;
+static_assert(BLOCK_BYTES % 128 == 0, "chunk blocks stay 128-byte aligned");
+}  // namespace pt
+}  // namespace sb

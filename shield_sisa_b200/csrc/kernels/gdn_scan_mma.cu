@@ -39,6 +39,7 @@
 
 #include "device_utils.cuh"
 #include "gdn_scan_mma.cuh"
+#include "status_words.cuh"
 #include "tma_utils.cuh"
 
 namespace sb {
@@ -560,6 +561,12 @@ int launch_gdn_scan_mma(const float* P, const float* conv_w, const float* conv_b
         return int(cudaErrorInvalidValue);
     }
     return int(cudaGetLastError());
+}
+
+int* gdn_scan_mma_status_word() {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_scan_mma_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return p;
 }
 
 int gdn_scan_mma_status(int* status_out) {

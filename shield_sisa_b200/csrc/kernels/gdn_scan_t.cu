@@ -1,0 +1,454 @@
+// Gated delta rule + gated RMSNorm for the 16-bit modes, fed by the chunk-blocked bf16 operand tiles of the fused
+// in-projection (gdn_inproj.cu, layout in gdn_pt_layout.cuh): the delta rule in chunks of 16 tokens on the tensor cores.
+//
+// One CTA (four warps) owns one (clip, head) and walks its 21 chunk blocks.  A block (q^T, k^T, v^T, gate^T tiles,
+// log decays, betas: 12,416 contiguous bytes) arrives by ONE bulk copy into a three-slot ring, two chunks ahead.
+// Nothing is converted or re-laid-out here: every operand fragment of the chunk's products comes straight out of the
+// landed tiles with ldmatrix (transposing where the product wants tokens along the contraction).
+//
+// For a chunk with inclusive cumulative log decay c_i, e_i = exp(c_i), state S0 (keys x values) entering the chunk:
+//     A = K K^T, B = Q K^T                                      (16 x 16, contraction over the 64 keys)
+//     L_ij = beta_i exp(c_i - c_j) A_ij (j < i),  T = (I + L)^-1,  T2 = T diag(beta),  M_ij = exp(c_i - c_j) B_ij (j <= i)
+//     R = K S0,  QS = Q S0                                       (16 x 128)
+//     U = T2 (V - diag(e) R)                                    (16 x 128)
+//     O = M U + diag(e) QS
+//     S' = e_16 S0 + K^T diag(exp(c_16 - c_j)) U
+// Everything is computed transposed (value dimension = MMA rows): warp w owns value columns 32w .. 32w+31, keeps its
+// slice of S^T (32 x 64, fp32) as the accumulator fragments of mma.sync.m16n8k16 for the whole sequence, and the
+// accumulator layout of one product is exactly the A-operand layout of the next, so every hand-over is a register
+// repack.  Only T2 and M pass through shared memory (written by warps 0 and 1, read as B fragments by all).  k and q
+// arrive un-normalised; their L2 norms are the diagonals of the Gram products K K^T and Q Q^T and enter as per-token
+// scalars.  The 16 x 16 triangular inverse is a 16-lane forward substitution in fp32.  Operands are bf16, the state
+// and all accumulation fp32.
+//
+// Schedule of one chunk (two CTA barriers): warps 0 / 1 Gram products, masks, inverse, while warps 1-3 finish the
+// PREVIOUS chunk (its o tile times rstd and the norm weight -> `on`); all warps R and Q S0 | barrier | U, O (times the
+// output gate, into the o tile), state update, each warp's share of sum(o^2) | barrier.
+//
+// Token slots past the end of the clip hold zeros in every tile (the producer writes them), which makes them inert:
+// beta = 0, no decay, zero keys and values.  Their output rows are not stored.
+//
+// Warp-level mma.sync rather than tcgen05: per 16-token chunk the products form a dependency chain five deep on tiles of
+// 16 tokens; tcgen05 needs M >= 64 rows and an asynchronous issue / commit / tensor-memory round trip per link of that
+// chain, which costs more than the products themselves.  tcgen05 carries the projections (gemm_tc.cu, gdn_inproj.cu).
+//
+// Reference: engine/cuda/seq.cu:107-214 (delta + gated_norm), oracle/shieldv_ref.py:121-163.
+#include <type_traits>
+
+#include "device_utils.cuh"
+#include "gdn_pt_layout.cuh"
+#include "shv_seq_kernels.h"
+#include "status_words.cuh"
+#include "tma_utils.cuh"
+
+namespace sb {
+namespace {
+
+constexpr int TC = pt::CHUNK, NCHUNK = pt::NCHUNK, NSLOT = 3;
+constexpr uint32_t WAIT_POLLS = 1u << 22;    // about a quarter second
+constexpr int KT_PITCH = 24;                 // bf16 per row of the T2 and M tiles (48 bytes)
+constexpr int OT_PITCH = kDV + 4;            // floats per token row of the o tile: the fragment stores of a warp (eight value rows
+                                             // x four token pairs) then fall into 32 different banks
+
+__device__ int g_scan_t_status = 0;
+
+struct Block {                               // one chunk block as it lies in global memory
+    __nv_bfloat16 qt[kDK][TC], kt[kDK][TC], vt[kDV][TC], gt[kDV][TC];
+    float dec[TC], beta[TC];
+};
+static_assert(sizeof(Block) == pt::BLOCK_BYTES, "chunk block layout");
+
+struct Smem {
+    Block blk[NSLOT];                        // ring: chunk c lands in blk[c % 3]
+    float ot[TC][OT_PITCH];                  // o * gate of the chunk, [token][value]; read back by the next chunk's norm
+    float lf[TC][TC];                        // L
+    __nv_bfloat16 t2[TC][KT_PITCH];          // (I + L)^-1 diag(beta)
+    __nv_bfloat16 mq[TC][KT_PITCH];          // decay-masked Q K^T
+    float ssq[TC][4];                        // per token: each warp's share of sum(o^2) over its 32 value columns
+    float cw[2][TC];                         // c_i as warps 0 and 1 each computed it (no barrier between them)
+    float iq[TC], ik[TC];                    // 0.125/|q|, 1/|k|
+    float eg[TC], dj[TC];                    // exp(c_i), exp(c_last - c_i)
+    unsigned long long full[NSLOT];          // mbarriers: chunk block in ring slot i landed
+};
+constexpr int SMEM_BYTES = int(sizeof(Smem)) + 128;
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+// D (16x8, fp32) += A (16x16, bf16, row) * B (16x8, bf16, col)
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Four 8 x 8 bf16 matrices; lane l supplies the address of row l % 8 of matrix l / 8.  Thread (g, t) receives from
+// matrix i the pair [row g][2t, 2t + 1] (plain) or [rows 2t, 2t + 1][column g] (transposed).
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128, 3)
+gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_norm_w, T* __restrict__ on, int* __restrict__ status,
+                  uint32_t wait_polls, int starve) {
+    extern __shared__ uint8_t scan_t_smem_raw[];
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(scan_t_smem_raw) + 127) & ~uintptr_t(127));
+    const int clip = blockIdx.x / kHeads, head = blockIdx.x % kHeads;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;               // mma fragment coordinates
+    const long long row_base = (long long)clip * kTok;
+    const int dvb = warp * 32;                           // this warp's value columns
+    const uint8_t* src = ptb + (long long)blockIdx.x * pt::HEAD_BYTES;
+    // ldmatrix lane roles: matrix lane / 8, row lane % 8
+    const int lm = lane >> 3, lr = lane & 7;
+
+    // S^T slice of this warp as accumulator fragments: S[mi][nj][.] = values dvb + 16 mi + {g, g + 8}, keys 8 nj + 2t, + 1
+    float S[2][8][4];
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int nj = 0; nj < 8; ++nj)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) S[mi][nj][e] = 0.0f;
+
+    const uint32_t bars0 = tma::smem_addr(&sm.full[0]);   // + 8 * ring slot
+    auto issue = [&](int chunk) {                         // thread 0: the block of `chunk`
+        if (starve) return;
+        const uint32_t bar = bars0 + 8u * uint32_t(chunk % NSLOT);
+        tma::mbar_expect_tx(bar, uint32_t(pt::BLOCK_BYTES));
+        tma::load_bulk(tma::smem_addr(&sm.blk[chunk % NSLOT]), src + (long long)chunk * pt::BLOCK_BYTES, uint32_t(pt::BLOCK_BYTES), bar);
+    };
+    if (tid == 0) {
+        for (int i = 0; i < NSLOT; ++i) tma::mbar_init(bars0 + 8u * i, 1);
+        tma::fence_barrier_init();
+        tma::fence_proxy_async();
+        issue(0);
+        issue(1);
+    }
+    __syncthreads();
+
+    // The previous chunk's output: o tile times rstd times the norm weight, tokens first .. first + count - 1 of chunk pc.
+    // Loads and arithmetic run unconditionally (the tile rows exist), only the store is guarded.
+    auto finish_norm = [&](int pc, int first, auto count_c) {
+        constexpr int count = decltype(count_c)::value;   // compile-time, so a warp with few tokens does only their work
+        const float4 onw = __ldg(reinterpret_cast<const float4*>(o_norm_w + lane * 4));
+        const int pnt = min(min(TC, kTok - pc * TC), first + count);
+        const float* op = &sm.ot[first][lane * 4];
+        const float* sp = &sm.ssq[first][0];
+        T* dst = on + (row_base + pc * TC + first) * kVD + head * kDV + lane * 4;
+#pragma unroll
+        for (int k = 0; k < count; ++k) {
+            const float4 o = *reinterpret_cast<const float4*>(op + k * OT_PITCH);
+            const float4 pp = *reinterpret_cast<const float4*>(sp + 4 * k);   // the four warps' partial sums of o^2
+            const float rstd = rsqrtf(((pp.x + pp.y) + (pp.z + pp.w)) * (1.0f / float(kDV)) + 1e-6f);
+            if (first + k < pnt)
+                store_quad<T>(dst + k * kVD, (o.x * rstd) * onw.x, (o.y * rstd) * onw.y, (o.z * rstd) * onw.z, (o.w * rstd) * onw.w);
+        }
+    };
+
+    for (int chunk = 0; chunk < NCHUNK; ++chunk) {
+        Block& b = sm.blk[chunk % NSLOT];
+        if (tid == 0 && chunk + 2 < NCHUNK) {
+            // ring slot (chunk + 2) % 3 was last read by chunk - 1, which ended at the previous barrier
+            tma::fence_proxy_async();
+            issue(chunk + 2);
+        }
+        if (!tma::mbar_wait_bounded(bars0 + 8u * uint32_t(chunk % NSLOT), uint32_t(chunk / NSLOT) & 1u, wait_polls)) {
+            if (tid == 0) atomicCAS(status, 0, 1);
+            return;                                       // every thread times out on the same barrier and leaves
+        }
+        const uint32_t kt_s = tma::smem_addr(&b.kt[0][0]), qt_s = tma::smem_addr(&b.qt[0][0]);
+        // transposed fragment of keys 16p .. 16p+15 x all 16 tokens: matrices (keys lo, tokens 0-7), (keys lo, tokens 8-15),
+        // (keys hi, tokens 0-7), (keys hi, tokens 8-15) = A fragment of [token][key], and B fragments (r[ni], r[ni + 2])
+        const uint32_t tr_off = uint32_t(((lm >> 1) * 8 + lr) * (TC * 2) + (lm & 1) * 16);
+        // ---------------------------------------------------------------- warp 0: norms of k, L, T2; warp 1: norms of q, masked Q K^T
+        if (warp < 2) {
+            // inclusive prefix sum of the log decays, once per warp (the two warps do not wait for each other)
+            float c = b.dec[lane & (TC - 1)];
+#pragma unroll
+            for (int o = 1; o < TC; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, c, o);
+                if ((lane & (TC - 1)) >= o) c += up;
+            }
+            const float last = __shfl_sync(0xffffffffu, c, TC - 1);
+            if (lane < TC) {
+                sm.cw[warp][lane] = c;
+                if (warp == 0) {
+                    sm.eg[lane] = __expf(c);
+                    sm.dj[lane] = __expf(last - c);
+                }
+            }
+            // Gram products over the 64 keys: warp 0 K K^T; warp 1 Q K^T and the diagonal of Q Q^T
+            float acc[2][4], dq[2][4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { acc[ni][e] = 0.0f; dq[ni][e] = 0.0f; }
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                uint32_t kf[4], qf[4];
+                ldsm4t(kt_s + uint32_t(p * 16 * TC * 2) + tr_off, kf);
+                if (warp == 1) ldsm4t(qt_s + uint32_t(p * 16 * TC * 2) + tr_off, qf);
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) {
+                    if (warp == 0) {
+                        mma16816(acc[ni], kf, kf[ni], kf[ni + 2]);
+                    } else {
+                        mma16816(acc[ni], qf, kf[ni], kf[ni + 2]);
+                        mma16816(dq[ni], qf, qf[ni], qf[ni + 2]);
+                    }
+                }
+            }
+            // diagonal entries: row g sits in tile 0 at column 2t + e == g, row g + 8 in tile 1 at the same lane / slot
+            if (t == (g >> 1)) {
+                const bool odd = g & 1;                   // selects, not a runtime index: the fragments stay in registers
+                if (warp == 0) {
+                    sm.ik[g] = rsqrtf((odd ? acc[0][1] : acc[0][0]) + 1e-6f);
+                    sm.ik[g + 8] = rsqrtf((odd ? acc[1][3] : acc[1][2]) + 1e-6f);
+                } else {
+                    sm.iq[g] = rsqrtf((odd ? dq[0][1] : dq[0][0]) + 1e-6f) * 0.125f;
+                    sm.iq[g + 8] = rsqrtf((odd ? dq[1][3] : dq[1][2]) + 1e-6f) * 0.125f;
+                }
+            }
+            __syncwarp();
+            // acc[ni][0,1]: row i = g, columns j = 8 ni + 2t, + 1;  acc[ni][2,3]: row i = g + 8
+            const float* cum = sm.cw[warp];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = g + (e >> 1) * 8, j = 8 * ni + 2 * t + (e & 1);
+                    const bool keep = warp == 0 ? j < i : j <= i;
+                    const float dec = __expf(keep ? cum[i] - cum[j] : 0.0f);
+                    // warp 0: L_ij carries both key norms; warp 1: the key norm of column j is applied to U in the O product
+                    const float f = warp == 0 ? b.beta[i] * sm.ik[i] * sm.ik[j] : sm.iq[i];
+                    acc[ni][e] = keep ? dec * acc[ni][e] * f : 0.0f;
+                }
+            if (warp == 0) {
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sm.lf[g + (e >> 1) * 8][8 * ni + 2 * t + (e & 1)] = acc[ni][e];
+                __syncwarp();
+                if (lane < TC) {                          // column `lane` of (I + L)^-1 by forward substitution
+                    float x[TC];
+#pragma unroll
+                    for (int i = 0; i < TC; ++i) {
+                        // four partial sums: the dependent chain per row is i / 4 long instead of i
+                        float s0 = i == lane ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < i; ++j) {
+                            const float l = sm.lf[i][j];
+                            if ((j & 3) == 0) s0 = fmaf(-l, x[j], s0);
+                            else if ((j & 3) == 1) s1 = fmaf(-l, x[j], s1);
+                            else if ((j & 3) == 2) s2 = fmaf(-l, x[j], s2);
+                            else s3 = fmaf(-l, x[j], s3);
+                        }
+                        x[i] = (s0 + s1) + (s2 + s3);
+                    }
+                    const float bc = b.beta[lane];
+#pragma unroll
+                    for (int i = 0; i < TC; ++i) sm.t2[i][lane] = __float2bfloat16_rn(x[i] * bc);
+                }
+            } else {
+                uint32_t* mw = reinterpret_cast<uint32_t*>(&sm.mq[0][0]);        // 12 words per row
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) {
+                    mw[g * 12 + 4 * ni + t] = pack_bf16(acc[ni][0], acc[ni][1]);
+                    mw[(g + 8) * 12 + 4 * ni + t] = pack_bf16(acc[ni][2], acc[ni][3]);
+                }
+            }
+        }
+        // meanwhile the previous chunk is finished: seven tokens each on warps 2 and 3 and two behind the Gram work of
+        // warp 1 (warp 0 has the inverse)
+        if (chunk > 0) {
+            if (warp == 1) finish_norm(chunk - 1, 14, std::integral_constant<int, 2>());
+            else if (warp >= 2) finish_norm(chunk - 1, 7 * (warp - 2), std::integral_constant<int, 7>());
+        }
+        // ---------------------------------------------------------------- R^T = S0^T K^T and (Q S0)^T, all warps
+        float R[2][2][4], QS[2][2][4];
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { R[mi][ni][e] = 0.0f; QS[mi][ni][e] = 0.0f; }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            uint32_t bk[4], bq[4];
+            ldsm4t(kt_s + uint32_t(p * 16 * TC * 2) + tr_off, bk);
+            ldsm4t(qt_s + uint32_t(p * 16 * TC * 2) + tr_off, bq);
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi) {
+                // keys 16p .. 16p+15 of the state as an A fragment: two adjacent accumulator tiles, rounded to bf16
+                const uint32_t sa[4] = {pack_bf16(S[mi][2 * p][0], S[mi][2 * p][1]), pack_bf16(S[mi][2 * p][2], S[mi][2 * p][3]),
+                                        pack_bf16(S[mi][2 * p + 1][0], S[mi][2 * p + 1][1]),
+                                        pack_bf16(S[mi][2 * p + 1][2], S[mi][2 * p + 1][3])};
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) {
+                    mma16816(R[mi][ni], sa, bk[ni], bk[ni + 2]);
+                    mma16816(QS[mi][ni], sa, bq[ni], bq[ni + 2]);
+                }
+            }
+        }
+        __syncthreads();                                  // T2, masked Q K^T, norms and decays are in shared memory; the
+                                                          // previous chunk's o tile has been read
+        // ---------------------------------------------------------------- U^T = (V - diag(e) R)^T T2^T
+        const uint32_t* t2w = reinterpret_cast<const uint32_t*>(&sm.t2[0][0]);   // 12 words per row
+        const uint32_t* mqw = reinterpret_cast<const uint32_t*>(&sm.mq[0][0]);
+        // per-token scalars of this lane's tokens 8 ni + 2t, + 1, with the norms folded in:
+        //   er = exp(c) / |k|  (R = K S0),  eq = exp(c) * 0.125 / |q|  (Q S0),  dj2 = exp(c_last - c) / |k|  (state update)
+        float er[2][2], eq[2][2], dj2[2][2], ikt[2][2];
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = 8 * ni + 2 * t + e;
+                const float egv = sm.eg[tok], ikv = sm.ik[tok];
+                er[ni][e] = egv * ikv;
+                eq[ni][e] = egv * sm.iq[tok];
+                dj2[ni][e] = sm.dj[tok] * ikv;
+                ikt[ni][e] = ikv;
+            }
+        uint32_t bt[2][2], bm[2][2];
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni) {
+            bt[ni][0] = t2w[(8 * ni + g) * 12 + t]; bt[ni][1] = t2w[(8 * ni + g) * 12 + t + 4];
+            bm[ni][0] = mqw[(8 * ni + g) * 12 + t]; bm[ni][1] = mqw[(8 * ni + g) * 12 + t + 4];
+        }
+        float sq[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};    // sum of o^2 over this thread's value rows, per token 8 ni + 2t + e
+        uint32_t da[2][4];                                // decay-scaled U^T as A fragments, for the state update
+        // every shared-memory load of this phase is issued before its first o-tile store (a store would hold back the
+        // loads behind it): V^T and gate^T for both row halves and the K^T fragments of the state update
+        // plain fragments of rows r0 .. r0+15 x 16 tokens: matrices (rows lo, tokens 0-7), (rows lo, tokens 8-15),
+        // (rows hi, tokens 0-7), (rows hi, tokens 8-15): r[ni + 2 h] = tokens 8 ni + 2t, + 1 of row r0 + 8 h + g
+        const uint32_t pl_off = uint32_t(((lm >> 1) * 8 + lr) * (TC * 2) + (lm & 1) * 16);
+        uint32_t vv[2][4], gg[2][4], kf[4][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ldsm4(kt_s + uint32_t(q * 16 * TC * 2) + pl_off, kf[q]);   // kf[q][2 h + c]: keys 16 q + 8 h + g, tokens 8 c + 2t
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+            ldsm4(tma::smem_addr(&b.vt[dvb + 16 * mi][0]) + pl_off, vv[mi]);
+            ldsm4(tma::smem_addr(&b.gt[dvb + 16 * mi][0]) + pl_off, gg[mi]);
+        }
+        float* otile = &sm.ot[0][0];
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+            const int r0 = dvb + 16 * mi + g, r1 = r0 + 8;
+            uint32_t va[4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+                const uint32_t v0 = vv[mi][ni], v1 = vv[mi][ni + 2];
+                va[2 * ni] = pack_bf16(bf_lo(v0) - er[ni][0] * R[mi][ni][0], bf_hi(v0) - er[ni][1] * R[mi][ni][1]);
+                va[2 * ni + 1] = pack_bf16(bf_lo(v1) - er[ni][0] * R[mi][ni][2], bf_hi(v1) - er[ni][1] * R[mi][ni][3]);
+            }
+            float U[2][4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) U[ni][e] = 0.0f;
+                mma16816(U[ni], va, bt[ni][0], bt[ni][1]);
+            }
+            uint32_t ua[4];
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+                ua[2 * ni] = pack_bf16(U[ni][0] * ikt[ni][0], U[ni][1] * ikt[ni][1]);      // U / |k| for the O product
+                ua[2 * ni + 1] = pack_bf16(U[ni][2] * ikt[ni][0], U[ni][3] * ikt[ni][1]);
+                da[mi][2 * ni] = pack_bf16(U[ni][0] * dj2[ni][0], U[ni][1] * dj2[ni][1]);
+                da[mi][2 * ni + 1] = pack_bf16(U[ni][2] * dj2[ni][0], U[ni][3] * dj2[ni][1]);
+            }
+            // O^T = U^T M^T + diag(e) (Q S0)^T, stored times the output gate; sum(o^2) is taken before the gate
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni) {
+                float O[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                mma16816(O, ua, bm[ni][0], bm[ni][1]);
+                const int tok = 8 * ni + 2 * t;
+                const float o00 = O[0] + eq[ni][0] * QS[mi][ni][0], o01 = O[1] + eq[ni][1] * QS[mi][ni][1];
+                const float o10 = O[2] + eq[ni][0] * QS[mi][ni][2], o11 = O[3] + eq[ni][1] * QS[mi][ni][3];
+                const uint32_t g0 = gg[mi][ni], g1 = gg[mi][ni + 2];
+                otile[tok * OT_PITCH + r0] = o00 * bf_lo(g0);
+                otile[(tok + 1) * OT_PITCH + r0] = o01 * bf_hi(g0);
+                otile[tok * OT_PITCH + r1] = o10 * bf_lo(g1);
+                otile[(tok + 1) * OT_PITCH + r1] = o11 * bf_hi(g1);
+                sq[ni][0] = fmaf(o00, o00, fmaf(o10, o10, sq[ni][0]));
+                sq[ni][1] = fmaf(o01, o01, fmaf(o11, o11, sq[ni][1]));
+            }
+        }
+        // ---------------------------------------------------------------- S^T <- e_last S^T + (diag(d) U)^T K
+        {
+            const float elast = sm.eg[TC - 1];
+#pragma unroll
+            for (int nj = 0; nj < 8; ++nj) {
+                // keys 8 nj + g: fragment kf[nj / 2], row half nj % 2; tokens 2t, + 1 (b0) and 8 + 2t, + 1 (b1)
+                const uint32_t b0 = kf[nj >> 1][2 * (nj & 1)], b1 = kf[nj >> 1][2 * (nj & 1) + 1];
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) S[mi][nj][e] *= elast;
+                    mma16816(S[mi][nj], da[mi], b0, b1);
+                }
+            }
+        }
+        // this warp's share of sum(o^2): reduce over the eight row groups g (lane bits 2-4), lanes 0-3 publish it
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float v = sq[ni][e];
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                if (g == 0) sm.ssq[8 * ni + 2 * t + e][warp] = v;
+            }
+        __syncthreads();                                  // o tile complete; the block's ring slot is free
+    }
+    finish_norm(NCHUNK - 1, 4 * warp, std::integral_constant<int, 4>());
+}
+
+template <typename T>
+int launch(const void* ptb, const float* o_norm_w, void* on, int B, uint32_t polls, int starve, cudaStream_t stream) {
+    const cudaError_t e = cudaFuncSetAttribute(gdn_scan_t_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    int* status = gdn_scan_t_status_word();
+    if (!status) return int(cudaErrorInvalidSymbol);
+    gdn_scan_t_kernel<T><<<unsigned(B) * kHeads, 128, SMEM_BYTES, stream>>>(static_cast<const uint8_t*>(ptb), o_norm_w,
+                                                                            static_cast<T*>(on), status, polls, starve);
+    return int(cudaGetLastError());
+}
+
+int launch_any(const void* ptb, const float* o_norm_w, void* on, int on_dtype, int B, uint32_t polls, int starve, void* stream) {
+    if (B <= 0) return 0;
+    if (!ptb || !o_norm_w || !on || (reinterpret_cast<uintptr_t>(ptb) & 127) || (reinterpret_cast<uintptr_t>(on) & 7))
+        return int(cudaErrorInvalidValue);
+    if (on_dtype == DT_BF16) return launch<__nv_bfloat16>(ptb, o_norm_w, on, B, polls, starve, cudaStream_t(stream));
+    if (on_dtype == DT_F16) return launch<__half>(ptb, o_norm_w, on, B, polls, starve, cudaStream_t(stream));
+    return int(cudaErrorInvalidValue);
+}
+
+}  // namespace
+
+int* gdn_scan_t_status_word() {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_scan_t_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return p;
+}
+
+}  // namespace sb
+
+extern "C" int shvk_gdn_scan_t(const void* ptb, const float* o_norm_w, void* on, int on_dtype, int B, void* stream) {
+    return sb::launch_any(ptb, o_norm_w, on, on_dtype, B, sb::WAIT_POLLS, 0, stream);
+}
+
+extern "C" int shvk_gdn_scan_t_starved(const void* ptb, const float* o_norm_w, void* on, int on_dtype, int B, int polls,
+                                       void* stream) {
+    const uint32_t lim = polls < 256 ? 256u : (uint32_t(polls) > sb::WAIT_POLLS ? sb::WAIT_POLLS : uint32_t(polls));
+    return sb::launch_any(ptb, o_norm_w, on, on_dtype, B, lim, 1, stream);
+}

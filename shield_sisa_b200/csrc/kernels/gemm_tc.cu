@@ -24,9 +24,13 @@
 // The host reads the status word (shvk_gemm_tc_status) and fails the batch.
 #include "device_utils.cuh"
 #include "shv_seq_kernels.h"
+#include "status_words.cuh"
+#include "tc_ptx.cuh"
 
 #include <cuda.h>
 #include <stdlib.h>
+
+#include <atomic>
 #include <string.h>
 
 namespace sb {
@@ -57,132 +61,22 @@ struct TcParams {
     float r_div;
     uint32_t idesc;
     int m_major;    // tile order: 1 = a CTA finishes all column tiles of a row block before its next row block
-    int probe;      // development timing probes (SHVK_TC_PROBE): 2 no epilogue work, 4 no MMA, 8 no W load, 16 no A load,
-                    // 32 column-tile-major order always, 64 padding columns left unwritten, 128 no L2 eviction hints
+    uint32_t spin_limit;   // polls before a wait gives up (SPIN_LIMIT; the starved test launch passes a small number)
+    int starve;     // test launch only: the producer withholds the first operand stage of its first tile
+    int probe;      // timing probes of a development build (see probe_bits): 2 no epilogue work, 4 no MMA, 8 no W load,
+                    // 16 no A load, 32 column-tile-major order always, 64 padding columns left unwritten, 128 no L2 hints
 };
 
-// ---------------------------------------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+// Timing probes exist only in a build compiled with -DSHVK_DEV_PROBES (never the shipped libraries): there the plan
+// takes the bits from the SHVK_TC_PROBE environment variable.  Otherwise this is the constant 0 and every probe branch
+// below is dead code, so no environment variable can change what the kernel computes.
+#ifdef SHVK_DEV_PROBES
+__host__ __device__ __forceinline__ int probe_bits(const TcParams& p) { return p.probe; }
+#else
+__host__ __device__ __forceinline__ constexpr int probe_bits(const TcParams&) { return 0; }
+#endif
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false if the phase did not complete within the poll budget or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if ((i & 63u) == 63u) {
-            if (*abort_flag) return false;
-            __nanosleep(64);
-        }
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(src) : "memory");
-}
-// L2 eviction policies for the streams of one GEMM: C (written once, never re-read by this kernel) leaves first, W
-// (re-read by every row block) leaves last, A stays on the default policy.
-__device__ __forceinline__ uint64_t policy_evict_first() {
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-__device__ __forceinline__ uint64_t policy_evict_last() {
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar, uint64_t pol) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar), "l"(pol) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, int c0, int c1, uint32_t src, uint64_t pol) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;"
-                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(src), "l"(pol) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// Waits until all but the newest N store groups of this thread have finished reading shared memory.
-template <int N> __device__ __forceinline__ void bulk_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void sts128(uint32_t addr, float a, float b, float c, float d) {
-    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-__device__ __forceinline__ void sts128u(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ float4 lds128(uint32_t addr) {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
-    return v;
-}
-
-// Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows of 128 bytes, groups of
-// 8 rows 1024 bytes apart (stride byte offset), leading byte offset unused (1), descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= uint64_t((addr & 0x3ffffu) >> 4);           // start address, bits [0,14)
-    d |= uint64_t(1) << 16;                          // leading byte offset (16-byte units), bits [16,30)
-    d |= uint64_t(1024 >> 4) << 32;                  // stride byte offset, bits [32,46)
-    d |= uint64_t(1) << 46;                          // version, bits [46,48)
-    d |= uint64_t(2) << 61;                          // SWIZZLE_128B, bits [61,64)
-    return d;
-}
-
-template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
+using namespace tc;
 
 struct TcMaps {
     CUtensorMap a, w;             // operands, 128-byte swizzle
@@ -311,12 +205,16 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             bool ok = true;
             int mt, nt;
             const uint64_t pol_w = policy_evict_last();
-            const bool hint = !(p.probe & 128);
+            const bool hint = !(probe_bits(p) & 128);
             for (long long it = 0; ok && tile_at(p, it, mt, nt); ++it) {
                 for (int kb = 0; kb < nk; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp)) { ok = false; break; }
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
+                    if (p.starve && it == 0 && kb == 0) {           // test launch: this stage never fills
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
                     const uint32_t sa = base + stage * STAGE_BYTES, sb_ = sa + A_BYTES;
-                    const bool la = !(p.probe & 16), lw = !(p.probe & 8);
+                    const bool la = !(probe_bits(p) & 16), lw = !(probe_bits(p) & 8);
                     if (la || lw) {
                         mbar_expect_tx(full_bar(stage), (la ? uint32_t(A_BYTES) : 0u) + (lw ? stage_tx - uint32_t(A_BYTES) : 0u));
                         if (la) tma_load_2d(sa, &maps.a, kb * TILE_K, mt * TILE_M, full_bar(stage));
@@ -339,17 +237,17 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             bool ok = true;
             int mt, nt;
             for (long long it = 0; ok && tile_at(p, it, mt, nt); ++it) {
-                if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abortp)) { ok = false; break; }
+                if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + uint32_t(acc * ACC_COLS);
                 for (int kb = 0; kb < nk; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abortp)) { ok = false; break; }
+                    if (!mbar_wait(full_bar(stage), phase, abortp, p.spin_limit)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = base + stage * STAGE_BYTES, sb_ = sa + A_BYTES;
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb_);
 #pragma unroll
                     for (int k = 0; k < TILE_K / 16; ++k)          // 16 elements = 32 bytes = 2 descriptor units
-                        if (!(p.probe & 4)) tc_mma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
+                        if (!(probe_bits(p) & 4)) tc_mma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
                     tc_commit(empty_bar(stage));
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -371,9 +269,9 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             rbars[i] = r_bar(ew, i);
             rphase[i] = 0u;
         }
-        const bool active = half < nblk && !(p.probe & 2);          // this warp has blocks to write
+        const bool active = half < nblk && !(probe_bits(p) & 2);          // this warp has blocks to write
         const uint64_t pol_c = policy_evict_first();
-        const bool hint = !(p.probe & 128);
+        const bool hint = !(probe_bits(p) & 128);
         uint32_t nb = 0;                                            // blocks done by this warp; tile buffer = nb % NBUF
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -389,7 +287,7 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         if (EPI == EPI_RESID && active && lane == 0 && tile_at(p, 0, mt, nt)) load_r(mt, nt, half, 0);
 
         for (long long it = 0; ok && tile_at(p, it, mt, nt); ++it) {
-            if (!mbar_wait(accf_bar(acc), acc_phase, abortp)) { ok = false; break; }
+            if (!mbar_wait(accf_bar(acc), acc_phase, abortp, p.spin_limit)) { ok = false; break; }
             tc_fence_after();
             const int m0 = mt * TILE_M + quad * 32;
             const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * ACC_COLS);
@@ -415,7 +313,7 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                             load_r(mt2, nt2, nblk2, bn_);
                         }
                     }
-                    if (!mbar_wait(rbars[b], rphase[b], abortp)) return false;
+                    if (!mbar_wait(rbars[b], rphase[b], abortp, p.spin_limit)) return false;
                     rphase[b] ^= 1u;
                 } else {
                     if (lane == 0) bulk_wait_read<NBUF - 1>();    // the store that last used this buffer has left it
@@ -532,18 +430,20 @@ int choose_bn(int n) {
 template <typename T, int EPI, typename SH> int launch_tc(const TcMaps& maps, const TcParams& p, cudaStream_t s) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
-    static unsigned long long attr_done = 0;   // one bit per device ordinal: dynamic shared memory opt-in is per device
-    if (dev < 64 && !((attr_done >> dev) & 1ull)) {
+    // one bit per device ordinal: the dynamic shared memory opt-in is per device.  Engines of several devices launch
+    // from their own threads, hence the atomic; setting the attribute twice is harmless.
+    static std::atomic<unsigned long long> attr_done{0};
+    if (dev >= 64 || !((attr_done.load(std::memory_order_acquire) >> dev) & 1ull)) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<T, EPI, SH>, cudaFuncAttributeMaxDynamicSharedMemorySize, SH::SMEM_BYTES);
         if (e != cudaSuccess) return int(e);
-        attr_done |= 1ull << dev;
+        if (dev < 64) attr_done.fetch_or(1ull << dev, std::memory_order_release);
     }
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long total = (long long)p.m_tiles * p.n_tiles;
     const unsigned grid = unsigned(total < sms ? total : sms);
     TcParams q = p;
     // whole row blocks per CTA once there are enough of them to keep every SM equally busy (under 1/8 idle at the tail)
-    q.m_major = p.n_tiles > 1 && p.m_tiles >= 8ll * grid && !(p.probe & 32);
+    q.m_major = p.n_tiles > 1 && p.m_tiles >= 8ll * grid && !(probe_bits(p) & 32);
     gemm_tc_kernel<T, EPI, SH><<<grid, SH::NTHREADS, SH::SMEM_BYTES, s>>>(maps, q);
     return int(cudaGetLastError());
 }
@@ -588,7 +488,13 @@ extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* ho
     // instruction descriptor: D fp32 (bits 4-5 = 1), A/B format (bits 7-9, 10-12), both K-major, N/8 at bit 17,
     // M/16 at bit 24
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(TILE_M >> 4) << 24);
+#ifdef SHVK_DEV_PROBES
     { const char* e = getenv("SHVK_TC_PROBE"); p.probe = e ? atoi(e) : 0; }
+#else
+    p.probe = 0;
+#endif
+    p.spin_limit = SPIN_LIMIT;
+    p.starve = 0;
     hp->C = g->C; hp->ldc = g->ldc; hp->c_dtype = g->c_dtype;
     hp->R = g->R; hp->ldr = g->ldr;
     hp->epi = epi;
@@ -599,12 +505,15 @@ extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* ho
 
 // `rows` <= the M the plan was made for; rows beyond `rows` are neither read for the residual nor written (the output
 // tensor maps are encoded for exactly `rows` rows, so the TMA stores clip there).
-extern "C" int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream) {
-    using namespace sb;
+namespace sb {
+namespace {
+int launch_rows(const void* host_plan, int rows, void* stream, int starve, uint32_t spin_limit) {
     const HostPlan* hp = static_cast<const HostPlan*>(host_plan);
     if (!hp || hp->valid != 0x5b200 || rows > hp->p.M) return int(cudaErrorInvalidValue);
     if (rows <= 0) return 0;
     TcParams p = hp->p;
+    p.starve = starve;
+    p.spin_limit = spin_limit;
     p.M = rows;
     p.m_tiles = (rows + TILE_M - 1) / TILE_M;
     TcMaps maps;
@@ -620,7 +529,7 @@ extern "C" int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream) 
         // up to seven padding columns right of N are written too where the last column tile covers them (zeros: the
         // weight rows there read as zero fill); a row that ended inside a 32-byte sector would cost a DRAM
         // read-modify-write per row
-        const bool pad = hp->epi == EPI_PLAIN && hp->ldc - p.N < 8 && hp->ldc <= (long long)p.n_tiles * p.BN && !(p.probe & 64);
+        const bool pad = hp->epi == EPI_PLAIN && hp->ldc - p.N < 8 && hp->ldc <= (long long)p.n_tiles * p.BN && !(probe_bits(p) & 64);
         const long long c_cols = pad ? hp->ldc : p.N;
         ok = make_map(&maps.c_full, hp->C, 4, rows, c_cols, hp->ldc, 32, 32, true) &&
              make_map(&maps.c_half, hp->C, 4, rows, c_cols, hp->ldc, 32, 16, false);
@@ -636,6 +545,20 @@ extern "C" int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream) 
     if (hp->c_dtype == DT_BF16) return launch_tc<__nv_bfloat16, EPI_SWIGLU, ShapeDefault>(maps, p, s);
     return launch_tc<__half, EPI_SWIGLU, ShapeDefault>(maps, p, s);
 }
+}  // namespace
+}  // namespace sb
+
+extern "C" int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream) {
+    return sb::launch_rows(host_plan, rows, stream, 0, sb::SPIN_LIMIT);
+}
+
+// Test launch: every CTA's producer withholds the first operand stage of its first tile, so the MMA role's wait on
+// that stage runs out after `polls` polls (clamped to 256 .. 2^22); the CTA then takes its abort path (status word
+// set, roles leave, copies in flight given time to land, tensor memory freed) and returns.  C is left partly written.
+extern "C" int shvk_gemm_tc_rows_starved(const void* host_plan, int rows, int polls, void* stream) {
+    const uint32_t lim = polls < 256 ? 256u : (uint32_t(polls) > sb::SPIN_LIMIT ? sb::SPIN_LIMIT : uint32_t(polls));
+    return sb::launch_rows(host_plan, rows, stream, 1, lim);
+}
 
 extern "C" int shvk_gemm_tc(const void* host_plan, void* stream) {
     const sb::HostPlan* hp = static_cast<const sb::HostPlan*>(host_plan);
@@ -649,3 +572,13 @@ extern "C" int shvk_gemm_tc_status(int* status_out) {
     if (status_out) *status_out = v;
     return int(e);
 }
+
+namespace sb {
+// Device address of this file's status word on the current device (looked up per call: it is cheap and stays right
+// across a device reset).
+int* gemm_tc_status_word() {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_tc_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return p;
+}
+}  // namespace sb

@@ -5,7 +5,7 @@ reference's PyTorch oracle (oracle/shieldv_ref.py) and, if oracle/_ref/libshield
 oracle/Makefile, also runs the reference's exact-FP32 CPU engine.  The tests read only the .npz files; inputs are
 regenerated from the seeds stored in them (shield_sisa_b200/weights.py), so no weights or tokens are committed.
 
-  python tests/golden/make_golden.py [/path/to/reference]
+  python tests/golden/make_golden.py /path/to/reference
 
 Each case file holds: recipe / seeds / batch; float64 and float32 logits of the PyTorch oracle; logits of the CPU
 engine; and (for the first two cases), for selected rows of the first and last window, float64 intermediates under the
@@ -24,7 +24,9 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py <reference checkout>")
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF / "oracle"))
 sys.path.insert(0, str(ROOT))
 

@@ -185,6 +185,30 @@ def test_failed_batch_reports_nan_and_engine_recovers(weight_files):
     m.close()
 
 
+@pytest.mark.parametrize("kind", [1, 2])
+def test_kernel_wait_that_runs_out_fails_the_batch_and_the_model_recovers(kind, weight_files):
+    """A bounded wait inside a kernel that really runs out: one launch of the next batch gets no input (kind 1: a
+    tensor-core GEMM whose producer withholds an operand stage; kind 2: the scan, whose chunk copy is never issued), its
+    poll loop hits the limit, the kernel sets the status word and returns.  The batch fails with NaN logits, the
+    scheduler clears the word, and the following batch is scored bit for bit like the one before the failure."""
+    path, _ = weight_files("W3", 1)
+    tok = W.synth_tokens(3, 31)
+    with binding.CudaModel(path, "bf16", max_windows=4, max_host_tokens=80) as m:
+        first = m.classify(tok)
+        m.test_starve(kind, 1)
+        rc, lg, err = m.classify_rc(tok)
+        assert rc == -1 and np.isnan(lg).all() and "gave up waiting" in err
+        again = m.classify(tok)
+    np.testing.assert_array_equal(again.view(np.uint32), first.view(np.uint32))
+
+
+def test_starve_hook_is_refused_where_it_does_not_apply(weight_files):
+    path, _ = weight_files("W3", 1)
+    with binding.CudaModel(path, "fp32", max_windows=2, max_host_tokens=40) as m:
+        with pytest.raises(RuntimeError, match="16-bit"):
+            m.test_starve(1, 1)
+
+
 def test_free_completes_queued_jobs(weight_files):
     path, _ = weight_files("W1", 1)
     tok = W.synth_tokens(1, 28)

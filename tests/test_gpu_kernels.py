@@ -277,6 +277,188 @@ def test_gdn_scan_matches_oracle(L, weight_files, recipe, stage, B):
             assert err < tol and rms < tol
 
 
+# ---------------------------------------------------------------------------------------------- fused in-projection + 16-bit scan
+PT_BLOCK = 12416
+
+
+def bf16_round(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
+
+
+def rounded_mixer_weights(w, stage):
+    """Copy of the weight dict whose mixer projections are exactly representable in bf16 (so the oracle and the kernel
+    multiply the same numbers)."""
+    m = f"{stage}.mixer"
+    out = dict(w)
+    for n in ("q_proj", "k_proj", "v_proj", "g_proj", "a_proj", "b_proj"):
+        out[f"{m}.{n}.weight"] = bf16_round(w[f"{m}.{n}.weight"]).astype(np.float32)
+    return out
+
+
+def run_inproj(L, w, stage, xn16, B):
+    """xn16: [B,321,384] float64 holding bf16-representable values.  Returns (PT device buffer, keep-alive list)."""
+    import torch
+    m = f"{stage}.mixer"
+    fused = np.concatenate([w[f"{m}.{n}_proj.weight"] for n in ("q", "k", "v", "g", "a", "b")]).astype(np.float32)   # [2316,384]
+    rows = L.shvk_gdn_inproj_rows()
+    order = np.full(rows, -2, np.int32)
+    L.shvk_gdn_inproj_row_order(order.ctypes.data)
+    assert sorted(order[order >= 0].tolist()) == list(range(2316))          # a permutation of the fused rows, rest zero
+    perm = np.zeros((rows, 384), np.float32)
+    perm[order >= 0] = fused[order[order >= 0]]
+    conv_w = np.concatenate([w[f"{m}.{n}_conv1d.weight"].reshape(-1, 4) for n in "qkv"]).astype(np.float32)
+    conv_b = np.concatenate([w[f"{m}.{n}_conv1d.bias"] for n in "qkv"]).astype(np.float32)
+    X = dev(xn16.reshape(B * 321, 384).astype(np.float32), torch.bfloat16)
+    Wp = dev(perm, torch.bfloat16)
+    d = [X, Wp, dev(conv_w), dev(conv_b), dev(w[f"{m}.A_log"]), dev(w[f"{m}.dt_bias"])]
+    nbytes = L.shvk_gdn_pt_bytes(B)
+    assert nbytes == B * 6 * 21 * PT_BLOCK
+    pt = torch.full((nbytes,), 0x7f, device="cuda", dtype=torch.uint8)      # poison: 0x7f7f is a large finite bf16
+    buf = (C.c_char * 1024)()
+    plan = (C.addressof(buf) + 63) & ~63
+    ok(L.shvk_gdn_inproj_plan(X.data_ptr(), B * 321, Wp.data_ptr(), d[2].data_ptr(), d[3].data_ptr(), d[4].data_ptr(),
+                              d[5].data_ptr(), pt.data_ptr(), 1, plan))
+    ok(L.shvk_gdn_inproj(plan, B, stream_ptr()))
+    sync()
+    return pt, (d, buf)
+
+
+def unpack_pt(pt, B):
+    """PT buffer -> q, k [B,6,336,64], v, g [B,6,336,128] (float64 from bf16), dec, beta [B,6,336]."""
+    import torch
+    raw = pt.cpu().numpy().reshape(B, 6, 21, PT_BLOCK)
+
+    def tile(off, rows):
+        t = np.ascontiguousarray(raw[..., off:off + rows * 32]).view(np.int16).reshape(B, 6, 21, rows, 16)
+        f = torch.from_numpy(t.copy()).view(torch.bfloat16).float().numpy().astype(np.float64)
+        return f.transpose(0, 1, 2, 4, 3).reshape(B, 6, 336, rows)
+
+    def gate(off):
+        return np.ascontiguousarray(raw[..., off:off + 64]).view(np.float32).reshape(B, 6, 336).astype(np.float64)
+
+    return tile(0, 64), tile(2048, 64), tile(4096, 128), tile(8192, 128), gate(12288), gate(12352)
+
+
+@pytest.mark.parametrize("recipe,stage,B", [("W3", "gdn_a", 2), ("W3", "gdn_b", 3), ("W1", "gdn_a", 1)])
+def test_gdn_inproj_tiles_match_oracle(L, weight_files, recipe, stage, B):
+    """The fused in-projection against the oracle's conv / SiLU / gate intermediates, on operands that are exact in
+    bf16: what is left is fp32 accumulation, the tanh-form SiLU and the bf16 rounding of the tiles."""
+    _, w0 = weight_files(recipe, 1)
+    w = rounded_mixer_weights(w0, stage)
+    xn = bf16_round(np.random.default_rng(29).standard_normal((B, 321, 384)))
+    tr = {}
+    O.gdn_mixer(w, f"{stage}.mixer", xn, tr, "t")
+    pt, keep = run_inproj(L, w, stage, xn, B)
+    q, k, v, g, dec, beta = unpack_pt(pt, B)
+    assert tc_status(L) == 0
+    for name, got, ref in (("q", q, tr["t.q_conv"]), ("k", k, tr["t.k_conv"]), ("v", v, tr["t.v_conv"]),
+                           ("gate", g, O.silu(tr["t.gate"]))):
+        ref = ref.transpose(0, 2, 1, 3)                                       # [B,6,321,*]
+        err = rel_err(got[:, :, :321], ref)
+        print(f"inproj {recipe} {stage} {name}: max-rel {err:.3e}")
+        assert err < 6e-3                                                     # bf16 rounding (2^-9) + the approximate SiLU
+        assert (got[:, :, 321:] == 0).all()                                   # padding token slots are zeros
+    assert np.abs(dec[:, :, :321] - tr["t.g"].transpose(0, 2, 1)).max() < 2e-5 * max(1.0, np.abs(tr["t.g"]).max())
+    assert np.abs(beta[:, :, :321] - tr["t.beta"].transpose(0, 2, 1)).max() < 2e-6
+    assert (dec[:, :, 321:] == 0).all() and (beta[:, :, 321:] == 0).all()
+
+
+@pytest.mark.parametrize("recipe,stage,B", [("W3", "gdn_a", 2), ("W3", "gdn_b", 1), ("W1", "gdn_a", 3)])
+def test_gdn_inproj_scan_matches_oracle(L, weight_files, recipe, stage, B):
+    """In-projection + scan of the 16-bit modes against the oracle's gated delta-rule output."""
+    import torch
+    _, w0 = weight_files(recipe, 1)
+    w = rounded_mixer_weights(w0, stage)
+    xn = bf16_round(np.random.default_rng(17).standard_normal((B, 321, 384)))
+    tr = {}
+    O.gdn_mixer(w, f"{stage}.mixer", xn, tr, "t")
+    ow = (1.0 + 0.1 * np.random.default_rng(1).standard_normal(128)).astype(np.float32)
+    ref = (tr["t.o_gated"] * ow.astype(np.float64)).reshape(B * 321, 768)
+    pt, keep = run_inproj(L, w, stage, xn, B)
+    d_ow = dev(ow)
+    for code, tdt in ((1, torch.bfloat16), (2, torch.float16)):
+        on = torch.full((B * 321 + 8, 768), 9.0, device="cuda", dtype=tdt)
+        ok(L.shvk_gdn_scan_t(pt.data_ptr(), d_ow.data_ptr(), on.data_ptr(), code, B, stream_ptr()))
+        sync()
+        st = C.c_int(-1)
+        ok(L.shvk_gdn_scan_status(C.byref(st)))
+        assert st.value == 0
+        got = on.float().cpu().numpy()
+        assert (got[B * 321:] == 9.0).all()                                   # nothing is written past the last clip
+        err = rel_err(got[:B * 321], ref)
+        rms = float(np.sqrt(((got[:B * 321] - ref) ** 2).mean() / (ref ** 2).mean()))
+        print(f"inproj+scan {recipe} {stage} dtype {code}: max-rel {err:.3e} rms-rel {rms:.3e}")
+        assert err < 2e-2 and rms < 2e-2
+
+
+def test_gdn_inproj_scan_clips_are_independent(L, weight_files):
+    """A clip's tiles and outputs are bitwise the same alone and inside a batch, whatever its neighbours hold
+    (non-finite neighbours included: the padding token slots of a clip never carry the next clip's values)."""
+    import torch
+    _, w0 = weight_files("W3", 1)
+    w = rounded_mixer_weights(w0, "gdn_a")
+    xn = bf16_round(np.random.default_rng(41).standard_normal((3, 321, 384)))
+    xn_bad = xn.copy()
+    xn_bad[2] = np.inf                                                        # the clip after clip 1 is garbage
+    ow = dev(np.ones(128, np.float32))
+    outs = []
+    for x, B, pick in ((xn_bad, 3, 1), (xn[1:2], 1, 0)):
+        pt, keep = run_inproj(L, w, "gdn_a", x, B)
+        on = torch.zeros((B * 321, 768), device="cuda", dtype=torch.bfloat16)
+        ok(L.shvk_gdn_scan_t(pt.data_ptr(), ow.data_ptr(), on.data_ptr(), 1, B, stream_ptr()))
+        sync()
+        outs.append((pt.reshape(B, -1)[pick].clone(), on.reshape(B, 321, 768)[pick].clone()))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1], outs[1][1])
+    assert torch.isfinite(outs[0][1].float()).all()
+
+
+def test_starved_launches_give_up_and_the_status_clears(L, weight_files):
+    """A bounded wait that runs out: the tensor-core GEMM and the scan are each launched once with their input withheld.
+    Each must return by itself with its status word set and nothing else disturbed; after the words are cleared the
+    same launches work normally."""
+    import torch
+    rng = np.random.default_rng(3)
+    M, N, K = 1000, 384, 768
+    a, wm = rng.standard_normal((M, K)).astype(np.float32), (rng.standard_normal((N, K)) / 30).astype(np.float32)
+    A, Wt = dev(a, torch.bfloat16), dev(wm, torch.bfloat16)
+    Cm = torch.zeros((M, N), device="cuda")
+    keep, plan = tc_plan(L, gemm_args(M, N, K, A, Wt, Cm, N), 1)
+    words = torch.zeros(8, dtype=torch.int32).pin_memory()
+
+    def fetch():
+        ok(L.shvk_status_fetch_async(words.data_ptr(), stream_ptr()))
+        sync()
+        return words[:4].tolist()
+
+    assert fetch() == [0, 0, 0, 0]
+    ok(L.shvk_gemm_tc_rows_starved(plan, M, 1024, stream_ptr()))
+    sync()                                                                    # returns: the waits are bounded
+    assert tc_status(L) != 0 and fetch()[0] != 0
+    ok(L.shvk_status_clear_async(stream_ptr()))
+    assert fetch() == [0, 0, 0, 0]
+    ok(L.shvk_gemm_tc(plan, stream_ptr()))
+    sync()
+    assert tc_status(L) == 0
+    ref = A.float().cpu().numpy().astype(np.float64) @ Wt.float().cpu().numpy().astype(np.float64).T
+    assert np.abs(Cm.cpu().numpy() - ref).max() < 1e-4
+    # the scan
+    _, w0 = weight_files("W3", 1)
+    w = rounded_mixer_weights(w0, "gdn_a")
+    xn = bf16_round(rng.standard_normal((2, 321, 384)))
+    pt, keep2 = run_inproj(L, w, "gdn_a", xn, 2)
+    ow = dev(np.ones(128, np.float32))
+    on = torch.full((2 * 321, 768), 5.0, device="cuda", dtype=torch.bfloat16)
+    ok(L.shvk_gdn_scan_t_starved(pt.data_ptr(), ow.data_ptr(), on.data_ptr(), 1, 2, 1024, stream_ptr()))
+    sync()
+    assert fetch()[3] == 1 and (on == 5.0).all()                              # gave up before writing anything
+    ok(L.shvk_status_clear_async(stream_ptr()))
+    ok(L.shvk_gdn_scan_t(pt.data_ptr(), ow.data_ptr(), on.data_ptr(), 1, 2, stream_ptr()))
+    sync()
+    assert fetch() == [0, 0, 0, 0] and torch.isfinite(on.float()).all() and not (on == 5.0).all()
+
+
 # ---------------------------------------------------------------------------------------------- SISA attention + head
 def test_sisa_attention_matches_oracle(L, weight_files):
     import torch
