@@ -33,6 +33,42 @@ int shv_cuda_b200_launches_per_batch(const shv_cuda_model* m);
  * hangs: the wait is a poll loop with a limit, the kernel's ordinary abort path is what the test exercises. */
 int shv_cuda_b200_test_starve(shv_cuda_model* m, int kind, int batches);
 
+/* ---------------------------------------------------------------- several GPUs of one box behind one object
+ * The reference's service engine owns one GPU model and gives every session a block of 24 device token slots out of
+ * that model's pool (service/src/shield_av.cpp:824-850 load, :1013-1020 slot blocks, :556-577 submit;
+ * service/include/shield_av.h:205-211).  shv_box is that for N GPUs in one process: one model per device (loaded side
+ * by side; `opt` applies to each, its token_slots is replaced by the box's own sizing), sessions placed by
+ * crc32(participant id) mod N -- spilling to the device with the most free blocks when the home device is full -- and
+ * batches of independent clips cut into contiguous per-device shards.  Nothing crosses between devices.
+ * max_sessions sizes the slot pools: each device can hold its even share of the sessions plus a quarter. */
+typedef struct shv_box shv_box;
+shv_box* shv_box_load(const char* weights, const char* mode, const int* devices, int n_devices, const shv_cuda_options* opt,
+                      int max_sessions);
+void shv_box_free(shv_box* box);                                     /* drains every device's queue first */
+int shv_box_devices(const shv_box* box);
+shv_cuda_model* shv_box_model(shv_box* box, int device_index);       /* the device's model, for queries and direct use */
+int shv_box_home_device(const shv_box* box, const char* participant_id);   /* crc32(id) mod N, before any spill */
+/* Places a session and takes a block of 24 token slots on its device: slots slot_base .. slot_base + 23 of
+ * shv_box_model(box, *device_index).  -1 with "max_sessions reached" when every device is full. */
+int shv_box_session_open(shv_box* box, const char* participant_id, int* device_index, int* slot_base);
+int shv_box_session_close(shv_box* box, int device_index, int slot_base);
+int shv_box_free_sessions(shv_box* box, int device_index);           /* free session blocks on that device */
+/* shv_cuda_submit on the session's device. */
+shv_cuda_job* shv_box_submit(shv_box* box, int device_index, const shv_cuda_request* req);
+/* shv_cuda_classify over all devices: clip i goes to device floor(i * N / b) (shard sizes differ by at most one), the
+ * shards run concurrently, logits arrive in clip order.  Bitwise the single-device result (row independence). */
+int shv_box_classify(shv_box* box, const float* tokens, size_t b, float* logits);
+/* The same box over stand-in entry points (tests drive placement, slot accounting and sharding without a GPU). */
+typedef struct shv_box_ops {
+    shv_cuda_model* (*load_ex)(const char* weights, const char* mode, int device, const shv_cuda_options* opt);
+    void (*free_model)(shv_cuda_model* m);
+    shv_cuda_job* (*submit)(shv_cuda_model* m, const shv_cuda_request* req);
+    int (*classify)(shv_cuda_model* m, const float* tokens, size_t b, float* logits);
+    const char* (*last_error)(void);
+} shv_box_ops;
+shv_box* shv_box_load_with(const shv_box_ops* ops, const char* weights, const char* mode, const int* devices, int n_devices,
+                           const shv_cuda_options* opt, int max_sessions);
+
 /* ---------------------------------------------------------------- engine core for harnesses
  * The reference's internal C++ engine API (engine/cuda/engine.hpp:20-62: make_engine, Engine::slot, Engine::classify,
  * set_dump_dir), which its kernel benchmark and dump tools compile against (bench/gpu_kbench.cu:55-103,

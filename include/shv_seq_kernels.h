@@ -124,10 +124,27 @@ int shvk_gdn_chunked(const void* q, const void* k, const void* v, const float* g
  * Replaces launch_sisa_attn (engine/cuda/seq.cu:217-306,372-374). */
 int shvk_sisa_attn(const float* S, const float* QC, const float* lambda_raw, float* Y, int B, void* stream);
 
-/* Final RMSNorm + Linear(384,128) + SiLU + Linear(128,1).  w0t: [384][128] (transposed head.0.weight).
- * Replaces launch_head (engine/cuda/seq.cu:309-336,375-378). */
-int shvk_head(const float* X, const float* norm_w, const float* w0t, const float* b0, const float* w2, const float* b2,
-              float* logits, int B, void* stream);
+/* Readout row (token 320) of the SISA block, fp32 in every mode, part 1: xl = rmsnorm(h_last) * norm_w, then
+ * QC = xl * W_qc^T.  h_last: row 320 of clip c at h_last + c * ldh (elements); wqc_t: [384][576] = [W_Q | W_C]
+ * transposed; QC: [B][576].  Replaces launch_rmsnorm + gemm<float> (engine/cuda/engine.cu:451-452). */
+int shvk_readout_qc(const float* h_last, long long ldh, const float* norm_w, const float* wqc_t, float* QC, int B, void* stream);
+/* Part 2, after the attention: x1 = h_last + Y * W_O^T; x2 = x1 + down(silu(gate(n)) * up(n)) with n = rmsnorm(x1);
+ * logit = head(rmsnorm(x2)).  All matrices transposed to [K][N] (fp32); up_t holds the (gate, up) output pairs of the
+ * SwiGLU FFN in adjacent columns (2j, 2j + 1).  Y: [B][384]; x2_out: [B][384] or NULL; logits: [B].
+ * Replaces three gemm<float>, one launch_rmsnorm and launch_head (engine/cuda/engine.cu:455-469, seq.cu:309-336). */
+typedef struct shvk_readout_weights {
+    const float* wo_t;          /* [384][384]  */
+    const float* ffn_norm_w;    /* [384]       */
+    const float* up_t;          /* [384][1920] */
+    const float* down_t;        /* [960][384]  */
+    const float* final_norm_w;  /* [384]       */
+    const float* head_w0_t;     /* [384][128]  */
+    const float* head_b0;       /* [128]       */
+    const float* head_w2;       /* [128]       */
+    const float* head_b2;       /* [1]         */
+} shvk_readout_weights;
+int shvk_readout_tail(const float* Y, const float* h_last, long long ldh, const shvk_readout_weights* w, float* x2_out,
+                      float* logits, int B, void* stream);
 
 /* pool[slots[f]] = tokens[f] (6144 floats) for slots[f] >= 0.  Replaces launch_store_tokens (seq.cu:338-351). */
 int shvk_store_tokens(const float* tokens, const int32_t* slots, float* pool, int F, void* stream);

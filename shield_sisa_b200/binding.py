@@ -39,6 +39,24 @@ class GemmArgs(C.Structure):
                 ("ldr", C.c_longlong), ("r_div", C.c_float), ("swiglu", C.c_int)]
 
 
+class ReadoutWeights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("wo_t", "ffn_norm_w", "up_t", "down_t", "final_norm_w", "head_w0_t", "head_b0",
+                                          "head_w2", "head_b2")]
+
+
+LOAD_FN = C.CFUNCTYPE(C.c_void_p, C.c_char_p, C.c_char_p, C.c_int, C.POINTER(Options))
+FREE_FN = C.CFUNCTYPE(None, C.c_void_p)
+SUBMIT_FN = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.POINTER(Request))
+CLASSIFY_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p)
+ERROR_FN = C.CFUNCTYPE(C.c_char_p)
+
+
+class BoxOps(C.Structure):
+    """shv_box_ops: the entry points a box reaches its per-device models through."""
+    _fields_ = [("load_ex", LOAD_FN), ("free_model", FREE_FN), ("submit", SUBMIT_FN), ("classify", CLASSIFY_FN),
+                ("last_error", ERROR_FN)]
+
+
 _libs: dict[bool, C.CDLL] = {}
 
 
@@ -83,6 +101,17 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shv_cuda_b200_upload_tokens": (i32, [vp, vp, sz, vp]),
         "shv_cuda_b200_launches_per_batch": (i32, [vp]),
         "shv_cuda_b200_test_starve": (i32, [vp, i32, i32]),
+        "shv_box_load": (vp, [C.c_char_p, C.c_char_p, C.POINTER(i32), i32, C.POINTER(Options), i32]),
+        "shv_box_load_with": (vp, [C.POINTER(BoxOps), C.c_char_p, C.c_char_p, C.POINTER(i32), i32, C.POINTER(Options), i32]),
+        "shv_box_free": (None, [vp]),
+        "shv_box_devices": (i32, [vp]),
+        "shv_box_model": (vp, [vp, i32]),
+        "shv_box_home_device": (i32, [vp, C.c_char_p]),
+        "shv_box_session_open": (i32, [vp, C.c_char_p, C.POINTER(i32), C.POINTER(i32)]),
+        "shv_box_session_close": (i32, [vp, i32, i32]),
+        "shv_box_free_sessions": (i32, [vp, i32]),
+        "shv_box_submit": (vp, [vp, i32, C.POINTER(Request)]),
+        "shv_box_classify": (i32, [vp, vp, sz, vp]),
         "shvb_engine_create": (vp, [C.c_char_p, C.c_char_p, i32, i32, i32]),
         "shvb_engine_create_ex": (vp, [C.c_char_p, C.c_char_p, i32, i32, i32, i32]),
         "shvb_engine_destroy": (None, [vp]),
@@ -124,7 +153,8 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_gdn_scan_status": (i32, [C.POINTER(i32)]),
         "shvk_gdn_chunked": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, vp]),
         "shvk_sisa_attn": (i32, [vp, vp, vp, vp, i32, vp]),
-        "shvk_head": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, vp]),
+        "shvk_readout_qc": (i32, [vp, C.c_longlong, vp, vp, vp, i32, vp]),
+        "shvk_readout_tail": (i32, [vp, vp, C.c_longlong, C.POINTER(ReadoutWeights), vp, vp, i32, vp]),
         "shvk_store_tokens": (i32, [vp, vp, vp, i32, vp]),
         "shvk_cnn_stem": (i32, [vp, vp, vp, vp, vp, i32, vp]),
         "shvk_cnn_depthwise": (i32, [vp, vp, vp, vp] + [i32] * 9 + [vp]),
@@ -327,6 +357,71 @@ class CudaModel:
             self.close()
         except Exception:
             pass
+
+
+class Box:
+    """shv_box_*: one model per device of a box behind one object (sessions placed by participant, batches sharded)."""
+
+    def __init__(self, weights, mode, devices, max_sessions=0, experimental=True, ops=None, **options):
+        self.L = load_library(experimental)
+        opt = Options()
+        self.L.shv_cuda_default_options(C.byref(opt))
+        for k, v in options.items():
+            if not hasattr(opt, k):
+                raise TypeError(f"unknown option {k}")
+            setattr(opt, k, int(v))
+        devs = (C.c_int * len(devices))(*devices)
+        self._ops = ops                                      # keeps the stand-in callbacks alive
+        if ops is None:
+            self.b = self.L.shv_box_load(str(weights).encode(), mode.encode(), devs, len(devices), C.byref(opt), max_sessions)
+        else:
+            self.b = self.L.shv_box_load_with(C.byref(ops), str(weights).encode(), mode.encode(), devs, len(devices),
+                                              C.byref(opt), max_sessions)
+        if not self.b:
+            raise RuntimeError(last_error(self.L))
+        self.n = len(devices)
+
+    def home_device(self, participant):
+        return self.L.shv_box_home_device(self.b, participant.encode())
+
+    def session_open(self, participant):
+        """-> (device index, first of the session's 24 token slots on that device)."""
+        d, s = C.c_int(-1), C.c_int(-1)
+        if self.L.shv_box_session_open(self.b, participant.encode(), C.byref(d), C.byref(s)):
+            raise RuntimeError(last_error(self.L))
+        return d.value, s.value
+
+    def session_close(self, device, slot_base):
+        if self.L.shv_box_session_close(self.b, device, slot_base):
+            raise RuntimeError(last_error(self.L))
+
+    def free_sessions(self, device):
+        return self.L.shv_box_free_sessions(self.b, device)
+
+    def model_handle(self, device):
+        return self.L.shv_box_model(self.b, device)
+
+    def classify(self, tokens):
+        t = np.ascontiguousarray(tokens, dtype=np.float32)
+        out = np.empty(t.shape[0], np.float32)
+        if self.L.shv_box_classify(self.b, t.ctypes.data, t.shape[0], out.ctypes.data):
+            raise RuntimeError(last_error(self.L))
+        return out
+
+    def submit(self, device, request):
+        """request: a filled binding.Request; returns the job handle (or None)."""
+        return self.L.shv_box_submit(self.b, device, C.byref(request))
+
+    def close(self):
+        if self.b:
+            self.L.shv_box_free(self.b)
+            self.b = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
 
 
 class EngineCore:

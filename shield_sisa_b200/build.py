@@ -53,9 +53,11 @@ def _run(cmd):
         raise RuntimeError("build failed: " + " ".join(map(str, cmd)) + "\n" + r.stdout + r.stderr)
 
 
-def build(force: bool = False, verbose: bool = False) -> list[Path]:
+def build(force: bool = False, verbose: bool = False, dev_probes: bool = False) -> list[Path]:
+    """dev_probes: compile the kernels with -DSHVK_DEV_PROBES (timing probes read from the environment; for
+    measurements only, never the build that is shipped or tested)."""
     cu, cpp = sources()
-    rev = revision()
+    rev = revision() + ("-probes" if dev_probes else "")
     OBJ.mkdir(parents=True, exist_ok=True)
     stamp = LIB / "revision.txt"
     libs = [LIB / "libshield_v_cuda.so", LIB / "libshield_v_cuda_experimental.so"]
@@ -66,7 +68,7 @@ def build(force: bool = False, verbose: bool = False) -> list[Path]:
     for src in cu:
         o = OBJ / (src.stem + ".cu.o")
         objs_common.append(o)
-        jobs.append([NVCC, *NVCC_FLAGS, "-c", str(src), "-o", str(o)])
+        jobs.append([NVCC, *NVCC_FLAGS, *(["-DSHVK_DEV_PROBES=1"] if dev_probes else []), "-c", str(src), "-o", str(o)])
     api_objs = {}
     for src in cpp:
         if src.name == "api.cpp":
@@ -90,4 +92,4 @@ def build(force: bool = False, verbose: bool = False) -> list[Path]:
 
 
 if __name__ == "__main__":
-    build(force="--force" in sys.argv, verbose=True)
+    build(force="--force" in sys.argv, verbose=True, dev_probes="--dev-probes" in sys.argv)

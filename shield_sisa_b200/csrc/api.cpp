@@ -1,19 +1,23 @@
-// C ABI of libshield_v_cuda.so over the sequence engine: asynchronous jobs, FIFO batch coalescing, two-slot
-// pipelining, pinned staging, NaN-on-failure.  Contract: include/shv_cuda.h; behaviour follows the reference's
-// scheduler (engine/cuda/api.cu:131-383,466-729) entry point by entry point:
-//   * jobs run in submission order; the worker coalesces queued jobs while the batch limits hold and no job stores
-//     into a token slot that an earlier job of the batch reads or stores (api.cu:208-232)
-//   * while batch n computes on the compute stream, batch n+1 is staged and copied on the copy stream into the
-//     other buffer set (api.cu:346-383)
-//   * a failed batch fails all its jobs, whose logits become NaN; a non-finite logit is reported as NaN
-//     (api.cu:177-181,334-338)
-//   * shv_cuda_job_free waits for completion and for the callback to return before deleting (api.cu:194-203,630-637)
-// Beyond the reference: host token blocks that live in pinned memory are DMA'd straight from the caller's buffer as
-// contiguous runs (the reference stages every block through a memcpy), staging buffers are allocated on first use,
-// and shv_cuda_b200_upload_tokens fills device token slots from host tokens.
-//   * frames of a request are encoded first, their tokens stored into the token slots the request names, then the
-//     windows of the batch are classified (api.cu:233-318): a window sees the frames and stores of its own request and
-//     of every earlier request
+// C ABI of libshield_v_cuda.so (contract: include/shv_cuda.h) over the engine core: an asynchronous job pipeline.
+//
+//   caller threads           feeder thread                       GPU (copy stream | compute stream)     finisher thread
+//   submit(job) -> pending   forms a batch from the head of      H2D of batch n+2 | kernels of batch n  waits for the oldest batch in
+//                            `pending`, fills a free lane,       ...                                     flight, hands results to its
+//                            enqueues copies + kernels           up to kLanes batches in flight          jobs, runs callbacks, frees the lane
+//
+// A lane is one set of buffers (an engine slot plus its pinned host companions).  With four lanes the copy engine runs
+// up to three batches ahead of the kernels, and completing a batch (callbacks included) never holds up the staging of
+// the next one.  Jobs run in submission order.  The feeder coalesces consecutive jobs while the batch limits hold and
+// no job stores into a token slot that the batch already reads or stores; while the pipeline is not yet full it also
+// closes a batch early (at an eighth of the limits), so that the first kernels of a burst start while the rest of the
+// burst is still being uploaded; and a batch never carries more than an eighth of the limits in data that has to be
+// uploaded first, so a stream of batches keeps copy engine and SMs busy together -- a single large synchronous call
+// overlaps its own uploads and kernels this way.
+// Within a batch: frames are encoded, their tokens stored into the slots the requests name, host token blocks
+// uploaded (pinned runs by DMA straight from the caller's memory, the rest through a pinned staging copy), then all
+// windows are classified together; a window sees the frames and stores of its own request and of every earlier one.
+// A batch that fails (a CUDA error, a kernel whose bounded wait gave up) fails all its jobs: their outputs become NaN;
+// a non-finite logit is reported as NaN.  shv_cuda_job_free returns only after the job's callback has.
 #include "shv_cuda.h"
 #include "shv_cuda_b200.h"
 #include "engine.hpp"
@@ -29,95 +33,152 @@
 #include <limits>
 #include <mutex>
 #include <thread>
-#include <unordered_set>
 
 #ifndef SHV_CUDA_REVISION
 #define SHV_CUDA_REVISION "unversioned"
 #endif
 
 namespace {
+
 using Clock = std::chrono::steady_clock;
-thread_local std::string t_error;
-constexpr float kNaN = std::numeric_limits<float>::quiet_NaN();
-constexpr size_t kBlockFloats = SHV_CUDA_TOKEN_FLOATS, kBlockBytes = kBlockFloats * 4, kFrameBytes = SHV_CUDA_FRAME_BYTES;
+constexpr int kLanes = 4;
+constexpr size_t kTokFloats = SHV_CUDA_TOKEN_FLOATS, kTokBytes = kTokFloats * sizeof(float), kCropBytes = SHV_CUDA_FRAME_BYTES;
+constexpr int kWin = SHV_CUDA_WINDOW_FRAMES;
+const float kUnavailable = std::numeric_limits<float>::quiet_NaN();
 
-void cuda_ok(cudaError_t e, const char* what) {
-    if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA error ") + cudaGetErrorString(e) + " in " + what);
+thread_local std::string tls_error;
+
+struct ApiError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+void check(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) throw ApiError(std::string("CUDA error ") + cudaGetErrorString(e) + " in " + what);
 }
+void check(int e, const char* what) { check(cudaError_t(e), what); }
 
-bool host_pinned(const void* p, size_t bytes) {
+// True if [p, p + bytes) starts and ends in page-locked host memory, i.e. the copy engine can read or write it directly.
+bool is_pinned(const void* p, size_t bytes) {
     if (!p || !bytes) return false;
-    for (const void* q : {p, static_cast<const void*>(static_cast<const uint8_t*>(p) + bytes - 1)}) {
-        cudaPointerAttributes a{};
-        if (cudaPointerGetAttributes(&a, q) != cudaSuccess) { cudaGetLastError(); return false; }
-        if (a.type != cudaMemoryTypeHost) return false;
+    const uint8_t* ends[2] = {static_cast<const uint8_t*>(p), static_cast<const uint8_t*>(p) + bytes - 1};
+    for (const uint8_t* q : ends) {
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, q) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        if (attr.type != cudaMemoryTypeHost) return false;
     }
     return true;
 }
 
-// A maximal run of host token blocks that are contiguous in memory, in window-entry order.
-struct HostRun {
-    const float* src;
-    int blocks;
+template <typename T> T* pinned_array(size_t n, const char* what) {
+    void* p = nullptr;
+    check(cudaHostAlloc(&p, std::max<size_t>(n, 1) * sizeof(T), cudaHostAllocDefault), what);
+    return static_cast<T*>(p);
+}
+
+// Where one window entry (window w, frame position f) of a job takes its 16 x 384 block from.
+enum class Src : uint8_t { Host, Slot, Frame };
+struct Entry {
+    Src src;
+    int32_t index;      // Slot: token slot; Frame: frame of the job's own request; Host: ordinal among the job's host blocks
+};
+// Host token blocks that follow one another in memory travel as one copy.
+struct Span {
+    const float* first;
+    int count;
     bool pinned;
 };
+
 }  // namespace
 
 struct shv_cuda_job {
-    // request
-    size_t n_windows = 0;
-    const uint8_t* frames = nullptr;        // request frames [n_frames][172800], borrowed until completion
-    size_t n_frames = 0;
-    float* tokens_out = nullptr;            // optional: tokens of the request's frames
-    bool frames_pinned = false, tokens_out_pinned = false;
-    std::vector<int32_t> frame_store;       // per frame: token slot its tokens are stored into, -1 = none (may be empty)
-    std::vector<int32_t> wframes;           // per entry: frame of this request, -1 = none (may be empty)
-    int frame_off = 0;                      // first frame of this job in its batch
-    std::vector<int32_t> wslots;            // per entry, -1 = host block or frame
-    std::vector<HostRun> runs;              // host blocks in entry order
-    int host_blocks = 0;
+    // ---- what was asked (index arrays copied, buffers borrowed)
+    const uint8_t* crops = nullptr;
+    int n_crops = 0;
+    bool crops_pinned = false;
+    float* tokens_out = nullptr;
+    bool tokens_out_pinned = false;
+    std::vector<int32_t> crop_slot;         // per crop: token slot that receives its tokens, or -1 (empty = none)
+    int n_windows = 0;
+    std::vector<Entry> entries;             // n_windows * 20
+    std::vector<Span> spans;                // the job's host blocks in entry order (or in upload order)
+    int n_host = 0;
+    std::vector<int32_t> host_slot;         // upload job: destination slot of every host block (empty otherwise)
     float* logits_out = nullptr;
-    std::vector<int32_t> store_slots;       // upload job: slot per host block
-    shv_cuda_callback cb = nullptr;
+    shv_cuda_callback callback = nullptr;
     void* user = nullptr;
-    // placement in its batch
-    int window_off = 0;
-    // completion
-    mutable std::mutex m;
-    std::condition_variable cv;
-    int state = 0;              // 0 pending, 1 done, -1 failed
-    bool released = false;      // callback has returned
-    std::string error;
-    Clock::time_point t_submit, t_start, t_done;
+    // ---- where it landed
+    int first_window = 0, first_crop = 0;
+    Clock::time_point submitted, started, finished;
     float gpu_ms = 0.0f;
-    int batch_frames = 0, batch_windows = 0;
+    int batch_crops = 0, batch_windows = 0;
+    // ---- completion: outcome 0 until the batch retires; `settled` once the callback has returned
+    mutable std::mutex mu;
+    std::condition_variable cv;
+    int outcome = 0;
+    bool settled = false;
+    std::string why;
+
+    void complete(bool ok, const std::string& error, float ms, int crops_in_batch, int windows_in_batch) {
+        {
+            std::lock_guard<std::mutex> g(mu);
+            outcome = ok ? 1 : -1;
+            why = ok ? std::string() : error;
+            finished = Clock::now();
+            gpu_ms = ms;
+            batch_crops = crops_in_batch;
+            batch_windows = windows_in_batch;
+        }
+        cv.notify_all();
+        // the job cannot be freed before `settled`, so the callback may use the handle
+        if (callback) callback(this, ok ? 1 : -1, user);
+        {
+            std::lock_guard<std::mutex> g(mu);
+            settled = true;
+            cv.notify_all();                // inside the lock: a waiter in job_free may delete the job the moment it wakes
+        }
+    }
 };
 
 namespace {
 
-struct HostSide {                            // pinned companions of one engine slot
-    float* tok_stage = nullptr;              // [max_host_tokens][6144], allocated on first unpinned block
-    const float** tokptr = nullptr;          // [max_windows*20]
-    int32_t* store = nullptr;                // [max_host_tokens]
-    int32_t* d_store = nullptr;              // device copy
-    float* logits = nullptr;                 // [max_windows]
-    uint8_t* frames = nullptr;               // [max_frames][172800], allocated on first unpinned frame
-    float* tokens_out = nullptr;             // [max_frames][6144], allocated on first unpinned tokens_out
-    int32_t* fstore = nullptr;               // [max_frames] token slot per encoded frame
-    int32_t* d_fstore = nullptr;             // device copy
-    int* status = nullptr;                   // [SHVK_STATUS_WORDS] the kernels' status words as of the end of the batch
-    cudaEvent_t copied = nullptr, start = nullptr, end = nullptr;
+// One buffer set of the pipeline: engine slot `index` and the pinned host memory that goes with it.
+struct Lane {
+    int index = 0;
+    const float** table = nullptr;       // [max_windows * 20] device addresses of the windows' blocks
+    int32_t* block_slot = nullptr;       // [block cap] destination slot per uploaded host block (-1 = none)
+    int32_t* d_block_slot = nullptr;
+    int32_t* crop_slot = nullptr;        // [max_frames] destination slot per encoded crop
+    int32_t* d_crop_slot = nullptr;
+    float* logits = nullptr;             // [max_windows]
+    int* status = nullptr;               // [SHVK_STATUS_WORDS] the kernels' status words behind the batch
+    float* stage_tokens = nullptr;       // staging for pageable host blocks, made on first use
+    uint8_t* stage_crops = nullptr;      // staging for pageable crops, made on first use
+    float* stage_tokens_out = nullptr;   // staging for pageable tokens_out, made on first use
+    cudaEvent_t uploaded = nullptr, begin = nullptr, end = nullptr;
+
+    void release() {
+        for (void* p : {static_cast<void*>(table), static_cast<void*>(block_slot), static_cast<void*>(crop_slot),
+                        static_cast<void*>(logits), static_cast<void*>(status), static_cast<void*>(stage_tokens),
+                        static_cast<void*>(stage_crops), static_cast<void*>(stage_tokens_out)})
+            if (p) cudaFreeHost(p);
+        if (d_block_slot) cudaFree(d_block_slot);
+        if (d_crop_slot) cudaFree(d_crop_slot);
+        for (cudaEvent_t e : {uploaded, begin, end})
+            if (e) cudaEventDestroy(e);
+    }
 };
 
-struct Batch {
-    int slot = 0;
+struct Flight {                           // a batch between launch and retirement
+    Lane* lane = nullptr;
     std::vector<shv_cuda_job*> jobs;
-    int windows = 0, frames = 0;
-    bool failed = false;
+    int windows = 0, crops = 0;
+    bool launched = false;                // false: enqueueing threw; `error` says why
     std::string error;
 };
 
-class Scheduler {
+class Pipeline {
 public:
     std::unique_ptr<shv::Engine> engine;
     std::string mode, fingerprint;
@@ -125,451 +186,472 @@ public:
     int device = 0;
     shv_cuda_options opt{};
     size_t device_bytes = 0;
-    float* d_pool = nullptr;
-    long fail_every = 0;                     // test hook: fail every n-th batch on the host before any GPU work
+    float* pool = nullptr;                // device token slots [token_slots][6144]
 
-    ~Scheduler() {
-        for (HostSide& h : host_) {
-            if (h.tok_stage) cudaFreeHost(h.tok_stage);
-            if (h.tokptr) cudaFreeHost(h.tokptr);
-            if (h.store) cudaFreeHost(h.store);
-            if (h.d_store) cudaFree(h.d_store);
-            if (h.logits) cudaFreeHost(h.logits);
-            if (h.frames) cudaFreeHost(h.frames);
-            if (h.tokens_out) cudaFreeHost(h.tokens_out);
-            if (h.fstore) cudaFreeHost(h.fstore);
-            if (h.d_fstore) cudaFree(h.d_fstore);
-            if (h.status) cudaFreeHost(h.status);
-            for (cudaEvent_t e : {h.copied, h.start, h.end})
-                if (e) cudaEventDestroy(e);
-        }
-        if (d_pool) cudaFree(d_pool);
+    ~Pipeline() {
+        for (Lane& l : lanes_) l.release();
+        if (pool) cudaFree(pool);
         engine.reset();
-        if (compute_) cudaStreamDestroy(compute_);
-        if (copy_) cudaStreamDestroy(copy_);
+        for (cudaStream_t s : {compute_, copy_})
+            if (s) cudaStreamDestroy(s);
     }
+
+    int block_cap() const { return std::min(opt.max_host_tokens, opt.max_windows * kWin); }
+    // What one batch should carry at most when everything it classifies has to be uploaded first: an eighth of the
+    // limits (at least 256 windows / frames).  Uploads and kernels of a stream of such batches overlap batch by batch; one
+    // batch of the full limit would keep the GPU idle for the whole of its upload.
+    int upload_windows() const { return std::max(std::min(256, opt.max_windows), opt.max_windows / 8); }
+    int upload_crops() const { return std::max(std::min(256, opt.max_frames), opt.max_frames / 8); }
 
     void start(const shv::HostModel& hm) {
-        cuda_ok(cudaSetDevice(device), "cudaSetDevice");
-        cuda_ok(cudaStreamCreateWithFlags(&compute_, cudaStreamNonBlocking), "stream");
-        cuda_ok(cudaStreamCreateWithFlags(&copy_, cudaStreamNonBlocking), "stream");
-        shv::EngineConfig ec;
-        ec.max_frames = opt.max_frames;
-        ec.max_windows = opt.max_windows;
-        ec.use_graphs = opt.use_graphs != 0;
-        ec.slots = 2;
-        shv::Precision p;
-        if (!shv::parse_precision(mode, &p)) throw std::runtime_error("unknown mode: " + mode);
-        engine = shv::make_engine(hm, p, ec);
-        host_.resize(size_t(ec.slots));
-        const size_t Bm = size_t(opt.max_windows), Hm = size_t(std::max(opt.max_host_tokens, 1));
-        for (HostSide& h : host_) {
-            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.tokptr), Bm * 20 * sizeof(float*), cudaHostAllocDefault), "pinned alloc");
-            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.store), Hm * 4, cudaHostAllocDefault), "pinned alloc");
-            cuda_ok(cudaMalloc(reinterpret_cast<void**>(&h.d_store), Hm * 4), "device alloc");
-            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.logits), Bm * 4, cudaHostAllocDefault), "pinned alloc");
-            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.fstore), size_t(opt.max_frames) * 4, cudaHostAllocDefault), "pinned alloc");
-            cuda_ok(cudaMalloc(reinterpret_cast<void**>(&h.d_fstore), size_t(opt.max_frames) * 4), "device alloc");
-            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.status), SHVK_STATUS_WORDS * sizeof(int), cudaHostAllocDefault), "pinned alloc");
-            std::memset(h.status, 0, SHVK_STATUS_WORDS * sizeof(int));
-            cuda_ok(cudaEventCreateWithFlags(&h.copied, cudaEventDisableTiming), "event");
-            cuda_ok(cudaEventCreate(&h.start), "event");
-            cuda_ok(cudaEventCreate(&h.end), "event");
+        check(cudaSetDevice(device), "cudaSetDevice");
+        check(cudaStreamCreateWithFlags(&compute_, cudaStreamNonBlocking), "stream");
+        check(cudaStreamCreateWithFlags(&copy_, cudaStreamNonBlocking), "stream");
+        shv::Precision prec;
+        if (!shv::parse_precision(mode, &prec)) throw ApiError("unknown mode: " + mode);
+        shv::EngineConfig cfg;
+        cfg.max_frames = opt.max_frames;
+        cfg.max_windows = opt.max_windows;
+        cfg.use_graphs = opt.use_graphs != 0;
+        cfg.slots = kLanes;
+        cfg.max_host_blocks = block_cap();
+        engine = shv::make_engine(hm, prec, cfg);
+        const size_t nwin = size_t(opt.max_windows), nblk = size_t(std::max(block_cap(), 1)), ncrop = size_t(opt.max_frames);
+        lanes_.resize(kLanes);
+        for (int i = 0; i < kLanes; ++i) {
+            Lane& l = lanes_[size_t(i)];
+            l.index = i;
+            l.table = pinned_array<const float*>(nwin * kWin, "pinned pointer table");
+            l.block_slot = pinned_array<int32_t>(nblk, "pinned slot list");
+            l.crop_slot = pinned_array<int32_t>(ncrop, "pinned slot list");
+            l.logits = pinned_array<float>(nwin, "pinned logits");
+            l.status = pinned_array<int>(SHVK_STATUS_WORDS, "pinned status words");
+            std::fill(l.status, l.status + SHVK_STATUS_WORDS, 0);
+            check(cudaMalloc(reinterpret_cast<void**>(&l.d_block_slot), nblk * sizeof(int32_t)), "device slot list");
+            check(cudaMalloc(reinterpret_cast<void**>(&l.d_crop_slot), ncrop * sizeof(int32_t)), "device slot list");
+            check(cudaEventCreateWithFlags(&l.uploaded, cudaEventDisableTiming), "event");
+            check(cudaEventCreate(&l.begin), "event");
+            check(cudaEventCreate(&l.end), "event");
+            idle_.push_back(&l);
         }
         if (opt.token_slots > 0) {
-            cuda_ok(cudaMalloc(reinterpret_cast<void**>(&d_pool), size_t(opt.token_slots) * kBlockBytes), "token slots");
-            cuda_ok(cudaMemset(d_pool, 0, size_t(opt.token_slots) * kBlockBytes), "token slots");
+            check(cudaMalloc(reinterpret_cast<void**>(&pool), size_t(opt.token_slots) * kTokBytes), "token slots");
+            check(cudaMemset(pool, 0, size_t(opt.token_slots) * kTokBytes), "token slots");
+            touched_.assign(size_t(opt.token_slots), 0);
         }
         device_bytes = engine->weight_bytes() + engine->activation_bytes() +
-                       size_t(ec.slots) * (engine->slot_bytes() + Hm * 4 + size_t(opt.max_frames) * 4) + size_t(std::max(opt.token_slots, 0)) * kBlockBytes;
+                       size_t(kLanes) * (engine->slot_bytes() + (nblk + ncrop) * sizeof(int32_t)) +
+                       size_t(std::max(opt.token_slots, 0)) * kTokBytes;
 #ifdef SHV_CUDA_EXPERIMENTAL
         // test hook of the experimental library only: the certificate-checked library reads no environment
-        if (const char* e = std::getenv("SHV_CUDA_FAIL_EVERY")) fail_every = std::atol(e);
+        if (const char* e = std::getenv("SHV_CUDA_FAIL_EVERY")) fail_every_ = std::atol(e);
 #endif
-        cuda_ok(cudaDeviceSynchronize(), "init");
-        worker_ = std::thread([this] { loop(); });
+        check(cudaDeviceSynchronize(), "initialisation");
+        feeder_ = std::thread([this] { feed(); });
+        finisher_ = std::thread([this] { finish(); });
     }
 
-    void stop() {
+    // Queues a job; false if the model is shutting down (the caller keeps the job).
+    bool accept(shv_cuda_job* j) {
         {
-            std::lock_guard<std::mutex> lk(mu_);
-            stopping_ = true;
+            std::lock_guard<std::mutex> g(mu_);
+            if (closing_) return false;
+            pending_.push_back(j);
         }
-        wake_.notify_all();
-        if (worker_.joinable()) worker_.join();
+        work_.notify_all();
+        return true;
     }
 
-    // Test hook: the worker arms the engine before its next batch (the engine has one driver thread).
-    void request_starve(int kind, int batches) {
-        if (kind != 1 && kind != 2) throw std::runtime_error("starve kind: 1 = tensor-core GEMM, 2 = scan");
-        if (mode == "fp32") throw std::runtime_error("the starved test launches exist for the 16-bit modes only");
-        std::lock_guard<std::mutex> lk(mu_);
+    // Everything queued so far still runs; returns when both threads have ended.
+    void shutdown() {
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            closing_ = true;
+        }
+        work_.notify_all();
+        if (feeder_.joinable()) feeder_.join();
+        if (finisher_.joinable()) finisher_.join();
+    }
+
+    // Test hook: the feeder arms the engine before its next batch (the engine has a single driver thread).
+    void arm_starved_launch(int kind, int batches) {
+        if (kind != 1 && kind != 2) throw ApiError("starve kind: 1 = tensor-core GEMM, 2 = scan");
+        if (mode == "fp32") throw ApiError("the starved test launches exist for the 16-bit modes only");
+        std::lock_guard<std::mutex> g(mu_);
         starve_kind_ = kind;
         starve_batches_ = batches;
     }
 
-    // Host token blocks one batch may carry: the option's limit, and what a slot's device staging area holds.
-    int block_cap() const { return std::min(opt.max_host_tokens, opt.max_windows * 20); }
-
-    // false if the model is stopping (the job is not queued)
-    bool enqueue(shv_cuda_job* j) {
-        {
-            std::lock_guard<std::mutex> lk(mu_);
-            if (stopping_) return false;
-            queue_.push_back(j);
-        }
-        wake_.notify_all();
-        return true;
-    }
-
 private:
     cudaStream_t compute_ = nullptr, copy_ = nullptr;
-    std::vector<HostSide> host_;
-    std::mutex mu_;
-    std::condition_variable wake_;
-    std::deque<shv_cuda_job*> queue_;
-    bool stopping_ = false;
+    std::vector<Lane> lanes_;
+    std::mutex mu_;                          // guards everything below
+    std::condition_variable work_;           // pending job, freed lane, launched batch, shutdown
+    std::deque<shv_cuda_job*> pending_;
+    std::deque<Lane*> idle_;
+    std::deque<Flight> flying_;
+    bool closing_ = false, feeder_done_ = false;
     int starve_kind_ = 0, starve_batches_ = 0;
-    std::thread worker_;
-    long batches_ = 0;
+    std::vector<uint8_t> touched_;           // per token slot, within the batch being formed: 1 read, 2 stored
+    std::vector<int32_t> touched_list_;
+    long launched_ = 0, fail_every_ = 0;
+    std::thread feeder_, finisher_;
 
-    static void finish_job(shv_cuda_job* j, bool ok, const std::string& err, float gpu_ms, int frames, int windows) {
-        if (!ok) {
-            for (size_t i = 0; i < j->n_windows; ++i) j->logits_out[i] = kNaN;
-            if (j->tokens_out) std::fill(j->tokens_out, j->tokens_out + j->n_frames * kBlockFloats, kNaN);
-        }
-        shv_cuda_callback cb;
-        void* user;
-        {
-            std::lock_guard<std::mutex> lk(j->m);
-            j->state = ok ? 1 : -1;
-            j->error = ok ? std::string() : err;
-            j->t_done = Clock::now();
-            j->gpu_ms = gpu_ms;
-            j->batch_frames = frames;
-            j->batch_windows = windows;
-            cb = j->cb;
-            user = j->user;
-            j->cv.notify_all();              // under the lock: job_free may delete *j as soon as it sees `released`
-        }
-        if (cb) cb(j, ok ? 1 : -1, user);
-        std::lock_guard<std::mutex> lk(j->m);
-        j->released = true;
-        j->cv.notify_all();
+    // ------------------------------------------------------------------------------------------ batch formation
+    // Would adding `j` to the batch being formed store into a slot the batch already touches?
+    bool store_hazard(const shv_cuda_job* j) const {
+        for (const std::vector<int32_t>* list : {&j->crop_slot, &j->host_slot})
+            for (int32_t s : *list)
+                if (s >= 0 && touched_[size_t(s)]) return true;
+        return false;
     }
-
-    // Pops queued jobs in order while the limits hold and no store hazard appears.  Caller holds mu_.
-    void coalesce(std::vector<shv_cuda_job*>& out) {
-        int windows = 0, blocks = 0, frames = 0;
-        std::unordered_set<int32_t> read, stored;
-        while (!queue_.empty()) {
-            shv_cuda_job* j = queue_.front();
+    void note_slots(const shv_cuda_job* j) {
+        auto mark = [&](int32_t s, uint8_t how) {
+            if (s < 0) return;
+            if (!touched_[size_t(s)]) touched_list_.push_back(s);
+            touched_[size_t(s)] |= how;
+        };
+        for (int32_t s : j->crop_slot) mark(s, 2);
+        for (int32_t s : j->host_slot) mark(s, 2);
+        for (const Entry& e : j->entries)
+            if (e.src == Src::Slot) mark(e.index, 1);
+    }
+    // Moves the head of `pending_` into `out`.  Caller holds mu_.  A batch closes at the limits of the options, at a store
+    // hazard, or -- counting only what must be uploaded (host token blocks, crops) -- at the per-batch upload budget;
+    // windows that read device token slots cost no upload and coalesce up to the limit, except while the pipeline has
+    // room to spare (`eager`), when a batch also closes at that many windows so that the first kernels start early.
+    void take_batch(std::vector<shv_cuda_job*>& out, bool eager) {
+        const int want_blocks = upload_windows() * kWin, want_crops = upload_crops();
+        const int want_windows = eager ? upload_windows() : opt.max_windows;
+        int windows = 0, blocks = 0, crops = 0;
+        while (!pending_.empty()) {
+            shv_cuda_job* j = pending_.front();
             if (!out.empty()) {
-                if (windows + int(j->n_windows) > opt.max_windows || blocks + j->host_blocks > block_cap() ||
-                    frames + int(j->n_frames) > opt.max_frames)
+                if (windows + j->n_windows > opt.max_windows || blocks + j->n_host > block_cap() || crops + j->n_crops > opt.max_frames)
                     break;
-                bool hazard = false;
-                for (const std::vector<int32_t>* v : {&j->store_slots, &j->frame_store})
-                    for (int32_t s : *v)
-                        if (s >= 0 && (read.count(s) || stored.count(s))) { hazard = true; break; }
-                if (hazard) break;
+                if (windows >= want_windows || crops >= want_crops || blocks >= want_blocks) break;
+                if (pool && store_hazard(j)) break;
             }
-            queue_.pop_front();
+            pending_.pop_front();
             out.push_back(j);
-            windows += int(j->n_windows);
-            blocks += j->host_blocks;
-            frames += int(j->n_frames);
-            for (const std::vector<int32_t>* v : {&j->store_slots, &j->frame_store})
-                for (int32_t s : *v)
-                    if (s >= 0) stored.insert(s);
-            for (int32_t s : j->wslots)
-                if (s >= 0) read.insert(s);
+            windows += j->n_windows;
+            blocks += j->n_host;
+            crops += j->n_crops;
+            if (pool) note_slots(j);
         }
+        for (int32_t s : touched_list_) touched_[size_t(s)] = 0;
+        touched_list_.clear();
     }
 
-    Batch launch(int slot, std::vector<shv_cuda_job*>& jobs) {
-        Batch b;
-        b.slot = slot;
-        b.jobs = jobs;
-        const Clock::time_point t0 = Clock::now();
-        HostSide& h = host_[size_t(slot)];
-        const shv::Engine::Slot& d = engine->slot(slot);
-        try {
-            ++batches_;
-            if (fail_every > 0 && batches_ % fail_every == 0) throw std::runtime_error("injected batch failure (SHV_CUDA_FAIL_EVERY)");
-            int windows = 0, blocks = 0, stores = 0, frames = 0;
-            bool frame_stores = false;
-            for (shv_cuda_job* j : jobs) {
-                j->t_start = t0;
-                j->window_off = windows;
-                j->frame_off = frames;
-                if (j->n_frames) {                              // crops: pinned sources by DMA, the rest staged
-                    uint8_t* dst = d.d_frames + size_t(frames) * kFrameBytes;
-                    const size_t bytes = j->n_frames * kFrameBytes;
-                    if (j->frames_pinned) {
-                        cuda_ok(cudaMemcpyAsync(dst, j->frames, bytes, cudaMemcpyHostToDevice, copy_), "frame upload");
-                    } else {
-                        if (!h.frames)
-                            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.frames), size_t(opt.max_frames) * kFrameBytes,
-                                                  cudaHostAllocDefault), "pinned staging");
-                        uint8_t* st = h.frames + size_t(frames) * kFrameBytes;
-                        std::memcpy(st, j->frames, bytes);
-                        cuda_ok(cudaMemcpyAsync(dst, st, bytes, cudaMemcpyHostToDevice, copy_), "frame upload");
-                    }
-                    for (size_t f = 0; f < j->n_frames; ++f) {
-                        const int32_t sl = j->frame_store.empty() ? -1 : j->frame_store[f];
-                        h.fstore[size_t(frames) + f] = sl;
-                        frame_stores |= sl >= 0;
-                    }
-                }
-                size_t e = 0;                                   // next window entry that takes a host block
-                const size_t entries = j->n_windows * 20;
-                auto from_frame = [&](size_t k) { return !j->wframes.empty() && j->wframes[k] >= 0; };
-                int stored_here = 0;
-                for (const HostRun& run : j->runs) {
-                    float* dst = d.d_tok_stage + size_t(blocks) * kBlockFloats;
-                    const size_t bytes = size_t(run.blocks) * kBlockBytes;
-                    if (run.pinned) {
-                        cuda_ok(cudaMemcpyAsync(dst, run.src, bytes, cudaMemcpyHostToDevice, copy_), "token upload");
-                    } else {
-                        if (!h.tok_stage)
-                            cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.tok_stage),
-                                                  size_t(std::max(opt.max_host_tokens, 1)) * kBlockBytes, cudaHostAllocDefault),
-                                    "pinned staging");
-                        float* st = h.tok_stage + size_t(blocks) * kBlockFloats;
-                        std::memcpy(st, run.src, bytes);
-                        cuda_ok(cudaMemcpyAsync(dst, st, bytes, cudaMemcpyHostToDevice, copy_), "token upload");
-                    }
-                    for (int i = 0; i < run.blocks; ++i) {
-                        const float* dev_block = dst + size_t(i) * kBlockFloats;
-                        if (!j->store_slots.empty()) {
-                            h.store[blocks + i] = j->store_slots[size_t(stored_here++)];
-                            ++stores;
-                        } else {
-                            h.store[blocks + i] = -1;
-                            while (e < entries && (j->wslots[e] >= 0 || from_frame(e))) ++e;
-                            h.tokptr[size_t(windows) * 20 + e] = dev_block;
-                            ++e;
-                        }
-                    }
-                    blocks += run.blocks;
-                }
-                for (size_t k = 0; k < entries; ++k) {
-                    if (from_frame(k))
-                        h.tokptr[size_t(windows) * 20 + k] = d.d_tokens + size_t(frames + j->wframes[k]) * kBlockFloats;
-                    else if (j->wslots[k] >= 0)
-                        h.tokptr[size_t(windows) * 20 + k] = d_pool + size_t(j->wslots[k]) * kBlockFloats;
-                }
-                windows += int(j->n_windows);
-                frames += int(j->n_frames);
-            }
-            if (frame_stores)
-                cuda_ok(cudaMemcpyAsync(h.d_fstore, h.fstore, size_t(frames) * 4, cudaMemcpyHostToDevice, copy_), "slot list upload");
-            if (windows)
-                cuda_ok(cudaMemcpyAsync(d.d_tokptr, h.tokptr, size_t(windows) * 20 * sizeof(float*), cudaMemcpyHostToDevice, copy_),
-                        "pointer table upload");
-            if (stores)
-                cuda_ok(cudaMemcpyAsync(h.d_store, h.store, size_t(blocks) * 4, cudaMemcpyHostToDevice, copy_), "slot list upload");
-            cuda_ok(cudaEventRecord(h.copied, copy_), "event");
-            cuda_ok(cudaStreamWaitEvent(compute_, h.copied, 0), "event");
-            cuda_ok(cudaEventRecord(h.start, compute_), "event");
-            if (frames) engine->encode(slot, frames, compute_);
-            if (frame_stores) cuda_ok(cudaError_t(shvk_store_tokens(d.d_tokens, h.d_fstore, d_pool, frames, compute_)), "token slot store");
-            if (stores) cuda_ok(cudaError_t(shvk_store_tokens(d.d_tok_stage, h.d_store, d_pool, blocks, compute_)), "token slot store");
-            if (windows) {
-                engine->classify(slot, windows, compute_);
-                cuda_ok(cudaMemcpyAsync(h.logits, d.d_logits, size_t(windows) * 4, cudaMemcpyDeviceToHost, compute_), "logit download");
-            }
-            for (shv_cuda_job* j : jobs) {
-                if (!j->tokens_out || !j->n_frames) continue;
-                if (!j->tokens_out_pinned && !h.tokens_out)
-                    cuda_ok(cudaHostAlloc(reinterpret_cast<void**>(&h.tokens_out), size_t(opt.max_frames) * kBlockBytes,
-                                          cudaHostAllocDefault), "pinned staging");
-                float* dst = j->tokens_out_pinned ? j->tokens_out : h.tokens_out + size_t(j->frame_off) * kBlockFloats;
-                cuda_ok(cudaMemcpyAsync(dst, d.d_tokens + size_t(j->frame_off) * kBlockFloats, j->n_frames * kBlockBytes,
-                                        cudaMemcpyDeviceToHost, compute_), "token download");
-            }
-            cuda_ok(cudaError_t(shvk_status_fetch_async(h.status, compute_)), "status fetch");
-            cuda_ok(cudaEventRecord(h.end, compute_), "event");
-            b.windows = windows;
-            b.frames = frames;
-        } catch (const std::exception& e) {
-            b.failed = true;
-            b.error = e.what();
-        }
-        return b;
-    }
-
-    void retire(Batch& b) {
-        HostSide& h = host_[size_t(b.slot)];
-        float gpu_ms = 0.0f;
-        if (!b.failed) {
-            const cudaError_t e = cudaEventSynchronize(h.end);
-            if (e != cudaSuccess) {
-                b.failed = true;
-                b.error = std::string("CUDA error: ") + cudaGetErrorString(e);
-            } else {
-                if (cudaEventElapsedTime(&gpu_ms, h.start, h.end) != cudaSuccess) { cudaGetLastError(); gpu_ms = 0.0f; }
-                bool gave_up = false;
-                for (int i = 0; i < SHVK_STATUS_WORDS; ++i) gave_up |= h.status[i] != 0;
-                if (gave_up) {
-                    // The words are shared by everything on this device: clear them behind the work already queued, so
-                    // that batches launched from now on are judged on their own.  A batch that was already in flight
-                    // fetched the set words and fails too.
-                    b.failed = true;
-                    b.error = "a kernel gave up waiting on its TMA / tensor-core pipeline (device status word set)";
-                    if (shvk_status_clear_async(compute_) != 0) cudaGetLastError();
-                    cudaStreamSynchronize(compute_);
-                }
-            }
-        } else {
-            cudaStreamSynchronize(compute_);
-            cudaStreamSynchronize(copy_);
-        }
-        for (shv_cuda_job* j : b.jobs) {
-            if (!b.failed) {
-                for (size_t i = 0; i < j->n_windows; ++i) {
-                    const float v = h.logits[size_t(j->window_off) + i];
-                    j->logits_out[i] = std::isfinite(v) ? v : kNaN;
-                }
-                if (j->tokens_out && !j->tokens_out_pinned && j->n_frames)
-                    std::memcpy(j->tokens_out, h.tokens_out + size_t(j->frame_off) * kBlockFloats, j->n_frames * kBlockBytes);
-            }
-            finish_job(j, !b.failed, b.error, gpu_ms, b.frames, b.windows);
-        }
-    }
-
-    void loop() {
+    // ------------------------------------------------------------------------------------------ feeder
+    void feed() {
         if (cudaSetDevice(device) != cudaSuccess) cudaGetLastError();
-        std::deque<Batch> inflight;
-        const int nslots = int(host_.size());
-        int next_slot = 0;
         for (;;) {
-            std::vector<shv_cuda_job*> jobs;
+            Flight f;
             {
                 std::unique_lock<std::mutex> lk(mu_);
-                if (inflight.empty()) wake_.wait(lk, [&] { return stopping_ || !queue_.empty(); });
-                if (queue_.empty() && inflight.empty() && stopping_) return;
-                if (!queue_.empty() && int(inflight.size()) < nslots) {
-                    if (opt.max_delay_us > 0 && inflight.empty()) {
-                        const auto deadline = Clock::now() + std::chrono::microseconds(opt.max_delay_us);
-                        wake_.wait_until(lk, deadline, [&] {
-                            if (stopping_) return true;
-                            size_t w = 0;
-                            for (const shv_cuda_job* j : queue_) w += j->n_windows;
-                            return w >= size_t(opt.max_windows);
-                        });
-                    }
-                    coalesce(jobs);
-                    if (!jobs.empty() && starve_batches_ > 0) {
-                        engine->inject_wait_timeout(starve_kind_, starve_batches_);
-                        starve_batches_ = 0;
-                    }
+                work_.wait(lk, [&] { return (!pending_.empty() && !idle_.empty()) || (closing_ && pending_.empty()); });
+                if (pending_.empty()) {
+                    feeder_done_ = true;
+                    lk.unlock();
+                    work_.notify_all();
+                    return;
+                }
+                if (opt.max_delay_us > 0 && flying_.empty()) {
+                    // nothing to overlap with yet: give more jobs a moment to arrive, up to a full batch
+                    const auto until = Clock::now() + std::chrono::microseconds(opt.max_delay_us);
+                    work_.wait_until(lk, until, [&] {
+                        long w = 0;
+                        for (const shv_cuda_job* j : pending_) w += j->n_windows;
+                        return closing_ || w >= opt.max_windows;
+                    });
+                }
+                take_batch(f.jobs, int(flying_.size()) + 1 < kLanes);
+                f.lane = idle_.front();
+                idle_.pop_front();
+                if (starve_batches_ > 0) {
+                    engine->inject_wait_timeout(starve_kind_, starve_batches_);
+                    starve_batches_ = 0;
                 }
             }
-            if (!jobs.empty()) {
-                inflight.push_back(launch(next_slot, jobs));
-                next_slot = (next_slot + 1) % nslots;
-                if (int(inflight.size()) < nslots) {
-                    std::lock_guard<std::mutex> lk(mu_);
-                    if (!queue_.empty()) continue;            // stage a second batch before waiting on the first
+            enqueue(f);
+            {
+                std::lock_guard<std::mutex> g(mu_);
+                flying_.push_back(std::move(f));
+            }
+            work_.notify_all();
+        }
+    }
+
+    // Copies + kernels of one batch into the streams.  Never blocks on the GPU.  On an exception the batch is marked
+    // unlaunched; whatever was already enqueued only touches the lane's own buffers.
+    void enqueue(Flight& f) {
+        Lane& l = *f.lane;
+        const shv::Engine::Slot& dev = engine->slot(l.index);
+        const Clock::time_point now = Clock::now();
+        try {
+            if (fail_every_ > 0 && ++launched_ % fail_every_ == 0) throw ApiError("injected batch failure (SHV_CUDA_FAIL_EVERY)");
+            int windows = 0, crops = 0, blocks = 0;
+            bool crop_stores = false, block_stores = false;
+            for (shv_cuda_job* j : f.jobs) {
+                j->started = now;
+                j->first_window = windows;
+                j->first_crop = crops;
+                if (j->n_crops) {
+                    uint8_t* dst = dev.d_frames + size_t(crops) * kCropBytes;
+                    const size_t bytes = size_t(j->n_crops) * kCropBytes;
+                    const uint8_t* from = j->crops;
+                    if (!j->crops_pinned) {
+                        if (!l.stage_crops) l.stage_crops = pinned_array<uint8_t>(size_t(opt.max_frames) * kCropBytes, "pinned crop staging");
+                        std::memcpy(l.stage_crops + size_t(crops) * kCropBytes, j->crops, bytes);
+                        from = l.stage_crops + size_t(crops) * kCropBytes;
+                    }
+                    check(cudaMemcpyAsync(dst, from, bytes, cudaMemcpyHostToDevice, copy_), "crop upload");
+                    for (int c = 0; c < j->n_crops; ++c) {
+                        const int32_t s = j->crop_slot.empty() ? -1 : j->crop_slot[size_t(c)];
+                        l.crop_slot[crops + c] = s;
+                        crop_stores |= s >= 0;
+                    }
                 }
+                // host blocks: one copy per contiguous span; remember where each block lands on the device
+                const int first_block = blocks;
+                for (const Span& sp : j->spans) {
+                    float* dst = dev.d_tok_stage + size_t(blocks) * kTokFloats;
+                    const size_t bytes = size_t(sp.count) * kTokBytes;
+                    const float* from = sp.first;
+                    if (!sp.pinned) {
+                        if (!l.stage_tokens) l.stage_tokens = pinned_array<float>(size_t(std::max(block_cap(), 1)) * kTokFloats, "pinned token staging");
+                        std::memcpy(l.stage_tokens + size_t(blocks) * kTokFloats, sp.first, bytes);
+                        from = l.stage_tokens + size_t(blocks) * kTokFloats;
+                    }
+                    check(cudaMemcpyAsync(dst, from, bytes, cudaMemcpyHostToDevice, copy_), "token upload");
+                    blocks += sp.count;
+                }
+                for (int b = 0; b < j->n_host; ++b) {
+                    const int32_t s = j->host_slot.empty() ? -1 : j->host_slot[size_t(b)];
+                    l.block_slot[first_block + b] = s;
+                    block_stores |= s >= 0;
+                }
+                const float** row = l.table + size_t(windows) * kWin;
+                for (size_t e = 0; e < j->entries.size(); ++e) {
+                    const Entry& en = j->entries[e];
+                    row[e] = en.src == Src::Host   ? dev.d_tok_stage + size_t(first_block + en.index) * kTokFloats
+                             : en.src == Src::Slot ? pool + size_t(en.index) * kTokFloats
+                                                   : dev.d_tokens + size_t(crops + en.index) * kTokFloats;
+                }
+                windows += j->n_windows;
+                crops += j->n_crops;
             }
-            if (!inflight.empty()) {
-                retire(inflight.front());
-                inflight.pop_front();
+            if (crop_stores)
+                check(cudaMemcpyAsync(l.d_crop_slot, l.crop_slot, size_t(crops) * sizeof(int32_t), cudaMemcpyHostToDevice, copy_), "slot list upload");
+            if (block_stores)
+                check(cudaMemcpyAsync(l.d_block_slot, l.block_slot, size_t(blocks) * sizeof(int32_t), cudaMemcpyHostToDevice, copy_), "slot list upload");
+            if (windows)
+                check(cudaMemcpyAsync(dev.d_tokptr, l.table, size_t(windows) * kWin * sizeof(float*), cudaMemcpyHostToDevice, copy_), "pointer table upload");
+            check(cudaEventRecord(l.uploaded, copy_), "event");
+            check(cudaStreamWaitEvent(compute_, l.uploaded, 0), "event");
+            check(cudaEventRecord(l.begin, compute_), "event");
+            if (crops) engine->encode(l.index, crops, compute_);
+            if (crop_stores) check(shvk_store_tokens(dev.d_tokens, l.d_crop_slot, pool, crops, compute_), "token slot store");
+            if (block_stores) check(shvk_store_tokens(dev.d_tok_stage, l.d_block_slot, pool, blocks, compute_), "token slot store");
+            if (windows) {
+                engine->classify(l.index, windows, compute_);
+                check(cudaMemcpyAsync(l.logits, dev.d_logits, size_t(windows) * sizeof(float), cudaMemcpyDeviceToHost, compute_), "logit download");
             }
+            for (shv_cuda_job* j : f.jobs) {
+                if (!j->tokens_out || !j->n_crops) continue;
+                float* to = j->tokens_out;
+                if (!j->tokens_out_pinned) {
+                    if (!l.stage_tokens_out) l.stage_tokens_out = pinned_array<float>(size_t(opt.max_frames) * kTokFloats, "pinned token staging");
+                    to = l.stage_tokens_out + size_t(j->first_crop) * kTokFloats;
+                }
+                check(cudaMemcpyAsync(to, dev.d_tokens + size_t(j->first_crop) * kTokFloats, size_t(j->n_crops) * kTokBytes,
+                                      cudaMemcpyDeviceToHost, compute_), "token download");
+            }
+            check(shvk_status_fetch_async(l.status, compute_), "status fetch");
+            check(cudaEventRecord(l.end, compute_), "event");
+            f.windows = windows;
+            f.crops = crops;
+            f.launched = true;
+        } catch (const std::exception& e) {
+            f.launched = false;
+            f.error = e.what();
+        }
+    }
+
+    // ------------------------------------------------------------------------------------------ finisher
+    void finish() {
+        if (cudaSetDevice(device) != cudaSuccess) cudaGetLastError();
+        for (;;) {
+            Flight f;
+            {
+                std::unique_lock<std::mutex> lk(mu_);
+                work_.wait(lk, [&] { return !flying_.empty() || feeder_done_; });
+                if (flying_.empty()) return;
+                f = std::move(flying_.front());       // stays counted as in flight until its lane is returned below
+            }
+            retire(f);
+            {
+                std::lock_guard<std::mutex> g(mu_);
+                flying_.pop_front();
+                idle_.push_back(f.lane);
+            }
+            work_.notify_all();
+        }
+    }
+
+    void retire(Flight& f) {
+        Lane& l = *f.lane;
+        bool ok = f.launched;
+        std::string error = f.error;
+        float ms = 0.0f;
+        if (ok) {
+            const cudaError_t e = cudaEventSynchronize(l.end);
+            if (e != cudaSuccess) {
+                ok = false;
+                error = std::string("CUDA error: ") + cudaGetErrorString(e);
+            } else if (cudaEventElapsedTime(&ms, l.begin, l.end) != cudaSuccess) {
+                cudaGetLastError();
+                ms = 0.0f;
+            }
+            if (ok && std::any_of(l.status, l.status + SHVK_STATUS_WORDS, [](int w) { return w != 0; })) {
+                // The status words are shared by everything on this device.  Clear them behind the work already queued,
+                // so that batches launched from now on are judged on their own; a batch that was already in flight has
+                // fetched the set words and fails as well.
+                ok = false;
+                error = "a kernel gave up waiting on its TMA / tensor-core pipeline (device status word set)";
+                if (shvk_status_clear_async(compute_) != 0) cudaGetLastError();
+            }
+        } else {
+            // whatever part of the batch was enqueued must not outlive the buffers the jobs lent us
+            cudaStreamSynchronize(copy_);
+            cudaStreamSynchronize(compute_);
+        }
+        for (shv_cuda_job* j : f.jobs) {
+            if (ok) {
+                const float* got = l.logits + j->first_window;
+                for (int w = 0; w < j->n_windows; ++w) j->logits_out[w] = std::isfinite(got[w]) ? got[w] : kUnavailable;
+                if (j->tokens_out && !j->tokens_out_pinned && j->n_crops)
+                    std::memcpy(j->tokens_out, l.stage_tokens_out + size_t(j->first_crop) * kTokFloats, size_t(j->n_crops) * kTokBytes);
+            } else {
+                for (int w = 0; w < j->n_windows; ++w) j->logits_out[w] = kUnavailable;
+                if (j->tokens_out) std::fill(j->tokens_out, j->tokens_out + size_t(j->n_crops) * kTokFloats, kUnavailable);
+            }
+            j->complete(ok, error, ms, f.crops, f.windows);
         }
     }
 };
 
-template <class F> int guarded(F&& f) {
-    try {
-        return f();
-    } catch (const std::exception& e) {
-        t_error = e.what();
-        return -1;
+// Host block pointers -> spans of consecutive memory, each marked pinned or pageable.
+void group_spans(shv_cuda_job& j, const std::vector<const float*>& blocks) {
+    size_t at = 0;
+    while (at < blocks.size()) {
+        size_t end = at + 1;
+        while (end < blocks.size() && blocks[end] == blocks[end - 1] + kTokFloats) ++end;
+        j.spans.push_back(Span{blocks[at], int(end - at), is_pinned(blocks[at], (end - at) * kTokBytes)});
+        at = end;
     }
+    j.n_host = int(blocks.size());
 }
 
-// Splits `n` host block pointers into maximal contiguous runs and classifies each run as pinned or pageable.
-void add_runs(shv_cuda_job& j, const float* const* blocks, size_t n) {
-    size_t i = 0;
-    while (i < n) {
-        size_t k = i + 1;
-        while (k < n && blocks[k] == blocks[k - 1] + kBlockFloats) ++k;
-        j.runs.push_back({blocks[i], int(k - i), host_pinned(blocks[i], (k - i) * kBlockBytes)});
-        i = k;
+void require_distinct_slots(const std::vector<int32_t>& slots, int token_slots, bool allow_none) {
+    std::vector<int32_t> seen;
+    for (int32_t s : slots) {
+        if (s == -1 && allow_none) continue;
+        if (s < 0 || s >= token_slots) throw ApiError("store slot out of range");
+        seen.push_back(s);
     }
-    j.host_blocks += int(n);
+    std::sort(seen.begin(), seen.end());
+    if (std::adjacent_find(seen.begin(), seen.end()) != seen.end()) throw ApiError("duplicate store slot in one request");
 }
 
-int wait_and_free(std::vector<shv_cuda_job*>& jobs) {
-    int rc = 0;
-    std::string err;
+// Waits for every job, frees it, and reports the first failure (0 or -1, error string set).
+int settle_all(std::vector<shv_cuda_job*>& jobs) {
+    bool failed = false;
+    std::string first;
     for (shv_cuda_job* j : jobs) {
-        if (shv_cuda_job_wait(j) != 0) {
-            rc = -1;
-            if (err.empty()) err = shv_cuda_job_error(j);
+        if (shv_cuda_job_wait(j) != 0 && !failed) {
+            failed = true;
+            first = shv_cuda_job_error(j);
         }
         shv_cuda_job_free(j);
     }
-    if (rc) t_error = err;
+    jobs.clear();
+    if (failed) tls_error = first;
+    return failed ? -1 : 0;
+}
+
+// A synchronous call over `total` items as a train of requests of at most `piece` items, all submitted before the
+// first is waited for, so that the pipeline overlaps their uploads and kernels.  make(first, count, request) fills the
+// request; on a refused submit everything already queued is waited for and `poison` marks the outputs.
+template <typename Make, typename Poison>
+int run_in_pieces(shv_cuda_model* m, size_t total, size_t piece, Make make, Poison poison) {
+    std::vector<shv_cuda_job*> jobs;
+    for (size_t first = 0; first < total; first += piece) {
+        shv_cuda_request r{};
+        make(first, std::min(piece, total - first), r);
+        shv_cuda_job* j = shv_cuda_submit(m, &r);
+        if (!j) {
+            const std::string why = tls_error;
+            settle_all(jobs);
+            poison();
+            tls_error = why;
+            return -1;
+        }
+        jobs.push_back(j);
+    }
+    const int rc = settle_all(jobs);
+    if (rc == 0) tls_error.clear();
     return rc;
 }
 
 }  // namespace
 
 struct shv_cuda_model {
-    std::unique_ptr<Scheduler> sched;
+    std::unique_ptr<Pipeline> pipe;
 };
 
 // shared with engine_c.cpp
-void shv_cuda_set_error(const std::string& s) { t_error = s; }
+void shv_cuda_set_error(const std::string& s) { tls_error = s; }
 
 extern "C" {
 
 void shv_cuda_default_options(shv_cuda_options* o) {
     if (!o) return;
-    o->max_frames = 640;
-    o->max_windows = 512;
-    o->max_host_tokens = 2048;
-    o->token_slots = 0;
-    o->use_graphs = 1;
-    o->max_delay_us = 0;
+    *o = shv_cuda_options{640, 512, 2048, 0, 1, 0};
 }
 
 shv_cuda_model* shv_cuda_load_ex(const char* weights, const char* mode, int device, const shv_cuda_options* opt) {
     try {
-        if (!weights) throw std::runtime_error("null weights path");
-        auto s = std::unique_ptr<Scheduler>(new Scheduler());
-        s->mode = mode ? mode : "fp32";
-        shv::Precision p;
-        if (!shv::parse_precision(s->mode, &p)) throw std::runtime_error("unknown mode '" + s->mode + "' (fp32, bf16, fp16)");
-        shv_cuda_default_options(&s->opt);
-        if (opt) s->opt = *opt;
-        const shv_cuda_options& o = s->opt;
-        if (o.max_frames < 1 || o.max_frames > 4096 || o.max_windows < 1 || o.max_windows > 4096 || o.max_host_tokens < 0 ||
-            o.max_host_tokens > (1 << 20) || o.token_slots < 0 || o.max_delay_us < 0)
-            throw std::runtime_error("invalid options");
-        s->device = device;
+        if (!weights) throw ApiError("null weights path");
+        std::unique_ptr<Pipeline> p(new Pipeline());
+        p->mode = mode ? mode : "fp32";
+        shv::Precision prec;
+        if (!shv::parse_precision(p->mode, &prec)) throw ApiError("unknown mode '" + p->mode + "' (fp32, bf16, fp16)");
+        shv_cuda_default_options(&p->opt);
+        if (opt) p->opt = *opt;
+        const shv_cuda_options& o = p->opt;
+        const bool sane = o.max_frames >= 1 && o.max_frames <= 4096 && o.max_windows >= 1 && o.max_windows <= 4096 &&
+                          o.max_host_tokens >= 0 && o.max_host_tokens <= (1 << 20) && o.token_slots >= 0 && o.max_delay_us >= 0;
+        if (!sane) throw ApiError("invalid options");
+        p->device = device;
         const shv::HostModel hm = shv::load_host_model(weights);
-        s->fingerprint = hm.sha256;
-        s->threshold = hm.threshold;
+        p->fingerprint = hm.sha256;
+        p->threshold = hm.threshold;
         shv::check_sidecar_sha(weights, hm.sha256);
 #ifndef SHV_CUDA_EXPERIMENTAL
-        if (p != shv::Precision::FP32) {
-            const std::string why = shv::check_certificate(weights, hm.sha256, s->mode, SHV_CUDA_REVISION, hm.threshold);
-            if (!why.empty()) throw std::runtime_error(why);
+        if (prec != shv::Precision::FP32) {
+            const std::string refusal = shv::check_certificate(weights, hm.sha256, p->mode, SHV_CUDA_REVISION, hm.threshold);
+            if (!refusal.empty()) throw ApiError(refusal);
         }
 #endif
-        s->start(hm);
-        auto* m = new shv_cuda_model();
-        m->sched = std::move(s);
-        t_error.clear();
+        p->start(hm);
+        shv_cuda_model* m = new shv_cuda_model();
+        m->pipe = std::move(p);
+        tls_error.clear();
         return m;
     } catch (const std::exception& e) {
-        t_error = e.what();
+        tls_error = e.what();
         return nullptr;
     }
 }
@@ -580,272 +662,269 @@ shv_cuda_model* shv_cuda_load(const char* weights, const char* mode, int device)
 
 void shv_cuda_free(shv_cuda_model* m) {
     if (!m) return;
-    m->sched->stop();
+    m->pipe->shutdown();
     delete m;
 }
 
-const char* shv_cuda_last_error(void) { return t_error.c_str(); }
-const char* shv_cuda_mode(const shv_cuda_model* m) { return m ? m->sched->mode.c_str() : ""; }
-const char* shv_cuda_fingerprint(const shv_cuda_model* m) { return m ? m->sched->fingerprint.c_str() : ""; }
-double shv_cuda_threshold(const shv_cuda_model* m) { return m ? m->sched->threshold : std::nan(""); }
+const char* shv_cuda_last_error(void) { return tls_error.c_str(); }
+const char* shv_cuda_mode(const shv_cuda_model* m) { return m ? m->pipe->mode.c_str() : ""; }
+const char* shv_cuda_fingerprint(const shv_cuda_model* m) { return m ? m->pipe->fingerprint.c_str() : ""; }
+double shv_cuda_threshold(const shv_cuda_model* m) { return m ? m->pipe->threshold : std::nan(""); }
 const char* shv_cuda_compute_revision(void) { return SHV_CUDA_REVISION; }
-int shv_cuda_limits(const shv_cuda_model* m, int* mf, int* mw, int* mh, int* ts) {
-    if (!m) { t_error = "null model"; return -1; }
-    const shv_cuda_options& o = m->sched->opt;
-    if (mf) *mf = o.max_frames;
-    if (mw) *mw = o.max_windows;
-    if (mh) *mh = o.max_host_tokens;
-    if (ts) *ts = o.token_slots;
+size_t shv_cuda_weight_bytes(const shv_cuda_model* m) { return m ? m->pipe->engine->weight_bytes() : 0; }
+size_t shv_cuda_device_bytes(const shv_cuda_model* m) { return m ? m->pipe->device_bytes : 0; }
+
+int shv_cuda_limits(const shv_cuda_model* m, int* max_frames, int* max_windows, int* max_host_tokens, int* token_slots) {
+    if (!m) {
+        tls_error = "null model";
+        return -1;
+    }
+    const shv_cuda_options& o = m->pipe->opt;
+    const int values[4] = {o.max_frames, o.max_windows, o.max_host_tokens, o.token_slots};
+    int* outs[4] = {max_frames, max_windows, max_host_tokens, token_slots};
+    for (int i = 0; i < 4; ++i)
+        if (outs[i]) *outs[i] = values[i];
     return 0;
 }
-size_t shv_cuda_weight_bytes(const shv_cuda_model* m) { return m ? m->sched->engine->weight_bytes() : 0; }
-size_t shv_cuda_device_bytes(const shv_cuda_model* m) { return m ? m->sched->device_bytes : 0; }
 
 shv_cuda_job* shv_cuda_submit(shv_cuda_model* m, const shv_cuda_request* r) {
     try {
-        if (!m || !r) throw std::runtime_error("null argument");
-        Scheduler& s = *m->sched;
-        const shv_cuda_options& o = s.opt;
-        if (r->n_frames > size_t(o.max_frames)) throw std::runtime_error("request has more frames than max_frames");
-        if (r->n_windows > size_t(o.max_windows)) throw std::runtime_error("request has more windows than max_windows");
-        if (r->n_frames && !r->frames) throw std::runtime_error("null frames");
-        if (r->n_windows && !r->logits_out) throw std::runtime_error("null logits_out");
-        if (!r->n_frames && !r->n_windows) throw std::runtime_error("empty request");
-        auto j = std::unique_ptr<shv_cuda_job>(new shv_cuda_job());
-        j->frames = r->frames;
-        j->n_frames = r->n_frames;
-        j->tokens_out = r->n_frames ? r->tokens_out : nullptr;
-        if (r->store_slots && r->n_frames) {
-            if (!s.d_pool) throw std::runtime_error("store_slots needs options.token_slots > 0");
-            j->frame_store.assign(r->store_slots, r->store_slots + r->n_frames);
-            std::unordered_set<int32_t> seen;
-            for (int32_t sl : j->frame_store) {
-                if (sl < -1 || sl >= o.token_slots) throw std::runtime_error("store slot out of range");
-                if (sl >= 0 && !seen.insert(sl).second) throw std::runtime_error("duplicate store slot in one request");
-            }
+        if (!m || !r) throw ApiError("null argument");
+        Pipeline& p = *m->pipe;
+        const shv_cuda_options& o = p.opt;
+        if (r->n_frames > size_t(o.max_frames)) throw ApiError("request has more frames than max_frames");
+        if (r->n_windows > size_t(o.max_windows)) throw ApiError("request has more windows than max_windows");
+        if (r->n_frames && !r->frames) throw ApiError("null frames");
+        if (r->n_windows && !r->logits_out) throw ApiError("null logits_out");
+        if (!r->n_frames && !r->n_windows) throw ApiError("empty request");
+
+        std::unique_ptr<shv_cuda_job> job(new shv_cuda_job());
+        job->crops = r->frames;
+        job->n_crops = int(r->n_frames);
+        job->tokens_out = r->n_frames ? r->tokens_out : nullptr;
+        job->n_windows = int(r->n_windows);
+        job->logits_out = r->logits_out;
+        job->callback = r->callback;
+        job->user = r->user;
+        if (r->n_frames && r->store_slots) {
+            if (!p.pool) throw ApiError("store_slots needs options.token_slots > 0");
+            job->crop_slot.assign(r->store_slots, r->store_slots + r->n_frames);
+            require_distinct_slots(job->crop_slot, o.token_slots, true);
         }
-        j->n_windows = r->n_windows;
-        j->logits_out = r->logits_out;
-        j->cb = r->callback;
-        j->user = r->user;
-        const size_t entries = r->n_windows * 20;
-        j->wslots.assign(entries, -1);
-        if (r->window_frames && r->n_frames) j->wframes.assign(entries, -1);
+        // every window entry names exactly one source, in this order of precedence: frame, slot, host pointer
         std::vector<const float*> host;
-        host.reserve(entries);
-        for (size_t e = 0; e < entries; ++e) {
-            const int32_t wf = r->window_frames ? r->window_frames[e] : -1;
-            const int32_t ws = r->window_slots ? r->window_slots[e] : -1;
-            if (wf >= 0) {
-                if (size_t(wf) >= r->n_frames) throw std::runtime_error("window frame index out of range");
-                j->wframes[e] = wf;
-            } else if (ws >= 0) {
-                if (!s.d_pool || ws >= o.token_slots) throw std::runtime_error("window slot out of range");
-                j->wslots[e] = ws;
+        job->entries.reserve(r->n_windows * kWin);
+        for (size_t e = 0; e < r->n_windows * kWin; ++e) {
+            const int32_t frame = r->window_frames ? r->window_frames[e] : -1;
+            const int32_t slot = r->window_slots ? r->window_slots[e] : -1;
+            if (frame >= 0) {
+                if (size_t(frame) >= r->n_frames) throw ApiError("window frame index out of range");
+                job->entries.push_back(Entry{Src::Frame, frame});
+            } else if (slot >= 0) {
+                if (!p.pool || slot >= o.token_slots) throw ApiError("window slot out of range");
+                job->entries.push_back(Entry{Src::Slot, slot});
             } else {
-                if (!r->window_tokens || !r->window_tokens[e]) throw std::runtime_error("window entry has no token source");
-                host.push_back(r->window_tokens[e]);
+                const float* block = r->window_tokens ? r->window_tokens[e] : nullptr;
+                if (!block) throw ApiError("window entry has no token source");
+                job->entries.push_back(Entry{Src::Host, int32_t(host.size())});
+                host.push_back(block);
             }
         }
-        if (host.size() > size_t(o.max_host_tokens))
-            throw std::runtime_error("request has more host token blocks than max_host_tokens");
-        add_runs(*j, host.data(), host.size());
-        j->frames_pinned = host_pinned(r->frames, r->n_frames * kFrameBytes);
-        j->tokens_out_pinned = j->tokens_out && host_pinned(j->tokens_out, r->n_frames * kBlockBytes);
-        j->t_submit = Clock::now();
-        shv_cuda_job* raw = j.release();
-        if (!s.enqueue(raw)) {
-            delete raw;
-            throw std::runtime_error("model is stopping");
-        }
-        t_error.clear();
-        return raw;
+        if (host.size() > size_t(o.max_host_tokens)) throw ApiError("request has more host token blocks than max_host_tokens");
+        group_spans(*job, host);
+        job->crops_pinned = is_pinned(r->frames, r->n_frames * kCropBytes);
+        job->tokens_out_pinned = job->tokens_out && is_pinned(job->tokens_out, r->n_frames * kTokBytes);
+        job->submitted = Clock::now();
+        if (!p.accept(job.get())) throw ApiError("model is stopping");
+        tls_error.clear();
+        return job.release();
     } catch (const std::exception& e) {
-        t_error = e.what();
+        tls_error = e.what();
         return nullptr;
     }
 }
 
 int shv_cuda_job_status(const shv_cuda_job* j) {
     if (!j) return -1;
-    std::lock_guard<std::mutex> lk(j->m);
-    return j->state;
+    std::lock_guard<std::mutex> g(j->mu);
+    return j->outcome;
 }
+
 int shv_cuda_job_wait(shv_cuda_job* j) {
-    if (!j) { t_error = "null job"; return -1; }
-    std::unique_lock<std::mutex> lk(j->m);
-    j->cv.wait(lk, [&] { return j->state != 0; });
-    if (j->state < 0) { t_error = j->error; return -1; }
-    return 0;
+    if (!j) {
+        tls_error = "null job";
+        return -1;
+    }
+    std::unique_lock<std::mutex> lk(j->mu);
+    while (j->outcome == 0) j->cv.wait(lk);
+    if (j->outcome > 0) return 0;
+    tls_error = j->why;
+    return -1;
 }
+
 const char* shv_cuda_job_error(const shv_cuda_job* j) {
     if (!j) return "null job";
-    std::lock_guard<std::mutex> lk(j->m);
-    return j->error.c_str();
+    std::lock_guard<std::mutex> g(j->mu);
+    return j->why.c_str();
 }
-int shv_cuda_job_timing(const shv_cuda_job* j, double* queue_ms, double* run_ms, double* gpu_ms, int* bf, int* bw) {
+
+int shv_cuda_job_timing(const shv_cuda_job* j, double* queue_ms, double* run_ms, double* gpu_ms, int* batch_frames, int* batch_windows) {
     if (!j) return -1;
-    std::lock_guard<std::mutex> lk(j->m);
-    if (j->state == 0) return 1;
-    auto ms = [](Clock::duration d) { return std::chrono::duration<double, std::milli>(d).count(); };
-    if (queue_ms) *queue_ms = ms(j->t_start - j->t_submit);
-    if (run_ms) *run_ms = ms(j->t_done - j->t_start);
-    if (gpu_ms) *gpu_ms = j->gpu_ms;
-    if (bf) *bf = j->batch_frames;
-    if (bw) *bw = j->batch_windows;
+    std::lock_guard<std::mutex> g(j->mu);
+    if (j->outcome == 0) return 1;                               // still pending: nothing to report yet
+    using Ms = std::chrono::duration<double, std::milli>;
+    if (queue_ms) *queue_ms = Ms(j->started - j->submitted).count();
+    if (run_ms) *run_ms = Ms(j->finished - j->started).count();
+    if (gpu_ms) *gpu_ms = double(j->gpu_ms);
+    if (batch_frames) *batch_frames = j->batch_crops;
+    if (batch_windows) *batch_windows = j->batch_windows;
     return 0;
 }
+
 void shv_cuda_job_free(shv_cuda_job* j) {
     if (!j) return;
     {
-        std::unique_lock<std::mutex> lk(j->m);
-        j->cv.wait(lk, [&] { return j->released; });
+        std::unique_lock<std::mutex> lk(j->mu);
+        while (!j->settled) j->cv.wait(lk);
     }
     delete j;
 }
 
 void* shv_cuda_host_alloc(size_t bytes) {
     void* p = nullptr;
-    if (cudaHostAlloc(&p, bytes, cudaHostAllocPortable) != cudaSuccess) {
-        cudaGetLastError();
-        t_error = "cudaHostAlloc failed";
-        return nullptr;
-    }
-    return p;
+    if (cudaHostAlloc(&p, bytes, cudaHostAllocPortable) == cudaSuccess) return p;
+    cudaGetLastError();
+    tls_error = "cudaHostAlloc failed";
+    return nullptr;
 }
+
 void shv_cuda_host_free(void* p) {
     if (p) cudaFreeHost(p);
 }
 
 int shv_cuda_encode_frames(shv_cuda_model* m, const uint8_t* rgb, size_t n, float* tokens) {
-    return guarded([&]() -> int {
-        if (!m || (n && (!rgb || !tokens))) throw std::runtime_error("null argument");
-        const size_t step = size_t(m->sched->opt.max_frames);
-        std::vector<shv_cuda_job*> jobs;
-        for (size_t off = 0; off < n; off += step) {
-            shv_cuda_request r{};
-            r.frames = rgb + off * kFrameBytes;
-            r.n_frames = std::min(step, n - off);
-            r.tokens_out = tokens + off * kBlockFloats;
-            shv_cuda_job* j = shv_cuda_submit(m, &r);
-            if (!j) {
-                const std::string why = t_error;
-                wait_and_free(jobs);
-                std::fill(tokens, tokens + n * kBlockFloats, kNaN);
-                throw std::runtime_error(why);
-            }
-            jobs.push_back(j);
-        }
-        return wait_and_free(jobs);
-    });
+    if (!m || (n && (!rgb || !tokens))) {
+        tls_error = "null argument";
+        return -1;
+    }
+    const size_t piece = size_t(m->pipe->opt.max_frames);
+    return run_in_pieces(
+        m, n, piece,
+        [&](size_t first, size_t count, shv_cuda_request& r) {
+            r.frames = rgb + first * kCropBytes;
+            r.n_frames = count;
+            r.tokens_out = tokens + first * kTokFloats;
+        },
+        [&] { std::fill(tokens, tokens + n * kTokFloats, kUnavailable); });
 }
 
 int shv_cuda_predict(shv_cuda_model* m, const uint8_t* clips, size_t b, float* logits) {
-    return guarded([&]() -> int {
-        if (!m || (b && (!clips || !logits))) throw std::runtime_error("null argument");
-        const shv_cuda_options& o = m->sched->opt;
-        const size_t step = size_t(std::min(o.max_windows, o.max_frames / 20));
-        if (step < 1) throw std::runtime_error("predict needs max_frames >= 20");
-        std::vector<int32_t> idx(step * 20);
-        for (size_t e = 0; e < idx.size(); ++e) idx[e] = int32_t(e);
-        std::vector<shv_cuda_job*> jobs;
-        for (size_t off = 0; off < b; off += step) {
-            const size_t w = std::min(step, b - off);
-            shv_cuda_request r{};
-            r.frames = clips + off * 20 * kFrameBytes;
-            r.n_frames = w * 20;
-            r.n_windows = w;
-            r.window_frames = idx.data();
-            r.logits_out = logits + off;
-            shv_cuda_job* j = shv_cuda_submit(m, &r);
-            if (!j) {
-                const std::string why = t_error;
-                wait_and_free(jobs);
-                std::fill(logits, logits + b, kNaN);
-                throw std::runtime_error(why);
-            }
-            jobs.push_back(j);
-        }
-        return wait_and_free(jobs);
-    });
+    if (!m || (b && (!clips || !logits))) {
+        tls_error = "null argument";
+        return -1;
+    }
+    const shv_cuda_options& o = m->pipe->opt;
+    const size_t piece = size_t(std::min(o.max_windows, o.max_frames / kWin));
+    if (b && piece < 1) {
+        tls_error = "predict needs max_frames >= 20";
+        return -1;
+    }
+    std::vector<int32_t> own_frames(std::max<size_t>(piece, 1) * kWin);   // window w, position f -> frame w * 20 + f of the same request
+    for (size_t e = 0; e < own_frames.size(); ++e) own_frames[e] = int32_t(e);
+    return run_in_pieces(
+        m, b, std::max<size_t>(piece, 1),
+        [&](size_t first, size_t count, shv_cuda_request& r) {
+            r.frames = clips + first * kWin * kCropBytes;
+            r.n_frames = count * kWin;
+            r.n_windows = count;
+            r.window_frames = own_frames.data();
+            r.logits_out = logits + first;
+        },
+        [&] { std::fill(logits, logits + b, kUnavailable); });
 }
 
 int shv_cuda_classify(shv_cuda_model* m, const float* tokens, size_t b, float* logits) {
-    return guarded([&]() -> int {
-        if (!m || (b && (!tokens || !logits))) throw std::runtime_error("null argument");
-        const shv_cuda_options& o = m->sched->opt;
-        if (o.max_host_tokens < 20) throw std::runtime_error("classify needs max_host_tokens >= 20");
-        const size_t step = size_t(std::max(1, std::min(o.max_windows, o.max_host_tokens / 20)));
-        std::vector<shv_cuda_job*> jobs;
-        std::vector<const float*> ptrs;
-        for (size_t off = 0; off < b; off += step) {
-            const size_t w = std::min(step, b - off);
-            ptrs.resize(w * 20);
-            for (size_t e = 0; e < w * 20; ++e) ptrs[e] = tokens + (off * 20 + e) * kBlockFloats;
-            shv_cuda_request r{};
-            r.n_windows = w;
-            r.window_tokens = ptrs.data();
-            r.logits_out = logits + off;
-            shv_cuda_job* j = shv_cuda_submit(m, &r);
-            if (!j) {
-                const std::string why = t_error;
-                wait_and_free(jobs);
-                std::fill(logits, logits + b, kNaN);
-                throw std::runtime_error(why);
-            }
-            jobs.push_back(j);
-        }
-        return wait_and_free(jobs);
-    });
+    if (!m || (b && (!tokens || !logits))) {
+        tls_error = "null argument";
+        return -1;
+    }
+    const shv_cuda_options& o = m->pipe->opt;
+    if (b && o.max_host_tokens < kWin) {
+        tls_error = "classify needs max_host_tokens >= 20";
+        return -1;
+    }
+    // Pieces of at most a batch, and small enough that a large call becomes a train of requests whose uploads overlap
+    // the kernels of the requests before them (the feeder closes batches early while the pipeline is filling).
+    const size_t fit = size_t(std::max(1, std::min(o.max_windows, o.max_host_tokens / kWin)));
+    const size_t piece = std::min(fit, size_t(m->pipe->upload_windows()));
+    std::vector<std::vector<const float*>> ptrs;                 // one pointer list per request, alive until the call returns
+    ptrs.reserve((b + piece - 1) / piece + 1);
+    return run_in_pieces(
+        m, b, piece,
+        [&](size_t first, size_t count, shv_cuda_request& r) {
+            ptrs.emplace_back(count * kWin);
+            std::vector<const float*>& list = ptrs.back();
+            for (size_t e = 0; e < list.size(); ++e) list[e] = tokens + (first * kWin + e) * kTokFloats;
+            r.n_windows = count;
+            r.window_tokens = list.data();
+            r.logits_out = logits + first;
+        },
+        [&] { std::fill(logits, logits + b, kUnavailable); });
 }
 
 // ---------------------------------------------------------------- extensions (include/shv_cuda_b200.h)
 int shv_cuda_b200_upload_tokens(shv_cuda_model* m, const float* tokens, size_t n, const int32_t* slots) {
-    return guarded([&]() -> int {
-        if (!m || (n && (!tokens || !slots))) throw std::runtime_error("null argument");
-        Scheduler& s = *m->sched;
-        if (!s.d_pool) throw std::runtime_error("upload_tokens needs options.token_slots > 0");
-        if (s.block_cap() < 1) throw std::runtime_error("upload_tokens needs max_host_tokens >= 1");
-        const size_t step = size_t(s.block_cap());
-        std::vector<shv_cuda_job*> jobs;
-        for (size_t off = 0; off < n; off += step) {
-            const size_t cnt = std::min(step, n - off);
-            auto j = std::unique_ptr<shv_cuda_job>(new shv_cuda_job());
-            std::unordered_set<int32_t> seen;
-            for (size_t i = 0; i < cnt; ++i) {
-                const int32_t sl = slots[off + i];
-                if (sl < 0 || sl >= s.opt.token_slots) throw std::runtime_error("store slot out of range");
-                if (!seen.insert(sl).second) throw std::runtime_error("duplicate store slot in one request");
-                j->store_slots.push_back(sl);
-            }
-            std::vector<const float*> ptrs(cnt);
-            for (size_t i = 0; i < cnt; ++i) ptrs[i] = tokens + (off + i) * kBlockFloats;
-            add_runs(*j, ptrs.data(), cnt);
-            j->t_submit = Clock::now();
-            shv_cuda_job* raw = j.release();
-            if (!s.enqueue(raw)) {
-                delete raw;
-                wait_and_free(jobs);
-                throw std::runtime_error("model is stopping");
-            }
-            jobs.push_back(raw);
+    try {
+        if (!m || (n && (!tokens || !slots))) throw ApiError("null argument");
+        Pipeline& p = *m->pipe;
+        if (!p.pool) throw ApiError("upload_tokens needs options.token_slots > 0");
+        if (p.block_cap() < 1) throw ApiError("upload_tokens needs max_host_tokens >= 1");
+        const size_t piece = size_t(p.block_cap());
+        // validate everything before anything is queued: a bad slot must not leave half the upload done
+        std::vector<std::unique_ptr<shv_cuda_job>> ready;
+        for (size_t first = 0; first < n; first += piece) {
+            const size_t count = std::min(piece, n - first);
+            std::unique_ptr<shv_cuda_job> job(new shv_cuda_job());
+            job->host_slot.assign(slots + first, slots + first + count);
+            require_distinct_slots(job->host_slot, p.opt.token_slots, false);
+            std::vector<const float*> blocks(count);
+            for (size_t i = 0; i < count; ++i) blocks[i] = tokens + (first + i) * kTokFloats;
+            group_spans(*job, blocks);
+            ready.push_back(std::move(job));
         }
-        return wait_and_free(jobs);
-    });
+        std::vector<shv_cuda_job*> queued;
+        for (std::unique_ptr<shv_cuda_job>& job : ready) {
+            job->submitted = Clock::now();
+            if (!p.accept(job.get())) {
+                settle_all(queued);
+                throw ApiError("model is stopping");
+            }
+            queued.push_back(job.release());
+        }
+        const int rc = settle_all(queued);
+        if (rc == 0) tls_error.clear();
+        return rc;
+    } catch (const std::exception& e) {
+        tls_error = e.what();
+        return -1;
+    }
 }
 
-int shv_cuda_b200_launches_per_batch(const shv_cuda_model* m) { return m ? m->sched->engine->launches_per_classify() : 0; }
+int shv_cuda_b200_launches_per_batch(const shv_cuda_model* m) { return m ? m->pipe->engine->launches_per_classify() : 0; }
 
 int shv_cuda_b200_test_starve(shv_cuda_model* m, int kind, int batches) {
 #ifdef SHV_CUDA_EXPERIMENTAL
-    return guarded([&]() -> int {
-        if (!m) throw std::runtime_error("null model");
-        m->sched->request_starve(kind, batches);
+    try {
+        if (!m) throw ApiError("null model");
+        m->pipe->arm_starved_launch(kind, batches);
         return 0;
-    });
+    } catch (const std::exception& e) {
+        tls_error = e.what();
+        return -1;
+    }
 #else
     (void)m; (void)kind; (void)batches;
-    t_error = "test hooks exist in the experimental library only";
+    tls_error = "test hooks exist in the experimental library only";
     return -1;
 #endif
 }

@@ -7,7 +7,8 @@
 //       | o-proj GEMM + residual -> h | norm h -> xn
 //   2 FFNs: up GEMM + SwiGLU -> hid | down GEMM + residual -> h | norm -> xn
 //   SISA: all-row GEMM + bias -> S [M,1072] fp32 (aliases P); readout row: norm, QC GEMM, attention kernel,
-//       W_O + residual, norm, FFN, head -> logits.  Everything on the readout row is fp32 in every mode.
+//       W_O + residual, norm, FFN, head -> logits, as two fused kernels around the attention kernel.  Everything on
+//       the readout row is fp32 in every mode.
 //
 // encode (F frames, reference run_encode engine/cuda/engine.cu:338-403): stem -> 15 inverted-residual blocks
 //   (expand 1x1 | depthwise | squeeze-excite gate | project 1x1 with the gate applied to its input rows, + residual)
@@ -183,7 +184,7 @@ public:
         starve_kind_ = kind;
         starve_batches_ = batches > 0 ? batches : 0;
     }
-    int launches_per_classify() const override { return 28; }
+    int launches_per_classify() const override { return 22; }
 
     // One eager classify / encode with an event after every launch; returns (kernel name, milliseconds) per launch.
     std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) override {
@@ -206,14 +207,15 @@ private:
     std::vector<std::unique_ptr<Arena>> slot_mem_;
     const float *pos_ = nullptr, *readout_ = nullptr;
     GdnDev gdn_[2]{};
-    const float *s_attn_norm_ = nullptr, *s_b_all_ = nullptr, *s_w_qc_ = nullptr, *s_w_o_ = nullptr, *s_lambda_ = nullptr;
-    const float *s_ffn_norm_ = nullptr, *s_ffn_up_ = nullptr, *s_ffn_down_ = nullptr;
+    const float *s_attn_norm_ = nullptr, *s_b_all_ = nullptr, *s_lambda_ = nullptr;
+    const float *s_ffn_norm_ = nullptr;
+    const float *s_wqc_t_ = nullptr, *s_wo_t_ = nullptr, *s_up_t_ = nullptr, *s_down_t_ = nullptr;   // readout-row matrices, [K][N]
     const void* s_w_all_ = nullptr;
     const float *fn_w_ = nullptr, *h_w0t_ = nullptr, *h_b0_ = nullptr, *h_w2_ = nullptr, *h_b2_ = nullptr;
     // activations
     float *h_ = nullptr, *P_ = nullptr;
     void *xn_ = nullptr, *on_ = nullptr, *hid_ = nullptr;
-    float *xl_ = nullptr, *qc_ = nullptr, *y_ = nullptr, *x1_ = nullptr, *x2_ = nullptr, *hidl_ = nullptr;
+    float *qc_ = nullptr, *y_ = nullptr, *x2_ = nullptr;
     Site in_[2], oproj_[2], up_[2], down_[2], sisa_in_;
     alignas(64) unsigned char inproj_plan_[2][512];   // 16-bit modes: fused in-projection (TMA maps for xn, W', PT = P_)
     int starve_kind_ = 0, starve_batches_ = 0;        // test hook: see inject_wait_timeout
@@ -336,8 +338,17 @@ private:
         const SisaHost& sh = hm.sisa;
         f32(&s_attn_norm_, sh.attn_norm_w);
         stor(&s_w_all_, sh.w_all);
-        f32(&s_b_all_, sh.b_all); f32(&s_w_qc_, sh.w_qc); f32(&s_w_o_, sh.w_o); f32(&s_lambda_, sh.lambda_raw);
-        f32(&s_ffn_norm_, sh.ffn_norm_w); f32(&s_ffn_up_, sh.ffn_up); f32(&s_ffn_down_, sh.ffn_down);
+        f32(&s_b_all_, sh.b_all); f32(&s_lambda_, sh.lambda_raw);
+        f32(&s_ffn_norm_, sh.ffn_norm_w);
+        // the readout-row kernels read their matrices column-wise across a warp: [K][N] copies
+        auto transposed = [](const std::vector<float>& w, int n, int k) {
+            std::vector<float> t(w.size());
+            for (int r = 0; r < n; ++r)
+                for (int c = 0; c < k; ++c) t[size_t(c) * n + r] = w[size_t(r) * k + c];
+            return t;
+        };
+        f32(&s_wqc_t_, transposed(sh.w_qc, SQN, D)); f32(&s_wo_t_, transposed(sh.w_o, D, D));
+        f32(&s_up_t_, transposed(sh.ffn_up, 2 * DFF, D)); f32(&s_down_t_, transposed(sh.ffn_down, D, DFF));
         f32(&fn_w_, hm.final_norm_w);
         std::vector<float> w0t(size_t(D) * 128);            // [D][128]: the head kernel reads consecutive outputs
         for (int o = 0; o < 128; ++o)
@@ -364,8 +375,7 @@ private:
         const size_t Bm = size_t(cfg_.max_windows), Mm = Bm * NTOK, Fm = size_t(cfg_.max_frames), ts = dtype_bytes(prec_);
         const size_t o_h = acts_.reserve(Mm * D * 4), o_p = acts_.reserve(Mm * GLD * 4), o_xn = acts_.reserve(Mm * D * ts);
         const size_t o_on = acts_.reserve(Mm * VD * ts), o_hid = acts_.reserve(Mm * DFF * ts);
-        const size_t o_xl = acts_.reserve(Bm * D * 4), o_qc = acts_.reserve(Bm * SQN * 4), o_y = acts_.reserve(Bm * D * 4);
-        const size_t o_x1 = acts_.reserve(Bm * D * 4), o_x2 = acts_.reserve(Bm * D * 4), o_hl = acts_.reserve(Bm * DFF * 4);
+        const size_t o_qc = acts_.reserve(Bm * SQN * 4), o_y = acts_.reserve(Bm * D * 4), o_x2 = acts_.reserve(Bm * D * 4);
         // frame encoder: block input / output X, expanded E, depthwise output Dd (largest layer of each kind), the
         // squeeze-excite partial sums and gates, the pooled map
         size_t x_fl = size_t(90) * 160 * 16, e_fl = size_t(60) * CNN_OUT, d_fl = 0, part_fl = 0;
@@ -383,8 +393,7 @@ private:
         se_part_ = acts_.at<float>(o_sp); se_gate_ = acts_.at<float>(o_sg); pooled_ = acts_.at<float>(o_po);
         h_ = acts_.at<float>(o_h); P_ = acts_.at<float>(o_p);
         xn_ = acts_.at<void>(o_xn); on_ = acts_.at<void>(o_on); hid_ = acts_.at<void>(o_hid);
-        xl_ = acts_.at<float>(o_xl); qc_ = acts_.at<float>(o_qc); y_ = acts_.at<float>(o_y);
-        x1_ = acts_.at<float>(o_x1); x2_ = acts_.at<float>(o_x2); hidl_ = acts_.at<float>(o_hl);
+        qc_ = acts_.at<float>(o_qc); y_ = acts_.at<float>(o_y); x2_ = acts_.at<float>(o_x2);
         act_bytes_ = acts_.size();
 
         slots_.resize(size_t(cfg_.slots));
@@ -392,7 +401,8 @@ private:
             slot_mem_.emplace_back(new Arena());
             Arena& a = *slot_mem_.back();
             const size_t o_frm = a.reserve(Fm * IMG_H * IMG_W * 3);
-            const size_t o_tok = a.reserve(Fm * 16 * D * 4), o_stage = a.reserve(Bm * FRAMES * 16 * D * 4);
+            const size_t stage_blocks = cfg_.max_host_blocks >= 0 ? size_t(std::max(cfg_.max_host_blocks, 1)) : Bm * FRAMES;
+            const size_t o_tok = a.reserve(Fm * 16 * D * 4), o_stage = a.reserve(stage_blocks * 16 * D * 4);
             const size_t o_ptr = a.reserve(Bm * FRAMES * sizeof(float*)), o_log = a.reserve(Bm * 4);
             a.commit("slot buffers");
             Slot& sl = slots_[size_t(i)];
@@ -450,16 +460,6 @@ private:
             launch_ok(shvk_gemm_f32(&a, s), "fp32 GEMM");
         }
     }
-    // fp32 GEMM on the B readout rows
-    void last_gemm(int B, int N, int K, const float* A, const float* W, float* C, const float* R, long long ldr, int swiglu,
-                   cudaStream_t s) {
-        shvk_gemm_args a{};
-        a.M = B; a.N = N; a.K = K; a.A = A; a.lda = K; a.W = W; a.ldw = K;
-        a.C = C; a.ldc = swiglu ? N / 2 : N; a.c_dtype = SHVK_F32;
-        a.R = R; a.ldr = ldr; a.r_div = 1.0f; a.swiglu = swiglu;
-        launch_ok(shvk_gemm_f32(&a, s), "readout-row GEMM");
-    }
-
     // ---------------------------------------------------------------- debug dumps
     void dump(const char* name, const void* dev, size_t n, int dtype, cudaStream_t s) {
         if (dump_dir_.empty()) return;
@@ -590,24 +590,15 @@ private:
         mark("gemm.sisa_in", s);
         const float* h_last = h_ + size_t(NTOK - 1) * D;
         const long long ld_last = (long long)NTOK * D;
-        launch_ok(shvk_rmsnorm(h_last, ld_last, s_attn_norm_, xl_, SHVK_F32, D, B, s), "rmsnorm (readout)");
-        mark("readout.rmsnorm", s);
-        last_gemm(B, SQN, D, xl_, s_w_qc_, qc_, nullptr, 0, 0, s);
-        mark("readout.gemm_qc", s);
+        launch_ok(shvk_readout_qc(h_last, ld_last, s_attn_norm_, s_wqc_t_, qc_, B, s), "readout q / c");
+        mark("readout.qc", s);
         launch_ok(shvk_sisa_attn(S, qc_, s_lambda_, y_, B, s), "sisa attention");
         mark("sisa_attn", s);
         dump("sisa.y", y_, size_t(D), SHVK_F32, s);
-        last_gemm(B, D, D, y_, s_w_o_, x1_, h_last, ld_last, 0, s);
-        mark("readout.gemm_wo", s);
-        launch_ok(shvk_rmsnorm(x1_, D, s_ffn_norm_, xl_, SHVK_F32, D, B, s), "rmsnorm (readout ffn)");
-        mark("readout.rmsnorm", s);
-        last_gemm(B, 2 * DFF, D, xl_, s_ffn_up_, hidl_, nullptr, 0, 1, s);
-        mark("readout.gemm_ffn_up", s);
-        last_gemm(B, D, DFF, hidl_, s_ffn_down_, x2_, x1_, D, 0, s);
-        mark("readout.gemm_ffn_down", s);
+        const shvk_readout_weights rw{s_wo_t_, s_ffn_norm_, s_up_t_, s_down_t_, fn_w_, h_w0t_, h_b0_, h_w2_, h_b2_};
+        launch_ok(shvk_readout_tail(y_, h_last, ld_last, &rw, x2_, sl.d_logits, B, s), "readout tail");
+        mark("readout.tail", s);
         dump("after_sisa_row", x2_, size_t(D), SHVK_F32, s);
-        launch_ok(shvk_head(x2_, fn_w_, h_w0t_, h_b0_, h_w2_, h_b2_, sl.d_logits, B, s), "head");
-        mark("head", s);
         dump("logit", sl.d_logits, 1, SHVK_F32, s);
     }
 };

@@ -26,6 +26,7 @@ struct EngineConfig {
     int max_windows = 512;   // windows per classify launch
     bool use_graphs = true;  // one CUDA graph per (slot, bucket); off for dumps and debugging
     int slots = 2;           // input/output buffer sets, so the scheduler can stage batch n+1 while n runs
+    int max_host_blocks = -1;  // token blocks a slot's upload area holds (d_tok_stage); -1 = max_windows * 20
 };
 
 class Engine {

@@ -5,22 +5,26 @@
 // channels of a tile on the MMA rows (= tensor-memory lanes) and the tokens of a clip on the accumulator columns.
 // An epilogue thread therefore owns ONE channel and finds consecutive tokens in consecutive registers, so the
 // 4-tap causal convolution runs along registers (three carried values, no shuffles, no shared memory), and what
-// leaves the kernel is not the fp32 projection [321][2316] but the bf16 operand tiles the scan multiplies with, in the
+// leaves the kernel is not the fp32 projection [321][2316] but the 16-bit operand tiles the scan multiplies with, in the
 // chunk-blocked layout of gdn_pt_layout.cuh: 1.56 MB per clip written here and read once by the scan, instead of
 // 2.97 MB each way.  Stores need no staging: a thread writes the 32 contiguous bytes of its channel row of a chunk,
 // a warp 1 KB contiguous.
 //
 // Channel tiles (rows of W', permuted from the reference's fused layout [q | k | v | gate | a | b] by
 // shvk_gdn_inproj_row_order): tile 3h = [q_h | k_h], 3h + 1 = v_h, 3h + 2 = gate_h for head h; tile 18 = [a | b | 0].
-// Token tiles per clip: tokens 0..175 (accumulator 0) and 176..335 (accumulator 1; 321.. are written as zeros).
-// One work item = (clip, channel tile) = both token tiles; items are dealt round-robin to the persistent CTAs, so
-// neighbouring CTAs work on the same clip and share its xn rows in L2.
+// Token tiles per clip: tokens 0..175 and tokens 160..335 (176 columns each; the second tile computes tokens 160..175
+// again only as the convolution's history and writes chunks 11..20; token slots 321.. are written as zeros).
+// One work item = (clip, token tile) = all 19 channel tiles: the item's xn rows (176 x 384, 132 KB) are brought into
+// shared memory ONCE and stay there while the 19 weight tiles stream past them through a five-stage ring, so the
+// operand traffic out of L2 is 4.0 MB per clip instead of 8.6 MB with both operands streamed (which alone took
+// 2.0 ms per launch at 4096 clips, more than the products).  Neighbouring CTAs take the two tiles of one clip.
 //
-// Roles (320 threads): warp 0 TMA producer (W' tile 128 x 64 and xn tile N x 64 per stage, 128-byte swizzle, no
-// multicast), warp 1 MMA issuer (tcgen05.mma M 128, N 176 / 160, K 16) and owner of tensor memory, warps 2-5 epilogue
-// of accumulator 0, warps 6-9 epilogue of accumulator 1.  The conv history of token 176 is tokens 173..175, which
-// the second group reads from accumulator 0 before that is released.  K is walked in order and never split; a token's
-// column depends on no other token of the batch, so clips stay independent bitwise.
+// Roles (352 threads): warp 0 streams W' tiles (TMA, 128-byte swizzle, no multicast), warp 2 loads the xn tile of the
+// next item as soon as the last product of the current one has read it, warp 1 issues tcgen05.mma (M 128, N 176,
+// K 16) into one of two accumulators and owns tensor memory, warps 3-10 are the epilogue: two warps per lane quadrant,
+// one for the first six chunks of the accumulator and one for the other five (it reads its three history columns
+// from the neighbour's range).  K is walked in order and never split; a token's column depends on no other token of
+// the batch, so clips stay independent bitwise.
 //
 // Every mbarrier wait is bounded (status word of the tensor-core GEMM, shvk_gemm_tc_status).
 //
@@ -34,34 +38,45 @@
 #include "tma_utils.cuh"
 
 #include <atomic>
+#include <stdlib.h>
 #include <string.h>
 
 namespace sb {
 namespace {
 using namespace tc;
 
-constexpr int TILE_M = 128, TILE_K = 64, N0 = 176, N1 = 160, M_TILES = 19, KBLOCKS = kD / TILE_K;
+constexpr int TILE_M = 128, TILE_K = 64, NT = 176, TT_STRIDE = 160, M_TILES = 19, KBLOCKS = kD / TILE_K;
 constexpr int W_ROWS = M_TILES * TILE_M;                         // 2432 rows of W' (2316 used)
-constexpr int A_BYTES = TILE_M * TILE_K * 2, B_BYTES = N0 * TILE_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 4, BAR_BYTES = 128;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
-constexpr int NTHREADS = 320;
+constexpr int W_STAGE_BYTES = TILE_M * TILE_K * 2, W_STAGES = 5;
+constexpr int XN_KB_BYTES = NT * TILE_K * 2, XN_BYTES = KBLOCKS * XN_KB_BYTES;
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_BYTES = XN_BYTES + W_STAGES * W_STAGE_BYTES + BAR_BYTES + 1024;
+constexpr int NTHREADS = 352;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-static_assert(N0 + N1 == pt::TOK_PAD && N0 % pt::CHUNK == 0, "token tiles cover the padded clip in whole chunks");
-static_assert(STAGE_BYTES % 1024 == 0 && A_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
-static_assert((2 * STAGES + 4) * 8 <= BAR_BYTES && SMEM_BYTES <= 232448, "shared memory budget");
+static_assert(TT_STRIDE + NT == pt::TOK_PAD && TT_STRIDE % pt::CHUNK == 0 && NT % pt::CHUNK == 0, "token tiles cover the padded clip in whole chunks");
+static_assert(XN_KB_BYTES % 1024 == 0 && W_STAGE_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert((2 * W_STAGES + 6) * 8 <= BAR_BYTES && SMEM_BYTES <= 232448, "shared memory budget");
 
 struct InprojMaps {
     CUtensorMap w;        // W' [2432][384], box 128 x 64
-    CUtensorMap x0, x1;   // xn [rows][384], boxes 176 x 64 and 160 x 64
+    CUtensorMap x;        // xn [rows][384], box 176 x 64
 };
 struct InprojParams {
     int B;
-    uint32_t idesc0, idesc1;
+    uint32_t idesc;
     const float *conv_w, *conv_b, *a_log, *dt_bias;
     uint8_t* pt;
     uint32_t spin_limit;
+    int qk_f16;      // q^T / k^T tiles in fp16 (fp16 mode) instead of bf16
+    int probe;       // timing probes of a development build (-DSHVK_DEV_PROBES, SHVK_INPROJ_PROBE): 1 no global stores,
+                     // 2 no activation arithmetic, 4 no tensor-memory loads, 8 no MMA.  Constant 0 in the shipped libraries.
 };
+#ifdef SHVK_DEV_PROBES
+__device__ int g_inproj_probe = 0;
+#define INPROJ_PROBE(bit) (g_inproj_probe & (bit))
+#else
+#define INPROJ_PROBE(bit) 0
+#endif
 
 // x * sigmoid(x) = 0.5 x (1 + tanh(x / 2)) with the hardware tanh: absolute error ~5e-4 |x|, below the bf16 rounding
 // that follows
@@ -75,117 +90,189 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+    uint32_t r;                                                     // saturating: a finite fp16 even where fp32 exceeds 65504
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 __device__ __forceinline__ void stg128(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-enum : int { KIND_CONV = 0, KIND_SILU = 1, KIND_GATES = 2 };
+// What an epilogue does with its channel: q, k (conv + SiLU, stored in the mode's operand type: KIND_CONV_BF16 or
+// KIND_CONV_F16), v (conv + SiLU, fp16), output gate (SiLU, fp16), a | b (log decay and beta, fp32).
+enum : int { KIND_CONV_BF16 = 0, KIND_CONV_F16 = 1, KIND_SILU = 2, KIND_GATES = 3 };
 
 struct ChanConst {            // what the epilogue thread knows about its channel
     float4 w;                 // conv taps: tap j multiplies x[t - 3 + j]
     float bias;
     float rate, dtb;          // KIND_GATES, decay rows: -exp(A_log), dt_bias
     bool is_beta, active;     // KIND_GATES: beta row; lane has a channel at all
+    int half0;                // byte offset (0 or 16) of tokens 0-7 within the channel's 32-byte row of a chunk block
 };
 
-// One token tile of one channel: NCOLS accumulator columns starting at tensor-memory address taddr, tokens TOK0 ..
-// TOK0 + NCOLS - 1 of the clip, written to this channel's rows of the chunk blocks starting at dst (chunk TOK0 / 16).
-// x1, x2, x3: raw projections of tokens TOK0 - 1, - 2, - 3 (KIND_CONV).
-template <int KIND, int TOK0, int NCOLS>
-__device__ __forceinline__ void emit_tile(uint32_t taddr, uint8_t* dst, const ChanConst& cc, float x1, float x2, float x3) {
-    constexpr int NB = (NCOLS + 31) / 32;
-    uint32_t r[2][32];
-    tc_ld32(taddr, r[0]);
+// Sixteen accumulator columns = one chunk of 16 tokens of one channel: activation, packing, and the channel's 32-byte
+// (KIND_GATES: 64-byte) row of the chunk block at `row`.  nvalid: how many of the 16 token slots lie inside the clip
+// (16 everywhere except in the clip's last chunk); the others are written as zeros.  x1, x2, x3: raw projections of the
+// three tokens before this chunk (conv kinds), updated to the chunk's last three.
+template <int KIND>
+__device__ __forceinline__ void emit_chunk(const uint32_t (&in)[16], uint8_t* row, const ChanConst& cc, int nvalid,
+                                           float& x1, float& x2, float& x3) {
+    if (KIND == KIND_GATES) {
+        uint32_t v[16];
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
-        tc_wait_ld();
-        if (b + 1 < NB) {
-            if (NCOLS - 32 * (b + 1) >= 32) tc_ld32(taddr + uint32_t(32 * (b + 1)), r[(b + 1) & 1]);
-            else tc_ld16(taddr + uint32_t(32 * (b + 1)), r[(b + 1) & 1]);
+        for (int j = 0; j < 16; ++j) {
+            const float raw = __uint_as_float(in[j]);
+            float o;
+            if (cc.is_beta) {
+                o = __fdividef(1.0f, 1.0f + __expf(-raw));
+            } else {
+                const float ax = raw + cc.dtb;
+                o = cc.rate * (ax > 15.0f ? ax : __logf(1.0f + __expf(ax)));
+            }
+            v[j] = __float_as_uint(o);
         }
-        const int ncol = NCOLS - 32 * b >= 32 ? 32 : 16;          // compile-time after unrolling
-        const uint32_t* in = r[b & 1];
-        if (KIND == KIND_GATES) {
-            float v[32];
+        if (nvalid < 16) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                if (j < ncol) {
-                    const float raw = __uint_as_float(in[j]);
-                    float o;
-                    if (cc.is_beta) {
-                        o = __fdividef(1.0f, 1.0f + __expf(-raw));
-                    } else {
-                        const float ax = raw + cc.dtb;
-                        o = cc.rate * (ax > 15.0f ? ax : __logf(1.0f + __expf(ax)));
-                    }
-                    v[j] = (TOK0 + 32 * b + j < kTok) ? o : 0.0f;
+            for (int j = 0; j < 16; ++j) v[j] = j < nvalid ? v[j] : 0u;
+        }
+        if (cc.active) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) stg128(row + 16 * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        }
+    } else {
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+            float y[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float raw = __uint_as_float(in[j + e]);
+                float a = raw;
+                if (KIND == KIND_CONV_BF16 || KIND == KIND_CONV_F16) {
+                    a = fmaf(cc.w.x, x3, cc.bias);
+                    a = fmaf(cc.w.y, x2, a);
+                    a = fmaf(cc.w.z, x1, a);
+                    a = fmaf(cc.w.w, raw, a);
+                    x3 = x2; x2 = x1; x1 = raw;
                 }
+                y[e] = INPROJ_PROBE(2) ? raw : silu_tanh(a);
             }
-            if (cc.active) {
+            o[j >> 1] = KIND == KIND_CONV_BF16 ? pack_bf16(y[0], y[1]) : pack_f16(y[0], y[1]);
+        }
+        if (nvalid < 16) {                                        // the clip's last chunk: zero the token slots past its end
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    if (16 * c < ncol) {
-                        uint8_t* row = dst + (long long)(2 * b + c) * pt::BLOCK_BYTES;
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            stg128(row + 16 * q, __float_as_uint(v[16 * c + 4 * q]), __float_as_uint(v[16 * c + 4 * q + 1]),
-                                   __float_as_uint(v[16 * c + 4 * q + 2]), __float_as_uint(v[16 * c + 4 * q + 3]));
-                    }
-                }
-            }
-        } else {
-            uint32_t o[16];
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-                if (j < ncol) {
-                    float y[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const float raw = __uint_as_float(in[j + e]);
-                        float a = raw;
-                        if (KIND == KIND_CONV) {
-                            a = fmaf(cc.w.x, x3, cc.bias);
-                            a = fmaf(cc.w.y, x2, a);
-                            a = fmaf(cc.w.z, x1, a);
-                            a = fmaf(cc.w.w, raw, a);
-                            x3 = x2; x2 = x1; x1 = raw;
-                        }
-                        y[e] = (TOK0 + 32 * b + j + e < kTok) ? silu_tanh(a) : 0.0f;
-                    }
-                    o[j >> 1] = pack_bf16(y[0], y[1]);
-                }
-            }
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                if (16 * c < ncol) {
-                    uint8_t* row = dst + (long long)(2 * b + c) * pt::BLOCK_BYTES;
-                    stg128(row, o[8 * c], o[8 * c + 1], o[8 * c + 2], o[8 * c + 3]);
-                    stg128(row + 16, o[8 * c + 4], o[8 * c + 5], o[8 * c + 6], o[8 * c + 7]);
-                }
-            }
+            for (int i = 0; i < 8; ++i) o[i] = (2 * i < nvalid ? (o[i] & 0x0000ffffu) : 0u) | (2 * i + 1 < nvalid ? (o[i] & 0xffff0000u) : 0u);
+        }
+        // the two 16-byte halves of the row trade places in rows 4-7 of every eight, so that the scan's ldmatrix reads
+        // (eight rows of one half at a time) fall into eight different bank groups
+        if (!INPROJ_PROBE(1)) {
+            stg128(row + cc.half0, o[0], o[1], o[2], o[3]);
+            stg128(row + (cc.half0 ^ 16), o[4], o[5], o[6], o[7]);
+        } else if (o[0] == 0x12345678u && o[7] == 0x9abcdef0u) {
+            stg128(row, o[0], o[1], o[2], o[3]);          // keeps the arithmetic alive
         }
     }
+}
+
+// One token tile of one channel: ncols accumulator columns (a multiple of 16) starting at tensor-memory address taddr,
+// tokens tok0 .. tok0 + ncols - 1 of the clip, written to this channel's rows of the chunk blocks starting at dst (chunk
+// tok0 / 16).  x1, x2, x3: raw projections of tokens tok0 - 1, - 2, - 3 (conv kinds).  A real loop over pairs of chunks,
+// not unrolled over the tile: the body then stays resident in the instruction cache (fully unrolled, the eight epilogue
+// warps spent more cycles waiting for instructions than issuing them).
+template <int KIND>
+__device__ __noinline__ void emit_tile(uint32_t taddr, uint8_t* dst, float4 cw, float bias, float rate, float dtb, int flags,
+                                       int tok0, int ncols, float x1, float x2, float x3) {
+    // the channel constants travel as scalars (registers), not as a struct behind a pointer (local memory)
+    ChanConst cc;
+    cc.w = cw; cc.bias = bias; cc.rate = rate; cc.dtb = dtb;
+    cc.is_beta = flags & 1; cc.active = flags & 2; cc.half0 = flags & 16;
+    uint32_t ra[16], rb[16];
+#ifdef SHVK_DEV_PROBES
+    if (INPROJ_PROBE(4)) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { ra[i] = 0x3f000000u + i; rb[i] = 0x3f100000u + i; }
+#pragma unroll 1
+        for (int c = 0; c < ncols; c += 32) {
+            emit_chunk<KIND>(ra, dst + (long long)(c >> 4) * pt::BLOCK_BYTES, cc, kTok - (tok0 + c), x1, x2, x3);
+            if (c + 16 >= ncols) break;
+            emit_chunk<KIND>(rb, dst + (long long)((c >> 4) + 1) * pt::BLOCK_BYTES, cc, kTok - (tok0 + c + 16), x1, x2, x3);
+        }
+        return;
+    }
+#endif
+    tc_ld16(taddr, ra);
+#pragma unroll 1
+    for (int c = 0; c < ncols; c += 32) {
+        tc_wait_ld();
+        if (c + 16 < ncols) tc_ld16(taddr + uint32_t(c + 16), rb);
+        emit_chunk<KIND>(ra, dst + (long long)(c >> 4) * pt::BLOCK_BYTES, cc, kTok - (tok0 + c), x1, x2, x3);
+        if (c + 16 >= ncols) break;
+        tc_wait_ld();
+        if (c + 32 < ncols) tc_ld16(taddr + uint32_t(c + 32), ra);
+        emit_chunk<KIND>(rb, dst + (long long)((c >> 4) + 1) * pt::BLOCK_BYTES, cc, kTok - (tok0 + c + 16), x1, x2, x3);
+    }
+}
+
+// Constants of channel row r of channel tile m, and where its rows of the chunk blocks start within a (clip, head).
+struct ChanSite {
+    float4 w;
+    float bias, rate, dtb;
+    int flags;      // 1 beta row, 2 lane has a channel, 16 = byte offset of tokens 0-7 within the row
+    int head, section;
+};
+__device__ __forceinline__ ChanSite chan_site(const InprojParams& p, int m, int r) {
+    ChanSite c;
+    c.w = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    c.bias = 0.0f; c.rate = 0.0f; c.dtb = 0.0f;
+    c.flags = 2 | (((r >> 2) & 1) << 4);
+    c.head = m / 3;
+    const int type = m % 3;
+    if (m == M_TILES - 1) {
+        const bool active = r < 12, is_beta = r >= 6;
+        c.flags = (is_beta ? 1 : 0) | (active ? 2 : 0);
+        c.head = active ? (r < 6 ? r : r - 6) : 0;
+        c.rate = -expf(__ldg(p.a_log + c.head));
+        c.dtb = __ldg(p.dt_bias + c.head);
+        c.section = is_beta ? pt::BETA_OFF : pt::DEC_OFF;
+    } else if (type == 0) {
+        const int ci = (r < kDK ? 0 : kD) + c.head * kDK + (r & (kDK - 1));
+        c.w = __ldg(reinterpret_cast<const float4*>(p.conv_w) + ci);
+        c.bias = __ldg(p.conv_b + ci);
+        c.section = pt::Q_OFF + r * 32;
+    } else if (type == 1) {
+        const int ci = 2 * kD + c.head * kDV + r;
+        c.w = __ldg(reinterpret_cast<const float4*>(p.conv_w) + ci);
+        c.bias = __ldg(p.conv_b + ci);
+        c.section = pt::V_OFF + r * 32;
+    } else {
+        c.section = pt::G_OFF + r * 32;
+    }
+    return c;
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = base + STAGES * STAGE_BYTES;           // full[S], empty[S], acc_full[2], acc_empty[2]
+    const uint32_t xn_base = base;                               // six k-block tiles [176 rows][128 bytes] of the item's xn rows
+    const uint32_t w_base = base + XN_BYTES;                     // ring of W' k-block tiles [128 rows][128 bytes]
+    const uint32_t bars = w_base + W_STAGES * W_STAGE_BYTES;     // wfull[S], wempty[S], accf[2], acce[2], xfull, xempty
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    auto accf_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
-    auto acce_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    auto wfull_bar = [&](int s) { return bars + 8u * s; };
+    auto wempty_bar = [&](int s) { return bars + 8u * (W_STAGES + s); };
+    auto accf_bar = [&](int a) { return bars + 8u * (2 * W_STAGES + a); };
+    auto acce_bar = [&](int a) { return bars + 8u * (2 * W_STAGES + 2 + a); };
+    const uint32_t xfull_bar = bars + 8u * (2 * W_STAGES + 4), xempty_bar = bars + 8u * (2 * W_STAGES + 5);
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(accf_bar(0), 1); mbar_init(accf_bar(1), 1);
-        mbar_init(acce_bar(0), 8);                                // both epilogue groups read accumulator 0
-        mbar_init(acce_bar(1), 4);
+        for (int s = 0; s < W_STAGES; ++s) { mbar_init(wfull_bar(s), 1); mbar_init(wempty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), 8); }
+        mbar_init(xfull_bar, 1);
+        mbar_init(xempty_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
@@ -198,125 +285,108 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abortp = &abort_flag;
-    const long long items = (long long)p.B * M_TILES;
+    const long long items = 2ll * p.B;                           // item = 2 * clip + token tile
 
     if (warp == 0) {
-        if (lane == 0) {
+        if (lane == 0) {                                         // ---- W' tiles: 19 x 6 k-blocks per item through the ring
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             const uint64_t pol_w = policy_evict_last();
             for (long long item = blockIdx.x; ok && item < items; item += gridDim.x) {
-                const int clip = int(item / M_TILES), m = int(item - (long long)clip * M_TILES);
-                for (int tt = 0; ok && tt < 2; ++tt) {
-                    const int row0 = clip * kTok + tt * N0;
-                    const uint32_t tx = uint32_t(A_BYTES + (tt ? N1 : N0) * TILE_K * 2);
+                for (int m = 0; ok && m < M_TILES; ++m) {
                     for (int kb = 0; kb < KBLOCKS; ++kb) {
-                        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
-                        const uint32_t sa = base + stage * STAGE_BYTES, sb_ = sa + A_BYTES;
-                        mbar_expect_tx(full_bar(stage), tx);
-                        tma_load_2d_hint(sa, &maps.w, kb * TILE_K, m * TILE_M, full_bar(stage), pol_w);
-                        tma_load_2d(sb_, tt ? &maps.x1 : &maps.x0, kb * TILE_K, row0, full_bar(stage));
-                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        if (!mbar_wait(wempty_bar(stage), phase ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
+                        mbar_expect_tx(wfull_bar(stage), uint32_t(W_STAGE_BYTES));
+                        tma_load_2d_hint(w_base + stage * W_STAGE_BYTES, &maps.w, kb * TILE_K, m * TILE_M, wfull_bar(stage), pol_w);
+                        if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
                     }
                 }
             }
             if (!ok && !*abortp) { *abortp = 1; atomicCAS(status, 0, 1); }
         }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0, acc_phase = 0;
+    } else if (warp == 2) {
+        if (lane == 0) {                                         // ---- the item's xn rows, once per item
+            uint32_t n = 0;
             bool ok = true;
-            for (long long item = blockIdx.x; ok && item < items; item += gridDim.x) {
-                for (int tt = 0; ok && tt < 2; ++tt) {
-                    if (!mbar_wait(acce_bar(tt), acc_phase ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
+            for (long long item = blockIdx.x; ok && item < items; item += gridDim.x, ++n) {
+                const int row0 = int(item >> 1) * kTok + int(item & 1) * TT_STRIDE;
+                if (!mbar_wait(xempty_bar, (n & 1u) ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
+                mbar_expect_tx(xfull_bar, uint32_t(XN_BYTES));
+                for (int kb = 0; kb < KBLOCKS; ++kb) tma_load_2d(xn_base + kb * XN_KB_BYTES, &maps.x, kb * TILE_K, row0, xfull_bar);
+            }
+            if (!ok && !*abortp) { *abortp = 1; atomicCAS(status, 0, 4); }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                         // ---- MMA issue
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0, n = 0;
+            bool ok = true;
+            for (long long item = blockIdx.x; ok && item < items; item += gridDim.x, ++n) {
+                if (!mbar_wait(xfull_bar, n & 1u, abortp, p.spin_limit)) { ok = false; break; }
+                for (int m = 0; ok && m < M_TILES; ++m) {
+                    if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + uint32_t(tt * 256);
-                    const uint32_t idesc = tt ? p.idesc1 : p.idesc0;
+                    const uint32_t d_tmem = tmem_base + uint32_t(acc * 256);
                     for (int kb = 0; kb < KBLOCKS; ++kb) {
-                        if (!mbar_wait(full_bar(stage), phase, abortp, p.spin_limit)) { ok = false; break; }
+                        if (!mbar_wait(wfull_bar(stage), phase, abortp, p.spin_limit)) { ok = false; break; }
                         tc_fence_after();
-                        const uint32_t sa = base + stage * STAGE_BYTES, sb_ = sa + A_BYTES;
-                        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb_);
+                        const uint64_t da = smem_desc_sw128(w_base + stage * W_STAGE_BYTES), db = smem_desc_sw128(xn_base + kb * XN_KB_BYTES);
 #pragma unroll
                         for (int k = 0; k < TILE_K / 16; ++k)
-                            tc_mma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc, uint32_t((kb | k) != 0));
-                        tc_commit(empty_bar(stage));
-                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                            if (!INPROJ_PROBE(8)) tc_mma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
+                        tc_commit(wempty_bar(stage));
+                        if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
                     }
                     if (!ok) break;
-                    tc_commit(accf_bar(tt));
+                    tc_commit(accf_bar(acc));
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
                 }
-                acc_phase ^= 1u;
+                if (ok) tc_commit(xempty_bar);                   // the item's last product has read the xn tile
             }
             if (!ok && !*abortp) { *abortp = 1; atomicCAS(status, 0, 2); }
         }
     } else {
         // ------------------------------------------------------------------------------------------ epilogue
-        const int ew = warp - 2, quad = warp & 3, half = ew >> 2;    // half 0: tokens 0..175, half 1: tokens 176..335
+        const int ew = warp - 3, quad = warp & 3, half = ew >> 2;    // half 0: the accumulator's first chunks, half 1: the rest
         const int r = quad * 32 + lane;                              // channel row within the tile
         const uint32_t tlane = tmem_base + (uint32_t(quad * 32) << 16);
+        int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         for (long long item = blockIdx.x; ok && item < items; item += gridDim.x) {
-            const int clip = int(item / M_TILES), m = int(item - (long long)clip * M_TILES);
-            const int type = m % 3;
-            int head = m / 3;
-            ChanConst cc;
-            cc.w = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            cc.bias = 0.0f; cc.rate = 0.0f; cc.dtb = 0.0f; cc.is_beta = false; cc.active = true;
-            int section = 0;
-            if (m == M_TILES - 1) {
-                cc.active = r < 12;
-                cc.is_beta = r >= 6;
-                head = cc.active ? (r < 6 ? r : r - 6) : 0;
-                cc.rate = -expf(__ldg(p.a_log + head));
-                cc.dtb = __ldg(p.dt_bias + head);
-                section = cc.is_beta ? pt::BETA_OFF : pt::DEC_OFF;
-            } else if (type == 0) {
-                const int ci = (r < kDK ? 0 : kD) + head * kDK + (r & (kDK - 1));
-                cc.w = __ldg(reinterpret_cast<const float4*>(p.conv_w) + ci);
-                cc.bias = __ldg(p.conv_b + ci);
-                section = pt::Q_OFF + r * 32;
-            } else if (type == 1) {
-                const int ci = 2 * kD + head * kDV + r;
-                cc.w = __ldg(reinterpret_cast<const float4*>(p.conv_w) + ci);
-                cc.bias = __ldg(p.conv_b + ci);
-                section = pt::V_OFF + r * 32;
-            } else {
-                section = pt::G_OFF + r * 32;
-            }
-            uint8_t* dst = p.pt + ((long long)clip * kHeads + head) * pt::HEAD_BYTES + section;
-
-            if (!mbar_wait(accf_bar(0), acc_phase, abortp, p.spin_limit)) { ok = false; break; }
-            tc_fence_after();
-            if (half == 0) {
-                if (m == M_TILES - 1) { if (quad == 0) emit_tile<KIND_GATES, 0, N0>(tlane, dst, cc, 0.0f, 0.0f, 0.0f); }
-                else if (type == 2) emit_tile<KIND_SILU, 0, N0>(tlane, dst, cc, 0.0f, 0.0f, 0.0f);
-                else emit_tile<KIND_CONV, 0, N0>(tlane, dst, cc, 0.0f, 0.0f, 0.0f);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(acce_bar(0));
-            } else {
-                uint32_t hr[16];                                     // tokens 160..175: the last three are the conv history
-                tc_ld16(tlane + uint32_t(N0 - 16), hr);
-                tc_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(acce_bar(0));
-                if (!mbar_wait(accf_bar(1), acc_phase, abortp, p.spin_limit)) { ok = false; break; }
+            const int clip = int(item >> 1), tt = int(item & 1);
+            // this warp's columns of the accumulator: [col0, col0 + ncols), written from chunk `chunk0` on; its three
+            // history tokens are the columns just before col0 (none at the start of the clip)
+            const int col0 = half ? 96 : (tt ? 16 : 0);
+            const int ncols = half ? 80 : (tt ? 80 : 96);
+            const int tok0 = tt * TT_STRIDE + col0, chunk0 = tok0 >> 4;
+            const bool has_hist = col0 > 0;
+            ChanSite cur = chan_site(p, 0, r);
+            for (int m = 0; m < M_TILES; ++m) {
+                const ChanSite nxt = chan_site(p, m + 1 < M_TILES ? m + 1 : m, r);   // its loads fly during this tile's work
+                if (!mbar_wait(accf_bar(acc), acc_phase, abortp, p.spin_limit)) { ok = false; break; }
                 tc_fence_after();
-                uint8_t* dst1 = dst + (long long)(N0 / pt::CHUNK) * pt::BLOCK_BYTES;
-                const float x1 = __uint_as_float(hr[15]), x2 = __uint_as_float(hr[14]), x3 = __uint_as_float(hr[13]);
-                if (m == M_TILES - 1) { if (quad == 0) emit_tile<KIND_GATES, N0, N1>(tlane + 256u, dst1, cc, 0.0f, 0.0f, 0.0f); }
-                else if (type == 2) emit_tile<KIND_SILU, N0, N1>(tlane + 256u, dst1, cc, 0.0f, 0.0f, 0.0f);
-                else emit_tile<KIND_CONV, N0, N1>(tlane + 256u, dst1, cc, x1, x2, x3);
+                const uint32_t tacc = tlane + uint32_t(acc * 256);
+                float x1 = 0.0f, x2 = 0.0f, x3 = 0.0f;
+                if (has_hist) {
+                    uint32_t hr[16];
+                    tc_ld16(tacc + uint32_t(col0 - 16), hr);
+                    tc_wait_ld();
+                    x1 = __uint_as_float(hr[15]); x2 = __uint_as_float(hr[14]); x3 = __uint_as_float(hr[13]);
+                }
+                uint8_t* dst = p.pt + ((long long)clip * kHeads + cur.head) * pt::HEAD_BYTES + cur.section + (long long)chunk0 * pt::BLOCK_BYTES;
+                const int type = m % 3;
+                if (m == M_TILES - 1) { if (quad == 0) emit_tile<KIND_GATES>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, 0.0f, 0.0f, 0.0f); }
+                else if (type == 2) emit_tile<KIND_SILU>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, 0.0f, 0.0f, 0.0f);
+                else if (type == 1 || p.qk_f16) emit_tile<KIND_CONV_F16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, x1, x2, x3);
+                else emit_tile<KIND_CONV_BF16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, x1, x2, x3);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(acce_bar(1));
+                if (lane == 0) mbar_arrive(acce_bar(acc));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                cur = nxt;
             }
-            acc_phase ^= 1u;
         }
         if (!ok && lane == 0 && !*abortp) { *abortp = 1; atomicCAS(status, 0, 3); }
     }
@@ -335,7 +405,7 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
 }
 
 struct HostPlan {
-    CUtensorMap map_w, map_x0, map_x1;   // 128 bytes each, 64-byte aligned
+    CUtensorMap map_w, map_x;            // 128 bytes each, 64-byte aligned
     InprojParams p;
     long long max_rows;
     int valid;
@@ -377,18 +447,16 @@ extern "C" int shvk_gdn_inproj_plan(const void* xn, long long max_rows, const vo
     HostPlan* hp = static_cast<HostPlan*>(host_plan);
     memset(hp, 0, sizeof(HostPlan));
     if (!tma::make_map_2d(&hp->map_w, w_perm, 2, W_ROWS, kD, kD, TILE_M, TILE_K, true) ||
-        !tma::make_map_2d(&hp->map_x0, xn, 2, max_rows, kD, kD, N0, TILE_K, true) ||
-        !tma::make_map_2d(&hp->map_x1, xn, 2, max_rows, kD, kD, N1, TILE_K, true))
+        !tma::make_map_2d(&hp->map_x, xn, 2, max_rows, kD, kD, NT, TILE_K, true))
         return int(cudaErrorNotSupported);
     InprojParams& p = hp->p;
     const uint32_t fmt = ab_dtype == DT_BF16 ? 1u : 0u;
     // instruction descriptor: D fp32 (bits 4-5 = 1), A/B format (bits 7-9, 10-12), both K-major, N/8 at bit 17, M/16 at bit 24
-    const uint32_t common = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(TILE_M >> 4) << 24);
-    p.idesc0 = common | (uint32_t(N0 >> 3) << 17);
-    p.idesc1 = common | (uint32_t(N1 >> 3) << 17);
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(NT >> 3) << 17) | (uint32_t(TILE_M >> 4) << 24);
     p.conv_w = conv_w; p.conv_b = conv_b; p.a_log = a_log; p.dt_bias = dt_bias;
     p.pt = static_cast<uint8_t*>(pt_out);
     p.spin_limit = SPIN_LIMIT;
+    p.qk_f16 = ab_dtype == DT_F16;
     hp->max_rows = max_rows;
     hp->valid = 0x5b201;
     return 0;
@@ -411,11 +479,18 @@ extern "C" int shvk_gdn_inproj(const void* host_plan, int B, void* stream) {
     int* status = gemm_tc_status_word();
     if (!status) return int(cudaErrorInvalidSymbol);
     InprojMaps maps;
-    maps.w = hp->map_w; maps.x0 = hp->map_x0; maps.x1 = hp->map_x1;
+    maps.w = hp->map_w; maps.x = hp->map_x;
     InprojParams p = hp->p;
     p.B = B;
-    const long long items = (long long)B * M_TILES;
+    const long long items = 2ll * B;
     const unsigned grid = unsigned(items < sms ? items : sms);
+#ifdef SHVK_DEV_PROBES
+    {
+        const char* e = getenv("SHVK_INPROJ_PROBE");
+        const int bits = e ? atoi(e) : 0;
+        cudaMemcpyToSymbolAsync(g_inproj_probe, &bits, sizeof(int), 0, cudaMemcpyHostToDevice, cudaStream_t(stream));
+    }
+#endif
     gdn_inproj_kernel<<<grid, NTHREADS, SMEM_BYTES, cudaStream_t(stream)>>>(maps, p, status);
     return int(cudaGetLastError());
 }

@@ -2,13 +2,15 @@
 // writes and the 16-bit scan (gdn_scan_t.cu) reads.  Per clip and head the 321 tokens are padded to 21 chunks of 16;
 // one chunk block is 12,416 contiguous bytes, so the scan fetches a chunk with a single bulk copy:
 //
-//   offset     0   q^T  [64 keys  ][16 tokens] bf16   silu(conv(q projection)), not yet L2-normalised
-//           2048   k^T  [64 keys  ][16 tokens] bf16   silu(conv(k projection)), not yet L2-normalised
-//           4096   v^T  [128 values][16 tokens] bf16  silu(conv(v projection))
-//           8192   g^T  [128 values][16 tokens] bf16  silu(output-gate projection)
+//   offset     0   q^T  [64 keys  ][16 tokens] 16-bit  silu(conv(q projection)), not yet L2-normalised   } the mode's type:
+//           2048   k^T  [64 keys  ][16 tokens] 16-bit  silu(conv(k projection)), not yet L2-normalised   } bf16 or fp16
+//           4096   v^T  [128 values][16 tokens] fp16   silu(conv(v projection))       } fp16 in both modes (saturating): read
+//           8192   g^T  [128 values][16 tokens] fp16   silu(output-gate projection)   } element-wise only, combined in fp32
 //          12288   log decay [16] fp32                -exp(A_log) * softplus(a + dt_bias)
 //          12352   beta      [16] fp32                sigmoid(b)
 //
+// In the four bf16 tiles a row is 32 bytes = two halves of eight tokens; in rows 4-7 of every eight rows the halves
+// trade places (tokens 8-15 first), which spreads the eight rows of one ldmatrix read over eight bank groups.
 // Blocks are ordered [clip][head][chunk].  Token slots 321 .. 335 of a clip hold zeros in every section, which makes
 // them inert in the recurrence (beta 0, no decay, zero keys and values) whatever the neighbouring clips contain.
 #pragma once

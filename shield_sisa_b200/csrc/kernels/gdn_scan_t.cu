@@ -18,8 +18,8 @@
 // accumulator layout of one product is exactly the A-operand layout of the next, so every hand-over is a register
 // repack.  Only T2 and M pass through shared memory (written by warps 0 and 1, read as B fragments by all).  k and q
 // arrive un-normalised; their L2 norms are the diagonals of the Gram products K K^T and Q Q^T and enter as per-token
-// scalars.  The 16 x 16 triangular inverse is a 16-lane forward substitution in fp32.  Operands are bf16, the state
-// and all accumulation fp32.
+// scalars.  The 16 x 16 triangular inverse is a 16-lane forward substitution in fp32.  Operands are in the mode's
+// 16-bit type (the output type T: bf16 or fp16), the state and all accumulation fp32.
 //
 // Schedule of one chunk (two CTA barriers): warps 0 / 1 Gram products, masks, inverse, while warps 1-3 finish the
 // PREVIOUS chunk (its o tile times rstd and the norm weight -> `on`); all warps R and Q S0 | barrier | U, O (times the
@@ -53,7 +53,8 @@ constexpr int OT_PITCH = kDV + 4;            // floats per token row of the o ti
 __device__ int g_scan_t_status = 0;
 
 struct Block {                               // one chunk block as it lies in global memory
-    __nv_bfloat16 qt[kDK][TC], kt[kDK][TC], vt[kDV][TC], gt[kDV][TC];
+    uint16_t qt[kDK][TC], kt[kDK][TC];       // operand type of the mode
+    uint16_t vt[kDV][TC], gt[kDV][TC];       // fp16
     float dec[TC], beta[TC];
 };
 static_assert(sizeof(Block) == pt::BLOCK_BYTES, "chunk block layout");
@@ -62,8 +63,8 @@ struct Smem {
     Block blk[NSLOT];                        // ring: chunk c lands in blk[c % 3]
     float ot[TC][OT_PITCH];                  // o * gate of the chunk, [token][value]; read back by the next chunk's norm
     float lf[TC][TC];                        // L
-    __nv_bfloat16 t2[TC][KT_PITCH];          // (I + L)^-1 diag(beta)
-    __nv_bfloat16 mq[TC][KT_PITCH];          // decay-masked Q K^T
+    uint16_t t2[TC][KT_PITCH];               // (I + L)^-1 diag(beta), operand type
+    uint16_t mq[TC][KT_PITCH];               // decay-masked Q K^T, operand type
     float ssq[TC][4];                        // per token: each warp's share of sum(o^2) over its 32 value columns
     float cw[2][TC];                         // c_i as warps 0 and 1 each computed it (no barrier between them)
     float iq[TC], ik[TC];                    // 0.125/|q|, 1/|k|
@@ -72,15 +73,28 @@ struct Smem {
 };
 constexpr int SMEM_BYTES = int(sizeof(Smem)) + 128;
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+// Operand type of the products: the mode's 16-bit type (bf16 keeps fp32's range, fp16 has three more mantissa bits).
+// The v^T and gate^T tiles are fp16 in both modes: they are only read element-wise and combined in fp32.
+template <typename OP> __device__ __forceinline__ uint32_t pack_op(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_op<__nv_bfloat16>(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-// D (16x8, fp32) += A (16x16, bf16, row) * B (16x8, bf16, col)
-__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+template <> __device__ __forceinline__ uint32_t pack_op<__half>(float lo, float hi) {
+    uint32_t r;                                                     // saturating: a finite fp16 even where fp32 exceeds 65504
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float2 h2_floats(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2*>(&w)); }
+// D (16x8, fp32) += A (16x16, row) * B (16x8, col), operands in OP
+template <typename OP> __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -168,7 +182,8 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
         const uint32_t kt_s = tma::smem_addr(&b.kt[0][0]), qt_s = tma::smem_addr(&b.qt[0][0]);
         // transposed fragment of keys 16p .. 16p+15 x all 16 tokens: matrices (keys lo, tokens 0-7), (keys lo, tokens 8-15),
         // (keys hi, tokens 0-7), (keys hi, tokens 8-15) = A fragment of [token][key], and B fragments (r[ni], r[ni + 2])
-        const uint32_t tr_off = uint32_t(((lm >> 1) * 8 + lr) * (TC * 2) + (lm & 1) * 16);
+        // (in rows 4-7 of every eight the two token halves of a row trade places: gdn_pt_layout.cuh)
+        const uint32_t tr_off = uint32_t(((lm >> 1) * 8 + lr) * (TC * 2) + ((lm & 1) ^ ((lr >> 2) & 1)) * 16);
         // ---------------------------------------------------------------- warp 0: norms of k, L, T2; warp 1: norms of q, masked Q K^T
         if (warp < 2) {
             // inclusive prefix sum of the log decays, once per warp (the two warps do not wait for each other)
@@ -200,10 +215,10 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
 #pragma unroll
                 for (int ni = 0; ni < 2; ++ni) {
                     if (warp == 0) {
-                        mma16816(acc[ni], kf, kf[ni], kf[ni + 2]);
+                        mma16816<T>(acc[ni], kf, kf[ni], kf[ni + 2]);
                     } else {
-                        mma16816(acc[ni], qf, kf[ni], kf[ni + 2]);
-                        mma16816(dq[ni], qf, qf[ni], qf[ni + 2]);
+                        mma16816<T>(acc[ni], qf, kf[ni], kf[ni + 2]);
+                        mma16816<T>(dq[ni], qf, qf[ni], qf[ni + 2]);
                     }
                 }
             }
@@ -256,14 +271,14 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
                     }
                     const float bc = b.beta[lane];
 #pragma unroll
-                    for (int i = 0; i < TC; ++i) sm.t2[i][lane] = __float2bfloat16_rn(x[i] * bc);
+                    for (int i = 0; i < TC; ++i) sm.t2[i][lane] = uint16_t(pack_op<T>(x[i] * bc, 0.0f) & 0xffffu);
                 }
             } else {
                 uint32_t* mw = reinterpret_cast<uint32_t*>(&sm.mq[0][0]);        // 12 words per row
 #pragma unroll
                 for (int ni = 0; ni < 2; ++ni) {
-                    mw[g * 12 + 4 * ni + t] = pack_bf16(acc[ni][0], acc[ni][1]);
-                    mw[(g + 8) * 12 + 4 * ni + t] = pack_bf16(acc[ni][2], acc[ni][3]);
+                    mw[g * 12 + 4 * ni + t] = pack_op<T>(acc[ni][0], acc[ni][1]);
+                    mw[(g + 8) * 12 + 4 * ni + t] = pack_op<T>(acc[ni][2], acc[ni][3]);
                 }
             }
         }
@@ -289,13 +304,13 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
 #pragma unroll
             for (int mi = 0; mi < 2; ++mi) {
                 // keys 16p .. 16p+15 of the state as an A fragment: two adjacent accumulator tiles, rounded to bf16
-                const uint32_t sa[4] = {pack_bf16(S[mi][2 * p][0], S[mi][2 * p][1]), pack_bf16(S[mi][2 * p][2], S[mi][2 * p][3]),
-                                        pack_bf16(S[mi][2 * p + 1][0], S[mi][2 * p + 1][1]),
-                                        pack_bf16(S[mi][2 * p + 1][2], S[mi][2 * p + 1][3])};
+                const uint32_t sa[4] = {pack_op<T>(S[mi][2 * p][0], S[mi][2 * p][1]), pack_op<T>(S[mi][2 * p][2], S[mi][2 * p][3]),
+                                        pack_op<T>(S[mi][2 * p + 1][0], S[mi][2 * p + 1][1]),
+                                        pack_op<T>(S[mi][2 * p + 1][2], S[mi][2 * p + 1][3])};
 #pragma unroll
                 for (int ni = 0; ni < 2; ++ni) {
-                    mma16816(R[mi][ni], sa, bk[ni], bk[ni + 2]);
-                    mma16816(QS[mi][ni], sa, bq[ni], bq[ni + 2]);
+                    mma16816<T>(R[mi][ni], sa, bk[ni], bk[ni + 2]);
+                    mma16816<T>(QS[mi][ni], sa, bq[ni], bq[ni + 2]);
                 }
             }
         }
@@ -330,7 +345,7 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
         // loads behind it): V^T and gate^T for both row halves and the K^T fragments of the state update
         // plain fragments of rows r0 .. r0+15 x 16 tokens: matrices (rows lo, tokens 0-7), (rows lo, tokens 8-15),
         // (rows hi, tokens 0-7), (rows hi, tokens 8-15): r[ni + 2 h] = tokens 8 ni + 2t, + 1 of row r0 + 8 h + g
-        const uint32_t pl_off = uint32_t(((lm >> 1) * 8 + lr) * (TC * 2) + (lm & 1) * 16);
+        const uint32_t pl_off = tr_off;                   // same four matrices, read without the transpose
         uint32_t vv[2][4], gg[2][4], kf[4][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) ldsm4(kt_s + uint32_t(q * 16 * TC * 2) + pl_off, kf[q]);   // kf[q][2 h + c]: keys 16 q + 8 h + g, tokens 8 c + 2t
@@ -346,38 +361,38 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
             uint32_t va[4];
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni) {
-                const uint32_t v0 = vv[mi][ni], v1 = vv[mi][ni + 2];
-                va[2 * ni] = pack_bf16(bf_lo(v0) - er[ni][0] * R[mi][ni][0], bf_hi(v0) - er[ni][1] * R[mi][ni][1]);
-                va[2 * ni + 1] = pack_bf16(bf_lo(v1) - er[ni][0] * R[mi][ni][2], bf_hi(v1) - er[ni][1] * R[mi][ni][3]);
+                const float2 v0 = h2_floats(vv[mi][ni]), v1 = h2_floats(vv[mi][ni + 2]);
+                va[2 * ni] = pack_op<T>(v0.x - er[ni][0] * R[mi][ni][0], v0.y - er[ni][1] * R[mi][ni][1]);
+                va[2 * ni + 1] = pack_op<T>(v1.x - er[ni][0] * R[mi][ni][2], v1.y - er[ni][1] * R[mi][ni][3]);
             }
             float U[2][4];
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) U[ni][e] = 0.0f;
-                mma16816(U[ni], va, bt[ni][0], bt[ni][1]);
+                mma16816<T>(U[ni], va, bt[ni][0], bt[ni][1]);
             }
             uint32_t ua[4];
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni) {
-                ua[2 * ni] = pack_bf16(U[ni][0] * ikt[ni][0], U[ni][1] * ikt[ni][1]);      // U / |k| for the O product
-                ua[2 * ni + 1] = pack_bf16(U[ni][2] * ikt[ni][0], U[ni][3] * ikt[ni][1]);
-                da[mi][2 * ni] = pack_bf16(U[ni][0] * dj2[ni][0], U[ni][1] * dj2[ni][1]);
-                da[mi][2 * ni + 1] = pack_bf16(U[ni][2] * dj2[ni][0], U[ni][3] * dj2[ni][1]);
+                ua[2 * ni] = pack_op<T>(U[ni][0] * ikt[ni][0], U[ni][1] * ikt[ni][1]);      // U / |k| for the O product
+                ua[2 * ni + 1] = pack_op<T>(U[ni][2] * ikt[ni][0], U[ni][3] * ikt[ni][1]);
+                da[mi][2 * ni] = pack_op<T>(U[ni][0] * dj2[ni][0], U[ni][1] * dj2[ni][1]);
+                da[mi][2 * ni + 1] = pack_op<T>(U[ni][2] * dj2[ni][0], U[ni][3] * dj2[ni][1]);
             }
             // O^T = U^T M^T + diag(e) (Q S0)^T, stored times the output gate; sum(o^2) is taken before the gate
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni) {
                 float O[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                mma16816(O, ua, bm[ni][0], bm[ni][1]);
+                mma16816<T>(O, ua, bm[ni][0], bm[ni][1]);
                 const int tok = 8 * ni + 2 * t;
                 const float o00 = O[0] + eq[ni][0] * QS[mi][ni][0], o01 = O[1] + eq[ni][1] * QS[mi][ni][1];
                 const float o10 = O[2] + eq[ni][0] * QS[mi][ni][2], o11 = O[3] + eq[ni][1] * QS[mi][ni][3];
-                const uint32_t g0 = gg[mi][ni], g1 = gg[mi][ni + 2];
-                otile[tok * OT_PITCH + r0] = o00 * bf_lo(g0);
-                otile[(tok + 1) * OT_PITCH + r0] = o01 * bf_hi(g0);
-                otile[tok * OT_PITCH + r1] = o10 * bf_lo(g1);
-                otile[(tok + 1) * OT_PITCH + r1] = o11 * bf_hi(g1);
+                const float2 g0 = h2_floats(gg[mi][ni]), g1 = h2_floats(gg[mi][ni + 2]);
+                otile[tok * OT_PITCH + r0] = o00 * g0.x;
+                otile[(tok + 1) * OT_PITCH + r0] = o01 * g0.y;
+                otile[tok * OT_PITCH + r1] = o10 * g1.x;
+                otile[(tok + 1) * OT_PITCH + r1] = o11 * g1.y;
                 sq[ni][0] = fmaf(o00, o00, fmaf(o10, o10, sq[ni][0]));
                 sq[ni][1] = fmaf(o01, o01, fmaf(o11, o11, sq[ni][1]));
             }
@@ -393,7 +408,7 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
                 for (int mi = 0; mi < 2; ++mi) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) S[mi][nj][e] *= elast;
-                    mma16816(S[mi][nj], da[mi], b0, b1);
+                    mma16816<T>(S[mi][nj], da[mi], b0, b1);
                 }
             }
         }

@@ -68,14 +68,16 @@ rmsnorm_kernel(const float* __restrict__ x, long long ldx, const float* __restri
     norm_store<T>(v, w, out + row * ldo, lane);
 }
 
+// Scatter of token blocks into the slot pool, flat over all 128-bit words of the batch: word i belongs to block
+// i / 1536, so a warp's 32 consecutive words are one 512-byte segment of one block and of its slot.
+constexpr int kBlockWords = 16 * kD / 4;
 __global__ void __launch_bounds__(256)
-store_tokens_kernel(const float* __restrict__ src, const int32_t* __restrict__ slots, float* __restrict__ pool) {
-    const int f = blockIdx.x;
-    const int s = slots[f];
-    if (s < 0) return;
-    const float4* from = reinterpret_cast<const float4*>(src + (long long)f * 16 * kD);
-    float4* to = reinterpret_cast<float4*>(pool + (long long)s * 16 * kD);
-    for (int i = threadIdx.x; i < 16 * kD / 4; i += 256) to[i] = from[i];
+store_tokens_kernel(const float4* __restrict__ src, const int32_t* __restrict__ slots, float4* __restrict__ pool, long long words) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= words) return;
+    const long long f = i / kBlockWords;
+    const int s = __ldg(slots + f);
+    if (s >= 0) pool[(long long)s * kBlockWords + (i - f * kBlockWords)] = src[i];
 }
 
 }  // namespace
@@ -102,6 +104,8 @@ extern "C" int shvk_rmsnorm(const float* x, long long ldx, const float* w, void*
 
 extern "C" int shvk_store_tokens(const float* tokens, const int32_t* slots, float* pool, int F, void* stream) {
     if (F <= 0) return 0;
-    sb::store_tokens_kernel<<<F, 256, 0, cudaStream_t(stream)>>>(tokens, slots, pool);
+    const long long words = (long long)F * sb::kBlockWords;
+    sb::store_tokens_kernel<<<unsigned((words + 255) / 256), 256, 0, cudaStream_t(stream)>>>(
+        reinterpret_cast<const float4*>(tokens), slots, reinterpret_cast<float4*>(pool), words);
     return int(cudaGetLastError());
 }

@@ -145,47 +145,11 @@ sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, cons
     if (tid < kDK) Y[(long long)clip * kD + head * kDK + tid] = (ypart[0][tid] + ypart[1][tid]) + (ypart[2][tid] + ypart[3][tid]);
 }
 
-// Final RMSNorm + Linear(384,128) + bias + SiLU + Linear(128,1) + bias; one CTA of 128 threads per clip.
-__global__ void __launch_bounds__(128)
-head_kernel(const float* __restrict__ X, const float* __restrict__ nw, const float* __restrict__ w0t,
-            const float* __restrict__ b0, const float* __restrict__ w2, const float* __restrict__ b2,
-            float* __restrict__ logits) {
-    const int clip = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    __shared__ float z[kD];
-    __shared__ float red[4];
-    const float* x = X + (long long)clip * kD;
-    const float v0 = x[tid], v1 = x[tid + 128], v2 = x[tid + 256];
-    float ss = warp_sum((v0 * v0 + v1 * v1) + v2 * v2);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    const float r = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / float(kD) + 1e-6f);
-    z[tid] = (v0 * r) * nw[tid];
-    z[tid + 128] = (v1 * r) * nw[tid + 128];
-    z[tid + 256] = (v2 * r) * nw[tid + 256];
-    __syncthreads();
-    float acc = 0.0f;
-#pragma unroll 8
-    for (int k = 0; k < kD; ++k) acc = fmaf(w0t[k * 128 + tid], z[k], acc);
-    const float hid = silu_f(acc + b0[tid]);
-    const float dot = warp_sum(w2[tid] * hid);
-    __syncthreads();
-    if (lane == 0) red[warp] = dot;
-    __syncthreads();
-    if (tid == 0) logits[clip] = ((red[0] + red[1]) + (red[2] + red[3])) + b2[0];
-}
-
 }  // namespace
 }  // namespace sb
 
 extern "C" int shvk_sisa_attn(const float* S, const float* QC, const float* lambda_raw, float* Y, int B, void* stream) {
     if (B <= 0) return 0;
     sb::sisa_attn_kernel<<<unsigned(B) * sb::kHeads, sb::NT, 0, cudaStream_t(stream)>>>(S, QC, lambda_raw, Y);
-    return int(cudaGetLastError());
-}
-
-extern "C" int shvk_head(const float* X, const float* norm_w, const float* w0t, const float* b0, const float* w2,
-                         const float* b2, float* logits, int B, void* stream) {
-    if (B <= 0) return 0;
-    sb::head_kernel<<<unsigned(B), 128, 0, cudaStream_t(stream)>>>(X, norm_w, w0t, b0, w2, b2, logits);
     return int(cudaGetLastError());
 }

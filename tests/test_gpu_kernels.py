@@ -296,8 +296,9 @@ def rounded_mixer_weights(w, stage):
     return out
 
 
-def run_inproj(L, w, stage, xn16, B):
-    """xn16: [B,321,384] float64 holding bf16-representable values.  Returns (PT device buffer, keep-alive list)."""
+def run_inproj(L, w, stage, xn16, B, mode=1):
+    """xn16: [B,321,384] float64 holding values representable in the mode's type (1 bf16, 2 fp16).  Returns (PT device
+    buffer, keep-alive list)."""
     import torch
     m = f"{stage}.mixer"
     fused = np.concatenate([w[f"{m}.{n}_proj.weight"] for n in ("q", "k", "v", "g", "a", "b")]).astype(np.float32)   # [2316,384]
@@ -309,8 +310,9 @@ def run_inproj(L, w, stage, xn16, B):
     perm[order >= 0] = fused[order[order >= 0]]
     conv_w = np.concatenate([w[f"{m}.{n}_conv1d.weight"].reshape(-1, 4) for n in "qkv"]).astype(np.float32)
     conv_b = np.concatenate([w[f"{m}.{n}_conv1d.bias"] for n in "qkv"]).astype(np.float32)
-    X = dev(xn16.reshape(B * 321, 384).astype(np.float32), torch.bfloat16)
-    Wp = dev(perm, torch.bfloat16)
+    tdt = torch.bfloat16 if mode == 1 else torch.float16
+    X = dev(xn16.reshape(B * 321, 384).astype(np.float32), tdt)
+    Wp = dev(perm, tdt)
     d = [X, Wp, dev(conv_w), dev(conv_b), dev(w[f"{m}.A_log"]), dev(w[f"{m}.dt_bias"])]
     nbytes = L.shvk_gdn_pt_bytes(B)
     assert nbytes == B * 6 * 21 * PT_BLOCK
@@ -318,45 +320,48 @@ def run_inproj(L, w, stage, xn16, B):
     buf = (C.c_char * 1024)()
     plan = (C.addressof(buf) + 63) & ~63
     ok(L.shvk_gdn_inproj_plan(X.data_ptr(), B * 321, Wp.data_ptr(), d[2].data_ptr(), d[3].data_ptr(), d[4].data_ptr(),
-                              d[5].data_ptr(), pt.data_ptr(), 1, plan))
+                              d[5].data_ptr(), pt.data_ptr(), mode, plan))
     ok(L.shvk_gdn_inproj(plan, B, stream_ptr()))
     sync()
     return pt, (d, buf)
 
 
-def unpack_pt(pt, B):
-    """PT buffer -> q, k [B,6,336,64], v, g [B,6,336,128] (float64 from bf16), dec, beta [B,6,336]."""
+def unpack_pt(pt, B, mode=1):
+    """PT buffer -> q, k [B,6,336,64] (the mode's 16-bit type), v, g [B,6,336,128] (fp16), dec, beta [B,6,336]."""
     import torch
     raw = pt.cpu().numpy().reshape(B, 6, 21, PT_BLOCK)
 
-    def tile(off, rows):
+    def tile(off, rows, tdt):
         t = np.ascontiguousarray(raw[..., off:off + rows * 32]).view(np.int16).reshape(B, 6, 21, rows, 16)
-        f = torch.from_numpy(t.copy()).view(torch.bfloat16).float().numpy().astype(np.float64)
+        f = torch.from_numpy(t.copy()).view(tdt).float().numpy().astype(np.float64)
+        swapped = ((np.arange(rows) >> 2) & 1) == 1                            # rows whose two token halves trade places
+        f[..., swapped, :] = np.concatenate([f[..., swapped, 8:], f[..., swapped, :8]], axis=-1)
         return f.transpose(0, 1, 2, 4, 3).reshape(B, 6, 336, rows)
 
     def gate(off):
         return np.ascontiguousarray(raw[..., off:off + 64]).view(np.float32).reshape(B, 6, 336).astype(np.float64)
 
-    return tile(0, 64), tile(2048, 64), tile(4096, 128), tile(8192, 128), gate(12288), gate(12352)
+    qk = torch.bfloat16 if mode == 1 else torch.float16
+    return tile(0, 64, qk), tile(2048, 64, qk), tile(4096, 128, torch.float16), tile(8192, 128, torch.float16), gate(12288), gate(12352)
 
 
-@pytest.mark.parametrize("recipe,stage,B", [("W3", "gdn_a", 2), ("W3", "gdn_b", 3), ("W1", "gdn_a", 1)])
-def test_gdn_inproj_tiles_match_oracle(L, weight_files, recipe, stage, B):
+@pytest.mark.parametrize("recipe,stage,B,mode", [("W3", "gdn_a", 2, 1), ("W3", "gdn_b", 3, 2), ("W1", "gdn_a", 1, 1)])
+def test_gdn_inproj_tiles_match_oracle(L, weight_files, recipe, stage, B, mode):
     """The fused in-projection against the oracle's conv / SiLU / gate intermediates, on operands that are exact in
     bf16: what is left is fp32 accumulation, the tanh-form SiLU and the bf16 rounding of the tiles."""
     _, w0 = weight_files(recipe, 1)
-    w = rounded_mixer_weights(w0, stage)
+    w = rounded_mixer_weights(w0, stage)                                      # bf16 values are exact in fp16 too at this scale
     xn = bf16_round(np.random.default_rng(29).standard_normal((B, 321, 384)))
     tr = {}
     O.gdn_mixer(w, f"{stage}.mixer", xn, tr, "t")
-    pt, keep = run_inproj(L, w, stage, xn, B)
-    q, k, v, g, dec, beta = unpack_pt(pt, B)
+    pt, keep = run_inproj(L, w, stage, xn, B, mode)
+    q, k, v, g, dec, beta = unpack_pt(pt, B, mode)
     assert tc_status(L) == 0
     for name, got, ref in (("q", q, tr["t.q_conv"]), ("k", k, tr["t.k_conv"]), ("v", v, tr["t.v_conv"]),
                            ("gate", g, O.silu(tr["t.gate"]))):
         ref = ref.transpose(0, 2, 1, 3)                                       # [B,6,321,*]
         err = rel_err(got[:, :, :321], ref)
-        print(f"inproj {recipe} {stage} {name}: max-rel {err:.3e}")
+        print(f"inproj {recipe} {stage} mode {mode} {name}: max-rel {err:.3e}")
         assert err < 6e-3                                                     # bf16 rounding (2^-9) + the approximate SiLU
         assert (got[:, :, 321:] == 0).all()                                   # padding token slots are zeros
     assert np.abs(dec[:, :, :321] - tr["t.g"].transpose(0, 2, 1)).max() < 2e-5 * max(1.0, np.abs(tr["t.g"]).max())
@@ -375,9 +380,9 @@ def test_gdn_inproj_scan_matches_oracle(L, weight_files, recipe, stage, B):
     O.gdn_mixer(w, f"{stage}.mixer", xn, tr, "t")
     ow = (1.0 + 0.1 * np.random.default_rng(1).standard_normal(128)).astype(np.float32)
     ref = (tr["t.o_gated"] * ow.astype(np.float64)).reshape(B * 321, 768)
-    pt, keep = run_inproj(L, w, stage, xn, B)
     d_ow = dev(ow)
     for code, tdt in ((1, torch.bfloat16), (2, torch.float16)):
+        pt, keep = run_inproj(L, w, stage, xn, B, code)                       # the tiles' operand type follows the mode
         on = torch.full((B * 321 + 8, 768), 9.0, device="cuda", dtype=tdt)
         ok(L.shvk_gdn_scan_t(pt.data_ptr(), d_ow.data_ptr(), on.data_ptr(), code, B, stream_ptr()))
         sync()
@@ -486,20 +491,56 @@ def test_sisa_attention_matches_oracle(L, weight_files):
     assert np.abs(Y.cpu().numpy() - tr["sisa.attn_y_last"]).max() < 5e-5
 
 
-def test_head_matches_oracle(L, weight_files):
+def test_readout_row_kernels_match_oracle(L, weight_files):
+    """The two fused readout-row kernels (norm + Q/C projection; W_O, FFN, final norm, head) against the oracle, on a
+    batch that is not a multiple of the 16-clip tile, and bitwise independent of the batch."""
     import torch
     _, w = weight_files("W3", 1)
-    B = 5
-    x = np.random.default_rng(3).standard_normal((B, 384)) * 2
-    z = O.rms_norm(x, w["final_norm.weight"].astype(np.float64))
-    hid = silu(z @ w["head.0.weight"].astype(np.float64).T + w["head.0.bias"])
-    ref = hid @ w["head.2.weight"].astype(np.float64).reshape(128) + w["head.2.bias"][0]
-    out = torch.zeros(B, device="cuda")
-    t = [dev(x.astype(np.float32)), dev(w["final_norm.weight"]), dev(np.ascontiguousarray(w["head.0.weight"].T)),
-         dev(w["head.0.bias"]), dev(w["head.2.weight"].reshape(128)), dev(w["head.2.bias"])]
-    ok(L.shvk_head(*[v.data_ptr() for v in t], out.data_ptr(), B, stream_ptr()))
+    B = 37
+    rng = np.random.default_rng(3)
+    f64 = lambda n: w[n].astype(np.float64)  # noqa: E731
+    h = rng.standard_normal((B, 321, 384)) * 1.5
+    y = rng.standard_normal((B, 384)) * 0.5
+    a = "sisa.attn"
+    # part 1
+    xl = O.rms_norm(h[:, 320], f64("sisa.attn_norm.weight"))
+    wqc = np.concatenate([f64(f"{a}.W_Q.weight"), f64(f"{a}.W_C.weight")])                       # [576, 384]
+    H = dev(h.astype(np.float32))
+    h_last = H.data_ptr() + 320 * 384 * 4
+    qc = torch.zeros((B, 576), device="cuda")
+    d_nw, d_wqc = dev(w["sisa.attn_norm.weight"]), dev(np.ascontiguousarray(wqc.T).astype(np.float32))
+    ok(L.shvk_readout_qc(h_last, 321 * 384, d_nw.data_ptr(), d_wqc.data_ptr(), qc.data_ptr(), B, stream_ptr()))
     sync()
-    assert np.abs(out.cpu().numpy() - ref).max() < 1e-5
+    h32 = H.cpu().numpy().astype(np.float64)
+    xl = O.rms_norm(h32[:, 320], f64("sisa.attn_norm.weight"))
+    assert np.abs(qc.cpu().numpy() - xl @ wqc.T).max() < 2e-5
+    # part 2
+    up = np.empty((1920, 384))
+    up[0::2], up[1::2] = f64("sisa.ffn.w_gate.weight"), f64("sisa.ffn.w_up.weight")                # (gate, up) interleaved
+    mats = {"wo_t": f64(f"{a}.W_O.weight").T, "ffn_norm_w": f64("sisa.ffn_norm.weight"), "up_t": up.T,
+            "down_t": f64("sisa.ffn.w_down.weight").T, "final_norm_w": f64("final_norm.weight"),
+            "head_w0_t": f64("head.0.weight").T, "head_b0": f64("head.0.bias"), "head_w2": f64("head.2.weight").reshape(128),
+            "head_b2": f64("head.2.bias")}
+    keep = {k: dev(np.ascontiguousarray(v).astype(np.float32)) for k, v in mats.items()}
+    rw = binding.ReadoutWeights(**{k: v.data_ptr() for k, v in keep.items()})
+    Y = dev(y.astype(np.float32))
+    y32 = Y.cpu().numpy().astype(np.float64)
+    x1 = h32[:, 320] + y32 @ f64(f"{a}.W_O.weight").T
+    xf = O.rms_norm(x1, f64("sisa.ffn_norm.weight"))
+    x2 = x1 + (silu(xf @ f64("sisa.ffn.w_gate.weight").T) * (xf @ f64("sisa.ffn.w_up.weight").T)) @ f64("sisa.ffn.w_down.weight").T
+    z = O.rms_norm(x2, f64("final_norm.weight"))
+    ref = silu(z @ f64("head.0.weight").T + f64("head.0.bias")) @ f64("head.2.weight").reshape(128) + f64("head.2.bias")[0]
+    x2_out, logits = torch.zeros((B, 384), device="cuda"), torch.zeros(B, device="cuda")
+    ok(L.shvk_readout_tail(Y.data_ptr(), h_last, 321 * 384, C.byref(rw), x2_out.data_ptr(), logits.data_ptr(), B, stream_ptr()))
+    sync()
+    assert np.abs(x2_out.cpu().numpy() - x2).max() < 5e-5
+    assert np.abs(logits.cpu().numpy() - ref).max() < 2e-5
+    # clip 20 alone (first of a tile instead of fifth, no neighbours): bitwise the same
+    one = torch.zeros(1, device="cuda")
+    H1, Y1 = H[20:21].contiguous(), Y[20:21].contiguous()
+    ok(L.shvk_readout_tail(Y1.data_ptr(), H1.data_ptr() + 320 * 384 * 4, 321 * 384, C.byref(rw), None, one.data_ptr(), 1, stream_ptr()))
+    sync()
+    assert torch.equal(one[0], logits[20])
 
 
 def test_store_tokens(L):

@@ -119,3 +119,25 @@ def test_reference_cpu_engine_encoder_matches_golden(case, weight_files):
     clip = W.synth_frames(20, int(g["frame_seed"]) + 1)[None]
     assert np.abs(eng.predict(clip) - g["clip_logit_cpu_engine"]).max() < 1e-6
     eng.close()
+
+
+def test_storage_policy_floor_of_the_16_bit_modes(weight_files):
+    """What the reference's own 16-bit storage policy (xn, all-row weights, on, hid rounded; everything else exact)
+    costs on the golden sets, measured as the GPU tests measure the engine: max|err| / max|ref| of the logits against
+    the float64 oracle.  In bf16 the policy alone reaches or passes the 2e-2 budget on sets of two or three clips
+    (one logit's error is a draw of about 1e-2 of the set's largest logit), which is why the GPU tests judge the logits
+    of such small sets against 3e-2 and apply 2e-2 to the stage outputs and to logits of sets of 64 clips."""
+    from oracle import lowp_policy
+    from shield_sisa_b200 import weights as W
+    from tests.helpers import load_golden, rel_err
+    worst = {"bf16": 0.0, "fp16": 0.0}
+    for case in ("w3_s1_t2_b3", "w1_s1_t1_b2", "w3_s5_t7_b2"):
+        g = load_golden(case)
+        _, w = weight_files(str(g["recipe"]), int(g["weight_seed"]))
+        tok = W.synth_tokens(int(g["batch"]), int(g["token_seed"]))
+        for mode in worst:
+            e = rel_err(lowp_policy.classify_tokens_storage_policy(w, tok, mode), g["logits_f64"])
+            print(f"storage-policy floor {case} {mode}: {e:.3e}")
+            worst[mode] = max(worst[mode], e)
+    assert 1e-2 < worst["bf16"] < 4e-2          # the policy alone is of the order of the budget in bf16
+    assert worst["fp16"] < 5e-3                 # and an order of magnitude below it in fp16
