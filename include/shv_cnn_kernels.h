@@ -57,8 +57,9 @@ int shvk_cnn_se_gate(const float* x, float* partial, const float* w1, const floa
  * cudaErrorInvalidValue, and shv_cuda_last_error() says why, when shvk_cnn_se_partial_floats(F, HW, C) exceeds that
  * (the largest squeeze-excite layer of the encoder, 240 pixels x 672 channels, fits 97 frames).
  *
- * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
- * current); make that first call outside any stream capture.  All calls share the one array: it keeps whatever the
+ * Every call looks up the array's address on the device that is current (cudaGetSymbolAddress: no allocation, and the
+ * address stays right after a device reset); the first call on a device also makes the runtime load the library's
+ * image there, so make that first call outside any stream capture.  All calls share the one array: it keeps whatever the
  * previous call left, which is harmless because every partial sum a call reads it has written first (nothing needs
  * clearing), but two calls whose kernels overlap on the GPU (different streams, or different host threads) race on
  * it and must be ordered by the caller.  Results are bitwise those of shvk_cnn_se_gate. */
@@ -68,7 +69,7 @@ int shvk_cnn_se_gate_static(const float* x, const float* w1, const float* b1, co
 
 /* 1x1 convolution as a row GEMM: out[m][n] = act(sum_k (A[m][k] * gate[m / gate_rows][k]) * W[n][k] + b[n]) (+ R[m][n]).
  * A [M][K] (pitch K), W [N][K], out and R [M][N] (R may alias out); gate NULL = no squeeze-excite scaling, else
- * [M / gate_rows][K]; K and N multiples of 4.  Each output is one fma chain over k in order.
+ * [M / gate_rows][K]; K a multiple of 8, N a multiple of 4.  Each output is one fma chain over k in order.
  * Replaces gemm<T> as used by the frame encoder (engine/cuda/engine.cu:351-355,378-382,398-400;
  * engine/cuda/gemm.cuh:16-29). */
 int shvk_cnn_pointwise(const float* A, const float* W, const float* b, const float* gate, int gate_rows, const float* R,

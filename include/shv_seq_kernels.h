@@ -68,11 +68,11 @@ int shvk_gemm_tc_status(int* status_out);
  * faults or spins without bound.  Exists so that a test can watch the abort path work. */
 int shvk_gemm_tc_rows_starved(const void* host_plan, int rows, int polls, void* stream);
 
-/* The kernels' status words (tensor-core GEMMs, fp32 scan, the two 16-bit scans) are per device and per process.  These two
- * calls enqueue on `stream`: a copy of the SHVK_STATUS_WORDS words into host_words (pinned host memory, read it after
+/* The kernels' status words (tensor-core GEMMs, the scan that reads the fp32 projection, the 16-bit scan) are per
+ * device and per process.  These two calls enqueue on `stream`: a copy of the SHVK_STATUS_WORDS words into host_words (pinned host memory, read it after
  * the stream has passed this point), and their reset to zero.  A scheduler fetches the words behind a batch's last
  * kernel, fails the batch if one is set, and clears them so that later batches run normally. */
-enum { SHVK_STATUS_WORDS = 4 };
+enum { SHVK_STATUS_WORDS = 3 };
 int shvk_status_fetch_async(int* host_words, void* stream);
 int shvk_status_clear_async(void* stream);
 
@@ -100,7 +100,8 @@ int shvk_gdn_scan_t(const void* pt, const float* o_norm_w, void* on, int on_dtyp
  * `polls` polls, the status word is set and every CTA returns without writing. */
 int shvk_gdn_scan_t_starved(const void* pt, const float* o_norm_w, void* on, int on_dtype, int B, int polls, void* stream);
 
-/* Fused GatedDeltaNet core of one mixer over B clips: causal short conv (k=4, bias) + SiLU on q|k|v, L2 norm of q
+/* Fused GatedDeltaNet core of one mixer over B clips from the fp32 projection (the exact tier's path; the 16-bit
+ * modes use shvk_gdn_inproj + shvk_gdn_scan_t): causal short conv (k=4, bias) + SiLU on q|k|v, L2 norm of q
  * (then * 0.125) and k, decay = exp(-exp(A_log) * softplus(a + dt_bias)), beta = sigmoid(b), the gated delta rule
  * from a zero state with the head's 64x128 state held in registers (operands staged by TMA), and the gated RMSNorm
  * ((o * rstd) * w) * silu(gate).  P: [B*321][2320] fp32 fused projection output; on: [B*321][768] storage type.

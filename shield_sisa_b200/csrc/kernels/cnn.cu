@@ -659,51 +659,33 @@ extern "C" int shvk_cnn_se_gate(const float* x, float* partial, const float* w1,
 
 // ---------------------------------------------------------------------------------------------------- no-allocation gate
 // Scratch for shvk_cnn_se_gate_static.  In host code the name below is only a handle for cudaGetSymbolAddress, never a
-// device address: the address is looked up once per device and that pointer is what the kernels get.
+// device address: the address is looked up with the caller's device current (on every call: the lookup allocates
+// nothing, costs a table walk, and stays right after a device reset) and that pointer is what the kernels get.
 static __device__ __align__(256) float g_se_static_partial[SHVK_CNN_SE_STATIC_FLOATS];
 
 void shv_cuda_set_error(const std::string& s);   // thread-local error string behind shv_cuda_last_error (api.cpp)
 
-namespace sb {
-namespace {
-constexpr int kMaxDevices = 64;
-std::mutex g_se_static_mu;
-float* g_se_static_addr[kMaxDevices] = {};        // per device ordinal, filled on the first call on that device
-}  // namespace
-}  // namespace sb
-
 extern "C" int shvk_cnn_se_gate_static(const float* x, const float* w1, const float* b1, const float* w2, const float* b2,
                                        float* gate, int F, int HW, int C, int CS, void* stream) {
     if (F <= 0) return 0;
+    if (HW <= 0 || C <= 0) {
+        shv_cuda_set_error("shvk_cnn_se_gate_static: HW and C must be positive");
+        return int(cudaErrorInvalidValue);
+    }
     const size_t need = shvk_cnn_se_partial_floats(F, HW, C);
-    if (need == 0 || need > size_t(SHVK_CNN_SE_STATIC_FLOATS)) {
+    if (need > size_t(SHVK_CNN_SE_STATIC_FLOATS)) {
         shv_cuda_set_error("shvk_cnn_se_gate_static: " + std::to_string(need) + " floats of partial sums (F x ceil(HW / 64) x C) "
                            "do not fit the built-in " + std::to_string(SHVK_CNN_SE_STATIC_FLOATS) +
                            "; use shvk_cnn_se_gate with caller scratch or fewer frames per call");
         return int(cudaErrorInvalidValue);
     }
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return int(e);
-    if (dev < 0 || dev >= sb::kMaxDevices) {
-        shv_cuda_set_error("shvk_cnn_se_gate_static: device ordinal out of range");
-        return int(cudaErrorInvalidDevice);
+    void* scratch = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&scratch, g_se_static_partial);   // the current device's copy of the array
+    if (e != cudaSuccess) {
+        shv_cuda_set_error(std::string("shvk_cnn_se_gate_static: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+        return int(e);
     }
-    float* scratch = nullptr;
-    {
-        std::lock_guard<std::mutex> lk(sb::g_se_static_mu);
-        if (!sb::g_se_static_addr[dev]) {
-            void* p = nullptr;
-            e = cudaGetSymbolAddress(&p, g_se_static_partial);          // the current device's copy of the array
-            if (e != cudaSuccess) {
-                shv_cuda_set_error(std::string("shvk_cnn_se_gate_static: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
-                return int(e);
-            }
-            sb::g_se_static_addr[dev] = static_cast<float*>(p);
-        }
-        scratch = sb::g_se_static_addr[dev];
-    }
-    return shvk_cnn_se_gate(x, scratch, w1, b1, w2, b2, gate, F, HW, C, CS, stream);
+    return shvk_cnn_se_gate(x, static_cast<float*>(scratch), w1, b1, w2, b2, gate, F, HW, C, CS, stream);
 }
 
 namespace sb {

@@ -98,6 +98,12 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
 __device__ __forceinline__ void stg128(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+// One 32-byte store: a lane writes a whole sector, a warp 1 KB contiguous.  (Two 16-byte stores per row put 32 half-filled
+// sectors per instruction through the L1 store path, twice the sector traffic for the same bytes.)
+__device__ __forceinline__ void stg256(void* p, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
 
 // What an epilogue does with its channel: q, k (conv + SiLU, stored in the mode's operand type: KIND_CONV_BF16 or
 // KIND_CONV_F16), v (conv + SiLU, fp16), output gate (SiLU, fp16), a | b (log decay and beta, fp32).
@@ -167,8 +173,13 @@ __device__ __forceinline__ void emit_chunk(const uint32_t (&in)[16], uint8_t* ro
         // the two 16-byte halves of the row trade places in rows 4-7 of every eight, so that the scan's ldmatrix reads
         // (eight rows of one half at a time) fall into eight different bank groups
         if (!INPROJ_PROBE(1)) {
-            stg128(row + cc.half0, o[0], o[1], o[2], o[3]);
-            stg128(row + (cc.half0 ^ 16), o[4], o[5], o[6], o[7]);
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                w[i] = cc.half0 ? o[i + 4] : o[i];
+                w[i + 4] = cc.half0 ? o[i] : o[i + 4];
+            }
+            stg256(row, w);
         } else if (o[0] == 0x12345678u && o[7] == 0x9abcdef0u) {
             stg128(row, o[0], o[1], o[2], o[3]);          // keeps the arithmetic alive
         }
@@ -182,12 +193,13 @@ __device__ __forceinline__ void emit_chunk(const uint32_t (&in)[16], uint8_t* ro
 // warps spent more cycles waiting for instructions than issuing them).
 template <int KIND>
 __device__ __noinline__ void emit_tile(uint32_t taddr, uint8_t* dst, float4 cw, float bias, float rate, float dtb, int flags,
-                                       int tok0, int ncols, float x1, float x2, float x3) {
+                                       int tok0, int ncols, bool has_hist) {
     // the channel constants travel as scalars (registers), not as a struct behind a pointer (local memory)
     ChanConst cc;
     cc.w = cw; cc.bias = bias; cc.rate = rate; cc.dtb = dtb;
     cc.is_beta = flags & 1; cc.active = flags & 2; cc.half0 = flags & 16;
     uint32_t ra[16], rb[16];
+    float x1 = 0.0f, x2 = 0.0f, x3 = 0.0f;
 #ifdef SHVK_DEV_PROBES
     if (INPROJ_PROBE(4)) {
 #pragma unroll
@@ -201,10 +213,15 @@ __device__ __noinline__ void emit_tile(uint32_t taddr, uint8_t* dst, float4 cw, 
         return;
     }
 #endif
-    tc_ld16(taddr, ra);
+    // The 16 columns before this warp's range hold its convolution history (their last three tokens).  They come with
+    // the first chunk in ONE 32-column load: a tensor-memory load takes the better part of a microsecond to return while
+    // the MMA pipe is busy, and a separate history load would put that wait in front of every tile.
+    if (has_hist) tc_ld16x2(taddr - 16u, rb, ra);
+    else tc_ld16(taddr, ra);
 #pragma unroll 1
     for (int c = 0; c < ncols; c += 32) {
         tc_wait_ld();
+        if (c == 0 && has_hist) { x1 = __uint_as_float(rb[15]); x2 = __uint_as_float(rb[14]); x3 = __uint_as_float(rb[13]); }
         if (c + 16 < ncols) tc_ld16(taddr + uint32_t(c + 16), rb);
         emit_chunk<KIND>(ra, dst + (long long)(c >> 4) * pt::BLOCK_BYTES, cc, kTok - (tok0 + c), x1, x2, x3);
         if (c + 16 >= ncols) break;
@@ -368,19 +385,12 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
                 if (!mbar_wait(accf_bar(acc), acc_phase, abortp, p.spin_limit)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t tacc = tlane + uint32_t(acc * 256);
-                float x1 = 0.0f, x2 = 0.0f, x3 = 0.0f;
-                if (has_hist) {
-                    uint32_t hr[16];
-                    tc_ld16(tacc + uint32_t(col0 - 16), hr);
-                    tc_wait_ld();
-                    x1 = __uint_as_float(hr[15]); x2 = __uint_as_float(hr[14]); x3 = __uint_as_float(hr[13]);
-                }
                 uint8_t* dst = p.pt + ((long long)clip * kHeads + cur.head) * pt::HEAD_BYTES + cur.section + (long long)chunk0 * pt::BLOCK_BYTES;
                 const int type = m % 3;
-                if (m == M_TILES - 1) { if (quad == 0) emit_tile<KIND_GATES>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, 0.0f, 0.0f, 0.0f); }
-                else if (type == 2) emit_tile<KIND_SILU>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, 0.0f, 0.0f, 0.0f);
-                else if (type == 1 || p.qk_f16) emit_tile<KIND_CONV_F16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, x1, x2, x3);
-                else emit_tile<KIND_CONV_BF16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, x1, x2, x3);
+                if (m == M_TILES - 1) { if (quad == 0) emit_tile<KIND_GATES>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, false); }
+                else if (type == 2) emit_tile<KIND_SILU>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, false);
+                else if (type == 1 || p.qk_f16) emit_tile<KIND_CONV_F16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, has_hist);
+                else emit_tile<KIND_CONV_BF16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, has_hist);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acce_bar(acc));

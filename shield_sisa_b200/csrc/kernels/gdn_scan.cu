@@ -28,7 +28,6 @@
 #include "device_utils.cuh"
 #include "shv_seq_kernels.h"
 #include "tma_utils.cuh"
-#include "gdn_scan_mma.cuh"
 #include "status_words.cuh"
 
 #include <stdlib.h>
@@ -276,10 +275,6 @@ extern "C" int shvk_gdn_scan(const float* P, const float* conv_w, const float* c
     using namespace sb;
     if (B <= 0) return 0;
     if (reinterpret_cast<uintptr_t>(P) & 15) return int(cudaErrorInvalidValue);
-    // 16-bit output = a 16-bit mode: the chunked tensor-core form of the recurrence (gdn_scan_mma.cu).  The exact tier
-    // (fp32 output) keeps the per-token fp32 kernel below.
-    if (on_dtype != DT_F32)
-        return launch_gdn_scan_mma(P, conv_w, conv_b, a_log, dt_bias, o_norm_w, on, on_dtype, B, cudaStream_t(stream));
     ScanMaps maps;
     const long long rows = (long long)B * kTok;
     if (!tma::make_map_f32(&maps.qk, P, rows, kGLD, kGLD, TC, kDK) || !tma::make_map_f32(&maps.vg, P, rows, kGLD, kGLD, TC, kDV) ||
@@ -303,16 +298,16 @@ int* gdn_scan_status_word() {
 }
 }  // namespace sb
 
-// Combined status of the three scan kernels: 0, or the fp32 kernel's word, 8 + the word of the 16-bit kernel that reads
-// the fp32 projection, 16 + the word of the 16-bit kernel that reads operand tiles.
+// Combined status of the two scan kernels: 0, or the word of the kernel that reads the fp32 projection, or 16 + the word
+// of the 16-bit kernel that reads operand tiles.
 extern "C" int shvk_gdn_scan_status(int* status_out) {
-    int v[3] = {0, 0, 0};
-    int* words[3] = {sb::gdn_scan_status_word(), sb::gdn_scan_mma_status_word(), sb::gdn_scan_t_status_word()};
-    for (int i = 0; i < 3; ++i) {
+    int v[2] = {0, 0};
+    int* words[2] = {sb::gdn_scan_status_word(), sb::gdn_scan_t_status_word()};
+    for (int i = 0; i < 2; ++i) {
         if (!words[i]) return int(cudaErrorInvalidSymbol);
         const cudaError_t e = cudaMemcpy(&v[i], words[i], sizeof(int), cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) return int(e);
     }
-    if (status_out) *status_out = v[0] ? v[0] : v[1] ? 8 + v[1] : v[2] ? 16 + v[2] : 0;
+    if (status_out) *status_out = v[0] ? v[0] : v[1] ? 16 + v[1] : 0;
     return 0;
 }

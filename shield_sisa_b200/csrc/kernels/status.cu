@@ -8,8 +8,7 @@
 
 extern "C" int shvk_status_fetch_async(int* host_words, void* stream) {
     if (!host_words) return int(cudaErrorInvalidValue);
-    int* words[SHVK_STATUS_WORDS] = {sb::gemm_tc_status_word(), sb::gdn_scan_status_word(), sb::gdn_scan_mma_status_word(),
-                                     sb::gdn_scan_t_status_word()};
+    int* words[SHVK_STATUS_WORDS] = {sb::gemm_tc_status_word(), sb::gdn_scan_status_word(), sb::gdn_scan_t_status_word()};
     for (int i = 0; i < SHVK_STATUS_WORDS; ++i) {
         if (!words[i]) return int(cudaErrorInvalidSymbol);
         const cudaError_t e = cudaMemcpyAsync(host_words + i, words[i], sizeof(int), cudaMemcpyDeviceToHost, cudaStream_t(stream));
@@ -19,8 +18,7 @@ extern "C" int shvk_status_fetch_async(int* host_words, void* stream) {
 }
 
 extern "C" int shvk_status_clear_async(void* stream) {
-    int* words[SHVK_STATUS_WORDS] = {sb::gemm_tc_status_word(), sb::gdn_scan_status_word(), sb::gdn_scan_mma_status_word(),
-                                     sb::gdn_scan_t_status_word()};
+    int* words[SHVK_STATUS_WORDS] = {sb::gemm_tc_status_word(), sb::gdn_scan_status_word(), sb::gdn_scan_t_status_word()};
     for (int i = 0; i < SHVK_STATUS_WORDS; ++i) {
         if (!words[i]) return int(cudaErrorInvalidSymbol);
         const cudaError_t e = cudaMemsetAsync(words[i], 0, sizeof(int), cudaStream_t(stream));

@@ -8,6 +8,5 @@ namespace sb {
 // Device address of each word on the current device, or nullptr if the lookup failed.  Looked up per call.
 int* gemm_tc_status_word();        // gemm_tc.cu: 1 + role (producer, MMA issuer, epilogue) whose wait gave up
 int* gdn_scan_status_word();       // gdn_scan.cu: 1 = wait for a chunk's TMA tiles
-int* gdn_scan_mma_status_word();   // gdn_scan_mma.cu: 1 = chunk tiles, 2 = gate tile
 int* gdn_scan_t_status_word();     // gdn_scan_t.cu: 1 = wait for a chunk block
 }  // namespace sb

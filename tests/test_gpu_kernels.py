@@ -261,7 +261,7 @@ def test_gdn_scan_matches_oracle(L, weight_files, recipe, stage, B):
     ref = (tr["t.o_gated"] * ow.astype(np.float64)).reshape(B * 321, 768)
     assert np.all(w[f"{m}.o_norm.weight"] == 1.0)
     Pd, d_cw, d_cb, d_al, d_dt, d_ow = dev(P), dev(conv_w), dev(conv_b), dev(w[f"{m}.A_log"]), dev(w[f"{m}.dt_bias"]), dev(ow)
-    # 16-bit outputs select the chunked tensor-core form (bf16 operands, fp32 state): judged by the 16-bit modes' budget
+    # the per-token fp32 recurrence; 16-bit outputs only round the result
     for code, tdt, tol in ((0, torch.float32, None), (1, torch.bfloat16, 2e-2), (2, torch.float16, 2e-2)):
         on = torch.zeros((B * 321, 768), device="cuda", dtype=tdt)
         ok(L.shvk_gdn_scan(Pd.data_ptr(), d_cw.data_ptr(), d_cb.data_ptr(), d_al.data_ptr(), d_dt.data_ptr(),
@@ -435,14 +435,14 @@ def test_starved_launches_give_up_and_the_status_clears(L, weight_files):
     def fetch():
         ok(L.shvk_status_fetch_async(words.data_ptr(), stream_ptr()))
         sync()
-        return words[:4].tolist()
+        return words[:3].tolist()
 
-    assert fetch() == [0, 0, 0, 0]
+    assert fetch() == [0, 0, 0]
     ok(L.shvk_gemm_tc_rows_starved(plan, M, 1024, stream_ptr()))
     sync()                                                                    # returns: the waits are bounded
     assert tc_status(L) != 0 and fetch()[0] != 0
     ok(L.shvk_status_clear_async(stream_ptr()))
-    assert fetch() == [0, 0, 0, 0]
+    assert fetch() == [0, 0, 0]
     ok(L.shvk_gemm_tc(plan, stream_ptr()))
     sync()
     assert tc_status(L) == 0
@@ -457,11 +457,11 @@ def test_starved_launches_give_up_and_the_status_clears(L, weight_files):
     on = torch.full((2 * 321, 768), 5.0, device="cuda", dtype=torch.bfloat16)
     ok(L.shvk_gdn_scan_t_starved(pt.data_ptr(), ow.data_ptr(), on.data_ptr(), 1, 2, 1024, stream_ptr()))
     sync()
-    assert fetch()[3] == 1 and (on == 5.0).all()                              # gave up before writing anything
+    assert fetch()[2] == 1 and (on == 5.0).all()                              # gave up before writing anything
     ok(L.shvk_status_clear_async(stream_ptr()))
     ok(L.shvk_gdn_scan_t(pt.data_ptr(), ow.data_ptr(), on.data_ptr(), 1, 2, stream_ptr()))
     sync()
-    assert fetch() == [0, 0, 0, 0] and torch.isfinite(on.float()).all() and not (on == 5.0).all()
+    assert fetch() == [0, 0, 0] and torch.isfinite(on.float()).all() and not (on == 5.0).all()
 
 
 # ---------------------------------------------------------------------------------------------- SISA attention + head
