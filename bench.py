@@ -385,6 +385,34 @@ def run_chunked(args, local_rank: int):
                        "frac": cases[0]["hbm_frac"], "kernel": "gdn_chunked", "traffic": None},
           "gpu_launches": 2 * args.steps, "cases": cases})
 
+# ---------------------------------------------------------------------------------------------- same-box GPU baseline
+def reference_gpu_engine(wpath, mode: str, windows: int = 512):
+    """The reference's own CUDA engine (its sm_80-generation kernels: mma.sync, cp.async, no TMA) compiled for sm_100
+    from its sources by oracle/Makefile, timed by its own kernel benchmark (bench/gpu_kbench.cu: GPU-resident tokens,
+    CUDA events, graphs on, p50 over the iterations) on `windows` windows, its compiled-in maximum.  Context beside the
+    headline, not the `--impl reference` arm.  None if the binary did not travel with the tree."""
+    exe = ROOT / "oracle" / "_ref" / "gpu_kbench_ref"
+    if not exe.exists():
+        return None
+    crop = Path(tempfile.gettempdir()) / f"shv_bench_{os.getuid()}_crop.npz"
+    if not crop.exists():
+        np.savez(crop, frames=np.random.default_rng(6).integers(0, 256, size=(20, 180, 320, 3), dtype=np.uint8))
+    try:
+        r = subprocess.run([str(exe), str(wpath), mode, "--frames", "20", "--windows", str(windows), "--clips", "1", "--iters", "10",
+                            "--crop", str(crop)], capture_output=True, text=True, timeout=300)
+    except subprocess.TimeoutExpired:
+        return {"error": "gpu_kbench did not finish within 300 s"}
+    if r.returncode != 0:
+        return {"error": (r.stderr or r.stdout).strip()[-300:]}
+    for line in r.stdout.splitlines():
+        if line.startswith("{") and '"classify"' in line:
+            d = json.loads(line)
+            return {"clips_per_s": d["windows_per_s"], "p50_ms": d["p50_ms"], "windows": d["windows"], "mode": mode,
+                    "what": "reference CUDA engine (engine/cuda, compiled for sm_100) through its own bench/gpu_kbench: "
+                            "classify on GPU-resident tokens, graphs on, p50 of 10"}
+    return {"error": "no classify line in gpu_kbench output"}
+
+
 # ---------------------------------------------------------------------------------------------- CPU baseline
 def cpu_reference_rate(weights_path, tokens_host, budget_s: float, threads: int | None = None):
     """Windows/s of the reference CPU engine (oracle/_ref) on `threads` host threads over a bounded sample of
@@ -639,6 +667,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         torch.cuda.empty_cache()
         extras["gdn_chunked_b64_t2048"] = [chunked_case(torch, binding.load_library(True), dk, 5, 3) for dk in (64, 128)]
         torch.cuda.empty_cache()
+        extras["gpu_baseline"] = reference_gpu_engine(wpath, mode if mode != "fp32" else "fp32")
 
     # ------------------------------------------------------------ CPU baseline beside it (rank 0, N = 1)
     cpu = None
