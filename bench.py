@@ -14,13 +14,16 @@ collective on the data path (weak scaling).  Rank 0 prints one JSON line:
              stream, max over ranks
   e2e        the same metric through the C ABI (synchronous shv_cuda_classify calls covering B clips per step) with host
              buffers: pinned tokens are DMA'd to the device and logits read back inside the timed region, every step.
-             The scheduler option max_windows (--e2e-windows, default 1024) makes classify split a call into jobs
-             whose uploads overlap the previous job's kernels, and --e2e-threads (default 2) host threads each classify
-             their share of the batch so that the queue does not drain between steps (measured, one caller:
-             max_windows 4096 -> 49k, 1024 -> 69k, 512 -> 79k clips/s; two callers: 512 -> 84k, 1024 -> 85k)
+             The model is loaded with max_windows = --e2e-windows (default 4096); a synchronous call is cut by the library
+             into requests of an eighth of that, whose uploads overlap the kernels of the requests before them (four
+             buffer sets in flight), and --e2e-threads (default 2) host threads each classify their share of the batch
+             so that the queue does not drain between steps (measured: one caller 87.5k clips/s, two callers 95.4k)
   roofline   for the kernel with the largest share of the step: algorithmic bytes (or flops) per launch / its mean
              launch time, measured here with CUDA events, against the measured peak in MEASURED_PEAKS.json
   cpu_baseline  the reference's exact-FP32 CPU engine (oracle/_ref) on the host cores, on a bounded sample (N=1 only)
+  extras     beside the metric (N=1 only): the exact fp32 mode at B = 128, the long-sequence kernel, and the reference's own
+             CUDA engine compiled for sm_100 (oracle/_ref/gpu_kbench_ref) as a same-box GPU baseline
+  live_box   streaming hops of 4096 participants per GPU over all N GPUs from ONE process through one shv_box
   encoder    beside the metric (N=1 only): frames/s of the frame encoder (Engine::encode, 512 crops resident in HBM),
              its time by kernel kind and its fraction of the HBM peak under the layer-boundary byte model
 
@@ -315,6 +318,67 @@ def run_live(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+def live_box_leg(binding, wpath, mode: str, n_devices: int, participants: int, hops: int = 3, new: int = 4):
+    """Streaming hops over ALL the GPUs of the box from this one process, through one shv_box (one model per device,
+    sessions placed by participant id, one request per participant per hop routed to its device; BASELINE's service-load
+    configuration without the session layer).  Requests are prebuilt (the ring pattern repeats every six hops), so a hop
+    costs one C call per participant.  Returns windows/s and frames/s over `hops` hops after the 20-frame first hop."""
+    from shield_sisa_b200 import live
+    per_dev = -(-participants // n_devices)
+    cap_sessions = per_dev + per_dev // 4 + 8                    # what the box provisions per device
+    box = binding.Box(wpath, mode, list(range(n_devices)), max_sessions=participants, experimental=True,
+                      max_frames=min(4096, max(20, cap_sessions * 20)), max_windows=min(4096, cap_sessions), max_host_tokens=20)
+    L = box.L
+    drv = live.BoxLiveDriver(box, [f"participant-{i}" for i in range(participants)])
+    distinct = 64
+    pool = binding.PinnedBuffer(L, (distinct, 180, 320, 3), np.uint8)
+    pool.array[...] = np.random.default_rng(4).integers(0, 256, size=pool.array.shape, dtype=np.uint8)
+    logits = np.full(participants, np.nan, np.float32)
+    C = binding.C
+
+    def requests_for(n, frames_sent):
+        out = []
+        for p in range(participants):
+            first = (p * 7) % (distinct - n)
+            store, window = live.hop_slots(0, frames_sent, n)
+            base = drv.sessions[p][1]
+            out.append(binding.build_request(1, logits[p:p + 1], window_slots=window + base, frames=pool.array[first:first + n],
+                                             n_frames=n, store_slots=store + base))
+        return out
+
+    def run_hop(reqs):
+        jobs = [L.shv_box_submit(box.b, drv.sessions[p][0], C.byref(reqs[p][0])) for p in range(participants)]
+        if not all(jobs):
+            raise SystemExit(binding.last_error(L))
+        for j in jobs:
+            if L.shv_cuda_job_wait(j) != 0:
+                raise SystemExit(L.shv_cuda_job_error(j).decode())
+            L.shv_cuda_job_free(j)
+
+    run_hop(requests_for(20, 0))
+    sent = 20
+    phases = []
+    for h in range(6):                                            # 24 / 4: the ring positions repeat after six hops
+        phases.append(requests_for(new, sent))
+        sent += new
+    run_hop(phases[0])                                            # warm-up hop
+    t0 = time.perf_counter()
+    for h in range(hops):
+        run_hop(phases[(h + 1) % 6])
+    dt = time.perf_counter() - t0
+    ok = bool(np.isfinite(logits).all())
+    per_device = [sum(1 for d, _ in drv.sessions if d == i) for i in range(n_devices)]
+    box.close()
+    pool.free()
+    if not ok:
+        raise SystemExit("box live run returned non-finite logits")
+    return {"windows_per_s": participants * hops / dt, "frames_per_s": participants * new * hops / dt, "participants": participants,
+            "devices": n_devices, "participants_per_device": per_device, "hops": hops, "ms_per_hop": 1000.0 * dt / hops, "mode": mode,
+            "what": "one process, one shv_box over all devices: 4 new uint8 crops + 1 window of 20 ring slots per participant "
+                    "and hop, one request per participant routed to its device, crops in pinned host memory"}
+
+
+
 def make_weights(tag: str):
     from shield_sisa_b200 import weights as W
     path = Path(tempfile.gettempdir()) / f"shv_bench_{os.getuid()}_{tag}" / "w3_seed1.weights"
@@ -504,10 +568,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
     torch.cuda.set_device(local_rank)
+    host_group = None
     if world > 1 and not dist.is_initialized():
         # NCCL writes its version banner to stdout; stdout carries the one JSON line only
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        host_group = dist.new_group(backend="gloo")      # a barrier that keeps no kernel spinning on the waiting GPUs
 
     def barrier():
         if world > 1:
@@ -669,6 +735,19 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         torch.cuda.empty_cache()
         extras["gpu_baseline"] = reference_gpu_engine(wpath, mode if mode != "fp32" else "fp32")
 
+    # ------------------------------------------------------------ the whole box from one process (rank 0; the others idle)
+    live_box = None
+    if not args.no_extras and torch.cuda.device_count() >= world:
+        if host_group is not None:
+            dist.barrier(group=host_group)
+        if rank == 0:
+            try:
+                live_box = live_box_leg(binding, wpath, "fp16", world, 4096 * world)
+            except (RuntimeError, SystemExit) as e:          # reported, never fatal for the headline
+                live_box = {"error": str(e)[-300:]}
+        if host_group is not None:
+            dist.barrier(group=host_group)
+
     # ------------------------------------------------------------ CPU baseline beside it (rank 0, N = 1)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -687,7 +766,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
             "stack_hbm_fraction": {"algorithmic_bytes_per_clip": alg_bytes_clip, "frac": stack_frac,
                                    "note": "whole stack against the GEMM-boundary byte model and the measured HBM peak"},
-            "kernels": kernels, "encoder": encoder, "extras": extras,
+            "kernels": kernels, "encoder": encoder, "extras": extras, "live_box": live_box,
         }
         emit(line)
     if world > 1:
@@ -728,9 +807,9 @@ def main():
     ap.add_argument("--participants", type=int, default=4096, help="participants of the live workload")
     ap.add_argument("--e2e-threads", type=int, default=2,
                     help="host threads of the end-to-end leg, each calling shv_cuda_classify on its share of the batch")
-    ap.add_argument("--e2e-windows", type=int, default=1024,
-                    help="scheduler option max_windows of the end-to-end leg: shv_cuda_classify splits a call into jobs of "
-                         "this many clips, and the scheduler uploads job i+1 while job i computes")
+    ap.add_argument("--e2e-windows", type=int, default=4096,
+                    help="scheduler option max_windows of the end-to-end leg (a synchronous call travels as requests of an "
+                         "eighth of it, uploads overlapping kernels)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

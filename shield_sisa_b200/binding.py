@@ -197,6 +197,40 @@ class PinnedBuffer:
             self.ptr = None
 
 
+def build_request(n_windows, logits_out, window_tokens=None, window_slots=None, window_frames=None, callback=None,
+                  frames=None, n_frames=0, tokens_out=None, store_slots=None):
+    """A filled shv_cuda_request and the list of objects that must stay alive until the job completes."""
+    req = Request()
+    keep = [logits_out]
+    req.n_windows = n_windows
+    req.logits_out = logits_out.ctypes.data if logits_out is not None else None
+    if window_tokens is not None:
+        arr = (C.c_void_p * len(window_tokens))(*[None if a is None else a.ctypes.data for a in window_tokens])
+        req.window_tokens = C.cast(arr, C.POINTER(C.c_void_p))
+        keep += [arr, window_tokens]
+    for name, val in (("window_slots", window_slots), ("window_frames", window_frames)):
+        if val is not None:
+            a = np.ascontiguousarray(val, dtype=np.int32)
+            setattr(req, name, a.ctypes.data_as(C.POINTER(C.c_int32)))
+            keep.append(a)
+    if frames is not None:
+        req.frames = frames.ctypes.data
+        keep.append(frames)
+    req.n_frames = n_frames
+    if tokens_out is not None:
+        req.tokens_out = tokens_out.ctypes.data
+        keep.append(tokens_out)
+    if store_slots is not None:
+        a = np.ascontiguousarray(store_slots, dtype=np.int32)
+        req.store_slots = a.ctypes.data_as(C.POINTER(C.c_int32))
+        keep.append(a)
+    if callback is not None:
+        cb = CALLBACK(callback)
+        req.callback = cb
+        keep.append(cb)
+    return req, keep
+
+
 class CudaModel:
     """shv_cuda_load_ex / classify / submit / free of one model on one device."""
 
@@ -291,34 +325,8 @@ class CudaModel:
     def submit(self, n_windows, logits_out, window_tokens=None, window_slots=None, window_frames=None, callback=None,
                frames=None, n_frames=0, tokens_out=None, store_slots=None):
         """Returns (job handle or None, keepalive tuple).  window_tokens: list of numpy blocks (or None entries)."""
-        req = Request()
-        keep = [logits_out]
-        req.n_windows = n_windows
-        req.logits_out = logits_out.ctypes.data if logits_out is not None else None
-        if window_tokens is not None:
-            arr = (C.c_void_p * len(window_tokens))(*[None if a is None else a.ctypes.data for a in window_tokens])
-            req.window_tokens = C.cast(arr, C.POINTER(C.c_void_p))
-            keep += [arr, window_tokens]
-        for name, val in (("window_slots", window_slots), ("window_frames", window_frames)):
-            if val is not None:
-                a = np.ascontiguousarray(val, dtype=np.int32)
-                setattr(req, name, a.ctypes.data_as(C.POINTER(C.c_int32)))
-                keep.append(a)
-        if frames is not None:
-            req.frames = frames.ctypes.data
-            keep.append(frames)
-        req.n_frames = n_frames
-        if tokens_out is not None:
-            req.tokens_out = tokens_out.ctypes.data
-            keep.append(tokens_out)
-        if store_slots is not None:
-            a = np.ascontiguousarray(store_slots, dtype=np.int32)
-            req.store_slots = a.ctypes.data_as(C.POINTER(C.c_int32))
-            keep.append(a)
-        if callback is not None:
-            cb = CALLBACK(callback)
-            req.callback = cb
-            keep.append(cb)
+        req, keep = build_request(n_windows, logits_out, window_tokens, window_slots, window_frames, callback, frames, n_frames,
+                                  tokens_out, store_slots)
         job = self.L.shv_cuda_submit(self.m, C.byref(req))
         return job, keep
 

@@ -89,3 +89,54 @@ class LiveDriver:
         if failed:
             raise RuntimeError(failed)
         return logits, timings
+
+
+class BoxLiveDriver:
+    """The same hops over the GPUs of a box behind one binding.Box: a participant's session is opened on its home
+    device (crc32 of its id modulo the number of devices, spilling when that device is full), its ring is the block of 24
+    token slots the box handed out there, and every hop request of the participant goes to that device."""
+
+    def __init__(self, box, participant_ids):
+        self.box = box
+        self.ids = list(participant_ids)
+        self.sessions = [box.session_open(pid) for pid in self.ids]            # (device, first slot of the ring)
+        self.frames_sent = np.zeros(len(self.ids), np.int64)
+
+    def ring_slots(self, p: int, new: int):
+        """(store_slots, window_slots) of participant p's next hop, in the slot numbering of its device."""
+        store, window = hop_slots(0, int(self.frames_sent[p]), new)
+        base = self.sessions[p][1]
+        return store + base, window + base
+
+    def hop(self, crops_of, new: int):
+        """crops_of(p) -> uint8 array [new, 180, 320, 3] (pinned memory is DMA'd without staging).  One request per
+        participant to its device; returns (logits [participants], batch sizes seen by the jobs)."""
+        from . import binding
+        L = self.box.L
+        n = len(self.ids)
+        logits = np.full(n, np.nan, np.float32)
+        jobs, keep = [], []
+        for p in range(n):
+            store, window = self.ring_slots(p, new)
+            req, k = binding.build_request(1, logits[p:p + 1], window_slots=window, frames=crops_of(p), n_frames=new, store_slots=store)
+            job = self.box.submit(self.sessions[p][0], req)
+            if not job:
+                err = binding.last_error(L)
+                for j in jobs:
+                    L.shv_cuda_job_wait(j)
+                    L.shv_cuda_job_free(j)
+                raise RuntimeError(err)
+            jobs.append(job)
+            keep.append(k)
+            self.frames_sent[p] += new
+        sizes, failed = [], None
+        bw = binding.C.c_int()
+        for j in jobs:
+            if L.shv_cuda_job_wait(j) != 0 and failed is None:
+                failed = L.shv_cuda_job_error(j).decode()
+            L.shv_cuda_job_timing(j, None, None, None, None, binding.C.byref(bw))
+            sizes.append(bw.value)
+            L.shv_cuda_job_free(j)
+        if failed:
+            raise RuntimeError(failed)
+        return logits, sizes
