@@ -99,11 +99,12 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.rows = []
+        self.rows = []                      # (host time when the sample was read, fields)
+        self.t0 = self.t1 = None            # the timed region, host clock
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -112,7 +113,13 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def stop(self):
         if not self.proc:
@@ -124,7 +131,13 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        # samples read while the timed region ran (a sample describes the 100 ms before it was read, hence the slack);
+        # the sampler runs from before the warm-up steps, so a short region still has the samples around it
+        rows = [r for t, r in self.rows if self.t0 is None or (self.t0 <= t <= (self.t1 or t) + 0.15)]
+        if not rows and self.rows and self.t0 is not None:
+            nearest = min(self.rows, key=lambda tr: abs(tr[0] - self.t0))
+            rows = [nearest[1]]
+        for r in rows:
             if len(r) < 6:
                 continue
             try:
@@ -587,6 +600,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    # Each rank's caller threads and the library's worker threads (they inherit the mask) stay on their own cores.
+    affinity = None
+    if world > 1 and hasattr(os, "sched_setaffinity"):
+        cores = sorted(os.sched_getaffinity(0))
+        per = len(cores) // world
+        if per >= 2:
+            affinity = cores[local_rank * per:(local_rank + 1) * per]
+            os.sched_setaffinity(0, affinity)
     B, mode = args.batch, args.mode
     storage = 4 if mode == "fp32" else 2
     wpath = make_weights(f"r{rank}")
@@ -597,16 +618,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # ------------------------------------------------------------ device-resident throughput
     eng = binding.EngineCore(wpath, mode, device=local_rank, max_windows=B, use_graphs=True)
     eng.bind_tokens(0, tokens.data_ptr(), B, stream)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         eng.classify(0, B, stream)
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.mark_start()
     ev0.record()
     for _ in range(args.steps):
         eng.classify(0, B, stream)
     ev1.record()
     barrier()
+    if sampler:
+        sampler.mark_end()
     ms_step = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
     clocks = sampler.stop() if sampler else None
     if eng.status() != 0:
@@ -699,10 +724,36 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dt = time.perf_counter() - t0
         barrier()
         e2e_ms = max_over_ranks(1000.0 * dt / args.steps)
+        # The uploads alone: the same pinned buffer in the same request-sized pieces to the device, no kernels, all ranks
+        # at once.  What this rate leaves of the end-to-end rate is the host path (PCIe, host memory), not the engine.
+        piece = max(1, model.limits()["max_windows"] // 8)
+        src = torch.from_numpy(pin.array)
+        dst = torch.empty((piece, 20, 16, D), device="cuda", dtype=torch.float32)
+        copy_stream = torch.cuda.Stream()
+
+        def upload_steps(n_steps):
+            with torch.cuda.stream(copy_stream):
+                for _ in range(n_steps):
+                    for lo in range(0, B, piece):
+                        hi = min(B, lo + piece)
+                        dst[: hi - lo].copy_(src[lo:hi], non_blocking=True)
+            copy_stream.synchronize()
+
+        upload_steps(1)
+        barrier()
+        t0 = time.perf_counter()
+        upload_steps(args.steps)
+        h2d_ms = max_over_ranks(1000.0 * (time.perf_counter() - t0) / args.steps)
+        barrier()
+        del dst
         if not np.isfinite(out).all():
             raise SystemExit("end-to-end run returned non-finite logits")
         e2e = {"value": world * B / (e2e_ms / 1000.0), "unit": UNIT, "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": B * 20 * 6144 * 4 + B * 20 * 8, "d2h_bytes_per_step": B * 4,
+               "h2d_only": {"ms_per_step": h2d_ms, "gbs_per_rank": B * 20 * 6144 * 4 / h2d_ms / 1e6, "pinned": bool(src.is_pinned()),
+                            "clips_per_s_if_upload_bound": world * B / (h2d_ms / 1000.0),
+                            "note": "the step's token uploads alone (same pinned buffer, same piece size, no kernels), all "
+                                    "ranks at once, max over ranks"},
                "api": "%d host thread(s), each one synchronous shv_cuda_classify of its B/%d clips per step; pinned host "
                       "tokens (shv_cuda_host_alloc), max_windows = %d" % (nthr, nthr, mw)}
         model.close()
@@ -762,7 +813,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "config": {"workload": f"GDN+SISA sequence stack, B={B} clips per GPU x 321 rows x 384 (20 frames x 16 tokens + "
                                    f"readout), {mode} mode, weights W3 seed 1, tokens N(0,1)",
                        "l2": "inputs and activations exceed L2 (tokens 2 GB, activation arena ~20 GB per step)",
-                       "graphs": True, "sharding": f"{world} x {B} clips by batch, no collective"},
+                       "graphs": True, "sharding": f"{world} x {B} clips by batch, no collective",
+                       "host_cores_per_rank": len(affinity) if affinity else None},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
             "stack_hbm_fraction": {"algorithmic_bytes_per_clip": alg_bytes_clip, "frac": stack_frac,
                                    "note": "whole stack against the GEMM-boundary byte model and the measured HBM peak"},
