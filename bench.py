@@ -416,11 +416,13 @@ def chunked_case(torch, L, dk: int, steps: int, warmup: int):
     g = torch.nn.functional.logsigmoid(rn(B, T, H))
     beta = torch.sigmoid(rn(B, T, H))
     o = torch.zeros(B, T, H, DV, device="cuda", dtype=torch.bfloat16)
+    nws = L.shvk_gdn_chunked_workspace_bytes(B, T, H)
+    ws = torch.empty(nws, device="cuda", dtype=torch.uint8)
     stream = torch.cuda.current_stream().cuda_stream
 
     def run():
         rc = L.shvk_gdn_chunked(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), o.data_ptr(), 1,
-                                B, T, H, dk, DV, float(dk ** -0.5), stream)
+                                B, T, H, dk, DV, float(dk ** -0.5), ws.data_ptr(), nws, stream)
         if rc:
             raise SystemExit(f"shvk_gdn_chunked returned cudaError {rc}")
 
@@ -438,6 +440,7 @@ def chunked_case(torch, L, dk: int, steps: int, warmup: int):
         raise SystemExit("long-sequence kernel returned non-finite outputs")
     pk, src = peaks()
     nbytes = B * T * H * (2 * dk * 2 + DV * 2 + 8 + DV * 2)          # q, k, v in, g and beta in, o out: per token and head
+    # (the kernels also move q and k a second time and 72 bytes per token and head of prepared tiles: not algorithmic)
     C = 64                                                            # flops of the chunked form at chunk 64, per chunk and head
     flops = B * (T // C) * H * (2 * C * (3 * C * dk + 2 * C * DV + 3 * dk * DV) + C * C * C // 3)
     return {"head_dim": dk, "ms": ms, "tokens_per_s": B * T / (ms / 1000.0), "algorithmic_bytes": nbytes,
@@ -460,7 +463,7 @@ def run_chunked(args, local_rank: int):
                                  "DK=128, DV=128, bf16 q/k/v, seed 3", "l2": "inputs exceed L2 (610 / 812 MB per launch)"},
           "roofline": {"bound": "hbm", "achieved": cases[0]["gbs"], "peak": peaks()[0]["hbm_gbs"], "unit": "GB/s",
                        "frac": cases[0]["hbm_frac"], "kernel": "gdn_chunked", "traffic": None},
-          "gpu_launches": 2 * args.steps, "cases": cases})
+          "gpu_launches": 4 * args.steps, "cases": cases})
 
 # ---------------------------------------------------------------------------------------------- same-box GPU baseline
 def reference_gpu_engine(wpath, mode: str, windows: int = 512):

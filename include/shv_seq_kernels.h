@@ -114,10 +114,15 @@ int shvk_gdn_scan_status(int* status_out);
 /* Long-sequence gated delta rule in chunked (WY / UT-transform) form on the tensor cores: the recurrence of
  * oracle/shieldv_ref.py:121-139 (gated_delta_rule_recurrent) for any T, zero initial state.  q, k: [B,T,H,DK] bf16,
  * already L2-normalised; v: [B,T,H,128] bf16; g (log decay) and beta: [B,T,H] fp32; o: [B,T,H,128] in o_dtype (fp32 or
- * bf16); DK 64 or 128; q is multiplied by `scale`.  The reference has no long-T implementation (its sequence length is the
- * compile-time constant 321, engine/cuda/model.hpp:10); this is the stress configuration T = 2048. */
+ * bf16); DK 64 or 128; q is multiplied by `scale`.  Two launches: a chunk-parallel kernel that prepares, for every
+ * block of 16 tokens, everything that does not depend on the state (Gram products, decay masks, the triangular
+ * inverse), and a sequential kernel per (batch, head) that carries the state.  `workspace` (device memory, 16-byte
+ * aligned, at least shvk_gdn_chunked_workspace_bytes(B, T, H) bytes, contents irrelevant before and after) holds what
+ * the first kernel hands to the second: 1,152 bytes per block.  The reference has no long-T implementation (its
+ * sequence length is the compile-time constant 321, engine/cuda/model.hpp:10); this is the stress configuration T = 2048. */
+size_t shvk_gdn_chunked_workspace_bytes(int B, int T, int H);
 int shvk_gdn_chunked(const void* q, const void* k, const void* v, const float* g, const float* beta, void* o, int o_dtype,
-                     int B, int T, int H, int DK, int DV, float scale, void* stream);
+                     int B, int T, int H, int DK, int DV, float scale, void* workspace, size_t workspace_bytes, void* stream);
 
 /* SISA attention of the readout row per (clip, head): -softplus(alpha), logsigmoid(forget), theta prefix sums in
  * double rounded to fp32, pair rotation of B (all rows) and C (row 320), scores, softmax over 321 keys, y = P V.

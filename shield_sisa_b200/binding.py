@@ -151,7 +151,8 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_gdn_scan_t_starved": (i32, [vp, vp, vp, i32, i32, i32, vp]),
         "shvk_gdn_scan": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp]),
         "shvk_gdn_scan_status": (i32, [C.POINTER(i32)]),
-        "shvk_gdn_chunked": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, vp]),
+        "shvk_gdn_chunked_workspace_bytes": (sz, [i32, i32, i32]),
+        "shvk_gdn_chunked": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, vp, sz, vp]),
         "shvk_sisa_attn": (i32, [vp, vp, vp, vp, i32, vp]),
         "shvk_readout_qc": (i32, [vp, C.c_longlong, vp, vp, vp, i32, vp]),
         "shvk_readout_tail": (i32, [vp, vp, C.c_longlong, C.POINTER(ReadoutWeights), vp, vp, i32, vp]),

@@ -19,8 +19,11 @@ def run_chunked(L, q, k, v, g, beta, out_bf16=False):
     Q, K, V = (dev(x.astype(np.float32), torch.bfloat16) for x in (q, k, v))
     G, Bt = dev(g.astype(np.float32)), dev(beta.astype(np.float32))
     out = torch.zeros((b, t, h, dv), device="cuda", dtype=torch.bfloat16 if out_bf16 else torch.float32)
+    nws = L.shvk_gdn_chunked_workspace_bytes(b, t, h)
+    assert nws == b * h * ((t + 15) // 16) * 1152
+    ws = torch.full((nws,), 0xff, device="cuda", dtype=torch.uint8)            # poison: the kernels must not rely on its contents
     rc = L.shvk_gdn_chunked(Q.data_ptr(), K.data_ptr(), V.data_ptr(), G.data_ptr(), Bt.data_ptr(), out.data_ptr(),
-                            1 if out_bf16 else 0, b, t, h, dk, dv, float(dk ** -0.5), stream_ptr())
+                            1 if out_bf16 else 0, b, t, h, dk, dv, float(dk ** -0.5), ws.data_ptr(), nws, stream_ptr())
     assert rc == 0, rc
     sync()
     rounded = tuple(x.float().cpu().numpy().astype(np.float64) for x in (Q, K, V))
@@ -68,9 +71,11 @@ def test_long_sequence_stress_shape(L, dk):
 
 def test_rejects_unsupported_shapes(L):
     import torch
-    x = torch.zeros(16, device="cuda")
+    x = torch.zeros(4096, device="cuda")
     args = [x.data_ptr()] * 6
-    assert L.shvk_gdn_chunked(*args, 0, 1, 16, 1, 32, 128, 1.0, stream_ptr()) != 0      # DK
-    assert L.shvk_gdn_chunked(*args, 0, 1, 16, 1, 64, 64, 1.0, stream_ptr()) != 0       # DV
-    assert L.shvk_gdn_chunked(*args, 2, 1, 16, 1, 64, 128, 1.0, stream_ptr()) != 0      # output type
-    assert L.shvk_gdn_chunked(*args, 0, 0, 16, 1, 64, 128, 1.0, stream_ptr()) == 0      # empty batch
+    ws = (x.data_ptr(), 4096 * 4, stream_ptr())
+    assert L.shvk_gdn_chunked(*args, 0, 1, 16, 1, 32, 128, 1.0, *ws) != 0      # DK
+    assert L.shvk_gdn_chunked(*args, 0, 1, 16, 1, 64, 64, 1.0, *ws) != 0       # DV
+    assert L.shvk_gdn_chunked(*args, 2, 1, 16, 1, 64, 128, 1.0, *ws) != 0      # output type
+    assert L.shvk_gdn_chunked(*args, 0, 1, 16, 1, 64, 128, 1.0, x.data_ptr(), 100, stream_ptr()) != 0   # workspace too small
+    assert L.shvk_gdn_chunked(*args, 0, 0, 16, 1, 64, 128, 1.0, *ws) == 0      # empty batch
