@@ -184,7 +184,7 @@ public:
         starve_kind_ = kind;
         starve_batches_ = batches > 0 ? batches : 0;
     }
-    int launches_per_classify() const override { return 22; }
+    int launches_per_classify() const override { return 23; }
 
     // One eager classify / encode with an event after every launch; returns (kernel name, milliseconds) per launch.
     std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) override {
