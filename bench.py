@@ -55,7 +55,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per clip of one launch, from the ncu captures at B = 512 in the 16-bit
 # modes that are summarised under profiles/ (traffic grows in proportion to the clips of a launch: every clip's tiles
 # are fetched and written once); scaled to the bench's B for the `traffic` key
-NCU_TRAFFIC_PER_CLIP = {"gdn_scan": (801016320 + 234102784) / 512, "gdn_inproj": (128415488 + 744627712) / 512}
+NCU_TRAFFIC_PER_CLIP = {"gdn_scan": (801014016 + 231972608) / 512, "gdn_inproj": (128415488 + 744627712) / 512}
 PT_BYTES_PER_CLIP = 6 * 21 * 12416      # chunk-blocked bf16 operand tiles between the fused in-projection and the scan
 
 

@@ -53,10 +53,17 @@ typedef struct shvk_gemm_args {
 /* IEEE fp32 FMA chain on CUDA cores, k in order (exact tier and the fp32-only last-row projections). A, W fp32. */
 int shvk_gemm_f32(const shvk_gemm_args* g, void* stream);
 /* tcgen05 tensor-core GEMM, A and W in ab_dtype (bf16 or fp16), fp32 accumulation in tensor memory, operands
- * staged by TMA.  Needs K % 64 == 0, 16-byte aligned operands and pitches.  shvk_gemm_tc_plan encodes the two TMA
+ * staged by TMA.  Needs K % 64 == 0, 16-byte aligned operands and pitches.
+ * Exact tier (ab_dtype = SHVK_F32; replaces the SIMT class of engine/cuda/gemm.cuh:66-188 for the all-row GEMMs): fp32
+ * operands split into two TF32 pieces each by shvk_split_tf32, A = [lo | hi] (lda >= 2K), W = [hi | lo | hi]
+ * (ldw >= 3K), K % 32 == 0; one accumulator sums lo*hi, hi*lo, hi*hi over k in that fixed order (K never split, rows
+ * independent), what is dropped is below 2^-21 of each product.  SwiGLU then writes fp32 (c_dtype SHVK_F32).  shvk_gemm_tc_plan encodes the two TMA
  * tensor maps and the tile shape for exactly these operands into a host-side plan that launches reuse.  Plain fp32
  * output with ldc - N < 8: the padding columns N .. ldc-1 may be written with zeros (whole 32-byte sectors per row). */
 int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* host_plan /* >= 512 bytes, host, 64-byte aligned */);
+/* x = hi + lo, hi = x rounded to TF32, lo = x - hi rounded to TF32; rows of K fp32 (K % 4 == 0, 16-byte aligned).
+ * layout 0: out row = [lo | hi] (A operand of the exact tier), layout 1: out row = [hi | lo | hi] (W operand). */
+int shvk_split_tf32(const float* in, long long ld_in, int K, long long rows, float* out, long long ld_out, int layout, void* stream);
 int shvk_gemm_tc(const void* host_plan, void* stream);
 /* Same plan, first `rows` <= M rows only (a smaller batch in buffers sized for the planned M). */
 int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream);

@@ -94,6 +94,28 @@ private:
 int dtype_code(Precision p) { return p == Precision::FP32 ? SHVK_F32 : p == Precision::BF16 ? SHVK_BF16 : SHVK_F16; }
 size_t dtype_bytes(Precision p) { return p == Precision::FP32 ? 4 : 2; }
 
+// Exact tier: a weight matrix [rows][K] as the tensor-core GEMM's split operand [rows][hi | lo | hi], hi = w rounded
+// to TF32 (10 mantissa bits, ties away), lo = w - hi (exact) rounded the same way.
+float tf32_round(float x) {
+    uint32_t u;
+    std::memcpy(&u, &x, 4);
+    if ((u & 0x7f800000u) == 0x7f800000u) return x;       // inf / nan stay
+    u = (u + 0x1000u) & 0xffffe000u;
+    std::memcpy(&x, &u, 4);
+    return x;
+}
+std::vector<float> split_weight(const std::vector<float>& w, int K) {
+    const size_t rows = w.size() / size_t(K);
+    std::vector<float> out(rows * 3 * size_t(K));
+    for (size_t r = 0; r < rows; ++r)
+        for (int k = 0; k < K; ++k) {
+            const float x = w[r * K + k], hi = tf32_round(x), lo = tf32_round(x - hi);
+            float* o = &out[r * 3 * size_t(K)];
+            o[k] = hi; o[K + k] = lo; o[2 * K + k] = hi;
+        }
+    return out;
+}
+
 std::vector<uint8_t> to_storage(const std::vector<float>& v, Precision p) {
     std::vector<uint8_t> out(v.size() * dtype_bytes(p));
     if (p == Precision::FP32) {
@@ -125,6 +147,7 @@ struct Site {
     shvk_gemm_args args{};
     alignas(64) unsigned char plan[512];
     bool planned = false;
+    const float* split_src = nullptr;    // exact tier: the fp32 A operand, split into args.A = [lo | hi] before every launch
 };
 
 class SeqEngine final : public Engine {
@@ -175,7 +198,7 @@ public:
     int device_status() const override {
         int scan = 0, gemm = 0;
         if (shvk_gdn_scan_status(&scan) != 0) return -1;
-        if (prec_ != Precision::FP32 && shvk_gemm_tc_status(&gemm) != 0) return -1;
+        if (shvk_gemm_tc_status(&gemm) != 0) return -1;
         return scan ? 16 + scan : gemm;
     }
     void inject_wait_timeout(int kind, int batches) override {
@@ -184,7 +207,8 @@ public:
         starve_kind_ = kind;
         starve_batches_ = batches > 0 ? batches : 0;
     }
-    int launches_per_classify() const override { return 23; }
+    // 23 kernels; the exact tier splits the A operand of each of its 11 all-row GEMMs in a launch of its own
+    int launches_per_classify() const override { return prec_ == Precision::FP32 ? 34 : 23; }
 
     // One eager classify / encode with an event after every launch; returns (kernel name, milliseconds) per launch.
     std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) override {
@@ -215,6 +239,7 @@ private:
     // activations
     float *h_ = nullptr, *P_ = nullptr;
     void *xn_ = nullptr, *on_ = nullptr, *hid_ = nullptr;
+    float* a2_ = nullptr;
     float *qc_ = nullptr, *y_ = nullptr, *x2_ = nullptr;
     Site in_[2], oproj_[2], up_[2], down_[2], sisa_in_;
     alignas(64) unsigned char inproj_plan_[2][512];   // 16-bit modes: fused in-projection (TMA maps for xn, W', PT = P_)
@@ -320,7 +345,7 @@ private:
             f32(&g.conv_w, gh[i]->conv_w); f32(&g.conv_b, gh[i]->conv_b);
             f32(&g.a_log, gh[i]->a_log); f32(&g.dt_bias, gh[i]->dt_bias); f32(&g.o_norm_w, gh[i]->o_norm_w);
             if (prec_ == Precision::FP32) {
-                stor(&g.in_w, gh[i]->in_w);
+                f32(reinterpret_cast<const float**>(&g.in_w), split_weight(gh[i]->in_w, D));
             } else {
                 // rows of [q | k | v | gate | a | b] regrouped per head into the 128-row channel tiles of the fused
                 // in-projection kernel; rows it does not use are zero
@@ -332,12 +357,19 @@ private:
                     if (order[r] >= 0) std::memcpy(&perm[r * D], &gh[i]->in_w[size_t(order[r]) * D], D * sizeof(float));
                 stor(&g.in_w_perm, perm);
             }
-            stor(&g.o_proj, gh[i]->o_proj);
-            stor(&g.ffn_up, gh[i]->ffn_up); stor(&g.ffn_down, gh[i]->ffn_down);
+            if (prec_ == Precision::FP32) {
+                f32(reinterpret_cast<const float**>(&g.o_proj), split_weight(gh[i]->o_proj, VD));
+                f32(reinterpret_cast<const float**>(&g.ffn_up), split_weight(gh[i]->ffn_up, D));
+                f32(reinterpret_cast<const float**>(&g.ffn_down), split_weight(gh[i]->ffn_down, DFF));
+            } else {
+                stor(&g.o_proj, gh[i]->o_proj);
+                stor(&g.ffn_up, gh[i]->ffn_up); stor(&g.ffn_down, gh[i]->ffn_down);
+            }
         }
         const SisaHost& sh = hm.sisa;
         f32(&s_attn_norm_, sh.attn_norm_w);
-        stor(&s_w_all_, sh.w_all);
+        if (prec_ == Precision::FP32) f32(reinterpret_cast<const float**>(&s_w_all_), split_weight(sh.w_all, D));
+        else stor(&s_w_all_, sh.w_all);
         f32(&s_b_all_, sh.b_all); f32(&s_lambda_, sh.lambda_raw);
         f32(&s_ffn_norm_, sh.ffn_norm_w);
         // the readout-row kernels read their matrices column-wise across a warp: [K][N] copies
@@ -376,6 +408,8 @@ private:
         const size_t o_h = acts_.reserve(Mm * D * 4), o_p = acts_.reserve(Mm * GLD * 4), o_xn = acts_.reserve(Mm * D * ts);
         const size_t o_on = acts_.reserve(Mm * VD * ts), o_hid = acts_.reserve(Mm * DFF * ts);
         const size_t o_qc = acts_.reserve(Bm * SQN * 4), o_y = acts_.reserve(Bm * D * 4), o_x2 = acts_.reserve(Bm * D * 4);
+        // exact tier: the split A operand [lo | hi] of the GEMM about to run (widest: the FFN hidden layer)
+        const size_t o_a2 = acts_.reserve(prec_ == Precision::FP32 ? Mm * 2 * DFF * 4 : 0);
         // frame encoder: block input / output X, expanded E, depthwise output Dd (largest layer of each kind), the
         // squeeze-excite partial sums and gates, the pooled map
         size_t x_fl = size_t(90) * 160 * 16, e_fl = size_t(60) * CNN_OUT, d_fl = 0, part_fl = 0;
@@ -394,6 +428,7 @@ private:
         h_ = acts_.at<float>(o_h); P_ = acts_.at<float>(o_p);
         xn_ = acts_.at<void>(o_xn); on_ = acts_.at<void>(o_on); hid_ = acts_.at<void>(o_hid);
         qc_ = acts_.at<float>(o_qc); y_ = acts_.at<float>(o_y); x2_ = acts_.at<float>(o_x2);
+        a2_ = prec_ == Precision::FP32 ? acts_.at<float>(o_a2) : nullptr;
         act_bytes_ = acts_.size();
 
         slots_.resize(size_t(cfg_.slots));
@@ -424,6 +459,10 @@ private:
         a.A = A; a.lda = K; a.W = W; a.ldw = K;
         a.C = C; a.ldc = ldc; a.c_dtype = c_dtype;
         a.r_div = 1.0f;
+        if (prec_ == Precision::FP32) {          // split operands: A = [lo | hi] in a2_, W = [hi | lo | hi]
+            st.split_src = static_cast<const float*>(A);
+            a.A = a2_; a.lda = 2 * K; a.ldw = 3 * K;
+        }
     }
     void plan_sites() {
         const float inv_div[2] = {1.0f, float(std::sqrt(2.0))};
@@ -439,10 +478,16 @@ private:
         }
         make_site(sisa_in_, SN, D, xn_, s_w_all_, P_, SLD, SHVK_F32);
         sisa_in_.args.bias = s_b_all_;
-        if (prec_ == Precision::FP32) return;
         for (Site* st : {&oproj_[0], &oproj_[1], &up_[0], &up_[1], &down_[0], &down_[1], &sisa_in_}) {
             launch_ok(shvk_gemm_tc_plan(&st->args, dt_, st->plan), "tensor-core GEMM plan");
             st->planned = true;
+        }
+        if (prec_ == Precision::FP32) {
+            for (Site* st : {&in_[0], &in_[1]}) {
+                launch_ok(shvk_gemm_tc_plan(&st->args, dt_, st->plan), "tensor-core GEMM plan");
+                st->planned = true;
+            }
+            return;
         }
         // the chunk-blocked operand tiles of the in-projection live where the fp32 projection of the exact tier would
         if (shvk_gdn_pt_bytes(cfg_.max_windows) > size_t(cfg_.max_windows) * NTOK * GLD * 4)
@@ -453,6 +498,10 @@ private:
     }
     void rows_gemm(const Site& st, int rows, cudaStream_t s) {
         if (st.planned) {
+            if (st.split_src) {
+                launch_ok(shvk_split_tf32(st.split_src, st.args.K, st.args.K, rows, a2_, 2 * st.args.K, 0, s), "operand split");
+                mark("split_tf32", s);
+            }
             launch_ok(shvk_gemm_tc_rows(st.plan, rows, s), "tensor-core GEMM");
         } else {
             shvk_gemm_args a = st.args;

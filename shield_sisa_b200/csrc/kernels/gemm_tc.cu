@@ -1,6 +1,12 @@
 // Projection GEMMs on the 5th-generation tensor cores: C = epilogue(A * W^T), A [M,K] and W [N,K] both K-contiguous,
 // 16-bit operands (bf16 or fp16), fp32 accumulation in tensor memory.
 //
+// Exact tier: the same pipeline with fp32 operands split into two TF32 pieces each (x = hi + lo, hi = x rounded to
+// TF32, lo = x - hi rounded to TF32, what is dropped is below 2^-21 |x|).  A arrives as [lo | hi] (2K columns), W as
+// [hi | lo | hi] (3K columns); the k loop runs over the 3K columns of W and takes A's hi columns a second time for
+// the last third, so one accumulator sums lo*hi, then hi*lo, then hi*hi (small terms first) on kind::tf32 MMAs.  Per
+// k block of 128 bytes the timeline is the one of the 16-bit kernel; there are six times as many k blocks.
+//
 // One persistent CTA per SM, 320 threads in three roles:
 //   warp 0      TMA producer: one lane streams 128 x 64 tiles of A and BN x 64 tiles of W (128-byte swizzle) into a
 //               shared-memory ring, completion counted in bytes on an mbarrier per stage
@@ -36,8 +42,8 @@
 namespace sb {
 namespace {
 
-constexpr int TILE_M = 128, TILE_K = 64, MAX_BN = 240, ACC_COLS = 256;
-constexpr int A_BYTES = TILE_M * TILE_K * 2, B_BYTES = MAX_BN * TILE_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TILE_M = 128, ROW_BYTES = 128, MAX_BN = 240, ACC_COLS = 256;   // an operand stage row is 128 bytes: 64 16-bit or 32 fp32 elements
+constexpr int A_BYTES = TILE_M * ROW_BYTES, B_BYTES = MAX_BN * ROW_BYTES, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_TILE = 32 * 128;                               // 32 rows x 128 bytes
 constexpr int BAR_BYTES = 512;
 static_assert(STAGE_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
@@ -60,6 +66,9 @@ struct TcParams {
     const float* bias;
     float r_div;
     uint32_t idesc;
+    int tile_k;     // operand elements per 128-byte stage row: 64 (16-bit) or 32 (fp32 read as TF32)
+    int tf32;       // 1: kind::tf32 MMAs on split fp32 operands
+    int a_wrap;     // exact tier: A has a_wrap columns ([lo | hi]); k beyond them takes the second half again.  0: none
     int m_major;    // tile order: 1 = a CTA finishes all column tiles of a row block before its next row block
     uint32_t spin_limit;   // polls before a wait gives up (SPIN_LIMIT; the starved test launch passes a small number)
     int starve;     // test launch only: the producer withholds the first operand stage of its first tile
@@ -88,10 +97,22 @@ struct TcMaps {
 //   fp32 tiles, 32 columns: 128-byte rows, 16-byte chunk j of row l at chunk j ^ (l & 7) (the TMA 128-byte swizzle,
 //                           which also makes these stores bank-conflict free); 16 columns: dense 64-byte rows
 //   EPI_RESID: the tile already holds R (TMA load); v = R + acc / r_div overwrites it in place
-//   EPI_SWIGLU: adjacent accumulator columns are (gate, up): silu(gate) * up in storage type T, dense rows
+//   EPI_SWIGLU: adjacent accumulator columns are (gate, up): silu(gate) * up in storage type T, dense rows (16-bit T:
+//               hardware exp; T = float, the exact tier: expf and a true division, 64-byte rows)
 template <typename T, int EPI>
 __device__ __forceinline__ void stage_block(const TcParams& p, uint32_t tile, int lane, bool full, int n, const uint32_t* r) {
-    if constexpr (EPI == EPI_SWIGLU) {
+    if constexpr (EPI == EPI_SWIGLU && sizeof(T) == 4) {
+        const uint32_t row = tile + uint32_t(lane) * (full ? 64u : 32u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (j < 2 || full) {
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] = silu_f(__uint_as_float(r[8 * j + 2 * e])) * __uint_as_float(r[8 * j + 2 * e + 1]);
+                sts128(row + 16u * j, v[0], v[1], v[2], v[3]);
+            }
+        }
+    } else if constexpr (EPI == EPI_SWIGLU) {
         uint32_t o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -195,8 +216,8 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abortp = &abort_flag;
 
-    const int nk = p.K / TILE_K;
-    const uint32_t stage_tx = uint32_t(A_BYTES + p.BN * TILE_K * 2);
+    const int nk = p.K / p.tile_k;
+    const uint32_t stage_tx = uint32_t(A_BYTES + p.BN * ROW_BYTES);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -214,13 +235,15 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                         continue;
                     }
                     const uint32_t sa = base + stage * STAGE_BYTES, sb_ = sa + A_BYTES;
+                    const int kw = kb * p.tile_k;
+                    const int ka = p.a_wrap && kw >= p.a_wrap ? kw - (p.a_wrap >> 1) : kw;
                     const bool la = !(probe_bits(p) & 16), lw = !(probe_bits(p) & 8);
                     if (la || lw) {
                         mbar_expect_tx(full_bar(stage), (la ? uint32_t(A_BYTES) : 0u) + (lw ? stage_tx - uint32_t(A_BYTES) : 0u));
-                        if (la) tma_load_2d(sa, &maps.a, kb * TILE_K, mt * TILE_M, full_bar(stage));
+                        if (la) tma_load_2d(sa, &maps.a, ka, mt * TILE_M, full_bar(stage));
                         if (lw) {
-                            if (hint) tma_load_2d_hint(sb_, &maps.w, kb * TILE_K, nt * p.BN, full_bar(stage), pol_w);
-                            else tma_load_2d(sb_, &maps.w, kb * TILE_K, nt * p.BN, full_bar(stage));
+                            if (hint) tma_load_2d_hint(sb_, &maps.w, kw, nt * p.BN, full_bar(stage), pol_w);
+                            else tma_load_2d(sb_, &maps.w, kw, nt * p.BN, full_bar(stage));
                         }
                     } else {
                         mbar_arrive(full_bar(stage));
@@ -245,9 +268,15 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                     tc_fence_after();
                     const uint32_t sa = base + stage * STAGE_BYTES, sb_ = sa + A_BYTES;
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb_);
+                    if (p.tf32) {
 #pragma unroll
-                    for (int k = 0; k < TILE_K / 16; ++k)          // 16 elements = 32 bytes = 2 descriptor units
-                        if (!(probe_bits(p) & 4)) tc_mma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
+                        for (int k = 0; k < ROW_BYTES / 32; ++k)       // 8 fp32 elements = 32 bytes = 2 descriptor units
+                            tc_mma_tf32(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < ROW_BYTES / 32; ++k)       // 16 elements = 32 bytes = 2 descriptor units
+                            if (!(probe_bits(p) & 4)) tc_mma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
+                    }
                     tc_commit(empty_bar(stage));
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -459,15 +488,19 @@ using ShapeDefault = Shape<3, 8, 2>;
 extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* host_plan) {
     using namespace sb;
     if (!g || !host_plan || (reinterpret_cast<uintptr_t>(host_plan) & 63)) return int(cudaErrorInvalidValue);
-    if (ab_dtype != DT_BF16 && ab_dtype != DT_F16) return int(cudaErrorInvalidValue);
-    if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->K % TILE_K || (g->lda & 7) || (g->ldw & 7) || (g->N & 3) ||
+    if (ab_dtype != DT_BF16 && ab_dtype != DT_F16 && ab_dtype != DT_F32) return int(cudaErrorInvalidValue);
+    const bool split = ab_dtype == DT_F32;              // exact tier: A = [lo | hi] (2K fp32), W = [hi | lo | hi] (3K fp32)
+    const int tile_k = split ? 32 : 64;
+    const int align = split ? 3 : 7;                    // 16-byte pitches
+    if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->K % tile_k || (g->lda & align) || (g->ldw & align) || (g->N & 3) ||
+        (split && (g->lda < 2ll * g->K || g->ldw < 3ll * g->K)) ||
         ((reinterpret_cast<uintptr_t>(g->A) | reinterpret_cast<uintptr_t>(g->W) | reinterpret_cast<uintptr_t>(g->C)) & 15) ||
         (g->R && ((g->ldr & 3) || (reinterpret_cast<uintptr_t>(g->R) & 15))) || g->act != 0)
         return int(cudaErrorInvalidValue);
-    // supported epilogues: fp32 C (+ bias), fp32 C = R + acc / r_div, SwiGLU into 16-bit C
+    // supported epilogues: fp32 C (+ bias), fp32 C = R + acc / r_div, SwiGLU into 16-bit C (fp32 C in the exact tier)
     int epi;
     if (g->swiglu) {
-        if ((g->N & 7) || g->c_dtype == DT_F32 || g->R || g->bias || (g->ldc & 7)) return int(cudaErrorInvalidValue);
+        if ((g->N & 7) || (g->c_dtype == DT_F32) != split || g->R || g->bias || (g->ldc & (split ? 3 : 7))) return int(cudaErrorInvalidValue);
         epi = EPI_SWIGLU;
     } else {
         if (g->c_dtype != DT_F32 || (g->ldc & 3) || (g->R && g->bias)) return int(cudaErrorInvalidValue);
@@ -476,15 +509,17 @@ extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* ho
     HostPlan* hp = static_cast<HostPlan*>(host_plan);
     memset(hp, 0, sizeof(HostPlan));
     const int bn = choose_bn(g->N);
-    if (!make_map(&hp->map_a, g->A, 2, g->M, g->K, g->lda, TILE_M, TILE_K, true)) return int(cudaErrorNotSupported);
-    if (!make_map(&hp->map_w, g->W, 2, g->N, g->K, g->ldw, bn, TILE_K, true)) return int(cudaErrorNotSupported);
+    const int eb = split ? 4 : 2;
+    if (!make_map(&hp->map_a, g->A, eb, g->M, split ? 2ll * g->K : g->K, g->lda, TILE_M, tile_k, true)) return int(cudaErrorNotSupported);
+    if (!make_map(&hp->map_w, g->W, eb, g->N, split ? 3ll * g->K : g->K, g->ldw, bn, tile_k, true)) return int(cudaErrorNotSupported);
     TcParams& p = hp->p;
-    p.M = g->M; p.N = g->N; p.K = g->K; p.BN = bn;
+    p.M = g->M; p.N = g->N; p.K = split ? 3 * g->K : g->K; p.BN = bn;
+    p.tile_k = tile_k; p.tf32 = split ? 1 : 0; p.a_wrap = split ? 2 * g->K : 0;
     p.n_tiles = (g->N + bn - 1) / bn;
     p.m_tiles = (g->M + TILE_M - 1) / TILE_M;
     p.bias = g->bias;
     p.r_div = g->r_div == 0.0f ? 1.0f : g->r_div;
-    const uint32_t fmt = ab_dtype == DT_BF16 ? 1u : 0u;
+    const uint32_t fmt = split ? 2u : (ab_dtype == DT_BF16 ? 1u : 0u);      // f16 0, bf16 1, tf32 2
     // instruction descriptor: D fp32 (bits 4-5 = 1), A/B format (bits 7-9, 10-12), both K-major, N/8 at bit 17,
     // M/16 at bit 24
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(TILE_M >> 4) << 24);
@@ -521,8 +556,9 @@ int launch_rows(const void* host_plan, int rows, void* stream, int starve, uint3
     maps.w = hp->map_w;
     bool ok;
     if (hp->epi == EPI_SWIGLU) {
-        ok = make_map(&maps.c_full, hp->C, 2, rows, p.N / 2, hp->ldc, 32, 16, false) &&
-             make_map(&maps.c_half, hp->C, 2, rows, p.N / 2, hp->ldc, 32, 8, false);
+        const int cb = hp->c_dtype == DT_F32 ? 4 : 2;
+        ok = make_map(&maps.c_full, hp->C, cb, rows, p.N / 2, hp->ldc, 32, 16, false) &&
+             make_map(&maps.c_half, hp->C, cb, rows, p.N / 2, hp->ldc, 32, 8, false);
         maps.r_full = maps.c_full;
         maps.r_half = maps.c_half;
     } else {
@@ -542,6 +578,7 @@ int launch_rows(const void* host_plan, int rows, void* stream, int starve, uint3
     cudaStream_t s = cudaStream_t(stream);
     if (hp->epi == EPI_PLAIN) return launch_tc<float, EPI_PLAIN, ShapeDefault>(maps, p, s);
     if (hp->epi == EPI_RESID) return launch_tc<float, EPI_RESID, ShapeDefault>(maps, p, s);
+    if (hp->c_dtype == DT_F32) return launch_tc<float, EPI_SWIGLU, ShapeDefault>(maps, p, s);
     if (hp->c_dtype == DT_BF16) return launch_tc<__nv_bfloat16, EPI_SWIGLU, ShapeDefault>(maps, p, s);
     return launch_tc<__half, EPI_SWIGLU, ShapeDefault>(maps, p, s);
 }

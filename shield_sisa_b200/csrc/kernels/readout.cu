@@ -6,25 +6,27 @@
 //                 z = rmsnorm(x2) * w;  logit = w2 . silu(W0 z + b0) + b2                           (after sisa_attn)
 //
 // Only row 320 leaves the SISA block, so this work is B rows, not 321 B (engine/cuda/engine.cu:451-469;
-// engine/model/isa_impl.hpp:1092-1133).  A CTA takes TB = 16 clips and walks the small matrix products one after the
+// engine/model/isa_impl.hpp:1092-1133).  A CTA takes TB clips (16 when the batch is large enough to give every SM a CTA that way, else 4 or 1) and walks the small matrix products one after the
 // other with all activations of its clips in shared memory: a thread owns one or two output columns for all 16 clips
 // (16 or 32 accumulators), reads its weights coalesced from a [K][N] (transposed) copy that stays in L2, and the
 // activations as 128-bit broadcast loads.  Every output is one fp32 FMA chain over k in ascending order, whatever the
-// batch, so a clip's logit does not depend on its neighbours (engine/include/shv_cuda.h:31-34).
+// batch and whatever TB, so a clip's logit does not depend on its neighbours (engine/include/shv_cuda.h:31-34).
 //
 // Replaces two launch_rmsnorm, five gemm<float> and launch_head of the reference's run_classify
 // (engine/cuda/engine.cu:451-469, engine/cuda/seq.cu:309-336).
 #include "device_utils.cuh"
 #include "shv_seq_kernels.h"
 
+#include <stdlib.h>
+
 namespace sb {
 namespace {
 
-constexpr int TB = 16, NT = 256;
+constexpr int NT = 256;
 constexpr int XP = kD + 4, HP = kDFF + 4;     // row pitches (floats) of the shared-memory activation tiles
 
 // acc[c][e] = sum_k X[c][k] * Wt[k][n0 + e], e < NC, for the TB clips of the tile; k ascending, one FMA chain per output.
-template <int K, int NC>
+template <int K, int NC, int TB>
 __device__ __forceinline__ void dot_columns(const float* __restrict__ X, int xp, const float* __restrict__ Wt, int ldw, int n0,
                                             float (&acc)[TB][NC]) {
 #pragma unroll
@@ -32,7 +34,9 @@ __device__ __forceinline__ void dot_columns(const float* __restrict__ X, int xp,
 #pragma unroll
         for (int e = 0; e < NC; ++e) acc[c][e] = 0.0f;
     const float* wp = Wt + n0;
-#pragma unroll 2
+    // few clips per CTA leave registers for a deeper run of weight loads in flight (the small-batch launch is bound by L2 latency)
+    constexpr int kDepth = TB >= 8 ? 2 : 8;
+#pragma unroll kDepth
     for (int k = 0; k < K; k += 4) {
         float w[4][NC];
 #pragma unroll
@@ -60,6 +64,7 @@ __device__ __forceinline__ void dot_columns(const float* __restrict__ X, int xp,
 
 // out[c] = (in[c] * (1 / sqrt(mean(in[c]^2) + 1e-6))) * w over rows of 384 in shared memory; warp w takes clips w, w + 8.
 // A row is read into registers before it is written, so out may be in.
+template <int TB>
 __device__ __forceinline__ void norm_rows(const float* in, float* out, const float* __restrict__ w, int warp, int lane) {
     for (int c = warp; c < TB; c += NT / 32) {
         float v[kD / 32];
@@ -76,6 +81,7 @@ __device__ __forceinline__ void norm_rows(const float* in, float* out, const flo
     }
 }
 
+template <int TB>
 __global__ void __launch_bounds__(NT)
 readout_qc_kernel(const float* __restrict__ h_last, long long ldh, const float* __restrict__ norm_w, const float* __restrict__ wqc_t,
                   float* __restrict__ QC, int B) {
@@ -87,11 +93,11 @@ readout_qc_kernel(const float* __restrict__ h_last, long long ldh, const float* 
         xs[c * XP + k] = clip0 + c < B ? h_last[(long long)(clip0 + c) * ldh + k] : 0.0f;
     }
     __syncthreads();
-    norm_rows(xs, xs, norm_w, warp, lane);
+    norm_rows<TB>(xs, xs, norm_w, warp, lane);
     __syncthreads();
     for (int n0 = 2 * tid; n0 < kSQN; n0 += 2 * NT) {          // 576 columns = 288 pairs
         float acc[TB][2];
-        dot_columns<kD, 2>(xs, XP, wqc_t, kSQN, n0, acc);
+        dot_columns<kD, 2, TB>(xs, XP, wqc_t, kSQN, n0, acc);
 #pragma unroll
         for (int c = 0; c < TB; ++c)
             if (clip0 + c < B) *reinterpret_cast<float2*>(QC + (long long)(clip0 + c) * kSQN + n0) = make_float2(acc[c][0], acc[c][1]);
@@ -110,6 +116,7 @@ struct TailWeights {
     const float *head_b2;       // [1]
 };
 
+template <int TB>
 __global__ void __launch_bounds__(NT)
 readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_last, long long ldh, const TailWeights tw,
                     float* __restrict__ x2_out, float* __restrict__ logits, int B) {
@@ -129,7 +136,7 @@ readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_las
     // x1 = h + Y . W_O^T: 192 column pairs
     float keep[TB][2];
     if (tid < kD / 2) {
-        dot_columns<kD, 2>(xa, XP, tw.wo_t, kD, 2 * tid, keep);
+        dot_columns<kD, 2, TB>(xa, XP, tw.wo_t, kD, 2 * tid, keep);
 #pragma unroll
         for (int c = 0; c < TB; ++c) {
             float2* p = reinterpret_cast<float2*>(x1 + c * XP + 2 * tid);
@@ -138,19 +145,19 @@ readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_las
         }
     }
     __syncthreads();
-    norm_rows(x1, xa, tw.ffn_norm_w, warp, lane);
+    norm_rows<TB>(x1, xa, tw.ffn_norm_w, warp, lane);
     __syncthreads();
     // hid[j] = silu(gate_j) * up_j: 960 (gate, up) column pairs
     for (int j = tid; j < kDFF; j += NT) {
         float acc[TB][2];
-        dot_columns<kD, 2>(xa, XP, tw.up_t, 2 * kDFF, 2 * j, acc);
+        dot_columns<kD, 2, TB>(xa, XP, tw.up_t, 2 * kDFF, 2 * j, acc);
 #pragma unroll
         for (int c = 0; c < TB; ++c) hid[c * HP + j] = silu_f(acc[c][0]) * acc[c][1];
     }
     __syncthreads();
     // x2 = x1 + hid . W_down^T
     if (tid < kD / 2) {
-        dot_columns<kDFF, 2>(hid, HP, tw.down_t, kD, 2 * tid, keep);
+        dot_columns<kDFF, 2, TB>(hid, HP, tw.down_t, kD, 2 * tid, keep);
 #pragma unroll
         for (int c = 0; c < TB; ++c) {
             float2* p = reinterpret_cast<float2*>(x1 + c * XP + 2 * tid);
@@ -161,13 +168,13 @@ readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_las
         }
     }
     __syncthreads();
-    norm_rows(x1, xa, tw.final_norm_w, warp, lane);
+    norm_rows<TB>(x1, xa, tw.final_norm_w, warp, lane);
     __syncthreads();
     // head: 128 hidden units (one column per thread of the first four warps), then their weighted sum per clip
     float* hh = hid;                         // [TB][128]; the SwiGLU product is consumed
     if (tid < 128) {
         float acc[TB][1];
-        dot_columns<kD, 1>(xa, XP, tw.head_w0_t, 128, tid, acc);
+        dot_columns<kD, 1, TB>(xa, XP, tw.head_w0_t, 128, tid, acc);
         const float b0 = __ldg(tw.head_b0 + tid), w2 = __ldg(tw.head_w2 + tid);
 #pragma unroll
         for (int c = 0; c < TB; ++c) hh[c * 128 + tid] = w2 * silu_f(acc[c][0] + b0);
@@ -179,7 +186,33 @@ readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_las
     }
 }
 
-constexpr int TAIL_SMEM_BYTES = (2 * TB * XP + TB * HP) * int(sizeof(float));
+constexpr int tail_smem_bytes(int tb) { return (2 * tb * XP + tb * HP) * int(sizeof(float)); }
+
+// Clips per CTA for a batch of B: 16 once that still gives every SM a CTA, else 4, else 1.
+int clips_per_cta(int B) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int tb = B >= 16 * sms ? 16 : B >= 4 * sms ? 4 : 1;
+#ifdef SHVK_DEV_PROBES
+    if (const char* e = getenv("SHVK_READOUT_TB")) tb = atoi(e);
+#endif
+    return tb;
+}
+
+template <int TB>
+int launch_qc(const float* h_last, long long ldh, const float* norm_w, const float* wqc_t, float* QC, int B, cudaStream_t s) {
+    readout_qc_kernel<TB><<<unsigned((B + TB - 1) / TB), NT, 0, s>>>(h_last, ldh, norm_w, wqc_t, QC, B);
+    return int(cudaGetLastError());
+}
+template <int TB>
+int launch_tail(const float* Y, const float* h_last, long long ldh, const TailWeights& tw, float* x2_out, float* logits, int B,
+                cudaStream_t s) {
+    const cudaError_t e = cudaFuncSetAttribute(readout_tail_kernel<TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, tail_smem_bytes(TB));
+    if (e != cudaSuccess) return int(e);
+    readout_tail_kernel<TB><<<unsigned((B + TB - 1) / TB), NT, tail_smem_bytes(TB), s>>>(Y, h_last, ldh, tw, x2_out, logits, B);
+    return int(cudaGetLastError());
+}
 
 }  // namespace
 }  // namespace sb
@@ -188,18 +221,27 @@ extern "C" int shvk_readout_qc(const float* h_last, long long ldh, const float* 
                                void* stream) {
     if (B <= 0) return 0;
     if (!h_last || !norm_w || !wqc_t || !QC) return int(cudaErrorInvalidValue);
-    sb::readout_qc_kernel<<<unsigned((B + sb::TB - 1) / sb::TB), sb::NT, 0, cudaStream_t(stream)>>>(h_last, ldh, norm_w, wqc_t, QC, B);
-    return int(cudaGetLastError());
+    cudaStream_t s = cudaStream_t(stream);
+    switch (sb::clips_per_cta(B)) {
+        case 16: return sb::launch_qc<16>(h_last, ldh, norm_w, wqc_t, QC, B, s);
+        case 8: return sb::launch_qc<8>(h_last, ldh, norm_w, wqc_t, QC, B, s);
+        case 4: return sb::launch_qc<4>(h_last, ldh, norm_w, wqc_t, QC, B, s);
+        case 2: return sb::launch_qc<2>(h_last, ldh, norm_w, wqc_t, QC, B, s);
+        default: return sb::launch_qc<1>(h_last, ldh, norm_w, wqc_t, QC, B, s);
+    }
 }
 
 extern "C" int shvk_readout_tail(const float* Y, const float* h_last, long long ldh, const shvk_readout_weights* w, float* x2_out,
                                  float* logits, int B, void* stream) {
     if (B <= 0) return 0;
     if (!Y || !h_last || !w || !logits) return int(cudaErrorInvalidValue);
-    sb::TailWeights tw{w->wo_t, w->ffn_norm_w, w->up_t, w->down_t, w->final_norm_w, w->head_w0_t, w->head_b0, w->head_w2, w->head_b2};
-    const cudaError_t e = cudaFuncSetAttribute(sb::readout_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sb::TAIL_SMEM_BYTES);
-    if (e != cudaSuccess) return int(e);
-    sb::readout_tail_kernel<<<unsigned((B + sb::TB - 1) / sb::TB), sb::NT, sb::TAIL_SMEM_BYTES, cudaStream_t(stream)>>>(
-        Y, h_last, ldh, tw, x2_out, logits, B);
-    return int(cudaGetLastError());
+    const sb::TailWeights tw{w->wo_t, w->ffn_norm_w, w->up_t, w->down_t, w->final_norm_w, w->head_w0_t, w->head_b0, w->head_w2, w->head_b2};
+    cudaStream_t s = cudaStream_t(stream);
+    switch (sb::clips_per_cta(B)) {
+        case 16: return sb::launch_tail<16>(Y, h_last, ldh, tw, x2_out, logits, B, s);
+        case 8: return sb::launch_tail<8>(Y, h_last, ldh, tw, x2_out, logits, B, s);
+        case 4: return sb::launch_tail<4>(Y, h_last, ldh, tw, x2_out, logits, B, s);
+        case 2: return sb::launch_tail<2>(Y, h_last, ldh, tw, x2_out, logits, B, s);
+        default: return sb::launch_tail<1>(Y, h_last, ldh, tw, x2_out, logits, B, s);
+    }
 }

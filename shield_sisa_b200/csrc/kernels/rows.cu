@@ -80,8 +80,50 @@ store_tokens_kernel(const float4* __restrict__ src, const int32_t* __restrict__ 
     if (s >= 0) pool[(long long)s * kBlockWords + (i - f * kBlockWords)] = src[i];
 }
 
+// Exact-tier operand split: x = hi + lo with hi = x rounded to TF32 (10 mantissa bits) and lo = x - hi (exact in
+// fp32) rounded to TF32 as well, so neither piece has bits the tensor core would drop.  One thread per four elements.
+//   layout 0 (activations): out row = [lo | hi]        (2K)
+//   layout 1 (weights):     out row = [hi | lo | hi]   (3K)
+__device__ __forceinline__ float tf32_rna(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+__global__ void __launch_bounds__(256)
+split_tf32_kernel(const float* __restrict__ in, long long ld_in, int k4, long long rows, float* __restrict__ out, long long ld_out,
+                  int K, int layout) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= rows * k4) return;
+    const long long r = i / k4;
+    const int c = int(i - r * k4) * 4;
+    const float4 x = *reinterpret_cast<const float4*>(in + r * ld_in + c);
+    float4 hi, lo;
+    hi.x = tf32_rna(x.x); hi.y = tf32_rna(x.y); hi.z = tf32_rna(x.z); hi.w = tf32_rna(x.w);
+    lo.x = tf32_rna(x.x - hi.x); lo.y = tf32_rna(x.y - hi.y); lo.z = tf32_rna(x.z - hi.z); lo.w = tf32_rna(x.w - hi.w);
+    float* o = out + r * ld_out + c;
+    if (layout == 0) {
+        *reinterpret_cast<float4*>(o) = lo;
+        *reinterpret_cast<float4*>(o + K) = hi;
+    } else {
+        *reinterpret_cast<float4*>(o) = hi;
+        *reinterpret_cast<float4*>(o + K) = lo;
+        *reinterpret_cast<float4*>(o + 2 * K) = hi;
+    }
+}
+
 }  // namespace
 }  // namespace sb
+
+extern "C" int shvk_split_tf32(const float* in, long long ld_in, int K, long long rows, float* out, long long ld_out, int layout,
+                               void* stream) {
+    if (rows <= 0) return 0;
+    if (!in || !out || K <= 0 || (K & 3) || (ld_in & 3) || (ld_out & 3) || (layout != 0 && layout != 1) ||
+        ld_out < (layout ? 3ll : 2ll) * K || ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15))
+        return int(cudaErrorInvalidValue);
+    const long long n = rows * (K / 4);
+    sb::split_tf32_kernel<<<unsigned((n + 255) / 256), 256, 0, cudaStream_t(stream)>>>(in, ld_in, K / 4, rows, out, ld_out, K, layout);
+    return int(cudaGetLastError());
+}
 
 extern "C" int shvk_assemble_norm(const float* const* tok_ptrs, const float* pos, const float* readout,
                                   const float* norm_w, float* h, void* xn, int xn_dtype, int B, void* stream) {

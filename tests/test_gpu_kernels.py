@@ -198,6 +198,99 @@ def test_gemm_tc_rows_do_not_depend_on_the_batch(L):
     assert torch.equal(big[515], one[0])
 
 
+# ---------------------------------------------------------------------------------------------- exact tier on tensor cores
+def split_operands(L, a, w):
+    """Device [lo | hi] of a and [hi | lo | hi] of w through shvk_split_tf32, checked against the definition."""
+    import torch
+    M, K = a.shape
+    N = w.shape[0]
+    A, Wm = dev(a), dev(w)
+    A2 = torch.zeros((M, 2 * K), device="cuda")
+    W3 = torch.zeros((N, 3 * K), device="cuda")
+    ok(L.shvk_split_tf32(A.data_ptr(), K, K, M, A2.data_ptr(), 2 * K, 0, stream_ptr()))
+    ok(L.shvk_split_tf32(Wm.data_ptr(), K, K, N, W3.data_ptr(), 3 * K, 1, stream_ptr()))
+    sync()
+    a2 = A2.cpu().numpy()
+    lo, hi = a2[:, :K], a2[:, K:]
+    assert ((hi.view(np.uint32) & 0x1fff) == 0).all() and ((lo.view(np.uint32) & 0x1fff) == 0).all()   # TF32-representable
+    assert np.abs(hi - a).max() <= np.abs(a).max() * 2.0 ** -11
+    resid = np.abs(a.astype(np.float64) - hi.astype(np.float64) - lo.astype(np.float64))
+    assert (resid <= np.abs(a) * 2.0 ** -21 + 1e-45).all()
+    w3 = W3.cpu().numpy()
+    np.testing.assert_array_equal(w3[:, :K], w3[:, 2 * K:])
+    return A2, W3
+
+
+@pytest.mark.parametrize("M,N,K", [(700, 2316, 384), (333, 384, 768), (257, 1068, 384)])
+def test_gemm_tc_split_tf32_matches_float64(L, M, N, K):
+    import torch
+    rng = np.random.default_rng(N + K + 1)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    A2, W3 = split_operands(L, a, w)
+    ldc = (N + 3) // 4 * 4 + 4
+    Cm = torch.full((M, ldc), 7.0, device="cuda")
+    g = gemm_args(M, N, K, A2, W3, Cm, ldc)
+    g.lda, g.ldw = 2 * K, 3 * K
+    keep, plan = tc_plan(L, g, 0)
+    ok(L.shvk_gemm_tc(plan, stream_ptr()))
+    sync()
+    assert tc_status(L) == 0
+    got = Cm.cpu().numpy()[:, :N]
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    err = np.abs(got - ref).max()
+    # the SIMT fp32 chain it replaces, for scale
+    chain = np.abs((a @ w.T).astype(np.float64) - ref).max()
+    scale = np.abs(ref).max()
+    print(f"split-TF32 GEMM {M}x{N}x{K}: max abs err {err:.2e} (fp32 matmul on the host: {chain:.2e}), max |ref| {scale:.2f}")
+    assert err < 2e-6 * max(1.0, scale)                    # fp32-class: a few ulp of the largest output
+
+
+def test_gemm_tc_split_tf32_epilogues_and_row_independence(L):
+    import torch
+    rng = np.random.default_rng(77)
+    M, K = 900, 384
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    # SwiGLU, fp32 output
+    w = (rng.standard_normal((1920, K)) / 20).astype(np.float32)
+    A2, W3 = split_operands(L, a, w)
+    Cm = torch.zeros((M, 960), device="cuda")
+    g = gemm_args(M, 1920, K, A2, W3, Cm, 960, c_dtype=0, swiglu=1)
+    g.lda, g.ldw = 2 * K, 3 * K
+    keep, plan = tc_plan(L, g, 0)
+    ok(L.shvk_gemm_tc_rows(plan, 777, stream_ptr()))
+    sync()
+    full = a.astype(np.float64) @ w.astype(np.float64).T
+    ref = silu(full[:, 0::2]) * full[:, 1::2]
+    got = Cm.cpu().numpy()
+    assert np.abs(got[:777] - ref[:777]).max() < 2e-6 * max(1.0, np.abs(ref).max())
+    assert (got[777:] == 0).all()
+    # one row alone equals the row inside the batch, bitwise
+    one = torch.zeros((1, 960), device="cuda")
+    one_a = A2[515:516].contiguous()
+    g1 = gemm_args(1, 1920, K, one_a, W3, one, 960, c_dtype=0, swiglu=1)
+    g1.lda, g1.ldw = 2 * K, 3 * K
+    k1, p1 = tc_plan(L, g1, 0)
+    ok(L.shvk_gemm_tc(p1, stream_ptr()))
+    sync()
+    assert torch.equal(Cm[515], one[0])
+    # residual in place / sqrt(2) with K = 960 (the FFN down projection)
+    K2 = 960
+    a2 = rng.standard_normal((M, K2)).astype(np.float32)
+    w2 = (rng.standard_normal((384, K2)) / 30).astype(np.float32)
+    A22, W32 = split_operands(L, a2, w2)
+    r = rng.standard_normal((M, 384)).astype(np.float32)
+    H = dev(r)
+    g = gemm_args(M, 384, K2, A22, W32, H, 384, R=H, ldr=384, r_div=float(np.float32(np.sqrt(2.0))))
+    g.lda, g.ldw = 2 * K2, 3 * K2
+    keep2, plan2 = tc_plan(L, g, 0)
+    ok(L.shvk_gemm_tc(plan2, stream_ptr()))
+    sync()
+    ref = r.astype(np.float64) + (a2.astype(np.float64) @ w2.astype(np.float64).T) / float(np.float32(np.sqrt(2.0)))
+    assert np.abs(H.cpu().numpy() - ref).max() < 2e-6 * max(1.0, np.abs(ref).max())
+    assert tc_status(L) == 0
+
+
 # ---------------------------------------------------------------------------------------------- row kernels
 def test_assemble_norm_and_rmsnorm(L, weight_files):
     import torch
@@ -541,6 +634,27 @@ def test_readout_row_kernels_match_oracle(L, weight_files):
     ok(L.shvk_readout_tail(Y1.data_ptr(), H1.data_ptr() + 320 * 384 * 4, 321 * 384, C.byref(rw), None, one.data_ptr(), 1, stream_ptr()))
     sync()
     assert torch.equal(one[0], logits[20])
+    # the clips-per-CTA variants (16 for large batches, 4, 1): the same clips give the same bits in each
+    Bbig = 2400
+    hb = rng.standard_normal((Bbig, 384)).astype(np.float32)
+    yb = (rng.standard_normal((Bbig, 384)) * 0.5).astype(np.float32)
+    Hb, Yb = dev(hb), dev(yb)
+    outs = {}
+    for n in (Bbig, 640, 37):
+        lg, q = torch.zeros(n, device="cuda"), torch.zeros((n, 576), device="cuda")
+        ok(L.shvk_readout_qc(Hb.data_ptr(), 384, d_nw.data_ptr(), d_wqc.data_ptr(), q.data_ptr(), n, stream_ptr()))
+        ok(L.shvk_readout_tail(Yb.data_ptr(), Hb.data_ptr(), 384, C.byref(rw), None, lg.data_ptr(), n, stream_ptr()))
+        sync()
+        outs[n] = (lg.cpu().numpy(), q.cpu().numpy())
+    for n in (640, 37):
+        np.testing.assert_array_equal(outs[n][0].view(np.uint32), outs[Bbig][0][:n].view(np.uint32))
+        np.testing.assert_array_equal(outs[n][1].view(np.uint32), outs[Bbig][1][:n].view(np.uint32))
+    x1 = hb.astype(np.float64) + yb.astype(np.float64) @ f64(f"{a}.W_O.weight").T
+    xf = O.rms_norm(x1, f64("sisa.ffn_norm.weight"))
+    x2 = x1 + (silu(xf @ f64("sisa.ffn.w_gate.weight").T) * (xf @ f64("sisa.ffn.w_up.weight").T)) @ f64("sisa.ffn.w_down.weight").T
+    z = O.rms_norm(x2, f64("final_norm.weight"))
+    ref = silu(z @ f64("head.0.weight").T + f64("head.0.bias")) @ f64("head.2.weight").reshape(128) + f64("head.2.bias")[0]
+    assert np.abs(outs[Bbig][0] - ref).max() < 2e-5
 
 
 def test_store_tokens(L):
