@@ -76,7 +76,9 @@ def algorithmic_work(name: str, storage_bytes: int):
     s = storage_bytes
     h = NTOK * D * 4
     xn, on, hid = NTOK * D * s, NTOK * 768 * s, NTOK * 960 * s
-    p_out, s_out = NTOK * 2316 * 4, NTOK * 1068 * 4
+    p_out = NTOK * 2316 * 4
+    # SISA projection row: fp32 in the exact tier; 16-bit modes: K | V | B as fp16 + theta | alpha | forget (pitch 112) as fp32
+    s_out = NTOK * 1068 * 4 if s == 4 else NTOK * (960 * 2 + 112 * 4)
     table = {
         "assemble_norm": (20 * 6144 * 4 + h + xn, 0),
         "rmsnorm": (h + xn, 0),
@@ -100,7 +102,9 @@ def boundary_model_bytes(name: str, storage_bytes: int):
     model's rows are what `roofline.achieved` is quoted on, the bytes that really cross are `interface_*` beside it."""
     s = storage_bytes
     p_out = NTOK * 2316 * 4
-    rows = {"gdn_inproj": NTOK * D * s + p_out, "gdn_scan": p_out + NTOK * 768 * s}
+    s_row = NTOK * 1068 * 4                   # the model's fp32 SISA projection row
+    rows = {"gdn_inproj": NTOK * D * s + p_out, "gdn_scan": p_out + NTOK * 768 * s,
+            "gemm.sisa_in": NTOK * D * s + s_row, "sisa_attn": s_row}
     return rows.get(name, algorithmic_work(name, storage_bytes)[0])
 
 
@@ -688,7 +692,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                  "interface_frac": k["gbs"] / pk["hbm_gbs"] if k["gbs"] else None,
                  "removed_boundary": ("fp32 projection row P [321 x 2316] between in-projection and scan: the model counts it "
                                       "written and read once, this build stores 16-bit operand tiles (1,564,416 B per clip) instead")
-                 if model_bytes != nbytes else None,
+                 if model_bytes != nbytes and top.startswith("gdn_") else None,
                  "traffic": B * NCU_TRAFFIC_PER_CLIP[top] if has_traffic else None,
                  "traffic_source": "ncu capture at B = 512 (profiles/), scaled by clips" if has_traffic else None})
     alg_bytes_clip = 45853824 if mode == "fp32" else 37471872

@@ -53,17 +53,23 @@ typedef struct shvk_gemm_args {
 /* IEEE fp32 FMA chain on CUDA cores, k in order (exact tier and the fp32-only last-row projections). A, W fp32. */
 int shvk_gemm_f32(const shvk_gemm_args* g, void* stream);
 /* tcgen05 tensor-core GEMM, A and W in ab_dtype (bf16 or fp16), fp32 accumulation in tensor memory, operands
- * staged by TMA.  Needs K % 64 == 0, 16-byte aligned operands and pitches.
+ * staged by TMA.  Needs K % 64 == 0, 16-byte aligned operands and pitches.  shvk_gemm_tc_plan encodes the two TMA
+ * tensor maps and the tile shape for exactly these operands into a host-side plan that launches reuse.  Plain fp32
+ * output with ldc - N < 8: the padding columns N .. ldc-1 may be written with zeros (whole 32-byte sectors per row).
  * Exact tier (ab_dtype = SHVK_F32; replaces the SIMT class of engine/cuda/gemm.cuh:66-188 for the all-row GEMMs): fp32
  * operands split into two TF32 pieces each by shvk_split_tf32, A = [lo | hi] (lda >= 2K), W = [hi | lo | hi]
  * (ldw >= 3K), K % 32 == 0; one accumulator sums lo*hi, hi*lo, hi*hi over k in that fixed order (K never split, rows
- * independent), what is dropped is below 2^-21 of each product.  SwiGLU then writes fp32 (c_dtype SHVK_F32).  shvk_gemm_tc_plan encodes the two TMA
- * tensor maps and the tile shape for exactly these operands into a host-side plan that launches reuse.  Plain fp32
- * output with ldc - N < 8: the padding columns N .. ldc-1 may be written with zeros (whole 32-byte sectors per row). */
+ * independent), what is dropped is below 2^-21 of each product.  SwiGLU then writes fp32 (c_dtype SHVK_F32). */
 int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* host_plan /* >= 512 bytes, host, 64-byte aligned */);
 /* x = hi + lo, hi = x rounded to TF32, lo = x - hi rounded to TF32; rows of K fp32 (K % 4 == 0, 16-byte aligned).
  * layout 0: out row = [lo | hi] (A operand of the exact tier), layout 1: out row = [hi | lo | hi] (W operand). */
 int shvk_split_tf32(const float* in, long long ld_in, int K, long long rows, float* out, long long ld_out, int layout, void* stream);
+/* Plain epilogue with a 16-bit part: output columns [0, split_col) are rounded to fp16 (saturating) into C16 (pitch
+ * ldc16 halves), columns [split_col, N) go to g->C as fp32 (+ bias[n]) at column n - split_col.  split_col % 32 == 0,
+ * 16-bit operands only, no residual / SwiGLU.  The SISA all-row projection of the 16-bit modes uses it with
+ * split_col = 960: K | V | B leave in 16 bits, theta | alpha | forget in fp32 (the reference keeps the whole row in fp32,
+ * engine/cuda/engine.cu:446-450). */
+int shvk_gemm_tc_plan_split16(const shvk_gemm_args* g, int ab_dtype, int split_col, void* C16, long long ldc16, void* host_plan);
 int shvk_gemm_tc(const void* host_plan, void* stream);
 /* Same plan, first `rows` <= M rows only (a smaller batch in buffers sized for the planned M). */
 int shvk_gemm_tc_rows(const void* host_plan, int rows, void* stream);
@@ -136,6 +142,10 @@ int shvk_gdn_chunked(const void* q, const void* k, const void* v, const float* g
  * S: [B*321][1072] fp32; QC: [B][576] fp32; Y: [B][384] fp32.
  * Replaces launch_sisa_attn (engine/cuda/seq.cu:217-306,372-374). */
 int shvk_sisa_attn(const float* S, const float* QC, const float* lambda_raw, float* Y, int B, void* stream);
+/* The same over the split row format of the 16-bit modes: S16 [B*321][960] fp16 = K | V | B, SG [B*321][112] fp32 =
+ * theta 96 | alpha 6 | forget 6 | pad (2,368 instead of 4,288 bytes per token; written by a shvk_gemm_tc_plan_split16
+ * launch with split_col 960).  Arithmetic as above on the widened values. */
+int shvk_sisa_attn_h16(const void* S16, const float* SG, const float* QC, const float* lambda_raw, float* Y, int B, void* stream);
 
 /* Readout row (token 320) of the SISA block, fp32 in every mode, part 1: xl = rmsnorm(h_last) * norm_w, then
  * QC = xl * W_qc^T.  h_last: row 320 of clip c at h_last + c * ldh (elements); wqc_t: [384][576] = [W_Q | W_C]

@@ -136,6 +136,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_rmsnorm": (i32, [vp, C.c_longlong, vp, vp, i32, C.c_longlong, i32, vp]),
         "shvk_gemm_f32": (i32, [C.POINTER(GemmArgs), vp]),
         "shvk_gemm_tc_plan": (i32, [C.POINTER(GemmArgs), i32, vp]),
+        "shvk_gemm_tc_plan_split16": (i32, [C.POINTER(GemmArgs), i32, i32, vp, C.c_longlong, vp]),
         "shvk_gemm_tc": (i32, [vp, vp]),
         "shvk_gemm_tc_rows": (i32, [vp, i32, vp]),
         "shvk_gemm_tc_status": (i32, [C.POINTER(i32)]),
@@ -154,6 +155,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_gdn_chunked_workspace_bytes": (sz, [i32, i32, i32]),
         "shvk_gdn_chunked": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, vp, sz, vp]),
         "shvk_sisa_attn": (i32, [vp, vp, vp, vp, i32, vp]),
+        "shvk_sisa_attn_h16": (i32, [vp, vp, vp, vp, vp, i32, vp]),
         "shvk_readout_qc": (i32, [vp, C.c_longlong, vp, vp, vp, i32, vp]),
         "shvk_readout_tail": (i32, [vp, vp, C.c_longlong, C.POINTER(ReadoutWeights), vp, vp, i32, vp]),
         "shvk_store_tokens": (i32, [vp, vp, vp, i32, vp]),

@@ -240,6 +240,8 @@ private:
     float *h_ = nullptr, *P_ = nullptr;
     void *xn_ = nullptr, *on_ = nullptr, *hid_ = nullptr;
     float* a2_ = nullptr;
+    static constexpr int SB_COLS = 960, SG_LD = 112;    // SISA rows of the 16-bit modes: [K | V | B] fp16, [theta | alpha | forget | pad] fp32
+    float *s16_ = nullptr, *sg_ = nullptr;
     float *qc_ = nullptr, *y_ = nullptr, *x2_ = nullptr;
     Site in_[2], oproj_[2], up_[2], down_[2], sisa_in_;
     alignas(64) unsigned char inproj_plan_[2][512];   // 16-bit modes: fused in-projection (TMA maps for xn, W', PT = P_)
@@ -478,10 +480,23 @@ private:
         }
         make_site(sisa_in_, SN, D, xn_, s_w_all_, P_, SLD, SHVK_F32);
         sisa_in_.args.bias = s_b_all_;
-        for (Site* st : {&oproj_[0], &oproj_[1], &up_[0], &up_[1], &down_[0], &down_[1], &sisa_in_}) {
+        for (Site* st : {&oproj_[0], &oproj_[1], &up_[0], &up_[1], &down_[0], &down_[1]}) {
             launch_ok(shvk_gemm_tc_plan(&st->args, dt_, st->plan), "tensor-core GEMM plan");
             st->planned = true;
         }
+        if (prec_ == Precision::FP32) {
+            launch_ok(shvk_gemm_tc_plan(&sisa_in_.args, dt_, sisa_in_.plan), "tensor-core GEMM plan");
+        } else {
+            // 16-bit modes: K | V | B of the SISA projection leave as fp16 rows (S16), theta | alpha | forget as fp32 rows
+            // (SG); both live where the mixers' operand tiles were
+            s16_ = P_;
+            sg_ = P_ + (size_t(cfg_.max_windows) * NTOK * SB_COLS / 2 + 3) / 4 * 4;     // halves -> floats, 16-byte aligned
+            if ((sg_ - P_) + size_t(cfg_.max_windows) * NTOK * SG_LD > size_t(cfg_.max_windows) * NTOK * GLD)
+                throw std::runtime_error("projection buffer too small for the SISA rows");
+            sisa_in_.args.C = sg_; sisa_in_.args.ldc = SG_LD;
+            launch_ok(shvk_gemm_tc_plan_split16(&sisa_in_.args, dt_, SB_COLS, s16_, SB_COLS, sisa_in_.plan), "tensor-core GEMM plan");
+        }
+        sisa_in_.planned = true;
         if (prec_ == Precision::FP32) {
             for (Site* st : {&in_[0], &in_[1]}) {
                 launch_ok(shvk_gemm_tc_plan(&st->args, dt_, st->plan), "tensor-core GEMM plan");
@@ -641,7 +656,8 @@ private:
         const long long ld_last = (long long)NTOK * D;
         launch_ok(shvk_readout_qc(h_last, ld_last, s_attn_norm_, s_wqc_t_, qc_, B, s), "readout q / c");
         mark("readout.qc", s);
-        launch_ok(shvk_sisa_attn(S, qc_, s_lambda_, y_, B, s), "sisa attention");
+        if (prec_ == Precision::FP32) launch_ok(shvk_sisa_attn(S, qc_, s_lambda_, y_, B, s), "sisa attention");
+        else launch_ok(shvk_sisa_attn_h16(s16_, sg_, qc_, s_lambda_, y_, B, s), "sisa attention");
         mark("sisa_attn", s);
         dump("sisa.y", y_, size_t(D), SHVK_F32, s);
         const shvk_readout_weights rw{s_wo_t_, s_ffn_norm_, s_up_t_, s_down_t_, fn_w_, h_w0t_, h_b0_, h_w2_, h_b2_};

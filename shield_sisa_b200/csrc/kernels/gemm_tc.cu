@@ -57,7 +57,7 @@ template <int STAGES_, int EPI_WARPS_, int NBUF_> struct Shape {
 };
 constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of ~64 ns each before a wait gives up (about a quarter second)
 
-enum : int { EPI_PLAIN = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+enum : int { EPI_PLAIN = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_SPLIT16 = 3 };
 
 __device__ int g_tc_status = 0;   // 0 ok; else 1 + role of the wait that gave up
 
@@ -69,6 +69,7 @@ struct TcParams {
     int tile_k;     // operand elements per 128-byte stage row: 64 (16-bit) or 32 (fp32 read as TF32)
     int tf32;       // 1: kind::tf32 MMAs on split fp32 operands
     int a_wrap;     // exact tier: A has a_wrap columns ([lo | hi]); k beyond them takes the second half again.  0: none
+    int split_n;    // EPI_SPLIT16: columns below go to the fp16 output, the rest (fp32, + bias) to C at column n - split_n
     int m_major;    // tile order: 1 = a CTA finishes all column tiles of a row block before its next row block
     uint32_t spin_limit;   // polls before a wait gives up (SPIN_LIMIT; the starved test launch passes a small number)
     int starve;     // test launch only: the producer withholds the first operand stage of its first tile
@@ -90,18 +91,34 @@ using namespace tc;
 struct TcMaps {
     CUtensorMap a, w;             // operands, 128-byte swizzle
     CUtensorMap c_full, c_half;   // output: boxes of 32 rows x (32 | 16) accumulator columns
-    CUtensorMap r_full, r_half;   // residual input (fp32), same boxes; only read by EPI_RESID
+    CUtensorMap r_full, r_half;   // EPI_RESID: residual input (fp32), same boxes; EPI_SPLIT16: the fp16 output, dense boxes
 };
 
 // Writes one epilogue block into its shared-memory tile.  Lane = accumulator row, r = its 32 (or 16) fp32 columns.
 //   fp32 tiles, 32 columns: 128-byte rows, 16-byte chunk j of row l at chunk j ^ (l & 7) (the TMA 128-byte swizzle,
 //                           which also makes these stores bank-conflict free); 16 columns: dense 64-byte rows
 //   EPI_RESID: the tile already holds R (TMA load); v = R + acc / r_div overwrites it in place
+//   EPI_SPLIT16: blocks left of split_n are rounded to fp16 (saturating) into dense 64-byte (32-byte) rows; the others
+//               are plain fp32 blocks (+ bias)
 //   EPI_SWIGLU: adjacent accumulator columns are (gate, up): silu(gate) * up in storage type T, dense rows (16-bit T:
 //               hardware exp; T = float, the exact tier: expf and a true division, 64-byte rows)
 template <typename T, int EPI>
 __device__ __forceinline__ void stage_block(const TcParams& p, uint32_t tile, int lane, bool full, int n, const uint32_t* r) {
-    if constexpr (EPI == EPI_SWIGLU && sizeof(T) == 4) {
+    if (EPI == EPI_SPLIT16 && n < p.split_n) {
+        const uint32_t row = tile + uint32_t(lane) * (full ? 64u : 32u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (j < 2 || full) {
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(o[e]) : "f"(__uint_as_float(r[8 * j + 2 * e + 1])),
+                        "f"(__uint_as_float(r[8 * j + 2 * e])));
+                }
+                sts128u(row + 16u * j, o[0], o[1], o[2], o[3]);
+            }
+        }
+    } else if constexpr (EPI == EPI_SWIGLU && sizeof(T) == 4) {
         const uint32_t row = tile + uint32_t(lane) * (full ? 64u : 32u);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -352,9 +369,11 @@ gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
-                    const int x = EPI == EPI_SWIGLU ? (n >> 1) : n;
-                    if (hint) tma_store_2d_hint(full ? &maps.c_full : &maps.c_half, x, m0, tiles[b], pol_c);
-                    else tma_store_2d(full ? &maps.c_full : &maps.c_half, x, m0, tiles[b]);
+                    const bool low = EPI == EPI_SPLIT16 && n < p.split_n;         // this block goes to the fp16 output
+                    const int x = EPI == EPI_SWIGLU ? (n >> 1) : (EPI == EPI_SPLIT16 && !low ? n - p.split_n : n);
+                    const CUtensorMap* cm = low ? (full ? &maps.r_full : &maps.r_half) : (full ? &maps.c_full : &maps.c_half);
+                    if (hint) tma_store_2d_hint(cm, x, m0, tiles[b], pol_c);
+                    else tma_store_2d(cm, x, m0, tiles[b]);
                     bulk_commit();
                 }
                 ++nb;
@@ -437,6 +456,7 @@ struct HostPlan {
     TcParams p;
     void* C; long long ldc; int c_dtype;
     const float* R; long long ldr;
+    void* C16; long long ldc16;     // EPI_SPLIT16: the fp16 output
     int epi, ab_dtype, valid;
 };
 static_assert(sizeof(HostPlan) <= 512, "plan must fit the caller's 512-byte buffer");
@@ -485,7 +505,22 @@ using ShapeDefault = Shape<3, 8, 2>;
 }  // namespace
 }  // namespace sb
 
+static int plan_impl(const shvk_gemm_args* g, int ab_dtype, void* host_plan, int split_col, void* C16, long long ldc16);
+
 extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* host_plan) {
+    return plan_impl(g, ab_dtype, host_plan, 0, nullptr, 0);
+}
+
+extern "C" int shvk_gemm_tc_plan_split16(const shvk_gemm_args* g, int ab_dtype, int split_col, void* C16, long long ldc16,
+                                         void* host_plan) {
+    // columns [0, split_col) leave as fp16 rows of C16, the rest as fp32 (+ bias) at column n - split_col of C
+    if (!g || !C16 || split_col <= 0 || split_col >= g->N || (split_col & 31) || (ldc16 & 7) || ldc16 < split_col ||
+        (reinterpret_cast<uintptr_t>(C16) & 15) || g->swiglu || g->R || g->c_dtype != sb::DT_F32 || ab_dtype == sb::DT_F32)
+        return int(cudaErrorInvalidValue);
+    return plan_impl(g, ab_dtype, host_plan, split_col, C16, ldc16);
+}
+
+static int plan_impl(const shvk_gemm_args* g, int ab_dtype, void* host_plan, int split_col, void* C16, long long ldc16) {
     using namespace sb;
     if (!g || !host_plan || (reinterpret_cast<uintptr_t>(host_plan) & 63)) return int(cudaErrorInvalidValue);
     if (ab_dtype != DT_BF16 && ab_dtype != DT_F16 && ab_dtype != DT_F32) return int(cudaErrorInvalidValue);
@@ -504,7 +539,7 @@ extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* ho
         epi = EPI_SWIGLU;
     } else {
         if (g->c_dtype != DT_F32 || (g->ldc & 3) || (g->R && g->bias)) return int(cudaErrorInvalidValue);
-        epi = g->R ? EPI_RESID : EPI_PLAIN;
+        epi = g->R ? EPI_RESID : (split_col ? EPI_SPLIT16 : EPI_PLAIN);
     }
     HostPlan* hp = static_cast<HostPlan*>(host_plan);
     memset(hp, 0, sizeof(HostPlan));
@@ -532,6 +567,9 @@ extern "C" int shvk_gemm_tc_plan(const shvk_gemm_args* g, int ab_dtype, void* ho
     p.starve = 0;
     hp->C = g->C; hp->ldc = g->ldc; hp->c_dtype = g->c_dtype;
     hp->R = g->R; hp->ldr = g->ldr;
+    hp->C16 = C16; hp->ldc16 = ldc16;
+    p.split_n = split_col;
+    if (split_col && (bn & 31)) return int(cudaErrorInvalidValue);      // a 32-column block must not straddle the split
     hp->epi = epi;
     hp->ab_dtype = ab_dtype;
     hp->valid = 0x5b200;
@@ -565,18 +603,24 @@ int launch_rows(const void* host_plan, int rows, void* stream, int starve, uint3
         // up to seven padding columns right of N are written too where the last column tile covers them (zeros: the
         // weight rows there read as zero fill); a row that ended inside a 32-byte sector would cost a DRAM
         // read-modify-write per row
-        const bool pad = hp->epi == EPI_PLAIN && hp->ldc - p.N < 8 && hp->ldc <= (long long)p.n_tiles * p.BN && !(probe_bits(p) & 64);
-        const long long c_cols = pad ? hp->ldc : p.N;
+        const int n_c = p.N - (hp->epi == EPI_SPLIT16 ? p.split_n : 0);        // columns that go to C
+        const bool pad = (hp->epi == EPI_PLAIN || hp->epi == EPI_SPLIT16) && hp->ldc - n_c < 8 &&
+                         hp->ldc - n_c <= (long long)p.n_tiles * p.BN - p.N && !(probe_bits(p) & 64);
+        const long long c_cols = pad ? hp->ldc : n_c;
         ok = make_map(&maps.c_full, hp->C, 4, rows, c_cols, hp->ldc, 32, 32, true) &&
              make_map(&maps.c_half, hp->C, 4, rows, c_cols, hp->ldc, 32, 16, false);
         if (hp->epi == EPI_RESID)
             ok = ok && make_map(&maps.r_full, hp->R, 4, rows, p.N, hp->ldr, 32, 32, true) &&
                  make_map(&maps.r_half, hp->R, 4, rows, p.N, hp->ldr, 32, 16, false);
+        else if (hp->epi == EPI_SPLIT16)
+            ok = ok && make_map(&maps.r_full, hp->C16, 2, rows, p.split_n, hp->ldc16, 32, 32, false) &&
+                 make_map(&maps.r_half, hp->C16, 2, rows, p.split_n, hp->ldc16, 32, 16, false);
         else { maps.r_full = maps.c_full; maps.r_half = maps.c_half; }
     }
     if (!ok) return int(cudaErrorNotSupported);
     cudaStream_t s = cudaStream_t(stream);
     if (hp->epi == EPI_PLAIN) return launch_tc<float, EPI_PLAIN, ShapeDefault>(maps, p, s);
+    if (hp->epi == EPI_SPLIT16) return launch_tc<float, EPI_SPLIT16, ShapeDefault>(maps, p, s);
     if (hp->epi == EPI_RESID) return launch_tc<float, EPI_RESID, ShapeDefault>(maps, p, s);
     if (hp->c_dtype == DT_F32) return launch_tc<float, EPI_SWIGLU, ShapeDefault>(maps, p, s);
     if (hp->c_dtype == DT_BF16) return launch_tc<__nv_bfloat16, EPI_SWIGLU, ShapeDefault>(maps, p, s);

@@ -9,22 +9,56 @@
 //   3  rotate C (row 320) by phi[320]; per token rotate B by phi[t], score = q.k/8 + softplus(lambda) *
 //      exp(g_last - g_t) * (c_rot . b_rot) + (f_last - f_t); thread per token, rows read as float4
 //   4  softmax over the 321 scores, y = sum_t p_t v_t with 4 token groups x 64 columns
+//
+// Two row formats.  fp32 (exact tier): one row [K | V | B | theta | alpha | forget] of 1,072 floats per token.  16-bit
+// modes: K, V, B travel as fp16 in a row of 960 halves (S16) and theta, alpha, forget as fp32 in a row of 112 floats
+// (SG), 2,368 instead of 4,288 bytes per token; the arithmetic is the same fp32 arithmetic on the widened values.
 #include "device_utils.cuh"
+
+#include <cuda_fp16.h>
 #include "shv_seq_kernels.h"
 
 namespace sb {
 namespace {
 
 constexpr int NT = 256, NCOL = 18, PER_LANE = 11;   // 32 * 11 = 352 >= 321
+constexpr int kS16LD = 960, kSGLD = 112;             // row pitches of the split format; SG = [theta 96 | alpha 6 | forget 6 | pad 4]
+
+// Eight consecutive K or B values of a token row, widened to fp32.
+template <bool H16> struct Row8;
+template <> struct Row8<false> {
+    static __device__ __forceinline__ void load(const void* base, int i, float (&v)[8]) {
+        const float4* p = static_cast<const float4*>(base) + 2 * i;
+        const float4 a = p[0], b = p[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+template <> struct Row8<true> {
+    static __device__ __forceinline__ void load(const void* base, int i, float (&v)[8]) {
+        const uint4 u = static_cast<const uint4*>(base)[i];
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(h[e]);
+            v[2 * e] = f.x; v[2 * e + 1] = f.y;
+        }
+    }
+};
 
 // Four CTAs per SM (64 registers, a 52-byte spill): the phases of one CTA alternate between loads and scans, and more
 // resident CTAs keep HBM busy through the scans: 1.75 ms at three CTAs, 1.48 ms at four, 1.63 ms at five (B = 4096).
+template <bool H16>
 __global__ void __launch_bounds__(NT, 4)
-sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, const float* __restrict__ lambda_raw,
-                 float* __restrict__ Y) {
+sisa_attn_kernel(const void* __restrict__ Skvb, const float* __restrict__ Sgate, const float* __restrict__ QC,
+                 const float* __restrict__ lambda_raw, float* __restrict__ Y) {
+    using KV = typename std::conditional<H16, __half, float>::type;
+    constexpr int LDK = H16 ? kS16LD : kSLD;                 // pitch of the K | V | B row (elements of KV)
+    constexpr int LDG = H16 ? kSGLD : kSLD;                  // pitch of the theta | alpha | forget row (floats)
+    constexpr int G0 = H16 ? 0 : kSTheta;                    // column of theta in that row
     const int clip = blockIdx.x / kHeads, head = blockIdx.x % kHeads;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float* S0 = S + (long long)clip * kTok * kSLD;
+    const KV* S0 = static_cast<const KV*>(Skvb) + (long long)clip * kTok * LDK;
+    const float* SG0 = Sgate + (long long)clip * kTok * LDG;
     __shared__ float term[NCOL][kTok + 3];     // column-major: a scan walks one row of this array
     __shared__ float score[kTok];
     __shared__ __align__(16) float sq[kDK];
@@ -34,10 +68,10 @@ sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, cons
 
     // per-token terms: theta[16] of this head is one 64-byte run, alpha and forget are single floats
     for (int tk = tid; tk < kTok; tk += NT) {
-        const float* row = S0 + (long long)tk * kSLD;
-        const float4* th = reinterpret_cast<const float4*>(row + kSTheta + head * kPairs);
+        const float* row = SG0 + (long long)tk * LDG + G0;
+        const float4* th = reinterpret_cast<const float4*>(row + head * kPairs);
         const float4 t0 = th[0], t1 = th[1], t2 = th[2], t3 = th[3];
-        const float al = row[kSAlpha + head], fg = row[kSForget + head];
+        const float al = row[kSAlpha - kSTheta + head], fg = row[kSForget - kSTheta + head];
         term[0][tk] = -softplus_f(al);
         term[1][tk] = logsigmoid_f(fg);
         term[2][tk] = t0.x; term[3][tk] = t0.y; term[4][tk] = t0.z; term[5][tk] = t0.w;
@@ -88,28 +122,29 @@ sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, cons
     const float g_last = term[0][kTok - 1], f_last = term[1][kTok - 1];
     float lmax = -INFINITY;
     for (int t = tid; t < kTok; t += NT) {
-        const float4* kr = reinterpret_cast<const float4*>(S0 + (long long)t * kSLD + kSK + head * kDK);
+        const KV* kr = S0 + (long long)t * LDK + kSK + head * kDK;
         float content = 0.0f;
 #pragma unroll
-        for (int j = 0; j < kDK / 4; ++j) {
-            const float4 kk = kr[j];
-            const float4 qq = *reinterpret_cast<const float4*>(&sq[j * 4]);
-            content = fmaf(qq.x, kk.x, content); content = fmaf(qq.y, kk.y, content);
-            content = fmaf(qq.z, kk.z, content); content = fmaf(qq.w, kk.w, content);
+        for (int j = 0; j < kDK / 8; ++j) {
+            float kk[8];
+            Row8<H16>::load(kr, j, kk);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) content = fmaf(sq[8 * j + e], kk[e], content);
         }
         content *= 0.125f;
-        const float4* br = reinterpret_cast<const float4*>(S0 + (long long)t * kSLD + kSB + head * kState);
+        const KV* br = S0 + (long long)t * LDK + kSB + head * kState;
         float ssm = 0.0f;
 #pragma unroll
-        for (int j = 0; j < kState / 4; ++j) {
-            const float4 bb = br[j];
-            float s0, c0, s1, c1;
-            sincosf(term[2 + 2 * j][t], &s0, &c0);
-            sincosf(term[3 + 2 * j][t], &s1, &c1);
-            ssm = fmaf(sc[4 * j], bb.x * c0 - bb.y * s0, ssm);
-            ssm = fmaf(sc[4 * j + 1], bb.x * s0 + bb.y * c0, ssm);
-            ssm = fmaf(sc[4 * j + 2], bb.z * c1 - bb.w * s1, ssm);
-            ssm = fmaf(sc[4 * j + 3], bb.z * s1 + bb.w * c1, ssm);
+        for (int j = 0; j < kState / 8; ++j) {
+            float bb[8];
+            Row8<H16>::load(br, j, bb);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {                 // pair 4 j + e: (bb[2e], bb[2e+1]) rotated by phi of that pair
+                float sn, cs;
+                sincosf(term[2 + 4 * j + e][t], &sn, &cs);
+                ssm = fmaf(sc[8 * j + 2 * e], bb[2 * e] * cs - bb[2 * e + 1] * sn, ssm);
+                ssm = fmaf(sc[8 * j + 2 * e + 1], bb[2 * e] * sn + bb[2 * e + 1] * cs, ssm);
+            }
         }
         float s = content + (lam * expf(g_last - term[0][t])) * ssm;
         s = s + (f_last - term[1][t]);
@@ -139,7 +174,7 @@ sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, cons
     const int j = tid & (kDK - 1), grp = tid >> 6;
     float y = 0.0f;
 #pragma unroll 8
-    for (int t = grp; t < kTok; t += 4) y = fmaf(score[t] * inv, S0[(long long)t * kSLD + kSV + head * kDK + j], y);
+    for (int t = grp; t < kTok; t += 4) y = fmaf(score[t] * inv, float(S0[(long long)t * LDK + kSV + head * kDK + j]), y);
     ypart[grp][j] = y;
     __syncthreads();
     if (tid < kDK) Y[(long long)clip * kD + head * kDK + tid] = (ypart[0][tid] + ypart[1][tid]) + (ypart[2][tid] + ypart[3][tid]);
@@ -150,6 +185,14 @@ sisa_attn_kernel(const float* __restrict__ S, const float* __restrict__ QC, cons
 
 extern "C" int shvk_sisa_attn(const float* S, const float* QC, const float* lambda_raw, float* Y, int B, void* stream) {
     if (B <= 0) return 0;
-    sb::sisa_attn_kernel<<<unsigned(B) * sb::kHeads, sb::NT, 0, cudaStream_t(stream)>>>(S, QC, lambda_raw, Y);
+    sb::sisa_attn_kernel<false><<<unsigned(B) * sb::kHeads, sb::NT, 0, cudaStream_t(stream)>>>(S, S, QC, lambda_raw, Y);
+    return int(cudaGetLastError());
+}
+
+extern "C" int shvk_sisa_attn_h16(const void* S16, const float* SG, const float* QC, const float* lambda_raw, float* Y, int B,
+                                  void* stream) {
+    if (B <= 0) return 0;
+    if (!S16 || !SG || ((reinterpret_cast<uintptr_t>(S16) | reinterpret_cast<uintptr_t>(SG)) & 15)) return int(cudaErrorInvalidValue);
+    sb::sisa_attn_kernel<true><<<unsigned(B) * sb::kHeads, sb::NT, 0, cudaStream_t(stream)>>>(S16, SG, QC, lambda_raw, Y);
     return int(cudaGetLastError());
 }

@@ -582,6 +582,56 @@ def test_sisa_attention_matches_oracle(L, weight_files):
     ok(L.shvk_sisa_attn(d_s.data_ptr(), d_qc.data_ptr(), d_lam.data_ptr(), Y.data_ptr(), B, stream_ptr()))
     sync()
     assert np.abs(Y.cpu().numpy() - tr["sisa.attn_y_last"]).max() < 5e-5
+    # the split row format of the 16-bit modes: K | V | B as fp16, theta | alpha | forget as fp32.  Exact for inputs
+    # that are fp16 numbers: same result as the fp32 kernel on those inputs, bit for bit
+    s32 = S.reshape(B * 321, 1072).astype(np.float32)
+    kvb16 = s32[:, :960].astype(np.float16)
+    s_rounded = s32.copy()
+    s_rounded[:, :960] = kvb16.astype(np.float32)
+    sg = np.zeros((B * 321, 112), np.float32)
+    sg[:, :108] = s32[:, 960:1068]
+    Y32, Y16 = torch.zeros((B, 384), device="cuda"), torch.zeros((B, 384), device="cuda")
+    d_r, d_16, d_sg = dev(s_rounded), dev(kvb16), dev(sg)
+    ok(L.shvk_sisa_attn(d_r.data_ptr(), d_qc.data_ptr(), d_lam.data_ptr(), Y32.data_ptr(), B, stream_ptr()))
+    ok(L.shvk_sisa_attn_h16(d_16.data_ptr(), d_sg.data_ptr(), d_qc.data_ptr(), d_lam.data_ptr(), Y16.data_ptr(), B, stream_ptr()))
+    sync()
+    assert torch.equal(Y32, Y16)
+    assert rel_err(Y16.cpu().numpy(), tr["sisa.attn_y_last"]) < 2e-3           # fp16 rounding of K, V, B only
+
+
+def test_gemm_tc_split16_epilogue(L):
+    """SISA projection shape: columns below 960 leave as fp16 rows, the rest as fp32 (+ bias) rows of pitch 112."""
+    import torch
+    rng = np.random.default_rng(5)
+    M, N, K = 700, 1068, 384
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    bias = np.zeros(N, np.float32)
+    bias[1056:] = rng.standard_normal(12).astype(np.float32)
+    for code, tdt in ((1, torch.bfloat16), (2, torch.float16)):
+        A, Wt, Bt = dev(a, tdt), dev(w, tdt), dev(bias)
+        C16 = torch.full((M, 960), 7.0, device="cuda", dtype=torch.float16)
+        Cg = torch.full((M, 112), 7.0, device="cuda")
+        g = gemm_args(M, N, K, A, Wt, Cg, 112, bias=Bt)
+        buf = (C.c_char * 1024)()
+        plan = (C.addressof(buf) + 63) & ~63
+        ok(L.shvk_gemm_tc_plan_split16(g, code, 960, C16.data_ptr(), 960, plan))
+        ok(L.shvk_gemm_tc_rows(plan, 613, stream_ptr()))
+        sync()
+        assert tc_status(L) == 0
+        ref = A.float().cpu().numpy().astype(np.float64) @ Wt.float().cpu().numpy().astype(np.float64).T + bias
+        got16, gotg = C16.float().cpu().numpy(), Cg.cpu().numpy()
+        assert np.abs(got16[:613] - ref[:613, :960]).max() < 4e-3          # fp16 rounding of O(1) values
+        assert np.abs(gotg[:613, :108] - ref[:613, 960:]).max() < 1e-4
+        assert (gotg[:613, 108:] == 0).all() or (gotg[:613, 108:] == 7.0).all()      # padding: zeros (whole sectors) or untouched
+        assert (got16[613:] == 7.0).all() and (gotg[613:] == 7.0).all()
+        # the fp32 part equals the plain epilogue's bits
+        Cp = torch.zeros((M, 1072), device="cuda")
+        k2, p2 = tc_plan(L, gemm_args(M, N, K, A, Wt, Cp, 1072, bias=Bt), code)
+        ok(L.shvk_gemm_tc_rows(p2, 613, stream_ptr()))
+        sync()
+        assert torch.equal(Cp[:613, 960:1068], Cg[:613, :108])
+        assert torch.equal(Cp[:613, :960].to(torch.float16), C16[:613])
 
 
 def test_readout_row_kernels_match_oracle(L, weight_files):
