@@ -86,6 +86,7 @@ def algorithmic_work(name: str, storage_bytes: int):
         "gdn_inproj": (xn + PT_BYTES_PER_CLIP, 2 * NTOK * 2316 * 384),             # 16-bit modes: projection + conv + SiLU + gates
         "gdn_scan": ((p_out if s == 4 else PT_BYTES_PER_CLIP) + on, 0),
         "gemm.o_proj": (on + 2 * h, 2 * NTOK * 384 * 768),
+        "ffn_fused": (xn + 2 * h, 2 * NTOK * 1920 * 384 + 2 * NTOK * 384 * 960),    # 16-bit modes: up + SwiGLU + down + residual
         "gemm.ffn_up": (xn + hid, 2 * NTOK * 1920 * 384),
         "gemm.ffn_down": (hid + 2 * h, 2 * NTOK * 384 * 960),
         "gemm.sisa_in": (xn + s_out, 2 * NTOK * 1068 * 384),
@@ -104,7 +105,8 @@ def boundary_model_bytes(name: str, storage_bytes: int):
     p_out = NTOK * 2316 * 4
     s_row = NTOK * 1068 * 4                   # the model's fp32 SISA projection row
     rows = {"gdn_inproj": NTOK * D * s + p_out, "gdn_scan": p_out + NTOK * 768 * s,
-            "gemm.sisa_in": NTOK * D * s + s_row, "sisa_attn": s_row}
+            "gemm.sisa_in": NTOK * D * s + s_row, "sisa_attn": s_row,
+            "ffn_fused": NTOK * D * s + 2 * NTOK * 960 * s + 2 * NTOK * D * 4}    # up (xn, hid) + down (hid, h read and written)
     return rows.get(name, algorithmic_work(name, storage_bytes)[0])
 
 

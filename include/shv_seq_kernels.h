@@ -81,6 +81,17 @@ int shvk_gemm_tc_status(int* status_out);
  * faults or spins without bound.  Exists so that a test can watch the abort path work. */
 int shvk_gemm_tc_rows_starved(const void* host_plan, int rows, int polls, void* stream);
 
+/* SwiGLU feed-forward block of the 16-bit modes in one launch: h += down(silu(gate(xn)) * up(xn)) with the hidden
+ * layer kept on the SM (shared memory -> tensor core), instead of an up launch writing [rows][960] and a down launch
+ * reading it back.  xn [max_rows][384] and the weights in ab_dtype (bf16 or fp16): w_up [1920][384] with (gate, up) rows
+ * interleaved (engine/cuda/model.cpp:95-102), w_down [384][960]; h [max_rows][384] fp32, updated in place.  Same
+ * arithmetic as the two shvk_gemm_tc launches it replaces (k in order, hidden layer rounded to ab_dtype), rows
+ * independent.  The plan (512 bytes, host, 64-byte aligned) holds the TMA tensor maps for exactly these buffers.
+ * Replaces the two FFN gemm<T> launches of the reference (engine/cuda/engine.cu:434-440). */
+int shvk_ffn_fused_plan(const void* xn, long long max_rows, const void* w_up, const void* w_down, float* h, int ab_dtype,
+                        void* host_plan);
+int shvk_ffn_fused(const void* host_plan, int rows, void* stream);
+
 /* The kernels' status words (tensor-core GEMMs, the scan that reads the fp32 projection, the 16-bit scan) are per
  * device and per process.  These two calls enqueue on `stream`: a copy of the SHVK_STATUS_WORDS words into host_words (pinned host memory, read it after
  * the stream has passed this point), and their reset to zero.  A scheduler fetches the words behind a batch's last

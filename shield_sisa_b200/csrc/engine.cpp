@@ -207,8 +207,9 @@ public:
         starve_kind_ = kind;
         starve_batches_ = batches > 0 ? batches : 0;
     }
-    // 23 kernels; the exact tier splits the A operand of each of its 11 all-row GEMMs in a launch of its own
-    int launches_per_classify() const override { return prec_ == Precision::FP32 ? 34 : 23; }
+    // 16-bit modes: 21 kernels.  Exact tier: 23 (its feed-forward blocks are two GEMMs each) + a launch that splits the
+    // A operand for each of its 11 all-row GEMMs
+    int launches_per_classify() const override { return prec_ == Precision::FP32 ? 34 : 21; }
 
     // One eager classify / encode with an event after every launch; returns (kernel name, milliseconds) per launch.
     std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) override {
@@ -244,6 +245,7 @@ private:
     float *s16_ = nullptr, *sg_ = nullptr;
     float *qc_ = nullptr, *y_ = nullptr, *x2_ = nullptr;
     Site in_[2], oproj_[2], up_[2], down_[2], sisa_in_;
+    alignas(64) unsigned char ffn_plan_[2][512];      // 16-bit modes: fused feed-forward block (TMA maps for xn, W_up, W_down)
     alignas(64) unsigned char inproj_plan_[2][512];   // 16-bit modes: fused in-projection (TMA maps for xn, W', PT = P_)
     int starve_kind_ = 0, starve_batches_ = 0;        // test hook: see inject_wait_timeout
     // frame encoder
@@ -408,7 +410,8 @@ private:
     void allocate() {
         const size_t Bm = size_t(cfg_.max_windows), Mm = Bm * NTOK, Fm = size_t(cfg_.max_frames), ts = dtype_bytes(prec_);
         const size_t o_h = acts_.reserve(Mm * D * 4), o_p = acts_.reserve(Mm * GLD * 4), o_xn = acts_.reserve(Mm * D * ts);
-        const size_t o_on = acts_.reserve(Mm * VD * ts), o_hid = acts_.reserve(Mm * DFF * ts);
+        // the hidden layer of the feed-forward blocks exists in memory only in the exact tier (the 16-bit modes keep it on the SM)
+        const size_t o_on = acts_.reserve(Mm * VD * ts), o_hid = acts_.reserve(prec_ == Precision::FP32 ? Mm * DFF * ts : 0);
         const size_t o_qc = acts_.reserve(Bm * SQN * 4), o_y = acts_.reserve(Bm * D * 4), o_x2 = acts_.reserve(Bm * D * 4);
         // exact tier: the split A operand [lo | hi] of the GEMM about to run (widest: the FFN hidden layer)
         const size_t o_a2 = acts_.reserve(prec_ == Precision::FP32 ? Mm * 2 * DFF * 4 : 0);
@@ -428,7 +431,8 @@ private:
         cx_ = acts_.at<float>(o_cx); ce_ = acts_.at<float>(o_ce); cd_ = acts_.at<float>(o_cd);
         se_part_ = acts_.at<float>(o_sp); se_gate_ = acts_.at<float>(o_sg); pooled_ = acts_.at<float>(o_po);
         h_ = acts_.at<float>(o_h); P_ = acts_.at<float>(o_p);
-        xn_ = acts_.at<void>(o_xn); on_ = acts_.at<void>(o_on); hid_ = acts_.at<void>(o_hid);
+        xn_ = acts_.at<void>(o_xn); on_ = acts_.at<void>(o_on);
+        hid_ = prec_ == Precision::FP32 ? acts_.at<void>(o_hid) : nullptr;
         qc_ = acts_.at<float>(o_qc); y_ = acts_.at<float>(o_y); x2_ = acts_.at<float>(o_x2);
         a2_ = prec_ == Precision::FP32 ? acts_.at<float>(o_a2) : nullptr;
         act_bytes_ = acts_.size();
@@ -473,18 +477,24 @@ private:
             if (prec_ == Precision::FP32) make_site(in_[i], GN, D, xn_, g.in_w, P_, GLD, SHVK_F32);
             make_site(oproj_[i], D, VD, on_, g.o_proj, h_, D, SHVK_F32);
             oproj_[i].args.R = h_; oproj_[i].args.ldr = D; oproj_[i].args.r_div = inv_div[i];
-            make_site(up_[i], 2 * DFF, D, xn_, g.ffn_up, hid_, DFF, dt_);
-            up_[i].args.swiglu = 1;
-            make_site(down_[i], D, DFF, hid_, g.ffn_down, h_, D, SHVK_F32);
-            down_[i].args.R = h_; down_[i].args.ldr = D;
+            if (prec_ == Precision::FP32) {
+                make_site(up_[i], 2 * DFF, D, xn_, g.ffn_up, hid_, DFF, dt_);
+                up_[i].args.swiglu = 1;
+                make_site(down_[i], D, DFF, hid_, g.ffn_down, h_, D, SHVK_F32);
+                down_[i].args.R = h_; down_[i].args.ldr = D;
+            }
         }
         make_site(sisa_in_, SN, D, xn_, s_w_all_, P_, SLD, SHVK_F32);
         sisa_in_.args.bias = s_b_all_;
-        for (Site* st : {&oproj_[0], &oproj_[1], &up_[0], &up_[1], &down_[0], &down_[1]}) {
+        for (Site* st : {&oproj_[0], &oproj_[1]}) {
             launch_ok(shvk_gemm_tc_plan(&st->args, dt_, st->plan), "tensor-core GEMM plan");
             st->planned = true;
         }
         if (prec_ == Precision::FP32) {
+            for (Site* st : {&up_[0], &up_[1], &down_[0], &down_[1]}) {
+                launch_ok(shvk_gemm_tc_plan(&st->args, dt_, st->plan), "tensor-core GEMM plan");
+                st->planned = true;
+            }
             launch_ok(shvk_gemm_tc_plan(&sisa_in_.args, dt_, sisa_in_.plan), "tensor-core GEMM plan");
         } else {
             // 16-bit modes: K | V | B of the SISA projection leave as fp16 rows (S16), theta | alpha | forget as fp32 rows
@@ -507,6 +517,9 @@ private:
         // the chunk-blocked operand tiles of the in-projection live where the fp32 projection of the exact tier would
         if (shvk_gdn_pt_bytes(cfg_.max_windows) > size_t(cfg_.max_windows) * NTOK * GLD * 4)
             throw std::runtime_error("projection buffer too small for the operand tiles");
+        for (int i = 0; i < 2; ++i)
+            launch_ok(shvk_ffn_fused_plan(xn_, (long long)cfg_.max_windows * NTOK, gdn_[i].ffn_up, gdn_[i].ffn_down, h_, dt_, ffn_plan_[i]),
+                      "feed-forward plan");
         for (int i = 0; i < 2; ++i)
             launch_ok(shvk_gdn_inproj_plan(xn_, (long long)cfg_.max_windows * NTOK, gdn_[i].in_w_perm, gdn_[i].conv_w, gdn_[i].conv_b,
                                            gdn_[i].a_log, gdn_[i].dt_bias, P_, dt_, inproj_plan_[i]), "in-projection plan");
@@ -640,10 +653,16 @@ private:
                 launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_, dt_, D, M, s), "rmsnorm");
                 mark("rmsnorm", s);
             }
-            rows_gemm(up_[st], M, s);
-            mark("gemm.ffn_up", s);
-            rows_gemm(down_[st], M, s);
-            mark("gemm.ffn_down", s);
+            if (prec_ == Precision::FP32) {
+                rows_gemm(up_[st], M, s);
+                mark("gemm.ffn_up", s);
+                rows_gemm(down_[st], M, s);
+                mark("gemm.ffn_down", s);
+            } else {
+                // up + SwiGLU + down + residual in one launch, the hidden layer staying on the SM
+                launch_ok(shvk_ffn_fused(ffn_plan_[st], M, s), "feed-forward block");
+                mark("ffn_fused", s);
+            }
             dump(st == 0 ? "after_gdn_a" : "after_gdn_b", h_, size_t(NTOK) * D, SHVK_F32, s);
             const float* next_norm = st == 0 ? gdn_[1].norm_w : s_attn_norm_;
             launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_, dt_, D, M, s), "rmsnorm");

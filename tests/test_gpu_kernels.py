@@ -198,6 +198,52 @@ def test_gemm_tc_rows_do_not_depend_on_the_batch(L):
     assert torch.equal(big[515], one[0])
 
 
+# ---------------------------------------------------------------------------------------------- fused feed-forward block
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+def test_ffn_fused_equals_the_two_gemm_path(L, dtype):
+    """One launch (hidden layer on the SM) against up + SwiGLU and down + residual as two tensor-core GEMMs: bitwise, on a
+    row count that is not a multiple of the 128-row block, and row-independent."""
+    import torch
+    code = binding.DTYPES[dtype]
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    rng = np.random.default_rng(91)
+    M, K, F = 128 * 150 + 77, 384, 960                     # more row blocks than SMs: every CTA walks two
+    xn = dev(rng.standard_normal((M, K)).astype(np.float32), tdt)
+    wu = dev((rng.standard_normal((2 * F, K)) / 20).astype(np.float32), tdt)
+    wd = dev((rng.standard_normal((K, F)) / 30).astype(np.float32), tdt)
+    h0 = rng.standard_normal((M, K)).astype(np.float32)
+    # two-kernel path
+    H2 = dev(h0)
+    hid = torch.zeros((M, F), device="cuda", dtype=tdt)
+    k1, p1 = tc_plan(L, gemm_args(M, 2 * F, K, xn, wu, hid, F, c_dtype=code, swiglu=1), code)
+    k2, p2 = tc_plan(L, gemm_args(M, K, F, hid, wd, H2, K, R=H2, ldr=K), code)
+    ok(L.shvk_gemm_tc(p1, stream_ptr()))
+    ok(L.shvk_gemm_tc(p2, stream_ptr()))
+    # fused
+    H1 = dev(h0)
+    buf = (C.c_char * 1024)()
+    plan = (C.addressof(buf) + 63) & ~63
+    ok(L.shvk_ffn_fused_plan(xn.data_ptr(), M, wu.data_ptr(), wd.data_ptr(), H1.data_ptr(), code, plan))
+    ok(L.shvk_ffn_fused(plan, M, stream_ptr()))
+    sync()
+    assert tc_status(L) == 0
+    assert torch.equal(H1, H2)
+    # against float64 on a sample of rows
+    rows = np.array([0, 1, 127, 128, 5000, M - 78, M - 1])
+    x64 = xn[rows].float().cpu().numpy().astype(np.float64)
+    full = x64 @ wu.float().cpu().numpy().astype(np.float64).T
+    hid64 = silu(full[:, 0::2]) * full[:, 1::2]
+    ref = h0[rows] + hid64 @ wd.float().cpu().numpy().astype(np.float64).T
+    assert rel_err(H1[rows].cpu().numpy(), ref) < (8e-3 if dtype == "bf16" else 1e-3)
+    # fewer rows through the same plan: the rows computed are the same bits, the others untouched
+    H3 = dev(h0)
+    ok(L.shvk_ffn_fused_plan(xn.data_ptr(), M, wu.data_ptr(), wd.data_ptr(), H3.data_ptr(), code, plan))
+    ok(L.shvk_ffn_fused(plan, 333, stream_ptr()))
+    sync()
+    assert torch.equal(H3[:333], H1[:333])
+    assert torch.equal(H3[333:], dev(h0)[333:])
+
+
 # ---------------------------------------------------------------------------------------------- exact tier on tensor cores
 def split_operands(L, a, w):
     """Device [lo | hi] of a and [hi | lo | hi] of w through shvk_split_tf32, checked against the definition."""
