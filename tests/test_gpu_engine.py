@@ -32,8 +32,10 @@ def test_fp32_logits_match_golden(case, weight_files):
     with binding.CudaModel(path, "fp32") as m:
         assert m.mode == "fp32" and m.fingerprint == W.sha256_file(path) and m.threshold == 0.5
         logits = m.classify(tok)
-    assert np.abs(logits - g["logits_f64"]).max() < FP32_TOL
-    assert np.abs(logits - g["logits_cpu_engine"]).max() < FP32_TOL
+    e64, ecpu = np.abs(logits - g["logits_f64"]).max(), np.abs(logits - g["logits_cpu_engine"]).max()
+    print(f"fp32 {case}: logits max abs err {e64:.2e} vs float64 oracle, {ecpu:.2e} vs the CPU engine")
+    assert e64 < FP32_TOL
+    assert ecpu < FP32_TOL
 
 
 @pytest.mark.parametrize("case", CASES[:2])
@@ -74,12 +76,16 @@ def test_fp32_matches_oracle_on_fresh_inputs(recipe, wseed, tseed, batch, weight
         logits = m.classify(tok)
     pick = np.unique(np.linspace(0, batch - 1, 6).astype(int))
     ref = O.classify_tokens(w, tok[pick], np.float64)
-    assert np.abs(logits[pick] - ref).max() < FP32_TOL
+    e64 = np.abs(logits[pick] - ref).max()
+    print(f"fp32 {recipe} seed {wseed} B={batch}: logits max abs err {e64:.2e} vs float64 oracle on {len(pick)} clips")
+    assert e64 < FP32_TOL
     if ref_cpu.available():
         eng = ref_cpu.RefCpuEngine(path, threads=4)
         cpu = eng.classify(tok)
         eng.close()
-        assert np.abs(logits - cpu).max() < FP32_TOL
+        ecpu = np.abs(logits - cpu).max()
+        print(f"fp32 {recipe} seed {wseed} B={batch}: logits max abs err {ecpu:.2e} vs the CPU engine on all {batch} clips")
+        assert ecpu < FP32_TOL
 
 
 @pytest.mark.parametrize("mode", ["bf16", "fp16"])
