@@ -9,8 +9,9 @@
 //     drain(j) eight epilogue warps read acc_up, form silu(gate) * up, round to the storage type and write the
 //              128 x 64 tile straight into shared memory in the swizzled K-major layout an MMA A operand has
 //     down(j)  acc_down[128 x 384] += hid(j) . W_down[:, 64 j .. 64 j + 63]^T    3 x 4 MMAs (N 128 each)
-//   after the last slab the epilogue adds acc_down to the residual rows of h (read straight from global memory,
-//   prefetched into registers) and stores them through swizzled tiles with TMA.
+//   after the last slab the epilogue adds acc_down to the residual rows of h: a 32 x 32 block leaves tensor memory one
+//   row per lane, is turned through a swizzled shared-memory tile, and residual loads (prefetched into registers) and
+//   stores run coalesced, eight lanes per 128-byte row segment.
 // Tensor memory: acc_up in columns 0-127, acc_down in columns 128-511 (all 512).  The MMA thread issues
 // up(j), down(j - 1), up(j + 1), ...: the tensor pipe works on down(j - 1) while the epilogue drains acc_up of slab j.
 // Weight tiles of both matrices travel through one ring of six 16 KB stages in the order they are consumed.
@@ -30,6 +31,7 @@
 #include "tma_utils.cuh"
 
 #include <atomic>
+#include <stdlib.h>
 #include <string.h>
 
 namespace sb {
@@ -54,9 +56,17 @@ struct FfnMaps {
     CUtensorMap x;        // xn [rows][384], box 128 x 64
     CUtensorMap wu;       // W_up [1920][384] (gate / up rows interleaved), box 128 x 64
     CUtensorMap wd;       // W_down [384][960], box 128 x 64
-    CUtensorMap h;        // h [rows][384] fp32, box 32 x 32 (stores only)
 };
+// Timing probes of a development build (-DSHVK_DEV_PROBES, SHVK_FFN_PROBE; never the shipped libraries): 1 no SwiGLU
+// arithmetic, 2 no acc_up loads, 4 no up MMAs, 8 no down MMAs, 16 no residual epilogue work.  The bits travel in the
+// kernel parameters (constant bank), so reading them costs nothing in the loops they switch.
+#ifdef SHVK_DEV_PROBES
+#define FFN_PROBE(bit) (p.probe & (bit))
+#else
+#define FFN_PROBE(bit) 0
+#endif
 struct FfnParams {
+    int probe;
     int rows, m_tiles;
     uint32_t idesc;
     float* h;
@@ -166,7 +176,7 @@ ffn_fused_kernel(const __grid_constant__ FfnMaps maps, const FfnParams p, int* _
                             const uint64_t da = smem_desc_sw128(xn_base + kb * TILE_BYTES), db = smem_desc_sw128(w_base + stage * TILE_BYTES);
 #pragma unroll
                             for (int k = 0; k < TILE_K / 16; ++k)
-                                tc_mma_f16(tmem_base + ACC_UP, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
+                                if (!FFN_PROBE(4)) tc_mma_f16(tmem_base + ACC_UP, da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc, uint32_t((kb | k) != 0));
                             release();
                         }
                         if (!ok) break;
@@ -185,7 +195,7 @@ ffn_fused_kernel(const __grid_constant__ FfnMaps maps, const FfnParams p, int* _
                             const uint64_t db = smem_desc_sw128(w_base + stage * TILE_BYTES);
 #pragma unroll
                             for (int k = 0; k < TILE_K / 16; ++k)
-                                tc_mma_f16(tmem_base + ACC_DOWN + uint32_t(c * TILE), da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc,
+                                if (!FFN_PROBE(8)) tc_mma_f16(tmem_base + ACC_DOWN + uint32_t(c * TILE), da + uint64_t(2 * k), db + uint64_t(2 * k), p.idesc,
                                            uint32_t((jj | k) != 0));
                             release();
                         }
@@ -206,23 +216,37 @@ ffn_fused_kernel(const __grid_constant__ FfnMaps maps, const FfnParams p, int* _
         // this lane's 64 bytes of the hidden-layer tile: 16-byte chunks 4 half .. 4 half + 3 of row `row`, chunk c at c ^ (row & 7)
         const uint32_t hid_row = uint32_t(row >> 3) * 1024u + uint32_t(row & 7) * 128u;
         const uint32_t stage_tile = hid_base + uint32_t(ew) * 4096u; // output staging: 32 rows x 128 bytes, swizzled
-        const uint64_t pol_c = policy_evict_first();
         uint32_t slab = 0, n = 0;
         uint32_t hpar = 0;                                           // bit b: parity of the fills of hidden-layer buffer b so far
         bool ok = true;
         for (int mt = blockIdx.x; ok && mt < p.m_tiles; mt += gridDim.x, ++n) {
+            // the block's residual rows (128 x 1536 bytes) are asked into L2 now, fifteen slabs before the epilogue reads them:
+            // its loads then wait for L2, not for DRAM
+            for (int id = ew * 32 + lane; id < TILE * (kD * 4 / 128); id += EPI_WARPS * 32) {
+                const int prow = id / (kD * 4 / 128), seg = id - prow * (kD * 4 / 128);
+                if (mt * TILE + prow < p.rows)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.h + (long long)(mt * TILE + prow) * kD + seg * 32));
+            }
             for (int j = 0; j < SLABS; ++j, ++slab) {
                 const int hb = j & 1;
                 if (!mbar_wait(accu_full, slab & 1u, abortp, p.spin_limit)) { ok = false; break; }
                 tc_fence_after();
                 uint32_t r[64];
-                tc_ld32(tlane + ACC_UP + uint32_t(half * 64), r);
-                tc_ld32(tlane + ACC_UP + uint32_t(half * 64 + 32), r + 32);
-                tc_wait_ld();
+                if (!FFN_PROBE(2)) {
+                    tc_ld32(tlane + ACC_UP + uint32_t(half * 64), r);
+                    tc_ld32(tlane + ACC_UP + uint32_t(half * 64 + 32), r + 32);
+                    tc_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) r[i] = 0x3f000000u + uint32_t(i);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(accu_empty);              // the next up product may overwrite acc_up
                 uint32_t o[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) o[i] = r[i];
+                if (!FFN_PROBE(1))
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {                       // the arithmetic of gemm_tc's SwiGLU epilogue
                     const float g0 = __uint_as_float(r[4 * i]), g1 = __uint_as_float(r[4 * i + 2]);
@@ -242,55 +266,63 @@ ffn_fused_kernel(const __grid_constant__ FfnMaps maps, const FfnParams p, int* _
                 if (lane == 0) mbar_arrive(hfull_bar(hb));
             }
             if (!ok) break;
-            // ---- h += acc_down: twelve 32-column blocks per row quadrant, alternate blocks to the quadrant's two warps
+            // ---- h += acc_down: twelve 32-column blocks per row quadrant, alternate blocks to the quadrant's two warps.
+            // A block leaves tensor memory with one row per lane; it is turned through the warp's staging tile so that
+            // residual loads and stores are coalesced: lane -> (row rr + 4 i, 16-byte column group c4), eight lanes per row.
             const int m0 = mt * TILE + quad * 32;
-            const bool live = m0 + lane < p.rows;
-            const float* hrow = p.h + (long long)(m0 + lane) * kD;
-            float4 res[8];
-            auto load_res = [&](int blk) {
+            const int rr = lane >> 3, c4 = lane & 7;
+            float* hblk = p.h + (long long)(m0 + rr) * kD + 4 * c4;
+            float4 resa[8], resb[8];                                 // residuals of this warp's next two blocks
+            auto load_res = [&](int blk, float4 (&res)[8]) {
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    res[q] = live ? *(reinterpret_cast<const float4*>(hrow + 32 * blk) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int i = 0; i < 8; ++i)
+                    res[i] = m0 + rr + 4 * i < p.rows ? *reinterpret_cast<const float4*>(hblk + (long long)(4 * i) * kD + 32 * blk)
+                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
             };
-            load_res(half);
-            if (!mbar_wait(accd_full, n & 1u, abortp, p.spin_limit)) { ok = false; break; }
-            tc_fence_after();
-            // both hidden-layer buffers are free now (every down product of the block is complete): they become the
-            // staging tiles of the eight warps
-            for (int blk = half; blk < kD / 32; blk += 2) {
+            // one block: tensor memory -> staging tile (a row per lane) -> coalesced add and store
+            auto emit = [&](int blk, const float4 (&res)[8]) {
                 uint32_t r[32];
                 tc_ld32(tlane + ACC_DOWN + uint32_t(32 * blk), r);
                 tc_wait_ld();
-                float4 v[8];
+                __syncwarp();                                        // the previous block's reads of the tile are done
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
-                    v[q] = make_float4(res[q].x + __uint_as_float(r[4 * q]), res[q].y + __uint_as_float(r[4 * q + 1]),
-                                       res[q].z + __uint_as_float(r[4 * q + 2]), res[q].w + __uint_as_float(r[4 * q + 3]));
-                if (blk + 2 < kD / 32) load_res(blk + 2);            // next block's residual flies during this block's store
-                if (lane == 0) bulk_wait_read<0>();                  // the previous store has left the staging tile
+                    sts128u(stage_tile + uint32_t(lane) * 128u + ((uint32_t(q) ^ uint32_t(lane & 7)) << 4), r[4 * q], r[4 * q + 1],
+                            r[4 * q + 2], r[4 * q + 3]);
                 __syncwarp();
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    sts128(stage_tile + uint32_t(lane) * 128u + ((uint32_t(q) ^ uint32_t(lane & 7)) << 4), v[q].x, v[q].y, v[q].z, v[q].w);
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) {
-                    tma_store_2d_hint(&maps.h, 32 * blk, m0, stage_tile, pol_c);
-                    bulk_commit();
+                for (int i = 0; i < 8; ++i) {
+                    const int row = rr + 4 * i;
+                    const float4 a = lds128(stage_tile + uint32_t(row) * 128u + ((uint32_t(c4) ^ uint32_t(row & 7)) << 4));
+                    if (m0 + row < p.rows)
+                        *reinterpret_cast<float4*>(hblk + (long long)(4 * i) * kD + 32 * blk) =
+                            make_float4(res[i].x + a.x, res[i].y + a.y, res[i].z + a.z, res[i].w + a.w);
+                }
+            };
+            load_res(half, resa);
+            load_res(half + 2, resb);
+            if (!mbar_wait(accd_full, n & 1u, abortp, p.spin_limit)) { ok = false; break; }
+            tc_fence_after();
+            // both hidden-layer buffers are free now (every down product of the block is complete): they hold the
+            // staging tiles of the eight warps.  Six blocks per warp, residuals fetched two blocks ahead.
+            if (!FFN_PROBE(16)) {
+#pragma unroll 1
+                for (int blk = half; blk < kD / 32; blk += 4) {
+                    emit(blk, resa);
+                    if (blk + 4 < kD / 32) load_res(blk + 4, resa);
+                    emit(blk + 2, resb);
+                    if (blk + 6 < kD / 32) load_res(blk + 6, resb);
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(accd_empty);                             // the next block's down products may overwrite acc_down
-                bulk_wait_read<0>();                                 // this warp's staging tile is hidden-layer space again ...
-                mbar_arrive(staging_free);
+                mbar_arrive(staging_free);                           // this warp's staging tile is hidden-layer space again ...
             }
-            __syncwarp();
-            // ... once every epilogue warp's stores have left theirs (the tiles of the next block's hidden layer span them all)
+            // ... once every epilogue warp is done with its own (the tiles of the next block's hidden layer span them all)
             if (!mbar_wait(staging_free, n & 1u, abortp, p.spin_limit)) { ok = false; break; }
         }
-        if (lane == 0) bulk_wait_all();                              // stores must have left shared memory before exit
         if (!ok && lane == 0 && !*abortp) { *abortp = 1; atomicCAS(status, 0, 3); }
     }
 
@@ -326,7 +358,12 @@ template <typename T> int launch_ffn(const FfnMaps& maps, const FfnParams& p, in
     }
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const unsigned grid = unsigned(p.m_tiles < sms ? p.m_tiles : sms);
-    ffn_fused_kernel<T><<<grid, NTHREADS, SMEM_BYTES, s>>>(maps, p, status);
+    FfnParams q = p;
+    q.probe = 0;
+#ifdef SHVK_DEV_PROBES
+    { const char* e = getenv("SHVK_FFN_PROBE"); q.probe = e ? atoi(e) : 0; }
+#endif
+    ffn_fused_kernel<T><<<grid, NTHREADS, SMEM_BYTES, s>>>(maps, q, status);
     return int(cudaGetLastError());
 }
 
@@ -369,8 +406,6 @@ extern "C" int shvk_ffn_fused(const void* host_plan, int rows, void* stream) {
     if (!status) return int(cudaErrorInvalidSymbol);
     FfnMaps maps;
     maps.x = hp->map_x; maps.wu = hp->map_wu; maps.wd = hp->map_wd;
-    // the output map covers exactly `rows` rows, so the stores of the last row block clip there
-    if (!tma::make_map_2d(&maps.h, hp->p.h, 4, rows, kD, kD, 32, 32, true)) return int(cudaErrorNotSupported);
     FfnParams p = hp->p;
     p.rows = rows;
     p.m_tiles = (rows + TILE - 1) / TILE;

@@ -26,6 +26,8 @@
 //
 // A wait on a TMA barrier is bounded; if it gives up the CTA records it in a status word and returns.
 #include "device_utils.cuh"
+
+#include <atomic>
 #include "shv_seq_kernels.h"
 #include "tma_utils.cuh"
 #include "status_words.cuh"
@@ -275,16 +277,30 @@ extern "C" int shvk_gdn_scan(const float* P, const float* conv_w, const float* c
     using namespace sb;
     if (B <= 0) return 0;
     if (reinterpret_cast<uintptr_t>(P) & 15) return int(cudaErrorInvalidValue);
-    ScanMaps maps;
+    // the three tensor maps depend on (P, rows) only: an engine thread launches with the same pair again and again, so
+    // the last encoding is kept per thread
+    struct Cached { const float* P = nullptr; long long rows = 0; ScanMaps maps; };
+    static thread_local Cached cache;
     const long long rows = (long long)B * kTok;
-    if (!tma::make_map_f32(&maps.qk, P, rows, kGLD, kGLD, TC, kDK) || !tma::make_map_f32(&maps.vg, P, rows, kGLD, kGLD, TC, kDV) ||
-        !tma::make_map_f32(&maps.ab, P, rows, kGLD, kGLD, TC, 16))
-        return int(cudaErrorNotSupported);
+    if (cache.P != P || cache.rows != rows) {
+        cache.P = nullptr;
+        if (!tma::make_map_f32(&cache.maps.qk, P, rows, kGLD, kGLD, TC, kDK) || !tma::make_map_f32(&cache.maps.vg, P, rows, kGLD, kGLD, TC, kDV) ||
+            !tma::make_map_f32(&cache.maps.ab, P, rows, kGLD, kGLD, TC, 16))
+            return int(cudaErrorNotSupported);
+        cache.P = P; cache.rows = rows;
+    }
     const unsigned grid = unsigned(B) * kHeads;
+    int dev = 0;
+    cudaGetDevice(&dev);
     SB_DISPATCH_DTYPE(on_dtype, T, {
-        const cudaError_t e = cudaFuncSetAttribute(gdn_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM_BYTES);
-        if (e != cudaSuccess) return int(e);
-        gdn_scan_kernel<T><<<grid, 128, SCAN_SMEM_BYTES, cudaStream_t(stream)>>>(maps, conv_w, conv_b, a_log, dt_bias, o_norm_w,
+        // the dynamic shared memory opt-in is per device and per instantiation; setting it twice is harmless
+        static std::atomic<unsigned long long> attr_done{0};
+        if (dev >= 64 || !((attr_done.load(std::memory_order_acquire) >> dev) & 1ull)) {
+            const cudaError_t e = cudaFuncSetAttribute(gdn_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM_BYTES);
+            if (e != cudaSuccess) return int(e);
+            if (dev < 64) attr_done.fetch_or(1ull << dev, std::memory_order_release);
+        }
+        gdn_scan_kernel<T><<<grid, 128, SCAN_SMEM_BYTES, cudaStream_t(stream)>>>(cache.maps, conv_w, conv_b, a_log, dt_bias, o_norm_w,
                                                                                  static_cast<T*>(on));
     });
     return int(cudaGetLastError());
