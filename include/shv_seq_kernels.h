@@ -91,6 +91,7 @@ int shvk_gemm_tc_rows_starved(const void* host_plan, int rows, int polls, void* 
 int shvk_ffn_fused_plan(const void* xn, long long max_rows, const void* w_up, const void* w_down, float* h, int ab_dtype,
                         void* host_plan);
 int shvk_ffn_fused(const void* host_plan, int rows, void* stream);
+int shvk_ffn_fused_starved(const void* host_plan, int rows, int polls, void* stream);   /* test launch, as shvk_gdn_inproj_starved */
 
 /* The kernels' status words (tensor-core GEMMs, the scan that reads the fp32 projection, the 16-bit scan) are per
  * device and per process.  These two calls enqueue on `stream`: a copy of the SHVK_STATUS_WORDS words into host_words (pinned host memory, read it after
@@ -116,6 +117,10 @@ size_t shvk_gdn_pt_bytes(int B);
 int shvk_gdn_inproj_plan(const void* xn, long long max_rows, const void* w_perm, const float* conv_w, const float* conv_b,
                          const float* a_log, const float* dt_bias, void* pt_out, int ab_dtype, void* host_plan);
 int shvk_gdn_inproj(const void* host_plan, int B, void* stream);
+/* Test launches of the two kernels above's kind (see shvk_gemm_tc_rows_starved): the producer withholds its first weight
+ * tile, the MMA role's bounded wait runs out after `polls` polls, the CTAs take their abort path and return with the
+ * status word of the tensor-core GEMMs set.  Outputs are left partly written.  Nothing faults or spins without bound. */
+int shvk_gdn_inproj_starved(const void* host_plan, int B, int polls, void* stream);
 /* Gated delta rule + gated RMSNorm of one mixer over B clips from the PT tiles: 16-token chunks in WY form on the
  * tensor cores, the head's 64 x 128 state in accumulator fragments for the whole sequence.  on: [B*321][768] in
  * on_dtype (bf16 or fp16).  Replaces launch_delta + launch_gated_norm (engine/cuda/seq.cu:107-214,364-371). */

@@ -161,6 +161,8 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_store_tokens": (i32, [vp, vp, vp, i32, vp]),
         "shvk_ffn_fused_plan": (i32, [vp, C.c_longlong, vp, vp, vp, i32, vp]),
         "shvk_ffn_fused": (i32, [vp, i32, vp]),
+        "shvk_ffn_fused_starved": (i32, [vp, i32, i32, vp]),
+        "shvk_gdn_inproj_starved": (i32, [vp, i32, i32, vp]),
         "shvk_split_tf32": (i32, [vp, C.c_longlong, i32, C.c_longlong, vp, C.c_longlong, i32, vp]),
         "shvk_cnn_stem": (i32, [vp, vp, vp, vp, vp, i32, vp]),
         "shvk_cnn_depthwise": (i32, [vp, vp, vp, vp] + [i32] * 9 + [vp]),

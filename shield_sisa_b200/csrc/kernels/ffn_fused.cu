@@ -71,6 +71,7 @@ struct FfnParams {
     uint32_t idesc;
     float* h;
     uint32_t spin_limit;
+    int starve;      // test launch only: the producer withholds the first weight tile of its first row block
 };
 
 template <typename T>
@@ -121,8 +122,14 @@ ffn_fused_kernel(const __grid_constant__ FfnMaps maps, const FfnParams p, int* _
             uint32_t phase = 0;
             bool ok = true;
             const uint64_t pol_w = policy_evict_last();
+            bool withheld = !p.starve;
             auto put = [&](const CUtensorMap* map, int k0, int row0) -> bool {
                 if (!mbar_wait(wempty_bar(stage), phase ^ 1u, abortp, p.spin_limit)) return false;
+                if (!withheld) {                                     // test launch: this stage never fills
+                    withheld = true;
+                    if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
+                    return true;
+                }
                 mbar_expect_tx(wfull_bar(stage), uint32_t(TILE_BYTES));
                 tma_load_2d_hint(w_base + stage * TILE_BYTES, map, k0, row0, wfull_bar(stage), pol_w);
                 if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
@@ -391,13 +398,28 @@ extern "C" int shvk_ffn_fused_plan(const void* xn, long long max_rows, const voi
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(TILE >> 3) << 17) | (uint32_t(TILE >> 4) << 24);
     p.h = h;
     p.spin_limit = SPIN_LIMIT;
+    p.starve = 0;
     hp->max_rows = max_rows;
     hp->ab_dtype = ab_dtype;
     hp->valid = 0x5b202;
     return 0;
 }
 
+static int ffn_launch_rows(const void* host_plan, int rows, void* stream, int starve, uint32_t spin_limit);
+
 extern "C" int shvk_ffn_fused(const void* host_plan, int rows, void* stream) {
+    return ffn_launch_rows(host_plan, rows, stream, 0, sb::SPIN_LIMIT);
+}
+
+// Test launch: every CTA's producer withholds the first weight tile of its first row block, so the MMA thread's wait on
+// that stage runs out after `polls` polls (clamped to 256 .. 2^22); the CTA takes its abort path (status word of the
+// tensor-core GEMMs set, every role leaves its loop, tensor memory freed) and returns.  h is left partly updated.
+extern "C" int shvk_ffn_fused_starved(const void* host_plan, int rows, int polls, void* stream) {
+    const uint32_t lim = polls < 256 ? 256u : (uint32_t(polls) > sb::SPIN_LIMIT ? sb::SPIN_LIMIT : uint32_t(polls));
+    return ffn_launch_rows(host_plan, rows, stream, 1, lim);
+}
+
+static int ffn_launch_rows(const void* host_plan, int rows, void* stream, int starve, uint32_t spin_limit) {
     using namespace sb;
     const HostPlan* hp = static_cast<const HostPlan*>(host_plan);
     if (!hp || hp->valid != 0x5b202 || rows > hp->max_rows) return int(cudaErrorInvalidValue);
@@ -407,6 +429,8 @@ extern "C" int shvk_ffn_fused(const void* host_plan, int rows, void* stream) {
     FfnMaps maps;
     maps.x = hp->map_x; maps.wu = hp->map_wu; maps.wd = hp->map_wd;
     FfnParams p = hp->p;
+    p.starve = starve;
+    p.spin_limit = spin_limit;
     p.rows = rows;
     p.m_tiles = (rows + TILE - 1) / TILE;
     cudaStream_t s = cudaStream_t(stream);

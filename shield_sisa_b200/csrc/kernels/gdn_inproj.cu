@@ -67,6 +67,7 @@ struct InprojParams {
     const float *conv_w, *conv_b, *a_log, *dt_bias;
     uint8_t* pt;
     uint32_t spin_limit;
+    int starve;      // test launch only: the producer withholds the first weight tile of its first work item
     int qk_f16;      // q^T / k^T tiles in fp16 (fp16 mode) instead of bf16
     int probe;       // timing probes of a development build (-DSHVK_DEV_PROBES, SHVK_INPROJ_PROBE): 1 no global stores,
                      // 2 no activation arithmetic, 4 no tensor-memory loads, 8 no MMA.  Constant 0 in the shipped libraries.
@@ -314,6 +315,10 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
                 for (int m = 0; ok && m < M_TILES; ++m) {
                     for (int kb = 0; kb < KBLOCKS; ++kb) {
                         if (!mbar_wait(wempty_bar(stage), phase ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
+                        if (p.starve && item == (long long)blockIdx.x && m == 0 && kb == 0) {   // test launch: this stage never fills
+                            if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
+                            continue;
+                        }
                         mbar_expect_tx(wfull_bar(stage), uint32_t(W_STAGE_BYTES));
                         tma_load_2d_hint(w_base + stage * W_STAGE_BYTES, &maps.w, kb * TILE_K, m * TILE_M, wfull_bar(stage), pol_w);
                         if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
@@ -466,13 +471,28 @@ extern "C" int shvk_gdn_inproj_plan(const void* xn, long long max_rows, const vo
     p.conv_w = conv_w; p.conv_b = conv_b; p.a_log = a_log; p.dt_bias = dt_bias;
     p.pt = static_cast<uint8_t*>(pt_out);
     p.spin_limit = SPIN_LIMIT;
+    p.starve = 0;
     p.qk_f16 = ab_dtype == DT_F16;
     hp->max_rows = max_rows;
     hp->valid = 0x5b201;
     return 0;
 }
 
+static int inproj_launch(const void* host_plan, int B, void* stream, int starve, uint32_t spin_limit);
+
 extern "C" int shvk_gdn_inproj(const void* host_plan, int B, void* stream) {
+    return inproj_launch(host_plan, B, stream, 0, sb::SPIN_LIMIT);
+}
+
+// Test launch: every CTA's producer withholds the first weight tile of its first work item, so the MMA thread's wait on
+// that stage runs out after `polls` polls (clamped to 256 .. 2^22); the CTA takes its abort path (status word of the
+// tensor-core GEMMs set, every role leaves its loop, tensor memory freed) and returns.  The tiles are left partly written.
+extern "C" int shvk_gdn_inproj_starved(const void* host_plan, int B, int polls, void* stream) {
+    const uint32_t lim = polls < 256 ? 256u : (uint32_t(polls) > sb::SPIN_LIMIT ? sb::SPIN_LIMIT : uint32_t(polls));
+    return inproj_launch(host_plan, B, stream, 1, lim);
+}
+
+static int inproj_launch(const void* host_plan, int B, void* stream, int starve, uint32_t spin_limit) {
     using namespace sb;
     const HostPlan* hp = static_cast<const HostPlan*>(host_plan);
     if (!hp || hp->valid != 0x5b201 || (long long)B * kTok > hp->max_rows) return int(cudaErrorInvalidValue);
@@ -492,6 +512,8 @@ extern "C" int shvk_gdn_inproj(const void* host_plan, int B, void* stream) {
     maps.w = hp->map_w; maps.x = hp->map_x;
     InprojParams p = hp->p;
     p.B = B;
+    p.starve = starve;
+    p.spin_limit = spin_limit;
     const long long items = 2ll * B;
     const unsigned grid = unsigned(items < sms ? items : sms);
 #ifdef SHVK_DEV_PROBES

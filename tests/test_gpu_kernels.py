@@ -559,7 +559,8 @@ def test_gdn_inproj_scan_clips_are_independent(L, weight_files):
 
 
 def test_starved_launches_give_up_and_the_status_clears(L, weight_files):
-    """A bounded wait that runs out: the tensor-core GEMM and the scan are each launched once with their input withheld.
+    """A bounded wait that runs out: the tensor-core GEMM, the scan, the fused in-projection and the fused feed-forward
+    block are each launched once with their input withheld.
     Each must return by itself with its status word set and nothing else disturbed; after the words are cleared the
     same launches work normally."""
     import torch
@@ -601,6 +602,38 @@ def test_starved_launches_give_up_and_the_status_clears(L, weight_files):
     ok(L.shvk_gdn_scan_t(pt.data_ptr(), ow.data_ptr(), on.data_ptr(), 1, 2, stream_ptr()))
     sync()
     assert fetch() == [0, 0, 0] and torch.isfinite(on.float()).all() and not (on == 5.0).all()
+    # the fused in-projection (its waits report through the tensor-core GEMM word)
+    d, buf = keep2
+    plan_in = (C.addressof(buf) + 63) & ~63
+    ref_pt = pt.clone()
+    ok(L.shvk_gdn_inproj_starved(plan_in, 2, 1024, stream_ptr()))
+    sync()
+    assert fetch()[0] != 0
+    ok(L.shvk_status_clear_async(stream_ptr()))
+    ok(L.shvk_gdn_inproj(plan_in, 2, stream_ptr()))
+    sync()
+    assert fetch() == [0, 0, 0] and torch.equal(pt, ref_pt)
+    # the fused feed-forward block
+    Mf = 700
+    xf = dev(rng.standard_normal((Mf, 384)).astype(np.float32), torch.bfloat16)
+    wu = dev((rng.standard_normal((1920, 384)) / 20).astype(np.float32), torch.bfloat16)
+    wd = dev((rng.standard_normal((384, 960)) / 30).astype(np.float32), torch.bfloat16)
+    h0 = rng.standard_normal((Mf, 384)).astype(np.float32)
+    Hs, Hn = dev(h0), dev(h0)
+    fbuf = (C.c_char * 1024)()
+    fplan = (C.addressof(fbuf) + 63) & ~63
+    ok(L.shvk_ffn_fused_plan(xf.data_ptr(), Mf, wu.data_ptr(), wd.data_ptr(), Hs.data_ptr(), 1, fplan))
+    ok(L.shvk_ffn_fused_starved(fplan, Mf, 1024, stream_ptr()))
+    sync()
+    assert fetch()[0] != 0
+    ok(L.shvk_status_clear_async(stream_ptr()))
+    ok(L.shvk_ffn_fused_plan(xf.data_ptr(), Mf, wu.data_ptr(), wd.data_ptr(), Hn.data_ptr(), 1, fplan))
+    ok(L.shvk_ffn_fused(fplan, Mf, stream_ptr()))
+    sync()
+    assert fetch() == [0, 0, 0]
+    full = xf.float().cpu().numpy().astype(np.float64) @ wu.float().cpu().numpy().astype(np.float64).T
+    ref_h = h0 + (silu(full[:, 0::2]) * full[:, 1::2]) @ wd.float().cpu().numpy().astype(np.float64).T
+    assert rel_err(Hn.cpu().numpy(), ref_h) < 8e-3
 
 
 # ---------------------------------------------------------------------------------------------- SISA attention + head
