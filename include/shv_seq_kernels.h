@@ -24,6 +24,9 @@ extern "C" {
 #endif
 
 enum { SHVK_F32 = 0, SHVK_BF16 = 1, SHVK_F16 = 2 };
+/* Output code of shvk_assemble_norm / shvk_rmsnorm only: the normalised row leaves as the exact tier's split A operand,
+ * a row of 2 x 384 floats [lo | hi] (x = hi + lo, both TF32-representable; see shvk_split_tf32). */
+enum { SHVK_F32_SPLIT = 3 };
 
 /* h[b*321 + t] = tokens(b, t/16, t%16) + pos[t] (t < 320), readout (t == 320), and in the same pass
  * xn = rmsnorm(h) * norm_w in storage type xn_dtype.  tok_ptrs: [B*20] device pointers to 16x384 fp32 blocks.

@@ -208,8 +208,8 @@ public:
         starve_batches_ = batches > 0 ? batches : 0;
     }
     // 16-bit modes: 21 kernels.  Exact tier: 23 (its feed-forward blocks are two GEMMs each) + a launch that splits the
-    // A operand for each of its 11 all-row GEMMs
-    int launches_per_classify() const override { return prec_ == Precision::FP32 ? 34 : 21; }
+    // A operand of the five GEMMs that do not read a normalised row (three o-projections, two FFN down projections)
+    int launches_per_classify() const override { return prec_ == Precision::FP32 ? 28 : 21; }
 
     // One eager classify / encode with an event after every launch; returns (kernel name, milliseconds) per launch.
     std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) override {
@@ -409,7 +409,7 @@ private:
     // ---------------------------------------------------------------- buffers
     void allocate() {
         const size_t Bm = size_t(cfg_.max_windows), Mm = Bm * NTOK, Fm = size_t(cfg_.max_frames), ts = dtype_bytes(prec_);
-        const size_t o_h = acts_.reserve(Mm * D * 4), o_p = acts_.reserve(Mm * GLD * 4), o_xn = acts_.reserve(Mm * D * ts);
+        const size_t o_h = acts_.reserve(Mm * D * 4), o_p = acts_.reserve(Mm * GLD * 4), o_xn = acts_.reserve(prec_ == Precision::FP32 ? 256 : Mm * D * ts);   // exact tier: the norm kernels write into a2_
         // the hidden layer of the feed-forward blocks exists in memory only in the exact tier (the 16-bit modes keep it on the SM)
         const size_t o_on = acts_.reserve(Mm * VD * ts), o_hid = acts_.reserve(prec_ == Precision::FP32 ? Mm * DFF * ts : 0);
         const size_t o_qc = acts_.reserve(Bm * SQN * 4), o_y = acts_.reserve(Bm * D * 4), o_x2 = acts_.reserve(Bm * D * 4);
@@ -466,7 +466,8 @@ private:
         a.C = C; a.ldc = ldc; a.c_dtype = c_dtype;
         a.r_div = 1.0f;
         if (prec_ == Precision::FP32) {          // split operands: A = [lo | hi] in a2_, W = [hi | lo | hi]
-            st.split_src = static_cast<const float*>(A);
+            // the norm kernels write their rows into a2_ already split; the other operands are split by a launch of their own
+            st.split_src = A == xn_ ? nullptr : static_cast<const float*>(A);
             a.A = a2_; a.lda = 2 * K; a.ldw = 3 * K;
         }
     }
@@ -622,7 +623,11 @@ private:
     void run(int slot, int B, cudaStream_t s, int starve = 0) {
         const Slot& sl = slots_[size_t(slot)];
         const int M = B * NTOK;
-        launch_ok(shvk_assemble_norm(sl.d_tokptr, pos_, readout_, gdn_[0].norm_w, h_, xn_, dt_, B, s), "assemble");
+        // exact tier: the normalised rows leave the norm kernels as the split A operand [lo | hi] of the GEMM that reads them
+        void* const xn_out = prec_ == Precision::FP32 ? static_cast<void*>(a2_) : xn_;
+        const int xn_code = prec_ == Precision::FP32 ? int(SHVK_F32_SPLIT) : dt_;
+        const long long xn_ld = prec_ == Precision::FP32 ? 2 * D : D;
+        launch_ok(shvk_assemble_norm(sl.d_tokptr, pos_, readout_, gdn_[0].norm_w, h_, xn_out, xn_code, B, s), "assemble");
         mark("assemble_norm", s);
         dump("h0", h_, size_t(NTOK) * D, SHVK_F32, s);
         for (int st = 0; st < 2; ++st) {
@@ -650,7 +655,7 @@ private:
                     rows_gemm(oproj_[st], M, s);
                 mark("gemm.o_proj", s);
                 const float* next_norm = r + 1 < reps ? g.norm_w : g.ffn_norm_w;
-                launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_, dt_, D, M, s), "rmsnorm");
+                launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_out, xn_code, xn_ld, M, s), "rmsnorm");
                 mark("rmsnorm", s);
             }
             if (prec_ == Precision::FP32) {
@@ -665,7 +670,7 @@ private:
             }
             dump(st == 0 ? "after_gdn_a" : "after_gdn_b", h_, size_t(NTOK) * D, SHVK_F32, s);
             const float* next_norm = st == 0 ? gdn_[1].norm_w : s_attn_norm_;
-            launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_, dt_, D, M, s), "rmsnorm");
+            launch_ok(shvk_rmsnorm(h_, D, next_norm, xn_out, xn_code, xn_ld, M, s), "rmsnorm");
             mark("rmsnorm", s);
         }
         float* S = P_;

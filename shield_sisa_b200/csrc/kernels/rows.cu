@@ -9,8 +9,29 @@ namespace {
 
 constexpr int kWarpsPerBlock = 8;
 
+// Exact-tier operand split: x = hi + lo with hi = x rounded to TF32 (10 mantissa bits) and lo = x - hi (exact in
+// fp32) rounded to TF32 as well, so neither piece has bits the tensor core would drop.
+__device__ __forceinline__ float tf32_rna(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+// Output type tag of the norm kernels in the exact tier: the normalised row leaves as the split A operand [lo | hi] of
+// the tensor-core GEMM that reads it (a row of 2 x 384 floats), with no fp32 copy and no split launch in between.
+struct Tf32Split {};
+template <typename T> struct OutRow { using type = T; static constexpr int pitch = kD; };
+template <> struct OutRow<Tf32Split> { using type = float; static constexpr int pitch = 2 * kD; };
+template <typename T> __device__ __forceinline__ void store_norm4(typename OutRow<T>::type* out, float a, float b, float c, float d) {
+    store_quad<T>(out, a, b, c, d);
+}
+template <> __device__ __forceinline__ void store_norm4<Tf32Split>(float* out, float a, float b, float c, float d) {
+    const float4 hi = make_float4(tf32_rna(a), tf32_rna(b), tf32_rna(c), tf32_rna(d));
+    *reinterpret_cast<float4*>(out) = make_float4(tf32_rna(a - hi.x), tf32_rna(b - hi.y), tf32_rna(c - hi.z), tf32_rna(d - hi.w));
+    *reinterpret_cast<float4*>(out + kD) = hi;
+}
+
 template <typename T>
-__device__ __forceinline__ void norm_store(const float4 (&v)[3], const float* __restrict__ w, T* __restrict__ out, int lane) {
+__device__ __forceinline__ void norm_store(const float4 (&v)[3], const float* __restrict__ w, typename OutRow<T>::type* __restrict__ out, int lane) {
     float ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < 3; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
@@ -20,7 +41,7 @@ __device__ __forceinline__ void norm_store(const float4 (&v)[3], const float* __
     for (int i = 0; i < 3; ++i) {
         const int c = i * 128 + lane * 4;
         const float4 g = *reinterpret_cast<const float4*>(w + c);
-        store_quad<T>(out + c, (v[i].x * r) * g.x, (v[i].y * r) * g.y, (v[i].z * r) * g.z, (v[i].w * r) * g.w);
+        store_norm4<T>(out + c, (v[i].x * r) * g.x, (v[i].y * r) * g.y, (v[i].z * r) * g.z, (v[i].w * r) * g.w);
     }
 }
 
@@ -28,7 +49,7 @@ template <typename T>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 assemble_norm_kernel(const float* const* __restrict__ tok_ptrs, const float* __restrict__ pos,
                      const float* __restrict__ readout, const float* __restrict__ norm_w, float* __restrict__ h,
-                     T* __restrict__ xn, long long rows) {
+                     typename OutRow<T>::type* __restrict__ xn, long long rows) {
     const long long row = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -51,12 +72,12 @@ assemble_norm_kernel(const float* const* __restrict__ tok_ptrs, const float* __r
     float* hr = h + row * kD;
 #pragma unroll
     for (int i = 0; i < 3; ++i) *reinterpret_cast<float4*>(hr + i * 128 + lane * 4) = v[i];
-    norm_store<T>(v, norm_w, xn + row * kD, lane);
+    norm_store<T>(v, norm_w, xn + row * OutRow<T>::pitch, lane);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-rmsnorm_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w, T* __restrict__ out,
+rmsnorm_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w, typename OutRow<T>::type* __restrict__ out,
                long long ldo, long long rows) {
     const long long row = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -84,11 +105,6 @@ store_tokens_kernel(const float4* __restrict__ src, const int32_t* __restrict__ 
 // fp32) rounded to TF32 as well, so neither piece has bits the tensor core would drop.  One thread per four elements.
 //   layout 0 (activations): out row = [lo | hi]        (2K)
 //   layout 1 (weights):     out row = [hi | lo | hi]   (3K)
-__device__ __forceinline__ float tf32_rna(float x) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return __uint_as_float(u);
-}
 __global__ void __launch_bounds__(256)
 split_tf32_kernel(const float* __restrict__ in, long long ld_in, int k4, long long rows, float* __restrict__ out, long long ld_out,
                   int K, int layout) {
@@ -130,6 +146,11 @@ extern "C" int shvk_assemble_norm(const float* const* tok_ptrs, const float* pos
     if (B <= 0) return 0;
     const long long rows = (long long)B * sb::kTok;
     const unsigned grid = unsigned((rows + sb::kWarpsPerBlock - 1) / sb::kWarpsPerBlock);
+    if (xn_dtype == SHVK_F32_SPLIT) {
+        sb::assemble_norm_kernel<sb::Tf32Split><<<grid, sb::kWarpsPerBlock * 32, 0, cudaStream_t(stream)>>>(
+            tok_ptrs, pos, readout, norm_w, h, static_cast<float*>(xn), rows);
+        return int(cudaGetLastError());
+    }
     SB_DISPATCH_DTYPE(xn_dtype, T, (sb::assemble_norm_kernel<T><<<grid, sb::kWarpsPerBlock * 32, 0, cudaStream_t(stream)>>>(
                                        tok_ptrs, pos, readout, norm_w, h, static_cast<T*>(xn), rows)));
     return int(cudaGetLastError());
@@ -139,6 +160,11 @@ extern "C" int shvk_rmsnorm(const float* x, long long ldx, const float* w, void*
                             int rows, void* stream) {
     if (rows <= 0) return 0;
     const unsigned grid = unsigned((rows + sb::kWarpsPerBlock - 1) / sb::kWarpsPerBlock);
+    if (out_dtype == SHVK_F32_SPLIT) {
+        if (ldo < 2 * sb::kD || (ldo & 3)) return int(cudaErrorInvalidValue);
+        sb::rmsnorm_kernel<sb::Tf32Split><<<grid, sb::kWarpsPerBlock * 32, 0, cudaStream_t(stream)>>>(x, ldx, w, static_cast<float*>(out), ldo, rows);
+        return int(cudaGetLastError());
+    }
     SB_DISPATCH_DTYPE(out_dtype, T, (sb::rmsnorm_kernel<T><<<grid, sb::kWarpsPerBlock * 32, 0, cudaStream_t(stream)>>>(
                                         x, ldx, w, static_cast<T*>(out), ldo, rows)));
     return int(cudaGetLastError());

@@ -361,6 +361,20 @@ def test_assemble_norm_and_rmsnorm(L, weight_files):
         np.testing.assert_array_equal(h.cpu().numpy().reshape(B, 321, 384), href)
         ref = O.rms_norm(href.astype(np.float64), nw.astype(np.float64)).reshape(B * 321, 384)
         assert rel_err(xn.float().cpu().numpy(), ref) < tol
+    # exact tier: the same rows as the split operand [lo | hi], from both kernels
+    xs = torch.zeros((B * 321, 768), device="cuda")
+    ok(L.shvk_assemble_norm(P.data_ptr(), d_pos.data_ptr(), d_ro.data_ptr(), d_nw.data_ptr(), h.data_ptr(), xs.data_ptr(), 3, B,
+                            stream_ptr()))
+    x32 = torch.zeros((B * 321, 384), device="cuda")
+    ok(L.shvk_rmsnorm(h.data_ptr(), 384, d_nw.data_ptr(), x32.data_ptr(), 0, 384, B * 321, stream_ptr()))
+    xs2 = torch.zeros((B * 321, 768), device="cuda")
+    ok(L.shvk_rmsnorm(h.data_ptr(), 384, d_nw.data_ptr(), xs2.data_ptr(), 3, 768, B * 321, stream_ptr()))
+    sync()
+    assert torch.equal(xs, xs2)
+    sp, full = xs.cpu().numpy(), x32.cpu().numpy()
+    assert ((sp.view(np.uint32) & 0x1fff) == 0).all()                          # both pieces are TF32 numbers
+    resid = np.abs(full.astype(np.float64) - sp[:, :384].astype(np.float64) - sp[:, 384:].astype(np.float64))
+    assert (resid <= np.abs(full) * 2.0 ** -21 + 1e-45).all()
     # strided rows: the readout row of every clip
     out = torch.zeros((B, 384), device="cuda")
     ok(L.shvk_rmsnorm(h.data_ptr() + 320 * 384 * 4, 321 * 384, d_nw.data_ptr(), out.data_ptr(), 0, 384, B, stream_ptr()))
