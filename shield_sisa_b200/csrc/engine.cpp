@@ -1,23 +1,28 @@
 // Sequence engine core.  Launch order of one classify (B windows, M = 321*B rows), following the reference's
-// run_classify (engine/cuda/engine.cu:406-470) with the memory-bound steps between GEMMs fused:
+// run_classify (engine/cuda/engine.cu:406-470) with the memory-bound steps between GEMMs fused.
 //
+// 16-bit modes (21 launches):
 //   assemble+norm -> h (fp32), xn
 //   3 mixers (GDN-A once, GDN-B twice with the same weights, delta / sqrt(2)):
-//       in-proj GEMM xn -> P [M,2320] fp32 | fused scan (conv, L2, gates, delta rule, gated norm) P -> on
-//       | o-proj GEMM + residual -> h | norm h -> xn
-//   2 FFNs: up GEMM + SwiGLU -> hid | down GEMM + residual -> h | norm -> xn
-//   SISA: all-row GEMM + bias -> S [M,1072] fp32 (aliases P); readout row: norm, QC GEMM, attention kernel,
-//       W_O + residual, norm, FFN, head -> logits, as two fused kernels around the attention kernel.  Everything on
-//       the readout row is fp32 in every mode.
+//       fused in-projection (W' xn^T on the tensor cores, conv + SiLU + gates in its epilogue) xn -> 16-bit operand tiles PT
+//       | scan (chunked delta rule, gated norm) PT -> on | o-proj GEMM + residual -> h | norm h -> xn
+//   2 FFNs: one kernel (up GEMM, SwiGLU into shared memory, down GEMM, residual) xn -> h | norm -> xn
+//   SISA: all-row GEMM + bias -> K | V | B as fp16 rows, theta | alpha | forget as fp32 rows (both alias PT);
+//       readout row: norm + Q/C projection, attention kernel, then W_O + residual, norm, FFN, head -> logits as one kernel.
+// fp32 mode (28 launches): the same sequence with the in-projection as a GEMM writing P [M,2320] fp32 and the scan
+//   reading it, the FFN as two GEMMs, S [M,1072] fp32; all-row GEMMs on the tensor cores with fp32 operands split into two
+//   TF32 pieces each (the norm kernels write their rows already split, the other A operands are split by a launch of their
+//   own).  Everything on the readout row is fp32 in every mode.
 //
 // encode (F frames, reference run_encode engine/cuda/engine.cu:338-403): stem -> 15 inverted-residual blocks
 //   (expand 1x1 | depthwise | squeeze-excite gate | project 1x1 with the gate applied to its input rows, + residual)
 //   -> 1x1 160 -> 960 -> 4x4 pooling -> 960 -> 384 token projection into slot.d_tokens.  float32 NHWC storage in every
 //   mode; in the bf16 / fp16 modes the 1x1 convolutions round their operands to that type and multiply on the tensor cores.
 //
-// Storage policy (engine/cuda/engine.cu:150-164,213-219): h, P/S and the readout-row buffers are fp32 always; xn, on,
-// hid and the all-row weights are the storage type of the mode.  fp32 mode runs the all-row GEMMs on CUDA cores
-// (IEEE fma chain), bf16/fp16 modes on the tcgen05 tensor-core kernel.
+// Storage policy (engine/cuda/engine.cu:150-164,213-219): h and the readout-row buffers are fp32 always; xn, on and the
+// all-row weights are the storage type of the mode.  Departures in the 16-bit modes, all inside the 2e-2 tolerance and
+// measured against the policy's own error: q, k, v, gate and the SISA K, V, B rows cross memory in 16 bits where the
+// reference keeps fp32, and the FFN hidden layer does not cross memory at all.
 #include "engine.hpp"
 #include "shv_seq_kernels.h"
 #include "shv_cnn_kernels.h"
