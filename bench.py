@@ -777,6 +777,46 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         del dst
         if not np.isfinite(out).all():
             raise SystemExit("end-to-end run returned non-finite logits")
+        # Beside it (an extra key, never the headline): the same calls with the tokens handed over as fp16 through the
+        # extension shv_cuda_b200_classify_f16, half the bytes to upload.  The reference's ABI fixes fp32 tokens; this shows
+        # what the end-to-end rate is when the host's upload bandwidth is shared by fewer bytes.
+        f16 = None
+        if mode != "fp32":
+            pin16 = binding.PinnedBuffer(model.L, (B, 20, 16, D), np.float16)
+            pin16.array[...] = pin.array
+            out16 = np.empty(B, np.float32)
+
+            def caller16(i, n_steps, errs):
+                lo, hi = cuts[i], cuts[i + 1]
+                try:
+                    for _ in range(n_steps):
+                        model.classify_f16(pin16.array[lo:hi], out16[lo:hi])
+                except Exception as e:
+                    errs.append(e)
+
+            def run16(n_steps):
+                errs = []
+                ts = [threading.Thread(target=caller16, args=(i, n_steps, errs)) for i in range(nthr)]
+                for th in ts:
+                    th.start()
+                for th in ts:
+                    th.join()
+                if errs:
+                    raise errs[0]
+
+            run16(max(1, min(args.warmup, 3)))
+            barrier()
+            t0 = time.perf_counter()
+            run16(args.steps)
+            ms16 = max_over_ranks(1000.0 * (time.perf_counter() - t0) / args.steps)
+            barrier()
+            if not np.isfinite(out16).all():
+                raise SystemExit("end-to-end run with fp16 tokens returned non-finite logits")
+            f16 = {"value": world * B / (ms16 / 1000.0), "unit": UNIT, "ms_per_step": ms16,
+                   "h2d_bytes_per_step": B * 20 * 6144 * 2 + B * 20 * 8, "d2h_bytes_per_step": B * 4,
+                   "max_abs_logit_change": float(np.abs(out16 - out).max()),
+                   "api": "the same callers through shv_cuda_b200_classify_f16 (extension: fp16 host tokens, widened on the device)"}
+            pin16.free()
         e2e = {"value": world * B / (e2e_ms / 1000.0), "unit": UNIT, "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": B * 20 * 6144 * 4 + B * 20 * 8, "d2h_bytes_per_step": B * 4,
                "h2d_only": {"ms_per_step": h2d_ms, "gbs_per_rank": B * 20 * 6144 * 4 / h2d_ms / 1e6, "pinned": bool(src.is_pinned()),
@@ -784,7 +824,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                             "note": "the step's token uploads alone (same pinned buffer, same piece size, no kernels), all "
                                     "ranks at once, max over ranks"},
                "api": "%d host thread(s), each one synchronous shv_cuda_classify of its B/%d clips per step; pinned host "
-                      "tokens (shv_cuda_host_alloc), max_windows = %d" % (nthr, nthr, mw)}
+                      "tokens (shv_cuda_host_alloc), max_windows = %d" % (nthr, nthr, mw),
+               "f16_tokens": f16}
         model.close()
         pin.free()
 

@@ -23,6 +23,14 @@ extern "C" {
  * earlier see the old contents, windows submitted later the new ones.  Blocks; 0 on success, -1 on error. */
 int shv_cuda_b200_upload_tokens(shv_cuda_model* m, const float* tokens, size_t n, const int32_t* slots);
 
+/* shv_cuda_classify (engine/include/shv_cuda.h:141) with the tokens handed over as IEEE fp16 instead of fp32:
+ * tokens_f16 is [b][20][16][384] halves (12,288 bytes per frame block, 16-byte aligned), half the bytes to bring to the
+ * device.  No counterpart in the reference, whose ABI fixes fp32 tokens; meant for callers whose frame embeddings are
+ * already 16-bit and whose GPUs share one host's upload bandwidth.  The blocks are widened to fp32 on the device before
+ * anything reads them, so the logits are those of shv_cuda_classify on the same values as fp32, in every mode (and
+ * differ from those of the unrounded embeddings by what fp16 rounding of the inputs costs).  Blocks; 0 or -1. */
+int shv_cuda_b200_classify_f16(shv_cuda_model* m, const uint16_t* tokens_f16, size_t b, float* logits);
+
 /* Number of kernels one GPU batch launches (for launch accounting in benchmarks). */
 int shv_cuda_b200_launches_per_batch(const shv_cuda_model* m);
 

@@ -39,6 +39,10 @@ int shvk_assemble_norm(const float* const* tok_ptrs, const float* pos, const flo
 int shvk_rmsnorm(const float* x, long long ldx, const float* w, void* out, int out_dtype, long long ldo, int rows,
                  void* stream);
 
+/* Token blocks (16 x 384) that arrived as fp16 in the upper half (bytes 12,288 ..) of their 24,576-byte fp32 staging
+ * blocks, widened to fp32 in place; `stage` points at the first of `blocks` consecutive staging blocks. */
+int shvk_expand_f16_tokens(float* stage, int blocks, void* stream);
+
 /* C = epilogue(A * W^T): A [M,K] row-major (pitch lda), W [N,K] row-major (pitch ldw) = Linear weight layout.
  * Epilogue, in this order: + bias[n]; SiLU if act == 1; residual C = R + v / r_div (R fp32, may alias C);
  * swiglu: columns (2j, 2j+1) = (gate, up), writes silu(gate)*up at column j.  Never splits K.

@@ -99,6 +99,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shv_cuda_host_alloc": (vp, [sz]),
         "shv_cuda_host_free": (None, [vp]),
         "shv_cuda_b200_upload_tokens": (i32, [vp, vp, sz, vp]),
+        "shv_cuda_b200_classify_f16": (i32, [vp, vp, sz, vp]),
         "shv_cuda_b200_launches_per_batch": (i32, [vp]),
         "shv_cuda_b200_test_starve": (i32, [vp, i32, i32]),
         "shv_box_load": (vp, [C.c_char_p, C.c_char_p, C.POINTER(i32), i32, C.POINTER(Options), i32]),
@@ -163,6 +164,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_ffn_fused": (i32, [vp, i32, vp]),
         "shvk_ffn_fused_starved": (i32, [vp, i32, i32, vp]),
         "shvk_gdn_inproj_starved": (i32, [vp, i32, i32, vp]),
+        "shvk_expand_f16_tokens": (i32, [vp, i32, vp]),
         "shvk_split_tf32": (i32, [vp, C.c_longlong, i32, C.c_longlong, vp, C.c_longlong, i32, vp]),
         "shvk_cnn_stem": (i32, [vp, vp, vp, vp, vp, i32, vp]),
         "shvk_cnn_depthwise": (i32, [vp, vp, vp, vp] + [i32] * 9 + [vp]),
@@ -297,6 +299,17 @@ class CudaModel:
         out = np.empty(t.shape[0], np.float32) if out is None else out
         rc = self.L.shv_cuda_classify(self.m, t.ctypes.data, t.shape[0], out.ctypes.data)
         if rc:
+            raise RuntimeError(last_error(self.L))
+        return out
+
+    def classify_f16(self, tokens_f16, out=None):
+        """tokens [b,20,16,384] float16 (numpy, possibly a PinnedBuffer array) -> logits [b] float32
+        (shv_cuda_b200_classify_f16: half the bytes to upload)."""
+        t = np.ascontiguousarray(tokens_f16, dtype=np.float16)
+        if t.ndim != 4 or t.shape[1:] != (20, 16, 384):
+            raise ValueError("expected [b,20,16,384] float16 tokens")
+        out = np.empty(t.shape[0], np.float32) if out is None else out
+        if self.L.shv_cuda_b200_classify_f16(self.m, t.ctypes.data, t.shape[0], out.ctypes.data):
             raise RuntimeError(last_error(self.L))
         return out
 

@@ -88,6 +88,7 @@ struct Span {
     const float* first;
     int count;
     bool pinned;
+    bool half;          // the blocks hold fp16 tokens (12,288 bytes each): shv_cuda_b200_classify_f16
 };
 
 }  // namespace
@@ -173,6 +174,7 @@ struct Lane {
 struct Flight {                           // a batch between launch and retirement
     Lane* lane = nullptr;
     std::vector<shv_cuda_job*> jobs;
+    std::vector<std::pair<int, int>> half_runs;   // (first staging block, count) of the runs that arrived as fp16 tokens
     int windows = 0, crops = 0;
     bool launched = false;                // false: enqueueing threw; `error` says why
     std::string error;
@@ -416,6 +418,22 @@ private:
                 // host blocks: one copy per contiguous span; remember where each block lands on the device
                 const int first_block = blocks;
                 for (const Span& sp : j->spans) {
+                    if (sp.half) {
+                        // fp16 tokens: each block lands in the upper half of its fp32 staging block (one strided copy per
+                        // span) and is widened in place on the device before anything reads it
+                        uint8_t* dst16 = reinterpret_cast<uint8_t*>(dev.d_tok_stage + size_t(blocks) * kTokFloats) + kTokBytes / 2;
+                        const void* from16 = sp.first;
+                        if (!sp.pinned) {
+                            if (!l.stage_tokens) l.stage_tokens = pinned_array<float>(size_t(std::max(block_cap(), 1)) * kTokFloats, "pinned token staging");
+                            std::memcpy(l.stage_tokens + size_t(blocks) * kTokFloats, sp.first, size_t(sp.count) * (kTokBytes / 2));
+                            from16 = l.stage_tokens + size_t(blocks) * kTokFloats;
+                        }
+                        check(cudaMemcpy2DAsync(dst16, kTokBytes, from16, kTokBytes / 2, kTokBytes / 2, size_t(sp.count),
+                                                cudaMemcpyHostToDevice, copy_), "token upload");
+                        f.half_runs.emplace_back(blocks, sp.count);
+                        blocks += sp.count;
+                        continue;
+                    }
                     float* dst = dev.d_tok_stage + size_t(blocks) * kTokFloats;
                     const size_t bytes = size_t(sp.count) * kTokBytes;
                     const float* from = sp.first;
@@ -451,6 +469,8 @@ private:
             check(cudaEventRecord(l.uploaded, copy_), "event");
             check(cudaStreamWaitEvent(compute_, l.uploaded, 0), "event");
             check(cudaEventRecord(l.begin, compute_), "event");
+            for (const std::pair<int, int>& run : f.half_runs)
+                check(shvk_expand_f16_tokens(dev.d_tok_stage + size_t(run.first) * kTokFloats, run.second, compute_), "token widening");
             if (crops) engine->encode(l.index, crops, compute_);
             if (crop_stores) check(shvk_store_tokens(dev.d_tokens, l.d_crop_slot, pool, crops, compute_), "token slot store");
             if (block_stores) check(shvk_store_tokens(dev.d_tok_stage, l.d_block_slot, pool, blocks, compute_), "token slot store");
@@ -543,12 +563,13 @@ private:
 };
 
 // Host block pointers -> spans of consecutive memory, each marked pinned or pageable.
-void group_spans(shv_cuda_job& j, const std::vector<const float*>& blocks) {
+void group_spans(shv_cuda_job& j, const std::vector<const float*>& blocks, bool half = false) {
+    const size_t step = half ? kTokFloats / 2 : kTokFloats, block_bytes = half ? kTokBytes / 2 : kTokBytes;   // in floats; bytes
     size_t at = 0;
     while (at < blocks.size()) {
         size_t end = at + 1;
-        while (end < blocks.size() && blocks[end] == blocks[end - 1] + kTokFloats) ++end;
-        j.spans.push_back(Span{blocks[at], int(end - at), is_pinned(blocks[at], (end - at) * kTokBytes)});
+        while (end < blocks.size() && blocks[end] == blocks[end - 1] + step) ++end;
+        j.spans.push_back(Span{blocks[at], int(end - at), is_pinned(blocks[at], (end - at) * block_bytes), half});
         at = end;
     }
     j.n_host = int(blocks.size());
@@ -584,13 +605,13 @@ int settle_all(std::vector<shv_cuda_job*>& jobs) {
 // A synchronous call over `total` items as a train of requests of at most `piece` items, all submitted before the
 // first is waited for, so that the pipeline overlaps their uploads and kernels.  make(first, count, request) fills the
 // request; on a refused submit everything already queued is waited for and `poison` marks the outputs.
-template <typename Make, typename Poison>
-int run_in_pieces(shv_cuda_model* m, size_t total, size_t piece, Make make, Poison poison) {
+template <typename Make, typename Poison, typename Submit>
+int run_in_pieces(shv_cuda_model* m, size_t total, size_t piece, Make make, Poison poison, Submit submit) {
     std::vector<shv_cuda_job*> jobs;
     for (size_t first = 0; first < total; first += piece) {
         shv_cuda_request r{};
         make(first, std::min(piece, total - first), r);
-        shv_cuda_job* j = shv_cuda_submit(m, &r);
+        shv_cuda_job* j = submit(m, &r);
         if (!j) {
             const std::string why = tls_error;
             settle_all(jobs);
@@ -687,7 +708,8 @@ int shv_cuda_limits(const shv_cuda_model* m, int* max_frames, int* max_windows, 
     return 0;
 }
 
-shv_cuda_job* shv_cuda_submit(shv_cuda_model* m, const shv_cuda_request* r) {
+// half_tokens: the request's window_tokens point at fp16 token blocks (12,288 bytes each) instead of fp32 ones.
+static shv_cuda_job* submit_request(shv_cuda_model* m, const shv_cuda_request* r, bool half_tokens) {
     try {
         if (!m || !r) throw ApiError("null argument");
         Pipeline& p = *m->pipe;
@@ -731,7 +753,7 @@ shv_cuda_job* shv_cuda_submit(shv_cuda_model* m, const shv_cuda_request* r) {
             }
         }
         if (host.size() > size_t(o.max_host_tokens)) throw ApiError("request has more host token blocks than max_host_tokens");
-        group_spans(*job, host);
+        group_spans(*job, host, half_tokens);
         job->crops_pinned = is_pinned(r->frames, r->n_frames * kCropBytes);
         job->tokens_out_pinned = job->tokens_out && is_pinned(job->tokens_out, r->n_frames * kTokBytes);
         job->submitted = Clock::now();
@@ -743,6 +765,8 @@ shv_cuda_job* shv_cuda_submit(shv_cuda_model* m, const shv_cuda_request* r) {
         return nullptr;
     }
 }
+
+shv_cuda_job* shv_cuda_submit(shv_cuda_model* m, const shv_cuda_request* r) { return submit_request(m, r, false); }
 
 int shv_cuda_job_status(const shv_cuda_job* j) {
     if (!j) return -1;
@@ -815,7 +839,7 @@ int shv_cuda_encode_frames(shv_cuda_model* m, const uint8_t* rgb, size_t n, floa
             r.n_frames = count;
             r.tokens_out = tokens + first * kTokFloats;
         },
-        [&] { std::fill(tokens, tokens + n * kTokFloats, kUnavailable); });
+        [&] { std::fill(tokens, tokens + n * kTokFloats, kUnavailable); }, shv_cuda_submit);
 }
 
 int shv_cuda_predict(shv_cuda_model* m, const uint8_t* clips, size_t b, float* logits) {
@@ -840,10 +864,12 @@ int shv_cuda_predict(shv_cuda_model* m, const uint8_t* clips, size_t b, float* l
             r.window_frames = own_frames.data();
             r.logits_out = logits + first;
         },
-        [&] { std::fill(logits, logits + b, kUnavailable); });
+        [&] { std::fill(logits, logits + b, kUnavailable); }, shv_cuda_submit);
 }
 
-int shv_cuda_classify(shv_cuda_model* m, const float* tokens, size_t b, float* logits) {
+// shv_cuda_classify over fp32 tokens (block_floats = 6144) or, for the extension below, fp16 tokens (block_floats = 3072:
+// a block of 6144 halves measured in floats).
+static int classify_blocks(shv_cuda_model* m, const float* tokens, size_t block_floats, bool half_tokens, size_t b, float* logits) {
     if (!m || (b && (!tokens || !logits))) {
         tls_error = "null argument";
         return -1;
@@ -864,15 +890,28 @@ int shv_cuda_classify(shv_cuda_model* m, const float* tokens, size_t b, float* l
         [&](size_t first, size_t count, shv_cuda_request& r) {
             ptrs.emplace_back(count * kWin);
             std::vector<const float*>& list = ptrs.back();
-            for (size_t e = 0; e < list.size(); ++e) list[e] = tokens + (first * kWin + e) * kTokFloats;
+            for (size_t e = 0; e < list.size(); ++e) list[e] = tokens + (first * kWin + e) * block_floats;
             r.n_windows = count;
             r.window_tokens = list.data();
             r.logits_out = logits + first;
         },
-        [&] { std::fill(logits, logits + b, kUnavailable); });
+        [&] { std::fill(logits, logits + b, kUnavailable); },
+        [&](shv_cuda_model* mm, const shv_cuda_request* rr) { return submit_request(mm, rr, half_tokens); });
+}
+
+int shv_cuda_classify(shv_cuda_model* m, const float* tokens, size_t b, float* logits) {
+    return classify_blocks(m, tokens, kTokFloats, false, b, logits);
 }
 
 // ---------------------------------------------------------------- extensions (include/shv_cuda_b200.h)
+int shv_cuda_b200_classify_f16(shv_cuda_model* m, const uint16_t* tokens_f16, size_t b, float* logits) {
+    if (tokens_f16 && (reinterpret_cast<uintptr_t>(tokens_f16) & 15)) {
+        tls_error = "fp16 tokens must be 16-byte aligned";
+        return -1;
+    }
+    return classify_blocks(m, reinterpret_cast<const float*>(tokens_f16), kTokFloats / 2, true, b, logits);
+}
+
 int shv_cuda_b200_upload_tokens(shv_cuda_model* m, const float* tokens, size_t n, const int32_t* slots) {
     try {
         if (!m || (n && (!tokens || !slots))) throw ApiError("null argument");

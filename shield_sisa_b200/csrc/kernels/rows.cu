@@ -127,8 +127,30 @@ split_tf32_kernel(const float* __restrict__ in, long long ld_in, int k4, long lo
     }
 }
 
+// fp16 token blocks that were uploaded into the upper halves of their fp32 staging blocks, widened in place: one CTA per
+// block of 16 x 384 tokens, every thread reads its eight halves before anyone writes (the floats of the first half of
+// the block land on bytes other threads still have to read).
+__global__ void __launch_bounds__(768)
+expand_f16_tokens_kernel(float* __restrict__ stage) {
+    float* blk = stage + (long long)blockIdx.x * (16 * kD);
+    const uint4 u = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(blk) + 16 * kD * 2)[threadIdx.x];
+    __syncthreads();
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+    const float2 a = __half22float2(h[0]), b = __half22float2(h[1]), c = __half22float2(h[2]), d = __half22float2(h[3]);
+    float4* out = reinterpret_cast<float4*>(blk) + 2 * threadIdx.x;
+    out[0] = make_float4(a.x, a.y, b.x, b.y);
+    out[1] = make_float4(c.x, c.y, d.x, d.y);
+}
+
 }  // namespace
 }  // namespace sb
+
+extern "C" int shvk_expand_f16_tokens(float* stage, int blocks, void* stream) {
+    if (blocks <= 0) return 0;
+    if (!stage || (reinterpret_cast<uintptr_t>(stage) & 15)) return int(cudaErrorInvalidValue);
+    sb::expand_f16_tokens_kernel<<<unsigned(blocks), 768, 0, cudaStream_t(stream)>>>(stage);
+    return int(cudaGetLastError());
+}
 
 extern "C" int shvk_split_tf32(const float* in, long long ld_in, int K, long long rows, float* out, long long ld_out, int layout,
                                void* stream) {

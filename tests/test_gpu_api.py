@@ -142,6 +142,31 @@ def test_pinned_and_pageable_tokens_agree(model):
     np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_fp16_tokens_equal_fp32_tokens_of_the_same_values(mode, weight_files):
+    """shv_cuda_b200_classify_f16: tokens handed over as fp16 are widened on the device before anything reads them, so
+    the logits are bitwise those of shv_cuda_classify on the same (fp16-representable) values as fp32, from pageable
+    and from pinned memory, for a call that is cut into several requests."""
+    path, _ = weight_files("W3", 1)
+    tok16 = W.synth_tokens(37, 31).astype(np.float16)
+    with binding.CudaModel(path, mode, max_windows=16, max_host_tokens=320) as m:
+        want = m.classify(tok16.astype(np.float32))
+        got = m.classify_f16(tok16)
+        np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+        pin = binding.PinnedBuffer(m.L, tok16.shape, np.float16)
+        pin.array[...] = tok16
+        got_pin = m.classify_f16(pin.array)
+        pin.free()
+        np.testing.assert_array_equal(got_pin.view(np.uint32), want.view(np.uint32))
+        # against the unrounded embeddings: what fp16 rounding of the inputs costs.  In fp32 mode that is the rounding
+        # itself; in bf16 mode any perturbation of the inputs moves the bf16 roundings inside the stack, so the logits
+        # move by about the mode's own error
+        full = m.classify(W.synth_tokens(37, 31))
+        change = np.abs(got - full).max() / max(1.0, np.abs(full).max())
+        print(f"fp16 host tokens, {mode} mode: max logit change {change:.2e} relative")
+        assert change < (2e-3 if mode == "fp32" else 4e-2)
+
+
 def test_concurrent_callers(model):
     tok = W.synth_tokens(6, 26)
     want = model.classify(tok)
