@@ -72,11 +72,19 @@ struct InprojParams {
     int probe;       // timing probes of a development build (-DSHVK_DEV_PROBES, SHVK_INPROJ_PROBE): 1 no global stores,
                      // 2 no activation arithmetic, 4 no tensor-memory loads, 8 no MMA.  Constant 0 in the shipped libraries.
 };
+// The probe bits travel in the kernel parameters (constant bank) and, to the tile functions, in bits 8+ of `flags`: a
+// word in global memory would add a load in front of every tile and change the timings it is meant to explain.
 #ifdef SHVK_DEV_PROBES
-__device__ int g_inproj_probe = 0;
-#define INPROJ_PROBE(bit) (g_inproj_probe & (bit))
+__device__ unsigned long long g_prof[11][8];
+#define PROF_T() clock64()
+#define PROF_ADD(slot, dt) do { if ((threadIdx.x & 31) == 0) prof_s[(threadIdx.x >> 5) * 8 + (slot)] += (unsigned long long)(dt); } while (0)
+#define INPROJ_PROBE(bit) (probe_bits & (bit))
+#define INPROJ_TILE_FLAGS(f) ((f) | (p.probe << 8))
 #else
+#define PROF_T() 0ll
+#define PROF_ADD(slot, dt) do { } while (0)
 #define INPROJ_PROBE(bit) 0
+#define INPROJ_TILE_FLAGS(f) (f)
 #endif
 
 // x * sigmoid(x) = 0.5 x (1 + tanh(x / 2)) with the hardware tanh: absolute error ~5e-4 |x|, below the bf16 rounding
@@ -116,6 +124,7 @@ struct ChanConst {            // what the epilogue thread knows about its channe
     float rate, dtb;          // KIND_GATES, decay rows: -exp(A_log), dt_bias
     bool is_beta, active;     // KIND_GATES: beta row; lane has a channel at all
     int half0;                // byte offset (0 or 16) of tokens 0-7 within the channel's 32-byte row of a chunk block
+    int probe;                // probe bits of a development build, else 0
 };
 
 // Sixteen accumulator columns = one chunk of 16 tokens of one channel: activation, packing, and the channel's 32-byte
@@ -125,18 +134,19 @@ struct ChanConst {            // what the epilogue thread knows about its channe
 template <int KIND>
 __device__ __forceinline__ void emit_chunk(const uint32_t (&in)[16], uint8_t* row, const ChanConst& cc, int nvalid,
                                            float& x1, float& x2, float& x3) {
+    [[maybe_unused]] const int probe_bits = cc.probe;
     if (KIND == KIND_GATES) {
         uint32_t v[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
+            // beta rows: 1 / (1 + exp(-raw)); decay rows: rate * softplus(raw + dt_bias).  Both from one exponential and
+            // without a branch: the rows of the two kinds sit in one warp, and a divergent branch per token would run
+            // the sixteen tokens one after the other.
             const float raw = __uint_as_float(in[j]);
-            float o;
-            if (cc.is_beta) {
-                o = __fdividef(1.0f, 1.0f + __expf(-raw));
-            } else {
-                const float ax = raw + cc.dtb;
-                o = cc.rate * (ax > 15.0f ? ax : __logf(1.0f + __expf(ax)));
-            }
+            const float ax = cc.is_beta ? -raw : raw + cc.dtb;
+            const float e1 = 1.0f + __expf(ax);
+            const float sp = cc.rate * (ax > 15.0f ? ax : __logf(e1));
+            const float o = cc.is_beta ? __fdividef(1.0f, e1) : sp;
             v[j] = __float_as_uint(o);
         }
         if (nvalid < 16) {
@@ -194,11 +204,12 @@ __device__ __forceinline__ void emit_chunk(const uint32_t (&in)[16], uint8_t* ro
 // warps spent more cycles waiting for instructions than issuing them).
 template <int KIND>
 __device__ __noinline__ void emit_tile(uint32_t taddr, uint8_t* dst, float4 cw, float bias, float rate, float dtb, int flags,
-                                       int tok0, int ncols, bool has_hist) {
+                                       int tok0, int ncols, bool has_hist, [[maybe_unused]] unsigned long long* prof_s) {
     // the channel constants travel as scalars (registers), not as a struct behind a pointer (local memory)
     ChanConst cc;
     cc.w = cw; cc.bias = bias; cc.rate = rate; cc.dtb = dtb;
-    cc.is_beta = flags & 1; cc.active = flags & 2; cc.half0 = flags & 16;
+    cc.is_beta = flags & 1; cc.active = flags & 2; cc.half0 = flags & 16; cc.probe = flags >> 8;
+    [[maybe_unused]] const int probe_bits = cc.probe;
     uint32_t ra[16], rb[16];
     float x1 = 0.0f, x2 = 0.0f, x3 = 0.0f;
 #ifdef SHVK_DEV_PROBES
@@ -221,12 +232,12 @@ __device__ __noinline__ void emit_tile(uint32_t taddr, uint8_t* dst, float4 cw, 
     else tc_ld16(taddr, ra);
 #pragma unroll 1
     for (int c = 0; c < ncols; c += 32) {
-        tc_wait_ld();
+        { [[maybe_unused]] const long long ta = PROF_T(); tc_wait_ld(); PROF_ADD(c == 0 ? 1 : 2, PROF_T() - ta); }
         if (c == 0 && has_hist) { x1 = __uint_as_float(rb[15]); x2 = __uint_as_float(rb[14]); x3 = __uint_as_float(rb[13]); }
         if (c + 16 < ncols) tc_ld16(taddr + uint32_t(c + 16), rb);
         emit_chunk<KIND>(ra, dst + (long long)(c >> 4) * pt::BLOCK_BYTES, cc, kTok - (tok0 + c), x1, x2, x3);
         if (c + 16 >= ncols) break;
-        tc_wait_ld();
+        { [[maybe_unused]] const long long ta = PROF_T(); tc_wait_ld(); PROF_ADD(2, PROF_T() - ta); }
         if (c + 32 < ncols) tc_ld16(taddr + uint32_t(c + 32), ra);
         emit_chunk<KIND>(rb, dst + (long long)((c >> 4) + 1) * pt::BLOCK_BYTES, cc, kTok - (tok0 + c + 16), x1, x2, x3);
     }
@@ -278,6 +289,13 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
     const uint32_t bars = w_base + W_STAGES * W_STAGE_BYTES;     // wfull[S], wempty[S], accf[2], acce[2], xfull, xempty
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
+#ifdef SHVK_DEV_PROBES
+    __shared__ unsigned long long prof_arr[11 * 8];
+    unsigned long long* prof_s = prof_arr;
+    if (threadIdx.x < 88) prof_arr[threadIdx.x] = 0;
+#else
+    unsigned long long* prof_s = nullptr;
+#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     auto wfull_bar = [&](int s) { return bars + 8u * s; };
     auto wempty_bar = [&](int s) { return bars + 8u * (W_STAGES + s); };
@@ -303,6 +321,7 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abortp = &abort_flag;
+    [[maybe_unused]] const long long tk0 = PROF_T();
     const long long items = 2ll * p.B;                           // item = 2 * clip + token tile
 
     if (warp == 0) {
@@ -314,7 +333,9 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
             for (long long item = blockIdx.x; ok && item < items; item += gridDim.x) {
                 for (int m = 0; ok && m < M_TILES; ++m) {
                     for (int kb = 0; kb < KBLOCKS; ++kb) {
+                        [[maybe_unused]] const long long tw0 = PROF_T();
                         if (!mbar_wait(wempty_bar(stage), phase ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
+                        PROF_ADD(0, PROF_T() - tw0);
                         if (p.starve && item == (long long)blockIdx.x && m == 0 && kb == 0) {   // test launch: this stage never fills
                             if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
                             continue;
@@ -344,14 +365,21 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0, n = 0;
             bool ok = true;
+            [[maybe_unused]] const int probe_bits = p.probe;
             for (long long item = blockIdx.x; ok && item < items; item += gridDim.x, ++n) {
-                if (!mbar_wait(xfull_bar, n & 1u, abortp, p.spin_limit)) { ok = false; break; }
+                { [[maybe_unused]] const long long tm2 = PROF_T();
+                  if (!mbar_wait(xfull_bar, n & 1u, abortp, p.spin_limit)) { ok = false; break; }
+                  PROF_ADD(2, PROF_T() - tm2); }
                 for (int m = 0; ok && m < M_TILES; ++m) {
+                    [[maybe_unused]] const long long tm0 = PROF_T();
                     if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abortp, p.spin_limit)) { ok = false; break; }
+                    PROF_ADD(0, PROF_T() - tm0);
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + uint32_t(acc * 256);
                     for (int kb = 0; kb < KBLOCKS; ++kb) {
+                        [[maybe_unused]] const long long tm1 = PROF_T();
                         if (!mbar_wait(wfull_bar(stage), phase, abortp, p.spin_limit)) { ok = false; break; }
+                        PROF_ADD(1, PROF_T() - tm1);
                         tc_fence_after();
                         const uint64_t da = smem_desc_sw128(w_base + stage * W_STAGE_BYTES), db = smem_desc_sw128(xn_base + kb * XN_KB_BYTES);
 #pragma unroll
@@ -387,15 +415,19 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
             ChanSite cur = chan_site(p, 0, r);
             for (int m = 0; m < M_TILES; ++m) {
                 const ChanSite nxt = chan_site(p, m + 1 < M_TILES ? m + 1 : m, r);   // its loads fly during this tile's work
+                [[maybe_unused]] const long long tp0 = PROF_T();
                 if (!mbar_wait(accf_bar(acc), acc_phase, abortp, p.spin_limit)) { ok = false; break; }
+                [[maybe_unused]] const long long tp1 = PROF_T();
+                PROF_ADD(0, tp1 - tp0);
                 tc_fence_after();
                 const uint32_t tacc = tlane + uint32_t(acc * 256);
                 uint8_t* dst = p.pt + ((long long)clip * kHeads + cur.head) * pt::HEAD_BYTES + cur.section + (long long)chunk0 * pt::BLOCK_BYTES;
                 const int type = m % 3;
-                if (m == M_TILES - 1) { if (quad == 0) emit_tile<KIND_GATES>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, false); }
-                else if (type == 2) emit_tile<KIND_SILU>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, false);
-                else if (type == 1 || p.qk_f16) emit_tile<KIND_CONV_F16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, has_hist);
-                else emit_tile<KIND_CONV_BF16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, cur.flags, tok0, ncols, has_hist);
+                if (m == M_TILES - 1) { if (quad == 0) emit_tile<KIND_GATES>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, INPROJ_TILE_FLAGS(cur.flags), tok0, ncols, false, prof_s); }
+                else if (type == 2) emit_tile<KIND_SILU>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, INPROJ_TILE_FLAGS(cur.flags), tok0, ncols, false, prof_s);
+                else if (type == 1 || p.qk_f16) emit_tile<KIND_CONV_F16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, INPROJ_TILE_FLAGS(cur.flags), tok0, ncols, has_hist, prof_s);
+                else emit_tile<KIND_CONV_BF16>(tacc + col0, dst, cur.w, cur.bias, cur.rate, cur.dtb, INPROJ_TILE_FLAGS(cur.flags), tok0, ncols, has_hist, prof_s);
+                PROF_ADD(3, PROF_T() - tp1);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acce_bar(acc));
@@ -406,7 +438,11 @@ gdn_inproj_kernel(const __grid_constant__ InprojMaps maps, const InprojParams p,
         if (!ok && lane == 0 && !*abortp) { *abortp = 1; atomicCAS(status, 0, 3); }
     }
 
+    PROF_ADD(7, PROF_T() - tk0);
     __syncthreads();
+#ifdef SHVK_DEV_PROBES
+    if (threadIdx.x < 88 && blockIdx.x == 5) atomicAdd(&g_prof[threadIdx.x >> 3][threadIdx.x & 7], prof_arr[threadIdx.x]);
+#endif
     if (abort_flag) {
         // A role gave up: copies already issued may still land in this CTA's shared memory.  Give them time (bounded)
         // before the block retires; nothing here waits on another thread.
@@ -519,10 +555,19 @@ static int inproj_launch(const void* host_plan, int B, void* stream, int starve,
 #ifdef SHVK_DEV_PROBES
     {
         const char* e = getenv("SHVK_INPROJ_PROBE");
-        const int bits = e ? atoi(e) : 0;
-        cudaMemcpyToSymbolAsync(g_inproj_probe, &bits, sizeof(int), 0, cudaMemcpyHostToDevice, cudaStream_t(stream));
+        p.probe = e ? atoi(e) : 0;
     }
 #endif
     gdn_inproj_kernel<<<grid, NTHREADS, SMEM_BYTES, cudaStream_t(stream)>>>(maps, p, status);
     return int(cudaGetLastError());
 }
+
+#ifdef SHVK_DEV_PROBES
+extern "C" __attribute__((visibility("default"))) int shvk_dev_inproj_prof(unsigned long long* out) {
+    unsigned long long zero[88] = {0};
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, sb::g_prof, sizeof(zero));
+    cudaMemcpyToSymbol(sb::g_prof, zero, sizeof(zero));
+    return 0;
+}
+#endif
