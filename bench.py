@@ -56,7 +56,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # modes that are summarised under profiles/ (traffic grows in proportion to the clips of a launch: every clip's tiles
 # are fetched and written once); scaled to the bench's B for the `traffic` key
 NCU_TRAFFIC_PER_CLIP = {"gdn_scan": (801014016 + 231972608) / 512, "gdn_inproj": (128415488 + 744627712) / 512}
-PT_BYTES_PER_CLIP = 6 * 21 * 12416      # chunk-blocked bf16 operand tiles between the fused in-projection and the scan
+PT_TILE_BYTES_PER_CLIP = 6 * 21 * 12416  # chunk-blocked 16-bit operand tiles and gates the fused in-projection writes
+PT_QK_BYTES_PER_CLIP = 6 * 21 * (4096 + 128)    # of which the chunk preparation reads q^T, k^T, decays and betas
+PT_EXT_BYTES_PER_CLIP = 6 * 21 * 1280    # and what it adds to every chunk block (T2, M, decays, norms)
+PT_BYTES_PER_CLIP = PT_TILE_BYTES_PER_CLIP + PT_EXT_BYTES_PER_CLIP             # what the scan reads
 
 
 def peaks():
@@ -83,7 +86,8 @@ def algorithmic_work(name: str, storage_bytes: int):
         "assemble_norm": (20 * 6144 * 4 + h + xn, 0),
         "rmsnorm": (h + xn, 0),
         "gemm.in_proj": (xn + p_out, 2 * NTOK * 2316 * 384),                       # fp32 mode
-        "gdn_inproj": (xn + PT_BYTES_PER_CLIP, 2 * NTOK * 2316 * 384),             # 16-bit modes: projection + conv + SiLU + gates
+        "gdn_inproj": (xn + PT_TILE_BYTES_PER_CLIP, 2 * NTOK * 2316 * 384),        # 16-bit modes: projection + conv + SiLU + gates
+        "gdn_prep": (PT_QK_BYTES_PER_CLIP + PT_EXT_BYTES_PER_CLIP, 0),            # 16-bit modes: per-chunk Gram products and inverse
         "gdn_scan": ((p_out if s == 4 else PT_BYTES_PER_CLIP) + on, 0),
         "gemm.o_proj": (on + 2 * h, 2 * NTOK * 384 * 768),
         "ffn_fused": (xn + 2 * h, 2 * NTOK * 1920 * 384 + 2 * NTOK * 384 * 960),    # 16-bit modes: up + SwiGLU + down + residual

@@ -111,8 +111,8 @@ int shvk_status_clear_async(void* stream);
 /* GDN in-projection of the 16-bit modes, fused with the steps between projection and recurrence (causal conv k = 4 +
  * bias + SiLU on q, k, v; SiLU on the output gate; log decay and beta).  Computes W' xn^T on the tensor cores with the
  * channels on the MMA rows and writes bf16 operand tiles in chunk blocks of 16 tokens ("PT": per clip, head and chunk
- * q^T [64][16], k^T [64][16], v^T [128][16], gate^T [128][16], log decay [16], beta [16]; shvk_gdn_pt_bytes(B) bytes
- * for B clips), which shvk_gdn_scan_t consumes.  xn: [max_rows][384] in ab_dtype (bf16 or fp16), rows of clip c at
+ * q^T [64][16], k^T [64][16], v^T [128][16], gate^T [128][16], log decay [16], beta [16], and room for what
+ * shvk_gdn_chunk_prep adds; shvk_gdn_pt_bytes(B) bytes for B clips), which shvk_gdn_scan_t consumes.  xn: [max_rows][384] in ab_dtype (bf16 or fp16), rows of clip c at
  * 321 c; w_perm: [shvk_gdn_inproj_rows()][384] in ab_dtype = the rows of the reference's fused in-projection weight
  * [q | k | v | gate | a | b] (engine/cuda/model.cpp:109-115) in the order shvk_gdn_inproj_row_order gives (source row
  * per row of w_perm, -1 = a zero row); conv_w [1536][4], conv_b [1536], a_log [6], dt_bias [6] fp32 as in the
@@ -128,8 +128,13 @@ int shvk_gdn_inproj(const void* host_plan, int B, void* stream);
  * tile, the MMA role's bounded wait runs out after `polls` polls, the CTAs take their abort path and return with the
  * status word of the tensor-core GEMMs set.  Outputs are left partly written.  Nothing faults or spins without bound. */
 int shvk_gdn_inproj_starved(const void* host_plan, int B, int polls, void* stream);
-/* Gated delta rule + gated RMSNorm of one mixer over B clips from the PT tiles: 16-token chunks in WY form on the
- * tensor cores, the head's 64 x 128 state in accumulator fragments for the whole sequence.  on: [B*321][768] in
+/* Completes the chunk blocks of B clips in place with what the delta rule needs per chunk and that does not depend on
+ * the recurrent state: the decay-masked Gram products, the key and query norms and the 16 x 16 triangular inverse of
+ * the WY form (written to the last 1,280 bytes of every block; one warp per block, all blocks at once).  op_dtype: the
+ * type of the q^T / k^T tiles (bf16 or fp16).  Must run between shvk_gdn_inproj and shvk_gdn_scan_t. */
+int shvk_gdn_chunk_prep(void* pt, int op_dtype, int B, void* stream);
+/* Gated delta rule + gated RMSNorm of one mixer over B clips from the completed PT tiles: 16-token chunks in WY form on
+ * the tensor cores, the head's 64 x 128 state in accumulator fragments for the whole sequence.  on: [B*321][768] in
  * on_dtype (bf16 or fp16).  Replaces launch_delta + launch_gated_norm (engine/cuda/seq.cu:107-214,364-371). */
 int shvk_gdn_scan_t(const void* pt, const float* o_norm_w, void* on, int on_dtype, int B, void* stream);
 /* Test launch of the same kernel: no CTA ever issues the copy of its first chunk, so the wait for it runs out after

@@ -149,6 +149,7 @@ def load_library(experimental: bool = True) -> C.CDLL:
         "shvk_gdn_pt_bytes": (sz, [i32]),
         "shvk_gdn_inproj_plan": (i32, [vp, C.c_longlong, vp, vp, vp, vp, vp, vp, i32, vp]),
         "shvk_gdn_inproj": (i32, [vp, i32, vp]),
+        "shvk_gdn_chunk_prep": (i32, [vp, i32, i32, vp]),
         "shvk_gdn_scan_t": (i32, [vp, vp, vp, i32, i32, vp]),
         "shvk_gdn_scan_t_starved": (i32, [vp, vp, vp, i32, i32, i32, vp]),
         "shvk_gdn_scan": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp]),

@@ -214,7 +214,7 @@ public:
     }
     // 16-bit modes: 21 kernels.  Exact tier: 23 (its feed-forward blocks are two GEMMs each) + a launch that splits the
     // A operand of the five GEMMs that do not read a normalised row (three o-projections, two FFN down projections)
-    int launches_per_classify() const override { return prec_ == Precision::FP32 ? 28 : 21; }
+    int launches_per_classify() const override { return prec_ == Precision::FP32 ? 28 : 24; }
 
     // One eager classify / encode with an event after every launch; returns (kernel name, milliseconds) per launch.
     std::vector<std::pair<std::string, float>> profile(int slot, int B, cudaStream_t s) override {
@@ -647,6 +647,9 @@ private:
                     // projection + conv + SiLU + gates in one tensor-core kernel, bf16 operand tiles for the scan
                     launch_ok(shvk_gdn_inproj(inproj_plan_[st], B, s), "gdn in-projection");
                     mark("gdn_inproj", s);
+                    // what the delta rule needs per chunk and that does not depend on the state, for all chunks at once
+                    launch_ok(shvk_gdn_chunk_prep(P_, dt_, B, s), "gdn chunk preparation");
+                    mark("gdn_prep", s);
                     if (starve == 2 && st == 0 && r == 0)
                         launch_ok(shvk_gdn_scan_t_starved(P_, g.o_norm_w, on_, dt_, B, 2048, s), "gdn scan (starved test launch)");
                     else

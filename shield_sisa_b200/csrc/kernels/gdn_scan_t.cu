@@ -46,32 +46,45 @@ namespace {
 
 constexpr int TC = pt::CHUNK, NCHUNK = pt::NCHUNK, NSLOT = 3;
 constexpr uint32_t WAIT_POLLS = 1u << 22;    // about a quarter second
-constexpr int KT_PITCH = 24;                 // bf16 per row of the T2 and M tiles (48 bytes)
 constexpr int OT_PITCH = kDV + 4;            // floats per token row of the o tile: the fragment stores of a warp (eight value rows
                                              // x four token pairs) then fall into 32 different banks
 
 __device__ int g_scan_t_status = 0;
 
+struct BlockExt {                            // what the preparation kernel adds to a chunk block
+    uint16_t t2[TC][TC];                     // (I + L)^-1 diag(beta), operand type
+    uint16_t mq[TC][TC];                     // decay-masked Q K^T, operand type
+    float eg[TC], dj[TC];                    // exp(c_i), exp(c_last - c_i)
+    float ik[TC], iq[TC];                    // 1/|k|, 0.125/|q|
+};
 struct Block {                               // one chunk block as it lies in global memory
     uint16_t qt[kDK][TC], kt[kDK][TC];       // operand type of the mode
     uint16_t vt[kDV][TC], gt[kDV][TC];       // fp16
     float dec[TC], beta[TC];
+    BlockExt ext;
 };
-static_assert(sizeof(Block) == pt::BLOCK_BYTES, "chunk block layout");
+static_assert(sizeof(BlockExt) == pt::EXT_BYTES && offsetof(Block, ext) == pt::EXT_OFF && sizeof(Block) == pt::BLOCK_BYTES,
+              "chunk block layout");
 
 struct Smem {
     Block blk[NSLOT];                        // ring: chunk c lands in blk[c % 3]
-    float ot[TC][OT_PITCH];                  // o * gate of the chunk, [token][value]; read back by the next chunk's norm
-    float lf[TC][TC];                        // L
-    uint16_t t2[TC][KT_PITCH];               // (I + L)^-1 diag(beta), operand type
-    uint16_t mq[TC][KT_PITCH];               // decay-masked Q K^T, operand type
-    float ssq[TC][4];                        // per token: each warp's share of sum(o^2) over its 32 value columns
-    float cw[2][TC];                         // c_i as warps 0 and 1 each computed it (no barrier between them)
-    float iq[TC], ik[TC];                    // 0.125/|q|, 1/|k|
-    float eg[TC], dj[TC];                    // exp(c_i), exp(c_last - c_i)
+    float ot[2][TC][OT_PITCH];               // o * gate of chunk c in ot[c % 2], [token][value]; read back by the next chunk's norm
+    float ssq[2][TC][4];                     // per token: each warp's share of sum(o^2) over its 32 value columns
     unsigned long long full[NSLOT];          // mbarriers: chunk block in ring slot i landed
 };
 constexpr int SMEM_BYTES = int(sizeof(Smem)) + 128;
+
+struct PrepWarp {                            // the preparation kernel's shared memory, per warp = per chunk
+    uint16_t qt[kDK][TC], kt[kDK][TC];
+    float dec[TC], beta[TC];
+    float lf[TC][TC];                        // L
+    float cw[TC];                            // inclusive cumulative log decay
+    BlockExt out;                            // staged, then copied to the block in 16-byte pieces
+    float pad[16];                           // size a multiple of 128
+};
+constexpr int PREP_WARPS = 8;
+static_assert(sizeof(PrepWarp) % 128 == 0 && offsetof(PrepWarp, out) % 16 == 0 && offsetof(PrepWarp, dec) == 4096, "prep layout");
+constexpr int PREP_SMEM_BYTES = PREP_WARPS * int(sizeof(PrepWarp)) + 128;
 
 // Operand type of the products: the mode's 16-bit type (bf16 keeps fp32's range, fp16 has three more mantissa bits).
 // The v^T and gate^T tiles are fp16 in both modes: they are only read element-wise and combined in fp32.
@@ -107,6 +120,133 @@ __device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t (&r)[4]) {
 __device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+
+
+// ---------------------------------------------------------------------------------------------- chunk preparation
+// The part of a chunk's work that does not depend on the recurrent state, for every chunk of the batch at once: one
+// warp per chunk block reads q^T, k^T, log decays and betas, forms the Gram products K K^T, Q K^T and diag(Q Q^T) on
+// the tensor cores, the key and query norms from their diagonals, the decay masks, the 16 x 16 triangular inverse
+// (forward substitution, fp32, one column per lane) and writes T2, M, exp(c), exp(c_last - c) and the norms into the
+// block's last 1,280 bytes.  Inside the scan this chain (about half of a chunk's critical path, most of it one warp's
+// dependent instructions while the other three waited) ran 21 times in sequence per (clip, head); here half a million
+// chunks are independent and 32 warps per SM hide its latency.
+template <typename T>
+__global__ void __launch_bounds__(PREP_WARPS * 32)
+gdn_chunk_prep_kernel(uint8_t* __restrict__ ptb, long long nblocks) {
+    extern __shared__ uint8_t prep_smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long blk = (long long)blockIdx.x * PREP_WARPS + warp;
+    if (blk >= nblocks) return;                           // whole warps leave; the kernel has no CTA barrier
+    PrepWarp& w = reinterpret_cast<PrepWarp*>((reinterpret_cast<uintptr_t>(prep_smem_raw) + 127) & ~uintptr_t(127))[warp];
+    uint8_t* gb = ptb + blk * pt::BLOCK_BYTES;
+    {
+        const uint4* g4 = reinterpret_cast<const uint4*>(gb);                  // q^T | k^T: 4 KB from the start of the block
+        uint4* s4 = reinterpret_cast<uint4*>(&w.qt[0][0]);
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = g4[lane + 32 * i];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s4[lane + 32 * i] = v[i];
+        if (lane < 8) reinterpret_cast<uint4*>(w.dec)[lane] = reinterpret_cast<const uint4*>(gb + pt::DEC_OFF)[lane];   // dec | beta
+    }
+    __syncwarp();
+    const int g = lane >> 2, t = lane & 3;                // mma fragment coordinates
+    const int lm = lane >> 3, lr = lane & 7;              // ldmatrix lane roles: matrix lane / 8, row lane % 8
+    const uint32_t kt_s = tma::smem_addr(&w.kt[0][0]), qt_s = tma::smem_addr(&w.qt[0][0]);
+    // transposed fragment of keys 16p .. 16p+15 x all 16 tokens (in rows 4-7 of every eight the two token halves of a
+    // row trade places: gdn_pt_layout.cuh)
+    const uint32_t tr_off = uint32_t(((lm >> 1) * 8 + lr) * (TC * 2) + ((lm & 1) ^ ((lr >> 2) & 1)) * 16);
+    // inclusive prefix sum of the log decays
+    float c = w.dec[lane & (TC - 1)];
+#pragma unroll
+    for (int o = 1; o < TC; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, c, o);
+        if ((lane & (TC - 1)) >= o) c += up;
+    }
+    const float last = __shfl_sync(0xffffffffu, c, TC - 1);
+    if (lane < TC) {
+        w.cw[lane] = c;
+        w.out.eg[lane] = __expf(c);
+        w.out.dj[lane] = __expf(last - c);
+    }
+    // Gram products over the 64 keys: K K^T, Q K^T and the diagonal of Q Q^T
+    float ak[2][4], aq[2][4], dq[2][4];
+#pragma unroll
+    for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { ak[ni][e] = 0.0f; aq[ni][e] = 0.0f; dq[ni][e] = 0.0f; }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        uint32_t kf[4], qf[4];
+        ldsm4t(kt_s + uint32_t(p * 16 * TC * 2) + tr_off, kf);
+        ldsm4t(qt_s + uint32_t(p * 16 * TC * 2) + tr_off, qf);
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni) {
+            mma16816<T>(ak[ni], kf, kf[ni], kf[ni + 2]);
+            mma16816<T>(aq[ni], qf, kf[ni], kf[ni + 2]);
+            mma16816<T>(dq[ni], qf, qf[ni], qf[ni + 2]);
+        }
+    }
+    // diagonal entries: row g sits in tile 0 at column 2t + e == g, row g + 8 in tile 1 at the same lane / slot
+    if (t == (g >> 1)) {
+        const bool odd = g & 1;                           // selects, not a runtime index: the fragments stay in registers
+        w.out.ik[g] = rsqrtf((odd ? ak[0][1] : ak[0][0]) + 1e-6f);
+        w.out.ik[g + 8] = rsqrtf((odd ? ak[1][3] : ak[1][2]) + 1e-6f);
+        w.out.iq[g] = rsqrtf((odd ? dq[0][1] : dq[0][0]) + 1e-6f) * 0.125f;
+        w.out.iq[g + 8] = rsqrtf((odd ? dq[1][3] : dq[1][2]) + 1e-6f) * 0.125f;
+    }
+    __syncwarp();
+    // a*[ni][0,1]: row i = g, columns j = 8 ni + 2t, + 1;  a*[ni][2,3]: row i = g + 8
+#pragma unroll
+    for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = g + (e >> 1) * 8, j = 8 * ni + 2 * t + (e & 1);
+            const float ci = w.cw[i], cj = w.cw[j];
+            // L_ij carries both key norms; in M the key norm of column j is applied to U in the scan's O product
+            const float decl = __expf(j < i ? ci - cj : 0.0f), decm = __expf(j <= i ? ci - cj : 0.0f);
+            const float fl = w.beta[i] * w.out.ik[i] * w.out.ik[j];
+            ak[ni][e] = j < i ? decl * ak[ni][e] * fl : 0.0f;
+            aq[ni][e] = j <= i ? decm * aq[ni][e] * w.out.iq[i] : 0.0f;
+        }
+    {
+        uint32_t* mw = reinterpret_cast<uint32_t*>(&w.out.mq[0][0]);             // 8 words per row
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) w.lf[g + (e >> 1) * 8][8 * ni + 2 * t + (e & 1)] = ak[ni][e];
+            mw[g * 8 + 4 * ni + t] = pack_op<T>(aq[ni][0], aq[ni][1]);
+            mw[(g + 8) * 8 + 4 * ni + t] = pack_op<T>(aq[ni][2], aq[ni][3]);
+        }
+    }
+    __syncwarp();
+    if (lane < TC) {                                      // column `lane` of (I + L)^-1 by forward substitution
+        float x[TC];
+#pragma unroll
+        for (int i = 0; i < TC; ++i) {
+            // four partial sums: the dependent chain per row is i / 4 long instead of i
+            float s0 = i == lane ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < i; ++j) {
+                const float l = w.lf[i][j];
+                if ((j & 3) == 0) s0 = fmaf(-l, x[j], s0);
+                else if ((j & 3) == 1) s1 = fmaf(-l, x[j], s1);
+                else if ((j & 3) == 2) s2 = fmaf(-l, x[j], s2);
+                else s3 = fmaf(-l, x[j], s3);
+            }
+            x[i] = (s0 + s1) + (s2 + s3);
+        }
+        const float bc = w.beta[lane];
+#pragma unroll
+        for (int i = 0; i < TC; ++i) w.out.t2[i][lane] = uint16_t(pack_op<T>(x[i] * bc, 0.0f) & 0xffffu);
+    }
+    __syncwarp();
+    {
+        const uint4* so = reinterpret_cast<const uint4*>(&w.out);
+        uint4* o4 = reinterpret_cast<uint4*>(gb + pt::EXT_OFF);
+        for (int i = lane; i < pt::EXT_BYTES / 16; i += 32) o4[i] = so[i];
+    }
 }
 
 template <typename T>
@@ -155,8 +295,8 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
         constexpr int count = decltype(count_c)::value;   // compile-time, so a warp with few tokens does only their work
         const float4 onw = __ldg(reinterpret_cast<const float4*>(o_norm_w + lane * 4));
         const int pnt = min(min(TC, kTok - pc * TC), first + count);
-        const float* op = &sm.ot[first][lane * 4];
-        const float* sp = &sm.ssq[first][0];
+        const float* op = &sm.ot[pc & 1][first][lane * 4];
+        const float* sp = &sm.ssq[pc & 1][first][0];
         T* dst = on + (row_base + pc * TC + first) * kVD + head * kDV + lane * 4;
 #pragma unroll
         for (int k = 0; k < count; ++k) {
@@ -184,110 +324,8 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
         // (keys hi, tokens 0-7), (keys hi, tokens 8-15) = A fragment of [token][key], and B fragments (r[ni], r[ni + 2])
         // (in rows 4-7 of every eight the two token halves of a row trade places: gdn_pt_layout.cuh)
         const uint32_t tr_off = uint32_t(((lm >> 1) * 8 + lr) * (TC * 2) + ((lm & 1) ^ ((lr >> 2) & 1)) * 16);
-        // ---------------------------------------------------------------- warp 0: norms of k, L, T2; warp 1: norms of q, masked Q K^T
-        if (warp < 2) {
-            // inclusive prefix sum of the log decays, once per warp (the two warps do not wait for each other)
-            float c = b.dec[lane & (TC - 1)];
-#pragma unroll
-            for (int o = 1; o < TC; o <<= 1) {
-                const float up = __shfl_up_sync(0xffffffffu, c, o);
-                if ((lane & (TC - 1)) >= o) c += up;
-            }
-            const float last = __shfl_sync(0xffffffffu, c, TC - 1);
-            if (lane < TC) {
-                sm.cw[warp][lane] = c;
-                if (warp == 0) {
-                    sm.eg[lane] = __expf(c);
-                    sm.dj[lane] = __expf(last - c);
-                }
-            }
-            // Gram products over the 64 keys: warp 0 K K^T; warp 1 Q K^T and the diagonal of Q Q^T
-            float acc[2][4], dq[2][4];
-#pragma unroll
-            for (int ni = 0; ni < 2; ++ni)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) { acc[ni][e] = 0.0f; dq[ni][e] = 0.0f; }
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                uint32_t kf[4], qf[4];
-                ldsm4t(kt_s + uint32_t(p * 16 * TC * 2) + tr_off, kf);
-                if (warp == 1) ldsm4t(qt_s + uint32_t(p * 16 * TC * 2) + tr_off, qf);
-#pragma unroll
-                for (int ni = 0; ni < 2; ++ni) {
-                    if (warp == 0) {
-                        mma16816<T>(acc[ni], kf, kf[ni], kf[ni + 2]);
-                    } else {
-                        mma16816<T>(acc[ni], qf, kf[ni], kf[ni + 2]);
-                        mma16816<T>(dq[ni], qf, qf[ni], qf[ni + 2]);
-                    }
-                }
-            }
-            // diagonal entries: row g sits in tile 0 at column 2t + e == g, row g + 8 in tile 1 at the same lane / slot
-            if (t == (g >> 1)) {
-                const bool odd = g & 1;                   // selects, not a runtime index: the fragments stay in registers
-                if (warp == 0) {
-                    sm.ik[g] = rsqrtf((odd ? acc[0][1] : acc[0][0]) + 1e-6f);
-                    sm.ik[g + 8] = rsqrtf((odd ? acc[1][3] : acc[1][2]) + 1e-6f);
-                } else {
-                    sm.iq[g] = rsqrtf((odd ? dq[0][1] : dq[0][0]) + 1e-6f) * 0.125f;
-                    sm.iq[g + 8] = rsqrtf((odd ? dq[1][3] : dq[1][2]) + 1e-6f) * 0.125f;
-                }
-            }
-            __syncwarp();
-            // acc[ni][0,1]: row i = g, columns j = 8 ni + 2t, + 1;  acc[ni][2,3]: row i = g + 8
-            const float* cum = sm.cw[warp];
-#pragma unroll
-            for (int ni = 0; ni < 2; ++ni)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int i = g + (e >> 1) * 8, j = 8 * ni + 2 * t + (e & 1);
-                    const bool keep = warp == 0 ? j < i : j <= i;
-                    const float dec = __expf(keep ? cum[i] - cum[j] : 0.0f);
-                    // warp 0: L_ij carries both key norms; warp 1: the key norm of column j is applied to U in the O product
-                    const float f = warp == 0 ? b.beta[i] * sm.ik[i] * sm.ik[j] : sm.iq[i];
-                    acc[ni][e] = keep ? dec * acc[ni][e] * f : 0.0f;
-                }
-            if (warp == 0) {
-#pragma unroll
-                for (int ni = 0; ni < 2; ++ni)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) sm.lf[g + (e >> 1) * 8][8 * ni + 2 * t + (e & 1)] = acc[ni][e];
-                __syncwarp();
-                if (lane < TC) {                          // column `lane` of (I + L)^-1 by forward substitution
-                    float x[TC];
-#pragma unroll
-                    for (int i = 0; i < TC; ++i) {
-                        // four partial sums: the dependent chain per row is i / 4 long instead of i
-                        float s0 = i == lane ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-#pragma unroll
-                        for (int j = 0; j < i; ++j) {
-                            const float l = sm.lf[i][j];
-                            if ((j & 3) == 0) s0 = fmaf(-l, x[j], s0);
-                            else if ((j & 3) == 1) s1 = fmaf(-l, x[j], s1);
-                            else if ((j & 3) == 2) s2 = fmaf(-l, x[j], s2);
-                            else s3 = fmaf(-l, x[j], s3);
-                        }
-                        x[i] = (s0 + s1) + (s2 + s3);
-                    }
-                    const float bc = b.beta[lane];
-#pragma unroll
-                    for (int i = 0; i < TC; ++i) sm.t2[i][lane] = uint16_t(pack_op<T>(x[i] * bc, 0.0f) & 0xffffu);
-                }
-            } else {
-                uint32_t* mw = reinterpret_cast<uint32_t*>(&sm.mq[0][0]);        // 12 words per row
-#pragma unroll
-                for (int ni = 0; ni < 2; ++ni) {
-                    mw[g * 12 + 4 * ni + t] = pack_op<T>(acc[ni][0], acc[ni][1]);
-                    mw[(g + 8) * 12 + 4 * ni + t] = pack_op<T>(acc[ni][2], acc[ni][3]);
-                }
-            }
-        }
-        // meanwhile the previous chunk is finished: seven tokens each on warps 2 and 3 and two behind the Gram work of
-        // warp 1 (warp 0 has the inverse)
-        if (chunk > 0) {
-            if (warp == 1) finish_norm(chunk - 1, 14, std::integral_constant<int, 2>());
-            else if (warp >= 2) finish_norm(chunk - 1, 7 * (warp - 2), std::integral_constant<int, 7>());
-        }
+        // the previous chunk is finished first: four tokens per warp (its o tile and sums of squares lie in the other buffer)
+        if (chunk > 0) finish_norm(chunk - 1, 4 * warp, std::integral_constant<int, 4>());
         // ---------------------------------------------------------------- R^T = S0^T K^T and (Q S0)^T, all warps
         float R[2][2][4], QS[2][2][4];
 #pragma unroll
@@ -314,11 +352,10 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
                 }
             }
         }
-        __syncthreads();                                  // T2, masked Q K^T, norms and decays are in shared memory; the
-                                                          // previous chunk's o tile has been read
         // ---------------------------------------------------------------- U^T = (V - diag(e) R)^T T2^T
-        const uint32_t* t2w = reinterpret_cast<const uint32_t*>(&sm.t2[0][0]);   // 12 words per row
-        const uint32_t* mqw = reinterpret_cast<const uint32_t*>(&sm.mq[0][0]);
+        const BlockExt& x = b.ext;                        // T2, M, decays and norms of this chunk, prepared ahead of the scan
+        const uint32_t* t2w = reinterpret_cast<const uint32_t*>(&x.t2[0][0]);    // 8 words per row
+        const uint32_t* mqw = reinterpret_cast<const uint32_t*>(&x.mq[0][0]);
         // per-token scalars of this lane's tokens 8 ni + 2t, + 1, with the norms folded in:
         //   er = exp(c) / |k|  (R = K S0),  eq = exp(c) * 0.125 / |q|  (Q S0),  dj2 = exp(c_last - c) / |k|  (state update)
         float er[2][2], eq[2][2], dj2[2][2], ikt[2][2];
@@ -327,17 +364,17 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int tok = 8 * ni + 2 * t + e;
-                const float egv = sm.eg[tok], ikv = sm.ik[tok];
+                const float egv = x.eg[tok], ikv = x.ik[tok];
                 er[ni][e] = egv * ikv;
-                eq[ni][e] = egv * sm.iq[tok];
-                dj2[ni][e] = sm.dj[tok] * ikv;
+                eq[ni][e] = egv * x.iq[tok];
+                dj2[ni][e] = x.dj[tok] * ikv;
                 ikt[ni][e] = ikv;
             }
         uint32_t bt[2][2], bm[2][2];
 #pragma unroll
         for (int ni = 0; ni < 2; ++ni) {
-            bt[ni][0] = t2w[(8 * ni + g) * 12 + t]; bt[ni][1] = t2w[(8 * ni + g) * 12 + t + 4];
-            bm[ni][0] = mqw[(8 * ni + g) * 12 + t]; bm[ni][1] = mqw[(8 * ni + g) * 12 + t + 4];
+            bt[ni][0] = t2w[(8 * ni + g) * 8 + t]; bt[ni][1] = t2w[(8 * ni + g) * 8 + t + 4];
+            bm[ni][0] = mqw[(8 * ni + g) * 8 + t]; bm[ni][1] = mqw[(8 * ni + g) * 8 + t + 4];
         }
         float sq[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};    // sum of o^2 over this thread's value rows, per token 8 ni + 2t + e
         uint32_t da[2][4];                                // decay-scaled U^T as A fragments, for the state update
@@ -354,7 +391,7 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
             ldsm4(tma::smem_addr(&b.vt[dvb + 16 * mi][0]) + pl_off, vv[mi]);
             ldsm4(tma::smem_addr(&b.gt[dvb + 16 * mi][0]) + pl_off, gg[mi]);
         }
-        float* otile = &sm.ot[0][0];
+        float* otile = &sm.ot[chunk & 1][0][0];
 #pragma unroll
         for (int mi = 0; mi < 2; ++mi) {
             const int r0 = dvb + 16 * mi + g, r1 = r0 + 8;
@@ -399,7 +436,7 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
         }
         // ---------------------------------------------------------------- S^T <- e_last S^T + (diag(d) U)^T K
         {
-            const float elast = sm.eg[TC - 1];
+            const float elast = x.eg[TC - 1];
 #pragma unroll
             for (int nj = 0; nj < 8; ++nj) {
                 // keys 8 nj + g: fragment kf[nj / 2], row half nj % 2; tokens 2t, + 1 (b0) and 8 + 2t, + 1 (b1)
@@ -421,9 +458,9 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
                 v += __shfl_xor_sync(0xffffffffu, v, 4);
                 v += __shfl_xor_sync(0xffffffffu, v, 8);
                 v += __shfl_xor_sync(0xffffffffu, v, 16);
-                if (g == 0) sm.ssq[8 * ni + 2 * t + e][warp] = v;
+                if (g == 0) sm.ssq[chunk & 1][8 * ni + 2 * t + e][warp] = v;
             }
-        __syncthreads();                                  // o tile complete; the block's ring slot is free
+        __syncthreads();                                  // the chunk's o tile is complete; its ring slot is free
     }
     finish_norm(NCHUNK - 1, 4 * warp, std::integral_constant<int, 4>());
 }
@@ -436,6 +473,16 @@ int launch(const void* ptb, const float* o_norm_w, void* on, int B, uint32_t pol
     if (!status) return int(cudaErrorInvalidSymbol);
     gdn_scan_t_kernel<T><<<unsigned(B) * kHeads, 128, SMEM_BYTES, stream>>>(static_cast<const uint8_t*>(ptb), o_norm_w,
                                                                             static_cast<T*>(on), status, polls, starve);
+    return int(cudaGetLastError());
+}
+
+template <typename T>
+int launch_prep(void* ptb, int B, cudaStream_t stream) {
+    const cudaError_t e = cudaFuncSetAttribute(gdn_chunk_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREP_SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    const long long nblocks = (long long)B * kHeads * NCHUNK;
+    gdn_chunk_prep_kernel<T><<<unsigned((nblocks + PREP_WARPS - 1) / PREP_WARPS), PREP_WARPS * 32, PREP_SMEM_BYTES, stream>>>(
+        static_cast<uint8_t*>(ptb), nblocks);
     return int(cudaGetLastError());
 }
 
@@ -457,6 +504,14 @@ int* gdn_scan_t_status_word() {
 }
 
 }  // namespace sb
+
+extern "C" int shvk_gdn_chunk_prep(void* ptb, int op_dtype, int B, void* stream) {
+    if (B <= 0) return 0;
+    if (!ptb || (reinterpret_cast<uintptr_t>(ptb) & 127)) return int(cudaErrorInvalidValue);
+    if (op_dtype == sb::DT_BF16) return sb::launch_prep<__nv_bfloat16>(ptb, B, cudaStream_t(stream));
+    if (op_dtype == sb::DT_F16) return sb::launch_prep<__half>(ptb, B, cudaStream_t(stream));
+    return int(cudaErrorInvalidValue);
+}
 
 extern "C" int shvk_gdn_scan_t(const void* ptb, const float* o_norm_w, void* on, int on_dtype, int B, void* stream) {
     return sb::launch_any(ptb, o_norm_w, on, on_dtype, B, sb::WAIT_POLLS, 0, stream);

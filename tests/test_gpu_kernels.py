@@ -431,7 +431,7 @@ def test_gdn_scan_matches_oracle(L, weight_files, recipe, stage, B):
 
 
 # ---------------------------------------------------------------------------------------------- fused in-projection + 16-bit scan
-PT_BLOCK = 12416
+PT_BLOCK = 13696          # 12,416 bytes of operand tiles and gates + 1,280 bytes added by the chunk preparation
 
 
 def bf16_round(a):
@@ -449,9 +449,9 @@ def rounded_mixer_weights(w, stage):
     return out
 
 
-def run_inproj(L, w, stage, xn16, B, mode=1):
+def run_inproj(L, w, stage, xn16, B, mode=1, prep=True):
     """xn16: [B,321,384] float64 holding values representable in the mode's type (1 bf16, 2 fp16).  Returns (PT device
-    buffer, keep-alive list)."""
+    buffer, keep-alive list).  prep: also run the chunk preparation, which completes the blocks for the scan."""
     import torch
     m = f"{stage}.mixer"
     fused = np.concatenate([w[f"{m}.{n}_proj.weight"] for n in ("q", "k", "v", "g", "a", "b")]).astype(np.float32)   # [2316,384]
@@ -475,6 +475,8 @@ def run_inproj(L, w, stage, xn16, B, mode=1):
     ok(L.shvk_gdn_inproj_plan(X.data_ptr(), B * 321, Wp.data_ptr(), d[2].data_ptr(), d[3].data_ptr(), d[4].data_ptr(),
                               d[5].data_ptr(), pt.data_ptr(), mode, plan))
     ok(L.shvk_gdn_inproj(plan, B, stream_ptr()))
+    if prep:
+        ok(L.shvk_gdn_chunk_prep(pt.data_ptr(), mode, B, stream_ptr()))
     sync()
     return pt, (d, buf)
 
@@ -496,6 +498,61 @@ def unpack_pt(pt, B, mode=1):
 
     qk = torch.bfloat16 if mode == 1 else torch.float16
     return tile(0, 64, qk), tile(2048, 64, qk), tile(4096, 128, torch.float16), tile(8192, 128, torch.float16), gate(12288), gate(12352)
+
+
+def unpack_ext(pt, B, mode=1):
+    """What the chunk preparation added: T2, M [B,6,21,16,16] (the mode's type), exp(c), exp(c_last - c), 1/|k|,
+    0.125/|q| [B,6,21,16]."""
+    import torch
+    raw = pt.cpu().numpy().reshape(B, 6, 21, PT_BLOCK)
+    tdt = torch.bfloat16 if mode == 1 else torch.float16
+
+    def mat(off):
+        t = np.ascontiguousarray(raw[..., off:off + 512]).view(np.int16).reshape(B, 6, 21, 16, 16)
+        return torch.from_numpy(t.copy()).view(tdt).float().numpy().astype(np.float64)
+
+    def vec(off):
+        return np.ascontiguousarray(raw[..., off:off + 64]).view(np.float32).reshape(B, 6, 21, 16).astype(np.float64)
+
+    return mat(12416), mat(12928), vec(13440), vec(13504), vec(13568), vec(13632)
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_chunk_prep_matches_numpy(L, weight_files, mode):
+    """The per-chunk products the scan reads (oracle/shieldv_ref.py:121-163 in WY form): from the tiles the in-projection
+    wrote, T2 = (I + L)^-1 diag(beta), the decay-masked Q K^T, the decays and the norms, against float64 numpy."""
+    _, w0 = weight_files("W3", 1)
+    w = rounded_mixer_weights(w0, "gdn_b")
+    B = 3
+    rng = np.random.default_rng(23)
+    rnd = bf16_round if mode == 1 else (lambda a: np.asarray(a, np.float32).astype(np.float16).astype(np.float64))
+    xn = rnd(rng.standard_normal((B, 321, 384)))
+    pt0, keep0 = run_inproj(L, w, "gdn_b", xn, B, mode, prep=False)
+    pt, keep = run_inproj(L, w, "gdn_b", xn, B, mode)
+    r0, r1 = pt0.cpu().numpy().reshape(-1, PT_BLOCK), pt.cpu().numpy().reshape(-1, PT_BLOCK)
+    assert np.array_equal(r0[:, :12416], r1[:, :12416])          # the preparation leaves the tiles alone
+    assert (r0[:, 12416:] == 0x7f).all()                         # and the in-projection leaves the last 1,280 bytes alone
+    q, k, v, g, dec, beta = unpack_pt(pt, B, mode)
+    t2, mq, eg, dj, ik, iq = unpack_ext(pt, B, mode)
+    q, k = q.reshape(B, 6, 21, 16, 64), k.reshape(B, 6, 21, 16, 64)
+    dec, beta = dec.reshape(B, 6, 21, 16), beta.reshape(B, 6, 21, 16)
+    c = np.cumsum(dec, axis=-1)
+    ik_ref = 1.0 / np.sqrt((k * k).sum(-1) + 1e-6)
+    iq_ref = 0.125 / np.sqrt((q * q).sum(-1) + 1e-6)
+    assert np.allclose(ik, ik_ref, rtol=1e-5) and np.allclose(iq, iq_ref, rtol=1e-5)
+    assert np.allclose(eg, np.exp(c), rtol=1e-5) and np.allclose(dj, np.exp(c[..., -1:] - c), rtol=1e-5)
+    dmask = np.exp(np.minimum(c[..., :, None] - c[..., None, :], 0.0))
+    kk = np.einsum("...ik,...jk->...ij", k, k) * ik_ref[..., :, None] * ik_ref[..., None, :]
+    lo = np.tril(np.ones((16, 16)), -1)
+    Lm = beta[..., :, None] * dmask * kk * lo
+    t2_ref = np.linalg.inv(np.eye(16) + Lm) * beta[..., None, :]
+    m_ref = dmask * np.einsum("...ik,...jk->...ij", q, k) * iq_ref[..., :, None] * np.tril(np.ones((16, 16)))
+    tol = 6e-3 if mode == 1 else 1.5e-3                          # one rounding to the operand type
+    for name, got, ref in (("T2", t2, t2_ref), ("M", mq, m_ref)):
+        err = np.abs(got - ref).max() / max(np.abs(ref).max(), 1.0)
+        print(f"chunk prep mode {mode} {name}: max abs err / max(1, |ref|max) {err:.3e}")
+        assert err < tol
+
 
 
 @pytest.mark.parametrize("recipe,stage,B,mode", [("W3", "gdn_a", 2, 1), ("W3", "gdn_b", 3, 2), ("W1", "gdn_a", 1, 1)])
