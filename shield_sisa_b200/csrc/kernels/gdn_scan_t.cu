@@ -289,11 +289,11 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
     }
     __syncthreads();
 
+    const float4 onw = __ldg(reinterpret_cast<const float4*>(o_norm_w + lane * 4));   // once: a load here every chunk would wait on L2
     // The previous chunk's output: o tile times rstd times the norm weight, tokens first .. first + count - 1 of chunk pc.
     // Loads and arithmetic run unconditionally (the tile rows exist), only the store is guarded.
     auto finish_norm = [&](int pc, int first, auto count_c) {
         constexpr int count = decltype(count_c)::value;   // compile-time, so a warp with few tokens does only their work
-        const float4 onw = __ldg(reinterpret_cast<const float4*>(o_norm_w + lane * 4));
         const int pnt = min(min(TC, kTok - pc * TC), first + count);
         const float* op = &sm.ot[pc & 1][first][lane * 4];
         const float* sp = &sm.ssq[pc & 1][first][0];
