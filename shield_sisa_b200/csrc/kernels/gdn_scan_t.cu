@@ -74,17 +74,19 @@ struct Smem {
 };
 constexpr int SMEM_BYTES = int(sizeof(Smem)) + 128;
 
-struct PrepWarp {                            // the preparation kernel's shared memory, per warp = per chunk
-    uint16_t qt[kDK][TC], kt[kDK][TC];
+struct PrepWarp {                            // the preparation kernel's shared memory, per warp = per pair of chunks
+    uint16_t qt[kDK][TC], kt[kDK][TC];       // tiles of the chunk being worked on
     float dec[TC], beta[TC];
-    float lf[TC][TC];                        // L
-    float cw[TC];                            // inclusive cumulative log decay
-    BlockExt out;                            // staged, then copied to the block in 16-byte pieces
+    float cw[TC];                            // its inclusive cumulative log decay
+    float beta2[2][TC];                      // betas of both chunks, for the inverse
+    float lf[2][TC][TC];                     // L of both chunks
+    BlockExt out[2];                         // staged, then copied to the blocks in 16-byte pieces
     float pad[16];                           // size a multiple of 128
 };
-constexpr int PREP_WARPS = 8;
+constexpr int PREP_WARPS = 4;
 static_assert(sizeof(PrepWarp) % 128 == 0 && offsetof(PrepWarp, out) % 16 == 0 && offsetof(PrepWarp, dec) == 4096, "prep layout");
 constexpr int PREP_SMEM_BYTES = PREP_WARPS * int(sizeof(PrepWarp)) + 128;
+constexpr int PREP_CTAS_PER_SM = 4;                   // by registers
 
 // Operand type of the products: the mode's 16-bit type (bf16 keeps fp32's range, fp16 has three more mantissa bits).
 // The v^T and gate^T tiles are fp16 in both modes: they are only read element-wise and combined in fp32.
@@ -124,35 +126,23 @@ __device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t (&r)[4]) {
 
 
 // ---------------------------------------------------------------------------------------------- chunk preparation
-// The part of a chunk's work that does not depend on the recurrent state, for every chunk of the batch at once: one
-// warp per chunk block reads q^T, k^T, log decays and betas, forms the Gram products K K^T, Q K^T and diag(Q Q^T) on
-// the tensor cores, the key and query norms from their diagonals, the decay masks, the 16 x 16 triangular inverse
-// (forward substitution, fp32, one column per lane) and writes T2, M, exp(c), exp(c_last - c) and the norms into the
-// block's last 1,280 bytes.  Inside the scan this chain (about half of a chunk's critical path, most of it one warp's
-// dependent instructions while the other three waited) ran 21 times in sequence per (clip, head); here half a million
-// chunks are independent and 32 warps per SM hide its latency.
+// The part of a chunk's work that does not depend on the recurrent state, for every chunk of the batch at once: from
+// q^T, k^T, log decays and betas the Gram products K K^T, Q K^T and diag(Q Q^T) on the tensor cores, the key and query
+// norms from their diagonals, the decay masks, the 16 x 16 triangular inverse (forward substitution, fp32, one column
+// per lane) and T2, M, exp(c), exp(c_last - c) and the norms into the block's last 1,280 bytes.  Inside the scan this
+// chain (about half of a chunk's critical path, most of it one warp's dependent instructions while the other three
+// waited) ran 21 times in sequence per (clip, head); here half a million chunks are independent.
+//
+// A warp walks pairs of chunk blocks.  The Gram products and masks of the two chunks run one after the other on all 32
+// lanes; the inverse, which has work for 16 lanes per chunk, runs once for both (lanes 0-15 the first chunk, 16-31 the
+// second).  The tiles of the next chunk are fetched into registers while the current one is computed.
+
+// One chunk: tiles (already in w.qt / w.kt / w.dec / w.beta) -> L in w.lf[slot], everything but T2 in w.out[slot]
 template <typename T>
-__global__ void __launch_bounds__(PREP_WARPS * 32)
-gdn_chunk_prep_kernel(uint8_t* __restrict__ ptb, long long nblocks) {
-    extern __shared__ uint8_t prep_smem_raw[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long blk = (long long)blockIdx.x * PREP_WARPS + warp;
-    if (blk >= nblocks) return;                           // whole warps leave; the kernel has no CTA barrier
-    PrepWarp& w = reinterpret_cast<PrepWarp*>((reinterpret_cast<uintptr_t>(prep_smem_raw) + 127) & ~uintptr_t(127))[warp];
-    uint8_t* gb = ptb + blk * pt::BLOCK_BYTES;
-    {
-        const uint4* g4 = reinterpret_cast<const uint4*>(gb);                  // q^T | k^T: 4 KB from the start of the block
-        uint4* s4 = reinterpret_cast<uint4*>(&w.qt[0][0]);
-        uint4 v[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = g4[lane + 32 * i];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s4[lane + 32 * i] = v[i];
-        if (lane < 8) reinterpret_cast<uint4*>(w.dec)[lane] = reinterpret_cast<const uint4*>(gb + pt::DEC_OFF)[lane];   // dec | beta
-    }
-    __syncwarp();
+__device__ __forceinline__ void prep_chunk(PrepWarp& w, int slot, int lane) {
     const int g = lane >> 2, t = lane & 3;                // mma fragment coordinates
     const int lm = lane >> 3, lr = lane & 7;              // ldmatrix lane roles: matrix lane / 8, row lane % 8
+    BlockExt& out = w.out[slot];
     const uint32_t kt_s = tma::smem_addr(&w.kt[0][0]), qt_s = tma::smem_addr(&w.qt[0][0]);
     // transposed fragment of keys 16p .. 16p+15 x all 16 tokens (in rows 4-7 of every eight the two token halves of a
     // row trade places: gdn_pt_layout.cuh)
@@ -167,8 +157,9 @@ gdn_chunk_prep_kernel(uint8_t* __restrict__ ptb, long long nblocks) {
     const float last = __shfl_sync(0xffffffffu, c, TC - 1);
     if (lane < TC) {
         w.cw[lane] = c;
-        w.out.eg[lane] = __expf(c);
-        w.out.dj[lane] = __expf(last - c);
+        w.beta2[slot][lane] = w.beta[lane];
+        out.eg[lane] = __expf(c);
+        out.dj[lane] = __expf(last - c);
     }
     // Gram products over the 64 keys: K K^T, Q K^T and the diagonal of Q Q^T
     float ak[2][4], aq[2][4], dq[2][4];
@@ -191,10 +182,10 @@ gdn_chunk_prep_kernel(uint8_t* __restrict__ ptb, long long nblocks) {
     // diagonal entries: row g sits in tile 0 at column 2t + e == g, row g + 8 in tile 1 at the same lane / slot
     if (t == (g >> 1)) {
         const bool odd = g & 1;                           // selects, not a runtime index: the fragments stay in registers
-        w.out.ik[g] = rsqrtf((odd ? ak[0][1] : ak[0][0]) + 1e-6f);
-        w.out.ik[g + 8] = rsqrtf((odd ? ak[1][3] : ak[1][2]) + 1e-6f);
-        w.out.iq[g] = rsqrtf((odd ? dq[0][1] : dq[0][0]) + 1e-6f) * 0.125f;
-        w.out.iq[g + 8] = rsqrtf((odd ? dq[1][3] : dq[1][2]) + 1e-6f) * 0.125f;
+        out.ik[g] = rsqrtf((odd ? ak[0][1] : ak[0][0]) + 1e-6f);
+        out.ik[g + 8] = rsqrtf((odd ? ak[1][3] : ak[1][2]) + 1e-6f);
+        out.iq[g] = rsqrtf((odd ? dq[0][1] : dq[0][0]) + 1e-6f) * 0.125f;
+        out.iq[g + 8] = rsqrtf((odd ? dq[1][3] : dq[1][2]) + 1e-6f) * 0.125f;
     }
     __syncwarp();
     // a*[ni][0,1]: row i = g, columns j = 8 ni + 2t, + 1;  a*[ni][2,3]: row i = g + 8
@@ -203,49 +194,88 @@ gdn_chunk_prep_kernel(uint8_t* __restrict__ ptb, long long nblocks) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int i = g + (e >> 1) * 8, j = 8 * ni + 2 * t + (e & 1);
-            const float ci = w.cw[i], cj = w.cw[j];
+            // one exponential serves both masks: exp(c_i - c_j) below the diagonal, exp(0) on it
+            const float dec = __expf(j <= i ? w.cw[i] - w.cw[j] : 0.0f);
             // L_ij carries both key norms; in M the key norm of column j is applied to U in the scan's O product
-            const float decl = __expf(j < i ? ci - cj : 0.0f), decm = __expf(j <= i ? ci - cj : 0.0f);
-            const float fl = w.beta[i] * w.out.ik[i] * w.out.ik[j];
-            ak[ni][e] = j < i ? decl * ak[ni][e] * fl : 0.0f;
-            aq[ni][e] = j <= i ? decm * aq[ni][e] * w.out.iq[i] : 0.0f;
+            const float fl = w.beta[i] * out.ik[i] * out.ik[j];
+            ak[ni][e] = j < i ? dec * ak[ni][e] * fl : 0.0f;
+            aq[ni][e] = j <= i ? dec * aq[ni][e] * out.iq[i] : 0.0f;
         }
-    {
-        uint32_t* mw = reinterpret_cast<uint32_t*>(&w.out.mq[0][0]);             // 8 words per row
+    uint32_t* mw = reinterpret_cast<uint32_t*>(&out.mq[0][0]);               // 8 words per row
 #pragma unroll
-        for (int ni = 0; ni < 2; ++ni) {
+    for (int ni = 0; ni < 2; ++ni) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) w.lf[g + (e >> 1) * 8][8 * ni + 2 * t + (e & 1)] = ak[ni][e];
-            mw[g * 8 + 4 * ni + t] = pack_op<T>(aq[ni][0], aq[ni][1]);
-            mw[(g + 8) * 8 + 4 * ni + t] = pack_op<T>(aq[ni][2], aq[ni][3]);
-        }
+        for (int e = 0; e < 4; ++e) w.lf[slot][g + (e >> 1) * 8][8 * ni + 2 * t + (e & 1)] = ak[ni][e];
+        mw[g * 8 + 4 * ni + t] = pack_op<T>(aq[ni][0], aq[ni][1]);
+        mw[(g + 8) * 8 + 4 * ni + t] = pack_op<T>(aq[ni][2], aq[ni][3]);
     }
-    __syncwarp();
-    if (lane < TC) {                                      // column `lane` of (I + L)^-1 by forward substitution
-        float x[TC];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PREP_WARPS * 32, PREP_CTAS_PER_SM)
+gdn_chunk_prep_kernel(uint8_t* __restrict__ ptb, long long npairs) {
+    extern __shared__ uint8_t prep_smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    PrepWarp& w = reinterpret_cast<PrepWarp*>((reinterpret_cast<uintptr_t>(prep_smem_raw) + 127) & ~uintptr_t(127))[warp];
+    const long long stride = (long long)gridDim.x * PREP_WARPS;
+    long long pair = (long long)blockIdx.x * PREP_WARPS + warp;
+    if (pair >= npairs) return;                           // whole warps leave; the kernel has no CTA barrier
+
+    uint4 v[8], vg = make_uint4(0u, 0u, 0u, 0u);          // q^T | k^T (4 KB from the start of a block) and dec | beta, in flight
+    auto fetch = [&](long long blk) {
+        const uint8_t* gb = ptb + blk * pt::BLOCK_BYTES;
+        const uint4* g4 = reinterpret_cast<const uint4*>(gb);
 #pragma unroll
-        for (int i = 0; i < TC; ++i) {
-            // four partial sums: the dependent chain per row is i / 4 long instead of i
-            float s0 = i == lane ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        for (int i = 0; i < 8; ++i) v[i] = g4[lane + 32 * i];
+        if (lane < 8) vg = reinterpret_cast<const uint4*>(gb + pt::DEC_OFF)[lane];
+    };
+    auto land = [&]() {                                   // registers -> the warp's tile buffer
+        uint4* s4 = reinterpret_cast<uint4*>(&w.qt[0][0]);
 #pragma unroll
-            for (int j = 0; j < i; ++j) {
-                const float l = w.lf[i][j];
-                if ((j & 3) == 0) s0 = fmaf(-l, x[j], s0);
-                else if ((j & 3) == 1) s1 = fmaf(-l, x[j], s1);
-                else if ((j & 3) == 2) s2 = fmaf(-l, x[j], s2);
-                else s3 = fmaf(-l, x[j], s3);
+        for (int i = 0; i < 8; ++i) s4[lane + 32 * i] = v[i];
+        if (lane < 8) reinterpret_cast<uint4*>(w.dec)[lane] = vg;
+        __syncwarp();
+    };
+    fetch(2 * pair);
+    for (; pair < npairs; pair += stride) {
+        land();
+        fetch(2 * pair + 1);                              // flies during the first chunk's products
+        prep_chunk<T>(w, 0, lane);
+        __syncwarp();                                     // every lane is done with the tile buffer
+        land();
+        if (pair + stride < npairs) fetch(2 * (pair + stride));   // flies during the second chunk's products and the inverse
+        prep_chunk<T>(w, 1, lane);
+        __syncwarp();
+        {
+            // column `lane % 16` of (I + L)^-1 of chunk `lane / 16` by forward substitution
+            const int h = lane >> 4, col = lane & (TC - 1);
+            float x[TC];
+#pragma unroll
+            for (int i = 0; i < TC; ++i) {
+                // four partial sums: the dependent chain per row is i / 4 long instead of i
+                float s0 = i == col ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+                for (int j = 0; j < i; ++j) {
+                    const float l = w.lf[h][i][j];
+                    if ((j & 3) == 0) s0 = fmaf(-l, x[j], s0);
+                    else if ((j & 3) == 1) s1 = fmaf(-l, x[j], s1);
+                    else if ((j & 3) == 2) s2 = fmaf(-l, x[j], s2);
+                    else s3 = fmaf(-l, x[j], s3);
+                }
+                x[i] = (s0 + s1) + (s2 + s3);
             }
-            x[i] = (s0 + s1) + (s2 + s3);
-        }
-        const float bc = w.beta[lane];
+            const float bc = w.beta2[h][col];
 #pragma unroll
-        for (int i = 0; i < TC; ++i) w.out.t2[i][lane] = uint16_t(pack_op<T>(x[i] * bc, 0.0f) & 0xffffu);
-    }
-    __syncwarp();
-    {
-        const uint4* so = reinterpret_cast<const uint4*>(&w.out);
-        uint4* o4 = reinterpret_cast<uint4*>(gb + pt::EXT_OFF);
-        for (int i = lane; i < pt::EXT_BYTES / 16; i += 32) o4[i] = so[i];
+            for (int i = 0; i < TC; ++i) w.out[h].t2[i][col] = uint16_t(pack_op<T>(x[i] * bc, 0.0f) & 0xffffu);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4* so = reinterpret_cast<const uint4*>(&w.out[h]);
+            uint4* o4 = reinterpret_cast<uint4*>(ptb + (2 * pair + h) * pt::BLOCK_BYTES + pt::EXT_OFF);
+            for (int i = lane; i < pt::EXT_BYTES / 16; i += 32) o4[i] = so[i];
+        }
+        __syncwarp();                                     // the staged outputs are read before the next pair overwrites them
     }
 }
 
@@ -480,9 +510,14 @@ template <typename T>
 int launch_prep(void* ptb, int B, cudaStream_t stream) {
     const cudaError_t e = cudaFuncSetAttribute(gdn_chunk_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREP_SMEM_BYTES);
     if (e != cudaSuccess) return int(e);
-    const long long nblocks = (long long)B * kHeads * NCHUNK;
-    gdn_chunk_prep_kernel<T><<<unsigned((nblocks + PREP_WARPS - 1) / PREP_WARPS), PREP_WARPS * 32, PREP_SMEM_BYTES, stream>>>(
-        static_cast<uint8_t*>(ptb), nblocks);
+    static_assert((kHeads * NCHUNK) % 2 == 0, "a clip's chunk blocks come in pairs");
+    const long long npairs = (long long)B * kHeads * NCHUNK / 2;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long want = (npairs + PREP_WARPS - 1) / PREP_WARPS, cap = (long long)sms * PREP_CTAS_PER_SM;
+    gdn_chunk_prep_kernel<T><<<unsigned(want < cap ? want : cap), PREP_WARPS * 32, PREP_SMEM_BYTES, stream>>>(
+        static_cast<uint8_t*>(ptb), npairs);
     return int(cudaGetLastError());
 }
 
