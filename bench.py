@@ -55,7 +55,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per clip of one launch, from the ncu captures at B = 512 in the 16-bit
 # modes that are summarised under profiles/ (traffic grows in proportion to the clips of a launch: every clip's tiles
 # are fetched and written once); scaled to the bench's B for the `traffic` key
-NCU_TRAFFIC_PER_CLIP = {"gdn_scan": (801014016 + 231972608) / 512, "gdn_inproj": (128415488 + 744627712) / 512}
+NCU_TRAFFIC_PER_CLIP = {"gdn_scan": (883577088 + 233556480) / 512, "gdn_inproj": (128459264 + 741220608) / 512,
+                        "gdn_prep": (272559104 + 60344064) / 512}
 PT_TILE_BYTES_PER_CLIP = 6 * 21 * 12416  # chunk-blocked 16-bit operand tiles and gates the fused in-projection writes
 PT_QK_BYTES_PER_CLIP = 6 * 21 * (4096 + 128)    # of which the chunk preparation reads q^T, k^T, decays and betas
 PT_EXT_BYTES_PER_CLIP = 6 * 21 * 1280    # and what it adds to every chunk block (T2, M, decays, norms)
@@ -701,6 +702,39 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                  if model_bytes != nbytes and top.startswith("gdn_") else None,
                  "traffic": B * NCU_TRAFFIC_PER_CLIP[top] if has_traffic else None,
                  "traffic_source": "ncu capture at B = 512 (profiles/), scaled by clips" if has_traffic else None})
+    # ------------------------------------------------------------ cycle counters of a development build (--dev-cycles)
+    dev_cycles = None
+    if args.dev_cycles and storage == 2:
+        import ctypes as C
+        L = binding.load_library(True)
+        try:
+            f_in, f_sc = L.shvk_dev_inproj_cycles, L.shvk_dev_scan_cycles
+        except AttributeError:
+            raise SystemExit("--dev-cycles needs the development build: python -m shield_sisa_b200.build --dev-probes")
+        b_in, b_sc = (C.c_ulonglong * 88)(), (C.c_ulonglong * 32)()
+        for f, b in ((f_in, b_in), (f_sc, b_sc)):
+            f.argtypes, f.restype = [C.c_void_p], C.c_int
+            f(b)                                          # discard what the steps above accumulated
+        eng.classify(0, B, stream)
+        torch.cuda.synchronize()
+        f_in(b_in)
+        f_sc(b_sc)
+
+        def shares(buf, w, names, total=None):
+            v = [buf[w * 8 + k] for k in range(8)]
+            tot = float(v[total] if total is not None else sum(v)) or 1.0
+            return {n: round(v[k] / tot, 3) for k, n in names}
+
+        dev_cycles = {
+            "note": "share of each role's cycles, one CTA (in-projection) / one CTA in 61 (scan), three launches each",
+            "gdn_inproj": {
+                "w_producer": shares(b_in, 0, [(0, "wait_free_stage")], 7),
+                "mma_thread": shares(b_in, 1, [(0, "wait_drained_accumulator"), (1, "wait_weight_stage"), (2, "wait_token_tile")], 7),
+                **{f"epilogue_warp_{w}": shares(b_in, w, [(0, "wait_full_accumulator"), (1, "first_tmem_load"),
+                                                          (2, "later_tmem_loads"), (3, "tile_total")], 7) for w in range(3, 11)}},
+            "gdn_scan_t": {f"warp_{w}": shares(b_sc, w, [(0, "until_block_landed"), (1, "deferred_norm"), (2, "r_and_qs"), (3, "u_and_o"),
+                                                         (4, "state_update"), (5, "sum_of_squares"), (6, "barrier")]) for w in range(4)}}
+        print(json.dumps(dev_cycles, indent=1), file=sys.stderr)
     alg_bytes_clip = 45853824 if mode == "fp32" else 37471872
     stack_frac = B * alg_bytes_clip / (ms_step / 1000.0) / (pk["hbm_gbs"] * 1e9)
     launches = eng.launches() * args.steps * world
@@ -893,6 +927,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "stack_hbm_fraction": {"algorithmic_bytes_per_clip": alg_bytes_clip, "frac": stack_frac,
                                    "note": "whole stack against the GEMM-boundary byte model and the measured HBM peak"},
             "kernels": kernels, "encoder": encoder, "extras": extras, "live_box": live_box,
+            **({"dev_cycles": dev_cycles} if dev_cycles else {}),
         }
         emit(line)
     if world > 1:
@@ -924,6 +959,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-encoder", action="store_true", help="skip the frame-encoder leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (small cases for profiling)")
+    ap.add_argument("--dev-cycles", action="store_true",
+                    help="development build only (python -m shield_sisa_b200.build --dev-probes): print the per-role cycle counters "
+                         "of the in-projection and the scan; the timings of such a run are not bench values")
     ap.add_argument("--no-extras", action="store_true", help="skip the extra keys (exact-tier B = 128 line, long-sequence kernel)")
     ap.add_argument("--workload", default="stack", choices=["stack", "live", "encoder", "chunked"],
                     help="stack: the headline metric (default); live: streaming hops with frames and device token rings; "

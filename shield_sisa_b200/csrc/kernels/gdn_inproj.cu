@@ -74,6 +74,11 @@ struct InprojParams {
 };
 // The probe bits travel in the kernel parameters (constant bank) and, to the tile functions, in bits 8+ of `flags`: a
 // word in global memory would add a load in front of every tile and change the timings it is meant to explain.
+// Cycle counters of the same builds: lane 0 of every warp adds clock64() differences to eight slots in shared memory
+// (W producer: 0 wait for a free stage.  MMA thread: 0 wait for a drained accumulator, 1 for a weight stage, 2 for the
+// token tile.  Epilogue warps: 0 wait for a full accumulator, 1 first tensor-memory load of a tile, 2 the later ones,
+// 3 the whole tile.  All: 7 the role's loop.)  CTA 5 adds its totals to g_prof, read and cleared by
+// shvk_dev_inproj_cycles.
 #ifdef SHVK_DEV_PROBES
 __device__ unsigned long long g_prof[11][8];
 #define PROF_T() clock64()
@@ -563,7 +568,8 @@ static int inproj_launch(const void* host_plan, int B, void* stream, int starve,
 }
 
 #ifdef SHVK_DEV_PROBES
-extern "C" __attribute__((visibility("default"))) int shvk_dev_inproj_prof(unsigned long long* out) {
+// Development builds only: the in-projection's cycle counters [11 warps][8 slots], read and cleared (synchronises the device).
+extern "C" __attribute__((visibility("default"))) int shvk_dev_inproj_cycles(unsigned long long* out) {
     unsigned long long zero[88] = {0};
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out, sb::g_prof, sizeof(zero));

@@ -279,6 +279,16 @@ gdn_chunk_prep_kernel(uint8_t* __restrict__ ptb, long long npairs) {
     }
 }
 
+// Cycle counters of a development build (-DSHVK_DEV_PROBES): every warp adds the clock() ticks between the phase
+// boundaries of its chunk loop to eight slots (0 block landed, 1 deferred norm, 2 R and Q S0, 3 U and O, 4 state update,
+// 5 sum of squares, 6 barrier); one CTA in 61 adds its totals to g_scan_cycles, read and cleared by shvk_dev_scan_cycles.
+#ifdef SHVK_DEV_PROBES
+__device__ unsigned long long g_scan_cycles[4][8];
+#define SCAN_TICK(slot) do { const unsigned now_ = unsigned(clock()); ticks[slot] += now_ - tick0; tick0 = now_; } while (0)
+#else
+#define SCAN_TICK(slot) do { } while (0)
+#endif
+
 template <typename T>
 __global__ void __launch_bounds__(128, 3)
 gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_norm_w, T* __restrict__ on, int* __restrict__ status,
@@ -338,6 +348,10 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
         }
     };
 
+#ifdef SHVK_DEV_PROBES
+    unsigned ticks[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    unsigned tick0 = unsigned(clock());
+#endif
     for (int chunk = 0; chunk < NCHUNK; ++chunk) {
         Block& b = sm.blk[chunk % NSLOT];
         if (tid == 0 && chunk + 2 < NCHUNK) {
@@ -349,6 +363,7 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
             if (tid == 0) atomicCAS(status, 0, 1);
             return;                                       // every thread times out on the same barrier and leaves
         }
+        SCAN_TICK(0);
         const uint32_t kt_s = tma::smem_addr(&b.kt[0][0]), qt_s = tma::smem_addr(&b.qt[0][0]);
         // transposed fragment of keys 16p .. 16p+15 x all 16 tokens: matrices (keys lo, tokens 0-7), (keys lo, tokens 8-15),
         // (keys hi, tokens 0-7), (keys hi, tokens 8-15) = A fragment of [token][key], and B fragments (r[ni], r[ni + 2])
@@ -356,6 +371,7 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
         const uint32_t tr_off = uint32_t(((lm >> 1) * 8 + lr) * (TC * 2) + ((lm & 1) ^ ((lr >> 2) & 1)) * 16);
         // the previous chunk is finished first: four tokens per warp (its o tile and sums of squares lie in the other buffer)
         if (chunk > 0) finish_norm(chunk - 1, 4 * warp, std::integral_constant<int, 4>());
+        SCAN_TICK(1);
         // ---------------------------------------------------------------- R^T = S0^T K^T and (Q S0)^T, all warps
         float R[2][2][4], QS[2][2][4];
 #pragma unroll
@@ -382,6 +398,7 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
                 }
             }
         }
+        SCAN_TICK(2);
         // ---------------------------------------------------------------- U^T = (V - diag(e) R)^T T2^T
         const BlockExt& x = b.ext;                        // T2, M, decays and norms of this chunk, prepared ahead of the scan
         const uint32_t* t2w = reinterpret_cast<const uint32_t*>(&x.t2[0][0]);    // 8 words per row
@@ -464,6 +481,7 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
                 sq[ni][1] = fmaf(o01, o01, fmaf(o11, o11, sq[ni][1]));
             }
         }
+        SCAN_TICK(3);
         // ---------------------------------------------------------------- S^T <- e_last S^T + (diag(d) U)^T K
         {
             const float elast = x.eg[TC - 1];
@@ -479,6 +497,7 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
                 }
             }
         }
+        SCAN_TICK(4);
         // this warp's share of sum(o^2): reduce over the eight row groups g (lane bits 2-4), lanes 0-3 publish it
 #pragma unroll
         for (int ni = 0; ni < 2; ++ni)
@@ -490,8 +509,14 @@ gdn_scan_t_kernel(const uint8_t* __restrict__ ptb, const float* __restrict__ o_n
                 v += __shfl_xor_sync(0xffffffffu, v, 16);
                 if (g == 0) sm.ssq[chunk & 1][8 * ni + 2 * t + e][warp] = v;
             }
+        SCAN_TICK(5);
         __syncthreads();                                  // the chunk's o tile is complete; its ring slot is free
+        SCAN_TICK(6);
     }
+#ifdef SHVK_DEV_PROBES
+    if (lane == 0 && blockIdx.x % 61 == 7)
+        for (int k = 0; k < 8; ++k) atomicAdd(&g_scan_cycles[warp][k], (unsigned long long)ticks[k]);
+#endif
     finish_norm(NCHUNK - 1, 4 * warp, std::integral_constant<int, 4>());
 }
 
@@ -557,3 +582,14 @@ extern "C" int shvk_gdn_scan_t_starved(const void* ptb, const float* o_norm_w, v
     const uint32_t lim = polls < 256 ? 256u : (uint32_t(polls) > sb::WAIT_POLLS ? sb::WAIT_POLLS : uint32_t(polls));
     return sb::launch_any(ptb, o_norm_w, on, on_dtype, B, lim, 1, stream);
 }
+
+#ifdef SHVK_DEV_PROBES
+// Development builds only: the scan's cycle counters [4 warps][8 slots], read and cleared (synchronises the device).
+extern "C" __attribute__((visibility("default"))) int shvk_dev_scan_cycles(unsigned long long* out) {
+    unsigned long long zero[32] = {0};
+    if (cudaDeviceSynchronize() != cudaSuccess) return int(cudaGetLastError());
+    cudaMemcpyFromSymbol(out, sb::g_scan_cycles, sizeof(zero));
+    cudaMemcpyToSymbol(sb::g_scan_cycles, zero, sizeof(zero));
+    return int(cudaGetLastError());
+}
+#endif
