@@ -8,7 +8,7 @@
 //      consecutive tokens, a shuffle scan combines the lane totals, all in double.
 //   3  rotate C (row 320) by phi[320]; per token rotate B by phi[t], score = q.k/8 + softplus(lambda) *
 //      exp(g_last - g_t) * (c_rot . b_rot) + (f_last - f_t); thread per token, rows read as float4
-//   4  softmax over the 321 scores, y = sum_t p_t v_t with 4 token groups x 64 columns
+//   4  softmax over the 321 scores, y = sum_t p_t v_t: eight threads per token row, 24 tokens per round
 //
 // Two row formats.  fp32 (exact tier): one row [K | V | B | theta | alpha | forget] of 1,072 floats per token.  16-bit
 // modes: K, V, B travel as fp16 in a row of 960 halves (S16) and theta, alpha, forget as fp32 in a row of 112 floats
@@ -21,7 +21,8 @@
 namespace sb {
 namespace {
 
-constexpr int NT = 256, NCOL = 18, PER_LANE = 11;   // 32 * 11 = 352 >= 321
+constexpr int NT = 192, NCOL = 18, PER_LANE = 11;   // 32 * 11 = 352 >= 321
+constexpr int VSLOTS = NT / 8;                       // tokens of the value sum in flight: eight threads share a token's 64 values
 constexpr int kS16LD = 960, kSGLD = 112;             // row pitches of the split format; SG = [theta 96 | alpha 6 | forget 6 | pad 4]
 
 // Eight consecutive K or B values of a token row, widened to fp32.
@@ -45,8 +46,20 @@ template <> struct Row8<true> {
     }
 };
 
-// Four CTAs per SM (64 registers, a 52-byte spill): the phases of one CTA alternate between loads and scans, and more
-// resident CTAs keep HBM busy through the scans: 1.75 ms at three CTAs, 1.48 ms at four, 1.63 ms at five (B = 4096).
+// sin and cos of a phase: reduction to [-pi, pi] with 2 pi split in two (exact to about 1e-7 for the phases that occur,
+// cumulative sums of theta over 321 tokens), then the hardware approximations (absolute error below 4e-7 on that range).
+// sincosf costs about 45 instructions, and a token needs sixteen of them.
+__device__ __forceinline__ void sincos_phase(float x, float& sn, float& cs) {
+    const float k = rintf(x * 0.15915494309189535f);
+    float r = fmaf(k, -6.2831854820251465f, x);       // fp32(2 pi) = 2 pi + 1.7484555e-7
+    r = fmaf(k, 1.7484555e-7f, r);
+    sn = __sinf(r);
+    cs = __cosf(r);
+}
+
+// Four CTAs of 192 threads per SM: the phases of one CTA alternate between loads and scans, and more resident CTAs keep
+// HBM busy through the scans (B = 4096, 16-bit rows, with sincosf and a value sum of one column per thread: 256 threads
+// x 4 CTAs 1.18 ms, 352 x 3 1.16, 352 x 2 1.45, 192 x 5 1.10; as written here 192 x 4 and 192 x 5 both 1.0 ms).
 template <bool H16>
 __global__ void __launch_bounds__(NT, 4)
 sisa_attn_kernel(const void* __restrict__ Skvb, const float* __restrict__ Sgate, const float* __restrict__ QC,
@@ -64,7 +77,7 @@ sisa_attn_kernel(const void* __restrict__ Skvb, const float* __restrict__ Sgate,
     __shared__ __align__(16) float sq[kDK];
     __shared__ __align__(16) float sc[kState];
     __shared__ float red[NT / 32];
-    __shared__ float ypart[4][kDK];
+    __shared__ float ypart[NT / 32][kDK];
 
     // per-token terms: theta[16] of this head is one 64-byte run, alpha and forget are single floats
     for (int tk = tid; tk < kTok; tk += NT) {
@@ -110,7 +123,7 @@ sisa_attn_kernel(const void* __restrict__ Skvb, const float* __restrict__ Sgate,
 
     if (tid < kPairs) {
         float si, co;
-        sincosf(term[2 + tid][kTok - 1], &si, &co);
+        sincos_phase(term[2 + tid][kTok - 1], si, co);
         const float e = sc[2 * tid], o = sc[2 * tid + 1];
         __syncwarp(0x0000ffffu);
         sc[2 * tid] = e * co - o * si;
@@ -134,14 +147,14 @@ sisa_attn_kernel(const void* __restrict__ Skvb, const float* __restrict__ Sgate,
         content *= 0.125f;
         const KV* br = S0 + (long long)t * LDK + kSB + head * kState;
         float ssm = 0.0f;
-#pragma unroll
+#pragma unroll 1                                      // unrolled, the sixteen phases of a token at once spill 300 bytes
         for (int j = 0; j < kState / 8; ++j) {
             float bb[8];
             Row8<H16>::load(br, j, bb);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {                 // pair 4 j + e: (bb[2e], bb[2e+1]) rotated by phi of that pair
                 float sn, cs;
-                sincosf(term[2 + 4 * j + e][t], &sn, &cs);
+                sincos_phase(term[2 + 4 * j + e][t], sn, cs);
                 ssm = fmaf(sc[8 * j + 2 * e], bb[2 * e] * cs - bb[2 * e + 1] * sn, ssm);
                 ssm = fmaf(sc[8 * j + 2 * e + 1], bb[2 * e] * sn + bb[2 * e + 1] * cs, ssm);
             }
@@ -171,13 +184,36 @@ sisa_attn_kernel(const void* __restrict__ Skvb, const float* __restrict__ Sgate,
 #pragma unroll
     for (int i = 0; i < NT / 32; ++i) sum += red[i];
     const float inv = 1.0f / sum;
-    const int j = tid & (kDK - 1), grp = tid >> 6;
-    float y = 0.0f;
-#pragma unroll 8
-    for (int t = grp; t < kTok; t += 4) y = fmaf(score[t] * inv, float(S0[(long long)t * LDK + kSV + head * kDK + j]), y);
-    ypart[grp][j] = y;
+    // y = sum_t p_t v_t: eight threads share a token's 64 values (16 bytes each in the 16-bit format), VSLOTS tokens per
+    // round; the token slots of a warp are added by shuffles, the warps through shared memory
+    const int part = tid & 7, slot = tid >> 3;
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = 0.0f;
+#pragma unroll 4
+    for (int t = slot; t < kTok; t += VSLOTS) {
+        float vv[8];
+        Row8<H16>::load(S0 + (long long)t * LDK + kSV + head * kDK, part, vv);
+        const float pt = score[t] * inv;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = fmaf(pt, vv[e], y[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        y[e] += __shfl_xor_sync(0xffffffffu, y[e], 8);
+        y[e] += __shfl_xor_sync(0xffffffffu, y[e], 16);
+    }
+    if (lane < 8) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ypart[warp][8 * lane + e] = y[e];
+    }
     __syncthreads();
-    if (tid < kDK) Y[(long long)clip * kD + head * kDK + tid] = (ypart[0][tid] + ypart[1][tid]) + (ypart[2][tid] + ypart[3][tid]);
+    if (tid < kDK) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NT / 32; ++w) acc += ypart[w][tid];
+        Y[(long long)clip * kD + head * kDK + tid] = acc;
+    }
 }
 
 }  // namespace
