@@ -7,7 +7,7 @@
 //      cumsum semantics both reference engines keep, seq.cu:249-258).  A warp scans one column: each lane sums 11
 //      consecutive tokens, a shuffle scan combines the lane totals, all in double.
 //   3  rotate C (row 320) by phi[320]; per token rotate B by phi[t], score = q.k/8 + softplus(lambda) *
-//      exp(g_last - g_t) * (c_rot . b_rot) + (f_last - f_t); thread per token, rows read as float4
+//      exp(g_last - g_t) * (c_rot . b_rot) + (f_last - f_t); eight threads per token, 16 bytes of K each
 //   4  softmax over the 321 scores, y = sum_t p_t v_t: eight threads per token row, 24 tokens per round
 //
 // Two row formats.  fp32 (exact tier): one row [K | V | B | theta | alpha | forget] of 1,072 floats per token.  16-bit
@@ -57,9 +57,27 @@ __device__ __forceinline__ void sincos_phase(float x, float& sn, float& cs) {
     cs = __cosf(r);
 }
 
+// Four consecutive B values of a token row, widened to fp32.
+template <bool H16> struct Row4;
+template <> struct Row4<false> {
+    static __device__ __forceinline__ void load(const void* base, int i, float (&v)[4]) {
+        const float4 a = static_cast<const float4*>(base)[i];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    }
+};
+template <> struct Row4<true> {
+    static __device__ __forceinline__ void load(const void* base, int i, float (&v)[4]) {
+        const uint2 u = static_cast<const uint2*>(base)[i];
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]);
+        v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+    }
+};
+
 // Four CTAs of 192 threads per SM: the phases of one CTA alternate between loads and scans, and more resident CTAs keep
-// HBM busy through the scans (B = 4096, 16-bit rows, with sincosf and a value sum of one column per thread: 256 threads
-// x 4 CTAs 1.18 ms, 352 x 3 1.16, 352 x 2 1.45, 192 x 5 1.10; as written here 192 x 4 and 192 x 5 both 1.0 ms).
+// HBM busy through the scans.  B = 4096, 16-bit rows: a thread per token with sincosf and a value sum of one column per
+// thread 1.18 ms (256 threads x 4 CTAs; 352 x 3 1.16, 352 x 2 1.45, 192 x 5 1.10); hardware sin / cos and 16-byte value
+// reads 0.98 ms; eight threads per token in the score phase as well 0.73 ms (four, five and six CTAs per SM the same).
 template <bool H16>
 __global__ void __launch_bounds__(NT, 4)
 sisa_attn_kernel(const void* __restrict__ Skvb, const float* __restrict__ Sgate, const float* __restrict__ QC,
@@ -133,36 +151,46 @@ sisa_attn_kernel(const void* __restrict__ Skvb, const float* __restrict__ Sgate,
 
     const float lam = softplus_f(lambda_raw[head]);
     const float g_last = term[0][kTok - 1], f_last = term[1][kTok - 1];
+    // scores: eight threads per token (16 bytes of K and two of the sixteen state pairs each), VSLOTS tokens per round;
+    // a warp then reads four whole rows per instruction instead of 32 different ones
     float lmax = -INFINITY;
-    for (int t = tid; t < kTok; t += NT) {
-        const KV* kr = S0 + (long long)t * LDK + kSK + head * kDK;
-        float content = 0.0f;
+    {
+        const int part = tid & 7, slot = tid >> 3;
+        float q8[8], c4[4];
 #pragma unroll
-        for (int j = 0; j < kDK / 8; ++j) {
-            float kk[8];
-            Row8<H16>::load(kr, j, kk);
+        for (int e = 0; e < 8; ++e) q8[e] = sq[8 * part + e];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) content = fmaf(sq[8 * j + e], kk[e], content);
-        }
-        content *= 0.125f;
-        const KV* br = S0 + (long long)t * LDK + kSB + head * kState;
-        float ssm = 0.0f;
-#pragma unroll 1                                      // unrolled, the sixteen phases of a token at once spill 300 bytes
-        for (int j = 0; j < kState / 8; ++j) {
-            float bb[8];
-            Row8<H16>::load(br, j, bb);
+        for (int e = 0; e < 4; ++e) c4[e] = sc[4 * part + e];
+#pragma unroll 2
+        for (int t0 = 0; t0 < kTok; t0 += VSLOTS) {
+            const int t = t0 + slot;
+            float content = 0.0f, ssm = 0.0f;
+            if (t < kTok) {
+                float kk[8], bb[4];
+                Row8<H16>::load(S0 + (long long)t * LDK + kSK + head * kDK, part, kk);
+                Row4<H16>::load(S0 + (long long)t * LDK + kSB + head * kState, part, bb);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {                 // pair 4 j + e: (bb[2e], bb[2e+1]) rotated by phi of that pair
-                float sn, cs;
-                sincos_phase(term[2 + 4 * j + e][t], sn, cs);
-                ssm = fmaf(sc[8 * j + 2 * e], bb[2 * e] * cs - bb[2 * e + 1] * sn, ssm);
-                ssm = fmaf(sc[8 * j + 2 * e + 1], bb[2 * e] * sn + bb[2 * e + 1] * cs, ssm);
+                for (int e = 0; e < 8; ++e) content = fmaf(q8[e], kk[e], content);
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {             // pair 2 part + e: (bb[2e], bb[2e+1]) rotated by phi of that pair
+                    float sn, cs;
+                    sincos_phase(term[2 + 2 * part + e][t], sn, cs);
+                    ssm = fmaf(c4[2 * e], bb[2 * e] * cs - bb[2 * e + 1] * sn, ssm);
+                    ssm = fmaf(c4[2 * e + 1], bb[2 * e] * sn + bb[2 * e + 1] * cs, ssm);
+                }
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                content += __shfl_xor_sync(0xffffffffu, content, o);
+                ssm += __shfl_xor_sync(0xffffffffu, ssm, o);
+            }
+            if (part == 0 && t < kTok) {
+                float sv = content * 0.125f + (lam * expf(g_last - term[0][t])) * ssm;
+                sv = sv + (f_last - term[1][t]);
+                score[t] = sv;
+                lmax = fmaxf(lmax, sv);
             }
         }
-        float s = content + (lam * expf(g_last - term[0][t])) * ssm;
-        s = s + (f_last - term[1][t]);
-        score[t] = s;
-        lmax = fmaxf(lmax, s);
     }
     lmax = warp_max(lmax);
     if (lane == 0) red[warp] = lmax;
