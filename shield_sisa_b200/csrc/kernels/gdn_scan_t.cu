@@ -1,10 +1,6 @@
-// Gated delta rule + gated RMSNorm for the 16-bit modes, fed by the chunk-blocked bf16 operand tiles of the fused
-// in-projection (gdn_inproj.cu, layout in gdn_pt_layout.cuh): the delta rule in chunks of 16 tokens on the tensor cores.
-//
-// One CTA (four warps) owns one (clip, head) and walks its 21 chunk blocks.  A block (q^T, k^T, v^T, gate^T tiles,
-// log decays, betas: 12,416 contiguous bytes) arrives by ONE bulk copy into a three-slot ring, two chunks ahead.
-// Nothing is converted or re-laid-out here: every operand fragment of the chunk's products comes straight out of the
-// landed tiles with ldmatrix (transposing where the product wants tokens along the contraction).
+// Gated delta rule + gated RMSNorm for the 16-bit modes, fed by the chunk-blocked 16-bit operand tiles of the fused
+// in-projection (gdn_inproj.cu, layout in gdn_pt_layout.cuh): the delta rule in chunks of 16 tokens on the tensor cores,
+// in two kernels.
 //
 // For a chunk with inclusive cumulative log decay c_i, e_i = exp(c_i), state S0 (keys x values) entering the chunk:
 //     A = K K^T, B = Q K^T                                      (16 x 16, contraction over the 64 keys)
@@ -13,22 +9,31 @@
 //     U = T2 (V - diag(e) R)                                    (16 x 128)
 //     O = M U + diag(e) QS
 //     S' = e_16 S0 + K^T diag(exp(c_16 - c_j)) U
-// Everything is computed transposed (value dimension = MMA rows): warp w owns value columns 32w .. 32w+31, keeps its
-// slice of S^T (32 x 64, fp32) as the accumulator fragments of mma.sync.m16n8k16 for the whole sequence, and the
-// accumulator layout of one product is exactly the A-operand layout of the next, so every hand-over is a register
-// repack.  Only T2 and M pass through shared memory (written by warps 0 and 1, read as B fragments by all).  k and q
-// arrive un-normalised; their L2 norms are the diagonals of the Gram products K K^T and Q Q^T and enter as per-token
-// scalars.  The 16 x 16 triangular inverse is a 16-lane forward substitution in fp32.  Operands are in the mode's
-// 16-bit type (the output type T: bf16 or fp16), the state and all accumulation fp32.
+// k and q arrive un-normalised; their L2 norms are the diagonals of the Gram products K K^T and Q Q^T and enter as
+// per-token scalars.  Operands are in the mode's 16-bit type (the output type T: bf16 or fp16), the state and all
+// accumulation fp32.
 //
-// Schedule of one chunk (two CTA barriers): warps 0 / 1 Gram products, masks, inverse, while warps 1-3 finish the
-// PREVIOUS chunk (its o tile times rstd and the norm weight -> `on`); all warps R and Q S0 | barrier | U, O (times the
-// output gate, into the o tile), state update, each warp's share of sum(o^2) | barrier.
+// gdn_chunk_prep_kernel: the first two lines above (T2, M, the decays and the norms) depend on nothing but the chunk's own
+// tiles, so they are computed for all chunks of the batch at once, a warp per pair of chunks, and stored behind the
+// chunk's tiles (the block's last 1,280 bytes).  The 16 x 16 triangular inverse is a forward substitution in fp32, one
+// column per lane.
+//
+// gdn_scan_t_kernel: one CTA (four warps) owns one (clip, head) and walks its 21 chunk blocks.  A block (q^T, k^T, v^T,
+// gate^T tiles, log decays, betas, and what the preparation added: 13,696 contiguous bytes) arrives by ONE bulk copy into
+// a three-slot ring, two chunks ahead.  Nothing is converted or re-laid-out: every operand fragment of the chunk's
+// products comes straight out of the landed tiles with ldmatrix (transposing where the product wants tokens along the
+// contraction).  Everything is computed transposed (value dimension = MMA rows): warp w owns value columns
+// 32w .. 32w+31, keeps its slice of S^T (32 x 64, fp32) as the accumulator fragments of mma.sync.m16n8k16 for the whole
+// sequence, and the accumulator layout of one product is exactly the A-operand layout of the next, so every hand-over
+// is a register repack; T2 and M are read as B fragments from the block.
+// Schedule of one chunk (one CTA barrier): every warp finishes four tokens of the PREVIOUS chunk (its o tile times rstd
+// and the norm weight -> `on`; o tile and sums of squares are double-buffered), then R and Q S0, U, O (times the output
+// gate, into the o tile), the state update and its share of sum(o^2) | barrier.
 //
 // Token slots past the end of the clip hold zeros in every tile (the producer writes them), which makes them inert:
 // beta = 0, no decay, zero keys and values.  Their output rows are not stored.
 //
-// Warp-level mma.sync rather than tcgen05: per 16-token chunk the products form a dependency chain five deep on tiles of
+// Warp-level mma.sync rather than tcgen05: per 16-token chunk the products form a dependency chain four deep on tiles of
 // 16 tokens; tcgen05 needs M >= 64 rows and an asynchronous issue / commit / tensor-memory round trip per link of that
 // chain, which costs more than the products themselves.  tcgen05 carries the projections (gemm_tc.cu, gdn_inproj.cu).
 //
