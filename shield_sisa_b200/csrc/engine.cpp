@@ -1,11 +1,13 @@
 // Sequence engine core.  Launch order of one classify (B windows, M = 321*B rows), following the reference's
 // run_classify (engine/cuda/engine.cu:406-470) with the memory-bound steps between GEMMs fused.
 //
-// 16-bit modes (21 launches):
+// 16-bit modes (24 launches):
 //   assemble+norm -> h (fp32), xn
 //   3 mixers (GDN-A once, GDN-B twice with the same weights, delta / sqrt(2)):
 //       fused in-projection (W' xn^T on the tensor cores, conv + SiLU + gates in its epilogue) xn -> 16-bit operand tiles PT
-//       | scan (chunked delta rule, gated norm) PT -> on | o-proj GEMM + residual -> h | norm h -> xn
+//       | chunk preparation (per-chunk Gram products, masks, triangular inverse: the part of the chunked delta rule that
+//       does not depend on the state) PT -> PT | scan (the state-dependent part, gated norm) PT -> on
+//       | o-proj GEMM + residual -> h | norm h -> xn
 //   2 FFNs: one kernel (up GEMM, SwiGLU into shared memory, down GEMM, residual) xn -> h | norm -> xn
 //   SISA: all-row GEMM + bias -> K | V | B as fp16 rows, theta | alpha | forget as fp32 rows (both alias PT);
 //       readout row: norm + Q/C projection, attention kernel, then W_O + residual, norm, FFN, head -> logits as one kernel.
@@ -212,7 +214,7 @@ public:
         starve_kind_ = kind;
         starve_batches_ = batches > 0 ? batches : 0;
     }
-    // 16-bit modes: 21 kernels.  Exact tier: 23 (its feed-forward blocks are two GEMMs each) + a launch that splits the
+    // 16-bit modes: 24 kernels.  Exact tier: 23 (its feed-forward blocks are two GEMMs each) + a launch that splits the
     // A operand of the five GEMMs that do not read a normalised row (three o-projections, two FFN down projections)
     int launches_per_classify() const override { return prec_ == Precision::FP32 ? 28 : 24; }
 
