@@ -22,7 +22,6 @@
 namespace sb {
 namespace {
 
-constexpr int NT = 256;
 constexpr int XP = kD + 4, HP = kDFF + 4;     // row pitches (floats) of the shared-memory activation tiles
 
 // acc[c][e] = sum_k X[c][k] * Wt[k][n0 + e], e < NC, for the TB clips of the tile; k ascending, one FMA chain per output.
@@ -34,37 +33,46 @@ __device__ __forceinline__ void dot_columns(const float* __restrict__ X, int xp,
 #pragma unroll
         for (int e = 0; e < NC; ++e) acc[c][e] = 0.0f;
     const float* wp = Wt + n0;
-    // few clips per CTA leave registers for a deeper run of weight loads in flight (the small-batch launch is bound by L2 latency)
-    constexpr int kDepth = TB >= 8 ? 2 : 8;
-#pragma unroll kDepth
-    for (int k = 0; k < K; k += 4) {
-        float w[4][NC];
+    // The weights of D steps of four k are loaded before the first of them is used, so that D x 4 loads are in flight per
+    // thread (with few clips per CTA the kernel is bound by the latency of exactly these loads).  This needs the registers
+    // for them: the kernels are declared with a minimum number of CTAs per SM, because without one the assembler keeps the
+    // register count low for occupancy by moving every load next to its use, which runs the steps one L2 round trip
+    // after the other (B = 512: 0.27 ms for the tail kernel against 0.14 ms).
+    constexpr int D = TB >= 8 ? 4 : 8;
+    static_assert(K % (4 * D) == 0, "the k loop walks whole groups of steps");
+#pragma unroll 1
+    for (int k0 = 0; k0 < K; k0 += 4 * D) {
+        float w[D][4][NC];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if constexpr (NC == 2) {
-                const float2 v = __ldg(reinterpret_cast<const float2*>(wp + (long long)(k + i) * ldw));
-                w[i][0] = v.x; w[i][1] = v.y;
-            } else {
-                w[i][0] = __ldg(wp + (long long)(k + i) * ldw);
+        for (int d = 0; d < D; ++d)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if constexpr (NC == 2) {
+                    const float2 v = __ldg(reinterpret_cast<const float2*>(wp + (long long)(k0 + 4 * d + i) * ldw));
+                    w[d][i][0] = v.x; w[d][i][1] = v.y;
+                } else {
+                    w[d][i][0] = __ldg(wp + (long long)(k0 + 4 * d + i) * ldw);
+                }
             }
-        }
 #pragma unroll
-        for (int c = 0; c < TB; ++c) {
-            const float4 x = *reinterpret_cast<const float4*>(X + c * xp + k);
+        for (int d = 0; d < D; ++d)
 #pragma unroll
-            for (int e = 0; e < NC; ++e) {
-                acc[c][e] = fmaf(x.x, w[0][e], acc[c][e]);
-                acc[c][e] = fmaf(x.y, w[1][e], acc[c][e]);
-                acc[c][e] = fmaf(x.z, w[2][e], acc[c][e]);
-                acc[c][e] = fmaf(x.w, w[3][e], acc[c][e]);
+            for (int c = 0; c < TB; ++c) {
+                const float4 x = *reinterpret_cast<const float4*>(X + c * xp + k0 + 4 * d);
+#pragma unroll
+                for (int e = 0; e < NC; ++e) {
+                    acc[c][e] = fmaf(x.x, w[d][0][e], acc[c][e]);
+                    acc[c][e] = fmaf(x.y, w[d][1][e], acc[c][e]);
+                    acc[c][e] = fmaf(x.z, w[d][2][e], acc[c][e]);
+                    acc[c][e] = fmaf(x.w, w[d][3][e], acc[c][e]);
+                }
             }
-        }
     }
 }
 
 // out[c] = (in[c] * (1 / sqrt(mean(in[c]^2) + 1e-6))) * w over rows of 384 in shared memory; warp w takes clips w, w + 8.
 // A row is read into registers before it is written, so out may be in.
-template <int TB>
+template <int TB, int NT>
 __device__ __forceinline__ void norm_rows(const float* in, float* out, const float* __restrict__ w, int warp, int lane) {
     for (int c = warp; c < TB; c += NT / 32) {
         float v[kD / 32];
@@ -81,8 +89,8 @@ __device__ __forceinline__ void norm_rows(const float* in, float* out, const flo
     }
 }
 
-template <int TB>
-__global__ void __launch_bounds__(NT)
+template <int TB, int NT>
+__global__ void __launch_bounds__(NT, NT <= 256 ? 2 : 1)
 readout_qc_kernel(const float* __restrict__ h_last, long long ldh, const float* __restrict__ norm_w, const float* __restrict__ wqc_t,
                   float* __restrict__ QC, int B) {
     __shared__ __align__(16) float xs[TB * XP];
@@ -93,7 +101,7 @@ readout_qc_kernel(const float* __restrict__ h_last, long long ldh, const float* 
         xs[c * XP + k] = clip0 + c < B ? h_last[(long long)(clip0 + c) * ldh + k] : 0.0f;
     }
     __syncthreads();
-    norm_rows<TB>(xs, xs, norm_w, warp, lane);
+    norm_rows<TB, NT>(xs, xs, norm_w, warp, lane);
     __syncthreads();
     for (int n0 = 2 * tid; n0 < kSQN; n0 += 2 * NT) {          // 576 columns = 288 pairs
         float acc[TB][2];
@@ -116,8 +124,8 @@ struct TailWeights {
     const float *head_b2;       // [1]
 };
 
-template <int TB>
-__global__ void __launch_bounds__(NT)
+template <int TB, int NT>
+__global__ void __launch_bounds__(NT, NT <= 256 ? 2 : 1)
 readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_last, long long ldh, const TailWeights tw,
                     float* __restrict__ x2_out, float* __restrict__ logits, int B) {
     extern __shared__ __align__(16) float tail_smem[];
@@ -145,7 +153,7 @@ readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_las
         }
     }
     __syncthreads();
-    norm_rows<TB>(x1, xa, tw.ffn_norm_w, warp, lane);
+    norm_rows<TB, NT>(x1, xa, tw.ffn_norm_w, warp, lane);
     __syncthreads();
     // hid[j] = silu(gate_j) * up_j: 960 (gate, up) column pairs
     for (int j = tid; j < kDFF; j += NT) {
@@ -168,7 +176,7 @@ readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_las
         }
     }
     __syncthreads();
-    norm_rows<TB>(x1, xa, tw.final_norm_w, warp, lane);
+    norm_rows<TB, NT>(x1, xa, tw.final_norm_w, warp, lane);
     __syncthreads();
     // head: 128 hidden units (one column per thread of the first four warps), then their weighted sum per clip
     float* hh = hid;                         // [TB][128]; the SwiGLU product is consumed
@@ -188,31 +196,39 @@ readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_las
 
 constexpr int tail_smem_bytes(int tb) { return (2 * tb * XP + tb * HP) * int(sizeof(float)); }
 
-// Clips per CTA for a batch of B: 16 once that still gives every SM a CTA, else 4, else 1.
-int clips_per_cta(int B) {
+// Clips and threads per CTA for a batch of B: 16 clips x 256 threads once that still gives every SM a CTA, else 4 x 256;
+// below that every CTA re-reads the 5 MB of weights from L2 for very few clips, and a batch of a few hundred clips (what
+// the job pipeline forms) is bound by exactly that traffic: two clips x 512 threads halve it and keep as many warps per
+// SM.  The arithmetic of an output does not depend on the choice (one FMA chain over k ascending in every form).
+struct ReadoutShape { int tb, nt; };
+ReadoutShape readout_shape(int B) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int tb = B >= 16 * sms ? 16 : B >= 4 * sms ? 4 : 1;
+    ReadoutShape r = B >= 16 * sms ? ReadoutShape{16, 256} : B >= 4 * sms ? ReadoutShape{4, 256} : B >= 2 * sms ? ReadoutShape{2, 512} : ReadoutShape{1, 256};
 #ifdef SHVK_DEV_PROBES
-    if (const char* e = getenv("SHVK_READOUT_TB")) tb = atoi(e);
+    if (const char* e = getenv("SHVK_READOUT_TB")) { r.tb = atoi(e); r.nt = 256; }
+    if (const char* e = getenv("SHVK_READOUT_NT")) r.nt = atoi(e);
 #endif
-    return tb;
+    return r;
 }
 
-template <int TB>
+template <int TB, int NT>
 int launch_qc(const float* h_last, long long ldh, const float* norm_w, const float* wqc_t, float* QC, int B, cudaStream_t s) {
-    readout_qc_kernel<TB><<<unsigned((B + TB - 1) / TB), NT, 0, s>>>(h_last, ldh, norm_w, wqc_t, QC, B);
+    readout_qc_kernel<TB, NT><<<unsigned((B + TB - 1) / TB), NT, 0, s>>>(h_last, ldh, norm_w, wqc_t, QC, B);
     return int(cudaGetLastError());
 }
-template <int TB>
+template <int TB, int NT>
 int launch_tail(const float* Y, const float* h_last, long long ldh, const TailWeights& tw, float* x2_out, float* logits, int B,
                 cudaStream_t s) {
-    const cudaError_t e = cudaFuncSetAttribute(readout_tail_kernel<TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, tail_smem_bytes(TB));
+    const cudaError_t e = cudaFuncSetAttribute(readout_tail_kernel<TB, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, tail_smem_bytes(TB));
     if (e != cudaSuccess) return int(e);
-    readout_tail_kernel<TB><<<unsigned((B + TB - 1) / TB), NT, tail_smem_bytes(TB), s>>>(Y, h_last, ldh, tw, x2_out, logits, B);
+    readout_tail_kernel<TB, NT><<<unsigned((B + TB - 1) / TB), NT, tail_smem_bytes(TB), s>>>(Y, h_last, ldh, tw, x2_out, logits, B);
     return int(cudaGetLastError());
 }
+
+// the shapes that are compiled: clips per CTA * 10000 + threads
+#define SHVK_READOUT_SHAPES(X) X(16, 256) X(8, 256) X(4, 256) X(2, 256) X(1, 256) X(2, 512) X(4, 512) X(4, 1024)
 
 }  // namespace
 }  // namespace sb
@@ -222,12 +238,12 @@ extern "C" int shvk_readout_qc(const float* h_last, long long ldh, const float* 
     if (B <= 0) return 0;
     if (!h_last || !norm_w || !wqc_t || !QC) return int(cudaErrorInvalidValue);
     cudaStream_t s = cudaStream_t(stream);
-    switch (sb::clips_per_cta(B)) {
-        case 16: return sb::launch_qc<16>(h_last, ldh, norm_w, wqc_t, QC, B, s);
-        case 8: return sb::launch_qc<8>(h_last, ldh, norm_w, wqc_t, QC, B, s);
-        case 4: return sb::launch_qc<4>(h_last, ldh, norm_w, wqc_t, QC, B, s);
-        case 2: return sb::launch_qc<2>(h_last, ldh, norm_w, wqc_t, QC, B, s);
-        default: return sb::launch_qc<1>(h_last, ldh, norm_w, wqc_t, QC, B, s);
+    const sb::ReadoutShape sh = sb::readout_shape(B);
+    switch (sh.tb * 10000 + sh.nt) {
+#define X(TB, NT) case TB * 10000 + NT: return sb::launch_qc<TB, NT>(h_last, ldh, norm_w, wqc_t, QC, B, s);
+        SHVK_READOUT_SHAPES(X)
+#undef X
+        default: return int(cudaErrorInvalidValue);
     }
 }
 
@@ -237,11 +253,11 @@ extern "C" int shvk_readout_tail(const float* Y, const float* h_last, long long 
     if (!Y || !h_last || !w || !logits) return int(cudaErrorInvalidValue);
     const sb::TailWeights tw{w->wo_t, w->ffn_norm_w, w->up_t, w->down_t, w->final_norm_w, w->head_w0_t, w->head_b0, w->head_w2, w->head_b2};
     cudaStream_t s = cudaStream_t(stream);
-    switch (sb::clips_per_cta(B)) {
-        case 16: return sb::launch_tail<16>(Y, h_last, ldh, tw, x2_out, logits, B, s);
-        case 8: return sb::launch_tail<8>(Y, h_last, ldh, tw, x2_out, logits, B, s);
-        case 4: return sb::launch_tail<4>(Y, h_last, ldh, tw, x2_out, logits, B, s);
-        case 2: return sb::launch_tail<2>(Y, h_last, ldh, tw, x2_out, logits, B, s);
-        default: return sb::launch_tail<1>(Y, h_last, ldh, tw, x2_out, logits, B, s);
+    const sb::ReadoutShape sh = sb::readout_shape(B);
+    switch (sh.tb * 10000 + sh.nt) {
+#define X(TB, NT) case TB * 10000 + NT: return sb::launch_tail<TB, NT>(Y, h_last, ldh, tw, x2_out, logits, B, s);
+        SHVK_READOUT_SHAPES(X)
+#undef X
+        default: return int(cudaErrorInvalidValue);
     }
 }

@@ -834,19 +834,19 @@ def test_readout_row_kernels_match_oracle(L, weight_files):
     ok(L.shvk_readout_tail(Y1.data_ptr(), H1.data_ptr() + 320 * 384 * 4, 321 * 384, C.byref(rw), None, one.data_ptr(), 1, stream_ptr()))
     sync()
     assert torch.equal(one[0], logits[20])
-    # the clips-per-CTA variants (16 for large batches, 4, 1): the same clips give the same bits in each
+    # the clips-per-CTA variants (16 for large batches, 4, 2 with 512 threads, 1): the same clips give the same bits in each
     Bbig = 2400
     hb = rng.standard_normal((Bbig, 384)).astype(np.float32)
     yb = (rng.standard_normal((Bbig, 384)) * 0.5).astype(np.float32)
     Hb, Yb = dev(hb), dev(yb)
     outs = {}
-    for n in (Bbig, 640, 37):
+    for n in (Bbig, 640, 400, 37):
         lg, q = torch.zeros(n, device="cuda"), torch.zeros((n, 576), device="cuda")
         ok(L.shvk_readout_qc(Hb.data_ptr(), 384, d_nw.data_ptr(), d_wqc.data_ptr(), q.data_ptr(), n, stream_ptr()))
         ok(L.shvk_readout_tail(Yb.data_ptr(), Hb.data_ptr(), 384, C.byref(rw), None, lg.data_ptr(), n, stream_ptr()))
         sync()
         outs[n] = (lg.cpu().numpy(), q.cpu().numpy())
-    for n in (640, 37):
+    for n in (640, 400, 37):
         np.testing.assert_array_equal(outs[n][0].view(np.uint32), outs[Bbig][0][:n].view(np.uint32))
         np.testing.assert_array_equal(outs[n][1].view(np.uint32), outs[Bbig][1][:n].view(np.uint32))
     x1 = hb.astype(np.float64) + yb.astype(np.float64) @ f64(f"{a}.W_O.weight").T
