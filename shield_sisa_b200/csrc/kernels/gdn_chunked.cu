@@ -74,8 +74,10 @@ template <int ROWB> __device__ __forceinline__ uint32_t tile_off(int row, int ch
 }
 
 // ---------------------------------------------------------------------------------------------------- prep kernel
+// (declared with a minimum of CTAs per SM: without one the assembler keeps the kernel at 40-48 registers by moving loads
+// next to their uses)
 template <int DK>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 gdn_chunked_prep_kernel(const __nv_bfloat16* __restrict__ Q, const __nv_bfloat16* __restrict__ K, const float* __restrict__ G,
                         const float* __restrict__ Beta, uint8_t* __restrict__ ws, int T, int H, int NB, long long blocks,
                         float scale) {

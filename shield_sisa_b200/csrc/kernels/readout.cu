@@ -196,16 +196,16 @@ readout_tail_kernel(const float* __restrict__ Y, const float* __restrict__ h_las
 
 constexpr int tail_smem_bytes(int tb) { return (2 * tb * XP + tb * HP) * int(sizeof(float)); }
 
-// Clips and threads per CTA for a batch of B: 16 clips x 256 threads once that still gives every SM a CTA, else 4 x 256;
-// below that every CTA re-reads the 5 MB of weights from L2 for very few clips, and a batch of a few hundred clips (what
-// the job pipeline forms) is bound by exactly that traffic: two clips x 512 threads halve it and keep as many warps per
-// SM.  The arithmetic of an output does not depend on the choice (one FMA chain over k ascending in every form).
+// Clips and threads per CTA for a batch of B: 16 clips once that still gives every SM a CTA, else 4, 2 (the few hundred
+// clips of a pipeline batch: at B = 512 two clips per CTA 0.087 ms for the tail kernel, one 0.144, four 0.108; two or four
+// clips with 512 threads 0.121 / 0.089, four with 1024 0.122), else 1.  The arithmetic of an output does not depend on
+// the choice (one FMA chain over k ascending in every form).
 struct ReadoutShape { int tb, nt; };
 ReadoutShape readout_shape(int B) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    ReadoutShape r = B >= 16 * sms ? ReadoutShape{16, 256} : B >= 4 * sms ? ReadoutShape{4, 256} : B >= 2 * sms ? ReadoutShape{2, 512} : ReadoutShape{1, 256};
+    ReadoutShape r = B >= 16 * sms ? ReadoutShape{16, 256} : B >= 4 * sms ? ReadoutShape{4, 256} : B >= 2 * sms ? ReadoutShape{2, 256} : ReadoutShape{1, 256};
 #ifdef SHVK_DEV_PROBES
     if (const char* e = getenv("SHVK_READOUT_TB")) { r.tb = atoi(e); r.nt = 256; }
     if (const char* e = getenv("SHVK_READOUT_NT")) r.nt = atoi(e);
@@ -228,7 +228,7 @@ int launch_tail(const float* Y, const float* h_last, long long ldh, const TailWe
 }
 
 // the shapes that are compiled: clips per CTA * 10000 + threads
-#define SHVK_READOUT_SHAPES(X) X(16, 256) X(8, 256) X(4, 256) X(2, 256) X(1, 256) X(2, 512) X(4, 512) X(4, 1024)
+#define SHVK_READOUT_SHAPES(X) X(16, 256) X(8, 256) X(4, 256) X(2, 256) X(1, 256)
 
 }  // namespace
 }  // namespace sb

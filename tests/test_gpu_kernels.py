@@ -834,7 +834,7 @@ def test_readout_row_kernels_match_oracle(L, weight_files):
     ok(L.shvk_readout_tail(Y1.data_ptr(), H1.data_ptr() + 320 * 384 * 4, 321 * 384, C.byref(rw), None, one.data_ptr(), 1, stream_ptr()))
     sync()
     assert torch.equal(one[0], logits[20])
-    # the clips-per-CTA variants (16 for large batches, 4, 2 with 512 threads, 1): the same clips give the same bits in each
+    # the clips-per-CTA variants (16 for large batches, 4, 2, 1): the same clips give the same bits in each
     Bbig = 2400
     hb = rng.standard_normal((Bbig, 384)).astype(np.float32)
     yb = (rng.standard_normal((Bbig, 384)) * 0.5).astype(np.float32)
