@@ -100,6 +100,14 @@ def algorithmic_work(name: str, storage_bytes: int):
     return table.get(name, (0, 0))
 
 
+# launches of one classify step in the 16-bit modes, by the names the engine's profile gives them; the readout row's two
+# kernels move B rows, not 321 B: the model has 124,416 bytes per clip for them
+STEP_LAUNCHES_16BIT = {"assemble_norm": 1, "gdn_inproj": 3, "gdn_prep": 3, "gdn_scan": 3, "gemm.o_proj": 3, "rmsnorm": 5,
+                       "ffn_fused": 2, "gemm.sisa_in": 1, "sisa_attn": 1, "readout.qc": 1, "readout.tail": 1}
+MODEL_READOUT_BYTES = 124416
+MODEL_BYTES_16BIT = 37471872
+
+
 def boundary_model_bytes(name: str, storage_bytes: int):
     """HBM bytes per clip of kernel `name` in the fixed GEMM-boundary model the whole-stack figure (37,471,872 B per clip
     in the 16-bit modes) is built from: each GEMM its own kernel writing an fp32 projection row P [321, 2316] per token,
@@ -110,6 +118,7 @@ def boundary_model_bytes(name: str, storage_bytes: int):
     p_out = NTOK * 2316 * 4
     s_row = NTOK * 1068 * 4                   # the model's fp32 SISA projection row
     rows = {"gdn_inproj": NTOK * D * s + p_out, "gdn_scan": p_out + NTOK * 768 * s,
+            "gdn_prep": 0,                        # not a kernel of the model: its work is part of the scan's row
             "gemm.sisa_in": NTOK * D * s + s_row, "sisa_attn": s_row,
             "ffn_fused": NTOK * D * s + 2 * NTOK * 960 * s + 2 * NTOK * D * 4}    # up (xn, hid) + down (hid, h read and written)
     return rows.get(name, algorithmic_work(name, storage_bytes)[0])
@@ -735,7 +744,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "gdn_scan_t": {f"warp_{w}": shares(b_sc, w, [(0, "until_block_landed"), (1, "deferred_norm"), (2, "r_and_qs"), (3, "u_and_o"),
                                                          (4, "state_update"), (5, "sum_of_squares"), (6, "barrier")]) for w in range(4)}}
         print(json.dumps(dev_cycles, indent=1), file=sys.stderr)
-    alg_bytes_clip = 45853824 if mode == "fp32" else 37471872
+    alg_bytes_clip = 45853824 if mode == "fp32" else MODEL_BYTES_16BIT
     stack_frac = B * alg_bytes_clip / (ms_step / 1000.0) / (pk["hbm_gbs"] * 1e9)
     launches = eng.launches() * args.steps * world
     eng.close()
