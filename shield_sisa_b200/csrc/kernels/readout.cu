@@ -6,9 +6,10 @@
 //                 z = rmsnorm(x2) * w;  logit = w2 . silu(W0 z + b0) + b2                           (after sisa_attn)
 //
 // Only row 320 leaves the SISA block, so this work is B rows, not 321 B (engine/cuda/engine.cu:451-469;
-// engine/model/isa_impl.hpp:1092-1133).  A CTA takes TB clips (16 when the batch is large enough to give every SM a CTA that way, else 4 or 1) and walks the small matrix products one after the
-// other with all activations of its clips in shared memory: a thread owns one or two output columns for all 16 clips
-// (16 or 32 accumulators), reads its weights coalesced from a [K][N] (transposed) copy that stays in L2, and the
+// engine/model/isa_impl.hpp:1092-1133).  A CTA takes TB clips (16 when the batch is large enough to give every SM a
+// CTA that way, else 4, 2 or 1) and walks the small matrix products one after the other with all activations of its
+// clips in shared memory: a thread owns one or two output columns for all TB clips (TB or 2 TB accumulators), reads its
+// weights coalesced from a [K][N] (transposed) copy that stays in L2, several steps of k in flight at a time, and the
 // activations as 128-bit broadcast loads.  Every output is one fp32 FMA chain over k in ascending order, whatever the
 // batch and whatever TB, so a clip's logit does not depend on its neighbours (engine/include/shv_cuda.h:31-34).
 //
